@@ -1,0 +1,147 @@
+/* otter_b200 — C-ABI of the B200 (sm_100a) int8 convolution path for Otter/Tensor.
+ *
+ * This is the whole boundary between host code (the C++17 Net / Layer / ConvolutionLayer mirror in
+ * tensor_b200/host, a test, a benchmark, or the reference itself through a thin stub) and the CUDA
+ * kernels. Plain pointers and sizes only. Every function returns an int status: 0 = success
+ * (the reference's convention, Tensor/Layer.hpp:44), negative = failure; nothing throws or aborts.
+ * There is no CPU path behind any entry point: without a CUDA device every compute call fails.
+ *
+ * Layouts
+ *   OTT_F32_NCHW  fp32, the reference's boundary layout (Tensor/TensorPacking.cpp:126-139 elempack 1).
+ *   OTT_S8_NHWC   int8, channels innermost, channel stride padded to ott_nhwc_channels(c)
+ *                 (a multiple of 16 so a pixel row can be a TMA box row). Padding channels hold 0.
+ *                 This replaces the reference's int8 elempack-8 blobs (Byte8) that flow between a
+ *                 requantizing convolution and its consumer (Tensor/ConvolutionLayer.cpp:770-775).
+ *   OTT_S32_NHWC  the exact s32 accumulators, same padding rule; for tests of the integer part alone.
+ */
+#ifndef OTTER_B200_H
+#define OTTER_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default) /* the library is built with -fvisibility=hidden; these are its exports */
+#endif
+
+#define OTT_OK 0
+#define OTT_ERR_UNSUPPORTED (-1) /* Layer.cpp:50-59 uses -1 for "not implemented" */
+#define OTT_ERR_INVALID (-2)     /* bad argument */
+#define OTT_ERR_CUDA (-3)        /* a CUDA runtime/driver call failed; see ott_last_error */
+#define OTT_ERR_DEVICE_WAIT (-4) /* a kernel gave up a bounded wait and reported it in its status word */
+#define OTT_ERR_ALLOC (-100)     /* Layer.cpp:50-59 uses -100 for allocation failure */
+
+typedef struct ott_ctx ott_ctx;   /* one per GPU: device, stream, caching allocator */
+typedef struct ott_conv ott_conv; /* one quantized ConvolutionLayer's device-side state */
+typedef struct ott_event ott_event;
+
+enum ott_dtype { OTT_F32_NCHW = 0, OTT_S8_NHWC = 1, OTT_S32_NHWC = 2 };
+
+/* int8 rounding rule of the epilogue and of the fused quantization.
+ * OTT_ROUND_ADD_HALF_TRUNC = float2int8_sse (Tensor/VecIntrinsic.hpp:71-161), the reference's default
+ * packed path; OTT_ROUND_HALF_AWAY = scalar float2int8 (Tensor/QuantizeX86.cpp:18-23) of its unpacked
+ * path and aarch64 (Tensor/QuantizeNeon.hpp:27-29). */
+enum ott_rounding { OTT_ROUND_ADD_HALF_TRUNC = 0, OTT_ROUND_HALF_AWAY = 1 };
+
+/* Which kernel family serves a layer; chosen at create time from the shape, reported for tests. */
+enum ott_kernel_kind {
+    OTT_KERNEL_DEPTHWISE = 1,   /* CUDA-core depthwise */
+    OTT_KERNEL_DENSE_UMMA = 2,  /* tcgen05 implicit GEMM */
+    OTT_KERNEL_DENSE_DIRECT = 3 /* CUDA-core direct convolution (few input channels, strided/dilated dense) */
+};
+
+/* The options of a quantized ConvolutionLayer (Tensor/ConvolutionLayer.hpp:41-62, option keys parsed at
+ * Tensor/ConvolutionLayer.cpp:58-156). act_type: 0 none, 1 ReLU, 2 LeakyReLU(act_param0), 3 ReLU6.
+ * int8_scale_term 1/2: fp32 output; 101/102: int8 output (ConvolutionLayer.cpp:834-844). */
+typedef struct {
+    int cin, cout, kh, kw, sh, sw, ph, pw, dh, dw, groups;
+    int bias_term;
+    int int8_scale_term;
+    int act_type;
+    float act_param0;
+    int rounding; /* enum ott_rounding */
+} ott_conv_desc;
+
+/* ---- device context: replaces otter::GetAllocator(Device) + the implicit single CPU "stream"
+ *      (Tensor/Allocator.hpp:125-144, Tensor/CPUCachingAllocator.hpp:18-72) ---- */
+int ott_cuda_device_count(int* n);
+int ott_ctx_create(int device, ott_ctx** out);
+int ott_ctx_destroy(ott_ctx* ctx);
+const char* ott_last_error(const ott_ctx* ctx); /* never NULL; valid until the next failing call on ctx */
+void* ott_ctx_stream(ott_ctx* ctx);             /* the cudaStream_t every call on ctx is ordered on */
+int ott_sync(ott_ctx* ctx);
+
+/* Stream-ordered, size-keyed caching allocator: a freed block is handed back to the next request of the
+ * same rounded size without touching cudaMalloc (the policy of CPUCachingAllocator::allocate/free,
+ * Tensor/CPUCachingAllocator.hpp:62-70, moved to device memory). */
+int ott_malloc(ott_ctx* ctx, size_t bytes, void** out);
+int ott_free(ott_ctx* ctx, void* p);
+int ott_alloc_stats(ott_ctx* ctx, uint64_t* n_device_mallocs, uint64_t* n_cache_hits, uint64_t* bytes_in_use,
+                    uint64_t* bytes_cached);
+int ott_alloc_release_cached(ott_ctx* ctx); /* CPUCachingAllocator::free_cached */
+int ott_host_alloc(size_t bytes, void** out); /* pinned host staging memory */
+int ott_host_free(void* p);
+int ott_memcpy_h2d(ott_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes); /* async on the stream */
+int ott_memcpy_d2h(ott_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes); /* async on the stream */
+int ott_memset(ott_ctx* ctx, void* dst_dev, int value, size_t bytes);
+
+/* CUDA events on the context's stream, for timing the kernels where they are launched. */
+int ott_event_create(ott_ctx* ctx, ott_event** out);
+int ott_event_record(ott_ctx* ctx, ott_event* ev);
+int ott_event_elapsed_ms(ott_event* start, ott_event* stop, float* ms); /* synchronizes on stop */
+int ott_event_destroy(ott_event* ev);
+
+/* channel stride (in elements) of the NHWC layouts for c logical channels */
+int ott_nhwc_channels(int c);
+
+/* ---- quantize: otter::quantize_to_int8 (Tensor/Quantize.cpp:52-58 -> Tensor/QuantizeX86.cpp:47-644)
+ *      fp32 NCHW -> int8 NHWC, scale per tensor (n_scales==1) or per channel; scales on the HOST. ---- */
+int ott_quantize_f32_nchw_to_s8_nhwc(ott_ctx* ctx, const float* x_dev, int n, int c, int h, int w,
+                                     const float* scales_host, int n_scales, int rounding, int8_t* out_dev);
+
+/* ---- the layer: ConvolutionLayer::create_pipeline_int8 / forward_int8
+ *      (Tensor/ConvolutionLayer.cpp:666-752, :754-847) ---- */
+
+/* All array arguments are HOST pointers, in the reference's own field layouts:
+ *   w_oihw      weight_data, int8 [cout][cin/groups][kh][kw]
+ *   bias        bias_data [cout] or NULL when bias_term == 0
+ *   w_scales    weight_data_int8_scales [cout]
+ *   in_scales   bottom_blob_int8_scales, n_in_scales = 1 (dense) or groups (depthwise)
+ *   out_scales  top_blob_int8_scales, n_out_scales = 1 or cout; ignored when int8_scale_term < 100
+ * Computes scale_in = 1/(in_scales[0]*w_scales[p]) (0 where w_scales[p]==0) in fp32 on the host exactly as
+ * ConvolutionLayer.cpp:667-679, re-lays the weights for the chosen kernel and uploads everything once. */
+int ott_conv_int8_create(ott_ctx* ctx, const ott_conv_desc* desc, const int8_t* w_oihw, const float* bias,
+                         const float* w_scales, const float* in_scales, int n_in_scales,
+                         const float* out_scales, int n_out_scales, ott_conv** out);
+int ott_conv_int8_destroy(ott_ctx* ctx, ott_conv* conv);
+int ott_conv_int8_kernel_kind(const ott_conv* conv); /* enum ott_kernel_kind */
+int ott_conv_int8_out_shape(const ott_conv* conv, int h, int w, int* oh, int* ow);
+
+/* One forward on DEVICE buffers, asynchronous on the context's stream.
+ *   in_dtype  OTT_F32_NCHW (quantized on the way in, as ConvolutionLayer.cpp:770-775) or OTT_S8_NHWC
+ *   out_dtype OTT_F32_NCHW (int8_scale_term < 100), OTT_S8_NHWC (int8_scale_term > 100), or OTT_S32_NHWC
+ *             (accumulators before the epilogue, any int8_scale_term)
+ * A batch of n images gives, per image, exactly what the reference gives for that image alone (its int8
+ * kernels are batch-1: Tensor/ConvolutionMM2DInt8X86Pack.cpp:159, Tensor/Padding.cpp:27-29).
+ * status_word_dev: optional device uint32 the kernels OR an error code into if a bounded wait gives up. */
+int ott_conv_int8_forward(ott_ctx* ctx, const ott_conv* conv, const void* in_dev, int in_dtype, int n, int h, int w,
+                          void* out_dev, int out_dtype, uint32_t* status_word_dev);
+
+/* The same forward on HOST buffers: copies the input to the device, runs, copies the output back and
+ * waits for it. This is the call a host-tensor Layer::forward maps to (Tensor/Net.cpp:442). */
+int ott_conv_int8_forward_host(ott_ctx* ctx, const ott_conv* conv, const void* in_host, int in_dtype, int n, int h,
+                               int w, void* out_host, int out_dtype);
+
+/* number of kernels this library launched on ctx since creation (for benchmark bookkeeping) */
+uint64_t ott_launch_count(const ott_ctx* ctx);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* OTTER_B200_H */

@@ -1,0 +1,227 @@
+"""ctypes binding of include/otter_b200.h (one Python function per exported symbol, plus two small
+convenience classes used by the tests and the benchmark)."""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+import numpy as np
+
+F32_NCHW, S8_NHWC, S32_NHWC = 0, 1, 2
+ROUND_ADD_HALF_TRUNC, ROUND_HALF_AWAY = 0, 1
+ACT_NONE, ACT_RELU, ACT_LRELU, ACT_RELU6 = 0, 1, 2, 3
+KERNEL_DEPTHWISE, KERNEL_DENSE_UMMA, KERNEL_DENSE_DIRECT = 1, 2, 3
+
+_LIB_PATH = Path(__file__).resolve().parent / "lib" / "libotter_b200.so"
+
+
+class OtterB200Error(RuntimeError):
+    def __init__(self, code: int, what: str):
+        super().__init__(f"otter_b200 error {code}: {what}")
+        self.code = code
+
+
+class OttConvDesc(C.Structure):
+    _fields_ = [(k, C.c_int) for k in ("cin", "cout", "kh", "kw", "sh", "sw", "ph", "pw", "dh", "dw", "groups", "bias_term",
+                                       "int8_scale_term", "act_type")] + [("act_param0", C.c_float), ("rounding", C.c_int)]
+
+
+# name -> (restype, argtypes); the single list of what include/otter_b200.h declares
+vp, i32, u64p, sz = C.c_void_p, C.c_int, C.POINTER(C.c_uint64), C.c_size_t
+SIGNATURES = {
+    "ott_cuda_device_count": (i32, [C.POINTER(i32)]),
+    "ott_ctx_create": (i32, [i32, C.POINTER(vp)]),
+    "ott_ctx_destroy": (i32, [vp]),
+    "ott_last_error": (C.c_char_p, [vp]),
+    "ott_ctx_stream": (vp, [vp]),
+    "ott_sync": (i32, [vp]),
+    "ott_malloc": (i32, [vp, sz, C.POINTER(vp)]),
+    "ott_free": (i32, [vp, vp]),
+    "ott_alloc_stats": (i32, [vp, u64p, u64p, u64p, u64p]),
+    "ott_alloc_release_cached": (i32, [vp]),
+    "ott_host_alloc": (i32, [sz, C.POINTER(vp)]),
+    "ott_host_free": (i32, [vp]),
+    "ott_memcpy_h2d": (i32, [vp, vp, vp, sz]),
+    "ott_memcpy_d2h": (i32, [vp, vp, vp, sz]),
+    "ott_memset": (i32, [vp, vp, i32, sz]),
+    "ott_event_create": (i32, [vp, C.POINTER(vp)]),
+    "ott_event_record": (i32, [vp, vp]),
+    "ott_event_elapsed_ms": (i32, [vp, vp, C.POINTER(C.c_float)]),
+    "ott_event_destroy": (i32, [vp]),
+    "ott_nhwc_channels": (i32, [i32]),
+    "ott_quantize_f32_nchw_to_s8_nhwc": (i32, [vp, vp, i32, i32, i32, i32, vp, i32, i32, vp]),
+    "ott_conv_int8_create": (i32, [vp, C.POINTER(OttConvDesc), vp, vp, vp, vp, i32, vp, i32, C.POINTER(vp)]),
+    "ott_conv_int8_destroy": (i32, [vp, vp]),
+    "ott_conv_int8_kernel_kind": (i32, [vp]),
+    "ott_conv_int8_out_shape": (i32, [vp, i32, i32, C.POINTER(i32), C.POINTER(i32)]),
+    "ott_conv_int8_forward": (i32, [vp, vp, vp, i32, i32, i32, i32, vp, i32, vp]),
+    "ott_conv_int8_forward_host": (i32, [vp, vp, vp, i32, i32, i32, i32, vp, i32]),
+    "ott_launch_count": (C.c_uint64, [vp]),
+}
+
+_lib = None
+
+
+def library_path() -> Path:
+    return _LIB_PATH
+
+
+def library():
+    """Load the native library. Raises if it has not been built: there is nothing to fall back to."""
+    global _lib
+    if _lib is None:
+        if not _LIB_PATH.exists():
+            raise OtterB200Error(-1, f"{_LIB_PATH} is missing; build it with `python -m tensor_b200.build`")
+        lib = C.CDLL(str(_LIB_PATH))
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)  # AttributeError if the library does not export a declared symbol
+            fn.restype, fn.argtypes = res, args
+        _lib = lib
+    return _lib
+
+
+def nhwc_channels(c: int) -> int:
+    return (c + 15) & ~15
+
+
+def _np_ptr(a):
+    return None if a is None else a.ctypes.data_as(C.c_void_p)
+
+
+class Context:
+    """One GPU: stream + caching allocator (ott_ctx)."""
+
+    def __init__(self, device: int = 0):
+        self.lib = library()
+        h = C.c_void_p()
+        rc = self.lib.ott_ctx_create(device, C.byref(h))
+        if rc != 0:
+            raise OtterB200Error(rc, f"ott_ctx_create(device={device}) failed (no sm_100 GPU?)")
+        self.h = h
+        self.device = device
+
+    def check(self, rc: int):
+        if rc != 0:
+            raise OtterB200Error(rc, self.lib.ott_last_error(self.h).decode(errors="replace"))
+
+    def close(self):
+        if self.h:
+            self.lib.ott_ctx_destroy(self.h)
+            self.h = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+    def malloc(self, nbytes: int) -> int:
+        p = C.c_void_p()
+        self.check(self.lib.ott_malloc(self.h, nbytes, C.byref(p)))
+        return p.value
+
+    def free(self, p: int):
+        self.check(self.lib.ott_free(self.h, C.c_void_p(p)))
+
+    def to_device(self, a: np.ndarray) -> int:
+        a = np.ascontiguousarray(a)
+        p = self.malloc(max(a.nbytes, 1))
+        self.check(self.lib.ott_memcpy_h2d(self.h, C.c_void_p(p), _np_ptr(a), a.nbytes))
+        self.sync()  # the source is pageable numpy memory
+        return p
+
+    def to_host(self, p: int, shape, dtype) -> np.ndarray:
+        out = np.empty(shape, dtype=dtype)
+        self.check(self.lib.ott_memcpy_d2h(self.h, _np_ptr(out), C.c_void_p(p), out.nbytes))
+        self.sync()
+        return out
+
+    def memset(self, p: int, value: int, nbytes: int):
+        self.check(self.lib.ott_memset(self.h, C.c_void_p(p), value, nbytes))
+
+    def sync(self):
+        self.check(self.lib.ott_sync(self.h))
+
+    def alloc_stats(self):
+        v = [C.c_uint64() for _ in range(4)]
+        self.check(self.lib.ott_alloc_stats(self.h, *[C.byref(x) for x in v]))
+        return {"device_mallocs": v[0].value, "cache_hits": v[1].value, "bytes_in_use": v[2].value, "bytes_cached": v[3].value}
+
+    def launch_count(self) -> int:
+        return int(self.lib.ott_launch_count(self.h))
+
+    def event(self):
+        e = C.c_void_p()
+        self.check(self.lib.ott_event_create(self.h, C.byref(e)))
+        return e
+
+    def record(self, e):
+        self.check(self.lib.ott_event_record(self.h, e))
+
+    def elapsed_ms(self, a, b) -> float:
+        ms = C.c_float()
+        self.check(self.lib.ott_event_elapsed_ms(a, b, C.byref(ms)))
+        return float(ms.value)
+
+    def quantize(self, x_dev: int, n, c, h, w, scales: np.ndarray, rounding: int, out_dev: int):
+        scales = np.ascontiguousarray(scales, dtype=np.float32)
+        self.check(self.lib.ott_quantize_f32_nchw_to_s8_nhwc(self.h, C.c_void_p(x_dev), n, c, h, w, _np_ptr(scales), scales.size,
+                                                              rounding, C.c_void_p(out_dev)))
+
+
+class ConvInt8:
+    """A quantized ConvolutionLayer on the GPU (ott_conv). Array arguments are host numpy arrays in the
+    reference's field layouts (weight OIHW int8, bias/scales fp32)."""
+
+    def __init__(self, ctx: Context, *, cin, cout, kh, kw, sh=1, sw=1, ph=0, pw=0, dh=1, dw=1, groups=1, bias_term=1,
+                 int8_scale_term=2, act_type=0, act_param0=0.0, rounding=0, weight, bias, w_scales, in_scales, out_scales=None):
+        self.ctx = ctx
+        self.desc = OttConvDesc(cin, cout, kh, kw, sh, sw, ph, pw, dh, dw, groups, bias_term, int8_scale_term, act_type,
+                                act_param0, rounding)
+        weight = np.ascontiguousarray(weight, dtype=np.int8)
+        bias = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+        w_scales = np.ascontiguousarray(w_scales, dtype=np.float32)
+        in_scales = np.ascontiguousarray(in_scales, dtype=np.float32)
+        out_scales = None if out_scales is None else np.ascontiguousarray(out_scales, dtype=np.float32)
+        h = C.c_void_p()
+        ctx.check(ctx.lib.ott_conv_int8_create(ctx.h, C.byref(self.desc), _np_ptr(weight), _np_ptr(bias), _np_ptr(w_scales),
+                                               _np_ptr(in_scales), in_scales.size, _np_ptr(out_scales),
+                                               0 if out_scales is None else out_scales.size, C.byref(h)))
+        self.h = h
+
+    @property
+    def kernel_kind(self) -> int:
+        return self.ctx.lib.ott_conv_int8_kernel_kind(self.h)
+
+    def out_hw(self, h, w):
+        oh, ow = C.c_int(), C.c_int()
+        self.ctx.check(self.ctx.lib.ott_conv_int8_out_shape(self.h, h, w, C.byref(oh), C.byref(ow)))
+        return oh.value, ow.value
+
+    def forward(self, in_dev: int, in_dtype: int, n, h, w, out_dev: int, out_dtype: int, status_dev=None):
+        self.ctx.check(self.ctx.lib.ott_conv_int8_forward(self.ctx.h, self.h, C.c_void_p(in_dev), in_dtype, n, h, w,
+                                                          C.c_void_p(out_dev), out_dtype, C.c_void_p(status_dev) if status_dev else None))
+
+    def out_array(self, n, h, w, out_dtype):
+        oh, ow = self.out_hw(h, w)
+        cout = self.desc.cout
+        if out_dtype == F32_NCHW:
+            return np.empty((n, cout, oh, ow), np.float32)
+        if out_dtype == S8_NHWC:
+            return np.empty((n, oh, ow, nhwc_channels(cout)), np.int8)
+        return np.empty((n, oh, ow, nhwc_channels(cout)), np.int32)
+
+    def forward_host(self, x: np.ndarray, in_dtype: int, out_dtype: int) -> np.ndarray:
+        x = np.ascontiguousarray(x)
+        if in_dtype == F32_NCHW:
+            n, _, h, w = x.shape
+        else:
+            n, h, w, _ = x.shape
+        out = self.out_array(n, h, w, out_dtype)
+        self.ctx.check(self.ctx.lib.ott_conv_int8_forward_host(self.ctx.h, self.h, _np_ptr(x), in_dtype, n, h, w, _np_ptr(out), out_dtype))
+        return out
+
+    def close(self):
+        if self.h:
+            self.ctx.lib.ott_conv_int8_destroy(self.ctx.h, self.h)
+            self.h = None

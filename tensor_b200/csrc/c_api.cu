@@ -1,0 +1,427 @@
+// The C-ABI of the library (include/otter_b200.h): device context, caching allocator, and the quantized
+// ConvolutionLayer's create_pipeline_int8 / forward_int8 (Tensor/ConvolutionLayer.cpp:666-752, :754-847)
+// mapped onto the CUDA kernels. No CPU compute path exists here: every forward launches kernels.
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "ctx.h"
+#include "dense_umma.h"
+#include "kernels.h"
+
+using namespace ottk;
+
+struct ott_conv {
+    ott_conv_desc d{};
+    int kind = 0;
+    bool depthwise = false;
+    int cin_pad = 0, cout_pad = 0;
+    int n_in_scales = 0;
+    // device state, owned (allocated from the context's allocator)
+    int8_t* w_dev = nullptr;
+    float* scale_in_dev = nullptr;
+    float* bias_dev = nullptr;
+    float* scale_out_dev = nullptr;
+    float* in_scales_dev = nullptr;
+    UmmaPlan plan{};
+    alignas(128) unsigned char weight_map[128];
+};
+
+namespace {
+
+int out_dim(int in, int k, int s, int p, int d) { return (in + 2 * p - d * (k - 1) - 1) / s + 1; }
+
+int upload(ott_ctx* ctx, const void* host, size_t bytes, void** dev) {
+    cudaError_t e = ctx->alloc->allocate(bytes, dev);
+    if (e != cudaSuccess) return ctx->fail(OTT_ERR_ALLOC, "device allocation of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
+    OTT_CUDA_CHECK(ctx, cudaMemcpyAsync(*dev, host, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    return OTT_OK;
+}
+
+int check_status_word(ott_ctx* ctx) {
+    OTT_CUDA_CHECK(ctx, cudaMemcpyAsync(ctx->status_host, ctx->status_dev, sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
+    OTT_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+    if (*ctx->status_host != 0) {
+        const uint32_t w = *ctx->status_host;
+        cudaMemsetAsync(ctx->status_dev, 0, sizeof(uint32_t), ctx->stream);
+        return ctx->fail(OTT_ERR_DEVICE_WAIT, "a kernel gave up a bounded wait (status word 0x%x)", w);
+    }
+    return OTT_OK;
+}
+
+size_t dtype_bytes(int dtype, int n, int c, int h, int w) {
+    const size_t pix = (size_t)n * h * w;
+    switch (dtype) {
+        case OTT_F32_NCHW: return pix * c * 4;
+        case OTT_S8_NHWC: return pix * nhwc_channels(c);
+        case OTT_S32_NHWC: return pix * nhwc_channels(c) * 4;
+        default: return 0;
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+int ott_cuda_device_count(int* n) {
+    if (!n) return OTT_ERR_INVALID;
+    int c = 0;
+    if (cudaGetDeviceCount(&c) != cudaSuccess) {
+        (void)cudaGetLastError();
+        *n = 0;
+        return OTT_ERR_CUDA;
+    }
+    *n = c;
+    return OTT_OK;
+}
+
+int ott_ctx_create(int device, ott_ctx** out) {
+    if (!out) return OTT_ERR_INVALID;
+    *out = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) {
+        (void)cudaGetLastError();
+        return OTT_ERR_CUDA;
+    }
+    if (cudaSetDevice(device) != cudaSuccess) return OTT_ERR_CUDA;
+    ott_ctx* ctx = new (std::nothrow) ott_ctx();
+    if (!ctx) return OTT_ERR_ALLOC;
+    ctx->device = device;
+    cudaDeviceProp prop{};
+    if (cudaGetDeviceProperties(&prop, device) != cudaSuccess || prop.major != 10) {
+        delete ctx;
+        return OTT_ERR_UNSUPPORTED;  // the kernels are sm_100a only
+    }
+    ctx->sm_count = prop.multiProcessorCount;
+    if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess) {
+        delete ctx;
+        return OTT_ERR_CUDA;
+    }
+    ctx->alloc = new DeviceCachingAllocator(device);
+    if (cudaMalloc((void**)&ctx->status_dev, sizeof(uint32_t)) != cudaSuccess ||
+        cudaMallocHost((void**)&ctx->status_host, sizeof(uint32_t)) != cudaSuccess) {
+        ott_ctx_destroy(ctx);
+        return OTT_ERR_ALLOC;
+    }
+    cudaMemsetAsync(ctx->status_dev, 0, sizeof(uint32_t), ctx->stream);
+    *ctx->status_host = 0;
+    *out = ctx;
+    return OTT_OK;
+}
+
+int ott_ctx_destroy(ott_ctx* ctx) {
+    if (!ctx) return OTT_OK;
+    cudaSetDevice(ctx->device);
+    if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+    delete ctx->alloc;
+    if (ctx->status_dev) cudaFree(ctx->status_dev);
+    if (ctx->status_host) cudaFreeHost(ctx->status_host);
+    if (ctx->stage_in) cudaFreeHost(ctx->stage_in);
+    if (ctx->stage_out) cudaFreeHost(ctx->stage_out);
+    if (ctx->stream) cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return OTT_OK;
+}
+
+const char* ott_last_error(const ott_ctx* ctx) { return ctx ? ctx->last_error.c_str() : "null context"; }
+void* ott_ctx_stream(ott_ctx* ctx) { return ctx ? (void*)ctx->stream : nullptr; }
+uint64_t ott_launch_count(const ott_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+int ott_sync(ott_ctx* ctx) {
+    if (!ctx) return OTT_ERR_INVALID;
+    cudaSetDevice(ctx->device);
+    return check_status_word(ctx);
+}
+
+int ott_malloc(ott_ctx* ctx, size_t bytes, void** out) {
+    if (!ctx || !out) return OTT_ERR_INVALID;
+    cudaSetDevice(ctx->device);
+    cudaError_t e = ctx->alloc->allocate(bytes, out);
+    if (e != cudaSuccess) {
+        (void)cudaGetLastError();
+        return ctx->fail(OTT_ERR_ALLOC, "device allocation of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
+    }
+    return OTT_OK;
+}
+
+int ott_free(ott_ctx* ctx, void* p) {
+    if (!ctx) return OTT_ERR_INVALID;
+    return ctx->alloc->free(p) ? OTT_OK : ctx->fail(OTT_ERR_INVALID, "pointer was not allocated by this context");
+}
+
+int ott_alloc_stats(ott_ctx* ctx, uint64_t* m, uint64_t* h, uint64_t* u, uint64_t* c) {
+    if (!ctx) return OTT_ERR_INVALID;
+    ctx->alloc->stats(m, h, u, c);
+    return OTT_OK;
+}
+
+int ott_alloc_release_cached(ott_ctx* ctx) {
+    if (!ctx) return OTT_ERR_INVALID;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    ctx->alloc->release_cached();
+    return OTT_OK;
+}
+
+int ott_host_alloc(size_t bytes, void** out) {
+    if (!out) return OTT_ERR_INVALID;
+    if (cudaMallocHost(out, bytes ? bytes : 1) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return OTT_ERR_ALLOC;
+    }
+    return OTT_OK;
+}
+
+int ott_host_free(void* p) { return cudaFreeHost(p) == cudaSuccess ? OTT_OK : OTT_ERR_CUDA; }
+
+int ott_memcpy_h2d(ott_ctx* ctx, void* dst, const void* src, size_t bytes) {
+    if (!ctx) return OTT_ERR_INVALID;
+    cudaSetDevice(ctx->device);
+    OTT_CUDA_CHECK(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
+    return OTT_OK;
+}
+
+int ott_memcpy_d2h(ott_ctx* ctx, void* dst, const void* src, size_t bytes) {
+    if (!ctx) return OTT_ERR_INVALID;
+    cudaSetDevice(ctx->device);
+    OTT_CUDA_CHECK(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    return OTT_OK;
+}
+
+int ott_memset(ott_ctx* ctx, void* dst, int value, size_t bytes) {
+    if (!ctx) return OTT_ERR_INVALID;
+    cudaSetDevice(ctx->device);
+    OTT_CUDA_CHECK(ctx, cudaMemsetAsync(dst, value, bytes, ctx->stream));
+    return OTT_OK;
+}
+
+int ott_event_create(ott_ctx* ctx, ott_event** out) {
+    if (!ctx || !out) return OTT_ERR_INVALID;
+    cudaSetDevice(ctx->device);
+    ott_event* e = new (std::nothrow) ott_event();
+    if (!e) return OTT_ERR_ALLOC;
+    if (cudaEventCreate(&e->ev) != cudaSuccess) {
+        delete e;
+        return ctx->fail(OTT_ERR_CUDA, "cudaEventCreate failed");
+    }
+    *out = e;
+    return OTT_OK;
+}
+
+int ott_event_record(ott_ctx* ctx, ott_event* ev) {
+    if (!ctx || !ev) return OTT_ERR_INVALID;
+    OTT_CUDA_CHECK(ctx, cudaEventRecord(ev->ev, ctx->stream));
+    return OTT_OK;
+}
+
+int ott_event_elapsed_ms(ott_event* start, ott_event* stop, float* ms) {
+    if (!start || !stop || !ms) return OTT_ERR_INVALID;
+    if (cudaEventSynchronize(stop->ev) != cudaSuccess) return OTT_ERR_CUDA;
+    return cudaEventElapsedTime(ms, start->ev, stop->ev) == cudaSuccess ? OTT_OK : OTT_ERR_CUDA;
+}
+
+int ott_event_destroy(ott_event* ev) {
+    if (!ev) return OTT_OK;
+    cudaEventDestroy(ev->ev);
+    delete ev;
+    return OTT_OK;
+}
+
+int ott_nhwc_channels(int c) { return nhwc_channels(c); }
+
+int ott_quantize_f32_nchw_to_s8_nhwc(ott_ctx* ctx, const float* x_dev, int n, int c, int h, int w, const float* scales_host,
+                                     int n_scales, int rounding, int8_t* out_dev) {
+    if (!ctx || !x_dev || !out_dev || !scales_host || n < 0 || c <= 0 || h < 0 || w < 0) return OTT_ERR_INVALID;
+    if (n_scales != 1 && n_scales != c) return ctx->fail(OTT_ERR_INVALID, "n_scales must be 1 or the channel count");
+    cudaSetDevice(ctx->device);
+    DeviceBlock sc;
+    if (sc.alloc(ctx, sizeof(float) * n_scales) != cudaSuccess) return ctx->fail(OTT_ERR_ALLOC, "scale upload allocation failed");
+    OTT_CUDA_CHECK(ctx, cudaMemcpyAsync(sc.p, scales_host, sizeof(float) * n_scales, cudaMemcpyHostToDevice, ctx->stream));
+    OTT_CUDA_CHECK(ctx, launch_quantize_nchw_to_nhwc(ctx->stream, x_dev, out_dev, (const float*)sc.p, n_scales, n, c, h, w, rounding));
+    ctx->launches += 1;
+    // the pageable scale array must stay readable until the copy has been issued; it has (pageable copies
+    // are staged synchronously)
+    return OTT_OK;
+}
+
+int ott_conv_int8_create(ott_ctx* ctx, const ott_conv_desc* d, const int8_t* w_oihw, const float* bias, const float* w_scales,
+                         const float* in_scales, int n_in_scales, const float* out_scales, int n_out_scales, ott_conv** out) {
+    if (!ctx || !d || !w_oihw || !w_scales || !in_scales || !out) return OTT_ERR_INVALID;
+    *out = nullptr;
+    if (d->cin <= 0 || d->cout <= 0 || d->kh <= 0 || d->kw <= 0 || d->sh <= 0 || d->sw <= 0 || d->dh <= 0 || d->dw <= 0 ||
+        d->ph < 0 || d->pw < 0 || d->groups <= 0)
+        return ctx->fail(OTT_ERR_INVALID, "bad convolution geometry");
+    if (d->int8_scale_term == 0) return ctx->fail(OTT_ERR_UNSUPPORTED, "int8_scale_term == 0 is the fp32 layer; only the int8 path lives here");
+    if (d->act_type < 0 || d->act_type > 3)
+        return ctx->fail(OTT_ERR_UNSUPPORTED, "activation %d is not reproducible bit-for-bit on the GPU (only none/ReLU/LeakyReLU/ReLU6)", d->act_type);
+    if (d->bias_term && !bias) return ctx->fail(OTT_ERR_INVALID, "bias_term set but bias is NULL");
+    const bool requant = d->int8_scale_term > 100;
+    if (requant && (!out_scales || (n_out_scales != 1 && n_out_scales != d->cout)))
+        return ctx->fail(OTT_ERR_INVALID, "int8 output needs top_blob_int8_scales of size 1 or cout");
+    const bool depthwise = d->groups == d->cin && d->groups == d->cout && d->groups > 1;
+    if (!depthwise && d->groups != 1)
+        return ctx->fail(OTT_ERR_UNSUPPORTED, "grouped (non-depthwise) int8 convolution is not supported");
+    if (n_in_scales != 1 && n_in_scales != d->cin) return ctx->fail(OTT_ERR_INVALID, "bottom_blob_int8_scales must have 1 or cin entries");
+    cudaSetDevice(ctx->device);
+
+    ott_conv* c = new (std::nothrow) ott_conv();
+    if (!c) return OTT_ERR_ALLOC;
+    c->d = *d;
+    c->depthwise = depthwise;
+    c->cin_pad = nhwc_channels(d->cin);
+    c->cout_pad = nhwc_channels(d->cout);
+    c->n_in_scales = n_in_scales;
+
+    // scale_in exactly as ConvolutionLayer.cpp:667-679: fp32 product, fp32 divide, 0 for a zero weight scale
+    std::vector<float> scale_in(c->cout_pad, 0.f), bias_p(c->cout_pad, 0.f), scale_out(c->cout_pad, 0.f);
+    for (int p = 0; p < d->cout; ++p) {
+        volatile float prod = in_scales[0] * w_scales[p];
+        scale_in[p] = w_scales[p] == 0.f ? 0.f : 1.f / prod;
+        if (d->bias_term) bias_p[p] = bias[p];
+        if (requant) scale_out[p] = n_out_scales == 1 ? out_scales[0] : out_scales[p];
+    }
+
+    int rc = OTT_OK;
+    std::vector<int8_t> wpacked;
+    const int taps = d->kh * d->kw;
+    if (depthwise) {
+        c->kind = OTT_KERNEL_DEPTHWISE;
+        // [tap][c_pad], channel innermost: what depthwise.cu reads as 32-bit words of 4 channels
+        wpacked.assign((size_t)taps * c->cout_pad, 0);
+        for (int ch = 0; ch < d->cout; ++ch)
+            for (int t = 0; t < taps; ++t) wpacked[(size_t)t * c->cout_pad + ch] = w_oihw[(size_t)ch * taps + t];
+    } else {
+        int smem_optin = 0;
+        cudaDeviceGetAttribute(&smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, ctx->device);
+        if (umma_plan_layer(d->cin, d->cout, d->kh, d->kw, d->sh, d->sw, d->dh, d->dw, smem_optin, &c->plan)) {
+            c->kind = OTT_KERNEL_DENSE_UMMA;
+            wpacked.resize((size_t)c->plan.cout_rows * c->plan.k_total);
+            umma_pack_weights(c->plan, w_oihw, d->cin, d->cout, d->kh, d->kw, wpacked.data());
+        } else {
+            c->kind = OTT_KERNEL_DENSE_DIRECT;
+            // [cout_pad][tap][cin_pad]
+            wpacked.assign((size_t)c->cout_pad * taps * c->cin_pad, 0);
+            for (int o = 0; o < d->cout; ++o)
+                for (int ci = 0; ci < d->cin; ++ci)
+                    for (int t = 0; t < taps; ++t)
+                        wpacked[((size_t)o * taps + t) * c->cin_pad + ci] = w_oihw[((size_t)o * d->cin + ci) * taps + t];
+        }
+    }
+    rc = upload(ctx, wpacked.data(), wpacked.size(), (void**)&c->w_dev);
+    if (rc == OTT_OK) rc = upload(ctx, scale_in.data(), sizeof(float) * c->cout_pad, (void**)&c->scale_in_dev);
+    if (rc == OTT_OK) rc = upload(ctx, bias_p.data(), sizeof(float) * c->cout_pad, (void**)&c->bias_dev);
+    if (rc == OTT_OK) rc = upload(ctx, scale_out.data(), sizeof(float) * c->cout_pad, (void**)&c->scale_out_dev);
+    if (rc == OTT_OK) rc = upload(ctx, in_scales, sizeof(float) * n_in_scales, (void**)&c->in_scales_dev);
+    if (rc == OTT_OK && c->kind == OTT_KERNEL_DENSE_UMMA) {
+        const char* err = umma_encode_weight_map(c->plan, c->w_dev, c->weight_map);
+        if (err) rc = ctx->fail(OTT_ERR_CUDA, "%s", err);
+    }
+    // host staging vectors die at return: make sure the uploads have consumed them
+    if (rc == OTT_OK && cudaStreamSynchronize(ctx->stream) != cudaSuccess) rc = ctx->fail(OTT_ERR_CUDA, "upload failed");
+    if (rc != OTT_OK) {
+        ott_conv_int8_destroy(ctx, c);
+        return rc;
+    }
+    *out = c;
+    return OTT_OK;
+}
+
+int ott_conv_int8_destroy(ott_ctx* ctx, ott_conv* c) {
+    if (!c) return OTT_OK;
+    if (ctx) {
+        ctx->alloc->free(c->w_dev);
+        ctx->alloc->free(c->scale_in_dev);
+        ctx->alloc->free(c->bias_dev);
+        ctx->alloc->free(c->scale_out_dev);
+        ctx->alloc->free(c->in_scales_dev);
+    }
+    delete c;
+    return OTT_OK;
+}
+
+int ott_conv_int8_kernel_kind(const ott_conv* c) { return c ? c->kind : OTT_ERR_INVALID; }
+
+int ott_conv_int8_out_shape(const ott_conv* c, int h, int w, int* oh, int* ow) {
+    if (!c || !oh || !ow) return OTT_ERR_INVALID;
+    *oh = out_dim(h, c->d.kh, c->d.sh, c->d.ph, c->d.dh);
+    *ow = out_dim(w, c->d.kw, c->d.sw, c->d.pw, c->d.dw);
+    return OTT_OK;
+}
+
+int ott_conv_int8_forward(ott_ctx* ctx, const ott_conv* c, const void* in_dev, int in_dtype, int n, int h, int w, void* out_dev,
+                          int out_dtype, uint32_t* status_word_dev) {
+    if (!ctx || !c || !in_dev || !out_dev || n < 0 || h <= 0 || w <= 0) return OTT_ERR_INVALID;
+    const ott_conv_desc& d = c->d;
+    if (in_dtype != OTT_F32_NCHW && in_dtype != OTT_S8_NHWC) return ctx->fail(OTT_ERR_INVALID, "input must be fp32 NCHW or int8 NHWC");
+    const bool requant = d.int8_scale_term > 100;
+    if (out_dtype == OTT_S8_NHWC && !requant) return ctx->fail(OTT_ERR_INVALID, "int8 output needs int8_scale_term > 100");
+    if (out_dtype == OTT_F32_NCHW && requant) return ctx->fail(OTT_ERR_INVALID, "fp32 output needs int8_scale_term < 100");
+    if (out_dtype != OTT_S8_NHWC && out_dtype != OTT_F32_NCHW && out_dtype != OTT_S32_NHWC) return ctx->fail(OTT_ERR_INVALID, "bad output dtype");
+    cudaSetDevice(ctx->device);
+
+    ConvShape s{};
+    s.n = n; s.h = h; s.w = w;
+    s.oh = out_dim(h, d.kh, d.sh, d.ph, d.dh);
+    s.ow = out_dim(w, d.kw, d.sw, d.pw, d.dw);
+    if (s.oh <= 0 || s.ow <= 0) return ctx->fail(OTT_ERR_INVALID, "empty output");
+    s.cin = d.cin; s.cout = d.cout; s.cin_pad = c->cin_pad; s.cout_pad = c->cout_pad;
+    s.kh = d.kh; s.kw = d.kw; s.sh = d.sh; s.sw = d.sw; s.ph = d.ph; s.pw = d.pw; s.dh = d.dh; s.dw = d.dw;
+    if (n == 0) return OTT_OK;
+
+    EpilogueParams ep{};
+    ep.scale_in = c->scale_in_dev; ep.bias = c->bias_dev; ep.scale_out = c->scale_out_dev;
+    ep.has_bias = d.bias_term ? 1 : 0;
+    ep.act_type = d.act_type; ep.act_param0 = d.act_param0; ep.rounding = d.rounding;
+
+    DeviceBlock xq;  // scratch: the quantized activations when the input arrives as fp32
+    const int8_t* x = static_cast<const int8_t*>(in_dev);
+    if (in_dtype == OTT_F32_NCHW) {
+        if (xq.alloc(ctx, (size_t)n * h * w * c->cin_pad) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return ctx->fail(OTT_ERR_ALLOC, "scratch allocation for quantized activations failed");
+        }
+        OTT_CUDA_CHECK(ctx, launch_quantize_nchw_to_nhwc(ctx->stream, static_cast<const float*>(in_dev), (int8_t*)xq.p, c->in_scales_dev,
+                                                          c->n_in_scales, n, d.cin, h, w, d.rounding));
+        ctx->launches += 1;
+        x = (const int8_t*)xq.p;
+    }
+    uint32_t* status = status_word_dev ? status_word_dev : ctx->status_dev;
+    switch (c->kind) {
+        case OTT_KERNEL_DEPTHWISE:
+            OTT_CUDA_CHECK(ctx, launch_depthwise(ctx->stream, s, x, c->w_dev, ep, out_dev, out_dtype));
+            break;
+        case OTT_KERNEL_DENSE_DIRECT:
+            OTT_CUDA_CHECK(ctx, launch_dense_direct(ctx->stream, s, x, c->w_dev, ep, out_dev, out_dtype));
+            break;
+        case OTT_KERNEL_DENSE_UMMA: {
+            const char* err = launch_dense_umma(ctx->stream, ctx->sm_count, c->plan, c->weight_map, s, x, ep, out_dev, out_dtype, status);
+            if (err) return ctx->fail(OTT_ERR_CUDA, "%s: %s", err, cudaGetErrorString(cudaGetLastError()));
+            break;
+        }
+        default: return ctx->fail(OTT_ERR_INVALID, "corrupt layer object");
+    }
+    ctx->launches += 1;
+    return OTT_OK;
+}
+
+int ott_conv_int8_forward_host(ott_ctx* ctx, const ott_conv* c, const void* in_host, int in_dtype, int n, int h, int w,
+                               void* out_host, int out_dtype) {
+    if (!ctx || !c || !in_host || !out_host) return OTT_ERR_INVALID;
+    cudaSetDevice(ctx->device);
+    int oh = 0, ow = 0;
+    ott_conv_int8_out_shape(c, h, w, &oh, &ow);
+    const size_t in_bytes = dtype_bytes(in_dtype, n, c->d.cin, h, w), out_bytes = dtype_bytes(out_dtype, n, c->d.cout, oh, ow);
+    if (in_bytes == 0 || out_bytes == 0) return ctx->fail(OTT_ERR_INVALID, "bad dtype or empty tensor");
+    DeviceBlock din, dout;
+    if (din.alloc(ctx, in_bytes) != cudaSuccess || dout.alloc(ctx, out_bytes) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return ctx->fail(OTT_ERR_ALLOC, "device allocation failed");
+    }
+    OTT_CUDA_CHECK(ctx, cudaMemcpyAsync(din.p, in_host, in_bytes, cudaMemcpyHostToDevice, ctx->stream));
+    int rc = ott_conv_int8_forward(ctx, c, din.p, in_dtype, n, h, w, dout.p, out_dtype, nullptr);
+    if (rc != OTT_OK) return rc;
+    OTT_CUDA_CHECK(ctx, cudaMemcpyAsync(out_host, dout.p, out_bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    return check_status_word(ctx);
+}
+
+}  // extern "C"

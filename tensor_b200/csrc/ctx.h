@@ -1,0 +1,157 @@
+// Device context shared by every translation unit of the library: one CUDA device, one stream and one
+// caching allocator per ott_ctx (include/otter_b200.h). Host code only.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <map>
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/otter_b200.h"
+
+// Stream-ordered, size-keyed cache of device blocks. Every block is used on the owning context's single
+// stream only, so a block freed at stream position p can be handed out again at any later position
+// without an event: the stream orders the old user's kernels before the new user's.
+class DeviceCachingAllocator {
+public:
+    explicit DeviceCachingAllocator(int device) : device_(device) {}
+    ~DeviceCachingAllocator() { release_cached(); }
+
+    static size_t round_size(size_t bytes) {
+        if (bytes == 0) bytes = 1;
+        if (bytes <= (1u << 20)) return (bytes + 511) & ~size_t(511);       // 512 B granules up to 1 MiB
+        return (bytes + (size_t(2) << 20) - 1) & ~((size_t(2) << 20) - 1);  // 2 MiB granules above
+    }
+
+    cudaError_t allocate(size_t bytes, void** out) {
+        const size_t sz = round_size(bytes);
+        std::lock_guard<std::mutex> g(mu_);
+        auto it = available_.find(sz);
+        if (it != available_.end() && !it->second.empty()) {
+            *out = it->second.back();
+            it->second.pop_back();
+            bytes_cached_ -= sz;
+            bytes_in_use_ += sz;
+            ++n_cache_hits_;
+            return cudaSuccess;
+        }
+        void* p = nullptr;
+        cudaError_t e = cudaMalloc(&p, sz);
+        if (e != cudaSuccess) {
+            // give cached blocks back to the driver and retry once
+            (void)cudaGetLastError();
+            release_cached_locked();
+            e = cudaMalloc(&p, sz);
+            if (e != cudaSuccess) return e;
+        }
+        ++n_device_mallocs_;
+        sizes_[p] = sz;
+        bytes_in_use_ += sz;
+        *out = p;
+        return cudaSuccess;
+    }
+
+    bool free(void* p) {
+        if (!p) return true;
+        std::lock_guard<std::mutex> g(mu_);
+        auto it = sizes_.find(p);
+        if (it == sizes_.end()) return false;
+        available_[it->second].push_back(p);
+        bytes_in_use_ -= it->second;
+        bytes_cached_ += it->second;
+        return true;
+    }
+
+    void release_cached() {
+        std::lock_guard<std::mutex> g(mu_);
+        release_cached_locked();
+    }
+
+    void stats(uint64_t* mallocs, uint64_t* hits, uint64_t* in_use, uint64_t* cached) {
+        std::lock_guard<std::mutex> g(mu_);
+        if (mallocs) *mallocs = n_device_mallocs_;
+        if (hits) *hits = n_cache_hits_;
+        if (in_use) *in_use = bytes_in_use_;
+        if (cached) *cached = bytes_cached_;
+    }
+
+private:
+    void release_cached_locked() {
+        for (auto& kv : available_) {
+            for (void* p : kv.second) {
+                cudaFree(p);
+                sizes_.erase(p);
+            }
+            kv.second.clear();
+        }
+        bytes_cached_ = 0;
+    }
+
+    int device_;
+    std::mutex mu_;
+    std::map<size_t, std::vector<void*>> available_;
+    std::unordered_map<void*, size_t> sizes_;
+    uint64_t n_device_mallocs_ = 0, n_cache_hits_ = 0, bytes_in_use_ = 0, bytes_cached_ = 0;
+};
+
+struct ott_ctx {
+    int device = 0;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;
+    DeviceCachingAllocator* alloc = nullptr;
+    std::string last_error;
+    uint64_t launches = 0;
+    uint32_t* status_dev = nullptr;   // default status word the kernels report into
+    uint32_t* status_host = nullptr;  // pinned mirror
+    // pinned staging buffers of the *_host entry points
+    void* stage_in = nullptr;
+    size_t stage_in_bytes = 0;
+    void* stage_out = nullptr;
+    size_t stage_out_bytes = 0;
+
+    int fail(int code, const char* fmt, ...) {
+        char buf[512];
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(buf, sizeof buf, fmt, ap);
+        va_end(ap);
+        last_error = buf;
+        return code;
+    }
+};
+
+struct ott_event {
+    cudaEvent_t ev = nullptr;
+};
+
+#define OTT_CUDA_CHECK(ctx, expr)                                                                         \
+    do {                                                                                                  \
+        cudaError_t _e = (expr);                                                                          \
+        if (_e != cudaSuccess)                                                                            \
+            return (ctx)->fail(OTT_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__, __LINE__); \
+    } while (0)
+
+// RAII device block from the context's caching allocator.
+struct DeviceBlock {
+    ott_ctx* ctx = nullptr;
+    void* p = nullptr;
+    DeviceBlock() = default;
+    DeviceBlock(const DeviceBlock&) = delete;
+    DeviceBlock& operator=(const DeviceBlock&) = delete;
+    ~DeviceBlock() { reset(); }
+    cudaError_t alloc(ott_ctx* c, size_t bytes) {
+        reset();
+        ctx = c;
+        return c->alloc->allocate(bytes, &p);
+    }
+    void reset() {
+        if (p && ctx) ctx->alloc->free(p);
+        p = nullptr;
+    }
+};

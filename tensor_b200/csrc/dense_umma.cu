@@ -1,0 +1,482 @@
+// Dense int8 convolution as an implicit GEMM on the sm_100a tensor cores.
+//
+// Replaces the reference's im2col + sgemm int8 path (Tensor/ConvolutionMM2DInt8X86Pack.cpp:2369-2445 builds
+// the im2col matrix, :1656-2223 is the s8 x s8 -> s32 GEMM, :2533-2556 the 1x1 shortcut) and the epilogue
+// passes that follow it (Tensor/QuantizeX86.cpp:851-903 dequantize, :1723-1870 requantize). No im2col
+// matrix, no s32 tensor and no padded copy ever reach HBM:
+//
+//   D[128 pixels, BN out-channels] (s32, in TMEM)  +=  A[128 pixels, 32..128 in-channels] * B[BN, same]^T
+//
+// * A tiles come straight from the NHWC int8 activations with 4-D TMA boxes {channels, TW, TH, 1}; one box
+//   per filter tap, shifted by the tap offset; out-of-image rows/columns are zero-filled by TMA, which is
+//   the reference's constant_pad (Tensor/Padding.cpp:22-36). 1x1 convolutions view the activations as a
+//   flat [pixels, channels] matrix so tiles never straddle anything.
+// * B (the layer's weights for this CTA's BN output channels, all taps) is loaded once per CTA and stays in
+//   shared memory while the CTA walks over its pixel tiles (persistent, weight-stationary).
+// * tcgen05.mma.kind::i8 accumulates exact s32 in TMEM; two accumulators are double-buffered so the
+//   epilogue of tile i overlaps the loads and MMAs of tile i+1.
+// * The epilogue warps read TMEM (tcgen05.ld), apply fma(acc, scale_in, bias) -> activation -> requantize
+//   (epilogue.cuh) and store int8 NHWC / fp32 NCHW / s32 NHWC.
+//
+// Warp roles (192 threads): warp 0 = TMA producer (one lane), warp 1 = TMEM owner + MMA issuer (one lane),
+// warps 2..5 = epilogue (warp w reads TMEM lanes 32*(w%4)..+31).
+// Every mbarrier wait is bounded in time: on expiry the waiter raises a CTA-wide abort flag, ORs a code
+// into the status word, and all roles fall through to the common teardown, which frees TMEM.
+#include <cuda.h>
+
+#include "dense_umma.h"
+
+namespace ottk {
+
+namespace {
+
+constexpr int kThreads = 192;
+constexpr int kTileM = 128;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per wait
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait. Returns false (after raising the CTA's abort flag) when the limit passes or another
+// role has already aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t* status,
+                                          uint32_t code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = globaltimer_ns();
+    for (uint32_t spin = 1;; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 255u) == 0) {
+            if (*abort_flag) return false;
+            if (globaltimer_ns() - t0 > kWaitLimitNs) {
+                *abort_flag = 1;
+                if (status) atomicOr(status, code);
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_4d(const CUtensorMap* map, uint32_t bar, uint32_t dst, int c0, int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint32_t bar, uint32_t dst, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
+        : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// K-major shared-memory operand descriptor: rows of `row_bytes` (= the swizzle span), 8-row groups
+// `8*row_bytes` apart. Bits: [0,14) address>>4, [16,30) leading offset>>4 (unused for swizzled K-major),
+// [32,46) stride offset>>4, [46,48) version=1, [61,64) swizzle (2=128B, 4=64B, 6=32B).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, int row_bytes) {
+    const uint64_t swz = row_bytes == 128 ? 2ull : (row_bytes == 64 ? 4ull : 6ull);
+    const uint64_t sbo = (uint64_t)(8 * row_bytes) >> 4;
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | (sbo << 32) | (1ull << 46) | (swz << 61);
+}
+
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t"
+        "}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, int v[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+struct SmemLayout {
+    uint32_t b_panel, a_stages, bars, tmem_slot, abort_flag, total;
+};
+
+__host__ __device__ inline SmemLayout smem_layout(const UmmaPlan& p) {
+    SmemLayout L;
+    L.b_panel = 0;
+    L.a_stages = (uint32_t)p.nkb * p.bn * p.bkc;
+    L.bars = L.a_stages + (uint32_t)p.stages * kTileM * p.bkc;
+    // barriers: full[stages], empty[stages], b_full, tmem_full[2], tmem_empty[2]
+    L.tmem_slot = L.bars + 8u * (2u * p.stages + 5u);
+    L.abort_flag = L.tmem_slot + 8;
+    L.total = L.abort_flag + 8;
+    return L;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+dense_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const UmmaPlan P,
+                  const ConvShape s, const EpilogueParams ep, void* __restrict__ out, const int out_dtype,
+                  uint32_t* __restrict__ status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+    const SmemLayout L = smem_layout(P);
+    const uint32_t sB = base + L.b_panel, sA = base + L.a_stages;
+    const uint32_t bar_full = base + L.bars, bar_empty = bar_full + 8u * P.stages, bar_b = bar_empty + 8u * P.stages;
+    const uint32_t bar_tfull = bar_b + 8, bar_tempty = bar_tfull + 16;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + L.tmem_slot);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + L.abort_flag);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_tile = blockIdx.x % P.n_tiles;
+    const int m_first = blockIdx.x / P.n_tiles, m_step = gridDim.x / P.n_tiles;
+    const uint32_t a_stage_bytes = (uint32_t)kTileM * P.bkc, b_tile_bytes = (uint32_t)P.bn * P.bkc;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < P.stages; ++i) {
+            mbar_init(bar_full + 8u * i, 1);
+            mbar_init(bar_empty + 8u * i, 1);
+        }
+        mbar_init(bar_b, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(bar_tfull + 8u * i, 1);
+            mbar_init(bar_tempty + 8u * i, 4);  // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)),
+                     "r"((uint32_t)P.tmem_cols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- TMA producer ----
+            mbar_expect_tx(bar_b, (uint32_t)P.nkb * b_tile_bytes);
+            for (int kb = 0; kb < P.nkb; ++kb) tma_load_2d(&tmB, bar_b, sB + kb * b_tile_bytes, kb * P.bkc, n_tile * P.bn);
+            uint32_t it = 0;
+            bool ok = true;
+            for (int m = m_first; ok && m < P.m_tiles; m += m_step) {
+                int img, y0, x0;
+                if (P.flat) {
+                    img = 0; y0 = 0; x0 = m * kTileM;
+                } else {
+                    const int per_img = P.tiles_x * P.tiles_y;
+                    img = m / per_img;
+                    const int r = m - img * per_img;
+                    y0 = (r / P.tiles_x) * P.th - s.ph;
+                    x0 = (r % P.tiles_x) * P.tw - s.pw;
+                }
+                for (int kb = 0; kb < P.nkb; ++kb, ++it) {
+                    const int tap = kb / P.ncb, cb = kb - tap * P.ncb;
+                    const int ky = tap / s.kw, kx = tap - ky * s.kw;
+                    const uint32_t st = it % P.stages, ph = (it / P.stages) & 1u;
+                    if (!mbar_wait(bar_empty + 8u * st, ph ^ 1u, abort_flag, status, 1u)) { ok = false; break; }
+                    mbar_expect_tx(bar_full + 8u * st, a_stage_bytes);
+                    tma_load_4d(&tmA, bar_full + 8u * st, sA + st * a_stage_bytes, cb * P.bkc, x0 + kx * s.dw, y0 + ky * s.dh, img);
+                }
+            }
+            if (!ok) {
+                // let bulk copies already in flight land before the CTA's shared memory is released
+                const unsigned long long t0 = globaltimer_ns();
+                while (globaltimer_ns() - t0 < 1000000ull) {}
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- MMA issuer ----
+            bool ok = mbar_wait(bar_b, 0, abort_flag, status, 16u);
+            tc_fence_after();
+            uint32_t it = 0, tile_i = 0;
+            for (int m = m_first; ok && m < P.m_tiles; m += m_step, ++tile_i) {
+                const uint32_t buf = tile_i & 1u, use = tile_i >> 1;
+                if (!mbar_wait(bar_tempty + 8u * buf, (use & 1u) ^ 1u, abort_flag, status, 4u)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d = tmem_base + buf * (uint32_t)P.acc_stride;
+                for (int kb = 0; kb < P.nkb; ++kb, ++it) {
+                    const uint32_t st = it % P.stages, ph = (it / P.stages) & 1u;
+                    if (!mbar_wait(bar_full + 8u * st, ph, abort_flag, status, 2u)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t adesc = make_smem_desc(sA + st * a_stage_bytes, P.bkc);
+                    const uint64_t bdesc = make_smem_desc(sB + kb * b_tile_bytes, P.bkc);
+                    for (int j = 0; j < P.bkc / 32; ++j)
+                        umma_i8(d, adesc + 2ull * j, bdesc + 2ull * j, P.idesc, (kb | j) != 0 ? 1u : 0u);
+                    umma_commit(bar_empty + 8u * st);  // frees the A stage once these MMAs have read it
+                }
+                if (!ok) break;
+                umma_commit(bar_tfull + 8u * buf);  // accumulator complete
+            }
+        }
+    } else {
+        // ---- epilogue warps ----
+        const int q = warp & 3;
+        const int row = q * 32 + lane;
+        const long plane = (long)s.oh * s.ow;
+        const long total_pix = (long)s.n * plane;
+        uint32_t tile_i = 0;
+        bool ok = true;
+        for (int m = m_first; ok && m < P.m_tiles; m += m_step, ++tile_i) {
+            const uint32_t buf = tile_i & 1u, use = tile_i >> 1;
+            if (!mbar_wait(bar_tfull + 8u * buf, use & 1u, abort_flag, status, 8u)) { ok = false; break; }
+            tc_fence_after();
+            // which output pixel this thread's TMEM lane holds
+            long pix;  // linear (img, oy, ox) index
+            bool valid;
+            if (P.flat) {
+                pix = (long)m * kTileM + row;
+                valid = pix < total_pix;
+            } else {
+                const int per_img = P.tiles_x * P.tiles_y;
+                const int img = m / per_img;
+                const int r = m - img * per_img;
+                const int oy = (r / P.tiles_x) * P.th + row / P.tw;
+                const int ox = (r % P.tiles_x) * P.tw + row % P.tw;
+                valid = oy < s.oh && ox < s.ow;
+                pix = (long)img * plane + (long)oy * s.ow + ox;
+            }
+            const uint32_t taddr = tmem_base + buf * (uint32_t)P.acc_stride + ((uint32_t)(q * 32) << 16);
+            for (int col0 = 0; col0 < P.bn; col0 += 16) {
+                int v[16];
+                __syncwarp();  // tcgen05.ld is warp-collective; rows skipped below must rejoin first
+                tmem_ld16(taddr + (uint32_t)col0, v);
+                const int c0 = n_tile * P.bn + col0;  // first global output channel of this chunk
+                if (!valid || c0 >= s.cout_pad) continue;
+                if (out_dtype == DT_S8_NHWC) {
+                    uint32_t wds[4];
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        int qv[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int c = c0 + g * 4 + j;
+                            qv[j] = requant(v[g * 4 + j], __ldg(ep.scale_in + c), __ldg(ep.bias + c), __ldg(ep.scale_out + c), ep);
+                        }
+                        wds[g] = pack4(qv[0], qv[1], qv[2], qv[3]);
+                    }
+                    *reinterpret_cast<uint4*>(reinterpret_cast<int8_t*>(out) + pix * s.cout_pad + c0) =
+                        make_uint4(wds[0], wds[1], wds[2], wds[3]);
+                } else if (out_dtype == DT_F32_NCHW) {
+                    const long img = pix / plane, inimg = pix - img * plane;
+                    float* o = reinterpret_cast<float*>(out) + (img * s.cout) * plane + inimg;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int c = c0 + j;
+                        if (c < s.cout) o[(long)c * plane] = dequant_act(v[j], __ldg(ep.scale_in + c), __ldg(ep.bias + c), ep);
+                    }
+                } else {  // DT_S32_NHWC
+                    int4* o = reinterpret_cast<int4*>(reinterpret_cast<int32_t*>(out) + pix * s.cout_pad + c0);
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) o[g] = make_int4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty + 8u * buf);
+        }
+    }
+
+    // ---- teardown (every path ends here) ----
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)P.tmem_cols) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+CUtensorMapSwizzle swizzle_for(int bkc) {
+    return bkc == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (bkc == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+}
+
+}  // namespace
+
+static int round_up(int a, int b) { return (a + b - 1) / b * b; }
+
+bool umma_plan_layer(int cin, int cout, int kh, int kw, int sh, int sw, int dh, int dw, int smem_budget, UmmaPlan* plan) {
+    UmmaPlan p{};
+    const int cin_pad = nhwc_channels(cin), cout_pad = nhwc_channels(cout);
+    if (sh != 1 || sw != 1) return false;  // strided dense convolutions go to the direct kernel
+    if (cin_pad < 32) return false;        // a TMA box may not be wider than the tensor
+    p.bkc = cin_pad >= 128 ? 128 : (cin_pad >= 64 ? 64 : 32);
+    p.ncb = (cin_pad + p.bkc - 1) / p.bkc;
+    p.taps = kh * kw;
+    p.nkb = p.taps * p.ncb;
+    const long k_total = (long)p.nkb * p.bkc;
+    // largest BN (multiple of 16, <= 256) whose weight panel leaves room for at least 3 A stages,
+    // preferring a split of cout_pad into equal tiles
+    const long a_stage = (long)kTileM * p.bkc;
+    const long avail = (long)smem_budget - 1024 /*alignment slack*/ - 256 /*barriers*/ - 3 * a_stage;
+    if (avail <= 0) return false;
+    long bn_max = avail / k_total;
+    bn_max = bn_max > 256 ? 256 : bn_max;
+    bn_max = bn_max / 16 * 16;
+    if (bn_max < 16) return false;
+    p.n_tiles = (cout_pad + (int)bn_max - 1) / (int)bn_max;
+    p.bn = round_up((cout_pad + p.n_tiles - 1) / p.n_tiles, 16);
+    if (p.bkc == 32) p.bn = round_up(p.bn, 32);  // keeps every weight tile on a 1 KiB boundary
+    if (p.bn > 256 || (long)p.bn * k_total > avail) return false;
+    const long left = (long)smem_budget - 1024 - 256 - (long)p.bn * k_total;
+    p.stages = (int)(left / a_stage);
+    if (p.stages > 8) p.stages = 8;
+    if (p.stages < 2) return false;
+    // two accumulators of bn columns each; TMEM allocations are powers of two >= 32 columns
+    p.acc_stride = p.bn <= 32 ? 32 : (p.bn <= 64 ? 64 : (p.bn <= 128 ? 128 : 256));
+    p.tmem_cols = 2 * p.acc_stride;
+    // instruction descriptor: D=s32 (2<<4), A=B=signed int8 (1<<7, 1<<10), both K-major, N>>3 at bit 17, M>>4 at bit 24
+    p.idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+    p.k_total = (int)k_total;
+    p.cout_rows = p.n_tiles * p.bn;
+    SmemLayout L = smem_layout(p);
+    p.smem_bytes = (int)L.total + 1024;
+    *plan = p;
+    return true;
+}
+
+void umma_pack_weights(const UmmaPlan& p, const int8_t* w_oihw, int cin, int cout, int kh, int kw, int8_t* dst) {
+    // dst[cout_rows][k_total], k = (tap*ncb + cb)*bkc + (channel - cb*bkc); zero elsewhere
+    const long kt = p.k_total;
+    for (long i = 0; i < (long)p.cout_rows * kt; ++i) dst[i] = 0;
+    for (int o = 0; o < cout; ++o)
+        for (int c = 0; c < cin; ++c)
+            for (int t = 0; t < kh * kw; ++t) {
+                const int cb = c / p.bkc, ci = c % p.bkc;
+                dst[o * kt + ((long)t * p.ncb + cb) * p.bkc + ci] = w_oihw[((long)o * cin + c) * kh * kw + t];
+            }
+}
+
+const char* umma_encode_weight_map(const UmmaPlan& p, const int8_t* w_dev, void* map_out) {
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return "cuTensorMapEncodeTiled entry point not available";
+    cuuint64_t dims[2] = {(cuuint64_t)p.k_total, (cuuint64_t)p.cout_rows};
+    cuuint64_t strides[1] = {(cuuint64_t)p.k_total};
+    cuuint32_t box[2] = {(cuuint32_t)p.bkc, (cuuint32_t)p.bn};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(reinterpret_cast<CUtensorMap*>(map_out), CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void*)w_dev, dims, strides, box,
+                     estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(p.bkc), CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? nullptr : "cuTensorMapEncodeTiled(weights) failed";
+}
+
+const char* launch_dense_umma(cudaStream_t stream, int sm_count, const UmmaPlan& plan_in, const void* weight_map,
+                              const ConvShape& s, const int8_t* x, const EpilogueParams& ep, void* out, int out_dtype,
+                              uint32_t* status) {
+    EncodeTiledFn enc = get_encode_fn();
+    if (!enc) return "cuTensorMapEncodeTiled entry point not available";
+    UmmaPlan p = plan_in;
+    const long pixels = (long)s.n * s.oh * s.ow;
+    if (pixels == 0) return nullptr;
+    CUtensorMap tmA;
+    const bool flat = s.kh == 1 && s.kw == 1 && s.ph == 0 && s.pw == 0;
+    p.flat = flat ? 1 : 0;
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r;
+    if (flat) {
+        p.tw = kTileM; p.th = 1; p.tiles_x = (int)((pixels + kTileM - 1) / kTileM); p.tiles_y = 1;
+        p.m_tiles = p.tiles_x;
+        cuuint64_t dims[4] = {(cuuint64_t)s.cin_pad, (cuuint64_t)pixels, 1, 1};
+        cuuint64_t strides[3] = {(cuuint64_t)s.cin_pad, (cuuint64_t)s.cin_pad * pixels, (cuuint64_t)s.cin_pad * pixels};
+        cuuint32_t box[4] = {(cuuint32_t)p.bkc, (cuuint32_t)kTileM, 1, 1};
+        r = enc(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)x, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                swizzle_for(p.bkc), CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else {
+        // rectangle of 128 output pixels with the least padding waste
+        long best = -1;
+        for (int tw = 8; tw <= 128; tw *= 2) {
+            const int th = kTileM / tw;
+            const long cover = (long)((s.ow + tw - 1) / tw) * tw * ((s.oh + th - 1) / th) * th;
+            if (best < 0 || cover < best) { best = cover; p.tw = tw; p.th = th; }
+        }
+        p.tiles_x = (s.ow + p.tw - 1) / p.tw;
+        p.tiles_y = (s.oh + p.th - 1) / p.th;
+        p.m_tiles = s.n * p.tiles_x * p.tiles_y;
+        cuuint64_t dims[4] = {(cuuint64_t)s.cin_pad, (cuuint64_t)s.w, (cuuint64_t)s.h, (cuuint64_t)s.n};
+        cuuint64_t strides[3] = {(cuuint64_t)s.cin_pad, (cuuint64_t)s.cin_pad * s.w, (cuuint64_t)s.cin_pad * s.w * s.h};
+        cuuint32_t box[4] = {(cuuint32_t)p.bkc, (cuuint32_t)p.tw, (cuuint32_t)p.th, 1};
+        r = enc(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)x, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                swizzle_for(p.bkc), CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
+    if (r != CUDA_SUCCESS) return "cuTensorMapEncodeTiled(activations) failed";
+
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        if (cudaFuncSetAttribute(dense_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
+            return "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed";
+        attr_set[dev] = true;
+    }
+    int per_n = sm_count / p.n_tiles;
+    if (per_n < 1) per_n = 1;
+    if (per_n > p.m_tiles) per_n = p.m_tiles;
+    const int grid = per_n * p.n_tiles;
+    dense_umma_kernel<<<grid, kThreads, p.smem_bytes, stream>>>(tmA, *reinterpret_cast<const CUtensorMap*>(weight_map), p, s, ep,
+                                                               out, out_dtype, status);
+    return cudaGetLastError() == cudaSuccess ? nullptr : "dense_umma_kernel launch failed";
+}
+
+}  // namespace ottk

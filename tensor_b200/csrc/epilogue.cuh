@@ -1,0 +1,90 @@
+// Bit-exact float epilogue and prologue arithmetic shared by all convolution kernels.
+//
+// Every rounding step of the reference's x86 code is written out with an explicit intrinsic so that
+// the compiler neither fuses nor splits anything (the library is also compiled with -fmad=false):
+//   dequantize  v = fma((float)acc, scale_in, bias)      Tensor/QuantizeX86.cpp:851-903 as built with the
+//                                                         reference's -Ofast -mfma flags (one FMA);
+//               without bias: (float)acc * scale_in       Tensor/QuantizeX86.cpp:864-880
+//   activation  ReLU / LeakyReLU / clip[0,6]              Tensor/QuantizeX86.hpp:72-106
+//   requantize  q = float2int8(v * scale_out)             Tensor/QuantizeX86.cpp:1723-1870
+//   float2int8  trunc(v + copysign(0.5, v)), clamp ±127   Tensor/VecIntrinsic.hpp:71-95   (rounding 0)
+//               round half away from zero, clamp ±127     Tensor/QuantizeX86.cpp:18-23    (rounding 1)
+//   quantize    q = float2int8(x * scale)                 Tensor/QuantizeX86.cpp:396-549
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ottk {
+
+enum : int { ACT_NONE = 0, ACT_RELU = 1, ACT_LRELU = 2, ACT_RELU6 = 3 };
+enum : int { ROUND_ADD_HALF_TRUNC = 0, ROUND_HALF_AWAY = 1 };
+
+// Per-layer epilogue parameters. Arrays are device pointers with one entry per (padded) output channel;
+// entries of padding channels are zero so those channels come out as 0.
+struct EpilogueParams {
+    const float* scale_in;   // [cout_pad]
+    const float* bias;       // [cout_pad] (zeros when the layer has no bias)
+    const float* scale_out;  // [cout_pad] (per-tensor scale replicated); unused for fp32 output
+    int has_bias;
+    int act_type;
+    float act_param0;
+    int rounding;
+};
+
+__device__ __forceinline__ float dequant(int acc, float scale_in, float bias, int has_bias) {
+    const float a = __int2float_rn(acc);
+    return has_bias ? __fmaf_rn(a, scale_in, bias) : __fmul_rn(a, scale_in);
+}
+
+template <int ACT>
+__device__ __forceinline__ float activate_t(float v, float p0) {
+    if (ACT == ACT_RELU) return v > 0.f ? v : 0.f;
+    if (ACT == ACT_LRELU) return v > 0.f ? v : __fmul_rn(v, p0);
+    if (ACT == ACT_RELU6) return fminf(fmaxf(v, 0.f), 6.f);
+    return v;
+}
+
+__device__ __forceinline__ float activate(float v, int act, float p0) {
+    switch (act) {
+        case ACT_RELU: return activate_t<ACT_RELU>(v, p0);
+        case ACT_LRELU: return activate_t<ACT_LRELU>(v, p0);
+        case ACT_RELU6: return activate_t<ACT_RELU6>(v, p0);
+        default: return v;
+    }
+}
+
+// float -> int in [-127,127], kept as int so four of them can be packed by the caller.
+__device__ __forceinline__ int float2int8(float v, int rounding) {
+    int i;
+    if (rounding == ROUND_HALF_AWAY) {
+        const float t = truncf(v);
+        const float frac = __fsub_rn(v, t);  // exact
+        i = __float2int_rz(t);
+        if (fabsf(frac) >= 0.5f) i += (v < 0.f) ? -1 : 1;
+    } else {
+        const float adj = __fadd_rn(v, copysignf(0.5f, v));
+        i = __float2int_rz(adj);
+    }
+    return max(-127, min(127, i));
+}
+
+__device__ __forceinline__ int requant(int acc, float scale_in, float bias, float scale_out, const EpilogueParams& ep) {
+    float v = dequant(acc, scale_in, bias, ep.has_bias);
+    v = activate(v, ep.act_type, ep.act_param0);
+    return float2int8(__fmul_rn(v, scale_out), ep.rounding);
+}
+
+__device__ __forceinline__ float dequant_act(int acc, float scale_in, float bias, const EpilogueParams& ep) {
+    return activate(dequant(acc, scale_in, bias, ep.has_bias), ep.act_type, ep.act_param0);
+}
+
+__device__ __forceinline__ int quantize1(float x, float scale, int rounding) {
+    return float2int8(__fmul_rn(x, scale), rounding);
+}
+
+__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
+    return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) | ((uint32_t)(d & 0xff) << 24);
+}
+
+}  // namespace ottk

@@ -1,0 +1,34 @@
+// Launchers of the CUDA kernels, as seen by the host-side C-ABI (c_api.cu). Device pointers only.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "epilogue.cuh"
+
+namespace ottk {
+
+// channel stride of the NHWC layouts: a multiple of 16 bytes so that one pixel row can be a TMA box row
+__host__ __device__ inline int nhwc_channels(int c) { return (c + 15) & ~15; }
+
+enum : int { DT_F32_NCHW = 0, DT_S8_NHWC = 1, DT_S32_NHWC = 2 };
+
+// Shape of one convolution call (all kernels).
+struct ConvShape {
+    int n, h, w, oh, ow;
+    int cin, cout, cin_pad, cout_pad;  // *_pad = NHWC channel strides
+    int kh, kw, sh, sw, ph, pw, dh, dw;
+};
+
+cudaError_t launch_quantize_nchw_to_nhwc(cudaStream_t stream, const float* x, int8_t* out, const float* scales_dev,
+                                         int n_scales, int n, int c, int h, int w, int rounding);
+
+// Depthwise: x int8 NHWC [n,h,w,c_pad]; weights int8 [kh*kw][c_pad] (tap-major, channel innermost).
+cudaError_t launch_depthwise(cudaStream_t stream, const ConvShape& s, const int8_t* x, const int8_t* w_taps,
+                             const EpilogueParams& ep, void* out, int out_dtype);
+
+// Direct dense convolution on CUDA cores: x int8 NHWC; weights int8 [cout_pad][kh*kw][cin_pad].
+cudaError_t launch_dense_direct(cudaStream_t stream, const ConvShape& s, const int8_t* x, const int8_t* w_okc,
+                                const EpilogueParams& ep, void* out, int out_dtype);
+
+}  // namespace ottk
