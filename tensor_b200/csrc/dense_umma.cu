@@ -18,8 +18,9 @@
 // * The epilogue warps read TMEM (tcgen05.ld), apply fma(acc, scale_in, bias) -> activation -> requantize
 //   (epilogue.cuh) and store int8 NHWC / fp32 NCHW / s32 NHWC.
 //
-// Warp roles (192 threads): warp 0 = TMA producer (one lane), warp 1 = TMEM owner + MMA issuer (one lane),
-// warps 2..5 = epilogue (warp w reads TMEM lanes 32*(w%4)..+31).
+// Warp roles (320 threads): warp 0 = TMA producer (one lane), warp 1 = TMEM owner + MMA issuer (one lane),
+// warps 2..9 = epilogue: warp w reads TMEM lanes 32*(w%4)..+31 (the hardware's lane window of a warp) and
+// takes every other 32-column chunk, so two warps share each lane quarter.
 // Every mbarrier wait is bounded in time: on expiry the waiter raises a CTA-wide abort flag, ORs a code
 // into the status word, and all roles fall through to the common teardown, which frees TMEM.
 #include <cuda.h>
@@ -30,7 +31,8 @@ namespace ottk {
 
 namespace {
 
-constexpr int kThreads = 192;
+constexpr int kEpiWarps = 8;
+constexpr int kThreads = 64 + 32 * kEpiWarps;
 constexpr int kTileM = 128;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per wait
 
@@ -128,6 +130,8 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// 16 consecutive TMEM columns of this thread's lane. The load is asynchronous; the wait names the
+// destination registers as in/out operands so that no use of them can be scheduled above it.
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, int v[16]) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
@@ -135,11 +139,29 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, int v[16]) {
           "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
         : "r"(taddr)
         : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_wait_ld16(int v[16]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]),
+                   "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15])
+                 :
+                 : "memory");
+}
+
+// two s32 -> two saturated s8 in the low half of d, upper half taken from c (cvt.pack)
+__device__ __forceinline__ uint32_t pack_sat_s8x2(int hi, int lo, uint32_t c) {
+    uint32_t d;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(hi), "r"(lo), "r"(c));
+    return d;
+}
+
+__device__ __forceinline__ uint32_t pack_sat_s8x4(int a, int b, int c, int d) {  // a -> byte 0
+    return pack_sat_s8x2(b, a, pack_sat_s8x2(d, c, 0));
 }
 
 struct SmemLayout {
-    uint32_t b_panel, a_stages, bars, tmem_slot, abort_flag, total;
+    uint32_t b_panel, a_stages, bars, tmem_slot, abort_flag, params, total;
 };
 
 __host__ __device__ inline SmemLayout smem_layout(const UmmaPlan& p) {
@@ -150,14 +172,15 @@ __host__ __device__ inline SmemLayout smem_layout(const UmmaPlan& p) {
     // barriers: full[stages], empty[stages], b_full, tmem_full[2], tmem_empty[2]
     L.tmem_slot = L.bars + 8u * (2u * p.stages + 5u);
     L.abort_flag = L.tmem_slot + 8;
-    L.total = L.abort_flag + 8;
+    L.params = (L.abort_flag + 8 + 15u) & ~15u;  // scale_in[bn], bias[bn], scale_out[bn]; read as float4
+    L.total = L.params + 3u * 4u * p.bn;
     return L;
 }
 
+template <int OUT, int ACT, bool BIAS, int ROUND>
 __global__ void __launch_bounds__(kThreads, 1)
 dense_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const UmmaPlan P,
-                  const ConvShape s, const EpilogueParams ep, void* __restrict__ out, const int out_dtype,
-                  uint32_t* __restrict__ status) {
+                  const ConvShape s, const EpilogueParams ep, void* __restrict__ out, uint32_t* __restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -181,11 +204,21 @@ dense_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         mbar_init(bar_b, 1);
         for (int i = 0; i < 2; ++i) {
             mbar_init(bar_tfull + 8u * i, 1);
-            mbar_init(bar_tempty + 8u * i, 4);  // one arrival per epilogue warp
+            mbar_init(bar_tempty + 8u * i, kEpiWarps);  // one arrival per epilogue warp
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    {
+        float* sp = reinterpret_cast<float*>(base_ptr + L.params);
+        for (int i = threadIdx.x; i < P.bn; i += kThreads) {
+            const int c = n_tile * P.bn + i;
+            const bool in = c < s.cout_pad;
+            sp[i] = in ? ep.scale_in[c] : 0.f;
+            sp[P.bn + i] = in ? ep.bias[c] : 0.f;
+            sp[2 * P.bn + i] = in ? ep.scale_out[c] : 0.f;
+        }
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)),
@@ -258,10 +291,14 @@ dense_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         }
     } else {
         // ---- epilogue warps ----
-        const int q = warp & 3;
+        const int q = warp & 3;            // TMEM lane quarter this warp may read
+        const int half = (warp - 2) >> 2;  // which of the two warps of that quarter
         const int row = q * 32 + lane;
         const long plane = (long)s.oh * s.ow;
         const long total_pix = (long)s.n * plane;
+        const float* s_si = reinterpret_cast<const float*>(base_ptr + L.params);
+        const float* s_bi = s_si + P.bn;
+        const float* s_so = s_bi + P.bn;
         uint32_t tile_i = 0;
         bool ok = true;
         for (int m = m_first; ok && m < P.m_tiles; m += m_step, ++tile_i) {
@@ -284,38 +321,66 @@ dense_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 pix = (long)img * plane + (long)oy * s.ow + ox;
             }
             const uint32_t taddr = tmem_base + buf * (uint32_t)P.acc_stride + ((uint32_t)(q * 32) << 16);
-            for (int col0 = 0; col0 < P.bn; col0 += 16) {
+            int8_t* out_s8 = reinterpret_cast<int8_t*>(out) + pix * s.cout_pad + n_tile * P.bn;
+            int32_t* out_s32 = reinterpret_cast<int32_t*>(out) + pix * s.cout_pad + n_tile * P.bn;
+            float* out_f32 = nullptr;
+            if (OUT == DT_F32_NCHW) {
+                const long img = pix / plane, inimg = pix - img * plane;
+                out_f32 = reinterpret_cast<float*>(out) + (img * s.cout + n_tile * P.bn) * plane + inimg;
+            }
+            for (int col0 = half * 16; col0 < P.bn; col0 += 32) {
                 int v[16];
-                __syncwarp();  // tcgen05.ld is warp-collective; rows skipped below must rejoin first
+                __syncwarp();  // tcgen05.ld is warp-collective
                 tmem_ld16(taddr + (uint32_t)col0, v);
+                tmem_wait_ld16(v);
                 const int c0 = n_tile * P.bn + col0;  // first global output channel of this chunk
                 if (!valid || c0 >= s.cout_pad) continue;
-                if (out_dtype == DT_S8_NHWC) {
+                if (OUT == DT_S32_NHWC) {
+                    int4* o = reinterpret_cast<int4*>(out_s32 + col0);
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) o[g] = make_int4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+                    continue;
+                }
+                float y[16];
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    const float4 si = *reinterpret_cast<const float4*>(s_si + col0 + g * 4);
+                    const float4 bi = *reinterpret_cast<const float4*>(s_bi + col0 + g * 4);
+                    const float sia[4] = {si.x, si.y, si.z, si.w}, bia[4] = {bi.x, bi.y, bi.z, bi.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float a = __int2float_rn(v[g * 4 + j]);
+                        const float t = BIAS ? __fmaf_rn(a, sia[j], bia[j]) : __fmul_rn(a, sia[j]);
+                        y[g * 4 + j] = activate_t<ACT>(t, ep.act_param0);
+                    }
+                }
+                if (OUT == DT_F32_NCHW) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (c0 + j < s.cout) out_f32[(long)(col0 + j) * plane] = y[j];
+                } else {
                     uint32_t wds[4];
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {
+                        const float4 so = *reinterpret_cast<const float4*>(s_so + col0 + g * 4);
+                        const float soa[4] = {so.x, so.y, so.z, so.w};
                         int qv[4];
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
-                            const int c = c0 + g * 4 + j;
-                            qv[j] = requant(v[g * 4 + j], __ldg(ep.scale_in + c), __ldg(ep.bias + c), __ldg(ep.scale_out + c), ep);
+                            const float t = __fmul_rn(y[g * 4 + j], soa[j]);
+                            if (ROUND == ROUND_HALF_AWAY) {
+                                qv[j] = float2int8(t, ROUND_HALF_AWAY);
+                            } else if (ACT == ACT_RELU || ACT == ACT_RELU6) {
+                                // t >= 0: copysign(0.5, t) is +0.5 (for t == -0 both forms truncate to 0)
+                                qv[j] = __float2int_rz(__fadd_rn(t, 0.5f));
+                            } else {
+                                // trunc(max(adj, -127.5)) == max(trunc(adj), -127); the upper clamp is the saturating pack
+                                qv[j] = __float2int_rz(fmaxf(__fadd_rn(t, copysignf(0.5f, t)), -127.5f));
+                            }
                         }
-                        wds[g] = pack4(qv[0], qv[1], qv[2], qv[3]);
+                        wds[g] = pack_sat_s8x4(qv[0], qv[1], qv[2], qv[3]);
                     }
-                    *reinterpret_cast<uint4*>(reinterpret_cast<int8_t*>(out) + pix * s.cout_pad + c0) =
-                        make_uint4(wds[0], wds[1], wds[2], wds[3]);
-                } else if (out_dtype == DT_F32_NCHW) {
-                    const long img = pix / plane, inimg = pix - img * plane;
-                    float* o = reinterpret_cast<float*>(out) + (img * s.cout) * plane + inimg;
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int c = c0 + j;
-                        if (c < s.cout) o[(long)c * plane] = dequant_act(v[j], __ldg(ep.scale_in + c), __ldg(ep.bias + c), ep);
-                    }
-                } else {  // DT_S32_NHWC
-                    int4* o = reinterpret_cast<int4*>(reinterpret_cast<int32_t*>(out) + pix * s.cout_pad + c0);
-#pragma unroll
-                    for (int g = 0; g < 4; ++g) o[g] = make_int4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+                    *reinterpret_cast<uint4*>(out_s8 + col0) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
                 }
             }
             tc_fence_before();
@@ -353,6 +418,22 @@ CUtensorMapSwizzle swizzle_for(int bkc) {
     return bkc == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (bkc == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
 }
 
+template <int OUT, int ACT, bool BIAS, int ROUND>
+const char* launch_variant(cudaStream_t stream, int grid, const CUtensorMap& tmA, const CUtensorMap& tmB, const UmmaPlan& p,
+                           const ConvShape& s, const EpilogueParams& ep, void* out, uint32_t* status) {
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    auto kernel = dense_umma_kernel<OUT, ACT, BIAS, ROUND>;
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
+            return "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed";
+        attr_set[dev] = true;
+    }
+    kernel<<<grid, kThreads, p.smem_bytes, stream>>>(tmA, tmB, p, s, ep, out, status);
+    return nullptr;
+}
+
 }  // namespace
 
 static int round_up(int a, int b) { return (a + b - 1) / b * b; }
@@ -370,7 +451,7 @@ bool umma_plan_layer(int cin, int cout, int kh, int kw, int sh, int sw, int dh, 
     // largest BN (multiple of 16, <= 256) whose weight panel leaves room for at least 3 A stages,
     // preferring a split of cout_pad into equal tiles
     const long a_stage = (long)kTileM * p.bkc;
-    const long avail = (long)smem_budget - 1024 /*alignment slack*/ - 256 /*barriers*/ - 3 * a_stage;
+    const long avail = (long)smem_budget - 1024 /*alignment slack*/ - 4096 /*barriers + epilogue parameters*/ - 3 * a_stage;
     if (avail <= 0) return false;
     long bn_max = avail / k_total;
     bn_max = bn_max > 256 ? 256 : bn_max;
@@ -380,7 +461,7 @@ bool umma_plan_layer(int cin, int cout, int kh, int kw, int sh, int sw, int dh, 
     p.bn = round_up((cout_pad + p.n_tiles - 1) / p.n_tiles, 16);
     if (p.bkc == 32) p.bn = round_up(p.bn, 32);  // keeps every weight tile on a 1 KiB boundary
     if (p.bn > 256 || (long)p.bn * k_total > avail) return false;
-    const long left = (long)smem_budget - 1024 - 256 - (long)p.bn * k_total;
+    const long left = (long)smem_budget - 1024 - 4096 - (long)p.bn * k_total;
     p.stages = (int)(left / a_stage);
     if (p.stages > 8) p.stages = 8;
     if (p.stages < 2) return false;
@@ -462,20 +543,33 @@ const char* launch_dense_umma(cudaStream_t stream, int sm_count, const UmmaPlan&
     }
     if (r != CUDA_SUCCESS) return "cuTensorMapEncodeTiled(activations) failed";
 
-    static bool attr_set[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        if (cudaFuncSetAttribute(dense_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
-            return "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed";
-        attr_set[dev] = true;
-    }
     int per_n = sm_count / p.n_tiles;
     if (per_n < 1) per_n = 1;
     if (per_n > p.m_tiles) per_n = p.m_tiles;
     const int grid = per_n * p.n_tiles;
-    dense_umma_kernel<<<grid, kThreads, p.smem_bytes, stream>>>(tmA, *reinterpret_cast<const CUtensorMap*>(weight_map), p, s, ep,
-                                                               out, out_dtype, status);
+    const CUtensorMap& tmB = *reinterpret_cast<const CUtensorMap*>(weight_map);
+    const char* err = nullptr;
+#define OTT_UMMA_LAUNCH(OUT, ACT, BIAS, ROUND) \
+    err = launch_variant<OUT, ACT, BIAS, ROUND>(stream, grid, tmA, tmB, p, s, ep, out, status)
+#define OTT_UMMA_ACT(OUT, BIAS, ROUND)                                   \
+    switch (ep.act_type) {                                               \
+        case ACT_RELU: OTT_UMMA_LAUNCH(OUT, ACT_RELU, BIAS, ROUND); break;   \
+        case ACT_LRELU: OTT_UMMA_LAUNCH(OUT, ACT_LRELU, BIAS, ROUND); break; \
+        case ACT_RELU6: OTT_UMMA_LAUNCH(OUT, ACT_RELU6, BIAS, ROUND); break; \
+        default: OTT_UMMA_LAUNCH(OUT, ACT_NONE, BIAS, ROUND); break;         \
+    }
+    if (out_dtype == DT_S32_NHWC) {
+        OTT_UMMA_LAUNCH(DT_S32_NHWC, ACT_NONE, false, ROUND_ADD_HALF_TRUNC);
+    } else if (out_dtype == DT_F32_NCHW) {
+        if (ep.has_bias) { OTT_UMMA_ACT(DT_F32_NCHW, true, ROUND_ADD_HALF_TRUNC) } else { OTT_UMMA_ACT(DT_F32_NCHW, false, ROUND_ADD_HALF_TRUNC) }
+    } else if (ep.rounding == ROUND_HALF_AWAY) {
+        if (ep.has_bias) { OTT_UMMA_ACT(DT_S8_NHWC, true, ROUND_HALF_AWAY) } else { OTT_UMMA_ACT(DT_S8_NHWC, false, ROUND_HALF_AWAY) }
+    } else {
+        if (ep.has_bias) { OTT_UMMA_ACT(DT_S8_NHWC, true, ROUND_ADD_HALF_TRUNC) } else { OTT_UMMA_ACT(DT_S8_NHWC, false, ROUND_ADD_HALF_TRUNC) }
+    }
+#undef OTT_UMMA_ACT
+#undef OTT_UMMA_LAUNCH
+    if (err) return err;
     return cudaGetLastError() == cudaSuccess ? nullptr : "dense_umma_kernel launch failed";
 }
 
