@@ -19,6 +19,7 @@ struct ott_conv {
     int n_in_scales = 0;
     // device state, owned (allocated from the context's allocator)
     int8_t* w_dev = nullptr;
+    uint32_t* w_tiled_dev = nullptr;  // depthwise only: filter rows packed for the tiled kernel
     float* scale_in_dev = nullptr;
     float* bias_dev = nullptr;
     float* scale_out_dev = nullptr;
@@ -308,6 +309,12 @@ int ott_conv_int8_create(ott_ctx* ctx, const ott_conv_desc* d, const int8_t* w_o
         }
     }
     rc = upload(ctx, wpacked.data(), wpacked.size(), (void**)&c->w_dev);
+    std::vector<uint32_t> wtiled;
+    if (rc == OTT_OK && depthwise && d->kh == d->kw && (d->kh == 3 || d->kh == 5)) {
+        wtiled.resize((size_t)c->cout_pad * depthwise_tiled_weight_words(d->kh));
+        depthwise_tiled_pack_weights(w_oihw, d->cout, c->cout_pad, d->kh, wtiled.data());
+        rc = upload(ctx, wtiled.data(), wtiled.size() * 4, (void**)&c->w_tiled_dev);
+    }
     if (rc == OTT_OK) rc = upload(ctx, scale_in.data(), sizeof(float) * c->cout_pad, (void**)&c->scale_in_dev);
     if (rc == OTT_OK) rc = upload(ctx, bias_p.data(), sizeof(float) * c->cout_pad, (void**)&c->bias_dev);
     if (rc == OTT_OK) rc = upload(ctx, scale_out.data(), sizeof(float) * c->cout_pad, (void**)&c->scale_out_dev);
@@ -330,6 +337,7 @@ int ott_conv_int8_destroy(ott_ctx* ctx, ott_conv* c) {
     if (!c) return OTT_OK;
     if (ctx) {
         ctx->alloc->free(c->w_dev);
+        ctx->alloc->free(c->w_tiled_dev);
         ctx->alloc->free(c->scale_in_dev);
         ctx->alloc->free(c->bias_dev);
         ctx->alloc->free(c->scale_out_dev);
@@ -373,6 +381,14 @@ int ott_conv_int8_forward(ott_ctx* ctx, const ott_conv* c, const void* in_dev, i
     ep.has_bias = d.bias_term ? 1 : 0;
     ep.act_type = d.act_type; ep.act_param0 = d.act_param0; ep.rounding = d.rounding;
 
+    uint32_t* status = status_word_dev ? status_word_dev : ctx->status_dev;
+    if (c->kind == OTT_KERNEL_DEPTHWISE && c->w_tiled_dev && depthwise_tiled_supports(s, out_dtype)) {
+        // one pass over HBM: quantize (when the input is fp32), depthwise and epilogue in the same kernel
+        OTT_CUDA_CHECK(ctx, launch_depthwise_tiled(ctx->stream, s, in_dev, in_dtype, c->w_tiled_dev, c->in_scales_dev, c->n_in_scales, ep,
+                                                    out_dev, out_dtype));
+        ctx->launches += 1;
+        return OTT_OK;
+    }
     DeviceBlock xq;  // scratch: the quantized activations when the input arrives as fp32
     const int8_t* x = static_cast<const int8_t*>(in_dev);
     if (in_dtype == OTT_F32_NCHW) {
@@ -385,7 +401,6 @@ int ott_conv_int8_forward(ott_ctx* ctx, const ott_conv* c, const void* in_dev, i
         ctx->launches += 1;
         x = (const int8_t*)xq.p;
     }
-    uint32_t* status = status_word_dev ? status_word_dev : ctx->status_dev;
     switch (c->kind) {
         case OTT_KERNEL_DEPTHWISE:
             OTT_CUDA_CHECK(ctx, launch_depthwise(ctx->stream, s, x, c->w_dev, ep, out_dev, out_dtype));

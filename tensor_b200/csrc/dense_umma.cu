@@ -149,17 +149,6 @@ __device__ __forceinline__ void tmem_wait_ld16(int v[16]) {
                  : "memory");
 }
 
-// two s32 -> two saturated s8 in the low half of d, upper half taken from c (cvt.pack)
-__device__ __forceinline__ uint32_t pack_sat_s8x2(int hi, int lo, uint32_t c) {
-    uint32_t d;
-    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(hi), "r"(lo), "r"(c));
-    return d;
-}
-
-__device__ __forceinline__ uint32_t pack_sat_s8x4(int a, int b, int c, int d) {  // a -> byte 0
-    return pack_sat_s8x2(b, a, pack_sat_s8x2(d, c, 0));
-}
-
 struct SmemLayout {
     uint32_t b_panel, a_stages, bars, tmem_slot, abort_flag, params, total;
 };
@@ -371,11 +360,9 @@ dense_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                             if (ROUND == ROUND_HALF_AWAY) {
                                 qv[j] = float2int8(t, ROUND_HALF_AWAY);
                             } else if (ACT == ACT_RELU || ACT == ACT_RELU6) {
-                                // t >= 0: copysign(0.5, t) is +0.5 (for t == -0 both forms truncate to 0)
-                                qv[j] = __float2int_rz(__fadd_rn(t, 0.5f));
+                                qv[j] = f2i8_nonneg(t);
                             } else {
-                                // trunc(max(adj, -127.5)) == max(trunc(adj), -127); the upper clamp is the saturating pack
-                                qv[j] = __float2int_rz(fmaxf(__fadd_rn(t, copysignf(0.5f, t)), -127.5f));
+                                qv[j] = f2i8_lo_clamped(t);  // the upper clamp is the saturating pack
                             }
                         }
                         wds[g] = pack_sat_s8x4(qv[0], qv[1], qv[2], qv[3]);

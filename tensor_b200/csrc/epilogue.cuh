@@ -83,6 +83,45 @@ __device__ __forceinline__ int quantize1(float x, float scale, int rounding) {
     return float2int8(__fmul_rn(x, scale), rounding);
 }
 
+// ---- fast forms used by the hot loops (same results as the functions above) ----
+
+// two s32 -> two saturated s8 in the low half of d, upper half taken from c (cvt.pack)
+__device__ __forceinline__ uint32_t pack_sat_s8x2(int hi, int lo, uint32_t c) {
+    uint32_t d;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(hi), "r"(lo), "r"(c));
+    return d;
+}
+
+// four s32 -> four saturated s8, a in byte 0
+__device__ __forceinline__ uint32_t pack_sat_s8x4(int a, int b, int c, int d) {
+    return pack_sat_s8x2(b, a, pack_sat_s8x2(d, c, 0));
+}
+
+// float2int8 with rounding 0, clamped below at -127 only: trunc(max(adj, -127.5)) == max(trunc(adj), -127).
+// The clamp at +127 is left to pack_sat_s8x4.
+__device__ __forceinline__ int f2i8_lo_clamped(float v) {
+    return __float2int_rz(fmaxf(__fadd_rn(v, copysignf(0.5f, v)), -127.5f));
+}
+
+// the same for v >= 0 (after ReLU / ReLU6): copysign(0.5, v) is +0.5; v == -0 truncates to 0 either way
+__device__ __forceinline__ int f2i8_nonneg(float v) { return __float2int_rz(__fadd_rn(v, 0.5f)); }
+
+// quantize 4 floats with one scale (rounding 0) and pack them, x in byte 0
+__device__ __forceinline__ uint32_t quantize4_pack(float x, float y, float z, float w, float scale) {
+    return pack_sat_s8x4(f2i8_lo_clamped(__fmul_rn(x, scale)), f2i8_lo_clamped(__fmul_rn(y, scale)),
+                         f2i8_lo_clamped(__fmul_rn(z, scale)), f2i8_lo_clamped(__fmul_rn(w, scale)));
+}
+
+// 4x4 byte transpose: inputs are 4 words of 4 bytes; o[i] byte j = input j byte i
+__device__ __forceinline__ void transpose4x4(uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t o[4]) {
+    const uint32_t t0 = __byte_perm(a, b, 0x5140), t1 = __byte_perm(c, d, 0x5140);
+    const uint32_t t2 = __byte_perm(a, b, 0x7362), t3 = __byte_perm(c, d, 0x7362);
+    o[0] = __byte_perm(t0, t1, 0x5410);
+    o[1] = __byte_perm(t0, t1, 0x7632);
+    o[2] = __byte_perm(t2, t3, 0x5410);
+    o[3] = __byte_perm(t2, t3, 0x7632);
+}
+
 __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
     return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) | ((uint32_t)(d & 0xff) << 24);
 }

@@ -27,6 +27,14 @@ cudaError_t launch_quantize_nchw_to_nhwc(cudaStream_t stream, const float* x, in
 cudaError_t launch_depthwise(cudaStream_t stream, const ConvShape& s, const int8_t* x, const int8_t* w_taps,
                              const EpilogueParams& ep, void* out, int out_dtype);
 
+// Shared-memory tiled depthwise (3x3 / 5x5, stride 1 / 2, no dilation) with the quantize prologue fused:
+// x is fp32 NCHW (in_dtype DT_F32_NCHW) or int8 NHWC; weights packed by depthwise_tiled_pack_weights.
+bool depthwise_tiled_supports(const ConvShape& s, int out_dtype);
+int depthwise_tiled_weight_words(int k);  // 32-bit words per channel
+void depthwise_tiled_pack_weights(const int8_t* w_oihw, int c, int c_pad, int k, uint32_t* dst);
+cudaError_t launch_depthwise_tiled(cudaStream_t stream, const ConvShape& s, const void* x, int in_dtype, const uint32_t* wq,
+                                   const float* in_scales, int n_in_scales, const EpilogueParams& ep, void* out, int out_dtype);
+
 // Direct dense convolution on CUDA cores: x int8 NHWC; weights int8 [cout_pad][kh*kw][cin_pad].
 cudaError_t launch_dense_direct(cudaStream_t stream, const ConvShape& s, const int8_t* x, const int8_t* w_okc,
                                 const EpilogueParams& ep, void* out, int out_dtype);

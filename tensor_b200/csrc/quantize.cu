@@ -3,7 +3,8 @@
 // Net::convert_layout (Tensor/Net.cpp:380-411).
 //
 // HBM-bound: 4 bytes read + 1 byte written per element. Each CTA moves a [64 channels x 128 pixels] tile
-// of one image through shared memory: reads are float4 along W (the contiguous axis of NCHW), writes are
+// of one image: reads are float4 along W (the contiguous axis of NCHW), the channel/pixel transpose of
+// 4x4 blocks happens in registers, 32-bit words of 4 channels go through shared memory, and writes are
 // 16-byte groups of channels (the contiguous axis of NHWC).
 #include "kernels.h"
 
@@ -12,11 +13,16 @@ namespace ottk {
 constexpr int QT_C = 64;    // channels per tile
 constexpr int QT_P = 128;   // pixels per tile
 constexpr int QT_THREADS = 256;
+constexpr int QT_PITCH = 17;  // words per pixel row in shared memory (16 used): odd, so columns spread over banks
+
+// pixel p of the tile lives in row (p%4)*33 + p/4: the four pixels a thread produces from one float4 land in
+// four row groups, and the 32 lanes of a warp land in 32 consecutive rows of a group (no bank conflicts).
+__device__ __forceinline__ int qt_row(int p) { return (p & 3) * 33 + (p >> 2); }
 
 __global__ void __launch_bounds__(QT_THREADS)
 quantize_nchw_to_nhwc_kernel(const float* __restrict__ x, int8_t* __restrict__ out, const float* __restrict__ scales,
                              int n_scales, int c, int cpad, int hw, int tiles_p, int tiles_c, int rounding) {
-    __shared__ __align__(16) int8_t tile[QT_P][QT_C + 16];  // +16 keeps rows 16-byte aligned and spreads banks
+    __shared__ uint32_t tile[4 * 33 * QT_PITCH];
     const long tile_id = blockIdx.x;
     const int tc = (int)(tile_id % tiles_c);
     const int tp = (int)((tile_id / tiles_c) % tiles_p);
@@ -24,41 +30,56 @@ quantize_nchw_to_nhwc_kernel(const float* __restrict__ x, int8_t* __restrict__ o
     const int c0 = tc * QT_C, p0 = tp * QT_P;
     const float* src = x + (long)img * c * hw;
 
-    // phase 1: each warp takes channels, each lane 4 consecutive pixels
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // phase 1: a thread quantizes 4 consecutive pixels of 4 consecutive channels and packs, per pixel, the
+    // 4 channels into one word. Lanes run along pixels (512 contiguous bytes per channel row per warp).
+    const int pq = threadIdx.x & 31, cq = threadIdx.x >> 5;
     const bool vec_ok = (hw % 4 == 0);
-    for (int ch = warp; ch < QT_C; ch += QT_THREADS / 32) {
-        const int cg = c0 + ch;
-        const int p = p0 + lane * 4;
-        int q[4] = {0, 0, 0, 0};
-        if (cg < c) {
-            const float s = n_scales == 1 ? scales[0] : scales[cg];
-            const float* row = src + (long)cg * hw;
-            if (vec_ok && p + 3 < hw) {
-                const float4 v = __ldg(reinterpret_cast<const float4*>(row + p));
-                q[0] = quantize1(v.x, s, rounding);
-                q[1] = quantize1(v.y, s, rounding);
-                q[2] = quantize1(v.z, s, rounding);
-                q[3] = quantize1(v.w, s, rounding);
-            } else {
+    const int p = p0 + pq * 4;
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
-                    if (p + j < hw) q[j] = quantize1(__ldg(row + p + j), s, rounding);
+    for (int pass = 0; pass < QT_C / 32; ++pass) {
+        const int cword = cq + 8 * pass;
+        uint32_t cw[4];  // channel i: its 4 pixels packed
+        float4 v[4];
+        float sc[4];
+        const bool fast = vec_ok && p + 3 < hw && c0 + cword * 4 + 3 < c && rounding == ROUND_ADD_HALF_TRUNC;
+        if (fast) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int cg = c0 + cword * 4 + i;
+                sc[i] = n_scales == 1 ? __ldg(scales) : __ldg(scales + cg);
+                v[i] = __ldg(reinterpret_cast<const float4*>(src + (long)cg * hw + p));
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) cw[i] = quantize4_pack(v[i].x, v[i].y, v[i].z, v[i].w, sc[i]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int cg = c0 + cword * 4 + i;
+                int q[4] = {0, 0, 0, 0};
+                if (cg < c) {
+                    const float s = n_scales == 1 ? __ldg(scales) : __ldg(scales + cg);
+                    const float* row = src + (long)cg * hw;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        if (p + j < hw) q[j] = quantize1(__ldg(row + p + j), s, rounding);
+                }
+                cw[i] = pack4(q[0], q[1], q[2], q[3]);
             }
         }
+        uint32_t pw[4];  // pixel j: its 4 channels packed
+        transpose4x4(cw[0], cw[1], cw[2], cw[3], pw);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) tile[lane * 4 + j][ch] = (int8_t)q[j];
+        for (int j = 0; j < 4; ++j) tile[(j * 33 + pq) * QT_PITCH + cword] = pw[j];
     }
     __syncthreads();
-    // phase 2: 16-byte channel groups, consecutive threads -> consecutive groups of one pixel
-    const int groups = QT_C / 16;
+    // phase 2: 16-byte channel groups; consecutive threads -> consecutive groups of one pixel
     int8_t* dst = out + (long)img * hw * cpad;
-    for (int i = threadIdx.x; i < QT_P * groups; i += QT_THREADS) {
-        const int pl = i / groups, g = i % groups;
-        const int p = p0 + pl, cg = c0 + g * 16;
-        if (p < hw && cg < cpad) {
-            const uint4 v = *reinterpret_cast<const uint4*>(&tile[pl][g * 16]);
-            *reinterpret_cast<uint4*>(dst + (long)p * cpad + cg) = v;
+    for (int i = threadIdx.x; i < QT_P * (QT_C / 16); i += QT_THREADS) {
+        const int pl = i >> 2, g = i & 3;
+        const int pg = p0 + pl, cg = c0 + g * 16;
+        if (pg < hw && cg < cpad) {
+            const uint32_t* r = tile + qt_row(pl) * QT_PITCH + g * 4;
+            *reinterpret_cast<uint4*>(dst + (long)pg * cpad + cg) = make_uint4(r[0], r[1], r[2], r[3]);
         }
     }
 }

@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 
 from cases import small_cases
-from support import GOLDEN_DIR, ACT_RELU, ACT_RELU6, ConvCase, rounding_for, run_port
+from support import GOLDEN_DIR, ACT_LRELU, ACT_RELU, ACT_RELU6, ConvCase, rounding_for, run_port
 
 pytestmark = pytest.mark.gpu
 
@@ -65,6 +65,12 @@ def test_batched_equals_single_images(ctx):
     ("many_tiles_pw", dict(cin=64, cout=256, k=1, n=6, h=56, w=56, int8_scale_term=101, act_type=ACT_RELU6)),
     ("many_tiles_3x3", dict(cin=64, cout=64, k=3, pad=1, n=4, h=56, w=56, int8_scale_term=2)),
     ("many_tiles_dw", dict(cin=256, cout=256, k=3, pad=1, groups=256, n=4, h=56, w=56, int8_scale_term=101, act_type=ACT_RELU, w_std=0.1)),
+    ("dw_tiles_xy_f32in", dict(cin=40, cout=40, k=3, pad=1, groups=40, n=2, h=37, w=75, int8_scale_term=101, act_type=ACT_RELU, w_std=0.1)),
+    ("dw_tiles_xy_s8in", dict(cin=72, cout=72, k=3, pad=1, groups=72, n=2, h=30, w=70, int8_scale_term=101, act_type=ACT_RELU6, w_std=0.1, s8_input=True)),
+    ("dw_s2_tiles_f32out", dict(cin=48, cout=48, k=3, stride=2, pad=1, groups=48, n=1, h=45, w=83, int8_scale_term=1, w_std=0.1)),
+    ("dw5_s1_tiles", dict(cin=96, cout=96, k=5, pad=2, groups=96, n=2, h=40, w=40, int8_scale_term=101, act_type=ACT_LRELU, act_param0=0.1, w_std=0.1, s8_input=True)),
+    ("dw5_s2_tiles_w_odd", dict(cin=32, cout=32, k=5, stride=2, pad=2, groups=32, n=1, h=41, w=77, int8_scale_term=101, w_std=0.1)),
+    ("dw_nopad", dict(cin=32, cout=32, k=3, pad=0, groups=32, n=1, h=20, w=24, int8_scale_term=101, act_type=ACT_RELU, w_std=0.1)),
     ("two_n_tiles", dict(cin=256, cout=512, k=1, n=3, h=28, w=28, int8_scale_term=101, act_type=ACT_RELU6)),
     ("four_n_tiles", dict(cin=512, cout=1024, k=1, n=2, h=14, w=14, int8_scale_term=101, act_type=ACT_RELU6)),
 ])
