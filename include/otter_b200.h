@@ -135,6 +135,27 @@ int ott_conv_int8_forward(ott_ctx* ctx, const ott_conv* conv, const void* in_dev
 int ott_conv_int8_forward_host(ott_ctx* ctx, const ott_conv* conv, const void* in_host, int in_dtype, int n, int h,
                                int w, void* out_host, int out_dtype);
 
+/* The forward for hosts that may not allocate device memory while running. No counterpart in the
+ * reference (its CPU path simply calls otter::empty for every temporary).
+ * Who needs it: a process whose device memory was divided into fixed pools at start-up and must not grow
+ * afterwards, or a loop with a hard latency bound that cannot absorb the device-wide synchronisation a
+ * cudaMalloc or cudaFree implies. ott_conv_int8_forward can end in cudaMalloc the first time it sees a new
+ * size, because it takes the buffer for the quantized activations from the context's allocator. This
+ * variant does the same work (quantize fp32 NCHW input, then the layer's convolution kernel) but keeps
+ * that buffer in a fixed array of OTT_NOALLOC_SCRATCH_BYTES that is part of the library image on every GPU
+ * that loads it, for the life of the process. It calls no cudaMalloc, cudaFree or allocating routine.
+ *   - Input is fp32 NCHW on the device; output as for ott_conv_int8_forward; the caller owns both.
+ *   - n*h*w*ott_nhwc_channels(cin) must fit OTT_NOALLOC_SCRATCH_BYTES; larger calls fail with
+ *     OTT_ERR_INVALID and a message naming both sizes (split the batch, or use the ordinary forward).
+ *   - The first call on each GPU looks up the array's device address (cudaGetSymbolAddress); make that
+ *     first call before starting any stream capture.
+ *   - All calls on one GPU share the one array. It keeps whatever the last call left; this entry point
+ *     overwrites every byte it later reads, so nothing has to be cleared. Two calls whose kernels can be
+ *     in flight on the same GPU at once (different contexts or streams) race on it: serialise them. */
+#define OTT_NOALLOC_SCRATCH_BYTES (32u << 20)
+int ott_conv_int8_forward_noalloc(ott_ctx* ctx, const ott_conv* conv, const float* in_f32_nchw_dev, int n, int h, int w,
+                                  void* out_dev, int out_dtype);
+
 /* number of kernels this library launched on ctx since creation (for benchmark bookkeeping) */
 uint64_t ott_launch_count(const ott_ctx* ctx);
 

@@ -1,0 +1,24 @@
+// Device-side state of one quantized ConvolutionLayer (the object behind the opaque ott_conv handle).
+#pragma once
+
+#include <cstdint>
+
+#include "../../include/otter_b200.h"
+#include "dense_umma.h"
+
+struct ott_conv {
+    ott_conv_desc d{};
+    int kind = 0;
+    bool depthwise = false;
+    int cin_pad = 0, cout_pad = 0;
+    int n_in_scales = 0;
+    // device state, owned (allocated from the context's allocator)
+    int8_t* w_dev = nullptr;
+    uint32_t* w_tiled_dev = nullptr;  // depthwise only: filter rows packed for the tiled kernel
+    float* scale_in_dev = nullptr;
+    float* bias_dev = nullptr;
+    float* scale_out_dev = nullptr;
+    float* in_scales_dev = nullptr;
+    ottk::UmmaPlan plan{};
+    alignas(128) unsigned char weight_map[128];
+};
