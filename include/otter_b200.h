@@ -135,6 +135,27 @@ int ott_conv_int8_forward(ott_ctx* ctx, const ott_conv* conv, const void* in_dev
 int ott_conv_int8_forward_host(ott_ctx* ctx, const ott_conv* conv, const void* in_host, int in_dtype, int n, int h,
                                int w, void* out_host, int out_dtype);
 
+/* ---- fp32 glue layers of the benchmark graphs (device fp32 NCHW tensors, asynchronous on the stream) ---- */
+
+/* dst[b][dst_c0 + j*dst_cstride][:] = src[b][src_c0 + j*src_cstride][:] for j < count, b < n; hw = H*W.
+ * One primitive for Concat along channels (Tensor/ConcatLayer.cpp:55-70), Crop along channels
+ * (Tensor/CropLayer.cpp:67-75 -> native::slice) and ChannelShuffle (Tensor/ChannelShuffleLayer.cpp:37-41:
+ * output channel i*g + k is input channel k*(C/g) + i, i.e. g strided copies). */
+int ott_copy_channels_f32(ott_ctx* ctx, const float* src, int src_channels, int src_c0, int src_cstride, float* dst,
+                          int dst_channels, int dst_c0, int dst_cstride, int count, int n, int hw);
+
+/* MaxPoolLayer::forward (Tensor/MaxPoolLayer.cpp:123-133 -> otter::max_pool2d, Tensor/Pool.cpp:1166-1201), no
+ * dilation, floor mode. pad_with_zero = 1 reproduces the reference's packed 3x3 stride-2 kernels, which pad the
+ * input with zeros (Tensor/Pool.cpp:972-975, :807-810); 0 reproduces its plain kernel (padding never wins). */
+int ott_maxpool_f32_nchw(ott_ctx* ctx, const float* in, int n, int c, int h, int w, int kh, int kw, int sh, int sw, int ph,
+                         int pw, int pad_with_zero, float* out);
+
+/* ShortCutLayer: out = a + b (Tensor/ShortCutLayer.cpp) */
+int ott_add_f32(ott_ctx* ctx, const float* a, const float* b, float* out, size_t count);
+
+/* stand-alone ReluLayer / LReluLayer / Relu6Layer, in place (act_type as in ott_conv_desc) */
+int ott_activation_f32(ott_ctx* ctx, float* x, size_t count, int act_type, float param0);
+
 /* The forward for hosts that may not allocate device memory while running. No counterpart in the
  * reference (its CPU path simply calls otter::empty for every temporary).
  * Who needs it: a process whose device memory was divided into fixed pools at start-up and must not grow

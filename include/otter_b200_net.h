@@ -1,0 +1,60 @@
+/* otter_b200 — C-ABI over the host-side graph runtime (tensor_b200/host: the C++17 mirror of the reference's
+ * Net / Layer / Extractor API). It exists so that hosts without a C++ toolchain — the Python tests and the
+ * benchmark here — can build a Net from the reference's own LayerOption key/value pairs and run it.
+ * C++ hosts use tensor_b200/host/otter_api.hpp directly. Status codes as in otter_b200.h.
+ */
+#ifndef OTTER_B200_NET_H
+#define OTTER_B200_NET_H
+
+#include "otter_b200.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+typedef struct ott_net ott_net;
+
+/* Net::Net + NetOption::device (Tensor/Net.hpp:22-27) */
+int ott_net_create(int device, ott_net** out);
+int ott_net_destroy(ott_net* net);
+const char* ott_net_last_error(const ott_net* net);
+ott_ctx* ott_net_context(ott_net* net); /* valid after ott_net_compile */
+
+/* Net::addLayer (Tensor/Net.cpp:40-80). `options` is one LayerOption as "key=value;key=value;...", with the
+ * keys of the .otter format (type, name, input, output, and the layer's own parameters: out_channels, kernel_h,
+ * stride, int8_scale_term, activation, groups, axis, start, end, ...). */
+int ott_net_add_layer(ott_net* net, const char* options);
+
+/* Net::compile(CompileMode::Initial) (Tensor/Net.cpp:174-280): builds the graph (automatic Split layers for
+ * fan-out), creates the layers, infers shapes, gives every layer random parameters and builds its pipeline. */
+int ott_net_compile(ott_net* net);
+
+int ott_net_layer_count(const ott_net* net);
+/* type and name of layer i; for Convolution layers geom = {cin, cout, kh, kw, sh, sw, ph, pw, groups, bias_term,
+ * int8_scale_term, activation_type}, else zeros */
+int ott_net_layer_info(const ott_net* net, int i, char* type, int type_cap, char* name, int name_cap, int geom[12]);
+int ott_net_blob_shape(const ott_net* net, const char* blob, int shape[4]);
+
+/* Replace a Convolution layer's parameters (the public fields weight_data, bias_data, weight_data_int8_scales,
+ * bottom_blob_int8_scales, top_blob_int8_scales of Tensor/ConvolutionLayer.hpp:62-77) and rebuild its pipeline. */
+int ott_net_set_conv_params(ott_net* net, const char* layer, const int8_t* w_oihw, const float* bias, const float* w_scales,
+                            const float* in_scales, int n_in_scales, const float* out_scales, int n_out_scales);
+
+/* Extractor::input + Extractor::extract (Tensor/Net.cpp:686-736) for one input blob and n_out output blobs.
+ * in: fp32 NCHW, on the host (in_on_device = 0; copied to the GPU) or already on the GPU (1).
+ * out_host[i]: NULL = only compute the blob; else a host buffer that receives the blob in the reference's plain
+ * layout (fp32 NCHW, or int8 NCHW for int8 blobs) after the stream has been synchronised.
+ * With every out_host NULL the call is asynchronous on the Net's stream. */
+int ott_net_forward(ott_net* net, const char* input_blob, const void* in, int in_on_device, int n, int c, int h, int w,
+                    int n_out, const char* const* out_blobs, void* const* out_host);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* OTTER_B200_NET_H */

@@ -22,6 +22,7 @@
 #include "NetOption.hpp"
 
 #include <chrono>
+#include <memory>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -268,4 +269,59 @@ REF_API int ref_requantize(const int32_t* acc, int c, int h, int w, const float*
         std::memcpy(out, y.raw_data(), (size_t)c * h * w);
         return 0;
     } catch (const std::exception& e) { g_err = e.what(); return -2; } catch (...) { g_err = "unknown"; return -4; }
+}
+
+// Any fp32 layer of the reference by its registry name ("MaxPool", "Concat", "Crop", "ChannelShuffle", "ShortCut",
+// "Relu", "LRelu", "Relu6", ...), driven the way Net::compile / do_forward_layer drive it (Tensor/Net.cpp:196-273,
+// :413-505). options = "key=value;key=value". Inputs and the output are fp32 NCHW with batch 1.
+// shapes: 4 ints per input. out_shape receives 4 ints. out may be NULL to query the shape only.
+#include "LayerRegistry.hpp"
+REF_API int ref_layer_forward(const char* type, const char* options, int n_in, const float* const* ins, const int* shapes,
+                              int packed, float* out, int* out_shape) {
+    try {
+        otter::Layer* layer = otter::LayerRegistry::CreateLayer(type);
+        std::unique_ptr<otter::Layer> guard(layer);
+        otter::LayerOption option;
+        std::string s(options ? options : "");
+        size_t pos = 0;
+        while (pos < s.size()) {
+            size_t end = s.find(';', pos);
+            if (end == std::string::npos) end = s.size();
+            const std::string item = s.substr(pos, end - pos);
+            const size_t eq = item.find('=');
+            if (eq != std::string::npos) option[item.substr(0, eq)] = item.substr(eq + 1);
+            pos = end + 1;
+        }
+        otter::NetOption opt;
+        opt.use_packing_layout = packed != 0;
+        otter::ParamDict pd;
+        layer->parse_param(option, pd);
+        layer->bottom_shapes.clear();
+        for (int i = 0; i < n_in; ++i)
+            layer->bottom_shapes.push_back(otter::tensor({shapes[4 * i], shapes[4 * i + 1], shapes[4 * i + 2], shapes[4 * i + 3]}, otter::ScalarType::Int).view({1, -1}));
+        layer->compute_output_shape(pd);
+        layer->load_param(pd);
+        layer->create_pipeline(opt);
+        std::vector<otter::Tensor> bottoms;
+        for (int i = 0; i < n_in; ++i) {
+            otter::Tensor t = otter::from_blob((void*)ins[i], {shapes[4 * i], shapes[4 * i + 1], shapes[4 * i + 2], shapes[4 * i + 3]}, otter::ScalarType::Float).clone();
+            if (packed && layer->support_packing) t = to_layer_layout(t, true, false);
+            bottoms.push_back(t);
+        }
+        otter::Tensor top;
+        int rc;
+        if (layer->one_blob_only) {
+            if (layer->support_inplace) { top = bottoms[0]; rc = layer->forward_inplace(top, opt); }
+            else rc = layer->forward(bottoms[0], top, opt);
+        } else {
+            std::vector<otter::Tensor> tops(1);
+            rc = layer->forward(bottoms, tops, opt);
+            top = tops[0];
+        }
+        if (rc != 0) { g_err = "layer forward failed"; return rc; }
+        otter::Tensor t1 = top.packing(1).contiguous();
+        for (int i = 0; i < 4; ++i) out_shape[i] = (int)t1.size(i);
+        if (out) std::memcpy(out, t1.raw_data(), (size_t)t1.numel() * 4);
+        return 0;
+    } catch (const std::exception& e) { g_err = e.what(); return -2; } catch (const char* s) { g_err = s; return -3; } catch (...) { g_err = "unknown"; return -4; }
 }

@@ -58,6 +58,22 @@ SIGNATURES = {
     "ott_conv_int8_forward_host": (i32, [vp, vp, vp, i32, i32, i32, i32, vp, i32]),
     "ott_conv_int8_forward_noalloc": (i32, [vp, vp, vp, i32, i32, i32, vp, i32]),
     "ott_launch_count": (C.c_uint64, [vp]),
+    "ott_copy_channels_f32": (i32, [vp, vp, i32, i32, i32, vp, i32, i32, i32, i32, i32, i32]),
+    "ott_maxpool_f32_nchw": (i32, [vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp]),
+    "ott_add_f32": (i32, [vp, vp, vp, vp, sz]),
+    "ott_activation_f32": (i32, [vp, vp, sz, i32, C.c_float]),
+    # include/otter_b200_net.h
+    "ott_net_create": (i32, [i32, C.POINTER(vp)]),
+    "ott_net_destroy": (i32, [vp]),
+    "ott_net_last_error": (C.c_char_p, [vp]),
+    "ott_net_context": (vp, [vp]),
+    "ott_net_add_layer": (i32, [vp, C.c_char_p]),
+    "ott_net_compile": (i32, [vp]),
+    "ott_net_layer_count": (i32, [vp]),
+    "ott_net_layer_info": (i32, [vp, i32, C.c_char_p, i32, C.c_char_p, i32, C.POINTER(i32)]),
+    "ott_net_blob_shape": (i32, [vp, C.c_char_p, C.POINTER(i32)]),
+    "ott_net_set_conv_params": (i32, [vp, C.c_char_p, vp, vp, vp, vp, i32, vp, i32]),
+    "ott_net_forward": (i32, [vp, C.c_char_p, vp, i32, i32, i32, i32, i32, i32, C.POINTER(C.c_char_p), C.POINTER(vp)]),
 }
 
 _lib = None

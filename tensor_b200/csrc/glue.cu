@@ -1,0 +1,129 @@
+// The fp32 glue layers between the int8 convolutions of the benchmark graphs, as small bandwidth-bound
+// CUDA kernels on the Net's stream: channel-plane copies (Concat, Crop, ChannelShuffle), MaxPool,
+// element-wise add (ShortCut) and the stand-alone activations. All tensors are fp32 NCHW on the device.
+// Reference: Tensor/ConcatLayer.cpp:55-70, Tensor/CropLayer.cpp:67-75, Tensor/ChannelShuffleLayer.cpp:37-41,
+// Tensor/MaxPoolLayer.cpp:123-133 + Tensor/Pool.cpp:1166-1201, Tensor/ShortCutLayer.cpp, Tensor/ReluLayer.cpp,
+// Tensor/LReluLayer.cpp, Tensor/Relu6Layer.cpp.
+#include "ctx.h"
+
+namespace {
+
+// dst[b][dst_c0 + j*dst_cs][p] = src[b][src_c0 + j*src_cs][p], j < count, p < hw
+template <typename V>
+__global__ void copy_channels_kernel(const V* __restrict__ src, V* __restrict__ dst, int src_channels, int src_c0, int src_cs,
+                                     int dst_channels, int dst_c0, int dst_cs, int count, long hwv, long total) {
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const long p = i % hwv;
+        const long r = i / hwv;
+        const int j = (int)(r % count);
+        const long b = r / count;
+        dst[(b * dst_channels + dst_c0 + (long)j * dst_cs) * hwv + p] = __ldg(src + (b * src_channels + src_c0 + (long)j * src_cs) * hwv + p);
+    }
+}
+
+// pad_zero: out-of-image taps count as 0 (the reference's packed 3x3 s2 path pads the input with zeros,
+// Tensor/Pool.cpp:972-975); otherwise they are ignored (its plain path, -inf padding).
+__global__ void maxpool_kernel(const float* __restrict__ x, float* __restrict__ y, int c, int h, int w, int oh, int ow, int kh,
+                               int kw, int sh, int sw, int ph, int pw, int pad_zero, long total) {
+    const long i = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int ox = (int)(i % ow);
+    long r = i / ow;
+    const int oy = (int)(r % oh);
+    const long plane = r / oh;  // b*c + ch
+    const float* xp = x + plane * h * w;
+    float m = -INFINITY;
+    for (int ky = 0; ky < kh; ++ky) {
+        const int iy = oy * sh - ph + ky;
+        for (int kx = 0; kx < kw; ++kx) {
+            const int ix = ox * sw - pw + kx;
+            const bool in = iy >= 0 && iy < h && ix >= 0 && ix < w;
+            if (in) m = fmaxf(m, __ldg(xp + (long)iy * w + ix));
+            else if (pad_zero) m = fmaxf(m, 0.f);
+        }
+    }
+    y[i] = m;
+}
+
+__global__ void add_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ o, long n) {
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) o[i] = __fadd_rn(a[i], b[i]);
+}
+
+__global__ void activation_kernel(float* __restrict__ x, long n, int act, float p0) {
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
+        float v = x[i];
+        if (act == 1) v = v > 0.f ? v : 0.f;
+        else if (act == 2) v = v < 0.f ? __fmul_rn(v, p0) : v;
+        else if (act == 3) v = fminf(fmaxf(v, 0.f), 6.f);
+        x[i] = v;
+    }
+}
+
+unsigned grid_for(const ott_ctx* ctx, long total, int block) {
+    long g = (total + block - 1) / block;
+    const long cap = (long)ctx->sm_count * 16;
+    return (unsigned)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+}  // namespace
+
+extern "C" {
+
+int ott_copy_channels_f32(ott_ctx* ctx, const float* src, int src_channels, int src_c0, int src_cstride, float* dst, int dst_channels,
+                          int dst_c0, int dst_cstride, int count, int n, int hw) {
+    if (!ctx || !src || !dst || count < 0 || n < 0 || hw < 0) return OTT_ERR_INVALID;
+    if (src_c0 < 0 || dst_c0 < 0 || (count > 0 && (src_c0 + (long)(count - 1) * src_cstride >= src_channels ||
+                                                   dst_c0 + (long)(count - 1) * dst_cstride >= dst_channels)))
+        return ctx->fail(OTT_ERR_INVALID, "channel range outside the tensor");
+    const long total = (long)n * count * hw;
+    if (total == 0) return OTT_OK;
+    cudaSetDevice(ctx->device);
+    const bool vec = hw % 4 == 0 && ((uintptr_t)src % 16 == 0) && ((uintptr_t)dst % 16 == 0);
+    if (vec) {
+        const long tv = total / 4;
+        copy_channels_kernel<float4><<<grid_for(ctx, tv, 256), 256, 0, ctx->stream>>>(
+            reinterpret_cast<const float4*>(src), reinterpret_cast<float4*>(dst), src_channels, src_c0, src_cstride, dst_channels, dst_c0,
+            dst_cstride, count, hw / 4, tv);
+    } else {
+        copy_channels_kernel<float><<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(src, dst, src_channels, src_c0, src_cstride,
+                                                                                      dst_channels, dst_c0, dst_cstride, count, hw, total);
+    }
+    OTT_CUDA_CHECK(ctx, cudaGetLastError());
+    ctx->launches += 1;
+    return OTT_OK;
+}
+
+int ott_maxpool_f32_nchw(ott_ctx* ctx, const float* in, int n, int c, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw,
+                         int pad_with_zero, float* out) {
+    if (!ctx || !in || !out || kh <= 0 || kw <= 0 || sh <= 0 || sw <= 0) return OTT_ERR_INVALID;
+    const int oh = (h + 2 * ph - kh) / sh + 1, ow = (w + 2 * pw - kw) / sw + 1;
+    const long total = (long)n * c * oh * ow;
+    if (total <= 0) return OTT_OK;
+    cudaSetDevice(ctx->device);
+    maxpool_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(in, out, c, h, w, oh, ow, kh, kw, sh, sw, ph, pw, pad_with_zero, total);
+    OTT_CUDA_CHECK(ctx, cudaGetLastError());
+    ctx->launches += 1;
+    return OTT_OK;
+}
+
+int ott_add_f32(ott_ctx* ctx, const float* a, const float* b, float* out, size_t count) {
+    if (!ctx || !a || !b || !out) return OTT_ERR_INVALID;
+    if (count == 0) return OTT_OK;
+    cudaSetDevice(ctx->device);
+    add_kernel<<<grid_for(ctx, (long)count, 256), 256, 0, ctx->stream>>>(a, b, out, (long)count);
+    OTT_CUDA_CHECK(ctx, cudaGetLastError());
+    ctx->launches += 1;
+    return OTT_OK;
+}
+
+int ott_activation_f32(ott_ctx* ctx, float* x, size_t count, int act_type, float param0) {
+    if (!ctx || !x || act_type < 0 || act_type > 3) return OTT_ERR_INVALID;
+    if (count == 0 || act_type == 0) return OTT_OK;
+    cudaSetDevice(ctx->device);
+    activation_kernel<<<grid_for(ctx, (long)count, 256), 256, 0, ctx->stream>>>(x, (long)count, act_type, param0);
+    OTT_CUDA_CHECK(ctx, cudaGetLastError());
+    ctx->launches += 1;
+    return OTT_OK;
+}
+
+}  // extern "C"

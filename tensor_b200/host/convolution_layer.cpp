@@ -1,0 +1,233 @@
+// ConvolutionLayer of the host-side API mirror: the quantized (int8_scale_term != 0) layer of
+// Tensor/ConvolutionLayer.cpp, with create_pipeline_int8 (:666-752) and forward_int8 (:754-847) handed to the
+// CUDA library through its C-ABI. Option keys, ParamDict ids, shape rule and field names follow the reference
+// (:58-206); the fp32 half of the layer (int8_scale_term == 0) does not exist here and create_pipeline refuses it.
+#include <cstring>
+#include <random>
+#include <sstream>
+
+#include "otter_api.hpp"
+
+namespace otter {
+
+ConvolutionLayer::ConvolutionLayer() {
+    one_blob_only = true;
+    support_inplace = false;
+    support_packing = true;
+}
+
+ConvolutionLayer::~ConvolutionLayer() {
+    if (gpu_conv_) ott_conv_int8_destroy(gpu_ctx_, gpu_conv_);
+}
+
+// Tensor/ConvolutionLayer.cpp:58-156
+int ConvolutionLayer::parse_param(LayerOption& option, ParamDict& pd) {
+    pd.clear();
+    auto pair = [&](const char* both, const char* h, const char* w, int def, int& oh, int& ow) {
+        oh = opt_find_int(option, h, -1);
+        ow = opt_find_int(option, w, -1);
+        const int b = opt_find_int(option, both, def);
+        if (oh < 0) oh = b;
+        if (ow < 0) ow = b;
+    };
+    int kh, kw, sh, sw, ph, pw, dh, dw, oph, opw;
+    pair("kernel", "kernel_h", "kernel_w", 3, kh, kw);
+    pair("stride", "stride_h", "stride_w", 1, sh, sw);
+    pair("padding", "padding_h", "padding_w", 0, ph, pw);
+    pair("dilation", "dilation_h", "dilation_w", 1, dh, dw);
+    pair("output_padding", "output_padding_h", "output_padding_w", 0, oph, opw);
+    int bias = opt_find(option, "batchnorm") ? 0 : 1;
+    if (opt_find(option, "bias_term")) bias = option["bias_term"] == "false" ? 0 : 1;
+    const std::string act = opt_find_string(option, "activation", "");
+    int act_type = act == "Relu" ? 1 : act == "LRelu" ? 2 : act == "Relu6" ? 3 : act == "Sigmoid" ? 4 : 0;
+    if (opt_find(option, "batchnorm")) act_type = 0;
+    Tensor act_params;
+    if (opt_check_string(option, "activation_params")) {
+        const std::string& s = option["activation_params"];
+        const int n = (int)std::count(s.begin(), s.end(), ',') + 1;
+        act_params = empty({n}, ScalarType::Float);
+        std::stringstream ss(s);
+        for (int i = 0; i < n; ++i) {
+            float v = 0;
+            char comma;
+            ss >> v >> comma;
+            act_params.data_ptr<float>()[i] = v;
+        }
+    }
+    pd.set((int)ConvParam::In_channels, opt_find_int(option, "in_channels", 1));
+    pd.set((int)ConvParam::Out_channels, opt_find_int(option, "out_channels", 1));
+    pd.set((int)ConvParam::Kernel_height, kh);
+    pd.set((int)ConvParam::Kernel_width, kw);
+    pd.set((int)ConvParam::Stride_height, sh);
+    pd.set((int)ConvParam::Stride_width, sw);
+    pd.set((int)ConvParam::Padding_height, ph);
+    pd.set((int)ConvParam::Padding_width, pw);
+    pd.set((int)ConvParam::Dilation_height, dh);
+    pd.set((int)ConvParam::Dilation_width, dw);
+    pd.set((int)ConvParam::Output_padding_height, oph);
+    pd.set((int)ConvParam::Output_padding_width, opw);
+    pd.set((int)ConvParam::Group, opt_find_int(option, "groups", 1));
+    pd.set((int)ConvParam::Bias_term, bias);
+    pd.set((int)ConvParam::Int8_scale_term, opt_find_int(option, "int8_scale_term", 0));
+    pd.set((int)ConvParam::Activation_type, act_type);
+    if (act_params.defined()) pd.set((int)ConvParam::Activation_params, act_params);
+    return 0;
+}
+
+// Tensor/ConvolutionLayer.cpp:158-183
+int ConvolutionLayer::compute_output_shape(ParamDict& pd) {
+    if (bottom_shapes.empty() || !bottom_shapes[0].defined()) return -1;
+    int n, c, h, w;
+    read_shape(bottom_shapes[0], n, c, h, w);
+    const int oc = pd.get((int)ConvParam::Out_channels, 1);
+    const int kh = pd.get((int)ConvParam::Kernel_height, 3), kw = pd.get((int)ConvParam::Kernel_width, 3);
+    const int sh = pd.get((int)ConvParam::Stride_height, 1), sw = pd.get((int)ConvParam::Stride_width, 1);
+    const int ph = pd.get((int)ConvParam::Padding_height, 0), pw = pd.get((int)ConvParam::Padding_width, 0);
+    const int dh = pd.get((int)ConvParam::Dilation_height, 1), dw = pd.get((int)ConvParam::Dilation_width, 1);
+    const int g = pd.get((int)ConvParam::Group, 1);
+    const int ow = (w + 2 * pw - dw * (kw - 1) - 1) / sw + 1;
+    const int oh = (h + 2 * ph - dh * (kh - 1) - 1) / sh + 1;
+    pd.set((int)ConvParam::In_channels, c);
+    pd.set((int)ConvParam::Weight_data_size, c / g * kh * kw * oc);
+    pd.set(OUTPUT_SHAPE_HINT, shape_tensor(n, oc, oh, ow));
+    return 0;
+}
+
+// Tensor/ConvolutionLayer.cpp:185-206
+int ConvolutionLayer::load_param(const ParamDict& pd) {
+    in_channels = pd.get((int)ConvParam::In_channels, 1);
+    out_channels = pd.get((int)ConvParam::Out_channels, 1);
+    kernel_height = pd.get((int)ConvParam::Kernel_height, 3);
+    kernel_width = pd.get((int)ConvParam::Kernel_width, 3);
+    stride_height = pd.get((int)ConvParam::Stride_height, 1);
+    stride_width = pd.get((int)ConvParam::Stride_width, 1);
+    padding_height = pd.get((int)ConvParam::Padding_height, 0);
+    padding_width = pd.get((int)ConvParam::Padding_width, 0);
+    dilation_height = pd.get((int)ConvParam::Dilation_height, 1);
+    dilation_width = pd.get((int)ConvParam::Dilation_width, 1);
+    output_padding_height = pd.get((int)ConvParam::Output_padding_height, 0);
+    output_padding_width = pd.get((int)ConvParam::Output_padding_width, 0);
+    groups = pd.get((int)ConvParam::Group, 1);
+    bias_term = pd.get((int)ConvParam::Bias_term, 0);
+    weight_data_size = pd.get((int)ConvParam::Weight_data_size, 0);
+    int8_scale_term = pd.get((int)ConvParam::Int8_scale_term, 0);
+    activation_type = pd.get((int)ConvParam::Activation_type, 0);
+    activation_params = pd.get((int)ConvParam::Activation_params, Tensor());
+    return 0;
+}
+
+// Random parameters of the right shapes, as CompileMode::Initial gives in the reference
+// (Tensor/ConvolutionLayer.cpp:208-243: int8 weights, [groups] or [1] activation scales, [Cout] weight scales).
+// Deterministic here: the generator is seeded from the layer name.
+int ConvolutionLayer::init_model() {
+    if (!int8_scale_term) return 0;
+    std::mt19937 rng((unsigned)std::hash<std::string>{}(name) ^ 0x0771E5u);
+    std::uniform_int_distribution<int> wd(-127, 127);
+    std::uniform_real_distribution<float> u(0.f, 1.f);
+    const bool depthwise = in_channels == groups && groups == out_channels && groups > 1;
+    weight_data = empty({out_channels, in_channels / groups, kernel_height, kernel_width}, ScalarType::Byte);
+    for (int64_t i = 0; i < weight_data.numel(); ++i) weight_data.data_ptr<int8_t>()[i] = (int8_t)wd(rng);
+    if (bias_term) {
+        bias_data = empty({out_channels}, ScalarType::Float);
+        for (int i = 0; i < out_channels; ++i) bias_data.data_ptr<float>()[i] = u(rng) - 0.5f;
+    }
+    weight_data_int8_scales = empty({out_channels}, ScalarType::Float);
+    for (int i = 0; i < out_channels; ++i) weight_data_int8_scales.data_ptr<float>()[i] = 50.f + 200.f * u(rng);
+    const float s_in = 20.f + 100.f * u(rng);
+    bottom_blob_int8_scales = full({depthwise ? groups : 1}, s_in, ScalarType::Float);
+    if (int8_scale_term > 100) top_blob_int8_scales = full({depthwise ? groups : 1}, 5.f + 20.f * u(rng), ScalarType::Float);
+    return 0;
+}
+
+// Tensor/ConvolutionLayer.cpp:298-304 -> create_pipeline_int8 (:666-752)
+int ConvolutionLayer::create_pipeline(const NetOption& opt) {
+    if (!int8_scale_term) return -1;  // the fp32 layer is not part of this build
+    if (!opt.gpu) return -1;
+    if (!weight_data.defined() || !weight_data_int8_scales.defined() || !bottom_blob_int8_scales.defined()) return -1;
+    if (gpu_conv_) {
+        ott_conv_int8_destroy(gpu_ctx_, gpu_conv_);
+        gpu_conv_ = nullptr;
+    }
+    gpu_ctx_ = opt.gpu;
+    ott_conv_desc d{};
+    d.cin = in_channels; d.cout = out_channels; d.kh = kernel_height; d.kw = kernel_width;
+    d.sh = stride_height; d.sw = stride_width; d.ph = padding_height; d.pw = padding_width;
+    d.dh = dilation_height; d.dw = dilation_width; d.groups = groups; d.bias_term = bias_term;
+    d.int8_scale_term = int8_scale_term; d.act_type = activation_type;
+    d.act_param0 = activation_params.defined() ? activation_params.data_ptr<float>()[0] : (activation_type == 2 ? 0.1f : 0.f);
+    d.rounding = opt.int8_rounding;
+    // scale_in_data is kept as a public field like the reference's (ConvolutionLayer.cpp:667-679); the library
+    // computes the same values from the same inputs for its own use
+    scale_in_data = empty({out_channels}, ScalarType::Float);
+    for (int p = 0; p < out_channels; ++p) {
+        const float ws = weight_data_int8_scales.data_ptr<float>()[p];
+        volatile float prod = bottom_blob_int8_scales.data_ptr<float>()[0] * ws;
+        scale_in_data.data_ptr<float>()[p] = ws == 0.f ? 0.f : 1.f / prod;
+    }
+    const bool requant = int8_scale_term > 100;
+    return ott_conv_int8_create(opt.gpu, &d, weight_data.data_ptr<int8_t>(), bias_term ? bias_data.data_ptr<float>() : nullptr,
+                                weight_data_int8_scales.data_ptr<float>(), bottom_blob_int8_scales.data_ptr<float>(),
+                                (int)bottom_blob_int8_scales.numel(), requant ? top_blob_int8_scales.data_ptr<float>() : nullptr,
+                                requant ? (int)top_blob_int8_scales.numel() : 0, &gpu_conv_);
+}
+
+// Tensor/ConvolutionLayer.cpp:507-511 -> forward_int8 (:754-847). Device tensors in and out; asynchronous.
+int ConvolutionLayer::forward(const Tensor& bottom_blob, Tensor& top_blob, const NetOption& opt) const {
+    if (!gpu_conv_ || !bottom_blob.defined() || bottom_blob.device() != Device::CUDA || bottom_blob.dim() != 4) return -1;
+    const int n = (int)bottom_blob.size(0), c = (int)bottom_blob.size(1), h = (int)bottom_blob.size(2), w = (int)bottom_blob.size(3);
+    if (c != in_channels) return -1;
+    int in_dtype;
+    if (bottom_blob.scalar_type() == ScalarType::Float && bottom_blob.layout() == Layout::NCHW) in_dtype = OTT_F32_NCHW;
+    else if (bottom_blob.scalar_type() == ScalarType::Byte && bottom_blob.layout() == Layout::NHWC16) in_dtype = OTT_S8_NHWC;
+    else return -1;
+    int oh = 0, ow = 0;
+    ott_conv_int8_out_shape(gpu_conv_, h, w, &oh, &ow);
+    const bool requant = int8_scale_term > 100;
+    top_blob = device_empty(opt, {n, out_channels, oh, ow}, requant ? ScalarType::Byte : ScalarType::Float,
+                            requant ? Layout::NHWC16 : Layout::NCHW);
+    if (!top_blob.defined()) return -100;
+    return ott_conv_int8_forward(opt.gpu, gpu_conv_, bottom_blob.raw_data(), in_dtype, n, h, w, top_blob.raw_data(),
+                                 requant ? OTT_S8_NHWC : OTT_F32_NCHW, nullptr);
+}
+
+// ---- Input (Tensor/InputLayer.cpp:19-71): declares the shape of a graph input; the blob is set by Extractor::input ----
+class InputLayer : public Layer {
+public:
+    InputLayer() { one_blob_only = true; support_inplace = true; }
+    int parse_param(LayerOption& option, ParamDict& pd) override {
+        pd.clear();
+        pd.set(0, opt_find_int(option, "batchsize", 1));
+        pd.set(1, opt_find_int(option, "channel", 1));
+        pd.set(2, opt_find_int(option, "height", 1));
+        pd.set(3, opt_find_int(option, "width", 1));
+        return 0;
+    }
+    int compute_output_shape(ParamDict& pd) override {
+        pd.set(OUTPUT_SHAPE_HINT, shape_tensor(pd.get(0, 1), pd.get(1, 1), pd.get(2, 1), pd.get(3, 1)));
+        return 0;
+    }
+    int forward_inplace(Tensor&, const NetOption&) const override { return 0; }
+    std::string type() const override { return "Input"; }
+};
+
+// ---- Split (Tensor/SplitLayer.cpp): every top is the bottom itself ----
+class SplitLayer : public Layer {
+public:
+    SplitLayer() { one_blob_only = false; support_inplace = false; }
+    int compute_output_shape(ParamDict& pd) override {
+        if (bottom_shapes.empty() || !bottom_shapes[0].defined()) return -1;
+        pd.set(OUTPUT_SHAPE_HINT, bottom_shapes[0]);
+        return 0;
+    }
+    int forward(const std::vector<Tensor>& bottom_blobs, std::vector<Tensor>& top_blobs, const NetOption&) const override {
+        for (auto& t : top_blobs) t = bottom_blobs[0];
+        return 0;
+    }
+    std::string type() const override { return "Split"; }
+};
+
+REGISTER_LAYER_CLASS(Convolution);
+REGISTER_LAYER_CLASS(Input);
+REGISTER_LAYER_CLASS(Split);
+
+}  // namespace otter

@@ -1,0 +1,233 @@
+// The fp32 glue layers of the benchmark graphs in the host-side API mirror: MaxPool, Concat, Crop,
+// ChannelShuffle, ShortCut and the stand-alone activations. Option keys and shape rules follow the reference
+// layer of the same name; forward enqueues one small CUDA kernel (include/otter_b200.h, "fp32 glue layers").
+// Blobs are device fp32 NCHW tensors.
+#include "otter_api.hpp"
+
+namespace otter {
+
+namespace {
+bool is_dev_f32(const Tensor& t) {
+    return t.defined() && t.device() == Device::CUDA && t.scalar_type() == ScalarType::Float && t.layout() == Layout::NCHW && t.dim() == 4;
+}
+}  // namespace
+
+// Tensor/MaxPoolLayer.cpp:28-133
+class MaxPoolLayer : public Layer {
+public:
+    MaxPoolLayer() { one_blob_only = true; support_inplace = false; support_packing = true; }
+    int parse_param(LayerOption& option, ParamDict& pd) override {
+        pd.clear();
+        auto pair = [&](const char* both, const char* h, const char* w, int def, int& oh, int& ow) {
+            oh = opt_find_int(option, h, -1);
+            ow = opt_find_int(option, w, -1);
+            const int b = opt_find_int(option, both, def);
+            if (oh < 0) oh = b;
+            if (ow < 0) ow = b;
+        };
+        int sh, sw, kh, kw, ph, pw;
+        pair("stride", "stride_h", "stride_w", 1, sh, sw);
+        pair("kernel", "kernel_h", "kernel_w", opt_find_int(option, "stride", 1), kh, kw);
+        pair("padding", "padding_h", "padding_w", 0, ph, pw);
+        if (opt_check_string(option, "ceil_mode") || opt_check_string(option, "darknet_mode")) return -1;  // not needed by the int8 graphs
+        if (opt_find_int(option, "dilation", 1) != 1 || opt_find_int(option, "dilation_h", 1) != 1 || opt_find_int(option, "dilation_w", 1) != 1) return -1;
+        pd.set(0, kh); pd.set(1, kw); pd.set(2, sh); pd.set(3, sw); pd.set(4, ph); pd.set(5, pw);
+        return 0;
+    }
+    int compute_output_shape(ParamDict& pd) override {
+        if (bottom_shapes.empty() || !bottom_shapes[0].defined()) return -1;
+        int n, c, h, w;
+        read_shape(bottom_shapes[0], n, c, h, w);
+        const int oh = (h + 2 * pd.get(4, 0) - pd.get(0, 3)) / pd.get(2, 1) + 1;
+        const int ow = (w + 2 * pd.get(5, 0) - pd.get(1, 3)) / pd.get(3, 1) + 1;
+        pd.set(OUTPUT_SHAPE_HINT, shape_tensor(n, c, oh, ow));
+        return 0;
+    }
+    int load_param(const ParamDict& pd) override {
+        kh = pd.get(0, 3); kw = pd.get(1, 3); sh = pd.get(2, 1); sw = pd.get(3, 1); ph = pd.get(4, 0); pw = pd.get(5, 0);
+        return 0;
+    }
+    int forward(const Tensor& bottom, Tensor& top, const NetOption& opt) const override {
+        if (!is_dev_f32(bottom)) return -1;
+        const int n = (int)bottom.size(0), c = (int)bottom.size(1), h = (int)bottom.size(2), w = (int)bottom.size(3);
+        const int oh = (h + 2 * ph - kh) / sh + 1, ow = (w + 2 * pw - kw) / sw + 1;
+        top = device_empty(opt, {n, c, oh, ow}, ScalarType::Float, Layout::NCHW);
+        if (!top.defined()) return -100;
+        // The reference's Net packs fp32 blobs whose channel count is a multiple of 4 (Tensor/Net.cpp:380-411), and its
+        // packed 3x3 stride-2 max-pool kernels pad with zeros (Tensor/Pool.cpp:972-975, :807-810); every other case
+        // goes through the plain kernel, where padding never wins.
+        const bool packed_zero_pad = opt.use_packing_layout && c % 4 == 0 && kh == 3 && kw == 3 && sh == 2 && sw == 2;
+        return ott_maxpool_f32_nchw(opt.gpu, bottom.data_ptr<float>(), n, c, h, w, kh, kw, sh, sw, ph, pw, packed_zero_pad ? 1 : 0,
+                                    top.data_ptr<float>());
+    }
+    std::string type() const override { return "MaxPool"; }
+    int kh = 3, kw = 3, sh = 1, sw = 1, ph = 0, pw = 0;
+};
+
+// Tensor/ConcatLayer.cpp:24-70 (channel axis only: the only use in the int8 graphs)
+class ConcatLayer : public Layer {
+public:
+    ConcatLayer() { one_blob_only = false; support_inplace = false; support_packing = true; }
+    int parse_param(LayerOption& option, ParamDict& pd) override {
+        pd.clear();
+        pd.set(0, opt_find_int(option, "axis", 1));
+        return 0;
+    }
+    int compute_output_shape(ParamDict& pd) override {
+        if (pd.get(0, 1) != 1 || bottom_shapes.empty()) return -1;
+        int n, c, h, w;
+        read_shape(bottom_shapes[0], n, c, h, w);
+        for (size_t i = 1; i < bottom_shapes.size(); ++i) {
+            int n2, c2, h2, w2;
+            read_shape(bottom_shapes[i], n2, c2, h2, w2);
+            c += c2;
+        }
+        pd.set(OUTPUT_SHAPE_HINT, shape_tensor(n, c, h, w));
+        return 0;
+    }
+    int forward(const std::vector<Tensor>& bottoms, std::vector<Tensor>& tops, const NetOption& opt) const override {
+        int total_c = 0;
+        for (const Tensor& b : bottoms) {
+            if (!is_dev_f32(b)) return -1;
+            total_c += (int)b.size(1);
+        }
+        const int n = (int)bottoms[0].size(0), h = (int)bottoms[0].size(2), w = (int)bottoms[0].size(3);
+        tops[0] = device_empty(opt, {n, total_c, h, w}, ScalarType::Float, Layout::NCHW);
+        if (!tops[0].defined()) return -100;
+        int off = 0;
+        for (const Tensor& b : bottoms) {
+            const int c = (int)b.size(1);
+            const int rc = ott_copy_channels_f32(opt.gpu, b.data_ptr<float>(), c, 0, 1, tops[0].data_ptr<float>(), total_c, off, 1, c, n, h * w);
+            if (rc != 0) return rc;
+            off += c;
+        }
+        return 0;
+    }
+    std::string type() const override { return "Concat"; }
+};
+
+// Tensor/CropLayer.cpp:25-76 (channel axis). The reference returns a view; here the channel range is copied.
+class CropLayer : public Layer {
+public:
+    CropLayer() { one_blob_only = true; support_inplace = false; support_packing = true; }
+    int parse_param(LayerOption& option, ParamDict& pd) override {
+        pd.clear();
+        pd.set(0, opt_find_int(option, "axis", 1));
+        pd.set(1, opt_find_int(option, "start", -1));
+        pd.set(2, opt_find_int(option, "end", -1));
+        return 0;
+    }
+    int compute_output_shape(ParamDict& pd) override {
+        if (pd.get(0, 1) != 1 || bottom_shapes.empty() || !bottom_shapes[0].defined()) return -1;
+        int n, c, h, w;
+        read_shape(bottom_shapes[0], n, c, h, w);
+        const int e = pd.get(2, -1) == -1 ? c : pd.get(2, -1);
+        pd.set(OUTPUT_SHAPE_HINT, shape_tensor(n, e - pd.get(1, 0), h, w));
+        return 0;
+    }
+    int load_param(const ParamDict& pd) override {
+        start = pd.get(1, -1);
+        end = pd.get(2, -1);
+        return 0;
+    }
+    int forward(const Tensor& bottom, Tensor& top, const NetOption& opt) const override {
+        if (!is_dev_f32(bottom)) return -1;
+        const int n = (int)bottom.size(0), c = (int)bottom.size(1), h = (int)bottom.size(2), w = (int)bottom.size(3);
+        const int e = end == -1 ? c : end;
+        if (start < 0 || e > c || e <= start) return -1;
+        top = device_empty(opt, {n, e - start, h, w}, ScalarType::Float, Layout::NCHW);
+        if (!top.defined()) return -100;
+        return ott_copy_channels_f32(opt.gpu, bottom.data_ptr<float>(), c, start, 1, top.data_ptr<float>(), e - start, 0, 1, e - start, n, h * w);
+    }
+    std::string type() const override { return "Crop"; }
+    int start = -1, end = -1;
+};
+
+// Tensor/ChannelShuffleLayer.cpp:20-41: output channel i*g + k is input channel k*(C/g) + i
+class ChannelShuffleLayer : public Layer {
+public:
+    ChannelShuffleLayer() { one_blob_only = true; support_inplace = false; support_packing = true; }
+    int parse_param(LayerOption& option, ParamDict& pd) override {
+        pd.clear();
+        pd.set(0, opt_find_int(option, "groups", 1));
+        return 0;
+    }
+    int load_param(const ParamDict& pd) override {
+        groups = pd.get(0, 1);
+        return 0;
+    }
+    int forward(const Tensor& bottom, Tensor& top, const NetOption& opt) const override {
+        if (!is_dev_f32(bottom)) return -1;
+        const int n = (int)bottom.size(0), c = (int)bottom.size(1), h = (int)bottom.size(2), w = (int)bottom.size(3);
+        if (groups < 1 || c % groups != 0) return -1;
+        top = device_empty(opt, {n, c, h, w}, ScalarType::Float, Layout::NCHW);
+        if (!top.defined()) return -100;
+        const int per = c / groups;
+        for (int k = 0; k < groups; ++k) {
+            const int rc = ott_copy_channels_f32(opt.gpu, bottom.data_ptr<float>(), c, k * per, 1, top.data_ptr<float>(), c, k, groups, per, n, h * w);
+            if (rc != 0) return rc;
+        }
+        return 0;
+    }
+    std::string type() const override { return "ChannelShuffle"; }
+    int groups = 1;
+};
+
+// Tensor/ShortCutLayer.cpp (element-wise add of two blobs of the same shape)
+class ShortCutLayer : public Layer {
+public:
+    ShortCutLayer() { one_blob_only = false; support_inplace = false; support_packing = true; }
+    int forward(const std::vector<Tensor>& bottoms, std::vector<Tensor>& tops, const NetOption& opt) const override {
+        if (bottoms.size() != 2 || !is_dev_f32(bottoms[0]) || !is_dev_f32(bottoms[1]) || bottoms[0].sizes() != bottoms[1].sizes()) return -1;
+        tops[0] = device_empty(opt, bottoms[0].sizes(), ScalarType::Float, Layout::NCHW);
+        if (!tops[0].defined()) return -100;
+        return ott_add_f32(opt.gpu, bottoms[0].data_ptr<float>(), bottoms[1].data_ptr<float>(), tops[0].data_ptr<float>(), (size_t)bottoms[0].numel());
+    }
+    std::string type() const override { return "ShortCut"; }
+};
+
+// Tensor/ReluLayer.cpp, Tensor/LReluLayer.cpp:28-113 (option "alpha", default 0.1), Tensor/Relu6Layer.cpp
+template <int ACT>
+class ActivationLayerT : public Layer {
+public:
+    ActivationLayerT() { one_blob_only = true; support_inplace = true; support_packing = true; }
+    int parse_param(LayerOption& option, ParamDict& pd) override {
+        pd.clear();
+        pd.set(0, opt_find_float(option, "alpha", 0.1f));
+        return 0;
+    }
+    int load_param(const ParamDict& pd) override {
+        slope = pd.get(0, 0.1f);
+        return 0;
+    }
+    int forward_inplace(Tensor& blob, const NetOption& opt) const override {
+        if (!is_dev_f32(blob)) return -1;
+        return ott_activation_f32(opt.gpu, blob.data_ptr<float>(), (size_t)blob.numel(), ACT, slope);
+    }
+    int forward(const Tensor& bottom, Tensor& top, const NetOption& opt) const override {
+        if (!is_dev_f32(bottom)) return -1;
+        top = device_empty(opt, bottom.sizes(), ScalarType::Float, Layout::NCHW);
+        if (!top.defined()) return -100;
+        const int c = (int)bottom.size(1);
+        int rc = ott_copy_channels_f32(opt.gpu, bottom.data_ptr<float>(), c, 0, 1, top.data_ptr<float>(), c, 0, 1, c, (int)bottom.size(0),
+                                       (int)(bottom.size(2) * bottom.size(3)));
+        if (rc != 0) return rc;
+        return forward_inplace(top, opt);
+    }
+    std::string type() const override { return ACT == 1 ? "Relu" : ACT == 2 ? "LRelu" : "Relu6"; }
+    float slope = 0.1f;
+};
+using ReluLayer = ActivationLayerT<1>;
+using LReluLayer = ActivationLayerT<2>;
+using Relu6Layer = ActivationLayerT<3>;
+
+REGISTER_LAYER_CLASS(MaxPool);
+REGISTER_LAYER_CLASS(Concat);
+REGISTER_LAYER_CLASS(Crop);
+REGISTER_LAYER_CLASS(ChannelShuffle);
+REGISTER_LAYER_CLASS(ShortCut);
+REGISTER_LAYER_CLASS(Relu);
+REGISTER_LAYER_CLASS(LRelu);
+REGISTER_LAYER_CLASS(Relu6);
+
+}  // namespace otter

@@ -1,0 +1,160 @@
+// C-ABI over the host-side graph runtime (include/otter_b200_net.h).
+#include <cstring>
+#include <sstream>
+
+#include "../../include/otter_b200_net.h"
+#include "otter_api.hpp"
+
+struct ott_net {
+    otter::Net net;
+    std::string error;
+};
+
+namespace {
+
+int fail(ott_net* n, int code, const std::string& what) {
+    n->error = what;
+    return code;
+}
+
+void copy_str(const std::string& s, char* dst, int cap) {
+    if (!dst || cap <= 0) return;
+    std::strncpy(dst, s.c_str(), (size_t)cap - 1);
+    dst[cap - 1] = 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ott_net_create(int device, ott_net** out) {
+    if (!out) return OTT_ERR_INVALID;
+    ott_net* n = new (std::nothrow) ott_net();
+    if (!n) return OTT_ERR_ALLOC;
+    n->net.option.device = device;
+    *out = n;
+    return OTT_OK;
+}
+
+int ott_net_destroy(ott_net* net) {
+    delete net;
+    return OTT_OK;
+}
+
+const char* ott_net_last_error(const ott_net* net) {
+    if (!net) return "null net";
+    return net->error.empty() ? net->net.last_error().c_str() : net->error.c_str();
+}
+
+ott_ctx* ott_net_context(ott_net* net) { return net ? net->net.context() : nullptr; }
+
+int ott_net_add_layer(ott_net* net, const char* options) {
+    if (!net || !options) return OTT_ERR_INVALID;
+    otter::LayerOption opt;
+    std::stringstream ss(options);
+    std::string item;
+    while (std::getline(ss, item, ';')) {
+        const size_t eq = item.find('=');
+        if (eq == std::string::npos) continue;
+        auto trim = [](std::string s) {
+            const size_t a = s.find_first_not_of(" \t\n"), b = s.find_last_not_of(" \t\n");
+            return a == std::string::npos ? std::string() : s.substr(a, b - a + 1);
+        };
+        opt[trim(item.substr(0, eq))] = trim(item.substr(eq + 1));
+    }
+    if (!opt.count("type")) return fail(net, OTT_ERR_INVALID, "layer option without a type");
+    net->net.addLayer(opt);
+    return OTT_OK;
+}
+
+int ott_net_compile(ott_net* net) {
+    if (!net) return OTT_ERR_INVALID;
+    net->error.clear();
+    return net->net.compile(otter::CompileMode::Initial);
+}
+
+int ott_net_layer_count(const ott_net* net) { return net ? net->net.layer_count() : 0; }
+
+int ott_net_layer_info(const ott_net* net, int i, char* type, int type_cap, char* name, int name_cap, int geom[12]) {
+    if (!net || i < 0 || i >= net->net.layer_count()) return OTT_ERR_INVALID;
+    const otter::Layer* l = net->net.layer(i);
+    copy_str(l->type(), type, type_cap);
+    copy_str(l->name, name, name_cap);
+    if (geom) {
+        std::memset(geom, 0, sizeof(int) * 12);
+        if (const auto* c = dynamic_cast<const otter::ConvolutionLayer*>(l)) {
+            const int g[12] = {c->in_channels, c->out_channels, c->kernel_height, c->kernel_width, c->stride_height, c->stride_width,
+                               c->padding_height, c->padding_width, c->groups, c->bias_term, c->int8_scale_term, c->activation_type};
+            std::memcpy(geom, g, sizeof g);
+        }
+    }
+    return OTT_OK;
+}
+
+int ott_net_blob_shape(const ott_net* net, const char* blob, int shape[4]) {
+    if (!net || !blob || !shape) return OTT_ERR_INVALID;
+    const int b = net->net.find_blob_index_by_name(blob);
+    if (b < 0 || !net->net.blob(b).shape.defined()) return OTT_ERR_INVALID;
+    std::memcpy(shape, net->net.blob(b).shape.data_ptr<int>(), sizeof(int) * 4);
+    return OTT_OK;
+}
+
+int ott_net_set_conv_params(ott_net* net, const char* layer, const int8_t* w_oihw, const float* bias, const float* w_scales,
+                            const float* in_scales, int n_in_scales, const float* out_scales, int n_out_scales) {
+    if (!net || !layer || !w_oihw || !w_scales || !in_scales) return OTT_ERR_INVALID;
+    const int idx = net->net.find_layer_index_by_name(layer);
+    auto* c = idx < 0 ? nullptr : dynamic_cast<otter::ConvolutionLayer*>(net->net.layer(idx));
+    if (!c) return fail(net, OTT_ERR_INVALID, std::string("no Convolution layer named ") + layer);
+    using otter::ScalarType;
+    c->weight_data = otter::empty({c->out_channels, c->in_channels / c->groups, c->kernel_height, c->kernel_width}, ScalarType::Byte);
+    std::memcpy(c->weight_data.raw_data(), w_oihw, (size_t)c->weight_data.numel());
+    auto fvec = [](const float* p, int n) {
+        otter::Tensor t = otter::empty({n}, ScalarType::Float);
+        std::memcpy(t.raw_data(), p, sizeof(float) * (size_t)n);
+        return t;
+    };
+    if (c->bias_term) {
+        if (!bias) return fail(net, OTT_ERR_INVALID, "layer has a bias term but bias is NULL");
+        c->bias_data = fvec(bias, c->out_channels);
+    }
+    c->weight_data_int8_scales = fvec(w_scales, c->out_channels);
+    c->bottom_blob_int8_scales = fvec(in_scales, n_in_scales);
+    if (c->int8_scale_term > 100) {
+        if (!out_scales || n_out_scales < 1) return fail(net, OTT_ERR_INVALID, "int8 output needs top_blob_int8_scales");
+        c->top_blob_int8_scales = fvec(out_scales, n_out_scales);
+    }
+    net->error.clear();
+    return net->net.recreate_pipeline(idx);
+}
+
+int ott_net_forward(ott_net* net, const char* input_blob, const void* in, int in_on_device, int n, int c, int h, int w, int n_out,
+                    const char* const* out_blobs, void* const* out_host) {
+    if (!net || !input_blob || !in || n_out < 1 || !out_blobs) return OTT_ERR_INVALID;
+    net->error.clear();
+    otter::Extractor ex = net->net.create_extractor();
+    otter::Tensor x;
+    if (in_on_device)
+        x = otter::Tensor::wrap(const_cast<void*>(in), (size_t)n * c * h * w * 4, otter::Device::CUDA, nullptr, {n, c, h, w}, otter::ScalarType::Float);
+    else
+        x = otter::from_blob(const_cast<void*>(in), {n, c, h, w}, otter::ScalarType::Float);
+    int rc = ex.input(input_blob, x);
+    if (rc != 0) return fail(net, rc, "Extractor::input failed");
+    // outputs are pulled in order; with lightmode a blob consumed on the way to an earlier output is gone, so
+    // keep every requested blob alive by extracting device handles first
+    ex.set_lightmode(n_out == 1);
+    std::vector<otter::Tensor> dev((size_t)n_out);
+    for (int i = 0; i < n_out; ++i) {
+        rc = ex.extract(out_blobs[i], dev[(size_t)i], 1);
+        if (rc != 0) return rc;
+    }
+    for (int i = 0; i < n_out; ++i) {
+        if (!out_host || !out_host[i]) continue;
+        otter::Tensor host;
+        rc = ex.extract(out_blobs[i], host, 0);
+        if (rc != 0) return rc;
+        std::memcpy(out_host[i], host.raw_data(), (size_t)host.numel() * otter::elementSize(host.scalar_type()));
+    }
+    return OTT_OK;
+}
+
+}  // extern "C"

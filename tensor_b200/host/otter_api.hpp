@@ -1,0 +1,274 @@
+// Host-side mirror of the reference's operator API for the int8 convolution path, in C++17.
+//
+// Same names, argument meaning and return codes as the reference, so that code written against
+//   otter::Net::addLayer / compile / create_extractor          (Tensor/Net.hpp:28-55)
+//   otter::Extractor::input / extract                          (Tensor/Net.hpp:92-98)
+//   otter::Layer::parse_param / compute_output_shape / load_param / init_model / create_pipeline / forward
+//                                                              (Tensor/Layer.hpp:30-49)
+//   otter::LayerRegistry::CreateLayer, REGISTER_LAYER_CLASS    (Tensor/LayerRegistry.hpp:36-43,79-86)
+//   otter::ParamDict                                           (Tensor/ParamDict.hpp:15-64)
+//   otter::LayerOption (string -> string)                      (Tensor/Layer.hpp:21)
+// keeps compiling and a quantized Convolution layer in a Net runs on the GPU "with no other change".
+// The one new switch is NetOption::device (>= 0: the CUDA device the Net lives on).
+//
+// Everything below the Layer objects is the C-ABI of include/otter_b200.h; this file contains no kernel
+// and no CPU arithmetic path: a Net without a GPU fails at compile().
+#pragma once
+
+#include <cstdint>
+#include <cstdio>
+#include <functional>
+#include <map>
+#include <memory>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/otter_b200.h"
+
+namespace otter {
+
+enum class ScalarType { Float, Byte, Int, Undefined };
+enum class Device { CPU, CUDA };
+// NCHW: the reference's plain layout. NHWC16: channels innermost, channel stride padded to a multiple of 16
+// (device int8 blobs between a requantizing convolution and its consumer; replaces Byte8 elempack blobs).
+enum class Layout { NCHW, NHWC16 };
+
+inline size_t elementSize(ScalarType t) { return t == ScalarType::Byte ? 1 : 4; }
+
+// A reference-counted handle over host or device memory (the subset of otter::Tensor the path needs:
+// Tensor/Tensor.hpp, Tensor/TensorBase.hpp; Memory/DataPtr with a deleter as in Tensor/Allocator.hpp:67-110).
+class Tensor {
+public:
+    Tensor() = default;
+    bool defined() const { return static_cast<bool>(st_); }
+    void reset() { st_.reset(); sizes_.clear(); }
+    long use_count() const { return st_.use_count(); }
+    int64_t dim() const { return (int64_t)sizes_.size(); }
+    int64_t size(int64_t i) const { return sizes_[(size_t)(i < 0 ? i + dim() : i)]; }
+    const std::vector<int64_t>& sizes() const { return sizes_; }
+    int64_t numel() const { int64_t n = 1; for (auto s : sizes_) n *= s; return sizes_.empty() ? 0 : n; }
+    ScalarType scalar_type() const { return dtype_; }
+    Device device() const { return st_ ? st_->dev : Device::CPU; }
+    Layout layout() const { return layout_; }
+    size_t nbytes() const { return st_ ? st_->bytes : 0; }
+    void* raw_data() const { return st_ ? static_cast<char*>(st_->ptr) + offset_ : nullptr; }
+    template <typename T> T* data_ptr() const { return static_cast<T*>(raw_data()); }
+    Tensor view(std::vector<int64_t> sizes) const;  // same storage, new sizes (-1 allowed once)
+    Tensor clone() const;                            // host tensors only
+    // channel sub-range [start, end) of a device NCHW tensor as a strided view is not expressible here: Crop copies.
+
+    static Tensor wrap(void* ptr, size_t bytes, Device dev, std::function<void(void*)> deleter, std::vector<int64_t> sizes,
+                       ScalarType dtype, Layout layout = Layout::NCHW);
+
+private:
+    struct Storage {
+        void* ptr = nullptr;
+        size_t bytes = 0;
+        Device dev = Device::CPU;
+        std::function<void(void*)> deleter;
+        ~Storage() { if (deleter && ptr) deleter(ptr); }
+    };
+    std::shared_ptr<Storage> st_;
+    size_t offset_ = 0;
+    std::vector<int64_t> sizes_;
+    ScalarType dtype_ = ScalarType::Undefined;
+    Layout layout_ = Layout::NCHW;
+};
+
+Tensor empty(std::vector<int64_t> sizes, ScalarType dtype);                       // host, zero-initialised
+Tensor from_blob(void* data, std::vector<int64_t> sizes, ScalarType dtype);       // host, not owned
+Tensor tensor(std::vector<int> values, ScalarType dtype);                         // 1-D host tensor of ints/floats
+Tensor full(std::vector<int64_t> sizes, float value, ScalarType dtype);
+
+#define MAX_PARAM_COUNT 32
+enum class ParamType { Undefined, Int, Float, Array };
+
+// 32 numbered slots of int / float / Tensor (Tensor/ParamDict.hpp:15-64)
+class ParamDict {
+public:
+    ParamDict() { clear(); }
+    ParamType type(int id) const { return params[id].type; }
+    int get(int id, int def) const { return params[id].type == ParamType::Int ? params[id].i : def; }
+    float get(int id, float def) const { return params[id].type == ParamType::Float ? params[id].f : def; }
+    Tensor get(int id, const Tensor& def) const { return params[id].type == ParamType::Array ? params[id].t : def; }
+    void set(int id, int i) { params[id].type = ParamType::Int; params[id].i = i; }
+    void set(int id, float f) { params[id].type = ParamType::Float; params[id].f = f; }
+    void set(int id, const Tensor& v) { params[id].type = ParamType::Array; params[id].t = v; }
+    void clear() { for (auto& p : params) { p.type = ParamType::Undefined; p.i = 0; p.t = Tensor(); } }
+private:
+    struct { ParamType type; union { int i; float f; }; Tensor t; } params[MAX_PARAM_COUNT];
+};
+
+// Tensor/NetOption.hpp:16-24 plus the device switch.
+class NetOption {
+public:
+    bool lightmode = true;
+    bool train = false;
+    bool use_non_lib_optimize = true;
+    bool use_packing_layout = true;   // kept for source compatibility; the GPU layouts do not depend on it
+    bool use_fp16_storage = false;
+    int openmp_blocktime = 20;
+    int device = 0;                   // NEW: CUDA device of the Net
+    ott_ctx* gpu = nullptr;           // set by Net::compile; what every Layer::forward launches on
+    int int8_rounding = OTT_ROUND_ADD_HALF_TRUNC;  // which reference build is mirrored (packed x86 default / aarch64)
+};
+
+class Initializer;  // weight readers (Tensor/Initializer.hpp) are not part of this build
+
+using LayerOption = std::unordered_map<std::string, std::string>;
+
+#define OUTPUT_SHAPE_HINT 30
+#define opt_find(opt, type) ((opt).find(type) != (opt).end())
+#define opt_get_int(opt, type) int(atoi((opt)[type].c_str()))
+#define opt_get_float(opt, type) float(atof((opt)[type].c_str()))
+#define opt_find_int(opt, type, default) (((opt).find(type) == (opt).end()) ? (default) : opt_get_int(opt, type))
+#define opt_find_float(opt, type, default) (((opt).find(type) == (opt).end()) ? (default) : opt_get_float(opt, type))
+#define opt_find_string(opt, type, default) (((opt).find(type) == (opt).end()) ? std::string(default) : (opt)[type])
+#define opt_check_string(opt, type) ((opt).find(type) != (opt).end())
+
+// Tensor/Layer.hpp:23-62. Return 0 for success; -1 unsupported; -100 allocation failure (Tensor/Layer.cpp:50-59).
+class Layer {
+public:
+    Layer();
+    virtual ~Layer();
+    virtual int parse_param(LayerOption& option, ParamDict& pd);
+    virtual int compute_output_shape(ParamDict& pd);
+    virtual int load_param(const ParamDict& pd);
+    virtual int init_model();
+    virtual int load_model(const Initializer& initializer);
+    virtual int create_pipeline(const NetOption& opt);
+    virtual std::string type() const { return "Undefined"; }
+
+    virtual int forward(const Tensor& bottom_blob, Tensor& top_blob, const NetOption& opt) const;
+    virtual int forward(const std::vector<Tensor>& bottom_blobs, std::vector<Tensor>& top_blobs, const NetOption& opt) const;
+    virtual int forward_inplace(Tensor& bottom_top_blob, const NetOption& opt) const;
+    virtual int forward_inplace(std::vector<Tensor>& bottom_top_blobs, const NetOption& opt) const;
+
+    bool support_inplace = false;
+    bool one_blob_only = false;
+    bool support_packing = false;
+    std::vector<int> bottoms, tops;
+    std::vector<Tensor> bottom_shapes, top_shapes;  // Int tensors [1,4] {N,C,H,W}
+    std::string name;
+};
+
+using LayerCreator = std::function<Layer*()>;
+class LayerRegistry {
+public:
+    static std::map<std::string, LayerCreator>& Registry();
+    static void AddCreator(const std::string& type, LayerCreator creator);
+    static Layer* CreateLayer(const std::string& type);  // unknown type -> nullptr (the reference exits the process)
+    static std::string LayerTypeListString();
+};
+struct LayerRegister {
+    LayerRegister(const std::string& type, LayerCreator c) { LayerRegistry::AddCreator(type, std::move(c)); }
+};
+#define REGISTER_LAYER_CLASS(type) \
+    static ::otter::LayerRegister g_creator_##type(#type, []() -> ::otter::Layer* { return new type##Layer(); })
+
+// helpers shared by the layers
+Tensor shape_tensor(int n, int c, int h, int w);                 // Int [1,4]
+void read_shape(const Tensor& shape, int& n, int& c, int& h, int& w);
+Tensor device_empty(const NetOption& opt, std::vector<int64_t> sizes, ScalarType dtype, Layout layout);  // from the ctx allocator
+
+// ---- ConvolutionLayer (Tensor/ConvolutionLayer.hpp:15-99): the quantized half only ----
+enum class ConvParam : int {
+    In_channels, Out_channels, Kernel_height, Kernel_width, Stride_height, Stride_width, Padding_height, Padding_width,
+    Dilation_height, Dilation_width, Output_padding_height, Output_padding_width, Group, Bias_term, Weight_data_size,
+    Int8_scale_term, Activation_type, Activation_params
+};
+
+class ConvolutionLayer : public Layer {
+public:
+    ConvolutionLayer();
+    ~ConvolutionLayer() override;
+    int parse_param(LayerOption& option, ParamDict& pd) override;
+    int compute_output_shape(ParamDict& pd) override;
+    int load_param(const ParamDict& pd) override;
+    int init_model() override;
+    int create_pipeline(const NetOption& opt) override;
+    int forward(const Tensor& bottom_blob, Tensor& top_blob, const NetOption& opt) const override;
+    std::string type() const override { return "Convolution"; }
+
+    int in_channels = 1, out_channels = 1, kernel_height = 3, kernel_width = 3, stride_height = 1, stride_width = 1;
+    int padding_height = 0, padding_width = 0, dilation_height = 1, dilation_width = 1;
+    int output_padding_height = 0, output_padding_width = 0, groups = 1, bias_term = 0, int8_scale_term = 0;
+    int weight_data_size = 0, activation_type = 0;
+    Tensor activation_params;
+    // the reference's own fields, host tensors: weight Byte OIHW, the rest Float
+    Tensor weight_data, bias_data, weight_data_int8_scales, bottom_blob_int8_scales, top_blob_int8_scales, scale_in_data;
+
+private:
+    ott_conv* gpu_conv_ = nullptr;
+    ott_ctx* gpu_ctx_ = nullptr;
+};
+
+// ---- graph runtime (Tensor/Net.hpp, Tensor/Blob.hpp) ----
+struct Blob {
+    std::string name;
+    int producer = -1, consumer = -1;
+    Tensor shape;
+};
+
+enum class CompileMode { Initial, OnlyStructure };
+class Extractor;
+
+class Net {
+    friend class Extractor;
+public:
+    Net();
+    ~Net();
+    Net(const Net&) = delete;
+    Net& operator=(const Net&) = delete;
+
+    void addLayer(LayerOption option);
+    int compile(CompileMode mode = CompileMode::Initial);  // 0 on success (the reference throws on a bad graph)
+    Extractor create_extractor() const;
+    void summary() const;
+    int find_blob_index_by_name(const std::string& name) const;
+    int find_layer_index_by_name(const std::string& name) const;
+    int layer_count() const { return (int)layers_.size(); }
+    Layer* layer(int index) const { return layers_[(size_t)index]; }
+    int recreate_pipeline(int layer_index);  // after the caller replaced a layer's weight fields
+    const std::vector<std::string>& input_names() const { return input_names_; }
+    const std::vector<std::string>& output_names() const { return output_names_; }
+    const Blob& blob(int index) const { return blobs_[(size_t)index]; }
+    const std::string& last_error() const { return error_; }
+    ott_ctx* context() const { return option.gpu; }
+
+    NetOption option;
+
+private:
+    void graph_construct();
+    int forward_layer(int layer_index, std::vector<Tensor>& blob_tensors, const NetOption& opt) const;
+    int do_forward_layer(const Layer* layer, std::vector<Tensor>& blob_tensors, const NetOption& opt) const;
+
+    std::vector<Layer*> layers_;
+    std::vector<Blob> blobs_;
+    std::vector<LayerOption> layer_options_;
+    std::vector<std::string> input_names_, output_names_;
+    mutable std::string error_;
+    bool owns_ctx_ = false;
+};
+
+class Extractor {
+    friend class Net;
+public:
+    void clear();
+    void set_lightmode(bool lightmode) { option.lightmode = lightmode; }
+    // `in` may be a host fp32 NCHW tensor (copied to the GPU here) or a device tensor made by device_empty
+    int input(const std::string& blob_name, const Tensor& in);
+    int input(int blob_index, const Tensor& in);
+    // type 0: result copied to a host tensor in the reference's plain layout (fp32 NCHW / int8 NCHW), after a
+    // stream synchronisation; type 1: the device tensor as it is (asynchronous)
+    int extract(const std::string& blob_name, Tensor& feat, int type = 0);
+    int extract(int blob_index, Tensor& feat, int type = 0);
+private:
+    Extractor(const Net* net, size_t blob_count);
+    const Net* net_;
+    std::vector<Tensor> blob_tensors_;
+    NetOption option;
+};
+
+}  // namespace otter

@@ -1,0 +1,421 @@
+// Tensor handle, Layer base class, LayerRegistry, Net and Extractor of the host-side API mirror
+// (declarations and reference citations in otter_api.hpp).
+#include <algorithm>
+#include <cstring>
+#include <sstream>
+
+#include "otter_api.hpp"
+
+namespace otter {
+
+// ---------------------------------------------------------------- Tensor
+Tensor Tensor::wrap(void* ptr, size_t bytes, Device dev, std::function<void(void*)> deleter, std::vector<int64_t> sizes,
+                    ScalarType dtype, Layout layout) {
+    Tensor t;
+    t.st_ = std::make_shared<Storage>();
+    t.st_->ptr = ptr;
+    t.st_->bytes = bytes;
+    t.st_->dev = dev;
+    t.st_->deleter = std::move(deleter);
+    t.sizes_ = std::move(sizes);
+    t.dtype_ = dtype;
+    t.layout_ = layout;
+    return t;
+}
+
+Tensor Tensor::view(std::vector<int64_t> sizes) const {
+    int64_t known = 1, unknown = -1;
+    for (size_t i = 0; i < sizes.size(); ++i) {
+        if (sizes[i] == -1) unknown = (int64_t)i; else known *= sizes[i];
+    }
+    if (unknown >= 0) sizes[(size_t)unknown] = known ? numel() / known : 0;
+    Tensor t = *this;
+    t.sizes_ = std::move(sizes);
+    return t;
+}
+
+Tensor Tensor::clone() const {
+    if (!defined() || device() != Device::CPU) return Tensor();
+    Tensor t = empty(sizes_, dtype_);
+    std::memcpy(t.raw_data(), raw_data(), (size_t)numel() * elementSize(dtype_));
+    t.layout_ = layout_;
+    return t;
+}
+
+Tensor empty(std::vector<int64_t> sizes, ScalarType dtype) {
+    int64_t n = sizes.empty() ? 0 : 1;
+    for (auto s : sizes) n *= s;
+    const size_t bytes = (size_t)(n > 0 ? n : 1) * elementSize(dtype);
+    void* p = ::operator new(bytes);
+    std::memset(p, 0, bytes);
+    return Tensor::wrap(p, bytes, Device::CPU, [](void* q) { ::operator delete(q); }, std::move(sizes), dtype);
+}
+
+Tensor from_blob(void* data, std::vector<int64_t> sizes, ScalarType dtype) {
+    int64_t n = sizes.empty() ? 0 : 1;
+    for (auto s : sizes) n *= s;
+    return Tensor::wrap(data, (size_t)n * elementSize(dtype), Device::CPU, nullptr, std::move(sizes), dtype);
+}
+
+Tensor tensor(std::vector<int> values, ScalarType dtype) {
+    Tensor t = empty({(int64_t)values.size()}, dtype);
+    for (size_t i = 0; i < values.size(); ++i) {
+        if (dtype == ScalarType::Float) t.data_ptr<float>()[i] = (float)values[i];
+        else if (dtype == ScalarType::Int) t.data_ptr<int>()[i] = values[i];
+        else t.data_ptr<int8_t>()[i] = (int8_t)values[i];
+    }
+    return t;
+}
+
+Tensor full(std::vector<int64_t> sizes, float value, ScalarType dtype) {
+    Tensor t = empty(std::move(sizes), dtype);
+    for (int64_t i = 0; i < t.numel(); ++i) {
+        if (dtype == ScalarType::Float) t.data_ptr<float>()[i] = value;
+        else if (dtype == ScalarType::Int) t.data_ptr<int>()[i] = (int)value;
+        else t.data_ptr<int8_t>()[i] = (int8_t)value;
+    }
+    return t;
+}
+
+Tensor shape_tensor(int n, int c, int h, int w) { return tensor({n, c, h, w}, ScalarType::Int).view({1, -1}); }
+
+void read_shape(const Tensor& shape, int& n, int& c, int& h, int& w) {
+    const int* p = shape.data_ptr<int>();
+    n = p[0]; c = p[1]; h = p[2]; w = p[3];
+}
+
+Tensor device_empty(const NetOption& opt, std::vector<int64_t> sizes, ScalarType dtype, Layout layout) {
+    if (!opt.gpu) return Tensor();
+    int64_t n = 1;
+    for (auto s : sizes) n *= s;
+    if (layout == Layout::NHWC16 && sizes.size() == 4)  // sizes are logical {N,C,H,W}; storage pads C
+        n = sizes[0] * sizes[2] * sizes[3] * ott_nhwc_channels((int)sizes[1]);
+    const size_t bytes = (size_t)(n > 0 ? n : 1) * elementSize(dtype);
+    void* p = nullptr;
+    if (ott_malloc(opt.gpu, bytes, &p) != OTT_OK) return Tensor();
+    ott_ctx* ctx = opt.gpu;
+    return Tensor::wrap(p, bytes, Device::CUDA, [ctx](void* q) { ott_free(ctx, q); }, std::move(sizes), dtype, layout);
+}
+
+// ---------------------------------------------------------------- Layer
+Layer::Layer() = default;
+Layer::~Layer() = default;
+int Layer::parse_param(LayerOption&, ParamDict& pd) { pd.clear(); return 0; }
+int Layer::compute_output_shape(ParamDict& pd) {
+    if (!bottom_shapes.empty() && bottom_shapes[0].defined()) pd.set(OUTPUT_SHAPE_HINT, bottom_shapes[0]);
+    return 0;
+}
+int Layer::load_param(const ParamDict&) { return 0; }
+int Layer::init_model() { return 0; }
+int Layer::load_model(const Initializer&) { return 0; }
+int Layer::create_pipeline(const NetOption&) { return 0; }
+int Layer::forward(const Tensor& bottom_blob, Tensor& top_blob, const NetOption& opt) const {
+    if (!support_inplace) return -1;
+    top_blob = bottom_blob;
+    return forward_inplace(top_blob, opt);
+}
+int Layer::forward(const std::vector<Tensor>& bottom_blobs, std::vector<Tensor>& top_blobs, const NetOption& opt) const {
+    if (!support_inplace) return -1;
+    top_blobs = bottom_blobs;
+    return forward_inplace(top_blobs, opt);
+}
+int Layer::forward_inplace(Tensor&, const NetOption&) const { return -1; }
+int Layer::forward_inplace(std::vector<Tensor>&, const NetOption&) const { return -1; }
+
+std::map<std::string, LayerCreator>& LayerRegistry::Registry() {
+    static std::map<std::string, LayerCreator> reg;
+    return reg;
+}
+void LayerRegistry::AddCreator(const std::string& type, LayerCreator creator) { Registry()[type] = std::move(creator); }
+Layer* LayerRegistry::CreateLayer(const std::string& type) {
+    auto it = Registry().find(type);
+    return it == Registry().end() ? nullptr : it->second();
+}
+std::string LayerRegistry::LayerTypeListString() {
+    std::string s;
+    for (auto& kv : Registry()) s += (s.empty() ? "" : ", ") + kv.first;
+    return s;
+}
+
+// ---------------------------------------------------------------- Net
+namespace {
+
+std::vector<std::string> split_names(const std::string& list) {
+    std::vector<std::string> out;
+    std::stringstream ss(list);
+    std::string item;
+    while (std::getline(ss, item, ',')) {
+        item.erase(std::remove_if(item.begin(), item.end(), [](unsigned char ch) { return ch == ' ' || ch == '"'; }), item.end());
+        if (!item.empty()) out.push_back(item);
+    }
+    return out;
+}
+
+}  // namespace
+
+Net::Net() = default;
+
+Net::~Net() {
+    for (Layer* l : layers_) delete l;
+    layers_.clear();
+    if (owns_ctx_ && option.gpu) {
+        ott_ctx_destroy(option.gpu);
+        option.gpu = nullptr;
+    }
+}
+
+// Tensor/Net.cpp:40-80 (the BatchNorm / activation auto-insertion belongs to the fp32 path and is not mirrored)
+void Net::addLayer(LayerOption option) {
+    if (!opt_check_string(option, "name")) option["name"] = std::to_string(layer_options_.size());
+    if (!opt_check_string(option, "output")) option["output"] = option["name"];
+    if (!opt_check_string(option, "input_id")) option["input_id"] = "0";
+    layer_options_.push_back(std::move(option));
+}
+
+// Tensor/Net.cpp:82-172: default input = previous layer's first output; a blob with several consumers gets an
+// automatic Split layer whose outputs rename the consumers' inputs.
+void Net::graph_construct() {
+    for (size_t i = 1; i < layer_options_.size(); ++i) {
+        LayerOption& l = layer_options_[i];
+        if (!opt_check_string(l, "input") && l["type"] != "Input") l["input"] = split_names(layer_options_[i - 1]["output"])[0];
+    }
+    int extra = 0;
+    for (size_t i = 0; i < layer_options_.size(); ++i) {
+        const std::vector<std::string> outs = split_names(layer_options_[i]["output"]);
+        for (const std::string& out : outs) {
+            std::vector<std::pair<size_t, size_t>> users;  // (layer, input position)
+            for (size_t j = 0; j < layer_options_.size(); ++j) {
+                if (layer_options_[j]["type"] == "Input") continue;
+                const auto ins = split_names(layer_options_[j]["input"]);
+                for (size_t k = 0; k < ins.size(); ++k)
+                    if (ins[k] == out) users.emplace_back(j, k);
+            }
+            if (users.size() <= 1) continue;
+            LayerOption sp;
+            sp["type"] = "Split";
+            sp["name"] = "auto_sp_" + std::to_string(++extra);
+            sp["input"] = out;
+            std::string outputs;
+            for (size_t u = 0; u < users.size(); ++u) {
+                const std::string nm = "asp_" + std::to_string(i) + "_" + out + "_" + std::to_string(u);
+                outputs += (u ? ", " : "") + nm;
+                auto ins = split_names(layer_options_[users[u].first]["input"]);
+                ins[users[u].second] = nm;
+                std::string joined;
+                for (size_t k = 0; k < ins.size(); ++k) joined += (k ? ", " : "") + ins[k];
+                layer_options_[users[u].first]["input"] = joined;
+            }
+            sp["output"] = outputs;
+            layer_options_.insert(layer_options_.begin() + (long)i + 1, sp);
+        }
+    }
+}
+
+int Net::find_blob_index_by_name(const std::string& name) const {
+    for (size_t i = 0; i < blobs_.size(); ++i)
+        if (blobs_[i].name == name) return (int)i;
+    return -1;
+}
+
+int Net::find_layer_index_by_name(const std::string& name) const {
+    for (size_t i = 0; i < layers_.size(); ++i)
+        if (layers_[i] && layers_[i]->name == name) return (int)i;
+    return -1;
+}
+
+// Tensor/Net.cpp:174-280
+int Net::compile(CompileMode mode) {
+    if (!option.gpu) {
+        if (option.device < 0) { error_ = "NetOption::device < 0: this build has no CPU path"; return -1; }
+        const int rc = ott_ctx_create(option.device, &option.gpu);
+        if (rc != OTT_OK) { error_ = "no usable sm_100 GPU (ott_ctx_create failed)"; return rc; }
+        owns_ctx_ = true;
+    }
+    graph_construct();
+    if (layer_options_.empty()) { error_ = "Invalid network"; return -1; }
+    size_t blob_count = 0;
+    for (auto& o : layer_options_) blob_count += split_names(o["output"]).size();
+    blobs_.assign(blob_count, Blob());
+    layers_.assign(layer_options_.size(), nullptr);
+    ParamDict pd;
+    int blob_index = 0;
+    for (size_t i = 0; i < layer_options_.size(); ++i) {
+        LayerOption& opt = layer_options_[i];
+        const std::string type = opt["type"];
+        Layer* layer = LayerRegistry::CreateLayer(type);
+        if (!layer) { error_ = "Unknown layer type: " + type + " (known layer types: " + LayerRegistry::LayerTypeListString() + ")"; return -1; }
+        layers_[i] = layer;
+        layer->name = opt["name"];
+        const auto ins = type == "Input" ? std::vector<std::string>() : split_names(opt["input"]);
+        const auto outs = split_names(opt["output"]);
+        layer->bottoms.resize(ins.size());
+        for (size_t j = 0; j < ins.size(); ++j) {
+            const int b = find_blob_index_by_name(ins[j]);
+            if (b < 0) { error_ = "layer " + layer->name + " consumes unknown blob " + ins[j]; return -1; }
+            blobs_[(size_t)b].consumer = (int)i;
+            layer->bottoms[j] = b;
+        }
+        layer->tops.resize(outs.size());
+        for (size_t j = 0; j < outs.size(); ++j) {
+            blobs_[(size_t)blob_index].name = outs[j];
+            blobs_[(size_t)blob_index].producer = (int)i;
+            layer->tops[j] = blob_index++;
+        }
+        if (layer->parse_param(opt, pd) != 0) { error_ = "ParamDict load " + layer->name + " failed"; return -1; }
+        layer->bottom_shapes.resize(ins.size());
+        for (size_t j = 0; j < ins.size(); ++j) layer->bottom_shapes[j] = blobs_[(size_t)layer->bottoms[j]].shape;
+        layer->top_shapes.resize(outs.size());
+        if (layer->compute_output_shape(pd) != 0) { error_ = "Layer " + layer->name + " output shape undefined"; return -1; }
+        Tensor hints = pd.get(OUTPUT_SHAPE_HINT, Tensor());
+        if (hints.defined()) {
+            const int64_t rows = hints.size(0);
+            for (size_t j = 0; j < outs.size(); ++j) {
+                const int64_t r = rows > 1 ? (int64_t)j : 0;
+                const int* p = hints.data_ptr<int>() + r * 4;
+                blobs_[(size_t)layer->tops[j]].shape = shape_tensor(p[0], p[1], p[2], p[3]);
+                layer->top_shapes[j] = blobs_[(size_t)layer->tops[j]].shape;
+            }
+        }
+        if (layer->load_param(pd) != 0) { error_ = "Layer load " + layer->name + " failed"; return -1; }
+        if (mode == CompileMode::Initial) {
+            if (layer->init_model() != 0) { error_ = "init_model of " + layer->name + " failed"; return -1; }
+            const int rc = layer->create_pipeline(option);
+            if (rc != 0) { error_ = "create_pipeline of " + layer->name + " failed: " + ott_last_error(option.gpu); return rc; }
+        }
+    }
+    input_names_.clear();
+    output_names_.clear();
+    for (Layer* l : layers_)
+        if (l->type() == "Input") input_names_.push_back(blobs_[(size_t)l->tops[0]].name);
+    for (const Blob& b : blobs_)
+        if (b.producer != -1 && b.consumer == -1) output_names_.push_back(b.name);
+    return 0;
+}
+
+int Net::recreate_pipeline(int layer_index) {
+    if (layer_index < 0 || layer_index >= (int)layers_.size()) return -1;
+    const int rc = layers_[(size_t)layer_index]->create_pipeline(option);
+    if (rc != 0) error_ = std::string("create_pipeline failed: ") + ott_last_error(option.gpu);
+    return rc;
+}
+
+void Net::summary() const {
+    printf("=============================================================\n");
+    printf("Layer count: %d Blob count: %zu\n", (int)layers_.size(), blobs_.size());
+    for (const Layer* l : layers_) {
+        printf("%-16s %-24s", l->type().c_str(), l->name.c_str());
+        for (int t : l->tops) {
+            const Tensor& s = blobs_[(size_t)t].shape;
+            if (s.defined()) printf(" -> %s(%d,%d,%d,%d)", blobs_[(size_t)t].name.c_str(), s.data_ptr<int>()[0], s.data_ptr<int>()[1], s.data_ptr<int>()[2], s.data_ptr<int>()[3]);
+        }
+        printf("\n");
+    }
+}
+
+Extractor Net::create_extractor() const { return Extractor(this, blobs_.size()); }
+
+// Tensor/Net.cpp:350-378: recursive pull of missing bottoms
+int Net::forward_layer(int layer_index, std::vector<Tensor>& blob_tensors, const NetOption& opt) const {
+    if (layer_index < 0) { error_ = "blob has no producer and was not given as input"; return -1; }
+    const Layer* layer = layers_[(size_t)layer_index];
+    for (int b : layer->bottoms) {
+        if (!blob_tensors[(size_t)b].defined()) {
+            const int ret = forward_layer(blobs_[(size_t)b].producer, blob_tensors, opt);
+            if (ret != 0) return ret;
+        }
+    }
+    return do_forward_layer(layer, blob_tensors, opt);
+}
+
+// Tensor/Net.cpp:413-505. Every kernel of the layer is enqueued on the Net's stream; nothing waits here.
+int Net::do_forward_layer(const Layer* layer, std::vector<Tensor>& blob_tensors, const NetOption& opt) const {
+    if (layer->type() == "Input") return blob_tensors[(size_t)layer->tops[0]].defined() ? 0 : -1;
+    int ret = 0;
+    if (layer->one_blob_only) {
+        Tensor bottom = blob_tensors[(size_t)layer->bottoms[0]];
+        Tensor top;
+        if (opt.lightmode && layer->support_inplace && bottom.use_count() <= 2) {  // ours + the blob table's
+            top = bottom;
+            ret = layer->forward_inplace(top, opt);
+        } else {
+            ret = layer->forward(bottom, top, opt);
+        }
+        if (ret != 0) { error_ = "forward of layer " + layer->name + " failed: " + ott_last_error(opt.gpu); return ret; }
+        blob_tensors[(size_t)layer->tops[0]] = top;
+    } else {
+        std::vector<Tensor> bottoms(layer->bottoms.size()), tops(layer->tops.size());
+        for (size_t i = 0; i < bottoms.size(); ++i) bottoms[i] = blob_tensors[(size_t)layer->bottoms[i]];
+        ret = layer->forward(bottoms, tops, opt);
+        if (ret != 0) { error_ = "forward of layer " + layer->name + " failed: " + ott_last_error(opt.gpu); return ret; }
+        for (size_t i = 0; i < tops.size(); ++i) blob_tensors[(size_t)layer->tops[i]] = tops[i];
+    }
+    if (opt.lightmode)  // Tensor/Net.cpp:449-451: a consumed blob is dropped at once (the allocator reuses it stream-ordered)
+        for (int b : layer->bottoms) blob_tensors[(size_t)b].reset();
+    return 0;
+}
+
+// ---------------------------------------------------------------- Extractor (Tensor/Net.cpp:659-736)
+Extractor::Extractor(const Net* net, size_t blob_count) : net_(net), blob_tensors_(blob_count), option(net->option) {}
+
+void Extractor::clear() { for (auto& t : blob_tensors_) t.reset(); }
+
+int Extractor::input(const std::string& blob_name, const Tensor& in) {
+    const int idx = net_->find_blob_index_by_name(blob_name);
+    if (idx == -1) fprintf(stderr, "Input failed!\n");
+    return input(idx, in);
+}
+
+int Extractor::input(int blob_index, const Tensor& in) {
+    if (blob_index < 0 || blob_index >= (int)blob_tensors_.size() || !in.defined()) return -1;
+    if (in.device() == Device::CUDA) {
+        blob_tensors_[(size_t)blob_index] = in;
+        return 0;
+    }
+    if (in.scalar_type() != ScalarType::Float || in.dim() != 4) return -1;
+    Tensor dev = device_empty(option, in.sizes(), ScalarType::Float, Layout::NCHW);
+    if (!dev.defined()) return -100;
+    const int rc = ott_memcpy_h2d(option.gpu, dev.raw_data(), in.raw_data(), (size_t)in.numel() * 4);
+    if (rc != OTT_OK) return rc;
+    blob_tensors_[(size_t)blob_index] = dev;
+    return 0;
+}
+
+int Extractor::extract(const std::string& blob_name, Tensor& feat, int type) {
+    const int idx = net_->find_blob_index_by_name(blob_name);
+    if (idx == -1) fprintf(stderr, "Extract failed!\n");
+    return extract(idx, feat, type);
+}
+
+int Extractor::extract(int blob_index, Tensor& feat, int type) {
+    if (blob_index < 0 || blob_index >= (int)blob_tensors_.size()) return -1;
+    if (!blob_tensors_[(size_t)blob_index].defined()) {
+        const int ret = net_->forward_layer(net_->blobs_[(size_t)blob_index].producer, blob_tensors_, option);
+        if (ret != 0) return ret;
+    }
+    const Tensor& dev = blob_tensors_[(size_t)blob_index];
+    if (type != 0) { feat = dev; return 0; }
+    // plain host layout, like `feat.packing(1)` of the reference (Tensor/Net.cpp:729-731)
+    if (dev.layout() == Layout::NCHW) {
+        feat = empty(dev.sizes(), dev.scalar_type());
+        int rc = ott_memcpy_d2h(option.gpu, feat.raw_data(), dev.raw_data(), (size_t)dev.numel() * elementSize(dev.scalar_type()));
+        if (rc == OTT_OK) rc = ott_sync(option.gpu);
+        return rc;
+    }
+    const int n = (int)dev.size(0), c = (int)dev.size(1), h = (int)dev.size(2), w = (int)dev.size(3);
+    const int cp = ott_nhwc_channels(c);
+    const size_t es = elementSize(dev.scalar_type());
+    std::vector<char> tmp((size_t)n * h * w * cp * es);
+    int rc = ott_memcpy_d2h(option.gpu, tmp.data(), dev.raw_data(), tmp.size());
+    if (rc == OTT_OK) rc = ott_sync(option.gpu);
+    if (rc != OTT_OK) return rc;
+    feat = empty(dev.sizes(), dev.scalar_type());
+    char* dst = static_cast<char*>(feat.raw_data());
+    for (int b = 0; b < n; ++b)
+        for (int y = 0; y < h; ++y)
+            for (int x = 0; x < w; ++x)
+                for (int ch = 0; ch < c; ++ch)
+                    std::memcpy(dst + ((((size_t)b * c + ch) * h + y) * w + x) * es, tmp.data() + ((((size_t)b * h + y) * w + x) * cp + ch) * es, es);
+    return 0;
+}
+
+}  // namespace otter

@@ -17,9 +17,11 @@ def lib():
 
 
 def declared_symbols():
-    text = (ROOT / "include" / "otter_b200.h").read_text()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(ott_[a-z0-9_]+)\s*\(", text)))
+    names = set()
+    for header in sorted((ROOT / "include").glob("*.h")):
+        text = re.sub(r"/\*.*?\*/", "", header.read_text(), flags=re.S)
+        names |= set(re.findall(r"\b(ott_[a-z0-9_]+)\s*\(", text))
+    return sorted(names)
 
 
 def test_header_and_binding_list_agree(lib):
