@@ -242,3 +242,83 @@ class ConvInt8:
         if self.h:
             self.ctx.lib.ott_conv_int8_destroy(self.ctx.h, self.h)
             self.h = None
+
+
+class Net:
+    """ctypes wrapper over include/otter_b200_net.h: a Net built from the reference's LayerOption key/value pairs."""
+
+    def __init__(self, device: int = 0):
+        self.lib = library()
+        h = C.c_void_p()
+        rc = self.lib.ott_net_create(device, C.byref(h))
+        if rc != 0:
+            raise OtterB200Error(rc, "ott_net_create failed")
+        self.h = h
+        self.layers = []
+
+    def check(self, rc: int):
+        if rc != 0:
+            raise OtterB200Error(rc, self.lib.ott_net_last_error(self.h).decode(errors="replace"))
+
+    def add_layer(self, **options):
+        """options as in the .otter format, e.g. type="Convolution", name="conv1", input="data", out_channels=24, ..."""
+        self.layers.append(dict(options))
+        text = ";".join(f"{k}={v}" for k, v in options.items())
+        self.check(self.lib.ott_net_add_layer(self.h, text.encode()))
+
+    def compile(self):
+        self.check(self.lib.ott_net_compile(self.h))
+
+    def context(self) -> "Context":
+        ctx = Context.__new__(Context)
+        ctx.lib, ctx.h, ctx.device = self.lib, C.c_void_p(self.lib.ott_net_context(self.h)), None
+        return ctx
+
+    def layer_infos(self):
+        out = []
+        for i in range(self.lib.ott_net_layer_count(self.h)):
+            t, n = C.create_string_buffer(64), C.create_string_buffer(128)
+            g = (C.c_int * 12)()
+            self.check(self.lib.ott_net_layer_info(self.h, i, t, 64, n, 128, g))
+            keys = ("cin", "cout", "kh", "kw", "sh", "sw", "ph", "pw", "groups", "bias_term", "int8_scale_term", "act_type")
+            out.append({"type": t.value.decode(), "name": n.value.decode(), **dict(zip(keys, list(g)))})
+        return out
+
+    def blob_shape(self, name: str):
+        s = (C.c_int * 4)()
+        self.check(self.lib.ott_net_blob_shape(self.h, name.encode(), s))
+        return tuple(s)
+
+    def set_conv_params(self, layer: str, weight, bias, w_scales, in_scales, out_scales=None):
+        weight = np.ascontiguousarray(weight, dtype=np.int8)
+        bias = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+        w_scales = np.ascontiguousarray(w_scales, dtype=np.float32)
+        in_scales = np.ascontiguousarray(in_scales, dtype=np.float32)
+        out_scales = None if out_scales is None else np.ascontiguousarray(out_scales, dtype=np.float32)
+        self.check(self.lib.ott_net_set_conv_params(self.h, layer.encode(), _np_ptr(weight), _np_ptr(bias), _np_ptr(w_scales),
+                                                    _np_ptr(in_scales), in_scales.size, _np_ptr(out_scales),
+                                                    0 if out_scales is None else out_scales.size))
+
+    def forward_raw(self, input_blob: str, in_ptr, in_on_device: bool, shape, out_blobs, out_ptrs=None):
+        n, c, h, w = shape
+        names = (C.c_char_p * len(out_blobs))(*[b.encode() for b in out_blobs])
+        ptrs = None
+        if out_ptrs is not None:
+            ptrs = (C.c_void_p * len(out_blobs))(*out_ptrs)
+        self.check(self.lib.ott_net_forward(self.h, input_blob.encode(), in_ptr, 1 if in_on_device else 0, n, c, h, w, len(out_blobs),
+                                            names, ptrs))
+
+    def forward(self, input_blob: str, x: np.ndarray, out_blobs, dtypes=None):
+        """Host fp32 NCHW in, list of host arrays out (fp32 NCHW, or int8 NCHW for blobs listed in dtypes as np.int8)."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        outs = []
+        for i, b in enumerate(out_blobs):
+            dt = np.float32 if not dtypes else dtypes[i]
+            outs.append(np.empty(self.blob_shape(b)[:0] + (x.shape[0],) + self.blob_shape(b)[1:], dtype=dt))
+        self.forward_raw(input_blob, _np_ptr(x), False, x.shape, out_blobs, [o.ctypes.data for o in outs])
+        return outs
+
+    def close(self):
+        if self.h:
+            self.lib.ott_net_destroy(self.h)
+            self.h = None

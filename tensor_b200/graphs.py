@@ -1,0 +1,186 @@
+"""Benchmark graphs as lists of the reference's LayerOption dictionaries, plus seeded parameters.
+
+`shufflenetv2_layers` writes ShuffleNetV2-1.0x in the same layer vocabulary and wiring as the reference's
+own int8 graph (benchmark/nanodet-plus-m-1.5x_416_int8_fused.otter: stem convolution -> MaxPool -> stages of
+[Crop, 1x1 (int8 out) -> depthwise 3x3 (int8 out) -> 1x1 (fp32 out), Concat, ChannelShuffle]), so the list can be
+fed to `Net.add_layer` here or written out as a .otter file for the reference.
+
+`walk` executes such a list on host numpy arrays with a caller-supplied convolution function. It is set-up
+and test plumbing, not a compute path of the library: the parity tests pass the CPU checker as the convolution,
+`calibrate` passes the GPU library's own layer to pick activation scales from one sample image.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+ACT_CODE = {"": 0, "Relu": 1, "LRelu": 2, "Relu6": 3}
+
+
+def _conv(name, inp, cout, k, stride, pad, term, act="", groups=1):
+    d = dict(type="Convolution", name=name, input=inp, output=name, out_channels=cout, kernel_h=k, kernel_w=k, stride_h=stride,
+             stride_w=stride, padding_h=pad, padding_w=pad, dilation_h=1, dilation_w=1, int8_scale_term=term, bias_term="true")
+    if groups != 1:
+        d["groups"] = groups
+    if act:
+        d["activation"] = act
+        if act == "LRelu":
+            d["activation_params"] = "0.100000"
+    return d
+
+
+def shufflenetv2_layers(height=320, width=320, batch=1, stage_repeats=(4, 8, 4), stage_channels=(116, 232, 464), stem=24, last=1024,
+                        act="Relu"):
+    """ShuffleNetV2-1.0x backbone (conv1 3x3 s2 24, maxpool, stages [4,8,4] x [116,232,464], conv5 1x1 1024), quantized
+    the way the reference's int8 graphs are: int8 only flows conv -> conv inside a branch, fp32 everywhere else."""
+    L = [dict(type="Input", name="data", output="data", batchsize=batch, channel=3, height=height, width=width)]
+    L.append(_conv("conv1", "data", stem, 3, 2, 1, 2, act))
+    L.append(dict(type="MaxPool", name="pool1", input="conv1", output="pool1", kernel_h=3, kernel_w=3, stride_h=2, stride_w=2,
+                  padding_h=1, padding_w=1))
+    prev, cin = "pool1", stem
+    for si, (rep, cout) in enumerate(zip(stage_repeats, stage_channels)):
+        half = cout // 2
+        s = f"s{si + 2}"
+        # down-sampling unit: both branches see the whole input
+        L.append(_conv(f"{s}b0_l_dw", prev, cin, 3, 2, 1, 101, "", groups=cin))
+        L.append(_conv(f"{s}b0_l_pw", f"{s}b0_l_dw", half, 1, 1, 0, 2, act))
+        L.append(_conv(f"{s}b0_r_pw1", prev, half, 1, 1, 0, 102, act))
+        L.append(_conv(f"{s}b0_r_dw", f"{s}b0_r_pw1", half, 3, 2, 1, 101, "", groups=half))
+        L.append(_conv(f"{s}b0_r_pw2", f"{s}b0_r_dw", half, 1, 1, 0, 2, act))
+        L.append(dict(type="Concat", name=f"{s}b0_cat", input=f"{s}b0_l_pw, {s}b0_r_pw2", output=f"{s}b0_cat", axis=1))
+        L.append(dict(type="ChannelShuffle", name=f"{s}b0_shuf", input=f"{s}b0_cat", output=f"{s}b0_shuf", groups=2))
+        prev = f"{s}b0_shuf"
+        for bi in range(1, rep):
+            b = f"{s}b{bi}"
+            L.append(dict(type="Crop", name=f"{b}_keep", input=prev, output=f"{b}_keep", start=0, end=half, axis=1))
+            L.append(dict(type="Crop", name=f"{b}_work", input=prev, output=f"{b}_work", start=half, end=cout, axis=1))
+            L.append(_conv(f"{b}_pw1", f"{b}_work", half, 1, 1, 0, 102, act))
+            L.append(_conv(f"{b}_dw", f"{b}_pw1", half, 3, 1, 1, 101, "", groups=half))
+            L.append(_conv(f"{b}_pw2", f"{b}_dw", half, 1, 1, 0, 2, act))
+            L.append(dict(type="Concat", name=f"{b}_cat", input=f"{b}_keep, {b}_pw2", output=f"{b}_cat", axis=1))
+            L.append(dict(type="ChannelShuffle", name=f"{b}_shuf", input=f"{b}_cat", output=f"{b}_shuf", groups=2))
+            prev = f"{b}_shuf"
+        cin = cout
+    L.append(_conv("conv5", prev, last, 1, 1, 0, 2, act))
+    return L
+
+
+def conv_geometry(layers):
+    """name -> dict(cin, cout, k, stride, pad, groups, term, act) for every Convolution, with cin from shape inference."""
+    chans = {}
+    geo = {}
+    for l in layers:
+        t = l["type"]
+        ins = [s.strip() for s in str(l.get("input", "")).split(",") if s.strip()]
+        if t == "Input":
+            chans[l["output"]] = int(l["channel"])
+        elif t == "Convolution":
+            cin = chans[ins[0]]
+            geo[l["name"]] = dict(cin=cin, cout=int(l["out_channels"]), k=int(l["kernel_h"]), stride=int(l["stride_h"]), pad=int(l["padding_h"]),
+                                  groups=int(l.get("groups", 1)), term=int(l["int8_scale_term"]), act=ACT_CODE[l.get("activation", "")],
+                                  act_param0=0.1 if l.get("activation") == "LRelu" else 0.0, input=ins[0])
+            chans[l["output"]] = int(l["out_channels"])
+        elif t == "Concat":
+            chans[l["output"]] = sum(chans[i] for i in ins)
+        elif t == "Crop":
+            chans[l["output"]] = int(l["end"]) - int(l["start"])
+        else:
+            chans[l["output"]] = chans[ins[0]]
+    return geo
+
+
+def make_params(layers, seed=0x0771E5):
+    """Seeded weights per Convolution: N(0, 0.05) (depthwise N(0, 0.1)) quantized per output channel, bias N(0, 0.01).
+    Activation scales are placeholders until `calibrate` fills them."""
+    rng = np.random.default_rng(seed)
+    params = {}
+    for name, g in conv_geometry(layers).items():
+        dw = g["groups"] > 1
+        wf = rng.normal(0.0, 0.1 if dw else 0.05, size=(g["cout"], g["cin"] // g["groups"], g["k"], g["k"])).astype(np.float32)
+        amax = np.abs(wf).reshape(g["cout"], -1).max(axis=1)
+        amax[amax == 0] = 1.0
+        w_scales = (np.float32(127.0) / amax).astype(np.float32)
+        params[name] = dict(weight=np.clip(np.rint(wf * w_scales[:, None, None, None]), -127, 127).astype(np.int8),
+                            bias=rng.normal(0.0, 0.01, size=(g["cout"],)).astype(np.float32), w_scales=w_scales,
+                            in_scales=np.ones((g["groups"] if dw else 1,), np.float32),
+                            out_scales=np.ones((g["groups"] if dw else 1,), np.float32) if g["term"] > 100 else None)
+    return params
+
+
+def maxpool_nchw(x, k, s, p, pad_zero):
+    n, c, h, w = x.shape
+    oh, ow = (h + 2 * p - k) // s + 1, (w + 2 * p - k) // s + 1
+    fill = np.float32(0.0) if pad_zero else np.float32(-np.inf)
+    xp = np.full((n, c, h + 2 * p, w + 2 * p), fill, np.float32)
+    xp[:, :, p:p + h, p:p + w] = x
+    out = np.full((n, c, oh, ow), -np.inf, np.float32)
+    for ky in range(k):
+        for kx in range(k):
+            out = np.maximum(out, xp[:, :, ky:ky + s * oh:s, kx:kx + s * ow:s][:, :, :oh, :ow])
+    return out
+
+
+def walk(layers, x, conv_fn, want=None, on_conv=None):
+    """Run the graph on host arrays. conv_fn(name, geometry, input_array) -> output array (fp32 NCHW, or int8 NCHW for
+    int8_scale_term > 100). Returns {blob name: array} for the names in `want` (default: the last layer's output)."""
+    geo = conv_geometry(layers)
+    blobs = {}
+    for l in layers:
+        t = l["type"]
+        ins = [s.strip() for s in str(l.get("input", "")).split(",") if s.strip()]
+        out = l["output"]
+        if t == "Input":
+            blobs[out] = x
+        elif t == "Convolution":
+            if on_conv:
+                on_conv(l["name"], geo[l["name"]], blobs[ins[0]])
+            blobs[out] = conv_fn(l["name"], geo[l["name"]], blobs[ins[0]])
+        elif t == "MaxPool":
+            a = blobs[ins[0]]
+            k, s, p = int(l["kernel_h"]), int(l["stride_h"]), int(l["padding_h"])
+            # the reference packs fp32 blobs with C % 4 == 0 and its packed 3x3 s2 kernels pad with zeros
+            blobs[out] = maxpool_nchw(a, k, s, p, pad_zero=(a.shape[1] % 4 == 0 and k == 3 and s == 2))
+        elif t == "Concat":
+            blobs[out] = np.concatenate([blobs[i] for i in ins], axis=1)
+        elif t == "Crop":
+            blobs[out] = np.ascontiguousarray(blobs[ins[0]][:, int(l["start"]):int(l["end"])])
+        elif t == "ChannelShuffle":
+            a = blobs[ins[0]]
+            g = int(l["groups"])
+            n, c, h, w = a.shape
+            blobs[out] = np.ascontiguousarray(a.reshape(n, g, c // g, h, w).transpose(0, 2, 1, 3, 4).reshape(n, c, h, w))
+        elif t == "ShortCut":
+            blobs[out] = blobs[ins[0]] + blobs[ins[1]]
+        elif t in ("Relu", "LRelu", "Relu6"):
+            a = blobs[ins[0]]
+            blobs[out] = {"Relu": lambda v: np.maximum(v, 0), "Relu6": lambda v: np.clip(v, 0, 6),
+                          "LRelu": lambda v: np.where(v < 0, v * np.float32(l.get("alpha", 0.1)), v)}[t](a).astype(np.float32)
+        else:
+            raise ValueError(f"layer type {t} not handled")
+    names = want or [layers[-1]["output"]]
+    return {k: blobs[k] for k in names}
+
+
+def calibrate(layers, params, x, conv_f32_fn):
+    """Fill in_scales / out_scales from one sample batch x (fp32 NCHW): 127 / max|blob| per tensor, walking the graph in
+    order. conv_f32_fn(name, geometry, params_of_layer, input_array, as_float) runs one layer; with as_float=True it must
+    return the layer's fp32 output even for a requantizing layer (int8_scale_term - 100), which gives the range its int8
+    output scale is taken from; the consumer of an int8 blob then uses that same scale as its input scale."""
+    scale_of_int8_blob = {}
+
+    def conv_fn(name, g, a):
+        p = params[name]
+        n_s = g["groups"] if g["groups"] > 1 else 1
+        if a.dtype == np.int8:
+            s_in = scale_of_int8_blob[g["input"]]
+        else:
+            s_in = np.float32(127.0) / np.float32(max(float(np.abs(a).max()), 1e-6))
+        p["in_scales"] = np.full((n_s,), s_in, np.float32)
+        if g["term"] > 100:
+            y = conv_f32_fn(name, g, p, a, True)
+            s_out = np.float32(127.0) / np.float32(max(float(np.abs(y).max()), 1e-6))
+            p["out_scales"] = np.full((n_s,), s_out, np.float32)
+            scale_of_int8_blob[name] = s_out
+        return conv_f32_fn(name, g, p, a, False)
+
+    walk(layers, x, conv_fn)
+    return params

@@ -1,0 +1,63 @@
+"""GPU: graphs built through the Net / Layer API mirror against the layer-by-layer CPU checker, bit-exact."""
+import numpy as np
+import pytest
+
+from tensor_b200 import graphs
+
+pytestmark = pytest.mark.gpu
+
+
+def bits(a):
+    return a.view(np.int32) if a.dtype == np.float32 else a
+
+
+def test_single_convolution_layer_net():
+    from graph_support import build_net, oracle_conv, oracle_conv_for_calibration
+    L = [dict(type="Input", name="data", output="data", channel=64, height=14, width=14),
+         dict(type="Convolution", name="c1", input="data", output="c1", out_channels=128, kernel=1, int8_scale_term=102, activation="Relu"),
+         dict(type="Convolution", name="c2", input="c1", output="c2", out_channels=128, kernel=3, padding=1, groups=128, int8_scale_term=101),
+         dict(type="Convolution", name="c3", input="c2", output="c3", out_channels=64, kernel=1, int8_scale_term=2, activation="LRelu",
+              activation_params="0.100000")]
+    for l in L[1:]:  # the test helpers read the long option names
+        k = l.pop("kernel")
+        p = l.pop("padding", 0)
+        l.update(kernel_h=k, kernel_w=k, stride_h=1, stride_w=1, padding_h=p, padding_w=p)
+    params = graphs.make_params(L)
+    x = np.random.default_rng(11).uniform(-1, 1, size=(3, 64, 14, 14)).astype(np.float32)
+    graphs.calibrate(L, params, x, oracle_conv_for_calibration)
+    want = graphs.walk(L, x, oracle_conv(params), want=["c1", "c2", "c3"])
+    net = build_net(L, params)
+    got = net.forward("data", x, ["c1", "c2", "c3"], dtypes=[np.int8, np.int8, np.float32])
+    for name, g in zip(["c1", "c2", "c3"], got):
+        assert np.array_equal(bits(g), bits(want[name])), name
+    net.close()
+
+
+def test_shufflenetv2_small_input_bit_exact():
+    from graph_support import build_net, oracle_conv, oracle_conv_for_calibration
+    L = graphs.shufflenetv2_layers(64, 64, batch=2)
+    params = graphs.make_params(L)
+    x = np.random.default_rng(12).uniform(0, 1, size=(2, 3, 64, 64)).astype(np.float32)
+    graphs.calibrate(L, params, x[:1], oracle_conv_for_calibration)
+    probes = ["pool1", "s2b0_shuf", "s2b3_shuf", "s3b0_shuf", "s4b3_shuf", "conv5"]
+    want = graphs.walk(L, x, oracle_conv(params), want=probes)
+    net = build_net(L, params)
+    got = net.forward("data", x, probes)
+    for name, g in zip(probes, got):
+        assert g.shape == want[name].shape, name
+        assert np.array_equal(bits(g), bits(want[name])), f"blob {name} differs"
+    # the default (lightmode) single-output path gives the same final blob
+    again = net.forward("data", x, ["conv5"])[0]
+    assert np.array_equal(bits(again), bits(want["conv5"]))
+    net.close()
+
+
+def test_unknown_layer_type_is_an_error_not_an_exit():
+    from tensor_b200 import Net, OtterB200Error
+    net = Net(0)
+    net.add_layer(type="Input", name="d", output="d", channel=3, height=8, width=8)
+    net.add_layer(type="NoSuchLayer", name="x", input="d")
+    with pytest.raises(OtterB200Error) as e:
+        net.compile()
+    assert "Unknown layer type" in str(e.value)
+    net.close()

@@ -1,0 +1,83 @@
+"""CPU tests of the graph plumbing: the numpy glue layers against the compiled reference's own layers, shape
+inference of the ShuffleNetV2 description, and the calibration walk."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from support import _p, have_ref, load_ref
+from tensor_b200 import graphs
+
+
+def ref_layer(type_, opts, ins, packed=1):
+    ref = load_ref()
+    n = len(ins)
+    arr = (C.POINTER(C.c_float) * n)(*[_p(np.ascontiguousarray(a), C.c_float) for a in ins])
+    shapes = np.array([d for a in ins for d in a.shape], np.int32)
+    osh = np.zeros(4, np.int32)
+    assert ref.ref_layer_forward(type_.encode(), opts.encode(), n, arr, _p(shapes, C.c_int), packed, None, _p(osh, C.c_int)) == 0
+    out = np.empty(tuple(osh), np.float32)
+    assert ref.ref_layer_forward(type_.encode(), opts.encode(), n, arr, _p(shapes, C.c_int), packed, _p(out, C.c_float), _p(osh, C.c_int)) == 0
+    return out
+
+
+@pytest.mark.skipif(not have_ref(), reason="oracle/_ref/libotter_ref.so not built")
+def test_numpy_glue_equals_reference_layers():
+    rng = np.random.default_rng(5)
+    x = (rng.normal(size=(1, 24, 17, 19)) - 0.7).astype(np.float32)  # mostly negative: zero padding must win at the border
+    layers = [dict(type="Input", name="d", output="d", channel=24, height=17, width=19),
+              dict(type="MaxPool", name="p", input="d", output="p", kernel_h=3, kernel_w=3, stride_h=2, stride_w=2, padding_h=1, padding_w=1)]
+    want = ref_layer("MaxPool", "kernel_h=3;kernel_w=3;stride_h=2;stride_w=2;padding_h=1;padding_w=1", [x])
+    assert np.array_equal(graphs.walk(layers, x, None)["p"], want)
+    x5 = np.ascontiguousarray(x[:, :5])  # 5 channels: not packed by the reference -> plain kernel, padding never wins
+    want5 = ref_layer("MaxPool", "kernel_h=3;kernel_w=3;stride_h=2;stride_w=2;padding_h=1;padding_w=1", [x5])
+    layers[0]["channel"] = 5
+    assert np.array_equal(graphs.walk(layers, x5, None)["p"], want5)
+    y = rng.normal(size=(1, 12, 4, 6)).astype(np.float32)
+    z = rng.normal(size=(1, 12, 4, 6)).astype(np.float32)
+    g = [dict(type="Input", name="a", output="a", channel=12, height=4, width=6),
+         dict(type="ChannelShuffle", name="s", input="a", output="s", groups=2),
+         dict(type="Crop", name="c", input="s", output="c", start=6, end=12, axis=1)]
+    got = graphs.walk(g, y, None, want=["s", "c"])
+    assert np.array_equal(got["s"], ref_layer("ChannelShuffle", "groups=2", [y]))
+    assert np.array_equal(got["c"], ref_layer("Crop", "start=6;end=12;axis=1", [got["s"]]))
+    assert np.array_equal(np.concatenate([y, z], 1), ref_layer("Concat", "axis=1", [y, z]))
+    assert np.array_equal(y + z, ref_layer("ShortCut", "", [y, z]))
+    assert np.array_equal(np.where(y < 0, y * np.float32(0.1), y), ref_layer("LRelu", "alpha=0.1", [y]))
+    assert np.array_equal(np.clip(y * 4, 0, 6), ref_layer("Relu6", "", [y * 4]))
+
+
+def test_shufflenetv2_description():
+    L = graphs.shufflenetv2_layers(320, 320)
+    geo = graphs.conv_geometry(L)
+    assert len(geo) == 2 + 3 * 5 + (3 + 7 + 3) * 3  # stem + conv5, 5 convs per down-sampling unit, 3 per basic unit
+    assert geo["conv1"]["cin"] == 3 and geo["conv5"]["cin"] == 464 and geo["conv5"]["cout"] == 1024
+    assert geo["s2b0_l_dw"]["groups"] == 24 and geo["s3b1_pw1"]["cin"] == 116 and geo["s4b3_dw"]["groups"] == 232
+    # multiply-accumulates per image at 320x320 (ops = 2x): the figure the images/s bench converts to TOP/s
+    macs, h = 0, {"data": 320}
+    for l in L:
+        ins = [s.strip() for s in str(l.get("input", "")).split(",") if s.strip()]
+        if l["type"] == "Input":
+            continue
+        hin = h[ins[0]]
+        if l["type"] in ("Convolution", "MaxPool"):
+            k, s, p = int(l["kernel_h"]), int(l["stride_h"]), int(l["padding_h"])
+            h[l["output"]] = (hin + 2 * p - k) // s + 1
+            if l["type"] == "Convolution":
+                g = geo[l["name"]]
+                macs += h[l["output"]] ** 2 * g["cout"] * (g["cin"] // g["groups"]) * k * k
+        else:
+            h[l["output"]] = hin
+    assert 2.5e8 < macs < 3.5e8, macs
+
+
+def test_calibration_walk_gives_usable_scales():
+    from graph_support import oracle_conv, oracle_conv_for_calibration
+    L = graphs.shufflenetv2_layers(32, 32, stage_repeats=(2, 2, 2))
+    params = graphs.make_params(L)
+    x = np.random.default_rng(3).uniform(0, 1, size=(1, 3, 32, 32)).astype(np.float32)
+    graphs.calibrate(L, params, x, oracle_conv_for_calibration)
+    out = graphs.walk(L, x, oracle_conv(params))["conv5"]
+    assert out.shape == (1, 1024, 1, 1) and np.isfinite(out).all() and (out != 0).mean() > 0.2
+    # an int8 blob's producer and consumer agree on its scale
+    assert params["s2b1_pw1"]["out_scales"][0] == params["s2b1_dw"]["in_scales"][0]
