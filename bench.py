@@ -181,7 +181,7 @@ class _Desc(C.Structure):
                                        "int8_scale_term", "act_type")] + [("act_param0", C.c_float)]
 
 
-def cpu_reference_time(wl, images, warmup=1, iters=None):
+def cpu_reference_time(wl, images, warmup=1, iters=None, packed=1, force_port=False):
     """Time the reference's CPU int8 ConvolutionLayer on `images` single-image forwards (its int8 path is
     batch-1), all host threads. Returns (seconds per image, kind, cores)."""
     ref_so = ROOT / "oracle" / "_ref" / "libotter_ref.so"
@@ -197,14 +197,14 @@ def cpu_reference_time(wl, images, warmup=1, iters=None):
     else:
         x = rng.integers(-127, 128, size=(1, wl["cin"], wl["h"], wl["w"]), dtype=np.int8)
         xf, xs = None, fp(x, C.c_int8)
-    if ref_so.exists():
+    if ref_so.exists() and not force_port:
         lib = C.CDLL(str(ref_so))
         lib.ref_conv_int8_time_ms.restype = C.c_double
         lib.ref_max_threads.restype = C.c_int
         cores = lib.ref_max_threads()
         mean = C.c_double()
         best = lib.ref_conv_int8_time_ms(C.byref(d), fp(weight, C.c_int8), fp(bias, C.c_float), fp(w_scales, C.c_float), fp(in_scales, C.c_float),
-                                         in_scales.size, fp(out_scales, C.c_float), out_scales.size, xf, xs, wl["h"], wl["w"], 1, warmup, images,
+                                         in_scales.size, fp(out_scales, C.c_float), out_scales.size, xf, xs, wl["h"], wl["w"], packed, warmup, images,
                                          C.byref(mean))
         if best < 0:
             raise RuntimeError("reference forward failed")
@@ -441,18 +441,253 @@ def run_gpu_arm(args, wl):
         dist.destroy_process_group()
 
 
+# ----------------------------------------------------------------------------------------------------
+# whole-graph workload: ShuffleNetV2-1.0x int8 backbone (configuration 4), images/s
+
+NET_WORKLOADS = {"shufflenetv2_320": dict(height=320, width=320, batch=256)}
+
+
+def _layer_wl(g, hw, in_f32):
+    """A graph convolution as a WORKLOADS-style dictionary (for the CPU reference timing)."""
+    return dict(cin=g["cin"], cout=g["cout"], k=g["k"], stride=g["stride"], pad=g["pad"], groups=g["groups"], n=1, h=hw[0], w=hw[1],
+                term=g["term"], act=g["act"], in_f32=in_f32, w_std=0.1 if g["groups"] > 1 else 0.05)
+
+
+def net_cpu_reference_time(layers, height, width, reps=2):
+    """Seconds per image of the reference's CPU int8 path, summed over the graph's convolution layers, each timed alone
+    on one image (a whole-Net run of this graph is impossible in the reference: its packed path corrupts memory on the
+    58/116-channel depthwise layers and miscomputes the 58/116-wide pointwise ones). Per layer the path that is valid
+    for its widths is used: packed when Cin%8==0 and Cout%4==0 (and the stem), unpacked for other dense layers, the C
+    restatement for depthwise layers whose channel count is not a multiple of 8. Glue layers are not timed."""
+    from tensor_b200 import graphs
+    geo = graphs.conv_geometry(layers)
+    hws, _ = graphs.conv_input_hw(layers, height, width)
+    int8_blobs = {n for n, g in geo.items() if g["term"] > 100}
+    total, how, cores, kind = 0.0, {"packed": 0, "unpacked": 0, "port": 0}, 1, "reference"
+    for name, g in geo.items():
+        wl = _layer_wl(g, hws[name], in_f32=g["input"] not in int8_blobs)
+        dw = g["groups"] > 1
+        if dw and g["cin"] % 8 != 0:
+            t, k, cores_l = cpu_reference_time(wl, images=reps, warmup=1, force_port=True)
+            how["port"] += 1
+        elif dw or (g["cin"] % 8 == 0 and g["cout"] % 4 == 0) or g["cin"] == 3:
+            t, k, cores_l = cpu_reference_time(wl, images=reps, warmup=1, packed=1)
+            how["packed"] += 1
+        else:
+            t, k, cores_l = cpu_reference_time(wl, images=reps, warmup=1, packed=0)
+            how["unpacked"] += 1
+        if k == "port" and not (dw and g["cin"] % 8 != 0):
+            kind = "port"
+        cores = max(cores, cores_l)
+        total += t
+    return total, how, cores, kind
+
+
+def run_net_reference_arm(args, cfg):
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    from tensor_b200 import graphs
+    layers = graphs.shufflenetv2_layers(cfg["height"], cfg["width"], batch=1)
+    secs = []
+    for i in range(args.warmup + args.steps):
+        t, how, cores, kind = net_cpu_reference_time(layers, cfg["height"], cfg["width"], reps=1)
+        if i >= args.warmup:
+            secs.append(t)
+    per_img = float(np.mean(secs))
+    sample = (f"one image per step: sum of the {sum(how.values())} convolution layers timed one by one on the reference's CPU int8 path "
+              f"({how['packed']} packed, {how['unpacked']} unpacked, {how['port']} depthwise layers with C%8!=0 on the C restatement because the "
+              f"reference cannot run them); glue layers not included; OpenMP {cores} threads")
+    value = 1.0 / per_img
+    print(json.dumps({
+        "impl": "reference", "metric": "shufflenetv2_int8_images_per_s", "value": value, "unit": "images/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_img * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "s8xs8->s32", "data": "synthetic",
+        "config": {"workload": args.workload, "input": f"3x{cfg['height']}x{cfg['width']} fp32", "images_per_step": 1},
+        "cpu_baseline": {"value": value, "unit": "images/s", "cores": cores, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def build_calibrated_net(cfg, batch, device, seed=0x0771E5):
+    """ShuffleNetV2 Net on `device` with seeded weights and activation scales calibrated on one synthetic image, the
+    convolutions of the calibration walk running through the GPU library's own layer objects."""
+    from tensor_b200 import F32_NCHW, S8_NHWC, ConvInt8, Context, Net, graphs, nhwc_channels as nc
+    layers = graphs.shufflenetv2_layers(cfg["height"], cfg["width"], batch=batch)
+    params = graphs.make_params(layers, seed)
+    x1 = np.random.default_rng(seed).random(size=(1, 3, cfg["height"], cfg["width"]), dtype=np.float32)
+    with Context(device) as ctx:
+        def conv(name, g, p, a, as_float):
+            term = g["term"] - 100 if (as_float and g["term"] > 100) else g["term"]
+            layer = ConvInt8(ctx, cin=g["cin"], cout=g["cout"], kh=g["k"], kw=g["k"], sh=g["stride"], sw=g["stride"], ph=g["pad"], pw=g["pad"],
+                             groups=g["groups"], bias_term=1, int8_scale_term=term, act_type=g["act"], act_param0=g["act_param0"],
+                             weight=p["weight"], bias=p["bias"], w_scales=p["w_scales"], in_scales=p["in_scales"],
+                             out_scales=p["out_scales"] if term > 100 else None)
+            if a.dtype == np.int8:
+                xin = np.zeros((a.shape[0], a.shape[2], a.shape[3], nc(a.shape[1])), np.int8)
+                xin[..., :a.shape[1]] = a.transpose(0, 2, 3, 1)
+                in_dtype = S8_NHWC
+            else:
+                xin, in_dtype = a, F32_NCHW
+            y = layer.forward_host(xin, in_dtype, S8_NHWC if term > 100 else F32_NCHW)
+            layer.close()
+            if term > 100:
+                y = np.ascontiguousarray(y[..., :g["cout"]].transpose(0, 3, 1, 2))
+            return y
+        graphs.calibrate(layers, params, x1, conv)
+    net = Net(device)
+    for l in layers:
+        net.add_layer(**l)
+    net.compile()
+    for name, p in params.items():
+        net.set_conv_params(name, p["weight"], p["bias"], p["w_scales"], p["in_scales"], p["out_scales"])
+    return net, layers
+
+
+def run_net_gpu_arm(args, cfg):
+    from tensor_b200 import graphs, library
+    library()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    n, H, W = (args.batch or cfg["batch"]), cfg["height"], cfg["width"]
+    net, layers = build_calibrated_net(cfg, n, local_rank)
+    ctx = net.context()
+    lib = ctx.lib
+    _, macs = graphs.conv_input_hw(layers, H, W)
+    out_shape = (n,) + net.blob_shape("conv5")[1:]
+    in_bytes, out_bytes = n * 3 * H * W * 4, int(np.prod(out_shape)) * 4
+    hin, hout = C.c_void_p(), C.c_void_p()
+    assert lib.ott_host_alloc(in_bytes, C.byref(hin)) == 0 and lib.ott_host_alloc(out_bytes, C.byref(hout)) == 0
+    host_in = np.ctypeslib.as_array(C.cast(hin, C.POINTER(C.c_float)), shape=(n, 3, H, W))
+    rng = np.random.default_rng(4321 + rank)
+    for i in range(0, n, 16):
+        host_in[i:i + 16] = rng.random(size=host_in[i:i + 16].shape, dtype=np.float32)
+    din = ctx.malloc(in_bytes)
+    ctx.check(lib.ott_memcpy_h2d(ctx.h, C.c_void_p(din), hin, in_bytes))
+    ctx.sync()
+    shape = (n, 3, H, W)
+
+    def step():
+        net.forward_raw("data", C.c_void_p(din), True, shape, ["conv5"], None)
+
+    def barrier():
+        ctx.sync()
+        if dist is not None:
+            dist.barrier()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    e0, e1 = ctx.event(), ctx.event()
+    l0 = ctx.launch_count()
+    barrier()
+    ctx.record(e0)
+    for _ in range(args.steps):
+        step()
+    ctx.record(e1)
+    barrier()
+    step_ms = ctx.elapsed_ms(e0, e1) / args.steps
+    launches = ctx.launch_count() - l0
+    clocks = sampler.stop() if rank == 0 else None
+
+    # per-layer device times (events around every layer; serialised) -> the dominant layer and kernel shares
+    prof = net.profile("data", C.c_void_p(din), True, shape, "conv5")
+    prof = net.profile("data", C.c_void_p(din), True, shape, "conv5")
+
+    # end to end: host fp32 images in (pinned), host fp32 features out, every step
+    e2e_steps = max(1, min(args.steps, args.e2e_steps))
+    names = ["conv5"]
+    net.forward_raw("data", hin, False, shape, names, [hout.value])
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        net.forward_raw("data", hin, False, shape, names, [hout.value])
+    barrier()
+    e2e_s = (time.perf_counter() - t0) / e2e_steps
+
+    if dist is not None:
+        import torch
+        t = torch.tensor([step_ms, e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        step_ms, e2e_s = (float(v) for v in t.tolist())
+    value = n * world / (step_ms * 1e-3)
+    if rank == 0:
+        hbm_peak, hbm_src = measured_peaks()
+        geo = graphs.conv_geometry(layers)
+        hws, _ = graphs.conv_input_hw(layers, H, W)
+        by_type = {}
+        for t_, nm, ms in prof:
+            key = t_ if t_ != "Convolution" else ("Convolution/depthwise" if geo[nm]["groups"] > 1 else
+                                                  ("Convolution/1x1" if geo[nm]["k"] == 1 else "Convolution/stem3x3"))
+            by_type[key] = by_type.get(key, 0.0) + ms
+        total_prof = sum(by_type.values())
+        # dominant single layer: algorithmic bytes at its boundary dtypes over its own measured time
+        int8_blobs = {k for k, g in geo.items() if g["term"] > 100}
+        t_, nm, ms = max((p for p in prof if p[0] == "Convolution"), key=lambda p: p[2])
+        g = geo[nm]
+        wl = _layer_wl(g, hws[nm], in_f32=g["input"] not in int8_blobs)
+        ops, byts = algorithmic_work(wl, n)
+        ach = byts / (ms * 1e-3) / 1e9
+        roof = {"bound": "hbm", "achieved": ach, "peak": hbm_peak, "unit": "GB/s", "frac": ach / hbm_peak, "traffic": None,
+                "peak_source": hbm_src, "kernel": f"layer {nm}: {g['cin']}->{g['cout']} k{g['k']} s{g['stride']} groups {g['groups']} "
+                f"@{hws[nm][0]}x{hws[nm][1]} ({'fp32' if wl['in_f32'] else 'int8'} in, {'int8' if g['term'] > 100 else 'fp32'} out)",
+                "kernel_ms": ms, "algorithmic_bytes_per_launch": byts, "ops_per_launch": ops,
+                "time_share_by_layer_kind": {k: round(v / total_prof, 4) for k, v in sorted(by_type.items(), key=lambda kv: -kv[1])},
+                "profiled_ms_per_step": total_prof}
+        cpu = None
+        if not args.no_cpu:
+            per_img, how, cores, kind = net_cpu_reference_time(graphs.shufflenetv2_layers(H, W, batch=1), H, W, reps=3)
+            cpu = {"value": 1.0 / per_img, "unit": "images/s", "cores": cores, "kind": kind,
+                   "sample": f"3 images: sum of the convolution layers timed one by one, N=1 ({how['packed']} packed, {how['unpacked']} unpacked reference "
+                             f"layers, {how['port']} depthwise layers with C%8!=0 on the C restatement); glue layers not included"}
+        print(json.dumps({
+            "metric": "shufflenetv2_int8_images_per_s", "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "s8xs8->s32", "data": "synthetic",
+            "config": {"workload": args.workload, "graph": "ShuffleNetV2-1.0x backbone, int8 convolutions, fp32 glue", "batch_per_gpu": n,
+                       "input": f"3x{H}x{W} fp32 NCHW", "output": "1024x%dx%d fp32" % out_shape[2:], "conv_gop_per_image": 2 * macs / 1e9,
+                       "l2": f"input batch {in_bytes / 1e6:.0f} MB and every stage's activations exceed the 126 MB L2; no flush"},
+            "conv_tops": 2.0 * macs * n * world / (step_ms * 1e-3) / 1e12,
+            "clocks": clocks, "gpu_launches": int(launches),
+            "e2e": {"value": n * world / e2e_s, "unit": "images/s", "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes,
+                    "ms_per_step": e2e_s * 1e3, "steps": e2e_steps},
+            "roofline": roof, "cpu_baseline": cpu,
+        }))
+    net.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + sorted(NET_WORKLOADS))
+    ap.add_argument("--batch", type=int, default=0, help="per-GPU batch of a graph workload (default: the configuration's)")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-peak", action="store_true", help="skip the live int8 GEMM peak measurement")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.workload in NET_WORKLOADS:
+        cfg = NET_WORKLOADS[args.workload]
+        if args.impl == "reference":
+            run_net_reference_arm(args, cfg)
+        else:
+            run_net_gpu_arm(args, cfg)
+        return
     wl = WORKLOADS[args.workload]
     if args.impl == "reference":
         run_reference_arm(args, wl)

@@ -51,6 +51,12 @@ int ott_net_set_conv_params(ott_net* net, const char* layer, const int8_t* w_oih
 int ott_net_forward(ott_net* net, const char* input_blob, const void* in, int in_on_device, int n, int c, int h, int w,
                     int n_out, const char* const* out_blobs, void* const* out_host);
 
+/* Extractor::benchmark_info (Tensor/Net.cpp:811-850, Tensor/Benchmark.cpp:45-102): the same forward with CUDA events
+ * around every layer; ms_per_layer[i] (ott_net_layer_count entries) receives layer i's device time in milliseconds.
+ * Layers run serialised while profiling. */
+int ott_net_profile(ott_net* net, const char* input_blob, const void* in, int in_on_device, int n, int c, int h, int w,
+                    const char* out_blob, float* ms_per_layer);
+
 #if defined(__GNUC__)
 #pragma GCC visibility pop
 #endif

@@ -73,6 +73,7 @@ SIGNATURES = {
     "ott_net_layer_info": (i32, [vp, i32, C.c_char_p, i32, C.c_char_p, i32, C.POINTER(i32)]),
     "ott_net_blob_shape": (i32, [vp, C.c_char_p, C.POINTER(i32)]),
     "ott_net_set_conv_params": (i32, [vp, C.c_char_p, vp, vp, vp, vp, i32, vp, i32]),
+    "ott_net_profile": (i32, [vp, C.c_char_p, vp, i32, i32, i32, i32, i32, C.c_char_p, C.POINTER(C.c_float)]),
     "ott_net_forward": (i32, [vp, C.c_char_p, vp, i32, i32, i32, i32, i32, i32, C.POINTER(C.c_char_p), C.POINTER(vp)]),
 }
 
@@ -307,6 +308,14 @@ class Net:
             ptrs = (C.c_void_p * len(out_blobs))(*out_ptrs)
         self.check(self.lib.ott_net_forward(self.h, input_blob.encode(), in_ptr, 1 if in_on_device else 0, n, c, h, w, len(out_blobs),
                                             names, ptrs))
+
+    def profile(self, input_blob: str, in_ptr, in_on_device: bool, shape, out_blob: str):
+        """Per-layer device time in ms (layers serialised by events): [(type, name, ms)]."""
+        n, c, h, w = shape
+        infos = self.layer_infos()
+        ms = (C.c_float * len(infos))()
+        self.check(self.lib.ott_net_profile(self.h, input_blob.encode(), in_ptr, 1 if in_on_device else 0, n, c, h, w, out_blob.encode(), ms))
+        return [(i["type"], i["name"], float(m)) for i, m in zip(infos, ms)]
 
     def forward(self, input_blob: str, x: np.ndarray, out_blobs, dtypes=None):
         """Host fp32 NCHW in, list of host arrays out (fp32 NCHW, or int8 NCHW for blobs listed in dtypes as np.int8)."""

@@ -88,6 +88,29 @@ def conv_geometry(layers):
     return geo
 
 
+def conv_input_hw(layers, height, width):
+    """name -> (h, w) of the blob each Convolution reads, and total multiply-accumulates per image."""
+    hw, out, macs = {}, {}, 0
+    geo = conv_geometry(layers)
+    for l in layers:
+        ins = [s.strip() for s in str(l.get("input", "")).split(",") if s.strip()]
+        if l["type"] == "Input":
+            hw[l["output"]] = (height, width)
+            continue
+        h, w = hw[ins[0]]
+        if l["type"] in ("Convolution", "MaxPool"):
+            k, s_, p_ = int(l["kernel_h"]), int(l["stride_h"]), int(l["padding_h"])
+            oh, ow = (h + 2 * p_ - k) // s_ + 1, (w + 2 * p_ - k) // s_ + 1
+            hw[l["output"]] = (oh, ow)
+            if l["type"] == "Convolution":
+                g = geo[l["name"]]
+                out[l["name"]] = (h, w)
+                macs += oh * ow * g["cout"] * (g["cin"] // g["groups"]) * k * k
+        else:
+            hw[l["output"]] = (h, w)
+    return out, macs
+
+
 def make_params(layers, seed=0x0771E5):
     """Seeded weights per Convolution: N(0, 0.05) (depthwise N(0, 0.1)) quantized per output channel, bias N(0, 0.01).
     Activation scales are placeholders until `calibrate` fills them."""

@@ -157,4 +157,21 @@ int ott_net_forward(ott_net* net, const char* input_blob, const void* in, int in
     return OTT_OK;
 }
 
+int ott_net_profile(ott_net* net, const char* input_blob, const void* in, int in_on_device, int n, int c, int h, int w,
+                    const char* out_blob, float* ms_per_layer) {
+    if (!net || !input_blob || !in || !out_blob || !ms_per_layer) return OTT_ERR_INVALID;
+    net->error.clear();
+    otter::Extractor ex = net->net.create_extractor();
+    otter::Tensor x = in_on_device ? otter::Tensor::wrap(const_cast<void*>(in), (size_t)n * c * h * w * 4, otter::Device::CUDA, nullptr,
+                                                          {n, c, h, w}, otter::ScalarType::Float)
+                                   : otter::from_blob(const_cast<void*>(in), {n, c, h, w}, otter::ScalarType::Float);
+    int rc = ex.input(input_blob, x);
+    if (rc != 0) return fail(net, rc, "Extractor::input failed");
+    std::vector<float> ms;
+    rc = ex.benchmark_info(out_blob, ms);
+    if (rc != 0) return rc;
+    std::memcpy(ms_per_layer, ms.data(), sizeof(float) * ms.size());
+    return ott_sync(net->net.context());
+}
+
 }  // extern "C"

@@ -112,6 +112,7 @@ public:
     int device = 0;                   // NEW: CUDA device of the Net
     ott_ctx* gpu = nullptr;           // set by Net::compile; what every Layer::forward launches on
     int int8_rounding = OTT_ROUND_ADD_HALF_TRUNC;  // which reference build is mirrored (packed x86 default / aarch64)
+    std::vector<float>* layer_ms = nullptr;  // when set: per-layer device time, indexed by layer (Extractor::benchmark_info)
 };
 
 class Initializer;  // weight readers (Tensor/Initializer.hpp) are not part of this build
@@ -264,6 +265,9 @@ public:
     // stream synchronisation; type 1: the device tensor as it is (asynchronous)
     int extract(const std::string& blob_name, Tensor& feat, int type = 0);
     int extract(int blob_index, Tensor& feat, int type = 0);
+    // per-layer device times in ms of the layers that ran to produce blob_name (Tensor/Net.cpp:811-850 benchmark_info):
+    // CUDA events around every layer, so the layers run serialised; ms has one entry per layer of the Net
+    int benchmark_info(const std::string& blob_name, std::vector<float>& ms);
 private:
     Extractor(const Net* net, size_t blob_count);
     const Net* net_;

@@ -331,6 +331,26 @@ int Net::forward_layer(int layer_index, std::vector<Tensor>& blob_tensors, const
 int Net::do_forward_layer(const Layer* layer, std::vector<Tensor>& blob_tensors, const NetOption& opt) const {
     if (layer->type() == "Input") return blob_tensors[(size_t)layer->tops[0]].defined() ? 0 : -1;
     int ret = 0;
+    ott_event *ev0 = nullptr, *ev1 = nullptr;
+    if (opt.layer_ms) {
+        ott_event_create(opt.gpu, &ev0);
+        ott_event_create(opt.gpu, &ev1);
+        ott_event_record(opt.gpu, ev0);
+    }
+    struct EventGuard {
+        const Net* net; const Layer* layer; const NetOption& opt; ott_event *a, *b;
+        ~EventGuard() {
+            if (!a) return;
+            ott_event_record(opt.gpu, b);
+            float ms = 0.f;
+            if (ott_event_elapsed_ms(a, b, &ms) == OTT_OK) {
+                const int idx = net->find_layer_index_by_name(layer->name);
+                if (idx >= 0 && idx < (int)opt.layer_ms->size()) (*opt.layer_ms)[(size_t)idx] += ms;
+            }
+            ott_event_destroy(a);
+            ott_event_destroy(b);
+        }
+    } guard{this, layer, opt, ev0, ev1};
     if (layer->one_blob_only) {
         Tensor bottom = blob_tensors[(size_t)layer->bottoms[0]];
         Tensor top;
@@ -378,6 +398,15 @@ int Extractor::input(int blob_index, const Tensor& in) {
     if (rc != OTT_OK) return rc;
     blob_tensors_[(size_t)blob_index] = dev;
     return 0;
+}
+
+int Extractor::benchmark_info(const std::string& blob_name, std::vector<float>& ms) {
+    ms.assign((size_t)net_->layer_count(), 0.f);
+    option.layer_ms = &ms;
+    Tensor feat;
+    const int rc = extract(blob_name, feat, 1);
+    option.layer_ms = nullptr;
+    return rc;
 }
 
 int Extractor::extract(const std::string& blob_name, Tensor& feat, int type) {
