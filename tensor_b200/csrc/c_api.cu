@@ -266,6 +266,11 @@ int ott_conv_int8_create(ott_ctx* ctx, const ott_conv_desc* d, const int8_t* w_o
         if (requant) scale_out[p] = n_out_scales == 1 ? out_scales[0] : out_scales[p];
     }
 
+    c->w_host.assign(w_oihw, w_oihw + (size_t)d->cout * (d->cin / d->groups) * d->kh * d->kw);
+    c->scale_in_host = scale_in;
+    c->bias_host = bias_p;
+    c->scale_out_host = scale_out;
+    c->in_scale0 = in_scales[0];
     int rc = OTT_OK;
     std::vector<int8_t> wpacked;
     const int taps = d->kh * d->kw;
@@ -370,6 +375,12 @@ int ott_conv_int8_forward(ott_ctx* ctx, const ott_conv* c, const void* in_dev, i
         // one pass over HBM: quantize (when the input is fp32), depthwise and epilogue in the same kernel
         OTT_CUDA_CHECK(ctx, launch_depthwise_tiled(ctx->stream, s, in_dev, in_dtype, c->w_tiled_dev, c->in_scales_dev, c->n_in_scales, ep,
                                                     out_dev, out_dtype));
+        ctx->launches += 1;
+        return OTT_OK;
+    }
+    if (c->kind == OTT_KERNEL_DENSE_DIRECT && dense_stem_supports(s, in_dtype, out_dtype)) {
+        OTT_CUDA_CHECK(ctx, launch_dense_stem(ctx->stream, s, static_cast<const float*>(in_dev), c->w_host.data(), c->scale_in_host.data(),
+                                               c->bias_host.data(), c->scale_out_host.data(), c->in_scale0, ep, out_dev, out_dtype));
         ctx->launches += 1;
         return OTT_OK;
     }

@@ -2,6 +2,7 @@
 #pragma once
 
 #include <cstdint>
+#include <vector>
 
 #include "../../include/otter_b200.h"
 #include "dense_umma.h"
@@ -19,6 +20,10 @@ struct ott_conv {
     float* bias_dev = nullptr;
     float* scale_out_dev = nullptr;
     float* in_scales_dev = nullptr;
+    // host copies for the kernels that take their parameters by value (stem kernel)
+    std::vector<int8_t> w_host;
+    std::vector<float> scale_in_host, bias_host, scale_out_host;
+    float in_scale0 = 1.f;
     ottk::UmmaPlan plan{};
     alignas(128) unsigned char weight_map[128];
 };

@@ -39,4 +39,11 @@ cudaError_t launch_depthwise_tiled(cudaStream_t stream, const ConvShape& s, cons
 cudaError_t launch_dense_direct(cudaStream_t stream, const ConvShape& s, const int8_t* x, const int8_t* w_okc,
                                 const EpilogueParams& ep, void* out, int out_dtype);
 
+// First-layer kernel: 3 input channels, 3x3, stride 1/2, fp32 NCHW in (quantize fused), fp32 NCHW or int8 NHWC out.
+// Filters (OIHW int8) and per-channel epilogue vectors are HOST pointers: they travel in the kernel parameter bank.
+bool dense_stem_supports(const ConvShape& s, int in_dtype, int out_dtype);
+cudaError_t launch_dense_stem(cudaStream_t stream, const ConvShape& s, const float* x, const int8_t* w_oihw_host, const float* scale_in_host,
+                              const float* bias_host, const float* scale_out_host, float in_scale, const EpilogueParams& ep, void* out,
+                              int out_dtype);
+
 }  // namespace ottk

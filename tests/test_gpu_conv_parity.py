@@ -71,6 +71,9 @@ def test_batched_equals_single_images(ctx):
     ("dw5_s1_tiles", dict(cin=96, cout=96, k=5, pad=2, groups=96, n=2, h=40, w=40, int8_scale_term=101, act_type=ACT_LRELU, act_param0=0.1, w_std=0.1, s8_input=True)),
     ("dw5_s2_tiles_w_odd", dict(cin=32, cout=32, k=5, stride=2, pad=2, groups=32, n=1, h=41, w=77, int8_scale_term=101, w_std=0.1)),
     ("dw_nopad", dict(cin=32, cout=32, k=3, pad=0, groups=32, n=1, h=20, w=24, int8_scale_term=101, act_type=ACT_RELU, w_std=0.1)),
+    ("stem_odd_s2", dict(cin=3, cout=24, k=3, stride=2, pad=1, n=2, h=45, w=71, int8_scale_term=2, act_type=ACT_RELU, x_lo=0.0)),
+    ("stem_s1_lrelu_s8", dict(cin=3, cout=16, k=3, stride=1, pad=1, n=2, h=33, w=40, int8_scale_term=101, act_type=ACT_LRELU, act_param0=0.1, x_lo=0.0)),
+    ("stem_tiles", dict(cin=3, cout=24, k=3, stride=2, pad=1, n=3, h=96, w=160, int8_scale_term=2, act_type=ACT_RELU, x_lo=0.0)),
     ("two_n_tiles", dict(cin=256, cout=512, k=1, n=3, h=28, w=28, int8_scale_term=101, act_type=ACT_RELU6)),
     ("four_n_tiles", dict(cin=512, cout=1024, k=1, n=2, h=14, w=14, int8_scale_term=101, act_type=ACT_RELU6)),
 ])
