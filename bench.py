@@ -58,7 +58,7 @@ WORKLOADS = {
     "dense3x3_64_hw56_n256": dict(cin=64, cout=64, k=3, stride=1, pad=1, groups=1, n=256, h=56, w=56, term=2, act=ACT_NONE, in_f32=True),
     "dense3x3_64_hw56_n256_s8": dict(cin=64, cout=64, k=3, stride=1, pad=1, groups=1, n=256, h=56, w=56, term=102, act=ACT_RELU, in_f32=False),
 }
-DEFAULT_WORKLOAD = "pw_512_1024_hw56"
+DEFAULT_WORKLOAD = "shufflenetv2_320"
 
 
 def nhwc_channels(c):

@@ -130,6 +130,13 @@ int ott_conv_int8_out_shape(const ott_conv* conv, int h, int w, int* oh, int* ow
 int ott_conv_int8_forward(ott_ctx* ctx, const ott_conv* conv, const void* in_dev, int in_dtype, int n, int h, int w,
                           void* out_dev, int out_dtype, uint32_t* status_word_dev);
 
+/* The same forward when the fp32 NCHW input is a channel range of a wider tensor (what the reference's Crop layer hands
+ * on: native::slice returns a view, Tensor/CropLayer.cpp:67-75): in_dev points at the first channel of the range and
+ * in_channels_total is the channel count of the tensor it lives in (the per-image stride in planes). For int8 NHWC input
+ * in_channels_total must equal cin. */
+int ott_conv_int8_forward_ex(ott_ctx* ctx, const ott_conv* conv, const void* in_dev, int in_dtype, int in_channels_total, int n,
+                             int h, int w, void* out_dev, int out_dtype, uint32_t* status_word_dev);
+
 /* The same forward on HOST buffers: copies the input to the device, runs, copies the output back and
  * waits for it. This is the call a host-tensor Layer::forward maps to (Tensor/Net.cpp:442). */
 int ott_conv_int8_forward_host(ott_ctx* ctx, const ott_conv* conv, const void* in_host, int in_dtype, int n, int h,

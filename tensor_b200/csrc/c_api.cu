@@ -347,9 +347,16 @@ int ott_conv_int8_out_shape(const ott_conv* c, int h, int w, int* oh, int* ow) {
 
 int ott_conv_int8_forward(ott_ctx* ctx, const ott_conv* c, const void* in_dev, int in_dtype, int n, int h, int w, void* out_dev,
                           int out_dtype, uint32_t* status_word_dev) {
+    return ott_conv_int8_forward_ex(ctx, c, in_dev, in_dtype, c ? c->d.cin : 0, n, h, w, out_dev, out_dtype, status_word_dev);
+}
+
+int ott_conv_int8_forward_ex(ott_ctx* ctx, const ott_conv* c, const void* in_dev, int in_dtype, int in_channels_total, int n, int h, int w,
+                             void* out_dev, int out_dtype, uint32_t* status_word_dev) {
     if (!ctx || !c || !in_dev || !out_dev || n < 0 || h <= 0 || w <= 0) return OTT_ERR_INVALID;
     const ott_conv_desc& d = c->d;
     if (in_dtype != OTT_F32_NCHW && in_dtype != OTT_S8_NHWC) return ctx->fail(OTT_ERR_INVALID, "input must be fp32 NCHW or int8 NHWC");
+    if (in_channels_total < d.cin || (in_dtype != OTT_F32_NCHW && in_channels_total != d.cin))
+        return ctx->fail(OTT_ERR_INVALID, "in_channels_total must be >= cin (and == cin for int8 NHWC input)");
     const bool requant = d.int8_scale_term > 100;
     if (out_dtype == OTT_S8_NHWC && !requant) return ctx->fail(OTT_ERR_INVALID, "int8 output needs int8_scale_term > 100");
     if (out_dtype == OTT_F32_NCHW && requant) return ctx->fail(OTT_ERR_INVALID, "fp32 output needs int8_scale_term < 100");
@@ -363,6 +370,7 @@ int ott_conv_int8_forward(ott_ctx* ctx, const ott_conv* c, const void* in_dev, i
     if (s.oh <= 0 || s.ow <= 0) return ctx->fail(OTT_ERR_INVALID, "empty output");
     s.cin = d.cin; s.cout = d.cout; s.cin_pad = c->cin_pad; s.cout_pad = c->cout_pad;
     s.kh = d.kh; s.kw = d.kw; s.sh = d.sh; s.sw = d.sw; s.ph = d.ph; s.pw = d.pw; s.dh = d.dh; s.dw = d.dw;
+    s.in_ctotal = in_channels_total;
     if (n == 0) return OTT_OK;
 
     EpilogueParams ep{};
@@ -392,7 +400,7 @@ int ott_conv_int8_forward(ott_ctx* ctx, const ott_conv* c, const void* in_dev, i
             return ctx->fail(OTT_ERR_ALLOC, "scratch allocation for quantized activations failed");
         }
         OTT_CUDA_CHECK(ctx, launch_quantize_nchw_to_nhwc(ctx->stream, static_cast<const float*>(in_dev), (int8_t*)xq.p, c->in_scales_dev,
-                                                          c->n_in_scales, n, d.cin, h, w, d.rounding));
+                                                          c->n_in_scales, n, d.cin, h, w, d.rounding, in_channels_total));
         ctx->launches += 1;
         x = (const int8_t*)xq.p;
     }

@@ -132,7 +132,7 @@ depthwise_tiled_kernel(const void* __restrict__ xin, const uint32_t* __restrict_
     // ---- 1. load the input tile ----
     if (IN_F32) {
         // warp = channel (4 per warp), lanes run over the (row, word) positions of the channel's plane
-        const float* x = static_cast<const float*>(xin) + (long)img * s.cin * s.h * s.w;
+        const float* x = static_cast<const float*>(xin) + (long)img * s.in_ctotal * s.h * s.w;
         const bool vec_ok = (s.w % 4 == 0) && ep.rounding == ROUND_ADD_HALF_TRUNC;
         const int per_plane = T.ir * T.rp;
         const float inv_rp = 1.0f / (float)T.rp;

@@ -18,10 +18,11 @@ struct ConvShape {
     int n, h, w, oh, ow;
     int cin, cout, cin_pad, cout_pad;  // *_pad = NHWC channel strides
     int kh, kw, sh, sw, ph, pw, dh, dw;
+    int in_ctotal;  // fp32 NCHW input only: channels per image in the input's storage (>= cin; > cin for a channel-range view)
 };
 
 cudaError_t launch_quantize_nchw_to_nhwc(cudaStream_t stream, const float* x, int8_t* out, const float* scales_dev,
-                                         int n_scales, int n, int c, int h, int w, int rounding);
+                                         int n_scales, int n, int c, int h, int w, int rounding, int c_total = 0);
 
 // Depthwise: x int8 NHWC [n,h,w,c_pad]; weights int8 [kh*kw][c_pad] (tap-major, channel innermost).
 cudaError_t launch_depthwise(cudaStream_t stream, const ConvShape& s, const int8_t* x, const int8_t* w_taps,

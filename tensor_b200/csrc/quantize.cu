@@ -21,14 +21,14 @@ __device__ __forceinline__ int qt_row(int p) { return (p & 3) * 33 + (p >> 2); }
 
 __global__ void __launch_bounds__(QT_THREADS)
 quantize_nchw_to_nhwc_kernel(const float* __restrict__ x, int8_t* __restrict__ out, const float* __restrict__ scales,
-                             int n_scales, int c, int cpad, int hw, int tiles_p, int tiles_c, int rounding) {
+                             int n_scales, int c, int cpad, int hw, int tiles_p, int tiles_c, int rounding, int c_total) {
     __shared__ uint32_t tile[4 * 33 * QT_PITCH];
     const long tile_id = blockIdx.x;
     const int tc = (int)(tile_id % tiles_c);
     const int tp = (int)((tile_id / tiles_c) % tiles_p);
     const int img = (int)(tile_id / ((long)tiles_c * tiles_p));
     const int c0 = tc * QT_C, p0 = tp * QT_P;
-    const float* src = x + (long)img * c * hw;
+    const float* src = x + (long)img * c_total * hw;
 
     // phase 1: a thread quantizes 4 consecutive pixels of 4 consecutive channels and packs, per pixel, the
     // 4 channels into one word. Lanes run along pixels (512 contiguous bytes per channel row per warp).
@@ -85,13 +85,13 @@ quantize_nchw_to_nhwc_kernel(const float* __restrict__ x, int8_t* __restrict__ o
 }
 
 cudaError_t launch_quantize_nchw_to_nhwc(cudaStream_t stream, const float* x, int8_t* out, const float* scales_dev,
-                                         int n_scales, int n, int c, int h, int w, int rounding) {
+                                         int n_scales, int n, int c, int h, int w, int rounding, int c_total) {
     const int hw = h * w, cpad = nhwc_channels(c);
     if (n == 0 || hw == 0) return cudaSuccess;
     const int tiles_p = (hw + QT_P - 1) / QT_P, tiles_c = (cpad + QT_C - 1) / QT_C;
     const long blocks = (long)n * tiles_p * tiles_c;
     quantize_nchw_to_nhwc_kernel<<<(unsigned)blocks, QT_THREADS, 0, stream>>>(x, out, scales_dev, n_scales, c, cpad, hw,
-                                                                            tiles_p, tiles_c, rounding);
+                                                                            tiles_p, tiles_c, rounding, c_total > 0 ? c_total : c);
     return cudaGetLastError();
 }
 

@@ -14,6 +14,7 @@ ConvolutionLayer::ConvolutionLayer() {
     one_blob_only = true;
     support_inplace = false;
     support_packing = true;
+    accepts_views = true;  // a Crop output is read in place through its per-image stride
 }
 
 ConvolutionLayer::~ConvolutionLayer() {
@@ -186,8 +187,9 @@ int ConvolutionLayer::forward(const Tensor& bottom_blob, Tensor& top_blob, const
     top_blob = device_empty(opt, {n, out_channels, oh, ow}, requant ? ScalarType::Byte : ScalarType::Float,
                             requant ? Layout::NHWC16 : Layout::NCHW);
     if (!top_blob.defined()) return -100;
-    return ott_conv_int8_forward(opt.gpu, gpu_conv_, bottom_blob.raw_data(), in_dtype, n, h, w, top_blob.raw_data(),
-                                 requant ? OTT_S8_NHWC : OTT_F32_NCHW, nullptr);
+    const int ctotal = in_dtype == OTT_F32_NCHW ? (int)bottom_blob.channels_total() : c;
+    return ott_conv_int8_forward_ex(opt.gpu, gpu_conv_, bottom_blob.raw_data(), in_dtype, ctotal, n, h, w, top_blob.raw_data(),
+                                    requant ? OTT_S8_NHWC : OTT_F32_NCHW, nullptr);
 }
 
 // ---- Input (Tensor/InputLayer.cpp:19-71): declares the shape of a graph input; the blob is set by Extractor::input ----

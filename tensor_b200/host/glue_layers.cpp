@@ -2,13 +2,16 @@
 // ChannelShuffle, ShortCut and the stand-alone activations. Option keys and shape rules follow the reference
 // layer of the same name; forward enqueues one small CUDA kernel (include/otter_b200.h, "fp32 glue layers").
 // Blobs are device fp32 NCHW tensors.
+#include <algorithm>
+
 #include "otter_api.hpp"
 
 namespace otter {
 
 namespace {
 bool is_dev_f32(const Tensor& t) {
-    return t.defined() && t.device() == Device::CUDA && t.scalar_type() == ScalarType::Float && t.layout() == Layout::NCHW && t.dim() == 4;
+    return t.defined() && !t.is_composite() && t.device() == Device::CUDA && t.scalar_type() == ScalarType::Float &&
+           t.layout() == Layout::NCHW && t.dim() == 4;
 }
 }  // namespace
 
@@ -67,7 +70,7 @@ public:
 // Tensor/ConcatLayer.cpp:24-70 (channel axis only: the only use in the int8 graphs)
 class ConcatLayer : public Layer {
 public:
-    ConcatLayer() { one_blob_only = false; support_inplace = false; support_packing = true; }
+    ConcatLayer() { one_blob_only = false; support_inplace = false; support_packing = true; accepts_views = true; }
     int parse_param(LayerOption& option, ParamDict& pd) override {
         pd.clear();
         pd.set(0, opt_find_int(option, "axis", 1));
@@ -85,31 +88,23 @@ public:
         pd.set(OUTPUT_SHAPE_HINT, shape_tensor(n, c, h, w));
         return 0;
     }
-    int forward(const std::vector<Tensor>& bottoms, std::vector<Tensor>& tops, const NetOption& opt) const override {
-        int total_c = 0;
+    // The result is handed on as the list of its parts: a consumer that can read the parts where they are
+    // (ChannelShuffle) does so; for any other consumer the Net materialises the concatenation with one plane copy per
+    // part, which is what an eager Concat would have done.
+    int forward(const std::vector<Tensor>& bottoms, std::vector<Tensor>& tops, const NetOption&) const override {
         for (const Tensor& b : bottoms) {
-            if (!is_dev_f32(b)) return -1;
-            total_c += (int)b.size(1);
+            if (!is_dev_f32(b) || b.size(0) != bottoms[0].size(0) || b.size(2) != bottoms[0].size(2) || b.size(3) != bottoms[0].size(3)) return -1;
         }
-        const int n = (int)bottoms[0].size(0), h = (int)bottoms[0].size(2), w = (int)bottoms[0].size(3);
-        tops[0] = device_empty(opt, {n, total_c, h, w}, ScalarType::Float, Layout::NCHW);
-        if (!tops[0].defined()) return -100;
-        int off = 0;
-        for (const Tensor& b : bottoms) {
-            const int c = (int)b.size(1);
-            const int rc = ott_copy_channels_f32(opt.gpu, b.data_ptr<float>(), c, 0, 1, tops[0].data_ptr<float>(), total_c, off, 1, c, n, h * w);
-            if (rc != 0) return rc;
-            off += c;
-        }
+        tops[0] = Tensor::composite(bottoms);
         return 0;
     }
     std::string type() const override { return "Concat"; }
 };
 
-// Tensor/CropLayer.cpp:25-76 (channel axis). The reference returns a view; here the channel range is copied.
+// Tensor/CropLayer.cpp:25-76 (channel axis): a view of the channel range, no copy
 class CropLayer : public Layer {
 public:
-    CropLayer() { one_blob_only = true; support_inplace = false; support_packing = true; }
+    CropLayer() { one_blob_only = true; support_inplace = false; support_packing = true; accepts_views = true; }
     int parse_param(LayerOption& option, ParamDict& pd) override {
         pd.clear();
         pd.set(0, opt_find_int(option, "axis", 1));
@@ -130,14 +125,13 @@ public:
         end = pd.get(2, -1);
         return 0;
     }
-    int forward(const Tensor& bottom, Tensor& top, const NetOption& opt) const override {
+    int forward(const Tensor& bottom, Tensor& top, const NetOption&) const override {
         if (!is_dev_f32(bottom)) return -1;
-        const int n = (int)bottom.size(0), c = (int)bottom.size(1), h = (int)bottom.size(2), w = (int)bottom.size(3);
+        const int c = (int)bottom.size(1);
         const int e = end == -1 ? c : end;
         if (start < 0 || e > c || e <= start) return -1;
-        top = device_empty(opt, {n, e - start, h, w}, ScalarType::Float, Layout::NCHW);
-        if (!top.defined()) return -100;
-        return ott_copy_channels_f32(opt.gpu, bottom.data_ptr<float>(), c, start, 1, top.data_ptr<float>(), e - start, 0, 1, e - start, n, h * w);
+        top = bottom.slice_channels(start, e);  // a view, as native::slice in the reference
+        return top.defined() ? 0 : -1;
     }
     std::string type() const override { return "Crop"; }
     int start = -1, end = -1;
@@ -146,7 +140,7 @@ public:
 // Tensor/ChannelShuffleLayer.cpp:20-41: output channel i*g + k is input channel k*(C/g) + i
 class ChannelShuffleLayer : public Layer {
 public:
-    ChannelShuffleLayer() { one_blob_only = true; support_inplace = false; support_packing = true; }
+    ChannelShuffleLayer() { one_blob_only = true; support_inplace = false; support_packing = true; accepts_views = true; accepts_composite = true; }
     int parse_param(LayerOption& option, ParamDict& pd) override {
         pd.clear();
         pd.set(0, opt_find_int(option, "groups", 1));
@@ -156,16 +150,31 @@ public:
         groups = pd.get(0, 1);
         return 0;
     }
+    // Reads a concatenation part by part where the parts lie (views included), so Concat -> ChannelShuffle costs one
+    // read and one write of the tensor instead of two of each.
     int forward(const Tensor& bottom, Tensor& top, const NetOption& opt) const override {
-        if (!is_dev_f32(bottom)) return -1;
+        if (!bottom.defined() || bottom.device() != Device::CUDA || bottom.scalar_type() != ScalarType::Float || bottom.dim() != 4) return -1;
         const int n = (int)bottom.size(0), c = (int)bottom.size(1), h = (int)bottom.size(2), w = (int)bottom.size(3);
         if (groups < 1 || c % groups != 0) return -1;
+        const int per = c / groups;
+        const std::vector<Tensor> parts = bottom.is_composite() ? bottom.parts() : std::vector<Tensor>{bottom};
         top = device_empty(opt, {n, c, h, w}, ScalarType::Float, Layout::NCHW);
         if (!top.defined()) return -100;
-        const int per = c / groups;
-        for (int k = 0; k < groups; ++k) {
-            const int rc = ott_copy_channels_f32(opt.gpu, bottom.data_ptr<float>(), c, k * per, 1, top.data_ptr<float>(), c, k, groups, per, n, h * w);
-            if (rc != 0) return rc;
+        int base = 0;  // first logical input channel of the current part
+        for (const Tensor& p : parts) {
+            if (p.is_composite()) return -1;
+            const int pc = (int)p.size(1), ptotal = (int)p.channels_total();
+            // logical input channel ch = k*per + i goes to output channel i*groups + k; split the part at group boundaries
+            int ch = base;
+            while (ch < base + pc) {
+                const int k = ch / per, i = ch % per;
+                const int run = std::min(per - i, base + pc - ch);
+                const int rc = ott_copy_channels_f32(opt.gpu, p.data_ptr<float>(), ptotal, ch - base, 1, top.data_ptr<float>(), c, i * groups + k,
+                                                     groups, run, n, h * w);
+                if (rc != 0) return rc;
+                ch += run;
+            }
+            base += pc;
         }
         return 0;
     }

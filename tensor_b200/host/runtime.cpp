@@ -34,6 +34,28 @@ Tensor Tensor::view(std::vector<int64_t> sizes) const {
     return t;
 }
 
+Tensor Tensor::slice_channels(int64_t start, int64_t end) const {
+    if (!st_ || dim() != 4 || layout_ != Layout::NCHW || start < 0 || end > size(1) || end <= start) return Tensor();
+    Tensor t = *this;
+    t.ctotal_ = channels_total();
+    t.offset_ = offset_ + (size_t)(start * size(2) * size(3)) * elementSize(dtype_);
+    t.sizes_[1] = end - start;
+    return t;
+}
+
+Tensor Tensor::composite(std::vector<Tensor> parts) {
+    Tensor t;
+    if (parts.empty()) return t;
+    t.sizes_ = parts[0].sizes();
+    int64_t c = 0;
+    for (const Tensor& p : parts) c += p.size(1);
+    t.sizes_[1] = c;
+    t.dtype_ = parts[0].scalar_type();
+    t.layout_ = parts[0].layout();
+    t.parts_ = std::make_shared<std::vector<Tensor>>(std::move(parts));
+    return t;
+}
+
 Tensor Tensor::clone() const {
     if (!defined() || device() != Device::CPU) return Tensor();
     Tensor t = empty(sizes_, dtype_);
@@ -95,6 +117,24 @@ Tensor device_empty(const NetOption& opt, std::vector<int64_t> sizes, ScalarType
     if (ott_malloc(opt.gpu, bytes, &p) != OTT_OK) return Tensor();
     ott_ctx* ctx = opt.gpu;
     return Tensor::wrap(p, bytes, Device::CUDA, [ctx](void* q) { ott_free(ctx, q); }, std::move(sizes), dtype, layout);
+}
+
+Tensor materialize(const NetOption& opt, const Tensor& t) {
+    if (!t.defined() || t.device() != Device::CUDA || t.scalar_type() != ScalarType::Float || t.dim() != 4) return t;
+    if (!t.is_composite() && t.is_dense()) return t;
+    const int n = (int)t.size(0), c = (int)t.size(1), hw = (int)(t.size(2) * t.size(3));
+    Tensor out = device_empty(opt, t.sizes(), ScalarType::Float, Layout::NCHW);
+    if (!out.defined()) return Tensor();
+    std::vector<Tensor> parts = t.is_composite() ? t.parts() : std::vector<Tensor>{t};
+    int off = 0;
+    for (const Tensor& p : parts) {
+        if (p.is_composite()) return Tensor();  // concatenations do not nest
+        const int pc = (int)p.size(1);
+        if (ott_copy_channels_f32(opt.gpu, p.data_ptr<float>(), (int)p.channels_total(), 0, 1, out.data_ptr<float>(), c, off, 1, pc, n, hw) != OTT_OK)
+            return Tensor();
+        off += pc;
+    }
+    return out;
 }
 
 // ---------------------------------------------------------------- Layer
@@ -351,8 +391,14 @@ int Net::do_forward_layer(const Layer* layer, std::vector<Tensor>& blob_tensors,
             ott_event_destroy(b);
         }
     } guard{this, layer, opt, ev0, ev1};
+    auto prepared = [&](const Tensor& t) {
+        const bool view = t.defined() && !t.is_composite() && !t.is_dense();
+        if ((t.is_composite() && !layer->accepts_composite) || (view && !layer->accepts_views)) return materialize(opt, t);
+        return t;
+    };
     if (layer->one_blob_only) {
-        Tensor bottom = blob_tensors[(size_t)layer->bottoms[0]];
+        Tensor bottom = prepared(blob_tensors[(size_t)layer->bottoms[0]]);
+        if (!bottom.defined()) { error_ = "could not materialise the input of layer " + layer->name; return -100; }
         Tensor top;
         if (opt.lightmode && layer->support_inplace && bottom.use_count() <= 2) {  // ours + the blob table's
             top = bottom;
@@ -364,7 +410,10 @@ int Net::do_forward_layer(const Layer* layer, std::vector<Tensor>& blob_tensors,
         blob_tensors[(size_t)layer->tops[0]] = top;
     } else {
         std::vector<Tensor> bottoms(layer->bottoms.size()), tops(layer->tops.size());
-        for (size_t i = 0; i < bottoms.size(); ++i) bottoms[i] = blob_tensors[(size_t)layer->bottoms[i]];
+        for (size_t i = 0; i < bottoms.size(); ++i) {
+            bottoms[i] = prepared(blob_tensors[(size_t)layer->bottoms[i]]);
+            if (!bottoms[i].defined()) { error_ = "could not materialise an input of layer " + layer->name; return -100; }
+        }
         ret = layer->forward(bottoms, tops, opt);
         if (ret != 0) { error_ = "forward of layer " + layer->name + " failed: " + ott_last_error(opt.gpu); return ret; }
         for (size_t i = 0; i < tops.size(); ++i) blob_tensors[(size_t)layer->tops[i]] = tops[i];
@@ -420,6 +469,11 @@ int Extractor::extract(int blob_index, Tensor& feat, int type) {
     if (!blob_tensors_[(size_t)blob_index].defined()) {
         const int ret = net_->forward_layer(net_->blobs_[(size_t)blob_index].producer, blob_tensors_, option);
         if (ret != 0) return ret;
+    }
+    if (blob_tensors_[(size_t)blob_index].is_composite() || !blob_tensors_[(size_t)blob_index].is_dense()) {
+        Tensor dense = materialize(option, blob_tensors_[(size_t)blob_index]);
+        if (!dense.defined()) return -100;
+        blob_tensors_[(size_t)blob_index] = dense;
     }
     const Tensor& dev = blob_tensors_[(size_t)blob_index];
     if (type != 0) { feat = dev; return 0; }
