@@ -274,6 +274,8 @@ def run_gpu_arm(args, wl):
         import torch
         import torch.distributed as dist
         torch.cuda.set_device(local_rank)
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"  # NCCL's version banner goes to stdout and would precede the JSON line
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     n = wl["n"]  # per-GPU batch (weak scaling)
     oh, ow = out_hw(wl)
@@ -554,6 +556,8 @@ def run_net_gpu_arm(args, cfg):
         import torch
         import torch.distributed as dist
         torch.cuda.set_device(local_rank)
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"  # NCCL's version banner goes to stdout and would precede the JSON line
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     n, H, W = (args.batch or cfg["batch"]), cfg["height"], cfg["width"]
     net, layers = build_calibrated_net(cfg, n, local_rank)
