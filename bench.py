@@ -107,6 +107,21 @@ def measured_peaks():
     return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
 
 
+def max_over_ranks(values, dist, device="cuda"):
+    """Element-wise maximum of a list of per-rank numbers over all ranks (the slowest rank sets the step time)."""
+    if dist is None:
+        return [float(v) for v in values]
+    import torch
+    t = torch.tensor([float(v) for v in values], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(v) for v in t.tolist()]
+
+
+def whole_job_rate(units_per_rank, world, step_ms):
+    """Weak scaling: every rank processes units_per_rank units per step; the job's rate uses the slowest rank's time."""
+    return units_per_rank * world / (step_ms * 1e-3)
+
+
 class ClockSampler:
     """nvidia-smi clock/throttle samples during the timed region."""
 
@@ -381,11 +396,7 @@ def run_gpu_arm(args, wl):
     e2e_s = (time.perf_counter() - t0) / e2e_steps
 
     step_ms = ms_total / args.steps
-    if dist is not None:
-        import torch
-        t = torch.tensor([step_ms, e2e_s, conv_ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        step_ms, e2e_s, conv_ms = (float(v) for v in t.tolist())
+    step_ms, e2e_s, conv_ms = max_over_ranks([step_ms, e2e_s, conv_ms], dist)
     ops, alg_bytes = algorithmic_work(wl, n)
     value = ops * world / (step_ms * 1e-3) / 1e12
     e2e_value = ops * world / e2e_s / 1e12
@@ -619,12 +630,8 @@ def run_net_gpu_arm(args, cfg):
     barrier()
     e2e_s = (time.perf_counter() - t0) / e2e_steps
 
-    if dist is not None:
-        import torch
-        t = torch.tensor([step_ms, e2e_s], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        step_ms, e2e_s = (float(v) for v in t.tolist())
-    value = n * world / (step_ms * 1e-3)
+    step_ms, e2e_s = max_over_ranks([step_ms, e2e_s], dist)
+    value = whole_job_rate(n, world, step_ms)
     if rank == 0:
         hbm_peak, hbm_src = measured_peaks()
         geo = graphs.conv_geometry(layers)
