@@ -654,7 +654,8 @@ def run_net_gpu_arm(args, cfg):
                 f"@{hws[nm][0]}x{hws[nm][1]} ({'fp32' if wl['in_f32'] else 'int8'} in, {'int8' if g['term'] > 100 else 'fp32'} out)",
                 "kernel_ms": ms, "algorithmic_bytes_per_launch": byts, "ops_per_launch": ops,
                 "time_share_by_layer_kind": {k: round(v / total_prof, 4) for k, v in sorted(by_type.items(), key=lambda kv: -kv[1])},
-                "profiled_ms_per_step": total_prof}
+                "profiled_ms_per_step": total_prof,
+                "top_layers_ms": [[nm_, round(ms_, 4)] for _, nm_, ms_ in sorted(prof, key=lambda p: -p[2])[:12]]}
         cpu = None
         if not args.no_cpu:
             per_img, how, cores, kind = net_cpu_reference_time(graphs.shufflenetv2_layers(H, W, batch=1), H, W, reps=3)
