@@ -137,6 +137,19 @@ int ott_conv_int8_forward(ott_ctx* ctx, const ott_conv* conv, const void* in_dev
 int ott_conv_int8_forward_ex(ott_ctx* ctx, const ott_conv* conv, const void* in_dev, int in_dtype, int in_channels_total, int n,
                              int h, int w, void* out_dev, int out_dtype, uint32_t* status_word_dev);
 
+/* The same forward when the fp32 input is scattered over several device tensors: logical input channel i is plane
+ * (plane_refs[i] & 0xFFFFFF) of buffers[plane_refs[i] >> 24], whose consecutive images are image_strides[b] floats apart.
+ * This is how a consumer reads the result of the reference's Concat / Crop / ChannelShuffle layers, which only select and
+ * re-order channel planes (Tensor/ConcatLayer.cpp:55-70, Tensor/CropLayer.cpp:67-75, Tensor/ChannelShuffleLayer.cpp:37-41),
+ * without those planes ever being copied. At most 12 buffers and 512 channels; plane_refs has cin entries (host array). */
+int ott_conv_int8_forward_gather(ott_ctx* ctx, const ott_conv* conv, const float* const* buffers, const int64_t* image_strides,
+                                 int n_buffers, const uint32_t* plane_refs, int n, int h, int w, void* out_dev, int out_dtype,
+                                 uint32_t* status_word_dev);
+
+/* Dense fp32 NCHW copy [n][channels][hw] of planes described the same way (for consumers that need one tensor). */
+int ott_gather_channels_f32(ott_ctx* ctx, const float* const* buffers, const int64_t* image_strides, int n_buffers,
+                            const uint32_t* plane_refs, int channels, int n, int hw, float* dst_dev);
+
 /* The same forward on HOST buffers: copies the input to the device, runs, copies the output back and
  * waits for it. This is the call a host-tensor Layer::forward maps to (Tensor/Net.cpp:442). */
 int ott_conv_int8_forward_host(ott_ctx* ctx, const ott_conv* conv, const void* in_host, int in_dtype, int n, int h,

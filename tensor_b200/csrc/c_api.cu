@@ -222,7 +222,10 @@ int ott_quantize_f32_nchw_to_s8_nhwc(ott_ctx* ctx, const float* x_dev, int n, in
     DeviceBlock sc;
     if (sc.alloc(ctx, sizeof(float) * n_scales) != cudaSuccess) return ctx->fail(OTT_ERR_ALLOC, "scale upload allocation failed");
     OTT_CUDA_CHECK(ctx, cudaMemcpyAsync(sc.p, scales_host, sizeof(float) * n_scales, cudaMemcpyHostToDevice, ctx->stream));
-    OTT_CUDA_CHECK(ctx, launch_quantize_nchw_to_nhwc(ctx->stream, x_dev, out_dev, (const float*)sc.p, n_scales, n, c, h, w, rounding));
+    if (c > kGatherMaxChannels) return ctx->fail(OTT_ERR_UNSUPPORTED, "more than %d channels", kGatherMaxChannels);
+    PlaneGather g;
+    gather_identity(&g, x_dev, c, c, (long)h * w);
+    OTT_CUDA_CHECK(ctx, launch_quantize_nchw_to_nhwc(ctx->stream, g, out_dev, (const float*)sc.p, n_scales, n, c, h, w, rounding));
     ctx->launches += 1;
     // the pageable scale array must stay readable until the copy has been issued; it has (pageable copies
     // are staged synchronously)
@@ -345,18 +348,73 @@ int ott_conv_int8_out_shape(const ott_conv* c, int h, int w, int* oh, int* ow) {
     return OTT_OK;
 }
 
+namespace {
+int conv_forward_impl(ott_ctx* ctx, const ott_conv* c, const void* in_dev, const PlaneGather* gather, int in_dtype, int n, int h, int w,
+                      void* out_dev, int out_dtype, uint32_t* status_word_dev);
+}
+
 int ott_conv_int8_forward(ott_ctx* ctx, const ott_conv* c, const void* in_dev, int in_dtype, int n, int h, int w, void* out_dev,
                           int out_dtype, uint32_t* status_word_dev) {
-    return ott_conv_int8_forward_ex(ctx, c, in_dev, in_dtype, c ? c->d.cin : 0, n, h, w, out_dev, out_dtype, status_word_dev);
+    if (!in_dev) return OTT_ERR_INVALID;
+    return conv_forward_impl(ctx, c, in_dev, nullptr, in_dtype, n, h, w, out_dev, out_dtype, status_word_dev);
 }
 
 int ott_conv_int8_forward_ex(ott_ctx* ctx, const ott_conv* c, const void* in_dev, int in_dtype, int in_channels_total, int n, int h, int w,
                              void* out_dev, int out_dtype, uint32_t* status_word_dev) {
+    if (!ctx || !c || !in_dev) return OTT_ERR_INVALID;
+    if (in_channels_total < c->d.cin || (in_dtype != OTT_F32_NCHW && in_channels_total != c->d.cin))
+        return ctx->fail(OTT_ERR_INVALID, "in_channels_total must be >= cin (and == cin for int8 NHWC input)");
+    if (in_dtype != OTT_F32_NCHW || in_channels_total == c->d.cin)
+        return conv_forward_impl(ctx, c, in_dev, nullptr, in_dtype, n, h, w, out_dev, out_dtype, status_word_dev);
+    if (c->d.cin > kGatherMaxChannels) return ctx->fail(OTT_ERR_UNSUPPORTED, "channel-range input with more than %d channels", kGatherMaxChannels);
+    PlaneGather g;
+    gather_identity(&g, static_cast<const float*>(in_dev), c->d.cin, in_channels_total, (long)h * w);
+    return conv_forward_impl(ctx, c, in_dev, &g, in_dtype, n, h, w, out_dev, out_dtype, status_word_dev);
+}
+
+int ott_conv_int8_forward_gather(ott_ctx* ctx, const ott_conv* c, const float* const* buffers, const int64_t* image_strides, int n_buffers,
+                                 const uint32_t* plane_refs, int n, int h, int w, void* out_dev, int out_dtype, uint32_t* status_word_dev) {
+    if (!ctx || !c || !buffers || !image_strides || !plane_refs) return OTT_ERR_INVALID;
+    if (n_buffers < 1 || n_buffers > kGatherMaxBufs || c->d.cin > kGatherMaxChannels)
+        return ctx->fail(OTT_ERR_UNSUPPORTED, "gathered input: at most %d buffers and %d channels", kGatherMaxBufs, kGatherMaxChannels);
+    PlaneGather g;
+    for (int i = 0; i < n_buffers; ++i) {
+        if (!buffers[i]) return ctx->fail(OTT_ERR_INVALID, "null buffer in the plane table");
+        g.base[i] = buffers[i];
+        g.img_stride[i] = image_strides[i];
+    }
+    for (int i = 0; i < c->d.cin; ++i) {
+        if ((int)(plane_refs[i] >> 24) >= n_buffers) return ctx->fail(OTT_ERR_INVALID, "plane reference %d names buffer %u of %d", i, plane_refs[i] >> 24, n_buffers);
+        g.ref[i] = plane_refs[i];
+    }
+    return conv_forward_impl(ctx, c, buffers[0], &g, OTT_F32_NCHW, n, h, w, out_dev, out_dtype, status_word_dev);
+}
+
+int ott_gather_channels_f32(ott_ctx* ctx, const float* const* buffers, const int64_t* image_strides, int n_buffers, const uint32_t* plane_refs,
+                            int channels, int n, int hw, float* dst_dev) {
+    if (!ctx || !buffers || !image_strides || !plane_refs || !dst_dev || channels < 0 || n < 0 || hw < 0) return OTT_ERR_INVALID;
+    if (n_buffers < 1 || n_buffers > kGatherMaxBufs || channels > kGatherMaxChannels)
+        return ctx->fail(OTT_ERR_UNSUPPORTED, "gather: at most %d buffers and %d channels", kGatherMaxBufs, kGatherMaxChannels);
+    PlaneGather g;
+    for (int i = 0; i < n_buffers; ++i) { g.base[i] = buffers[i]; g.img_stride[i] = image_strides[i]; }
+    for (int i = 0; i < channels; ++i) {
+        if ((int)(plane_refs[i] >> 24) >= n_buffers) return ctx->fail(OTT_ERR_INVALID, "plane reference names a buffer that was not given");
+        g.ref[i] = plane_refs[i];
+    }
+    cudaSetDevice(ctx->device);
+    OTT_CUDA_CHECK(ctx, launch_gather_planes(ctx->stream, g, dst_dev, n, channels, hw));
+    ctx->launches += 1;
+    return OTT_OK;
+}
+
+}  // extern "C"
+
+namespace {
+int conv_forward_impl(ott_ctx* ctx, const ott_conv* c, const void* in_dev, const PlaneGather* gather, int in_dtype, int n, int h, int w,
+                      void* out_dev, int out_dtype, uint32_t* status_word_dev) {
     if (!ctx || !c || !in_dev || !out_dev || n < 0 || h <= 0 || w <= 0) return OTT_ERR_INVALID;
     const ott_conv_desc& d = c->d;
     if (in_dtype != OTT_F32_NCHW && in_dtype != OTT_S8_NHWC) return ctx->fail(OTT_ERR_INVALID, "input must be fp32 NCHW or int8 NHWC");
-    if (in_channels_total < d.cin || (in_dtype != OTT_F32_NCHW && in_channels_total != d.cin))
-        return ctx->fail(OTT_ERR_INVALID, "in_channels_total must be >= cin (and == cin for int8 NHWC input)");
     const bool requant = d.int8_scale_term > 100;
     if (out_dtype == OTT_S8_NHWC && !requant) return ctx->fail(OTT_ERR_INVALID, "int8 output needs int8_scale_term > 100");
     if (out_dtype == OTT_F32_NCHW && requant) return ctx->fail(OTT_ERR_INVALID, "fp32 output needs int8_scale_term < 100");
@@ -370,7 +428,6 @@ int ott_conv_int8_forward_ex(ott_ctx* ctx, const ott_conv* c, const void* in_dev
     if (s.oh <= 0 || s.ow <= 0) return ctx->fail(OTT_ERR_INVALID, "empty output");
     s.cin = d.cin; s.cout = d.cout; s.cin_pad = c->cin_pad; s.cout_pad = c->cout_pad;
     s.kh = d.kh; s.kw = d.kw; s.sh = d.sh; s.sw = d.sw; s.ph = d.ph; s.pw = d.pw; s.dh = d.dh; s.dw = d.dw;
-    s.in_ctotal = in_channels_total;
     if (n == 0) return OTT_OK;
 
     EpilogueParams ep{};
@@ -381,12 +438,12 @@ int ott_conv_int8_forward_ex(ott_ctx* ctx, const ott_conv* c, const void* in_dev
     uint32_t* status = status_word_dev ? status_word_dev : ctx->status_dev;
     if (c->kind == OTT_KERNEL_DEPTHWISE && c->w_tiled_dev && depthwise_tiled_supports(s, out_dtype)) {
         // one pass over HBM: quantize (when the input is fp32), depthwise and epilogue in the same kernel
-        OTT_CUDA_CHECK(ctx, launch_depthwise_tiled(ctx->stream, s, in_dev, in_dtype, c->w_tiled_dev, c->in_scales_dev, c->n_in_scales, ep,
+        OTT_CUDA_CHECK(ctx, launch_depthwise_tiled(ctx->stream, s, in_dev, gather, in_dtype, c->w_tiled_dev, c->in_scales_dev, c->n_in_scales, ep,
                                                     out_dev, out_dtype));
         ctx->launches += 1;
         return OTT_OK;
     }
-    if (c->kind == OTT_KERNEL_DENSE_DIRECT && dense_stem_supports(s, in_dtype, out_dtype)) {
+    if (c->kind == OTT_KERNEL_DENSE_DIRECT && !gather && dense_stem_supports(s, in_dtype, out_dtype)) {
         OTT_CUDA_CHECK(ctx, launch_dense_stem(ctx->stream, s, static_cast<const float*>(in_dev), c->w_host.data(), c->scale_in_host.data(),
                                                c->bias_host.data(), c->scale_out_host.data(), c->in_scale0, ep, out_dev, out_dtype));
         ctx->launches += 1;
@@ -399,8 +456,13 @@ int ott_conv_int8_forward_ex(ott_ctx* ctx, const ott_conv* c, const void* in_dev
             (void)cudaGetLastError();
             return ctx->fail(OTT_ERR_ALLOC, "scratch allocation for quantized activations failed");
         }
-        OTT_CUDA_CHECK(ctx, launch_quantize_nchw_to_nhwc(ctx->stream, static_cast<const float*>(in_dev), (int8_t*)xq.p, c->in_scales_dev,
-                                                          c->n_in_scales, n, d.cin, h, w, d.rounding, in_channels_total));
+        PlaneGather ident;
+        if (!gather) {
+            if (d.cin > kGatherMaxChannels) return ctx->fail(OTT_ERR_UNSUPPORTED, "fp32 input with more than %d channels", kGatherMaxChannels);
+            gather_identity(&ident, static_cast<const float*>(in_dev), d.cin, d.cin, (long)h * w);
+        }
+        OTT_CUDA_CHECK(ctx, launch_quantize_nchw_to_nhwc(ctx->stream, gather ? *gather : ident, (int8_t*)xq.p, c->in_scales_dev, c->n_in_scales, n,
+                                                          d.cin, h, w, d.rounding));
         ctx->launches += 1;
         x = (const int8_t*)xq.p;
     }
@@ -421,6 +483,9 @@ int ott_conv_int8_forward_ex(ott_ctx* ctx, const ott_conv* c, const void* in_dev
     ctx->launches += 1;
     return OTT_OK;
 }
+}  // namespace
+
+extern "C" {
 
 int ott_conv_int8_forward_host(ott_ctx* ctx, const ott_conv* c, const void* in_host, int in_dtype, int n, int h, int w,
                                void* out_host, int out_dtype) {

@@ -43,7 +43,7 @@ dense_stem_kernel(const float* __restrict__ x, const __grid_constant__ StemParam
     const int sh = ix_first - ix_al;  // 0..3
 
     // ---- 1. quantize the halo tile ----
-    const float* ximg = x + (long)img * s.in_ctotal * s.h * s.w;
+    const float* ximg = x + (long)img * 3 * s.h * s.w;
     const bool vec_ok = (s.w % 4 == 0) && rounding == ROUND_ADD_HALF_TRUNC;
     for (int i = threadIdx.x; i < 3 * IH * RP; i += ST_TX * ST_TY) {
         const int xw = i % RP, r = (i / RP) % IH, c = i / (RP * IH);

@@ -22,12 +22,24 @@ void depthwise_tiled_pack_weights(const int8_t* w_oihw, int c, int c_pad, int k,
             }
 }
 
-cudaError_t launch_depthwise_tiled(cudaStream_t stream, const ConvShape& s, const void* x, int in_dtype, const uint32_t* wq,
+cudaError_t launch_depthwise_tiled(cudaStream_t stream, const ConvShape& s, const void* x, const PlaneGather* gather, int in_dtype, const uint32_t* wq,
                                    const float* in_scales, int n_in_scales, const EpilogueParams& ep, void* out, int out_dtype) {
-    if (s.kh == 3 && s.sh == 1) return launch_depthwise_tiled_k3s1(stream, s, x, in_dtype, wq, in_scales, n_in_scales, ep, out, out_dtype);
-    if (s.kh == 3 && s.sh == 2) return launch_depthwise_tiled_k3s2(stream, s, x, in_dtype, wq, in_scales, n_in_scales, ep, out, out_dtype);
-    if (s.kh == 5 && s.sh == 1) return launch_depthwise_tiled_k5s1(stream, s, x, in_dtype, wq, in_scales, n_in_scales, ep, out, out_dtype);
-    if (s.kh == 5 && s.sh == 2) return launch_depthwise_tiled_k5s2(stream, s, x, in_dtype, wq, in_scales, n_in_scales, ep, out, out_dtype);
+    static const PlaneGather none{};
+    PlaneGather ident;
+    const PlaneGather* G = gather;
+    if (!G) {
+        if (in_dtype == DT_F32_NCHW) {
+            if (s.cin > kGatherMaxChannels) return cudaErrorInvalidValue;
+            gather_identity(&ident, static_cast<const float*>(x), s.cin, s.cin, (long)s.h * s.w);
+            G = &ident;
+        } else {
+            G = &none;
+        }
+    }
+    if (s.kh == 3 && s.sh == 1) return launch_depthwise_tiled_k3s1(stream, s, x, *G, in_dtype, wq, in_scales, n_in_scales, ep, out, out_dtype);
+    if (s.kh == 3 && s.sh == 2) return launch_depthwise_tiled_k3s2(stream, s, x, *G, in_dtype, wq, in_scales, n_in_scales, ep, out, out_dtype);
+    if (s.kh == 5 && s.sh == 1) return launch_depthwise_tiled_k5s1(stream, s, x, *G, in_dtype, wq, in_scales, n_in_scales, ep, out, out_dtype);
+    if (s.kh == 5 && s.sh == 2) return launch_depthwise_tiled_k5s2(stream, s, x, *G, in_dtype, wq, in_scales, n_in_scales, ep, out, out_dtype);
     return cudaErrorInvalidValue;
 }
 

@@ -109,8 +109,8 @@ __device__ __forceinline__ void row_step(int oy, const uint32_t* __restrict__ pl
 
 template <int K, int S, bool IN_F32, int EPI, int ACT>
 __global__ void __launch_bounds__(THREADS)
-depthwise_tiled_kernel(const void* __restrict__ xin, const uint32_t* __restrict__ wq, const float* __restrict__ in_scales,
-                       int n_in_scales, EpilogueParams ep, void* __restrict__ out, ConvShape s, Tile T) {
+depthwise_tiled_kernel(const void* __restrict__ xin, const __grid_constant__ PlaneGather G, const uint32_t* __restrict__ wq,
+                       const float* __restrict__ in_scales, int n_in_scales, EpilogueParams ep, void* __restrict__ out, ConvShape s, Tile T) {
     constexpr int KK = Geo<K, S>::KK;
     extern __shared__ uint32_t smem[];
     uint32_t* tin = smem;                  // [32][ir][rp] (+pad): int8 channel planes of the input tile
@@ -132,7 +132,6 @@ depthwise_tiled_kernel(const void* __restrict__ xin, const uint32_t* __restrict_
     // ---- 1. load the input tile ----
     if (IN_F32) {
         // warp = channel (4 per warp), lanes run over the (row, word) positions of the channel's plane
-        const float* x = static_cast<const float*>(xin) + (long)img * s.in_ctotal * s.h * s.w;
         const bool vec_ok = (s.w % 4 == 0) && ep.rounding == ROUND_ADD_HALF_TRUNC;
         const int per_plane = T.ir * T.rp;
         const float inv_rp = 1.0f / (float)T.rp;
@@ -144,7 +143,7 @@ depthwise_tiled_kernel(const void* __restrict__ xin, const uint32_t* __restrict_
                 continue;
             }
             const float sc = n_in_scales == 1 ? __ldg(in_scales) : __ldg(in_scales + c);
-            const float* xc = x + (long)c * s.h * s.w;
+            const float* xc = G.plane(c, img, (long)s.h * s.w);
             if (vec_ok) {
                 // every aligned float4 is either wholly inside the image or wholly outside (w % 4 == 0, ix % 4 == 0);
                 // four independent loads per thread are issued before any is used
@@ -305,7 +304,7 @@ inline Tile plan_tile(const ConvShape& s) {
 }
 
 template <int K, int S, bool IN_F32, int EPI, int ACT>
-cudaError_t launch_t(cudaStream_t stream, const ConvShape& s, const void* x, const uint32_t* wq, const float* in_scales,
+cudaError_t launch_t(cudaStream_t stream, const ConvShape& s, const void* x, const PlaneGather& G, const uint32_t* wq, const float* in_scales,
                      int n_in_scales, const EpilogueParams& ep, void* out) {
     const Tile T = plan_tile<K, S>(s);
     const size_t smem = ((size_t)CG * T.ps + (EPI != EPI_F32 ? (size_t)CG * T.ops : 0)) * 4;
@@ -320,41 +319,41 @@ cudaError_t launch_t(cudaStream_t stream, const ConvShape& s, const void* x, con
     }
     const long blocks = (long)s.n * T.tiles_y * T.tiles_x * T.cgroups;
     if (blocks == 0) return cudaSuccess;
-    kernel<<<(unsigned)blocks, THREADS, smem, stream>>>(x, wq, in_scales, n_in_scales, ep, out, s, T);
+    kernel<<<(unsigned)blocks, THREADS, smem, stream>>>(x, G, wq, in_scales, n_in_scales, ep, out, s, T);
     return cudaGetLastError();
 }
 
 template <int K, int S, bool IN_F32, int EPI>
-cudaError_t launch_act(cudaStream_t stream, const ConvShape& s, const void* x, const uint32_t* wq, const float* in_scales,
+cudaError_t launch_act(cudaStream_t stream, const ConvShape& s, const void* x, const PlaneGather& G, const uint32_t* wq, const float* in_scales,
                        int n_in_scales, const EpilogueParams& ep, void* out) {
     switch (ep.act_type) {
-        case ACT_RELU: return launch_t<K, S, IN_F32, EPI, ACT_RELU>(stream, s, x, wq, in_scales, n_in_scales, ep, out);
-        case ACT_LRELU: return launch_t<K, S, IN_F32, EPI, ACT_LRELU>(stream, s, x, wq, in_scales, n_in_scales, ep, out);
-        case ACT_RELU6: return launch_t<K, S, IN_F32, EPI, ACT_RELU6>(stream, s, x, wq, in_scales, n_in_scales, ep, out);
-        default: return launch_t<K, S, IN_F32, EPI, ACT_NONE>(stream, s, x, wq, in_scales, n_in_scales, ep, out);
+        case ACT_RELU: return launch_t<K, S, IN_F32, EPI, ACT_RELU>(stream, s, x, G, wq, in_scales, n_in_scales, ep, out);
+        case ACT_LRELU: return launch_t<K, S, IN_F32, EPI, ACT_LRELU>(stream, s, x, G, wq, in_scales, n_in_scales, ep, out);
+        case ACT_RELU6: return launch_t<K, S, IN_F32, EPI, ACT_RELU6>(stream, s, x, G, wq, in_scales, n_in_scales, ep, out);
+        default: return launch_t<K, S, IN_F32, EPI, ACT_NONE>(stream, s, x, G, wq, in_scales, n_in_scales, ep, out);
     }
 }
 
 template <int K, int S>
-cudaError_t launch_ks(cudaStream_t stream, const ConvShape& s, const void* x, int in_dtype, const uint32_t* wq,
+cudaError_t launch_ks(cudaStream_t stream, const ConvShape& s, const void* x, const PlaneGather& G, int in_dtype, const uint32_t* wq,
                       const float* in_scales, int n_in_scales, const EpilogueParams& ep, void* out, int out_dtype) {
     const bool f32in = in_dtype == DT_F32_NCHW;
     if (out_dtype == DT_F32_NCHW)
-        return f32in ? launch_act<K, S, true, EPI_F32>(stream, s, x, wq, in_scales, n_in_scales, ep, out)
-                     : launch_act<K, S, false, EPI_F32>(stream, s, x, wq, in_scales, n_in_scales, ep, out);
+        return f32in ? launch_act<K, S, true, EPI_F32>(stream, s, x, G, wq, in_scales, n_in_scales, ep, out)
+                     : launch_act<K, S, false, EPI_F32>(stream, s, x, G, wq, in_scales, n_in_scales, ep, out);
     if (ep.rounding == ROUND_HALF_AWAY)
-        return f32in ? launch_act<K, S, true, EPI_S8_HALF_AWAY>(stream, s, x, wq, in_scales, n_in_scales, ep, out)
-                     : launch_act<K, S, false, EPI_S8_HALF_AWAY>(stream, s, x, wq, in_scales, n_in_scales, ep, out);
-    return f32in ? launch_act<K, S, true, EPI_S8>(stream, s, x, wq, in_scales, n_in_scales, ep, out)
-                 : launch_act<K, S, false, EPI_S8>(stream, s, x, wq, in_scales, n_in_scales, ep, out);
+        return f32in ? launch_act<K, S, true, EPI_S8_HALF_AWAY>(stream, s, x, G, wq, in_scales, n_in_scales, ep, out)
+                     : launch_act<K, S, false, EPI_S8_HALF_AWAY>(stream, s, x, G, wq, in_scales, n_in_scales, ep, out);
+    return f32in ? launch_act<K, S, true, EPI_S8>(stream, s, x, G, wq, in_scales, n_in_scales, ep, out)
+                 : launch_act<K, S, false, EPI_S8>(stream, s, x, G, wq, in_scales, n_in_scales, ep, out);
 }
 
 }  // namespace dwt
 
 // defined one per file (depthwise_tiled_k3s1.cu ...)
-cudaError_t launch_depthwise_tiled_k3s1(cudaStream_t, const ConvShape&, const void*, int, const uint32_t*, const float*, int, const EpilogueParams&, void*, int);
-cudaError_t launch_depthwise_tiled_k3s2(cudaStream_t, const ConvShape&, const void*, int, const uint32_t*, const float*, int, const EpilogueParams&, void*, int);
-cudaError_t launch_depthwise_tiled_k5s1(cudaStream_t, const ConvShape&, const void*, int, const uint32_t*, const float*, int, const EpilogueParams&, void*, int);
-cudaError_t launch_depthwise_tiled_k5s2(cudaStream_t, const ConvShape&, const void*, int, const uint32_t*, const float*, int, const EpilogueParams&, void*, int);
+cudaError_t launch_depthwise_tiled_k3s1(cudaStream_t, const ConvShape&, const void*, const PlaneGather&, int, const uint32_t*, const float*, int, const EpilogueParams&, void*, int);
+cudaError_t launch_depthwise_tiled_k3s2(cudaStream_t, const ConvShape&, const void*, const PlaneGather&, int, const uint32_t*, const float*, int, const EpilogueParams&, void*, int);
+cudaError_t launch_depthwise_tiled_k5s1(cudaStream_t, const ConvShape&, const void*, const PlaneGather&, int, const uint32_t*, const float*, int, const EpilogueParams&, void*, int);
+cudaError_t launch_depthwise_tiled_k5s2(cudaStream_t, const ConvShape&, const void*, const PlaneGather&, int, const uint32_t*, const float*, int, const EpilogueParams&, void*, int);
 
 }  // namespace ottk

@@ -18,11 +18,31 @@ struct ConvShape {
     int n, h, w, oh, ow;
     int cin, cout, cin_pad, cout_pad;  // *_pad = NHWC channel strides
     int kh, kw, sh, sw, ph, pw, dh, dw;
-    int in_ctotal;  // fp32 NCHW input only: channels per image in the input's storage (>= cin; > cin for a channel-range view)
 };
 
-cudaError_t launch_quantize_nchw_to_nhwc(cudaStream_t stream, const float* x, int8_t* out, const float* scales_dev,
-                                         int n_scales, int n, int c, int h, int w, int rounding, int c_total = 0);
+// Where the channel planes of an fp32 NCHW input live. The reference's Concat / Crop / ChannelShuffle only re-order or
+// select channel planes (Tensor/ConcatLayer.cpp:55-70, Tensor/CropLayer.cpp:67-75, Tensor/ChannelShuffleLayer.cpp:37-41), so
+// instead of copying planes around, a consumer kernel is told, per logical input channel, which buffer and which plane of
+// that buffer to read. Passed by value in the kernel parameter bank.
+constexpr int kGatherMaxBufs = 12, kGatherMaxChannels = 512;
+struct PlaneGather {
+    const float* base[kGatherMaxBufs];
+    long long img_stride[kGatherMaxBufs];  // elements between consecutive images of that buffer
+    uint32_t ref[kGatherMaxChannels];      // logical channel -> (buffer << 24) | plane index inside the buffer
+    __host__ __device__ const float* plane(int c, int img, long hw) const {
+        const uint32_t r = ref[c];
+        const int b = (int)(r >> 24);
+        return base[b] + (long long)img * img_stride[b] + (long long)(r & 0xFFFFFFu) * hw;
+    }
+};
+// the table of a plain tensor: one buffer of c_total channels per image, logical channel i = plane c0 + i
+void gather_identity(PlaneGather* g, const float* x, int c, int c_total, long hw);
+
+cudaError_t launch_quantize_nchw_to_nhwc(cudaStream_t stream, const PlaneGather& src, int8_t* out, const float* scales_dev,
+                                         int n_scales, int n, int c, int h, int w, int rounding);
+
+// dense fp32 NCHW copy of the gathered planes (for consumers that want one contiguous tensor)
+cudaError_t launch_gather_planes(cudaStream_t stream, const PlaneGather& src, float* dst, int n, int c, long hw);
 
 // Depthwise: x int8 NHWC [n,h,w,c_pad]; weights int8 [kh*kw][c_pad] (tap-major, channel innermost).
 cudaError_t launch_depthwise(cudaStream_t stream, const ConvShape& s, const int8_t* x, const int8_t* w_taps,
@@ -33,7 +53,7 @@ cudaError_t launch_depthwise(cudaStream_t stream, const ConvShape& s, const int8
 bool depthwise_tiled_supports(const ConvShape& s, int out_dtype);
 int depthwise_tiled_weight_words(int k);  // 32-bit words per channel
 void depthwise_tiled_pack_weights(const int8_t* w_oihw, int c, int c_pad, int k, uint32_t* dst);
-cudaError_t launch_depthwise_tiled(cudaStream_t stream, const ConvShape& s, const void* x, int in_dtype, const uint32_t* wq,
+cudaError_t launch_depthwise_tiled(cudaStream_t stream, const ConvShape& s, const void* x, const PlaneGather* gather, int in_dtype, const uint32_t* wq,
                                    const float* in_scales, int n_in_scales, const EpilogueParams& ep, void* out, int out_dtype);
 
 // Direct dense convolution on CUDA cores: x int8 NHWC; weights int8 [cout_pad][kh*kw][cin_pad].

@@ -20,15 +20,14 @@ constexpr int QT_PITCH = 17;  // words per pixel row in shared memory (16 used):
 __device__ __forceinline__ int qt_row(int p) { return (p & 3) * 33 + (p >> 2); }
 
 __global__ void __launch_bounds__(QT_THREADS)
-quantize_nchw_to_nhwc_kernel(const float* __restrict__ x, int8_t* __restrict__ out, const float* __restrict__ scales,
-                             int n_scales, int c, int cpad, int hw, int tiles_p, int tiles_c, int rounding, int c_total) {
+quantize_nchw_to_nhwc_kernel(const __grid_constant__ PlaneGather G, int8_t* __restrict__ out, const float* __restrict__ scales,
+                             int n_scales, int c, int cpad, int hw, int tiles_p, int tiles_c, int rounding) {
     __shared__ uint32_t tile[4 * 33 * QT_PITCH];
     const long tile_id = blockIdx.x;
     const int tc = (int)(tile_id % tiles_c);
     const int tp = (int)((tile_id / tiles_c) % tiles_p);
     const int img = (int)(tile_id / ((long)tiles_c * tiles_p));
     const int c0 = tc * QT_C, p0 = tp * QT_P;
-    const float* src = x + (long)img * c_total * hw;
 
     // phase 1: a thread quantizes 4 consecutive pixels of 4 consecutive channels and packs, per pixel, the
     // 4 channels into one word. Lanes run along pixels (512 contiguous bytes per channel row per warp).
@@ -47,7 +46,7 @@ quantize_nchw_to_nhwc_kernel(const float* __restrict__ x, int8_t* __restrict__ o
             for (int i = 0; i < 4; ++i) {
                 const int cg = c0 + cword * 4 + i;
                 sc[i] = n_scales == 1 ? __ldg(scales) : __ldg(scales + cg);
-                v[i] = __ldg(reinterpret_cast<const float4*>(src + (long)cg * hw + p));
+                v[i] = __ldg(reinterpret_cast<const float4*>(G.plane(cg, img, hw) + p));
             }
 #pragma unroll
             for (int i = 0; i < 4; ++i) cw[i] = quantize4_pack(v[i].x, v[i].y, v[i].z, v[i].w, sc[i]);
@@ -58,7 +57,7 @@ quantize_nchw_to_nhwc_kernel(const float* __restrict__ x, int8_t* __restrict__ o
                 int q[4] = {0, 0, 0, 0};
                 if (cg < c) {
                     const float s = n_scales == 1 ? __ldg(scales) : __ldg(scales + cg);
-                    const float* row = src + (long)cg * hw;
+                    const float* row = G.plane(cg, img, hw);
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
                         if (p + j < hw) q[j] = quantize1(__ldg(row + p + j), s, rounding);
@@ -84,14 +83,46 @@ quantize_nchw_to_nhwc_kernel(const float* __restrict__ x, int8_t* __restrict__ o
     }
 }
 
-cudaError_t launch_quantize_nchw_to_nhwc(cudaStream_t stream, const float* x, int8_t* out, const float* scales_dev,
-                                         int n_scales, int n, int c, int h, int w, int rounding, int c_total) {
+void gather_identity(PlaneGather* g, const float* x, int c, int c_total, long hw) {
+    g->base[0] = x;
+    g->img_stride[0] = (long long)c_total * hw;
+    for (int i = 0; i < c && i < kGatherMaxChannels; ++i) g->ref[i] = (uint32_t)i;
+}
+
+cudaError_t launch_quantize_nchw_to_nhwc(cudaStream_t stream, const PlaneGather& src, int8_t* out, const float* scales_dev,
+                                         int n_scales, int n, int c, int h, int w, int rounding) {
     const int hw = h * w, cpad = nhwc_channels(c);
     if (n == 0 || hw == 0) return cudaSuccess;
+    if (c > kGatherMaxChannels) return cudaErrorInvalidValue;
     const int tiles_p = (hw + QT_P - 1) / QT_P, tiles_c = (cpad + QT_C - 1) / QT_C;
     const long blocks = (long)n * tiles_p * tiles_c;
-    quantize_nchw_to_nhwc_kernel<<<(unsigned)blocks, QT_THREADS, 0, stream>>>(x, out, scales_dev, n_scales, c, cpad, hw,
-                                                                            tiles_p, tiles_c, rounding, c_total > 0 ? c_total : c);
+    quantize_nchw_to_nhwc_kernel<<<(unsigned)blocks, QT_THREADS, 0, stream>>>(src, out, scales_dev, n_scales, c, cpad, hw, tiles_p, tiles_c,
+                                                                            rounding);
+    return cudaGetLastError();
+}
+
+// dst[img][c][p] = plane(c, img)[p]
+__global__ void gather_planes_kernel(const __grid_constant__ PlaneGather G, float* __restrict__ dst, int c, long hw, long total4, int vec) {
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (long)gridDim.x * blockDim.x) {
+        const long per = vec ? hw / 4 : hw;
+        const long p = i % per;
+        const long r = i / per;
+        const int ch = (int)(r % c);
+        const int img = (int)(r / c);
+        const float* src = G.plane(ch, img, hw);
+        if (vec) reinterpret_cast<float4*>(dst)[i] = __ldg(reinterpret_cast<const float4*>(src) + p);
+        else dst[i] = __ldg(src + p);
+    }
+}
+
+cudaError_t launch_gather_planes(cudaStream_t stream, const PlaneGather& src, float* dst, int n, int c, long hw) {
+    if (n == 0 || c == 0 || hw == 0) return cudaSuccess;
+    if (c > kGatherMaxChannels) return cudaErrorInvalidValue;
+    const int vec = hw % 4 == 0 ? 1 : 0;
+    const long total = (long)n * c * (vec ? hw / 4 : hw);
+    long grid = (total + 255) / 256;
+    if (grid > 148 * 16) grid = 148 * 16;
+    gather_planes_kernel<<<(unsigned)grid, 256, 0, stream>>>(src, dst, c, hw, total, vec);
     return cudaGetLastError();
 }
 

@@ -14,7 +14,7 @@ ConvolutionLayer::ConvolutionLayer() {
     one_blob_only = true;
     support_inplace = false;
     support_packing = true;
-    accepts_views = true;  // a Crop output is read in place through its per-image stride
+    accepts_tables = true;  // the planes of a Concat / Crop / ChannelShuffle result are read where they lie
 }
 
 ConvolutionLayer::~ConvolutionLayer() {
@@ -177,19 +177,28 @@ int ConvolutionLayer::forward(const Tensor& bottom_blob, Tensor& top_blob, const
     if (!gpu_conv_ || !bottom_blob.defined() || bottom_blob.device() != Device::CUDA || bottom_blob.dim() != 4) return -1;
     const int n = (int)bottom_blob.size(0), c = (int)bottom_blob.size(1), h = (int)bottom_blob.size(2), w = (int)bottom_blob.size(3);
     if (c != in_channels) return -1;
-    int in_dtype;
-    if (bottom_blob.scalar_type() == ScalarType::Float && bottom_blob.layout() == Layout::NCHW) in_dtype = OTT_F32_NCHW;
-    else if (bottom_blob.scalar_type() == ScalarType::Byte && bottom_blob.layout() == Layout::NHWC16) in_dtype = OTT_S8_NHWC;
-    else return -1;
     int oh = 0, ow = 0;
     ott_conv_int8_out_shape(gpu_conv_, h, w, &oh, &ow);
     const bool requant = int8_scale_term > 100;
+    const int out_dtype = requant ? OTT_S8_NHWC : OTT_F32_NCHW;
+    Tensor src = bottom_blob;
+    std::vector<const float*> bufs;
+    std::vector<int64_t> strides;
+    if (src.is_table() && !table_arrays(src, bufs, strides)) {
+        src = materialize(opt, src);  // more buffers or channels than one kernel table holds
+        if (!src.defined()) return -100;
+    }
     top_blob = device_empty(opt, {n, out_channels, oh, ow}, requant ? ScalarType::Byte : ScalarType::Float,
                             requant ? Layout::NHWC16 : Layout::NCHW);
     if (!top_blob.defined()) return -100;
-    const int ctotal = in_dtype == OTT_F32_NCHW ? (int)bottom_blob.channels_total() : c;
-    return ott_conv_int8_forward_ex(opt.gpu, gpu_conv_, bottom_blob.raw_data(), in_dtype, ctotal, n, h, w, top_blob.raw_data(),
-                                    requant ? OTT_S8_NHWC : OTT_F32_NCHW, nullptr);
+    if (src.is_table())
+        return ott_conv_int8_forward_gather(opt.gpu, gpu_conv_, bufs.data(), strides.data(), (int)bufs.size(), src.table_refs().data(), n, h, w,
+                                            top_blob.raw_data(), out_dtype, nullptr);
+    int in_dtype;
+    if (src.scalar_type() == ScalarType::Float && src.layout() == Layout::NCHW) in_dtype = OTT_F32_NCHW;
+    else if (src.scalar_type() == ScalarType::Byte && src.layout() == Layout::NHWC16) in_dtype = OTT_S8_NHWC;
+    else return -1;
+    return ott_conv_int8_forward(opt.gpu, gpu_conv_, src.raw_data(), in_dtype, n, h, w, top_blob.raw_data(), out_dtype, nullptr);
 }
 
 // ---- Input (Tensor/InputLayer.cpp:19-71): declares the shape of a graph input; the blob is set by Extractor::input ----
@@ -215,7 +224,7 @@ public:
 // ---- Split (Tensor/SplitLayer.cpp): every top is the bottom itself ----
 class SplitLayer : public Layer {
 public:
-    SplitLayer() { one_blob_only = false; support_inplace = false; }
+    SplitLayer() { one_blob_only = false; support_inplace = false; accepts_tables = true; }
     int compute_output_shape(ParamDict& pd) override {
         if (bottom_shapes.empty() || !bottom_shapes[0].defined()) return -1;
         pd.set(OUTPUT_SHAPE_HINT, bottom_shapes[0]);

@@ -10,8 +10,11 @@ namespace otter {
 
 namespace {
 bool is_dev_f32(const Tensor& t) {
-    return t.defined() && !t.is_composite() && t.device() == Device::CUDA && t.scalar_type() == ScalarType::Float &&
+    return t.defined() && !t.is_table() && t.device() == Device::CUDA && t.scalar_type() == ScalarType::Float &&
            t.layout() == Layout::NCHW && t.dim() == 4;
+}
+bool is_dev_f32_or_table(const Tensor& t) {
+    return t.defined() && t.device() == Device::CUDA && t.scalar_type() == ScalarType::Float && t.layout() == Layout::NCHW && t.dim() == 4;
 }
 }  // namespace
 
@@ -70,7 +73,7 @@ public:
 // Tensor/ConcatLayer.cpp:24-70 (channel axis only: the only use in the int8 graphs)
 class ConcatLayer : public Layer {
 public:
-    ConcatLayer() { one_blob_only = false; support_inplace = false; support_packing = true; accepts_views = true; }
+    ConcatLayer() { one_blob_only = false; support_inplace = false; support_packing = true; accepts_tables = true; }
     int parse_param(LayerOption& option, ParamDict& pd) override {
         pd.clear();
         pd.set(0, opt_find_int(option, "axis", 1));
@@ -88,23 +91,21 @@ public:
         pd.set(OUTPUT_SHAPE_HINT, shape_tensor(n, c, h, w));
         return 0;
     }
-    // The result is handed on as the list of its parts: a consumer that can read the parts where they are
-    // (ChannelShuffle) does so; for any other consumer the Net materialises the concatenation with one plane copy per
-    // part, which is what an eager Concat would have done.
+    // No plane is copied: the result is a plane table over the inputs (Tensor::is_table). A consumer that reads through
+    // tables (Convolution) does so; for any other consumer the Net materialises the tensor with one gather kernel.
     int forward(const std::vector<Tensor>& bottoms, std::vector<Tensor>& tops, const NetOption&) const override {
-        for (const Tensor& b : bottoms) {
-            if (!is_dev_f32(b) || b.size(0) != bottoms[0].size(0) || b.size(2) != bottoms[0].size(2) || b.size(3) != bottoms[0].size(3)) return -1;
-        }
-        tops[0] = Tensor::composite(bottoms);
-        return 0;
+        for (const Tensor& b : bottoms)
+            if (!is_dev_f32_or_table(b) || b.size(0) != bottoms[0].size(0) || b.size(2) != bottoms[0].size(2) || b.size(3) != bottoms[0].size(3)) return -1;
+        tops[0] = Tensor::concat_channels(bottoms);
+        return tops[0].defined() ? 0 : -1;
     }
     std::string type() const override { return "Concat"; }
 };
 
-// Tensor/CropLayer.cpp:25-76 (channel axis): a view of the channel range, no copy
+// Tensor/CropLayer.cpp:25-76 (channel axis): a selection of channel planes, no copy
 class CropLayer : public Layer {
 public:
-    CropLayer() { one_blob_only = true; support_inplace = false; support_packing = true; accepts_views = true; }
+    CropLayer() { one_blob_only = true; support_inplace = false; support_packing = true; accepts_tables = true; }
     int parse_param(LayerOption& option, ParamDict& pd) override {
         pd.clear();
         pd.set(0, opt_find_int(option, "axis", 1));
@@ -126,11 +127,13 @@ public:
         return 0;
     }
     int forward(const Tensor& bottom, Tensor& top, const NetOption&) const override {
-        if (!is_dev_f32(bottom)) return -1;
+        if (!is_dev_f32_or_table(bottom)) return -1;
         const int c = (int)bottom.size(1);
         const int e = end == -1 ? c : end;
         if (start < 0 || e > c || e <= start) return -1;
-        top = bottom.slice_channels(start, e);  // a view, as native::slice in the reference
+        std::vector<int> pick((size_t)(e - start));
+        for (int i = start; i < e; ++i) pick[(size_t)(i - start)] = i;
+        top = bottom.select_channels(pick);  // a selection of planes, as the view native::slice gives the reference
         return top.defined() ? 0 : -1;
     }
     std::string type() const override { return "Crop"; }
@@ -140,7 +143,7 @@ public:
 // Tensor/ChannelShuffleLayer.cpp:20-41: output channel i*g + k is input channel k*(C/g) + i
 class ChannelShuffleLayer : public Layer {
 public:
-    ChannelShuffleLayer() { one_blob_only = true; support_inplace = false; support_packing = true; accepts_views = true; accepts_composite = true; }
+    ChannelShuffleLayer() { one_blob_only = true; support_inplace = false; support_packing = true; accepts_tables = true; }
     int parse_param(LayerOption& option, ParamDict& pd) override {
         pd.clear();
         pd.set(0, opt_find_int(option, "groups", 1));
@@ -150,33 +153,17 @@ public:
         groups = pd.get(0, 1);
         return 0;
     }
-    // Reads a concatenation part by part where the parts lie (views included), so Concat -> ChannelShuffle costs one
-    // read and one write of the tensor instead of two of each.
-    int forward(const Tensor& bottom, Tensor& top, const NetOption& opt) const override {
-        if (!bottom.defined() || bottom.device() != Device::CUDA || bottom.scalar_type() != ScalarType::Float || bottom.dim() != 4) return -1;
-        const int n = (int)bottom.size(0), c = (int)bottom.size(1), h = (int)bottom.size(2), w = (int)bottom.size(3);
+    // A permutation of planes: output channel i*groups + k is input channel k*(C/groups) + i. No plane is copied.
+    int forward(const Tensor& bottom, Tensor& top, const NetOption&) const override {
+        if (!is_dev_f32_or_table(bottom)) return -1;
+        const int c = (int)bottom.size(1);
         if (groups < 1 || c % groups != 0) return -1;
         const int per = c / groups;
-        const std::vector<Tensor> parts = bottom.is_composite() ? bottom.parts() : std::vector<Tensor>{bottom};
-        top = device_empty(opt, {n, c, h, w}, ScalarType::Float, Layout::NCHW);
-        if (!top.defined()) return -100;
-        int base = 0;  // first logical input channel of the current part
-        for (const Tensor& p : parts) {
-            if (p.is_composite()) return -1;
-            const int pc = (int)p.size(1), ptotal = (int)p.channels_total();
-            // logical input channel ch = k*per + i goes to output channel i*groups + k; split the part at group boundaries
-            int ch = base;
-            while (ch < base + pc) {
-                const int k = ch / per, i = ch % per;
-                const int run = std::min(per - i, base + pc - ch);
-                const int rc = ott_copy_channels_f32(opt.gpu, p.data_ptr<float>(), ptotal, ch - base, 1, top.data_ptr<float>(), c, i * groups + k,
-                                                     groups, run, n, h * w);
-                if (rc != 0) return rc;
-                ch += run;
-            }
-            base += pc;
-        }
-        return 0;
+        std::vector<int> pick((size_t)c);
+        for (int i = 0; i < per; ++i)
+            for (int k = 0; k < groups; ++k) pick[(size_t)(i * groups + k)] = k * per + i;
+        top = bottom.select_channels(pick);
+        return top.defined() ? 0 : -1;
     }
     std::string type() const override { return "ChannelShuffle"; }
     int groups = 1;

@@ -41,30 +41,31 @@ inline size_t elementSize(ScalarType t) { return t == ScalarType::Byte ? 1 : 4; 
 class Tensor {
 public:
     Tensor() = default;
-    bool defined() const { return static_cast<bool>(st_) || is_composite(); }
-    void reset() { st_.reset(); parts_.reset(); sizes_.clear(); ctotal_ = 0; offset_ = 0; }
+    bool defined() const { return static_cast<bool>(st_) || is_table(); }
+    void reset() { st_.reset(); table_.reset(); sizes_.clear(); offset_ = 0; }
     long use_count() const { return st_.use_count(); }
     int64_t dim() const { return (int64_t)sizes_.size(); }
     int64_t size(int64_t i) const { return sizes_[(size_t)(i < 0 ? i + dim() : i)]; }
     const std::vector<int64_t>& sizes() const { return sizes_; }
     int64_t numel() const { int64_t n = 1; for (auto s : sizes_) n *= s; return sizes_.empty() ? 0 : n; }
     ScalarType scalar_type() const { return dtype_; }
-    Device device() const { return st_ ? st_->dev : (is_composite() ? (*parts_)[0].device() : Device::CPU); }
+    Device device() const { return st_ ? st_->dev : (is_table() ? Device::CUDA : Device::CPU); }
     Layout layout() const { return layout_; }
     size_t nbytes() const { return st_ ? st_->bytes : 0; }
     void* raw_data() const { return st_ ? static_cast<char*>(st_->ptr) + offset_ : nullptr; }
     template <typename T> T* data_ptr() const { return static_cast<T*>(raw_data()); }
     Tensor view(std::vector<int64_t> sizes) const;  // same storage, new sizes (-1 allowed once)
     Tensor clone() const;                            // host tensors only
-    // Channel range [start, end) of an NCHW tensor as a view on the same storage (what native::slice gives the reference's
-    // Crop layer). The view keeps the parent's per-image stride: channels_total() planes.
-    Tensor slice_channels(int64_t start, int64_t end) const;
-    int64_t channels_total() const { return ctotal_ > 0 ? ctotal_ : (dim() == 4 ? size(1) : 0); }
-    bool is_dense() const { return ctotal_ == 0 || ctotal_ == size(1); }
-    // A channel-wise concatenation that has not been materialised: the parts in order (see ConcatLayer).
-    bool is_composite() const { return parts_ && !parts_->empty(); }
-    const std::vector<Tensor>& parts() const { return *parts_; }
-    static Tensor composite(std::vector<Tensor> parts);
+    // A "plane table": an fp32 NCHW tensor whose channel planes live in other device tensors. Logical channel i is plane
+    // (refs[i] & 0xFFFFFF) of bufs[refs[i] >> 24]. Concat, Crop and ChannelShuffle produce these instead of copying
+    // planes; consumers that can read through a table (Convolution) do, for the rest the Net materialises a dense copy.
+    bool is_table() const { return static_cast<bool>(table_); }
+    const std::vector<Tensor>& table_bufs() const { return table_->bufs; }
+    const std::vector<uint32_t>& table_refs() const { return table_->refs; }
+    // logical channels `pick` (indices into this tensor's channels) of a dense tensor or of a table, as a table;
+    // buffers no picked channel uses are dropped
+    Tensor select_channels(const std::vector<int>& pick) const;
+    static Tensor concat_channels(const std::vector<Tensor>& parts);
 
     static Tensor wrap(void* ptr, size_t bytes, Device dev, std::function<void(void*)> deleter, std::vector<int64_t> sizes,
                        ScalarType dtype, Layout layout = Layout::NCHW);
@@ -82,8 +83,11 @@ private:
     std::vector<int64_t> sizes_;
     ScalarType dtype_ = ScalarType::Undefined;
     Layout layout_ = Layout::NCHW;
-    int64_t ctotal_ = 0;  // planes per image in storage; 0 = dense
-    std::shared_ptr<std::vector<Tensor>> parts_;
+    struct PlaneTable {
+        std::vector<Tensor> bufs;    // dense device fp32 NCHW tensors
+        std::vector<uint32_t> refs;  // per logical channel: (buffer << 24) | plane
+    };
+    std::shared_ptr<const PlaneTable> table_;
 };
 
 Tensor empty(std::vector<int64_t> sizes, ScalarType dtype);                       // host, zero-initialised
@@ -159,8 +163,7 @@ public:
     bool support_inplace = false;
     bool one_blob_only = false;
     bool support_packing = false;
-    bool accepts_views = false;      // extension: forward understands channel-range views of fp32 NCHW blobs
-    bool accepts_composite = false;  // extension: forward understands un-materialised channel concatenations
+    bool accepts_tables = false;  // extension: forward reads fp32 blobs through plane tables (see Tensor::is_table)
     std::vector<int> bottoms, tops;
     std::vector<Tensor> bottom_shapes, top_shapes;  // Int tensors [1,4] {N,C,H,W}
     std::string name;
@@ -184,7 +187,9 @@ struct LayerRegister {
 Tensor shape_tensor(int n, int c, int h, int w);                 // Int [1,4]
 void read_shape(const Tensor& shape, int& n, int& c, int& h, int& w);
 Tensor device_empty(const NetOption& opt, std::vector<int64_t> sizes, ScalarType dtype, Layout layout);  // from the ctx allocator
-Tensor materialize(const NetOption& opt, const Tensor& t);  // dense fp32 NCHW copy of a view or composite (or t itself)
+bool table_arrays(const Tensor& t, std::vector<const float*>& bufs, std::vector<int64_t>& strides);
+Tensor materialize(const NetOption& opt, const Tensor& t);  // dense fp32 NCHW copy of a plane table (or t itself)
+constexpr int kMaxTableBufs = 12, kMaxTableChannels = 512;  // limits of the kernels' plane tables
 
 // ---- ConvolutionLayer (Tensor/ConvolutionLayer.hpp:15-99): the quantized half only ----
 enum class ConvParam : int {

@@ -34,25 +34,66 @@ Tensor Tensor::view(std::vector<int64_t> sizes) const {
     return t;
 }
 
-Tensor Tensor::slice_channels(int64_t start, int64_t end) const {
-    if (!st_ || dim() != 4 || layout_ != Layout::NCHW || start < 0 || end > size(1) || end <= start) return Tensor();
-    Tensor t = *this;
-    t.ctotal_ = channels_total();
-    t.offset_ = offset_ + (size_t)(start * size(2) * size(3)) * elementSize(dtype_);
-    t.sizes_[1] = end - start;
+Tensor Tensor::select_channels(const std::vector<int>& pick) const {
+    if (!defined() || dim() != 4 || scalar_type() != ScalarType::Float || layout_ != Layout::NCHW) return Tensor();
+    auto tab = std::make_shared<PlaneTable>();
+    std::vector<int> remap;  // old buffer index -> new
+    const int c = (int)size(1);
+    if (is_table()) remap.assign(table_->bufs.size(), -1);
+    for (int ch : pick) {
+        if (ch < 0 || ch >= c) return Tensor();
+        if (!is_table()) {
+            if (tab->bufs.empty()) tab->bufs.push_back(*this);
+            tab->refs.push_back((uint32_t)ch);
+        } else {
+            const uint32_t r = table_->refs[(size_t)ch];
+            const int ob = (int)(r >> 24);
+            if (remap[(size_t)ob] < 0) {
+                remap[(size_t)ob] = (int)tab->bufs.size();
+                tab->bufs.push_back(table_->bufs[(size_t)ob]);
+            }
+            tab->refs.push_back(((uint32_t)remap[(size_t)ob] << 24) | (r & 0xFFFFFFu));
+        }
+    }
+    Tensor t;
+    t.sizes_ = sizes_;
+    t.sizes_[1] = (int64_t)pick.size();
+    t.dtype_ = ScalarType::Float;
+    t.layout_ = Layout::NCHW;
+    t.table_ = tab;
     return t;
 }
 
-Tensor Tensor::composite(std::vector<Tensor> parts) {
-    Tensor t;
-    if (parts.empty()) return t;
-    t.sizes_ = parts[0].sizes();
+Tensor Tensor::concat_channels(const std::vector<Tensor>& parts) {
+    if (parts.empty()) return Tensor();
+    auto tab = std::make_shared<PlaneTable>();
     int64_t c = 0;
-    for (const Tensor& p : parts) c += p.size(1);
+    for (const Tensor& p : parts) {
+        if (!p.defined() || p.dim() != 4 || p.scalar_type() != ScalarType::Float) return Tensor();
+        const uint32_t base = (uint32_t)tab->bufs.size();
+        if (p.is_table()) {
+            // reuse a buffer already listed (same storage) instead of listing it twice
+            std::vector<uint32_t> map(p.table_->bufs.size());
+            for (size_t i = 0; i < p.table_->bufs.size(); ++i) {
+                size_t j = 0;
+                for (; j < tab->bufs.size(); ++j)
+                    if (tab->bufs[j].raw_data() == p.table_->bufs[i].raw_data()) break;
+                if (j == tab->bufs.size()) tab->bufs.push_back(p.table_->bufs[i]);
+                map[i] = (uint32_t)j;
+            }
+            for (uint32_t r : p.table_->refs) tab->refs.push_back((map[r >> 24] << 24) | (r & 0xFFFFFFu));
+        } else {
+            tab->bufs.push_back(p);
+            for (int64_t i = 0; i < p.size(1); ++i) tab->refs.push_back((base << 24) | (uint32_t)i);
+        }
+        c += p.size(1);
+    }
+    Tensor t;
+    t.sizes_ = parts[0].sizes();
     t.sizes_[1] = c;
-    t.dtype_ = parts[0].scalar_type();
-    t.layout_ = parts[0].layout();
-    t.parts_ = std::make_shared<std::vector<Tensor>>(std::move(parts));
+    t.dtype_ = ScalarType::Float;
+    t.layout_ = Layout::NCHW;
+    t.table_ = tab;
     return t;
 }
 
@@ -119,20 +160,40 @@ Tensor device_empty(const NetOption& opt, std::vector<int64_t> sizes, ScalarType
     return Tensor::wrap(p, bytes, Device::CUDA, [ctx](void* q) { ott_free(ctx, q); }, std::move(sizes), dtype, layout);
 }
 
+// the arrays ott_conv_int8_forward_gather / ott_gather_channels_f32 take, from a plane table
+bool table_arrays(const Tensor& t, std::vector<const float*>& bufs, std::vector<int64_t>& strides) {
+    if (!t.is_table() || t.table_bufs().size() > (size_t)kMaxTableBufs || t.size(1) > kMaxTableChannels) return false;
+    const int64_t hw = t.size(2) * t.size(3);
+    for (const Tensor& b : t.table_bufs()) {
+        bufs.push_back(b.data_ptr<float>());
+        strides.push_back(b.size(1) * hw);
+    }
+    return true;
+}
+
 Tensor materialize(const NetOption& opt, const Tensor& t) {
-    if (!t.defined() || t.device() != Device::CUDA || t.scalar_type() != ScalarType::Float || t.dim() != 4) return t;
-    if (!t.is_composite() && t.is_dense()) return t;
+    if (!t.is_table()) return t;
     const int n = (int)t.size(0), c = (int)t.size(1), hw = (int)(t.size(2) * t.size(3));
     Tensor out = device_empty(opt, t.sizes(), ScalarType::Float, Layout::NCHW);
     if (!out.defined()) return Tensor();
-    std::vector<Tensor> parts = t.is_composite() ? t.parts() : std::vector<Tensor>{t};
-    int off = 0;
-    for (const Tensor& p : parts) {
-        if (p.is_composite()) return Tensor();  // concatenations do not nest
-        const int pc = (int)p.size(1);
-        if (ott_copy_channels_f32(opt.gpu, p.data_ptr<float>(), (int)p.channels_total(), 0, 1, out.data_ptr<float>(), c, off, 1, pc, n, hw) != OTT_OK)
+    std::vector<const float*> bufs;
+    std::vector<int64_t> strides;
+    if (table_arrays(t, bufs, strides)) {
+        if (ott_gather_channels_f32(opt.gpu, bufs.data(), strides.data(), (int)bufs.size(), t.table_refs().data(), c, n, hw, out.data_ptr<float>()) != OTT_OK)
             return Tensor();
-        off += pc;
+        return out;
+    }
+    // too many buffers or channels for one table: plane by plane runs
+    const auto& refs = t.table_refs();
+    int i = 0;
+    while (i < c) {
+        const uint32_t b = refs[(size_t)i] >> 24, p0 = refs[(size_t)i] & 0xFFFFFFu;
+        int run = 1;
+        while (i + run < c && (refs[(size_t)(i + run)] >> 24) == b && (refs[(size_t)(i + run)] & 0xFFFFFFu) == p0 + (uint32_t)run) ++run;
+        const Tensor& src = t.table_bufs()[b];
+        if (ott_copy_channels_f32(opt.gpu, src.data_ptr<float>(), (int)src.size(1), (int)p0, 1, out.data_ptr<float>(), c, i, 1, run, n, hw) != OTT_OK)
+            return Tensor();
+        i += run;
     }
     return out;
 }
@@ -391,11 +452,7 @@ int Net::do_forward_layer(const Layer* layer, std::vector<Tensor>& blob_tensors,
             ott_event_destroy(b);
         }
     } guard{this, layer, opt, ev0, ev1};
-    auto prepared = [&](const Tensor& t) {
-        const bool view = t.defined() && !t.is_composite() && !t.is_dense();
-        if ((t.is_composite() && !layer->accepts_composite) || (view && !layer->accepts_views)) return materialize(opt, t);
-        return t;
-    };
+    auto prepared = [&](const Tensor& t) { return (t.is_table() && !layer->accepts_tables) ? materialize(opt, t) : t; };
     if (layer->one_blob_only) {
         Tensor bottom = prepared(blob_tensors[(size_t)layer->bottoms[0]]);
         if (!bottom.defined()) { error_ = "could not materialise the input of layer " + layer->name; return -100; }
@@ -470,7 +527,7 @@ int Extractor::extract(int blob_index, Tensor& feat, int type) {
         const int ret = net_->forward_layer(net_->blobs_[(size_t)blob_index].producer, blob_tensors_, option);
         if (ret != 0) return ret;
     }
-    if (blob_tensors_[(size_t)blob_index].is_composite() || !blob_tensors_[(size_t)blob_index].is_dense()) {
+    if (blob_tensors_[(size_t)blob_index].is_table()) {
         Tensor dense = materialize(option, blob_tensors_[(size_t)blob_index]);
         if (!dense.defined()) return -100;
         blob_tensors_[(size_t)blob_index] = dense;
