@@ -150,6 +150,14 @@ int ott_conv_int8_forward_gather(ott_ctx* ctx, const ott_conv* conv, const float
 int ott_gather_channels_f32(ott_ctx* ctx, const float* const* buffers, const int64_t* image_strides, int n_buffers,
                             const uint32_t* plane_refs, int channels, int n, int hw, float* dst_dev);
 
+/* First layer + the max-pool that consumes it, in one kernel: out = MaxPool3x3/stride2/pad1(forward(in)), fp32 NCHW
+ * [n][cout][(oh-1)/2+1][(ow-1)/2+1]. Replaces the pair conv1 -> pool1 of the reference's graphs (Tensor/ConvolutionLayer.cpp:754-847
+ * followed by Tensor/MaxPoolLayer.cpp:123-133) when nothing else reads conv1; the values pooled are exactly the ones the
+ * separate layer would have stored. Only for the 3-input-channel 3x3 layer with fp32 output (else OTT_ERR_UNSUPPORTED).
+ * pad_with_zero as in ott_maxpool_f32_nchw. */
+int ott_conv_int8_forward_maxpool(ott_ctx* ctx, const ott_conv* conv, const float* in_dev, int n, int h, int w, int pad_with_zero,
+                                  float* out_dev);
+
 /* The same forward on HOST buffers: copies the input to the device, runs, copies the output back and
  * waits for it. This is the call a host-tensor Layer::forward maps to (Tensor/Net.cpp:442). */
 int ott_conv_int8_forward_host(ott_ctx* ctx, const ott_conv* conv, const void* in_host, int in_dtype, int n, int h,

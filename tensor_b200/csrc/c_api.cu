@@ -390,6 +390,29 @@ int ott_conv_int8_forward_gather(ott_ctx* ctx, const ott_conv* c, const float* c
     return conv_forward_impl(ctx, c, buffers[0], &g, OTT_F32_NCHW, n, h, w, out_dev, out_dtype, status_word_dev);
 }
 
+int ott_conv_int8_forward_maxpool(ott_ctx* ctx, const ott_conv* c, const float* in_dev, int n, int h, int w, int pad_with_zero, float* out_dev) {
+    if (!ctx || !c || !in_dev || !out_dev || n < 0 || h <= 0 || w <= 0) return OTT_ERR_INVALID;
+    const ott_conv_desc& d = c->d;
+    ConvShape s{};
+    s.n = n; s.h = h; s.w = w;
+    s.oh = out_dim(h, d.kh, d.sh, d.ph, d.dh);
+    s.ow = out_dim(w, d.kw, d.sw, d.pw, d.dw);
+    s.cin = d.cin; s.cout = d.cout; s.cin_pad = c->cin_pad; s.cout_pad = c->cout_pad;
+    s.kh = d.kh; s.kw = d.kw; s.sh = d.sh; s.sw = d.sw; s.ph = d.ph; s.pw = d.pw; s.dh = d.dh; s.dw = d.dw;
+    if (d.int8_scale_term > 100 || c->kind != OTT_KERNEL_DENSE_DIRECT || !dense_stem_supports(s, OTT_F32_NCHW, OTT_F32_NCHW) || s.oh < 1 || s.ow < 1)
+        return ctx->fail(OTT_ERR_UNSUPPORTED, "the fused max-pool exists for the 3-channel 3x3 first layer with fp32 output only");
+    if (n == 0) return OTT_OK;
+    cudaSetDevice(ctx->device);
+    EpilogueParams ep{};
+    ep.scale_in = c->scale_in_dev; ep.bias = c->bias_dev; ep.scale_out = c->scale_out_dev;
+    ep.has_bias = d.bias_term ? 1 : 0;
+    ep.act_type = d.act_type; ep.act_param0 = d.act_param0; ep.rounding = d.rounding;
+    OTT_CUDA_CHECK(ctx, launch_dense_stem_pool(ctx->stream, s, in_dev, c->w_host.data(), c->scale_in_host.data(), c->bias_host.data(), c->in_scale0,
+                                                ep, out_dev, pad_with_zero));
+    ctx->launches += 1;
+    return OTT_OK;
+}
+
 int ott_gather_channels_f32(ott_ctx* ctx, const float* const* buffers, const int64_t* image_strides, int n_buffers, const uint32_t* plane_refs,
                             int channels, int n, int hw, float* dst_dev) {
     if (!ctx || !buffers || !image_strides || !plane_refs || !dst_dev || channels < 0 || n < 0 || hw < 0) return OTT_ERR_INVALID;

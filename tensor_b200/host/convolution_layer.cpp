@@ -172,6 +172,12 @@ int ConvolutionLayer::create_pipeline(const NetOption& opt) {
                                 requant ? (int)top_blob_int8_scales.numel() : 0, &gpu_conv_);
 }
 
+bool ConvolutionLayer::can_fuse_maxpool() const {
+    return int8_scale_term > 0 && int8_scale_term < 100 && groups == 1 && in_channels == 3 && kernel_height == 3 && kernel_width == 3 &&
+           dilation_height == 1 && dilation_width == 1 && stride_height == stride_width && (stride_height == 1 || stride_height == 2) &&
+           ott_nhwc_channels(out_channels) <= 32;
+}
+
 // Tensor/ConvolutionLayer.cpp:507-511 -> forward_int8 (:754-847). Device tensors in and out; asynchronous.
 int ConvolutionLayer::forward(const Tensor& bottom_blob, Tensor& top_blob, const NetOption& opt) const {
     if (!gpu_conv_ || !bottom_blob.defined() || bottom_blob.device() != Device::CUDA || bottom_blob.dim() != 4) return -1;
@@ -181,6 +187,12 @@ int ConvolutionLayer::forward(const Tensor& bottom_blob, Tensor& top_blob, const
     ott_conv_int8_out_shape(gpu_conv_, h, w, &oh, &ow);
     const bool requant = int8_scale_term > 100;
     const int out_dtype = requant ? OTT_S8_NHWC : OTT_F32_NCHW;
+    if (fused_maxpool && !bottom_blob.is_table() && bottom_blob.scalar_type() == ScalarType::Float) {
+        top_blob = device_empty(opt, {n, out_channels, (oh - 1) / 2 + 1, (ow - 1) / 2 + 1}, ScalarType::Float, Layout::NCHW);
+        if (!top_blob.defined()) return -100;
+        return ott_conv_int8_forward_maxpool(opt.gpu, gpu_conv_, bottom_blob.data_ptr<float>(), n, h, w, fused_maxpool == 2 ? 1 : 0,
+                                             top_blob.data_ptr<float>());
+    }
     Tensor src = bottom_blob;
     std::vector<const float*> bufs;
     std::vector<int64_t> strides;

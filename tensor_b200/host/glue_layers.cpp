@@ -53,8 +53,13 @@ public:
         kh = pd.get(0, 3); kw = pd.get(1, 3); sh = pd.get(2, 1); sw = pd.get(3, 1); ph = pd.get(4, 0); pw = pd.get(5, 0);
         return 0;
     }
+    bool is_pool3x3s2p1() const override { return kh == 3 && kw == 3 && sh == 2 && sw == 2 && ph == 1 && pw == 1; }
     int forward(const Tensor& bottom, Tensor& top, const NetOption& opt) const override {
         if (!is_dev_f32(bottom)) return -1;
+        if (absorbed) {  // the producing convolution already pooled (Net::compile fused the pair)
+            top = bottom;
+            return 0;
+        }
         const int n = (int)bottom.size(0), c = (int)bottom.size(1), h = (int)bottom.size(2), w = (int)bottom.size(3);
         const int oh = (h + 2 * ph - kh) / sh + 1, ow = (w + 2 * pw - kw) / sw + 1;
         top = device_empty(opt, {n, c, oh, ow}, ScalarType::Float, Layout::NCHW);

@@ -125,6 +125,7 @@ public:
     int openmp_blocktime = 20;
     int device = 0;                   // NEW: CUDA device of the Net
     ott_ctx* gpu = nullptr;           // set by Net::compile; what every Layer::forward launches on
+    bool fuse_first_layer_pool = true;  // run conv1 -> MaxPool(3x3, s2, p1) as one kernel when nothing else reads conv1
     int int8_rounding = OTT_ROUND_ADD_HALF_TRUNC;  // which reference build is mirrored (packed x86 default / aarch64)
     std::vector<float>* layer_ms = nullptr;  // when set: per-layer device time, indexed by layer (Extractor::benchmark_info)
 };
@@ -164,6 +165,9 @@ public:
     bool one_blob_only = false;
     bool support_packing = false;
     bool accepts_tables = false;  // extension: forward reads fp32 blobs through plane tables (see Tensor::is_table)
+    // extension: a 3x3 stride-2 pad-1 max-pool can be absorbed into the first convolution layer (Net::compile decides)
+    virtual bool is_pool3x3s2p1() const { return false; }
+    bool absorbed = false;  // this layer's work is done by its producer; forward passes the blob through
     std::vector<int> bottoms, tops;
     std::vector<Tensor> bottom_shapes, top_shapes;  // Int tensors [1,4] {N,C,H,W}
     std::string name;
@@ -218,6 +222,11 @@ public:
     // the reference's own fields, host tensors: weight Byte OIHW, the rest Float
     Tensor weight_data, bias_data, weight_data_int8_scales, bottom_blob_int8_scales, top_blob_int8_scales, scale_in_data;
 
+    // set by Net::compile when the layer's only consumer is an absorbable max-pool: 0 none, 1 pool (padding ignored),
+    // 2 pool with the reference's packed zero-padding rule
+    int fused_maxpool = 0;
+    bool can_fuse_maxpool() const;
+
 private:
     ott_conv* gpu_conv_ = nullptr;
     ott_ctx* gpu_ctx_ = nullptr;
@@ -267,6 +276,7 @@ private:
     std::vector<Blob> blobs_;
     std::vector<LayerOption> layer_options_;
     std::vector<std::string> input_names_, output_names_;
+    std::vector<char> blob_fused_away_;  // blobs that exist only inside a fused kernel
     mutable std::string error_;
     bool owns_ctx_ = false;
 };

@@ -384,6 +384,22 @@ int Net::compile(CompileMode mode) {
             if (rc != 0) { error_ = "create_pipeline of " + layer->name + " failed: " + ott_last_error(option.gpu); return rc; }
         }
     }
+    // first layer + max-pool fusion: conv1's blob must have the pool as its only reader
+    blob_fused_away_.assign(blobs_.size(), 0);
+    if (option.fuse_first_layer_pool && mode == CompileMode::Initial) {
+        for (Layer* l : layers_) {
+            auto* conv = dynamic_cast<ConvolutionLayer*>(l);
+            if (!conv || !conv->can_fuse_maxpool()) continue;
+            const Blob& b = blobs_[(size_t)conv->tops[0]];
+            if (b.consumer < 0) continue;
+            Layer* pool = layers_[(size_t)b.consumer];
+            if (!pool->is_pool3x3s2p1() || pool->bottoms.size() != 1) continue;
+            // same rule as MaxPoolLayer::forward: the reference's packed 3x3 s2 kernels pad with zeros
+            conv->fused_maxpool = (option.use_packing_layout && conv->out_channels % 4 == 0) ? 2 : 1;
+            pool->absorbed = true;
+            blob_fused_away_[(size_t)conv->tops[0]] = 1;
+        }
+    }
     input_names_.clear();
     output_names_.clear();
     for (Layer* l : layers_)
@@ -523,6 +539,10 @@ int Extractor::extract(const std::string& blob_name, Tensor& feat, int type) {
 
 int Extractor::extract(int blob_index, Tensor& feat, int type) {
     if (blob_index < 0 || blob_index >= (int)blob_tensors_.size()) return -1;
+    if (net_->blob_fused_away_[(size_t)blob_index]) {
+        net_->error_ = "blob " + net_->blobs_[(size_t)blob_index].name + " only exists inside a fused kernel; set NetOption::fuse_first_layer_pool = false to extract it";
+        return -1;
+    }
     if (!blob_tensors_[(size_t)blob_index].defined()) {
         const int ret = net_->forward_layer(net_->blobs_[(size_t)blob_index].producer, blob_tensors_, option);
         if (ret != 0) return ret;

@@ -61,3 +61,26 @@ def test_unknown_layer_type_is_an_error_not_an_exit():
         net.compile()
     assert "Unknown layer type" in str(e.value)
     net.close()
+
+
+@pytest.mark.parametrize("h,w,cout,act", [(45, 71, 24, "LRelu"), (64, 64, 16, "Relu"), (33, 130, 22, "LRelu")])
+def test_first_layer_and_maxpool_fused_kernel(h, w, cout, act):
+    """conv1 -> pool1 runs as one kernel; the pooled blob must equal the layer-by-layer checker, including the reference's
+    packed zero-padding rule (cout % 4 == 0) after an activation that leaves negative values."""
+    from graph_support import build_net, oracle_conv, oracle_conv_for_calibration
+    from tensor_b200 import OtterB200Error
+    L = [dict(type="Input", name="data", output="data", channel=3, height=h, width=w),
+         graphs._conv("conv1", "data", cout, 3, 2, 1, 2, act),
+         dict(type="MaxPool", name="pool1", input="conv1", output="pool1", kernel_h=3, kernel_w=3, stride_h=2, stride_w=2, padding_h=1, padding_w=1)]
+    params = graphs.make_params(L)
+    x = (np.random.default_rng(21).uniform(0, 1, size=(2, 3, h, w)).astype(np.float32))
+    graphs.calibrate(L, params, x[:1], oracle_conv_for_calibration)
+    params["conv1"]["bias"] -= np.float32(0.3)  # push many outputs negative so the padding rule decides border maxima
+    want = graphs.walk(L, x, oracle_conv(params))["pool1"]
+    net = build_net(L, params)
+    got = net.forward("data", x, ["pool1"])[0]
+    assert got.shape == want.shape
+    assert np.array_equal(bits(got), bits(want))
+    with pytest.raises(OtterB200Error):  # conv1 only exists inside the fused kernel
+        net.forward("data", x, ["conv1"])
+    net.close()
