@@ -49,6 +49,13 @@ WORKLOADS = {
     "pw_512_1024_hw56_s8": dict(cin=512, cout=1024, k=1, stride=1, pad=0, groups=1, n=128, h=56, w=56, term=101, act=ACT_RELU6, in_f32=False),
     "pw_256_512_hw56_s8": dict(cin=256, cout=512, k=1, stride=1, pad=0, groups=1, n=128, h=56, w=56, term=101, act=ACT_RELU6, in_f32=False),
     "pw_64_256_hw56_s8": dict(cin=64, cout=256, k=1, stride=1, pad=0, groups=1, n=128, h=56, w=56, term=101, act=ACT_RELU6, in_f32=False),
+    # ShuffleNetV2-1.0x stage-3 unit shapes at batch 256 (116 channels, 20x20): the layers the graph workload is made of
+    "sn_pw1_116_hw20": dict(cin=116, cout=116, k=1, stride=1, pad=0, groups=1, n=256, h=20, w=20, term=102, act=ACT_RELU, in_f32=True),
+    "sn_pw2_116_hw20": dict(cin=116, cout=116, k=1, stride=1, pad=0, groups=1, n=256, h=20, w=20, term=2, act=ACT_RELU, in_f32=False),
+    "sn_dw_116_hw20": dict(cin=116, cout=116, k=3, stride=1, pad=1, groups=116, n=256, h=20, w=20, term=101, act=ACT_NONE, in_f32=False, w_std=0.1),
+    "sn_pw1_58_hw40": dict(cin=58, cout=58, k=1, stride=1, pad=0, groups=1, n=256, h=40, w=40, term=102, act=ACT_RELU, in_f32=True),
+    "sn_pw2_58_hw40": dict(cin=58, cout=58, k=1, stride=1, pad=0, groups=1, n=256, h=40, w=40, term=2, act=ACT_RELU, in_f32=False),
+    "sn_dw_58_hw40": dict(cin=58, cout=58, k=3, stride=1, pad=1, groups=58, n=256, h=40, w=40, term=101, act=ACT_NONE, in_f32=False, w_std=0.1),
     # depthwise (config 2): N=64, C=256, 56x56, ReLU, int8 out
     "dw3x3s1_c256": dict(cin=256, cout=256, k=3, stride=1, pad=1, groups=256, n=64, h=56, w=56, term=101, act=ACT_RELU, in_f32=True, w_std=0.1),
     "dw3x3s2_c256": dict(cin=256, cout=256, k=3, stride=2, pad=1, groups=256, n=64, h=56, w=56, term=101, act=ACT_RELU, in_f32=True, w_std=0.1),
@@ -642,20 +649,35 @@ def run_net_gpu_arm(args, cfg):
                                                   ("Convolution/1x1" if geo[nm]["k"] == 1 else "Convolution/stem3x3"))
             by_type[key] = by_type.get(key, 0.0) + ms
         total_prof = sum(by_type.values())
-        # dominant single layer: algorithmic bytes at its boundary dtypes over its own measured time
+        # dominant layer kind: its layers' algorithmic bytes (boundary dtypes) over their measured device time
         int8_blobs = {k for k, g in geo.items() if g["term"] > 100}
-        t_, nm, ms = max((p for p in prof if p[0] == "Convolution"), key=lambda p: p[2])
-        g = geo[nm]
-        wl = _layer_wl(g, hws[nm], in_f32=g["input"] not in int8_blobs)
-        ops, byts = algorithmic_work(wl, n)
-        ach = byts / (ms * 1e-3) / 1e9
+        kind_of = lambda g: "Convolution/depthwise" if g["groups"] > 1 else ("Convolution/1x1" if g["k"] == 1 else "Convolution/stem3x3")  # noqa: E731
+        dom = max((k for k in by_type if k.startswith("Convolution")), key=lambda k: by_type[k])
+        dom_bytes = dom_ops = dom_ms = 0.0
+        dom_layers = 0
+        for t_, nm, ms in prof:
+            if t_ != "Convolution" or kind_of(geo[nm]) != dom:
+                continue
+            g = geo[nm]
+            wl = _layer_wl(g, hws[nm], in_f32=g["input"] not in int8_blobs)
+            ops, byts = algorithmic_work(wl, n)
+            dom_bytes += byts
+            dom_ops += ops
+            dom_ms += ms
+            dom_layers += 1
+        ach = dom_bytes / (dom_ms * 1e-3) / 1e9
+        kernels = {"Convolution/1x1": "quantize_nchw_to_nhwc_kernel (fp32 inputs) + dense_umma_kernel", "Convolution/depthwise": "depthwise_tiled_kernel",
+                   "Convolution/stem3x3": "dense_stem_pool_kernel"}[dom]
         roof = {"bound": "hbm", "achieved": ach, "peak": hbm_peak, "unit": "GB/s", "frac": ach / hbm_peak, "traffic": None,
-                "peak_source": hbm_src, "kernel": f"layer {nm}: {g['cin']}->{g['cout']} k{g['k']} s{g['stride']} groups {g['groups']} "
-                f"@{hws[nm][0]}x{hws[nm][1]} ({'fp32' if wl['in_f32'] else 'int8'} in, {'int8' if g['term'] > 100 else 'fp32'} out)",
-                "kernel_ms": ms, "algorithmic_bytes_per_launch": byts, "ops_per_launch": ops,
+                "peak_source": hbm_src, "kernel": f"{kernels}: the {dom_layers} {dom} layers of the graph",
+                "kernel_ms": dom_ms / dom_layers, "algorithmic_bytes_per_launch": dom_bytes / dom_layers, "ops_per_launch": dom_ops / dom_layers,
+                "launches_per_step": dom_layers,
                 "time_share_by_layer_kind": {k: round(v / total_prof, 4) for k, v in sorted(by_type.items(), key=lambda kv: -kv[1])},
                 "profiled_ms_per_step": total_prof,
                 "top_layers_ms": [[nm_, round(ms_, 4)] for _, nm_, ms_ in sorted(prof, key=lambda p: -p[2])[:12]]}
+        traffic_file = ROOT / "profiles" / "traffic.json"
+        if traffic_file.exists():
+            roof["traffic"] = json.loads(traffic_file.read_text()).get(args.workload)
         cpu = None
         if not args.no_cpu:
             per_img, how, cores, kind = net_cpu_reference_time(graphs.shufflenetv2_layers(H, W, batch=1), H, W, reps=3)

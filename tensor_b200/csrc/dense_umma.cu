@@ -451,6 +451,9 @@ bool umma_plan_layer(int cin, int cout, int kh, int kw, int sh, int sw, int dh, 
     const long left = (long)smem_budget - 1024 - 4096 - (long)p.bn * k_total;
     p.stages = (int)(left / a_stage);
     if (p.stages > 8) p.stages = 8;
+    // Small layers (few k-blocks, narrow panels) are latency-bound with one CTA per SM: keep the pipeline short so that
+    // several CTAs fit an SM and overlap each other's TMA / MMA / epilogue latencies.
+    if (p.nkb <= 2 && p.stages > 4) p.stages = 4;
     if (p.stages < 2) return false;
     // two accumulators of bn columns each; TMEM allocations are powers of two >= 32 columns
     p.acc_stride = p.bn <= 32 ? 32 : (p.bn <= 64 ? 64 : (p.bn <= 128 ? 128 : 256));
@@ -461,6 +464,16 @@ bool umma_plan_layer(int cin, int cout, int kh, int kw, int sh, int sw, int dh, 
     p.cout_rows = p.n_tiles * p.bn;
     SmemLayout L = smem_layout(p);
     p.smem_bytes = (int)L.total + 1024;
+    // CTAs per SM: TMEM has 512 columns per SM and the hardware scheduler does not account for them, so the shared-memory
+    // request is padded until no more CTAs fit an SM than TMEM can serve (a CTA that cannot get its columns would wait
+    // inside tcgen05.alloc for a neighbour to finish).
+    int by_tmem = 512 / p.tmem_cols;
+    int by_smem = smem_budget / p.smem_bytes;
+    p.ctas_per_sm = by_tmem < by_smem ? by_tmem : by_smem;
+    if (p.ctas_per_sm > 4) p.ctas_per_sm = 4;
+    if (p.ctas_per_sm < 1) p.ctas_per_sm = 1;
+    const int min_smem = smem_budget / (p.ctas_per_sm + 1) + 1;
+    if (p.smem_bytes < min_smem) p.smem_bytes = min_smem;
     *plan = p;
     return true;
 }
@@ -530,7 +543,7 @@ const char* launch_dense_umma(cudaStream_t stream, int sm_count, const UmmaPlan&
     }
     if (r != CUDA_SUCCESS) return "cuTensorMapEncodeTiled(activations) failed";
 
-    int per_n = sm_count / p.n_tiles;
+    int per_n = sm_count * p.ctas_per_sm / p.n_tiles;
     if (per_n < 1) per_n = 1;
     if (per_n > p.m_tiles) per_n = p.m_tiles;
     const int grid = per_n * p.n_tiles;
