@@ -119,15 +119,15 @@ dense_stem_kernel(const float* __restrict__ x, const __grid_constant__ StemParam
 
 // ---- stem convolution followed by a 3x3 stride-2 pad-1 max-pool, in one kernel ----
 // The pool is the only consumer of the first layer's output in the benchmark graphs (conv1 -> pool1), and that output is
-// the largest tensor of the whole network; here it never leaves the SM. One CTA produces a 32x4 tile of POOLED pixels for
-// all channels: it computes the 65x9 convolution outputs under that tile into shared memory (fp32, after the
+// the largest tensor of the whole network; here it never leaves the SM. One CTA produces a 16x7 tile of POOLED pixels for
+// all channels: it computes the 33x15 convolution outputs under that tile into shared memory (fp32, after the
 // dequantize epilogue and activation, exactly the values the separate layer would have stored) and max-reduces them.
 // pad_zero selects the reference's packed max-pool rule (padding counts as 0, Tensor/Pool.cpp:972-975) or its plain
 // rule (padding never wins).
-constexpr int SP_PX = 32, SP_PY = 4;                       // pooled tile
+constexpr int SP_PX = 16, SP_PY = 7;                       // pooled tile: 33x15 = 495 convolution outputs ~ 2 x 256 threads
 constexpr int SP_CX = 2 * SP_PX + 1, SP_CY = 2 * SP_PY + 1;  // convolution outputs under it
 
-template <int S, int ACT>
+template <int S, int ACT, int NCO>
 __global__ void __launch_bounds__(256)
 dense_stem_pool_kernel(const float* __restrict__ x, const __grid_constant__ StemParams P, float in_scale, int has_bias, float act_p0,
                        int rounding, float* __restrict__ out, ConvShape s, int ph_out, int pw_out, int tiles_x, int tiles_y, int pad_zero) {
@@ -193,16 +193,23 @@ dense_stem_pool_kernel(const float* __restrict__ x, const __grid_constant__ Stem
         kw[4] = __byte_perm(win[5], win[6], 0x5421);
         kw[5] = __byte_perm(win[6], win[7], 0x6542);
         kw[6] = __byte_perm(win[8], 0u, 0x4210);
+        // NCO (the channel count rounded up to 8) is a template parameter so that the channel loop unrolls completely:
+        // four independent accumulator chains at a time, weights as immediate constant-bank operands
 #pragma unroll
-        for (int co = 0; co < ST_COUT_MAX; ++co) {
-            if (co >= s.cout) break;
-            int acc = 0;
+        for (int g = 0; g < NCO / 4; ++g) {
+            int acc[4] = {0, 0, 0, 0};
 #pragma unroll
-            for (int k = 0; k < 7; ++k) acc = __dp4a((int)kw[k], (int)P.w[co][k], acc);
-            const float a = __int2float_rn(acc);
-            float v = has_bias ? __fmaf_rn(a, P.scale_in[co], P.bias[co]) : __fmul_rn(a, P.scale_in[co]);
-            v = activate_t<ACT>(v, act_p0);
-            conv[(co * SP_CY + ly) * SP_CX + lx] = inside ? v : outside;
+            for (int k = 0; k < 7; ++k)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[j] = __dp4a((int)kw[k], (int)P.w[g * 4 + j][k], acc[j]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int co = g * 4 + j;
+                const float a = __int2float_rn(acc[j]);
+                float v = has_bias ? __fmaf_rn(a, P.scale_in[co], P.bias[co]) : __fmul_rn(a, P.scale_in[co]);
+                v = activate_t<ACT>(v, act_p0);
+                if (co < s.cout) conv[(co * SP_CY + ly) * SP_CX + lx] = inside ? v : outside;
+            }
         }
     }
     __syncthreads();
@@ -266,9 +273,11 @@ static cudaError_t launch_pool_s(cudaStream_t stream, const float* x, const Stem
     if (blocks <= 0) return cudaSuccess;
     constexpr int IW = (SP_CX - 1) * S + 3, IH = (SP_CY - 1) * S + 3, RP = (IW + 3 + 3) / 4 + 1;
     const size_t smem = (size_t)3 * IH * RP * 4 + (size_t)s.cout * SP_CY * SP_CX * 4;
+    const int nco = (s.cout + 7) / 8 * 8;
 #define OTT_STEMPOOL_LAUNCH(ACT)                                                                                          \
     {                                                                                                                     \
-        auto kernel = dense_stem_pool_kernel<S, ACT>;                                                                     \
+        auto kernel = nco <= 8 ? dense_stem_pool_kernel<S, ACT, 8> : nco <= 16 ? dense_stem_pool_kernel<S, ACT, 16>      \
+                      : nco <= 24 ? dense_stem_pool_kernel<S, ACT, 24> : dense_stem_pool_kernel<S, ACT, 32>;              \
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);            \
         if (e != cudaSuccess) return e;                                                                                   \
         kernel<<<(unsigned)blocks, 256, smem, stream>>>(x, P, in_scale, ep.has_bias, ep.act_param0, ep.rounding, out, s, ph_out, pw_out,  \
