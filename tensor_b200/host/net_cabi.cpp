@@ -149,10 +149,8 @@ int ott_net_forward(ott_net* net, const char* input_blob, const void* in, int in
     }
     for (int i = 0; i < n_out; ++i) {
         if (!out_host || !out_host[i]) continue;
-        otter::Tensor host;
-        rc = ex.extract(out_blobs[i], host, 0);
+        rc = ex.extract_into(out_blobs[i], out_host[i]);
         if (rc != 0) return rc;
-        std::memcpy(out_host[i], host.raw_data(), (size_t)host.numel() * otter::elementSize(host.scalar_type()));
     }
     return OTT_OK;
 }

@@ -293,6 +293,8 @@ public:
     // stream synchronisation; type 1: the device tensor as it is (asynchronous)
     int extract(const std::string& blob_name, Tensor& feat, int type = 0);
     int extract(int blob_index, Tensor& feat, int type = 0);
+    // extract(..., type 0) straight into caller memory (pinned memory makes the copy run at PCIe speed): no staging tensor
+    int extract_into(const std::string& blob_name, void* host_dst);
     // per-layer device times in ms of the layers that ran to produce blob_name (Tensor/Net.cpp:811-850 benchmark_info):
     // CUDA events around every layer, so the layers run serialised; ms has one entry per layer of the Net
     int benchmark_info(const std::string& blob_name, std::vector<float>& ms);

@@ -537,6 +537,22 @@ int Extractor::extract(const std::string& blob_name, Tensor& feat, int type) {
     return extract(idx, feat, type);
 }
 
+int Extractor::extract_into(const std::string& blob_name, void* host_dst) {
+    Tensor dev;
+    int rc = extract(blob_name, dev, 1);
+    if (rc != 0) return rc;
+    if (dev.layout() == Layout::NCHW) {
+        rc = ott_memcpy_d2h(option.gpu, host_dst, dev.raw_data(), (size_t)dev.numel() * elementSize(dev.scalar_type()));
+        if (rc == OTT_OK) rc = ott_sync(option.gpu);
+        return rc;
+    }
+    Tensor host;
+    rc = extract(blob_name, host, 0);
+    if (rc != 0) return rc;
+    std::memcpy(host_dst, host.raw_data(), (size_t)host.numel() * elementSize(host.scalar_type()));
+    return 0;
+}
+
 int Extractor::extract(int blob_index, Tensor& feat, int type) {
     if (blob_index < 0 || blob_index >= (int)blob_tensors_.size()) return -1;
     if (net_->blob_fused_away_[(size_t)blob_index]) {
