@@ -28,6 +28,15 @@ ott_ctx* ott_net_context(ott_net* net); /* valid after ott_net_compile */
  * stride, int8_scale_term, activation, groups, axis, start, end, ...). */
 int ott_net_add_layer(ott_net* net, const char* options);
 
+/* Net::load_otter(path, CompileMode::Initial) (Tensor/Net.cpp:518-536): reads a `.otter` text graph (Tensor/Otter.cpp),
+ * adds its layers and compiles. Use instead of ott_net_add_layer + ott_net_compile. */
+int ott_net_load_otter(ott_net* net, const char* path);
+
+/* The `.otter` reader alone (no GPU needed): parses `text` and writes one line per layer, "key=value;key=value;..." with
+ * the layer type under key "type", into out (NUL-terminated, at most cap bytes). Returns the number of layers, or a
+ * negative status (OTT_ERR_INVALID on a syntax error or when cap is too small). */
+int ott_otter_parse_text(const char* text, char* out, int cap);
+
 /* Net::compile(CompileMode::Initial) (Tensor/Net.cpp:174-280): builds the graph (automatic Split layers for
  * fan-out), creates the layers, infers shapes, gives every layer random parameters and builds its pipeline. */
 int ott_net_compile(ott_net* net);

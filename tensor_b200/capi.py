@@ -73,6 +73,8 @@ SIGNATURES = {
     "ott_net_context": (vp, [vp]),
     "ott_net_add_layer": (i32, [vp, C.c_char_p]),
     "ott_net_compile": (i32, [vp]),
+    "ott_net_load_otter": (i32, [vp, C.c_char_p]),
+    "ott_otter_parse_text": (i32, [C.c_char_p, C.c_char_p, i32]),
     "ott_net_layer_count": (i32, [vp]),
     "ott_net_layer_info": (i32, [vp, i32, C.c_char_p, i32, C.c_char_p, i32, C.POINTER(i32)]),
     "ott_net_blob_shape": (i32, [vp, C.c_char_p, C.POINTER(i32)]),
@@ -249,6 +251,20 @@ class ConvInt8:
             self.h = None
 
 
+def parse_otter_text(text: str):
+    """The library's .otter reader on a string: list of option dictionaries (values as strings), in file order."""
+    lib = library()
+    cap = 64 + 4 * len(text)
+    buf = C.create_string_buffer(cap)
+    n = lib.ott_otter_parse_text(text.encode(), buf, cap)
+    if n < 0:
+        raise OtterB200Error(n, "otter syntax error")
+    out = []
+    for line in buf.value.decode().splitlines():
+        out.append(dict(item.split("=", 1) for item in line.split(";")))
+    return out
+
+
 class Net:
     """ctypes wrapper over include/otter_b200_net.h: a Net built from the reference's LayerOption key/value pairs."""
 
@@ -273,6 +289,10 @@ class Net:
 
     def compile(self):
         self.check(self.lib.ott_net_compile(self.h))
+
+    def load_otter(self, path: str):
+        """Read a .otter text graph (the reference's model-structure format) and compile it."""
+        self.check(self.lib.ott_net_load_otter(self.h, str(path).encode()))
 
     def context(self) -> "Context":
         ctx = Context.__new__(Context)

@@ -67,6 +67,29 @@ int ott_net_add_layer(ott_net* net, const char* options) {
     return OTT_OK;
 }
 
+int ott_net_load_otter(ott_net* net, const char* path) {
+    if (!net || !path) return OTT_ERR_INVALID;
+    net->error.clear();
+    return net->net.load_otter(path, otter::CompileMode::Initial);
+}
+
+int ott_otter_parse_text(const char* text, char* out, int cap) {
+    if (!text || !out || cap <= 0) return OTT_ERR_INVALID;
+    std::vector<otter::LayerOption> layers;
+    std::string err;
+    if (otter::parse_otter_text(text, layers, err) != 0) return OTT_ERR_INVALID;
+    std::string s;
+    for (auto& l : layers) {
+        s += "type=" + l["type"];
+        for (auto& kv : l)
+            if (kv.first != "type") s += ";" + kv.first + "=" + kv.second;
+        s += "\n";
+    }
+    if ((int)s.size() + 1 > cap) return OTT_ERR_INVALID;
+    std::memcpy(out, s.c_str(), s.size() + 1);
+    return (int)layers.size();
+}
+
 int ott_net_compile(ott_net* net) {
     if (!net) return OTT_ERR_INVALID;
     net->error.clear();

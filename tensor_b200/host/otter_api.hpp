@@ -241,6 +241,7 @@ struct Blob {
 
 enum class CompileMode { Initial, OnlyStructure };
 class Extractor;
+int parse_otter_text(const std::string& text, std::vector<LayerOption>& layers, std::string& err);  // the .otter reader
 
 class Net {
     friend class Extractor;
@@ -252,6 +253,7 @@ public:
 
     void addLayer(LayerOption option);
     int compile(CompileMode mode = CompileMode::Initial);  // 0 on success (the reference throws on a bad graph)
+    int load_otter(const char* model_structure, CompileMode mode = CompileMode::Initial);  // Tensor/Net.cpp:518-536
     Extractor create_extractor() const;
     void summary() const;
     int find_blob_index_by_name(const std::string& name) const;
