@@ -325,3 +325,64 @@ REF_API int ref_layer_forward(const char* type, const char* options, int n_in, c
         return 0;
     } catch (const std::exception& e) { g_err = e.what(); return -2; } catch (const char* s) { g_err = s; return -3; } catch (...) { g_err = "unknown"; return -4; }
 }
+
+// ---- the reference's whole Net (Tensor/Net.cpp) on a .otter graph, with caller-supplied convolution parameters ----
+// Net keeps its layers private; this test driver reaches them to replace the random parameters CompileMode::Initial
+// gives (the reference's own way in is a weight file). Access specifiers do not change object layout.
+#define private public
+#include "Net.hpp"
+#undef private
+
+namespace {
+std::unique_ptr<otter::Net> g_net;
+}
+
+REF_API int ref_net_open(const char* otter_path, int packed) {
+    try {
+        g_net.reset(new otter::Net());
+        g_net->option.use_packing_layout = packed != 0;
+        g_net->option.lightmode = true;
+        return g_net->load_otter(otter_path, otter::CompileMode::Initial);
+    } catch (const std::exception& e) { g_err = e.what(); g_net.reset(); return -2; } catch (const char* s) { g_err = s; g_net.reset(); return -3; } catch (...) { g_err = "unknown"; g_net.reset(); return -4; }
+}
+
+REF_API void ref_net_close() { g_net.reset(); }
+
+REF_API int ref_net_set_conv(const char* layer_name, const int8_t* w_oihw, const float* bias, const float* w_scales, const float* in_scales,
+                             int n_in_scales, const float* out_scales, int n_out_scales) {
+    try {
+        if (!g_net) { g_err = "no net"; return -1; }
+        for (otter::Layer* l : g_net->layers) {
+            if (l->name != layer_name) continue;
+            auto* c = dynamic_cast<otter::ConvolutionLayer*>(l);
+            if (!c) { g_err = "not a convolution"; return -1; }
+            const int wsize = c->out_channels * (c->in_channels / c->groups) * c->kernel_height * c->kernel_width;
+            c->weight_data = otter::empty({c->out_channels, c->in_channels / c->groups, c->kernel_height, c->kernel_width}, otter::ScalarType::Byte);
+            std::memcpy(c->weight_data.raw_data(), w_oihw, wsize);
+            if (c->bias_term) c->bias_data = vec_tensor(bias, c->out_channels);
+            c->weight_data_int8_scales = vec_tensor(w_scales, c->out_channels);
+            c->bottom_blob_int8_scales = vec_tensor(in_scales, n_in_scales);
+            if (c->int8_scale_term > 100) c->top_blob_int8_scales = vec_tensor(out_scales, n_out_scales);
+            return c->create_pipeline(g_net->option);
+        }
+        g_err = std::string("no layer named ") + layer_name;
+        return -1;
+    } catch (const std::exception& e) { g_err = e.what(); return -2; } catch (...) { g_err = "unknown"; return -4; }
+}
+
+// one image (the reference's int8 path is batch-1): fp32 NCHW in, the named blob out as fp32 NCHW
+REF_API int ref_net_forward(const char* input_blob, const float* x, int c, int h, int w, const char* out_blob, float* out, int* out_shape) {
+    try {
+        if (!g_net) { g_err = "no net"; return -1; }
+        otter::Extractor ex = g_net->create_extractor();
+        otter::Tensor in = otter::from_blob((void*)x, {1, c, h, w}, otter::ScalarType::Float).clone();
+        ex.input(input_blob, in);
+        otter::Tensor feat;
+        int rc = ex.extract(out_blob, feat, 0);
+        if (rc != 0) { g_err = "extract failed"; return rc; }
+        otter::Tensor t1 = feat.packing(1).contiguous();
+        for (int i = 0; i < 4; ++i) out_shape[i] = i < t1.dim() ? (int)t1.size(i) : 1;
+        if (out) std::memcpy(out, t1.raw_data(), (size_t)t1.numel() * 4);
+        return 0;
+    } catch (const std::exception& e) { g_err = e.what(); return -2; } catch (const char* s) { g_err = s; return -3; } catch (...) { g_err = "unknown"; return -4; }
+}

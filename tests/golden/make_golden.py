@@ -14,6 +14,8 @@ requantize/dequantize functions applied to them.
 Also writes tests/golden/epilogue_adversarial.npz: accumulators and scales picked so that a fused
 multiply-add and a separate multiply+add disagree, and values on both rounding rules' tie points,
 with the reference's answers.
+Also writes tests/golden/net_shufflenet_wide_small.npz: blobs of a whole ShuffleNetV2-shaped graph (channel widths all
+multiples of 8) run through the reference's own Net (load_otter -> Extractor), one 64x64 image.
 """
 import ctypes as C
 import hashlib
@@ -23,6 +25,7 @@ from pathlib import Path
 import numpy as np
 
 sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+sys.path.insert(0, str(Path(__file__).resolve().parent.parent.parent))
 from cases import small_cases  # noqa: E402
 from support import (GOLDEN_DIR, _p, load_port, load_ref, rounding_for, run_port,  # noqa: E402
                      run_ref)
@@ -115,7 +118,15 @@ def main():
         assert ref.ref_quantize(_p(ties, C.c_float), 8, 4, 68, _p(one, C.c_float), 1, packed, _p(q, C.c_int8)) == 0
         adv[f"ties_q_{'packed' if packed else 'unpacked'}"] = q
     np.savez_compressed(GOLDEN_DIR / "epilogue_adversarial.npz", **adv)
-    for f in ("conv_int8_small.npz", "epilogue_adversarial.npz"):
+    # whole graph through the reference's own Net (widths all multiples of 8)
+    from graph_support import reference_net_forward, wide_shufflenet_case
+    L, params, x, blobs = wide_shufflenet_case()
+    got = reference_net_forward(L, params, x, blobs)
+    net = {"input_sha256": np.frombuffer(digest(x, *[params[k]["weight"] for k in sorted(params)], *[params[k]["in_scales"] for k in sorted(params)]).encode(), dtype=np.uint8)}
+    for b in blobs:
+        net[b] = got[b]
+    np.savez_compressed(GOLDEN_DIR / "net_shufflenet_wide_small.npz", **net)
+    for f in ("conv_int8_small.npz", "epilogue_adversarial.npz", "net_shufflenet_wide_small.npz"):
         print(f, (GOLDEN_DIR / f).stat().st_size, "bytes")
 
 

@@ -41,3 +41,45 @@ def build_net(layers, params, device=0):
     for name, p in params.items():
         net.set_conv_params(name, p["weight"], p["bias"], p["w_scales"], p["in_scales"], p["out_scales"])
     return net
+
+
+def wide_shufflenet_case():
+    """A ShuffleNetV2-shaped graph whose widths are all multiples of 8 (24 / 176 / 352 / 704, the 1.5x widths of the
+    reference's own shipped graph), so that the reference's packed Net can run it whole; small input, one image."""
+    L = graphs.shufflenetv2_layers(64, 64, stage_repeats=(2, 3, 2), stage_channels=(176, 352, 704), stem=24, last=512)
+    params = graphs.make_params(L, seed=0x0771E5 + 15)
+    x = np.random.default_rng(515).uniform(0, 1, size=(1, 3, 64, 64)).astype(np.float32)
+    graphs.calibrate(L, params, x, oracle_conv_for_calibration)
+    return L, params, x, ["pool1", "s2b1_shuf", "s3b2_shuf", "conv5"]
+
+
+def reference_net_forward(layers, params, x, blobs, packed=1):
+    """The same graph through the compiled reference's own Net (oracle/_ref): .otter text -> Net::load_otter -> parameters
+    replaced -> Extractor. One image."""
+    import ctypes as C
+    import tempfile
+    from support import _p, load_ref
+    ref = load_ref()
+    with tempfile.NamedTemporaryFile("w", suffix=".otter", delete=False) as f:
+        f.write(graphs.to_otter_text(layers))
+        path = f.name
+    try:
+        assert ref.ref_net_open(path.encode(), packed) == 0, ref.ref_last_error()
+        for name, p in params.items():
+            os_ = p["out_scales"]
+            rc = ref.ref_net_set_conv(name.encode(), _p(p["weight"], C.c_int8), _p(p["bias"], C.c_float), _p(p["w_scales"], C.c_float),
+                                      _p(p["in_scales"], C.c_float), p["in_scales"].size, _p(os_, C.c_float) if os_ is not None else None,
+                                      0 if os_ is None else os_.size)
+            assert rc == 0, (name, ref.ref_last_error())
+        out = {}
+        for b in blobs:
+            shape = np.zeros(4, np.int32)
+            assert ref.ref_net_forward(b"data", _p(x, C.c_float), x.shape[1], x.shape[2], x.shape[3], b.encode(), None, _p(shape, C.c_int)) == 0
+            y = np.empty(tuple(shape), np.float32)
+            assert ref.ref_net_forward(b"data", _p(x, C.c_float), x.shape[1], x.shape[2], x.shape[3], b.encode(), _p(y, C.c_float), _p(shape, C.c_int)) == 0
+            out[b] = y
+        return out
+    finally:
+        ref.ref_net_close()
+        import os
+        os.unlink(path)

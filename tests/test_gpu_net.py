@@ -84,3 +84,43 @@ def test_first_layer_and_maxpool_fused_kernel(h, w, cout, act):
     with pytest.raises(OtterB200Error):  # conv1 only exists inside the fused kernel
         net.forward("data", x, ["conv1"])
     net.close()
+
+
+def test_whole_graph_equals_the_reference_s_own_net(tmp_path):
+    """A whole graph, read from a .otter file, against blobs frozen from the reference's own Net (not only against the
+    layer-by-layer checker)."""
+    from graph_support import wide_shufflenet_case
+    from support import GOLDEN_DIR
+    from tensor_b200 import Net
+    gold = np.load(GOLDEN_DIR / "net_shufflenet_wide_small.npz")
+    L, params, x, blobs = wide_shufflenet_case()
+    path = tmp_path / "graph.otter"
+    path.write_text(graphs.to_otter_text(L))
+    net = Net(0)
+    net.load_otter(path)
+    for name, p in params.items():
+        net.set_conv_params(name, p["weight"], p["bias"], p["w_scales"], p["in_scales"], p["out_scales"])
+    got = net.forward("data", x, blobs)
+    for b, g in zip(blobs, got):
+        assert np.array_equal(bits(g), bits(gold[b])), b
+    net.close()
+
+
+def test_whole_graph_equals_the_reference_s_own_net(tmp_path):
+    """A whole graph, read from a .otter file, against blobs frozen from the reference's own Net (not only against the
+    layer-by-layer checker)."""
+    from graph_support import wide_shufflenet_case
+    from support import GOLDEN_DIR
+    from tensor_b200 import Net
+    gold = np.load(GOLDEN_DIR / "net_shufflenet_wide_small.npz")
+    L, params, x, blobs = wide_shufflenet_case()
+    path = tmp_path / "graph.otter"
+    path.write_text(graphs.to_otter_text(L))
+    net = Net(0)
+    net.load_otter(path)
+    for name, p in params.items():
+        net.set_conv_params(name, p["weight"], p["bias"], p["w_scales"], p["in_scales"], p["out_scales"])
+    got = net.forward("data", x, blobs)
+    for b, g in zip(blobs, got):
+        assert np.array_equal(bits(g), bits(gold[b])), b
+    net.close()

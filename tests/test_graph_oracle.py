@@ -81,3 +81,26 @@ def test_calibration_walk_gives_usable_scales():
     assert out.shape == (1, 1024, 1, 1) and np.isfinite(out).all() and (out != 0).mean() > 0.2
     # an int8 blob's producer and consumer agree on its scale
     assert params["s2b1_pw1"]["out_scales"][0] == params["s2b1_dw"]["in_scales"][0]
+
+
+NET_GOLD = np.load(__import__("support").GOLDEN_DIR / "net_shufflenet_wide_small.npz")
+
+
+def test_layer_by_layer_walk_equals_frozen_reference_net():
+    """The graph-level checker (C restatement per convolution + numpy glue) against blobs frozen from the reference's
+    own Net on a whole graph."""
+    from graph_support import oracle_conv, wide_shufflenet_case
+    L, params, x, blobs = wide_shufflenet_case()
+    got = graphs.walk(L, x, oracle_conv(params), want=blobs)
+    for b in blobs:
+        assert np.array_equal(got[b].view(np.int32), NET_GOLD[b].view(np.int32)), b
+
+
+@pytest.mark.skipif(not have_ref(), reason="oracle/_ref/libotter_ref.so not built")
+def test_reference_net_live_equals_walk():
+    from graph_support import oracle_conv, reference_net_forward, wide_shufflenet_case
+    L, params, x, blobs = wide_shufflenet_case()
+    ref = reference_net_forward(L, params, x, blobs)
+    got = graphs.walk(L, x, oracle_conv(params), want=blobs)
+    for b in blobs:
+        assert np.array_equal(got[b].view(np.int32), ref[b].view(np.int32)), b
