@@ -222,10 +222,7 @@ int ott_quantize_f32_nchw_to_s8_nhwc(ott_ctx* ctx, const float* x_dev, int n, in
     DeviceBlock sc;
     if (sc.alloc(ctx, sizeof(float) * n_scales) != cudaSuccess) return ctx->fail(OTT_ERR_ALLOC, "scale upload allocation failed");
     OTT_CUDA_CHECK(ctx, cudaMemcpyAsync(sc.p, scales_host, sizeof(float) * n_scales, cudaMemcpyHostToDevice, ctx->stream));
-    if (c > kGatherMaxChannels) return ctx->fail(OTT_ERR_UNSUPPORTED, "more than %d channels", kGatherMaxChannels);
-    PlaneGather g;
-    gather_identity(&g, x_dev, c, c, (long)h * w);
-    OTT_CUDA_CHECK(ctx, launch_quantize_nchw_to_nhwc(ctx->stream, g, out_dev, (const float*)sc.p, n_scales, n, c, h, w, rounding));
+    OTT_CUDA_CHECK(ctx, launch_quantize_dense(ctx->stream, x_dev, c, out_dev, (const float*)sc.p, n_scales, n, c, h, w, rounding));
     ctx->launches += 1;
     // the pageable scale array must stay readable until the copy has been issued; it has (pageable copies
     // are staged synchronously)
@@ -459,7 +456,8 @@ int conv_forward_impl(ott_ctx* ctx, const ott_conv* c, const void* in_dev, const
     ep.act_type = d.act_type; ep.act_param0 = d.act_param0; ep.rounding = d.rounding;
 
     uint32_t* status = status_word_dev ? status_word_dev : ctx->status_dev;
-    if (c->kind == OTT_KERNEL_DEPTHWISE && c->w_tiled_dev && depthwise_tiled_supports(s, out_dtype)) {
+    if (c->kind == OTT_KERNEL_DEPTHWISE && c->w_tiled_dev && depthwise_tiled_supports(s, out_dtype) &&
+        (in_dtype != OTT_F32_NCHW || d.cin <= kGatherMaxChannels)) {
         // one pass over HBM: quantize (when the input is fp32), depthwise and epilogue in the same kernel
         OTT_CUDA_CHECK(ctx, launch_depthwise_tiled(ctx->stream, s, in_dev, gather, in_dtype, c->w_tiled_dev, c->in_scales_dev, c->n_in_scales, ep,
                                                     out_dev, out_dtype));
@@ -479,13 +477,13 @@ int conv_forward_impl(ott_ctx* ctx, const ott_conv* c, const void* in_dev, const
             (void)cudaGetLastError();
             return ctx->fail(OTT_ERR_ALLOC, "scratch allocation for quantized activations failed");
         }
-        PlaneGather ident;
-        if (!gather) {
-            if (d.cin > kGatherMaxChannels) return ctx->fail(OTT_ERR_UNSUPPORTED, "fp32 input with more than %d channels", kGatherMaxChannels);
-            gather_identity(&ident, static_cast<const float*>(in_dev), d.cin, d.cin, (long)h * w);
+        if (gather) {
+            OTT_CUDA_CHECK(ctx, launch_quantize_nchw_to_nhwc(ctx->stream, *gather, (int8_t*)xq.p, c->in_scales_dev, c->n_in_scales, n, d.cin, h, w,
+                                                              d.rounding));
+        } else {
+            OTT_CUDA_CHECK(ctx, launch_quantize_dense(ctx->stream, static_cast<const float*>(in_dev), d.cin, (int8_t*)xq.p, c->in_scales_dev,
+                                                       c->n_in_scales, n, d.cin, h, w, d.rounding));
         }
-        OTT_CUDA_CHECK(ctx, launch_quantize_nchw_to_nhwc(ctx->stream, gather ? *gather : ident, (int8_t*)xq.p, c->in_scales_dev, c->n_in_scales, n,
-                                                          d.cin, h, w, d.rounding));
         ctx->launches += 1;
         x = (const int8_t*)xq.p;
     }

@@ -41,6 +41,10 @@ void gather_identity(PlaneGather* g, const float* x, int c, int c_total, long hw
 cudaError_t launch_quantize_nchw_to_nhwc(cudaStream_t stream, const PlaneGather& src, int8_t* out, const float* scales_dev,
                                          int n_scales, int n, int c, int h, int w, int rounding);
 
+// the same for a plain tensor (c of c_total channels per image, any channel count)
+cudaError_t launch_quantize_dense(cudaStream_t stream, const float* x, int c_total, int8_t* out, const float* scales_dev, int n_scales,
+                                  int n, int c, int h, int w, int rounding);
+
 // dense fp32 NCHW copy of the gathered planes (for consumers that want one contiguous tensor)
 cudaError_t launch_gather_planes(cudaStream_t stream, const PlaneGather& src, float* dst, int n, int c, long hw);
 

@@ -59,10 +59,7 @@ extern "C" int ott_conv_int8_forward_noalloc(ott_ctx* ctx, const ott_conv* conv,
     OTT_CUDA_CHECK(ctx, cudaSetDevice(ctx->device));
     // The quantize kernel writes every byte of the [n, h, w, channel stride] block, padding channels included,
     // so nothing left in the array by an earlier call can leak into this one and nothing needs clearing.
-    if (conv->d.cin > kGatherMaxChannels) return ctx->fail(OTT_ERR_UNSUPPORTED, "more than %d input channels", kGatherMaxChannels);
-    PlaneGather src;
-    gather_identity(&src, in_f32_nchw_dev, conv->d.cin, conv->d.cin, (long)h * w);
-    OTT_CUDA_CHECK(ctx, launch_quantize_nchw_to_nhwc(ctx->stream, src, reinterpret_cast<int8_t*>(scratch), conv->in_scales_dev,
+    OTT_CUDA_CHECK(ctx, launch_quantize_dense(ctx->stream, in_f32_nchw_dev, conv->d.cin, reinterpret_cast<int8_t*>(scratch), conv->in_scales_dev,
                                                       conv->n_in_scales, n, conv->d.cin, h, w, conv->d.rounding));
     ctx->launches += 1;
     // int8 input: this path of the ordinary forward launches the convolution kernel and takes no scratch

@@ -21,7 +21,7 @@ __device__ __forceinline__ int qt_row(int p) { return (p & 3) * 33 + (p >> 2); }
 
 __global__ void __launch_bounds__(QT_THREADS)
 quantize_nchw_to_nhwc_kernel(const __grid_constant__ PlaneGather G, int8_t* __restrict__ out, const float* __restrict__ scales,
-                             int n_scales, int c, int cpad, int hw, int tiles_p, int tiles_c, int rounding) {
+                             int n_scales, int c, int cpad, int hw, int tiles_p, int tiles_c, int rounding, int out_stride, int scale_base) {
     __shared__ uint32_t tile[4 * 33 * QT_PITCH];
     const long tile_id = blockIdx.x;
     const int tc = (int)(tile_id % tiles_c);
@@ -45,7 +45,7 @@ quantize_nchw_to_nhwc_kernel(const __grid_constant__ PlaneGather G, int8_t* __re
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const int cg = c0 + cword * 4 + i;
-                sc[i] = n_scales == 1 ? __ldg(scales) : __ldg(scales + cg);
+                sc[i] = n_scales == 1 ? __ldg(scales) : __ldg(scales + scale_base + cg);
                 v[i] = __ldg(reinterpret_cast<const float4*>(G.plane(cg, img, hw) + p));
             }
 #pragma unroll
@@ -56,7 +56,7 @@ quantize_nchw_to_nhwc_kernel(const __grid_constant__ PlaneGather G, int8_t* __re
                 const int cg = c0 + cword * 4 + i;
                 int q[4] = {0, 0, 0, 0};
                 if (cg < c) {
-                    const float s = n_scales == 1 ? __ldg(scales) : __ldg(scales + cg);
+                    const float s = n_scales == 1 ? __ldg(scales) : __ldg(scales + scale_base + cg);
                     const float* row = G.plane(cg, img, hw);
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
@@ -72,13 +72,13 @@ quantize_nchw_to_nhwc_kernel(const __grid_constant__ PlaneGather G, int8_t* __re
     }
     __syncthreads();
     // phase 2: 16-byte channel groups; consecutive threads -> consecutive groups of one pixel
-    int8_t* dst = out + (long)img * hw * cpad;
+    int8_t* dst = out + (long)img * hw * out_stride;
     for (int i = threadIdx.x; i < QT_P * (QT_C / 16); i += QT_THREADS) {
         const int pl = i >> 2, g = i & 3;
         const int pg = p0 + pl, cg = c0 + g * 16;
         if (pg < hw && cg < cpad) {
             const uint32_t* r = tile + qt_row(pl) * QT_PITCH + g * 4;
-            *reinterpret_cast<uint4*>(dst + (long)pg * cpad + cg) = make_uint4(r[0], r[1], r[2], r[3]);
+            *reinterpret_cast<uint4*>(dst + (long)pg * out_stride + cg) = make_uint4(r[0], r[1], r[2], r[3]);
         }
     }
 }
@@ -97,8 +97,32 @@ cudaError_t launch_quantize_nchw_to_nhwc(cudaStream_t stream, const PlaneGather&
     const int tiles_p = (hw + QT_P - 1) / QT_P, tiles_c = (cpad + QT_C - 1) / QT_C;
     const long blocks = (long)n * tiles_p * tiles_c;
     quantize_nchw_to_nhwc_kernel<<<(unsigned)blocks, QT_THREADS, 0, stream>>>(src, out, scales_dev, n_scales, c, cpad, hw, tiles_p, tiles_c,
-                                                                            rounding);
+                                                                            rounding, cpad, 0);
     return cudaGetLastError();
+}
+
+// A plain tensor of any channel count: the plane table holds kGatherMaxChannels entries, so wider tensors are
+// quantized in channel chunks, each launch writing its slice of the NHWC rows.
+cudaError_t launch_quantize_dense(cudaStream_t stream, const float* x, int c_total, int8_t* out, const float* scales_dev, int n_scales,
+                                  int n, int c, int h, int w, int rounding) {
+    const int hw = h * w, cpad = nhwc_channels(c);
+    if (n == 0 || hw == 0) return cudaSuccess;
+    const int tiles_p = (hw + QT_P - 1) / QT_P;
+    for (int base = 0; base < cpad; base += kGatherMaxChannels) {
+        const int chunk_pad = cpad - base < kGatherMaxChannels ? cpad - base : kGatherMaxChannels;  // channels written by this launch
+        const int chunk = c - base < chunk_pad ? (c - base > 0 ? c - base : 0) : chunk_pad;          // of which real ones
+        PlaneGather g;
+        g.base[0] = x;
+        g.img_stride[0] = (long long)c_total * hw;
+        for (int i = 0; i < chunk; ++i) g.ref[i] = (uint32_t)(base + i);
+        const int tiles_c = (chunk_pad + QT_C - 1) / QT_C;
+        const long blocks = (long)n * tiles_p * tiles_c;
+        quantize_nchw_to_nhwc_kernel<<<(unsigned)blocks, QT_THREADS, 0, stream>>>(g, out + base, scales_dev, n_scales, chunk, chunk_pad, hw,
+                                                                                tiles_p, tiles_c, rounding, cpad, base);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+    }
+    return cudaSuccess;
 }
 
 // dst[img][c][p] = plane(c, img)[p]

@@ -17,7 +17,8 @@ def ctx():
 
 
 @pytest.mark.parametrize("n,c,h,w,per_channel", [(2, 64, 14, 14, False), (1, 3, 33, 31, False), (3, 58, 5, 7, True),
-                                                  (1, 256, 56, 56, True), (2, 24, 1, 1, False), (1, 130, 9, 4, False)])
+                                                  (1, 256, 56, 56, True), (2, 24, 1, 1, False), (1, 130, 9, 4, False),
+                                                  (2, 704, 6, 6, True), (1, 1100, 3, 4, False)])
 @pytest.mark.parametrize("rounding", [ROUND_ADD_HALF_TRUNC, ROUND_HALF_AWAY])
 def test_quantize_matches_oracle(ctx, n, c, h, w, per_channel, rounding):
     from tensor_b200 import nhwc_channels
