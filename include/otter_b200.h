@@ -87,6 +87,11 @@ int ott_host_free(void* p);
 int ott_memcpy_h2d(ott_ctx* ctx, void* dst_dev, const void* src_host, size_t bytes); /* async on the stream */
 int ott_memcpy_d2h(ott_ctx* ctx, void* dst_host, const void* src_dev, size_t bytes); /* async on the stream */
 int ott_memset(ott_ctx* ctx, void* dst_dev, int value, size_t bytes);
+/* Copies that overlap kernels: direction 0 = host->device on a side stream (compute work enqueued AFTER this call waits for
+ * the copy), 1 = device->host on another side stream (the copy waits for compute work enqueued BEFORE this call). Host
+ * memory should be pinned (ott_host_alloc). ott_sync waits for these copies too. The device source of a device->host copy
+ * must stay allocated until ott_sync. */
+int ott_memcpy_overlapped(ott_ctx* ctx, int direction, void* dst, const void* src, size_t bytes);
 
 /* CUDA events on the context's stream, for timing the kernels where they are launched. */
 int ott_event_create(ott_ctx* ctx, ott_event** out);

@@ -44,6 +44,7 @@ SIGNATURES = {
     "ott_memcpy_h2d": (i32, [vp, vp, vp, sz]),
     "ott_memcpy_d2h": (i32, [vp, vp, vp, sz]),
     "ott_memset": (i32, [vp, vp, i32, sz]),
+    "ott_memcpy_overlapped": (i32, [vp, i32, vp, vp, sz]),
     "ott_event_create": (i32, [vp, C.POINTER(vp)]),
     "ott_event_record": (i32, [vp, vp]),
     "ott_event_elapsed_ms": (i32, [vp, vp, C.POINTER(C.c_float)]),

@@ -26,6 +26,8 @@ int upload(ott_ctx* ctx, const void* host, size_t bytes, void** dev) {
 int check_status_word(ott_ctx* ctx) {
     OTT_CUDA_CHECK(ctx, cudaMemcpyAsync(ctx->status_host, ctx->status_dev, sizeof(uint32_t), cudaMemcpyDeviceToHost, ctx->stream));
     OTT_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+    for (cudaStream_t a : ctx->aux_stream)
+        if (a) OTT_CUDA_CHECK(ctx, cudaStreamSynchronize(a));
     if (*ctx->status_host != 0) {
         const uint32_t w = *ctx->status_host;
         cudaMemsetAsync(ctx->status_dev, 0, sizeof(uint32_t), ctx->stream);
@@ -98,6 +100,8 @@ int ott_ctx_destroy(ott_ctx* ctx) {
     if (!ctx) return OTT_OK;
     cudaSetDevice(ctx->device);
     if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+    for (cudaStream_t a : ctx->aux_stream)
+        if (a) { cudaStreamSynchronize(a); cudaStreamDestroy(a); }
     delete ctx->alloc;
     if (ctx->status_dev) cudaFree(ctx->status_dev);
     if (ctx->status_host) cudaFreeHost(ctx->status_host);
@@ -170,6 +174,28 @@ int ott_memcpy_d2h(ott_ctx* ctx, void* dst, const void* src, size_t bytes) {
     if (!ctx) return OTT_ERR_INVALID;
     cudaSetDevice(ctx->device);
     OTT_CUDA_CHECK(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
+    return OTT_OK;
+}
+
+int ott_memcpy_overlapped(ott_ctx* ctx, int direction, void* dst, const void* src, size_t bytes) {
+    if (!ctx || !dst || !src || (direction != 0 && direction != 1)) return OTT_ERR_INVALID;
+    cudaSetDevice(ctx->device);
+    cudaStream_t& aux = ctx->aux_stream[direction];
+    if (!aux) OTT_CUDA_CHECK(ctx, cudaStreamCreateWithFlags(&aux, cudaStreamNonBlocking));
+    cudaEvent_t ev;
+    OTT_CUDA_CHECK(ctx, cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+    if (direction == 0) {
+        // host -> device: runs beside whatever the compute stream is doing; later compute work waits for it
+        OTT_CUDA_CHECK(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, aux));
+        OTT_CUDA_CHECK(ctx, cudaEventRecord(ev, aux));
+        OTT_CUDA_CHECK(ctx, cudaStreamWaitEvent(ctx->stream, ev, 0));
+    } else {
+        // device -> host: waits for the compute work enqueued so far, then runs beside later compute work
+        OTT_CUDA_CHECK(ctx, cudaEventRecord(ev, ctx->stream));
+        OTT_CUDA_CHECK(ctx, cudaStreamWaitEvent(aux, ev, 0));
+        OTT_CUDA_CHECK(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, aux));
+    }
+    cudaEventDestroy(ev);  // released by the runtime once the recorded work has completed
     return OTT_OK;
 }
 

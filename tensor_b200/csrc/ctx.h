@@ -104,6 +104,7 @@ struct ott_ctx {
     int device = 0;
     int sm_count = 0;
     cudaStream_t stream = nullptr;
+    cudaStream_t aux_stream[2] = {nullptr, nullptr};  // host->device and device->host copies that overlap the compute stream
     DeviceCachingAllocator* alloc = nullptr;
     std::string last_error;
     uint64_t launches = 0;

@@ -154,6 +154,41 @@ int ott_net_forward(ott_net* net, const char* input_blob, const void* in, int in
                     const char* const* out_blobs, void* const* out_host) {
     if (!net || !input_blob || !in || n_out < 1 || !out_blobs) return OTT_ERR_INVALID;
     net->error.clear();
+    // Host in, host out, large batch: run the batch in chunks so that the upload of chunk i+1 and the download of chunk i-1
+    // overlap the kernels of chunk i (images are independent, so chunking changes no value).
+    bool all_host_out = out_host != nullptr;
+    for (int i = 0; all_host_out && i < n_out; ++i) all_host_out = out_host[i] != nullptr;
+    const int chunk = 64;
+    if (!in_on_device && all_host_out && n >= 2 * chunk) {
+        ott_ctx* ctx = net->net.context();
+        const size_t img_bytes = (size_t)c * h * w * sizeof(float);
+        void* dev_in = nullptr;
+        if (ott_malloc(ctx, img_bytes * n, &dev_in) != OTT_OK) return fail(net, OTT_ERR_ALLOC, "device allocation for the input batch failed");
+        std::vector<otter::Tensor> keep;  // chunk outputs stay allocated until the final synchronisation
+        int rc = OTT_OK;
+        for (int b0 = 0; b0 < n && rc == OTT_OK; b0 += chunk) {
+            const int nb = n - b0 < chunk ? n - b0 : chunk;
+            char* dptr = static_cast<char*>(dev_in) + img_bytes * b0;
+            rc = ott_memcpy_overlapped(ctx, 0, dptr, static_cast<const char*>(in) + img_bytes * b0, img_bytes * nb);
+            if (rc != OTT_OK) break;
+            otter::Extractor ex = net->net.create_extractor();
+            ex.set_lightmode(n_out == 1);
+            ex.input(input_blob, otter::Tensor::wrap(dptr, img_bytes * nb, otter::Device::CUDA, nullptr, {nb, c, h, w}, otter::ScalarType::Float));
+            std::vector<otter::Tensor> dev((size_t)n_out);
+            for (int i = 0; i < n_out && rc == OTT_OK; ++i) rc = ex.extract(out_blobs[i], dev[(size_t)i], 1);
+            for (int i = 0; i < n_out && rc == OTT_OK; ++i) {
+                const otter::Tensor& t = dev[(size_t)i];
+                if (t.layout() != otter::Layout::NCHW) { rc = OTT_ERR_UNSUPPORTED; break; }  // int8 NHWC blob: take the plain path below
+                const size_t per_img = (size_t)(t.numel() / t.size(0)) * otter::elementSize(t.scalar_type());
+                rc = ott_memcpy_overlapped(ctx, 1, static_cast<char*>(out_host[i]) + per_img * b0, t.raw_data(), per_img * nb);
+                keep.push_back(t);
+            }
+        }
+        const int rc_sync = ott_sync(ctx);
+        keep.clear();
+        ott_free(ctx, dev_in);
+        if (rc != OTT_ERR_UNSUPPORTED) return rc != OTT_OK ? rc : rc_sync;
+    }
     otter::Extractor ex = net->net.create_extractor();
     otter::Tensor x;
     if (in_on_device)

@@ -124,3 +124,19 @@ def test_whole_graph_equals_the_reference_s_own_net(tmp_path):
     for b, g in zip(blobs, got):
         assert np.array_equal(bits(g), bits(gold[b])), b
     net.close()
+
+
+def test_chunked_host_forward_equals_plain_forward():
+    """Large host batches run in chunks with overlapped copies; every image must come out as in a plain forward."""
+    from graph_support import build_net, oracle_conv_for_calibration
+    L = graphs.shufflenetv2_layers(32, 32, stage_repeats=(2, 2, 2))
+    params = graphs.make_params(L)
+    x = np.random.default_rng(31).uniform(0, 1, size=(150, 3, 32, 32)).astype(np.float32)
+    graphs.calibrate(L, params, x[:1], oracle_conv_for_calibration)
+    net = build_net(L, params)
+    whole = net.forward("data", x, ["conv5"])[0]              # 150 >= 128: chunks of 64, 64, 22
+    parts = [net.forward("data", x[i:i + 50], ["conv5"])[0] for i in range(0, 150, 50)]  # 50 < 128: plain path
+    assert np.array_equal(bits(whole), bits(np.concatenate(parts)))
+    two = net.forward("data", x, ["s2b1_shuf", "conv5"])      # two outputs, one of them a plane table
+    assert np.array_equal(bits(two[1]), bits(whole))
+    net.close()
