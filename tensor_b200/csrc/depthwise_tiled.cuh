@@ -33,6 +33,7 @@ struct Tile {
     int ir, rp, ps;   // input tile: rows, row pitch and plane stride in 32-bit words (ps odd)
     int orp, ops;     // output staging planes: row pitch (= txo/4) and plane stride in words (ops odd)
     int tiles_y, tiles_x, cgroups;
+    int threads;      // CTA size: one warp per group of 4 output columns, at most 8 warps
 };
 
 template <int K, int S>
@@ -135,7 +136,7 @@ depthwise_tiled_kernel(const void* __restrict__ xin, const __grid_constant__ Pla
         const bool vec_ok = (s.w % 4 == 0) && ep.rounding == ROUND_ADD_HALF_TRUNC;
         const int per_plane = T.ir * T.rp;
         const float inv_rp = 1.0f / (float)T.rp;
-        for (int cl = warp; cl < CG; cl += THREADS / 32) {
+        for (int cl = warp; cl < CG; cl += (int)blockDim.x / 32) {
             const int c = c0 + cl;
             uint32_t* dst = tin + cl * T.ps;
             if (c >= s.cin) {
@@ -187,7 +188,7 @@ depthwise_tiled_kernel(const void* __restrict__ xin, const __grid_constant__ Pla
     } else {
         const int8_t* x = static_cast<const int8_t*>(xin) + (long)img * s.h * s.w * s.cin_pad;
         const int items = T.ir * T.rp * 2;  // (pixel quad, 16-channel half)
-        for (int i = threadIdx.x; i < items; i += THREADS) {
+        for (int i = threadIdx.x; i < items; i += (int)blockDim.x) {
             const int half = i & 1;
             const int xw = (i >> 1) % T.rp;
             const int r = (i >> 1) / T.rp;
@@ -233,7 +234,7 @@ depthwise_tiled_kernel(const void* __restrict__ xin, const __grid_constant__ Pla
     const int rows_out = min(T.ty, s.oh - oy0);
     const long oplane = (long)s.oh * s.ow;
 
-    for (int xq = warp; xq < T.txo / 4; xq += THREADS / 32) {
+    for (int xq = warp; xq < T.txo / 4; xq += (int)blockDim.x / 32) {
         const int ox = ox0 + xq * 4;
         if (ox >= s.ow) break;
         uint32_t win[K][4][KK];
@@ -259,7 +260,7 @@ depthwise_tiled_kernel(const void* __restrict__ xin, const __grid_constant__ Pla
         // planes -> channel-innermost: a thread takes 4 pixels x 16 channels (16 words), transposes, stores 4 x 16 B
         int8_t* o = reinterpret_cast<int8_t*>(out);
         const int items = rows_out * T.orp * 2;
-        for (int i = threadIdx.x; i < items; i += THREADS) {
+        for (int i = threadIdx.x; i < items; i += (int)blockDim.x) {
             const int half = i & 1;
             const int xq = (i >> 1) % T.orp, oy = (i >> 1) / T.orp;
             const int cc = c0 + half * 16;
@@ -289,7 +290,9 @@ inline Tile plan_tile(const ConvShape& s) {
     const int ow4 = (s.ow + 3) / 4 * 4;
     T.txo = S == 1 ? (ow4 < 64 ? ow4 : 64) : (ow4 < 32 ? ow4 : 32);
     const int ty_max = S == 1 ? (K == 3 ? 14 : 12) : (K == 3 ? 7 : 6);
-    T.ty = s.oh < ty_max ? s.oh : ty_max;
+    // bands of equal height (20 rows -> 10 + 10, not 14 + 6), so no CTA is mostly idle
+    const int bands = (s.oh + ty_max - 1) / ty_max;
+    T.ty = (s.oh + bands - 1) / bands;
     T.ir = (T.ty - 1) * S + K;
     T.rp = (T.txo / 4 - 1) * S + NW + 1 + 1;  // +1 realignment word, +1 because the tile origin is rounded down
     T.ps = T.ir * T.rp;
@@ -300,6 +303,8 @@ inline Tile plan_tile(const ConvShape& s) {
     T.tiles_y = (s.oh + T.ty - 1) / T.ty;
     T.tiles_x = (s.ow + T.txo - 1) / T.txo;
     T.cgroups = (s.cout_pad + CG - 1) / CG;
+    const int nxq = T.txo / 4;
+    T.threads = 32 * (nxq < 8 ? nxq : 8);
     return T;
 }
 
@@ -319,7 +324,7 @@ cudaError_t launch_t(cudaStream_t stream, const ConvShape& s, const void* x, con
     }
     const long blocks = (long)s.n * T.tiles_y * T.tiles_x * T.cgroups;
     if (blocks == 0) return cudaSuccess;
-    kernel<<<(unsigned)blocks, THREADS, smem, stream>>>(x, G, wq, in_scales, n_in_scales, ep, out, s, T);
+    kernel<<<(unsigned)blocks, T.threads, smem, stream>>>(x, G, wq, in_scales, n_in_scales, ep, out, s, T);
     return cudaGetLastError();
 }
 

@@ -21,26 +21,33 @@ __device__ __forceinline__ int qt_row(int p) { return (p & 3) * 33 + (p >> 2); }
 
 __global__ void __launch_bounds__(QT_THREADS)
 quantize_nchw_to_nhwc_kernel(const __grid_constant__ PlaneGather G, int8_t* __restrict__ out, const float* __restrict__ scales,
-                             int n_scales, int c, int cpad, int hw, int tiles_p, int tiles_c, int rounding, int out_stride, int scale_base) {
+                             int n_scales, int c, int cpad, int hw, int tiles_p, int tiles_c, int rounding, int out_stride, int scale_base, int flat,
+                             long total_px) {
     __shared__ uint32_t tile[4 * 33 * QT_PITCH];
     const long tile_id = blockIdx.x;
     const int tc = (int)(tile_id % tiles_c);
     const int tp = (int)((tile_id / tiles_c) % tiles_p);
-    const int img = (int)(tile_id / ((long)tiles_c * tiles_p));
-    const int c0 = tc * QT_C, p0 = tp * QT_P;
+    // flat: the pixel axis runs over all images (hw % 4 == 0, so a thread's 4 pixels never straddle two images) and no
+    // tile is wasted on the tail of an image; otherwise tiles are per image
+    const int img_tile = flat ? 0 : (int)(tile_id / ((long)tiles_c * tiles_p));
+    const int c0 = tc * QT_C;
+    const long p0 = (long)tp * QT_P;                     // first pixel of the tile (global when flat, in-image otherwise)
+    const long px_end = flat ? total_px : (long)hw;      // pixels beyond this do not exist
 
     // phase 1: a thread quantizes 4 consecutive pixels of 4 consecutive channels and packs, per pixel, the
     // 4 channels into one word. Lanes run along pixels (512 contiguous bytes per channel row per warp).
     const int pq = threadIdx.x & 31, cq = threadIdx.x >> 5;
     const bool vec_ok = (hw % 4 == 0);
-    const int p = p0 + pq * 4;
+    const long gp = p0 + pq * 4;
+    const int img = flat ? (int)(gp / hw) : img_tile;
+    const int p = flat ? (int)(gp - (long)img * hw) : (int)gp;
 #pragma unroll
     for (int pass = 0; pass < QT_C / 32; ++pass) {
         const int cword = cq + 8 * pass;
         uint32_t cw[4];  // channel i: its 4 pixels packed
         float4 v[4];
         float sc[4];
-        const bool fast = vec_ok && p + 3 < hw && c0 + cword * 4 + 3 < c && rounding == ROUND_ADD_HALF_TRUNC;
+        const bool fast = vec_ok && gp + 3 < px_end && c0 + cword * 4 + 3 < c && rounding == ROUND_ADD_HALF_TRUNC;
         if (fast) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -60,7 +67,7 @@ quantize_nchw_to_nhwc_kernel(const __grid_constant__ PlaneGather G, int8_t* __re
                     const float* row = G.plane(cg, img, hw);
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
-                        if (p + j < hw) q[j] = quantize1(__ldg(row + p + j), s, rounding);
+                        if (gp + j < px_end) q[j] = quantize1(__ldg(row + p + j), s, rounding);
                 }
                 cw[i] = pack4(q[0], q[1], q[2], q[3]);
             }
@@ -72,13 +79,14 @@ quantize_nchw_to_nhwc_kernel(const __grid_constant__ PlaneGather G, int8_t* __re
     }
     __syncthreads();
     // phase 2: 16-byte channel groups; consecutive threads -> consecutive groups of one pixel
-    int8_t* dst = out + (long)img * hw * out_stride;
+    int8_t* dst = out + (long)img_tile * hw * out_stride;
     for (int i = threadIdx.x; i < QT_P * (QT_C / 16); i += QT_THREADS) {
         const int pl = i >> 2, g = i & 3;
-        const int pg = p0 + pl, cg = c0 + g * 16;
-        if (pg < hw && cg < cpad) {
+        const long pg = p0 + pl;
+        const int cg = c0 + g * 16;
+        if (pg < px_end && cg < cpad) {
             const uint32_t* r = tile + qt_row(pl) * QT_PITCH + g * 4;
-            *reinterpret_cast<uint4*>(dst + (long)pg * out_stride + cg) = make_uint4(r[0], r[1], r[2], r[3]);
+            *reinterpret_cast<uint4*>(dst + pg * out_stride + cg) = make_uint4(r[0], r[1], r[2], r[3]);
         }
     }
 }
@@ -94,10 +102,12 @@ cudaError_t launch_quantize_nchw_to_nhwc(cudaStream_t stream, const PlaneGather&
     const int hw = h * w, cpad = nhwc_channels(c);
     if (n == 0 || hw == 0) return cudaSuccess;
     if (c > kGatherMaxChannels) return cudaErrorInvalidValue;
-    const int tiles_p = (hw + QT_P - 1) / QT_P, tiles_c = (cpad + QT_C - 1) / QT_C;
-    const long blocks = (long)n * tiles_p * tiles_c;
+    const int flat = hw % 4 == 0 ? 1 : 0;
+    const long total_px = (long)n * hw;
+    const int tiles_p = flat ? (int)((total_px + QT_P - 1) / QT_P) : (hw + QT_P - 1) / QT_P, tiles_c = (cpad + QT_C - 1) / QT_C;
+    const long blocks = (long)(flat ? 1 : n) * tiles_p * tiles_c;
     quantize_nchw_to_nhwc_kernel<<<(unsigned)blocks, QT_THREADS, 0, stream>>>(src, out, scales_dev, n_scales, c, cpad, hw, tiles_p, tiles_c,
-                                                                            rounding, cpad, 0);
+                                                                            rounding, cpad, 0, flat, total_px);
     return cudaGetLastError();
 }
 
@@ -107,7 +117,9 @@ cudaError_t launch_quantize_dense(cudaStream_t stream, const float* x, int c_tot
                                   int n, int c, int h, int w, int rounding) {
     const int hw = h * w, cpad = nhwc_channels(c);
     if (n == 0 || hw == 0) return cudaSuccess;
-    const int tiles_p = (hw + QT_P - 1) / QT_P;
+    const int flat = hw % 4 == 0 ? 1 : 0;
+    const long total_px = (long)n * hw;
+    const int tiles_p = flat ? (int)((total_px + QT_P - 1) / QT_P) : (hw + QT_P - 1) / QT_P;
     for (int base = 0; base < cpad; base += kGatherMaxChannels) {
         const int chunk_pad = cpad - base < kGatherMaxChannels ? cpad - base : kGatherMaxChannels;  // channels written by this launch
         const int chunk = c - base < chunk_pad ? (c - base > 0 ? c - base : 0) : chunk_pad;          // of which real ones
@@ -116,9 +128,9 @@ cudaError_t launch_quantize_dense(cudaStream_t stream, const float* x, int c_tot
         g.img_stride[0] = (long long)c_total * hw;
         for (int i = 0; i < chunk; ++i) g.ref[i] = (uint32_t)(base + i);
         const int tiles_c = (chunk_pad + QT_C - 1) / QT_C;
-        const long blocks = (long)n * tiles_p * tiles_c;
+        const long blocks = (long)(flat ? 1 : n) * tiles_p * tiles_c;
         quantize_nchw_to_nhwc_kernel<<<(unsigned)blocks, QT_THREADS, 0, stream>>>(g, out + base, scales_dev, n_scales, chunk, chunk_pad, hw,
-                                                                                tiles_p, tiles_c, rounding, cpad, base);
+                                                                                tiles_p, tiles_c, rounding, cpad, base, flat, total_px);
         cudaError_t e = cudaGetLastError();
         if (e != cudaSuccess) return e;
     }
