@@ -23,6 +23,13 @@ int ott_net_destroy(ott_net* net);
 const char* ott_net_last_error(const ott_net* net);
 ott_ctx* ott_net_context(ott_net* net); /* valid after ott_net_compile */
 
+/* The public fields of Net::option (Tensor/NetOption.hpp:16-24), to be set before ott_net_compile. Keys: "lightmode",
+ * "use_packing_layout", "int8_rounding" (OTT_ROUND_*), and the two switches this library adds, both on by default:
+ * "fuse_first_layer_pool" (first convolution + 3x3 stride-2 max-pool as one kernel) and "int8_handover" (a convolution
+ * whose fp32 result is read only by another quantized convolution writes that layer's int8 input directly). Both
+ * leave every extracted blob bit-identical. Unknown key: OTT_ERR_INVALID. */
+int ott_net_set_option(ott_net* net, const char* key, int value);
+
 /* Net::addLayer (Tensor/Net.cpp:40-80). `options` is one LayerOption as "key=value;key=value;...", with the
  * keys of the .otter format (type, name, input, output, and the layer's own parameters: out_channels, kernel_h,
  * stride, int8_scale_term, activation, groups, axis, start, end, ...). */

@@ -72,6 +72,7 @@ SIGNATURES = {
     "ott_net_destroy": (i32, [vp]),
     "ott_net_last_error": (C.c_char_p, [vp]),
     "ott_net_context": (vp, [vp]),
+    "ott_net_set_option": (i32, [vp, C.c_char_p, i32]),
     "ott_net_add_layer": (i32, [vp, C.c_char_p]),
     "ott_net_compile": (i32, [vp]),
     "ott_net_load_otter": (i32, [vp, C.c_char_p]),
@@ -281,6 +282,10 @@ class Net:
     def check(self, rc: int):
         if rc != 0:
             raise OtterB200Error(rc, self.lib.ott_net_last_error(self.h).decode(errors="replace"))
+
+    def set_option(self, key: str, value: int):
+        """A field of Net::option (lightmode, int8_rounding, fuse_first_layer_pool, int8_handover, ...); before compile()."""
+        self.check(self.lib.ott_net_set_option(self.h, key.encode(), int(value)))
 
     def add_layer(self, **options):
         """options as in the .otter format, e.g. type="Convolution", name="conv1", input="data", out_channels=24, ..."""

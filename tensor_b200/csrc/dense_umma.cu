@@ -31,8 +31,8 @@ namespace ottk {
 
 namespace {
 
-constexpr int kEpiWarps = 8;
-constexpr int kThreads = 64 + 32 * kEpiWarps;
+constexpr int kMaxEpiWarps = 8;                     // 2 per TMEM lane quarter
+constexpr int kMaxThreads = 64 + 32 * kMaxEpiWarps;  // UmmaPlan::epi_warps is 4 or 8
 constexpr int kTileM = 128;
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per wait
 
@@ -166,8 +166,10 @@ __host__ __device__ inline SmemLayout smem_layout(const UmmaPlan& p) {
     return L;
 }
 
-template <int OUT, int ACT, bool BIAS, int ROUND>
-__global__ void __launch_bounds__(kThreads, 1)
+// MULTI: compiled for three resident CTAs per SM (64 registers per thread), which small layers need to hide latency; the
+// one-CTA-per-SM plans of large layers use the build without that register limit.
+template <int OUT, int ACT, bool BIAS, int ROUND, bool MULTI>
+__global__ void __launch_bounds__(kMaxThreads, MULTI ? 3 : 1)
 dense_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const UmmaPlan P,
                   const ConvShape s, const EpilogueParams ep, void* __restrict__ out, uint32_t* __restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
@@ -193,7 +195,7 @@ dense_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         mbar_init(bar_b, 1);
         for (int i = 0; i < 2; ++i) {
             mbar_init(bar_tfull + 8u * i, 1);
-            mbar_init(bar_tempty + 8u * i, kEpiWarps);  // one arrival per epilogue warp
+            mbar_init(bar_tempty + 8u * i, (uint32_t)P.epi_warps);  // one arrival per epilogue warp
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -201,7 +203,7 @@ dense_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     }
     {
         float* sp = reinterpret_cast<float*>(base_ptr + L.params);
-        for (int i = threadIdx.x; i < P.bn; i += kThreads) {
+        for (int i = threadIdx.x; i < P.bn; i += (int)blockDim.x) {
             const int c = n_tile * P.bn + i;
             const bool in = c < s.cout_pad;
             sp[i] = in ? ep.scale_in[c] : 0.f;
@@ -281,7 +283,8 @@ dense_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     } else {
         // ---- epilogue warps ----
         const int q = warp & 3;            // TMEM lane quarter this warp may read
-        const int half = (warp - 2) >> 2;  // which of the two warps of that quarter
+        const int sub = (warp - 2) >> 2;   // which of the epi_warps/4 warps sharing that quarter
+        const int col_step = 16 * (P.epi_warps / 4);
         const int row = q * 32 + lane;
         const long plane = (long)s.oh * s.ow;
         const long total_pix = (long)s.n * plane;
@@ -317,7 +320,7 @@ dense_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 const long img = pix / plane, inimg = pix - img * plane;
                 out_f32 = reinterpret_cast<float*>(out) + (img * s.cout + n_tile * P.bn) * plane + inimg;
             }
-            for (int col0 = half * 16; col0 < P.bn; col0 += 32) {
+            for (int col0 = sub * 16; col0 < P.bn; col0 += col_step) {
                 int v[16];
                 __syncwarp();  // tcgen05.ld is warp-collective
                 tmem_ld16(taddr + (uint32_t)col0, v);
@@ -405,19 +408,36 @@ CUtensorMapSwizzle swizzle_for(int bkc) {
     return bkc == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (bkc == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
 }
 
-template <int OUT, int ACT, bool BIAS, int ROUND>
-const char* launch_variant(cudaStream_t stream, int grid, const CUtensorMap& tmA, const CUtensorMap& tmB, const UmmaPlan& p,
+template <int OUT, int ACT, bool BIAS, int ROUND, bool MULTI>
+const char* launch_variant(cudaStream_t stream, int sm_count, const CUtensorMap& tmA, const CUtensorMap& tmB, const UmmaPlan& p,
                            const ConvShape& s, const EpilogueParams& ep, void* out, uint32_t* status) {
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    auto kernel = dense_umma_kernel<OUT, ACT, BIAS, ROUND>;
+    auto kernel = dense_umma_kernel<OUT, ACT, BIAS, ROUND, MULTI>;
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
             return "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed";
         attr_set[dev] = true;
     }
-    kernel<<<grid, kThreads, p.smem_bytes, stream>>>(tmA, tmB, p, s, ep, out, status);
+    // Tiles are dealt statically to the CTAs of the grid, so a grid larger than what is resident at once runs in waves.
+    // The plan bounds residency by shared memory and TMEM; registers and threads are bounded here.
+    const int threads = 64 + 32 * p.epi_warps;
+    static int regs_per_thread[64] = {};
+    if (dev >= 0 && dev < 64 && regs_per_thread[dev] == 0) {
+        cudaFuncAttributes fa{};
+        regs_per_thread[dev] = cudaFuncGetAttributes(&fa, kernel) == cudaSuccess && fa.numRegs > 0 ? fa.numRegs : 128;
+    }
+    const int regs_per_warp = (((dev >= 0 && dev < 64) ? regs_per_thread[dev] : 128) * 32 + 255) / 256 * 256;
+    int resident = 65536 / (regs_per_warp * (threads / 32));
+    if (resident > 2048 / threads) resident = 2048 / threads;
+    if (resident < 1) resident = 1;
+    const int per_sm = resident < p.ctas_per_sm ? resident : p.ctas_per_sm;
+    int per_n = sm_count * per_sm / p.n_tiles;
+    if (per_n < 1) per_n = 1;
+    if (per_n > p.m_tiles) per_n = p.m_tiles;
+    const int grid = per_n * p.n_tiles;
+    kernel<<<grid, threads, p.smem_bytes, stream>>>(tmA, tmB, p, s, ep, out, status);
     return nullptr;
 }
 
@@ -467,6 +487,8 @@ bool umma_plan_layer(int cin, int cout, int kh, int kw, int sh, int sw, int dh, 
     // CTAs per SM: TMEM has 512 columns per SM and the hardware scheduler does not account for them, so the shared-memory
     // request is padded until no more CTAs fit an SM than TMEM can serve (a CTA that cannot get its columns would wait
     // inside tcgen05.alloc for a neighbour to finish).
+    // wide tiles run alone on their SM: give them 16 epilogue warps so the per-element epilogue keeps up with the MMAs
+    p.epi_warps = 8;
     int by_tmem = 512 / p.tmem_cols;
     int by_smem = smem_budget / p.smem_bytes;
     p.ctas_per_sm = by_tmem < by_smem ? by_tmem : by_smem;
@@ -543,14 +565,11 @@ const char* launch_dense_umma(cudaStream_t stream, int sm_count, const UmmaPlan&
     }
     if (r != CUDA_SUCCESS) return "cuTensorMapEncodeTiled(activations) failed";
 
-    int per_n = sm_count * p.ctas_per_sm / p.n_tiles;
-    if (per_n < 1) per_n = 1;
-    if (per_n > p.m_tiles) per_n = p.m_tiles;
-    const int grid = per_n * p.n_tiles;
     const CUtensorMap& tmB = *reinterpret_cast<const CUtensorMap*>(weight_map);
     const char* err = nullptr;
-#define OTT_UMMA_LAUNCH(OUT, ACT, BIAS, ROUND) \
-    err = launch_variant<OUT, ACT, BIAS, ROUND>(stream, grid, tmA, tmB, p, s, ep, out, status)
+#define OTT_UMMA_LAUNCH(OUT, ACT, BIAS, ROUND)                                                                       \
+    err = p.ctas_per_sm > 1 ? launch_variant<OUT, ACT, BIAS, ROUND, true>(stream, sm_count, tmA, tmB, p, s, ep, out, status) \
+                            : launch_variant<OUT, ACT, BIAS, ROUND, false>(stream, sm_count, tmA, tmB, p, s, ep, out, status)
 #define OTT_UMMA_ACT(OUT, BIAS, ROUND)                                   \
     switch (ep.act_type) {                                               \
         case ACT_RELU: OTT_UMMA_LAUNCH(OUT, ACT_RELU, BIAS, ROUND); break;   \

@@ -16,6 +16,7 @@ struct UmmaPlan {
     int acc_stride;  // column offset of the second accumulator
     uint32_t idesc;  // tcgen05 instruction descriptor
     int smem_bytes;  // dynamic shared memory of the launch
+    int epi_warps;   // epilogue warps per CTA: 8 or 16
     int ctas_per_sm; // resident CTAs per SM the launch is sized for (limited by TMEM columns and shared memory)
     // per call
     int flat;                          // 1x1: activations viewed as one [pixels, channels] matrix

@@ -17,9 +17,7 @@ ConvolutionLayer::ConvolutionLayer() {
     accepts_tables = true;  // the planes of a Concat / Crop / ChannelShuffle result are read where they lie
 }
 
-ConvolutionLayer::~ConvolutionLayer() {
-    if (gpu_conv_) ott_conv_int8_destroy(gpu_ctx_, gpu_conv_);
-}
+ConvolutionLayer::~ConvolutionLayer() { release_gpu(); }
 
 // Tensor/ConvolutionLayer.cpp:58-156
 int ConvolutionLayer::parse_param(LayerOption& option, ParamDict& pd) {
@@ -145,18 +143,8 @@ int ConvolutionLayer::create_pipeline(const NetOption& opt) {
     if (!int8_scale_term) return -1;  // the fp32 layer is not part of this build
     if (!opt.gpu) return -1;
     if (!weight_data.defined() || !weight_data_int8_scales.defined() || !bottom_blob_int8_scales.defined()) return -1;
-    if (gpu_conv_) {
-        ott_conv_int8_destroy(gpu_ctx_, gpu_conv_);
-        gpu_conv_ = nullptr;
-    }
+    release_gpu();
     gpu_ctx_ = opt.gpu;
-    ott_conv_desc d{};
-    d.cin = in_channels; d.cout = out_channels; d.kh = kernel_height; d.kw = kernel_width;
-    d.sh = stride_height; d.sw = stride_width; d.ph = padding_height; d.pw = padding_width;
-    d.dh = dilation_height; d.dw = dilation_width; d.groups = groups; d.bias_term = bias_term;
-    d.int8_scale_term = int8_scale_term; d.act_type = activation_type;
-    d.act_param0 = activation_params.defined() ? activation_params.data_ptr<float>()[0] : (activation_type == 2 ? 0.1f : 0.f);
-    d.rounding = opt.int8_rounding;
     // scale_in_data is kept as a public field like the reference's (ConvolutionLayer.cpp:667-679); the library
     // computes the same values from the same inputs for its own use
     scale_in_data = empty({out_channels}, ScalarType::Float);
@@ -166,10 +154,46 @@ int ConvolutionLayer::create_pipeline(const NetOption& opt) {
         scale_in_data.data_ptr<float>()[p] = ws == 0.f ? 0.f : 1.f / prod;
     }
     const bool requant = int8_scale_term > 100;
+    int rc = make_gpu_conv(opt, int8_scale_term, requant ? top_blob_int8_scales : Tensor(), &gpu_conv_);
+    if (rc != 0) return rc;
+    if (!requant && handover_scales.defined()) rc = make_gpu_conv(opt, 101, handover_scales, &gpu_conv_handover_);
+    return rc;
+}
+
+int ConvolutionLayer::make_gpu_conv(const NetOption& opt, int scale_term, const Tensor& top_scales, ott_conv** out) const {
+    ott_conv_desc d{};
+    d.cin = in_channels; d.cout = out_channels; d.kh = kernel_height; d.kw = kernel_width;
+    d.sh = stride_height; d.sw = stride_width; d.ph = padding_height; d.pw = padding_width;
+    d.dh = dilation_height; d.dw = dilation_width; d.groups = groups; d.bias_term = bias_term;
+    d.int8_scale_term = scale_term; d.act_type = activation_type;
+    d.act_param0 = activation_params.defined() ? activation_params.data_ptr<float>()[0] : (activation_type == 2 ? 0.1f : 0.f);
+    d.rounding = opt.int8_rounding;
+    const bool requant = scale_term > 100;
+    if (requant && !top_scales.defined()) return -1;
     return ott_conv_int8_create(opt.gpu, &d, weight_data.data_ptr<int8_t>(), bias_term ? bias_data.data_ptr<float>() : nullptr,
                                 weight_data_int8_scales.data_ptr<float>(), bottom_blob_int8_scales.data_ptr<float>(),
-                                (int)bottom_blob_int8_scales.numel(), requant ? top_blob_int8_scales.data_ptr<float>() : nullptr,
-                                requant ? (int)top_blob_int8_scales.numel() : 0, &gpu_conv_);
+                                (int)bottom_blob_int8_scales.numel(), requant ? top_scales.data_ptr<float>() : nullptr,
+                                requant ? (int)top_scales.numel() : 0, out);
+}
+
+void ConvolutionLayer::release_gpu() {
+    if (gpu_conv_) ott_conv_int8_destroy(gpu_ctx_, gpu_conv_);
+    if (gpu_conv_handover_) ott_conv_int8_destroy(gpu_ctx_, gpu_conv_handover_);
+    gpu_conv_ = gpu_conv_handover_ = nullptr;
+}
+
+// The consumer quantizes its fp32 input with float2int8(v * scale) (Tensor/QuantizeX86.cpp:23-71, called from
+// ConvolutionLayer.cpp:763-779); the requantizing epilogue ends with float2int8(v * scale_out) on the same fp32 v
+// (Tensor/QuantizeX86.cpp:1723-1870). With scale_out = the consumer's input scale the two give the same bytes, so the fp32
+// blob between the two layers need not exist.
+int ConvolutionLayer::set_handover(const NetOption& opt, const Tensor& consumer_input_scales) {
+    handover_scales = consumer_input_scales;
+    if (gpu_conv_handover_) {
+        ott_conv_int8_destroy(gpu_ctx_, gpu_conv_handover_);
+        gpu_conv_handover_ = nullptr;
+    }
+    if (!handover_scales.defined() || !gpu_conv_ || int8_scale_term > 100) return 0;
+    return make_gpu_conv(opt, 101, handover_scales, &gpu_conv_handover_);
 }
 
 bool ConvolutionLayer::can_fuse_maxpool() const {
@@ -185,7 +209,10 @@ int ConvolutionLayer::forward(const Tensor& bottom_blob, Tensor& top_blob, const
     if (c != in_channels) return -1;
     int oh = 0, ow = 0;
     ott_conv_int8_out_shape(gpu_conv_, h, w, &oh, &ow);
-    const bool requant = int8_scale_term > 100;
+    // int8 hand-over: the only reader of the top blob is a quantized convolution, and nobody asked for the blob itself
+    const bool handover = gpu_conv_handover_ && opt.int8_handover && !tops.empty() && opt.blob_wanted != tops[0];
+    const bool requant = int8_scale_term > 100 || handover;
+    const ott_conv* conv = handover ? gpu_conv_handover_ : gpu_conv_;
     const int out_dtype = requant ? OTT_S8_NHWC : OTT_F32_NCHW;
     if (fused_maxpool && !bottom_blob.is_table() && bottom_blob.scalar_type() == ScalarType::Float) {
         top_blob = device_empty(opt, {n, out_channels, (oh - 1) / 2 + 1, (ow - 1) / 2 + 1}, ScalarType::Float, Layout::NCHW);
@@ -204,13 +231,13 @@ int ConvolutionLayer::forward(const Tensor& bottom_blob, Tensor& top_blob, const
                             requant ? Layout::NHWC16 : Layout::NCHW);
     if (!top_blob.defined()) return -100;
     if (src.is_table())
-        return ott_conv_int8_forward_gather(opt.gpu, gpu_conv_, bufs.data(), strides.data(), (int)bufs.size(), src.table_refs().data(), n, h, w,
+        return ott_conv_int8_forward_gather(opt.gpu, conv, bufs.data(), strides.data(), (int)bufs.size(), src.table_refs().data(), n, h, w,
                                             top_blob.raw_data(), out_dtype, nullptr);
     int in_dtype;
     if (src.scalar_type() == ScalarType::Float && src.layout() == Layout::NCHW) in_dtype = OTT_F32_NCHW;
     else if (src.scalar_type() == ScalarType::Byte && src.layout() == Layout::NHWC16) in_dtype = OTT_S8_NHWC;
     else return -1;
-    return ott_conv_int8_forward(opt.gpu, gpu_conv_, src.raw_data(), in_dtype, n, h, w, top_blob.raw_data(), out_dtype, nullptr);
+    return ott_conv_int8_forward(opt.gpu, conv, src.raw_data(), in_dtype, n, h, w, top_blob.raw_data(), out_dtype, nullptr);
 }
 
 // ---- Input (Tensor/InputLayer.cpp:19-71): declares the shape of a graph input; the blob is set by Extractor::input ----

@@ -48,6 +48,19 @@ const char* ott_net_last_error(const ott_net* net) {
 
 ott_ctx* ott_net_context(ott_net* net) { return net ? net->net.context() : nullptr; }
 
+int ott_net_set_option(ott_net* net, const char* key, int value) {
+    if (!net || !key) return OTT_ERR_INVALID;
+    otter::NetOption& o = net->net.option;
+    const std::string k = key;
+    if (k == "lightmode") o.lightmode = value != 0;
+    else if (k == "use_packing_layout") o.use_packing_layout = value != 0;
+    else if (k == "int8_rounding") o.int8_rounding = value;
+    else if (k == "fuse_first_layer_pool") o.fuse_first_layer_pool = value != 0;
+    else if (k == "int8_handover") o.int8_handover = value != 0;
+    else return fail(net, OTT_ERR_INVALID, "unknown Net option: " + k);
+    return OTT_OK;
+}
+
 int ott_net_add_layer(ott_net* net, const char* options) {
     if (!net || !options) return OTT_ERR_INVALID;
     otter::LayerOption opt;

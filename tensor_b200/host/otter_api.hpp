@@ -126,6 +126,11 @@ public:
     int device = 0;                   // NEW: CUDA device of the Net
     ott_ctx* gpu = nullptr;           // set by Net::compile; what every Layer::forward launches on
     bool fuse_first_layer_pool = true;  // run conv1 -> MaxPool(3x3, s2, p1) as one kernel when nothing else reads conv1
+    // a quantized convolution whose fp32 result is read by one other quantized convolution and nothing else writes that
+    // reader's int8 input itself (same bytes as dequantize -> store -> load -> quantize); a blob asked for through
+    // Extractor::extract is still delivered in fp32
+    bool int8_handover = true;
+    int blob_wanted = -1;  // set by Extractor::extract: the blob that must come out in the reference's own type
     int int8_rounding = OTT_ROUND_ADD_HALF_TRUNC;  // which reference build is mirrored (packed x86 default / aarch64)
     std::vector<float>* layer_ms = nullptr;  // when set: per-layer device time, indexed by layer (Extractor::benchmark_info)
 };
@@ -226,9 +231,17 @@ public:
     // 2 pool with the reference's packed zero-padding rule
     int fused_maxpool = 0;
     bool can_fuse_maxpool() const;
+    // set by Net::compile when the only reader of the fp32 top blob is another quantized convolution: that layer's
+    // bottom_blob_int8_scales. The layer then also owns a requantizing twin that writes the reader's int8 input directly.
+    Tensor handover_scales;
+    int set_handover(const NetOption& opt, const Tensor& consumer_input_scales);
+    bool hands_over_int8() const { return gpu_conv_handover_ != nullptr; }
 
 private:
+    int make_gpu_conv(const NetOption& opt, int scale_term, const Tensor& top_scales, ott_conv** out) const;
+    void release_gpu();
     ott_conv* gpu_conv_ = nullptr;
+    ott_conv* gpu_conv_handover_ = nullptr;
     ott_ctx* gpu_ctx_ = nullptr;
 };
 
@@ -271,6 +284,7 @@ public:
 
 private:
     void graph_construct();
+    int refresh_handover(int producer_layer);
     int forward_layer(int layer_index, std::vector<Tensor>& blob_tensors, const NetOption& opt) const;
     int do_forward_layer(const Layer* layer, std::vector<Tensor>& blob_tensors, const NetOption& opt) const;
 

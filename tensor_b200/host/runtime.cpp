@@ -400,6 +400,11 @@ int Net::compile(CompileMode mode) {
             blob_fused_away_[(size_t)conv->tops[0]] = 1;
         }
     }
+    if (mode == CompileMode::Initial)
+        for (size_t i = 0; i < layers_.size(); ++i) {
+            const int rc = refresh_handover((int)i);
+            if (rc != 0) { error_ = "create_pipeline (int8 hand-over) of " + layers_[i]->name + " failed: " + ott_last_error(option.gpu); return rc; }
+        }
     input_names_.clear();
     output_names_.clear();
     for (Layer* l : layers_)
@@ -409,9 +414,33 @@ int Net::compile(CompileMode mode) {
     return 0;
 }
 
+// Decides whether layer `producer_layer` hands its result to its reader in int8, and (re)builds its requantizing twin.
+// Holds when: both are quantized convolutions, the producer's own result is fp32, its top blob has this one reader (a blob
+// read twice goes through a Split layer and stays fp32), and the reader does not run as a fused first-layer kernel.
+int Net::refresh_handover(int producer_layer) {
+    auto* conv = dynamic_cast<ConvolutionLayer*>(layers_[(size_t)producer_layer]);
+    if (!conv || conv->tops.size() != 1) return 0;
+    Tensor scales;
+    const Blob& b = blobs_[(size_t)conv->tops[0]];
+    if (option.int8_handover && conv->int8_scale_term > 0 && conv->int8_scale_term < 100 && !conv->fused_maxpool && b.consumer >= 0) {
+        auto* reader = dynamic_cast<ConvolutionLayer*>(layers_[(size_t)b.consumer]);
+        if (reader && reader->int8_scale_term > 0 && !reader->fused_maxpool && reader->bottom_blob_int8_scales.defined()) {
+            const int64_t ns = reader->bottom_blob_int8_scales.numel();
+            if (ns == 1 || ns == conv->out_channels) scales = reader->bottom_blob_int8_scales;
+        }
+    }
+    if (!scales.defined() && !conv->handover_scales.defined()) return 0;
+    return conv->set_handover(option, scales);
+}
+
 int Net::recreate_pipeline(int layer_index) {
     if (layer_index < 0 || layer_index >= (int)layers_.size()) return -1;
-    const int rc = layers_[(size_t)layer_index]->create_pipeline(option);
+    Layer* layer = layers_[(size_t)layer_index];
+    int rc = layer->create_pipeline(option);
+    // the layer's input scales are the hand-over scales of the layer before it
+    if (rc == 0) rc = refresh_handover(layer_index);
+    for (int b : layer->bottoms)
+        if (rc == 0 && blobs_[(size_t)b].producer >= 0) rc = refresh_handover(blobs_[(size_t)b].producer);
     if (rc != 0) error_ = std::string("create_pipeline failed: ") + ott_last_error(option.gpu);
     return rc;
 }
@@ -559,8 +588,17 @@ int Extractor::extract(int blob_index, Tensor& feat, int type) {
         net_->error_ = "blob " + net_->blobs_[(size_t)blob_index].name + " only exists inside a fused kernel; set NetOption::fuse_first_layer_pool = false to extract it";
         return -1;
     }
+    {
+        // a blob that an earlier extract left in its int8 hand-over form is computed again in the reference's type
+        const int prod = net_->blobs_[(size_t)blob_index].producer;
+        const auto* conv = prod >= 0 ? dynamic_cast<const ConvolutionLayer*>(net_->layers_[(size_t)prod]) : nullptr;
+        const Tensor& have = blob_tensors_[(size_t)blob_index];
+        if (conv && conv->int8_scale_term < 100 && have.defined() && have.scalar_type() == ScalarType::Byte) blob_tensors_[(size_t)blob_index].reset();
+    }
     if (!blob_tensors_[(size_t)blob_index].defined()) {
+        option.blob_wanted = blob_index;
         const int ret = net_->forward_layer(net_->blobs_[(size_t)blob_index].producer, blob_tensors_, option);
+        option.blob_wanted = -1;
         if (ret != 0) return ret;
     }
     if (blob_tensors_[(size_t)blob_index].is_table()) {

@@ -32,9 +32,11 @@ def oracle_conv_for_calibration(name, g, p, a, as_float):
     return run_port(_case(name, g, p, a, term), 0, want_acc=False)["y"]
 
 
-def build_net(layers, params, device=0):
+def build_net(layers, params, device=0, options=None):
     from tensor_b200 import Net
     net = Net(device)
+    for key, value in (options or {}).items():
+        net.set_option(key, value)
     for l in layers:
         net.add_layer(**l)
     net.compile()

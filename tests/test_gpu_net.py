@@ -52,6 +52,41 @@ def test_shufflenetv2_small_input_bit_exact():
     net.close()
 
 
+def test_int8_handover_between_convolutions_changes_no_blob():
+    """pw1 -> dw -> pw2 chains hand their result over in int8 (no fp32 blob in between); every blob, the handed-over ones
+    included, must still come out as the reference's fp32 values, and equal to a Net with the hand-over switched off."""
+    from graph_support import build_net, oracle_conv, oracle_conv_for_calibration
+    L = graphs.shufflenetv2_layers(64, 64, batch=3)
+    for l in L:  # a graph in which every convolution dequantizes: all blobs are fp32 in the reference
+        if l["type"] == "Convolution" and int(l["int8_scale_term"]) > 100:
+            l["int8_scale_term"] = int(l["int8_scale_term"]) - 100
+    params = graphs.make_params(L, seed=77)
+    x = np.random.default_rng(13).uniform(0, 1, size=(3, 3, 64, 64)).astype(np.float32)
+    graphs.calibrate(L, params, x[:1], oracle_conv_for_calibration)
+    probes = ["s2b0_l_dw", "s2b0_r_pw1", "s2b0_r_dw", "s2b1_pw1", "s2b1_dw", "s2b1_pw2", "s3b0_shuf", "s4b0_l_dw", "conv5"]
+    want = graphs.walk(L, x, oracle_conv(params), want=probes)
+    on = build_net(L, params)
+    off = build_net(L, params, options={"int8_handover": 0})
+    for net in (on, off):
+        final = net.forward("data", x, ["conv5"])[0]
+        assert np.array_equal(bits(final), bits(want["conv5"]))
+        got = net.forward("data", x, probes)
+        for name, g in zip(probes, got):
+            assert g.dtype == np.float32 and g.shape == want[name].shape, name
+            assert np.array_equal(bits(g), bits(want[name])), f"blob {name} differs"
+    # the chain really runs in int8: fewer kernels per forward than with the switch off (no quantize pass before dw / pw2)
+    counts = []
+    for net in (on, off):
+        before = net.context().launch_count()
+        net.forward("data", x, ["conv5"])
+        counts.append(net.context().launch_count() - before)
+    assert counts[0] < counts[1], counts
+    with pytest.raises(Exception):
+        on.set_option("no_such_option", 1)
+    on.close()
+    off.close()
+
+
 def test_unknown_layer_type_is_an_error_not_an_exit():
     from tensor_b200 import Net, OtterB200Error
     net = Net(0)
