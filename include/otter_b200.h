@@ -183,6 +183,15 @@ int ott_copy_channels_f32(ott_ctx* ctx, const float* src, int src_channels, int 
 int ott_maxpool_f32_nchw(ott_ctx* ctx, const float* in, int n, int c, int h, int w, int kh, int kw, int sh, int sw, int ph,
                          int pw, int pad_with_zero, float* out);
 
+/* UpsampleLayer::forward, bilinear, align_corner = false (Tensor/UpsampleLayer.cpp:113-131 -> otter::Interpolate,
+ * Tensor/TensorInterpolation.cpp:1444-1472). scale_h / scale_w are the layer's scale factors (0: derive from the sizes).
+ * packed_rule = 1 reproduces what the reference computes on a packed blob (channels a multiple of 4 under
+ * use_packing_layout: ncnn-style coefficients and operand order, TensorInterpolation.cpp:16-46,161-273), 0 what it
+ * computes on a plain blob (Tensor/UpSampleKernel.cpp:74-140 with the coefficients of Tensor/UpSample.hpp:133-158). The two
+ * differ in the last bit of about a third of the outputs and in how the far border is weighted. */
+int ott_upsample_bilinear_f32_nchw(ott_ctx* ctx, const float* in, int n, int c, int h, int w, int oh, int ow, double scale_h,
+                                   double scale_w, int packed_rule, float* out);
+
 /* ShortCutLayer: out = a + b (Tensor/ShortCutLayer.cpp) */
 int ott_add_f32(ott_ctx* ctx, const float* a, const float* b, float* out, size_t count);
 

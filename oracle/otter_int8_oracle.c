@@ -185,3 +185,57 @@ int orc_conv_int8_forward(const orc_conv_desc* d, const int8_t* w_oihw, const fl
     free(xq);
     return 0;
 }
+
+/* ---- bilinear Upsample (fp32 glue between the convolutions of the detector graphs) ---- */
+typedef struct { int i0, i1; float w0, w1; } orc_tap;
+
+static orc_tap orc_axis_tap(int d, int in, int out, double user_scale, int packed_rule) {
+    orc_tap t;
+    if (packed_rule) { /* Tensor/TensorInterpolation.cpp:16-46 */
+        const double scale = (double)in / out;
+        float f = (float)((d + 0.5) * scale - 0.5);
+        int s = (int)floor(f);
+        f -= (float)s;
+        if (s < 0) { s = 0; f = 0.f; }
+        if (s >= in - 1) { s = in - 2; f = 1.f; }
+        t.i0 = s; t.i1 = s + 1; t.w0 = 1.f - f; t.w1 = f;
+        return t;
+    }
+    /* Tensor/UpSample.hpp:41-51,72-94,133-158 */
+    if (out == in) { t.i0 = t.i1 = d; t.w0 = 1.f; t.w1 = 0.f; return t; }
+    const float ratio = user_scale > 0. ? (float)(1.0 / user_scale) : (float)in / (float)out;
+    float real = (float)((double)ratio * (d + 0.5) - 0.5);
+    if (real < 0.f) real = 0.f;
+    t.i0 = (int)real;
+    t.i1 = t.i0 + (t.i0 < in - 1 ? 1 : 0);
+    t.w1 = real - (float)t.i0;
+    t.w0 = 1.f - t.w1;
+    return t;
+}
+
+void orc_upsample_bilinear(const float* x, int n, int c, int h, int w, int oh, int ow, double scale_h, double scale_w,
+                           int packed_rule, float* y) {
+    const long planes = (long)n * c;
+#pragma omp parallel for schedule(static)
+    for (long p = 0; p < planes; ++p) {
+        const float* xp = x + p * (long)h * w;
+        float* yp = y + p * (long)oh * ow;
+        for (int oy = 0; oy < oh; ++oy) {
+            const orc_tap ty = orc_axis_tap(oy, h, oh, scale_h, packed_rule);
+            for (int ox = 0; ox < ow; ++ox) {
+                const orc_tap tx = orc_axis_tap(ox, w, ow, scale_w, packed_rule);
+                const float a00 = xp[(long)ty.i0 * w + tx.i0], a01 = xp[(long)ty.i0 * w + tx.i1];
+                const float a10 = xp[(long)ty.i1 * w + tx.i0], a11 = xp[(long)ty.i1 * w + tx.i1];
+                float v;
+                if (packed_rule) {
+                    const float r0 = fmaf(a01, tx.w1, a00 * tx.w0), r1 = fmaf(a11, tx.w1, a10 * tx.w0);
+                    v = fmaf(r1, ty.w1, r0 * ty.w0);
+                } else {
+                    const float r0 = fmaf(a00, tx.w0, a01 * tx.w1), r1 = fmaf(a10, tx.w0, a11 * tx.w1);
+                    v = fmaf(r0, ty.w0, r1 * ty.w1);
+                }
+                yp[(long)oy * ow + ox] = v;
+            }
+        }
+    }
+}

@@ -73,6 +73,17 @@ int orc_conv_int8_forward(const orc_conv_desc* d, const int8_t* w_oihw, const fl
                           const float* x_f32, const int8_t* x_s8, int n, int h, int w, int rounding,
                           int8_t* xq_out, int32_t* acc_out, float* y_f32, int8_t* y_s8);
 
+/* UpsampleLayer::forward for upsample_mode = bilinear, align_corner = false (Tensor/UpsampleLayer.cpp:113-131), fp32 NCHW.
+ * packed_rule 1: the reference's resize of packed blobs (channels % 4 == 0 under use_packing_layout): coefficients
+ *   of linear_coeffs (Tensor/TensorInterpolation.cpp:16-46), rows = fma(S1, a1, S0 * a0), D = fma(rows1, b1, rows0 * b0)
+ *   (:199-207,:251-259).
+ * packed_rule 0: its resize of plain blobs: coefficients of compute_source_index_and_lambda (Tensor/UpSample.hpp:133-158,
+ *   scale from compute_scales_value :41-51), t0 * w0 + t1 * w1 per axis (Tensor/UpSampleKernel.cpp:125-139), which the
+ *   reference build (-Ofast -mfma) evaluates as fma(t0, w0, t1 * w1).
+ * scale_h / scale_w: the layer's scale factors (used by rule 0 only; <= 0: in / out). */
+void orc_upsample_bilinear(const float* x, int n, int c, int h, int w, int oh, int ow, double scale_h, double scale_w,
+                           int packed_rule, float* y);
+
 int orc_max_threads(void);
 void orc_set_threads(int n);
 

@@ -65,6 +65,7 @@ SIGNATURES = {
     "ott_launch_count": (C.c_uint64, [vp]),
     "ott_copy_channels_f32": (i32, [vp, vp, i32, i32, i32, vp, i32, i32, i32, i32, i32, i32]),
     "ott_maxpool_f32_nchw": (i32, [vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp]),
+    "ott_upsample_bilinear_f32_nchw": (i32, [vp, vp, i32, i32, i32, i32, i32, i32, C.c_double, C.c_double, i32, vp]),
     "ott_add_f32": (i32, [vp, vp, vp, vp, sz]),
     "ott_activation_f32": (i32, [vp, vp, sz, i32, C.c_float]),
     # include/otter_b200_net.h

@@ -3,7 +3,7 @@
 // element-wise add (ShortCut) and the stand-alone activations. All tensors are fp32 NCHW on the device.
 // Reference: Tensor/ConcatLayer.cpp:55-70, Tensor/CropLayer.cpp:67-75, Tensor/ChannelShuffleLayer.cpp:37-41,
 // Tensor/MaxPoolLayer.cpp:123-133 + Tensor/Pool.cpp:1166-1201, Tensor/ShortCutLayer.cpp, Tensor/ReluLayer.cpp,
-// Tensor/LReluLayer.cpp, Tensor/Relu6Layer.cpp.
+// Tensor/LReluLayer.cpp, Tensor/Relu6Layer.cpp, Tensor/UpsampleLayer.cpp:113-131.
 #include "ctx.h"
 
 namespace {
@@ -59,6 +59,67 @@ __global__ void activation_kernel(float* __restrict__ x, long n, int act, float 
     }
 }
 
+// One axis of the bilinear resize: the two source indices and their weights for output index d.
+// rule 1 (the reference's packed blobs, Tensor/TensorInterpolation.cpp:16-46): source position in double, floor, and a
+// border clamp that moves the pair inside the row with weights (1,0) / (0,1).
+// rule 0 (its plain blobs, Tensor/UpSample.hpp:53-94,133-158): scale and position in float, negative positions clamped to 0,
+// the second index clamped to the last element.
+struct AxisTap {
+    int i0, i1;
+    float w0, w1;
+};
+__device__ __forceinline__ AxisTap axis_tap(int d, int in, int out, double user_scale, int rule) {
+    AxisTap t;
+    if (rule == 1) {
+        const double scale = (double)in / out;
+        float f = (float)(((double)d + 0.5) * scale - 0.5);
+        int s = (int)floorf(f);
+        f -= (float)s;
+        if (s < 0) { s = 0; f = 0.f; }
+        if (s >= in - 1) { s = in - 2; f = 1.f; }
+        t.i0 = s; t.i1 = s + 1;
+        t.w0 = __fsub_rn(1.f, f); t.w1 = f;
+    } else {
+        if (out == in) { t.i0 = t.i1 = d; t.w0 = 1.f; t.w1 = 0.f; return t; }
+        const float ratio = user_scale > 0. ? (float)(1.0 / user_scale) : (float)in / (float)out;
+        float real = (float)((double)ratio * ((double)d + 0.5) - 0.5);
+        if (real < 0.f) real = 0.f;
+        t.i0 = (int)real;
+        t.i1 = t.i0 + (t.i0 < in - 1 ? 1 : 0);
+        t.w1 = __fsub_rn(real, (float)t.i0);
+        t.w0 = __fsub_rn(1.f, t.w1);
+    }
+    return t;
+}
+
+// Bilinear resize of fp32 NCHW planes, align_corners = false. Both rules resize along x first, then along y, with one
+// rounding per product and one per fused multiply-add, in the operand order of the reference build:
+//   rule 1: fma(S1, w1, S0 * w0)      (Tensor/TensorInterpolation.cpp:199-207,251-259)
+//   rule 0: fma(S0, w0, S1 * w1)      (Tensor/UpSampleKernel.cpp:125-139 as compiled with -Ofast -mfma)
+__global__ void upsample_bilinear_kernel(const float* __restrict__ x, float* __restrict__ y, int h, int w, int oh, int ow, double scale_h,
+                                         double scale_w, int rule, long total) {
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const int ox = (int)(i % ow);
+        const long r = i / ow;
+        const int oy = (int)(r % oh);
+        const float* xp = x + (r / oh) * (long)h * w;
+        const AxisTap tx = axis_tap(ox, w, ow, scale_w, rule), ty = axis_tap(oy, h, oh, scale_h, rule);
+        const float a00 = __ldg(xp + (long)ty.i0 * w + tx.i0), a01 = __ldg(xp + (long)ty.i0 * w + tx.i1);
+        const float a10 = __ldg(xp + (long)ty.i1 * w + tx.i0), a11 = __ldg(xp + (long)ty.i1 * w + tx.i1);
+        float v;
+        if (rule == 1) {
+            const float r0 = __fmaf_rn(a01, tx.w1, __fmul_rn(a00, tx.w0));
+            const float r1 = __fmaf_rn(a11, tx.w1, __fmul_rn(a10, tx.w0));
+            v = __fmaf_rn(r1, ty.w1, __fmul_rn(r0, ty.w0));
+        } else {
+            const float r0 = __fmaf_rn(a00, tx.w0, __fmul_rn(a01, tx.w1));
+            const float r1 = __fmaf_rn(a10, tx.w0, __fmul_rn(a11, tx.w1));
+            v = __fmaf_rn(r0, ty.w0, __fmul_rn(r1, ty.w1));
+        }
+        y[i] = v;
+    }
+}
+
 unsigned grid_for(const ott_ctx* ctx, long total, int block) {
     long g = (total + block - 1) / block;
     const long cap = (long)ctx->sm_count * 16;
@@ -101,6 +162,19 @@ int ott_maxpool_f32_nchw(ott_ctx* ctx, const float* in, int n, int c, int h, int
     if (total <= 0) return OTT_OK;
     cudaSetDevice(ctx->device);
     maxpool_kernel<<<(unsigned)((total + 255) / 256), 256, 0, ctx->stream>>>(in, out, c, h, w, oh, ow, kh, kw, sh, sw, ph, pw, pad_with_zero, total);
+    OTT_CUDA_CHECK(ctx, cudaGetLastError());
+    ctx->launches += 1;
+    return OTT_OK;
+}
+
+int ott_upsample_bilinear_f32_nchw(ott_ctx* ctx, const float* in, int n, int c, int h, int w, int oh, int ow, double scale_h, double scale_w,
+                                   int packed_rule, float* out) {
+    if (!ctx || !in || !out || n < 0 || c < 0 || h < 1 || w < 1 || oh < 1 || ow < 1) return OTT_ERR_INVALID;
+    if (packed_rule && (h < 2 || w < 2)) return ctx->fail(OTT_ERR_UNSUPPORTED, "bilinear resize of a packed blob needs at least 2 rows and 2 columns");
+    const long total = (long)n * c * oh * ow;
+    if (total == 0) return OTT_OK;
+    cudaSetDevice(ctx->device);
+    upsample_bilinear_kernel<<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(in, out, h, w, oh, ow, scale_h, scale_w, packed_rule ? 1 : 0, total);
     OTT_CUDA_CHECK(ctx, cudaGetLastError());
     ctx->launches += 1;
     return OTT_OK;

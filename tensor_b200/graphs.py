@@ -60,8 +60,65 @@ def shufflenetv2_layers(height=320, width=320, batch=1, stage_repeats=(4, 8, 4),
             L.append(dict(type="ChannelShuffle", name=f"{b}_shuf", input=f"{b}_cat", output=f"{b}_shuf", groups=2))
             prev = f"{b}_shuf"
         cin = cout
-    L.append(_conv("conv5", prev, last, 1, 1, 0, 2, act))
+    if last:
+        L.append(_conv("conv5", prev, last, 1, 1, 0, 2, act))
     return L
+
+
+def nanodet_plus_layers(height=320, width=320, batch=1, neck=96, classes=80, reg_max=7, stage_repeats=(4, 8, 4),
+                        stage_channels=(116, 232, 464), stem=24, act="LRelu"):
+    """A NanoDet-Plus-style int8 detector in the wiring of the reference's own graph
+    (benchmark/nanodet-plus-m-1.5x_416_int8_fused.otter, layers conv_56 ... conv_110) on the ShuffleNetV2-1.0x backbone:
+    three 1x1 reductions to `neck` channels; a Ghost-PAN neck (top-down with bilinear x2 Upsample + Concat, bottom-up with
+    depthwise 5x5 stride-2 + 1x1, each merge a Ghost block = two ghost modules [1x1 -> depthwise 3x3, Concat] plus a
+    depthwise 5x5 -> 1x1 shortcut, added by ShortCut); an extra stride-64 level; and per level a head of
+    2 x [depthwise 5x5 -> 1x1] and a 1x1 to classes + 4*(reg_max+1) channels. Outputs: head8, head16, head32, head64."""
+    L = shufflenetv2_layers(height, width, batch, stage_repeats, stage_channels, stem, last=0, act=act)
+    half = neck // 2
+    feats = [f"s{si + 2}b{rep - 1}_shuf" for si, rep in enumerate(stage_repeats)]
+    for tag, src in zip(("r8", "r16", "r32"), feats):
+        L.append(_conv(tag, src, neck, 1, 1, 0, 2, act))
+
+    def cat(name, a, b):
+        L.append(dict(type="Concat", name=name, input=f"{a}, {b}", output=name, axis=1))
+        return name
+
+    def ghost_block(tag, src):  # src has 2*neck channels; result has neck
+        L.append(_conv(f"{tag}_g1pw", src, half, 1, 1, 0, 2, act))
+        L.append(_conv(f"{tag}_g1dw", f"{tag}_g1pw", half, 3, 1, 1, 1, act, groups=half))
+        cat(f"{tag}_g1", f"{tag}_g1pw", f"{tag}_g1dw")
+        L.append(_conv(f"{tag}_g2pw", f"{tag}_g1", half, 1, 1, 0, 2))
+        L.append(_conv(f"{tag}_g2dw", f"{tag}_g2pw", half, 3, 1, 1, 1, "", groups=half))
+        cat(f"{tag}_g2", f"{tag}_g2pw", f"{tag}_g2dw")
+        L.append(_conv(f"{tag}_scdw", src, 2 * neck, 5, 1, 2, 101, "", groups=2 * neck))
+        L.append(_conv(f"{tag}_scpw", f"{tag}_scdw", neck, 1, 1, 0, 2))
+        L.append(dict(type="ShortCut", name=tag, input=f"{tag}_g2, {tag}_scpw", output=tag))
+        return tag
+
+    def up(name, src):
+        L.append(dict(type="Upsample", name=name, input=src, output=name, upsample_mode="bilinear", align_corner="false", stride="2.000000"))
+        return name
+
+    def down(tag, src):
+        L.append(_conv(f"{tag}_dw", src, neck, 5, 2, 2, 101, act, groups=neck))
+        L.append(_conv(tag, f"{tag}_dw", neck, 1, 1, 0, 2, act))
+        return tag
+
+    td16 = ghost_block("td16", cat("td16_in", up("up32", "r32"), "r16"))
+    td8 = ghost_block("td8", cat("td8_in", up("up16", td16), "r8"))
+    bu16 = ghost_block("bu16", cat("bu16_in", down("dn8", td8), td16))
+    bu32 = ghost_block("bu32", cat("bu32_in", down("dn16", bu16), "r32"))
+    L.append(dict(type="ShortCut", name="p64", input=f"{down('ex_a', 'r32')}, {down('ex_b', bu32)}", output="p64"))
+    for tag, src in zip(("head8", "head16", "head32", "head64"), (td8, bu16, bu32, "p64")):
+        L.append(_conv(f"{tag}_dw1", src, neck, 5, 1, 2, 101, act, groups=neck))
+        L.append(_conv(f"{tag}_pw1", f"{tag}_dw1", neck, 1, 1, 0, 102, act))
+        L.append(_conv(f"{tag}_dw2", f"{tag}_pw1", neck, 5, 1, 2, 101, act, groups=neck))
+        L.append(_conv(f"{tag}_pw2", f"{tag}_dw2", neck, 1, 1, 0, 102, act))
+        L.append(_conv(tag, f"{tag}_pw2", classes + 4 * (reg_max + 1), 1, 1, 0, 2))
+    return L
+
+
+NANODET_OUTPUTS = ("head8", "head16", "head32", "head64")
 
 
 def to_otter_text(layers, name="generated by tensor_b200.graphs") -> str:
@@ -126,6 +183,9 @@ def conv_input_hw(layers, height, width):
                 g = geo[l["name"]]
                 out[l["name"]] = (h, w)
                 macs += oh * ow * g["cout"] * (g["cin"] // g["groups"]) * k * k
+        elif l["type"] == "Upsample":
+            f = float(l.get("stride", 1.0))
+            hw[l["output"]] = (int(h * f), int(w * f))
         else:
             hw[l["output"]] = (h, w)
     return out, macs
@@ -162,9 +222,27 @@ def maxpool_nchw(x, k, s, p, pad_zero):
     return out
 
 
-def walk(layers, x, conv_fn, want=None, on_conv=None):
+def upsample_bilinear_approx(a, oh, ow, scale, packed_rule):
+    """Bilinear resize in float64, rounded once: good for picking calibration ranges, NOT bit-exact with the reference (the
+    checker's exact version is the C function orc_upsample_bilinear; tests pass it to `walk` as upsample_fn)."""
+    def taps(n_in, n_out):
+        d = np.arange(n_out, dtype=np.float64)
+        f = np.clip((d + 0.5) * (n_in / n_out) - 0.5, 0, n_in - 1)
+        i0 = np.floor(f).astype(np.int64)
+        i1 = np.minimum(i0 + 1, n_in - 1)
+        return i0, i1, f - i0
+    y0, y1, fy = taps(a.shape[2], oh)
+    x0, x1, fx = taps(a.shape[3], ow)
+    a = a.astype(np.float64)
+    rows = a[:, :, :, x0] * (1 - fx) + a[:, :, :, x1] * fx
+    return (rows[:, :, y0, :] * (1 - fy)[:, None] + rows[:, :, y1, :] * fy[:, None]).astype(np.float32)
+
+
+def walk(layers, x, conv_fn, want=None, on_conv=None, upsample_fn=None):
     """Run the graph on host arrays. conv_fn(name, geometry, input_array) -> output array (fp32 NCHW, or int8 NCHW for
-    int8_scale_term > 100). Returns {blob name: array} for the names in `want` (default: the last layer's output)."""
+    int8_scale_term > 100). upsample_fn(array, oh, ow, scale, packed_rule) -> array does the bilinear Upsample layers
+    (default: the float64 approximation above). Returns {blob name: array} for the names in `want` (default: the last
+    layer's output)."""
     geo = conv_geometry(layers)
     blobs = {}
     for l in layers:
@@ -193,6 +271,14 @@ def walk(layers, x, conv_fn, want=None, on_conv=None):
             blobs[out] = np.ascontiguousarray(a.reshape(n, g, c // g, h, w).transpose(0, 2, 1, 3, 4).reshape(n, c, h, w))
         elif t == "ShortCut":
             blobs[out] = blobs[ins[0]] + blobs[ins[1]]
+        elif t == "Upsample":
+            a = blobs[ins[0]]
+            if l.get("upsample_mode") != "bilinear" or str(l.get("align_corner", "false")) != "false":
+                raise ValueError("only bilinear Upsample with align_corner=false is handled")
+            f = float(l.get("stride", 1.0))
+            # the reference resizes packed blobs (C % 4 == 0) and plain blobs with different rounding
+            blobs[out] = (upsample_fn or upsample_bilinear_approx)(np.ascontiguousarray(a), int(a.shape[2] * f), int(a.shape[3] * f), f,
+                                                                   1 if a.shape[1] % 4 == 0 else 0)
         elif t in ("Relu", "LRelu", "Relu6"):
             a = blobs[ins[0]]
             blobs[out] = {"Relu": lambda v: np.maximum(v, 0), "Relu6": lambda v: np.clip(v, 0, 6),
@@ -203,7 +289,7 @@ def walk(layers, x, conv_fn, want=None, on_conv=None):
     return {k: blobs[k] for k in names}
 
 
-def calibrate(layers, params, x, conv_f32_fn):
+def calibrate(layers, params, x, conv_f32_fn, upsample_fn=None):
     """Fill in_scales / out_scales from one sample batch x (fp32 NCHW): 127 / max|blob| per tensor, walking the graph in
     order. conv_f32_fn(name, geometry, params_of_layer, input_array, as_float) runs one layer; with as_float=True it must
     return the layer's fp32 output even for a requantizing layer (int8_scale_term - 100), which gives the range its int8
@@ -225,5 +311,5 @@ def calibrate(layers, params, x, conv_f32_fn):
             scale_of_int8_blob[name] = s_out
         return conv_f32_fn(name, g, p, a, False)
 
-    walk(layers, x, conv_fn)
+    walk(layers, x, conv_fn, want=[l["output"] for l in layers if l["type"] == "Convolution"][-1:], upsample_fn=upsample_fn)
     return params

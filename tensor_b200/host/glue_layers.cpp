@@ -1,5 +1,5 @@
 // The fp32 glue layers of the benchmark graphs in the host-side API mirror: MaxPool, Concat, Crop,
-// ChannelShuffle, ShortCut and the stand-alone activations. Option keys and shape rules follow the reference
+// ChannelShuffle, ShortCut, Upsample and the stand-alone activations. Option keys and shape rules follow the reference
 // layer of the same name; forward enqueues one small CUDA kernel (include/otter_b200.h, "fp32 glue layers").
 // Blobs are device fp32 NCHW tensors.
 #include <algorithm>
@@ -187,6 +187,61 @@ public:
     std::string type() const override { return "ShortCut"; }
 };
 
+// Tensor/UpsampleLayer.cpp:26-131, the one-input form. Option keys upsample_mode, output_height/width, scale_height/width,
+// stride (wins over the scales when non-zero, :80-83) and align_corner. Built: bilinear with align_corner = false, which is
+// what the detector graphs use; nearest, bicubic and align_corner = true return -1.
+class UpsampleLayer : public Layer {
+public:
+    UpsampleLayer() { one_blob_only = true; support_inplace = false; support_packing = true; }
+    int parse_param(LayerOption& option, ParamDict& pd) override {
+        pd.clear();
+        const std::string m = opt_find_string(option, "upsample_mode", "nearest");
+        pd.set(0, m == "nearest" ? 1 : m == "bilinear" ? 2 : m == "bicubic" ? 3 : -1);
+        pd.set(1, opt_find_int(option, "output_height", 0));
+        pd.set(2, opt_find_int(option, "output_width", 0));
+        pd.set(3, opt_find_float(option, "scale_height", 1.f));
+        pd.set(4, opt_find_float(option, "scale_width", 1.f));
+        pd.set(5, opt_find_float(option, "stride", 1.f));
+        pd.set(6, opt_find(option, "align_corner") && option["align_corner"] != "false" ? 1 : 0);
+        return 0;
+    }
+    int compute_output_shape(ParamDict& pd) override {
+        if (bottom_shapes.empty() || !bottom_shapes[0].defined()) return -1;
+        int n, c, h, w;
+        read_shape(bottom_shapes[0], n, c, h, w);
+        int out_h = pd.get(1, 0), out_w = pd.get(2, 0);
+        float sh = pd.get(3, 0.f), sw = pd.get(4, 0.f);
+        const float stride = pd.get(5, 1.f);
+        if (out_h && out_w) { sh = (float)(out_h / h); sw = (float)(out_w / w); }  // integer division, as in the reference (:75-78)
+        if (stride != 0.f) sh = sw = stride;
+        if (sh != 0.f && sw != 0.f) { out_h = (int)(h * sh); out_w = (int)(w * sw); }
+        pd.set(1, out_h); pd.set(2, out_w); pd.set(3, sh); pd.set(4, sw);
+        pd.set(OUTPUT_SHAPE_HINT, shape_tensor(n, c, out_h, out_w));
+        return 0;
+    }
+    int load_param(const ParamDict& pd) override {
+        mode = pd.get(0, 0); scale_height = pd.get(3, 0.f); scale_width = pd.get(4, 0.f); align_corner = pd.get(6, 0);
+        return 0;
+    }
+    int forward(const Tensor& bottom, Tensor& top, const NetOption& opt) const override {
+        if (!is_dev_f32(bottom)) return -1;
+        if (mode != 2 || align_corner) return -1;
+        const int n = (int)bottom.size(0), c = (int)bottom.size(1), h = (int)bottom.size(2), w = (int)bottom.size(3);
+        const int oh = (int)(h * scale_height), ow = (int)(w * scale_width);
+        if (oh < 1 || ow < 1) return -1;
+        top = device_empty(opt, {n, c, oh, ow}, ScalarType::Float, Layout::NCHW);
+        if (!top.defined()) return -100;
+        // The reference's Net hands this layer a packed blob when the channel count is a multiple of 4 (Tensor/Net.cpp:380-411),
+        // and its resize of packed blobs rounds differently from its resize of plain ones (see ott_upsample_bilinear_f32_nchw).
+        const bool packed = opt.use_packing_layout && c % 4 == 0;
+        return ott_upsample_bilinear_f32_nchw(opt.gpu, bottom.data_ptr<float>(), n, c, h, w, oh, ow, scale_height, scale_width, packed ? 1 : 0,
+                                              top.data_ptr<float>());
+    }
+    std::string type() const override { return "Upsample"; }
+    int mode = 2, align_corner = 0;
+    float scale_height = 1.f, scale_width = 1.f;
+};
+
 // Tensor/ReluLayer.cpp, Tensor/LReluLayer.cpp:28-113 (option "alpha", default 0.1), Tensor/Relu6Layer.cpp
 template <int ACT>
 class ActivationLayerT : public Layer {
@@ -227,6 +282,7 @@ REGISTER_LAYER_CLASS(Concat);
 REGISTER_LAYER_CLASS(Crop);
 REGISTER_LAYER_CLASS(ChannelShuffle);
 REGISTER_LAYER_CLASS(ShortCut);
+REGISTER_LAYER_CLASS(Upsample);
 REGISTER_LAYER_CLASS(Relu);
 REGISTER_LAYER_CLASS(LRelu);
 REGISTER_LAYER_CLASS(Relu6);

@@ -14,7 +14,8 @@ requantize/dequantize functions applied to them.
 Also writes tests/golden/epilogue_adversarial.npz: accumulators and scales picked so that a fused
 multiply-add and a separate multiply+add disagree, and values on both rounding rules' tie points,
 with the reference's answers.
-Also writes tests/golden/net_shufflenet_wide_small.npz: blobs of a whole ShuffleNetV2-shaped graph (channel widths all
+Also writes tests/golden/net_nanodet_wide_small.npz (the same for the detector graph of graph_support.wide_nanodet_case) and
+tests/golden/net_shufflenet_wide_small.npz: blobs of a whole ShuffleNetV2-shaped graph (channel widths all
 multiples of 8) run through the reference's own Net (load_otter -> Extractor), one 64x64 image.
 """
 import ctypes as C
@@ -126,7 +127,15 @@ def main():
     for b in blobs:
         net[b] = got[b]
     np.savez_compressed(GOLDEN_DIR / "net_shufflenet_wide_small.npz", **net)
-    for f in ("conv_int8_small.npz", "epilogue_adversarial.npz", "net_shufflenet_wide_small.npz"):
+    # the detector graph (backbone + Ghost-PAN neck with bilinear Upsample / ShortCut + heads) through the reference's Net
+    from graph_support import wide_nanodet_case
+    L, params, x, blobs = wide_nanodet_case()
+    got = reference_net_forward(L, params, x, blobs)
+    det = {"input_sha256": np.frombuffer(digest(x, *[params[k]["weight"] for k in sorted(params)], *[params[k]["in_scales"] for k in sorted(params)]).encode(), dtype=np.uint8)}
+    for b in blobs:
+        det[b] = got[b]
+    np.savez_compressed(GOLDEN_DIR / "net_nanodet_wide_small.npz", **det)
+    for f in ("conv_int8_small.npz", "epilogue_adversarial.npz", "net_shufflenet_wide_small.npz", "net_nanodet_wide_small.npz"):
         print(f, (GOLDEN_DIR / f).stat().st_size, "bytes")
 
 

@@ -27,6 +27,21 @@ def oracle_conv(params, rounding=0):
     return fn
 
 
+def oracle_upsample(a, oh, ow, scale, packed_rule):
+    """The C checker's bilinear Upsample (exact fused multiply-adds), for graphs.walk(upsample_fn=...)."""
+    import ctypes as C
+    from support import _p, load_port
+    lib = load_port()
+    lib.orc_upsample_bilinear.restype = None
+    lib.orc_upsample_bilinear.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_double, C.c_double, C.c_int,
+                                          C.c_void_p]
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    n, c, h, w = a.shape
+    y = np.empty((n, c, oh, ow), np.float32)
+    lib.orc_upsample_bilinear(a.ctypes.data, n, c, h, w, oh, ow, float(scale), float(scale), int(packed_rule), y.ctypes.data)
+    return y
+
+
 def oracle_conv_for_calibration(name, g, p, a, as_float):
     term = g["term"] - 100 if (as_float and g["term"] > 100) else g["term"]
     return run_port(_case(name, g, p, a, term), 0, want_acc=False)["y"]
@@ -53,6 +68,16 @@ def wide_shufflenet_case():
     x = np.random.default_rng(515).uniform(0, 1, size=(1, 3, 64, 64)).astype(np.float32)
     graphs.calibrate(L, params, x, oracle_conv_for_calibration)
     return L, params, x, ["pool1", "s2b1_shuf", "s3b2_shuf", "conv5"]
+
+
+def wide_nanodet_case():
+    """The detector graph (backbone + Ghost-PAN neck + four heads) with widths that are all multiples of 8, so that the
+    reference's packed Net can run it whole; 64x64 input, one image: the levels are 8x8, 4x4, 2x2 and 1x1."""
+    L = graphs.nanodet_plus_layers(64, 64, neck=96, stage_repeats=(2, 2, 2), stage_channels=(176, 352, 704))
+    params = graphs.make_params(L, seed=0x0771E5 + 25)
+    x = np.random.default_rng(525).uniform(0, 1, size=(1, 3, 64, 64)).astype(np.float32)
+    graphs.calibrate(L, params, x, oracle_conv_for_calibration, upsample_fn=oracle_upsample)
+    return L, params, x, ["up32", "td16", "td8", "bu16", "bu32", "p64"] + list(graphs.NANODET_OUTPUTS)
 
 
 def reference_net_forward(layers, params, x, blobs, packed=1):

@@ -141,15 +141,53 @@ def test_whole_graph_equals_the_reference_s_own_net(tmp_path):
     net.close()
 
 
-def test_whole_graph_equals_the_reference_s_own_net(tmp_path):
-    """A whole graph, read from a .otter file, against blobs frozen from the reference's own Net (not only against the
-    layer-by-layer checker)."""
-    from graph_support import wide_shufflenet_case
+@pytest.mark.parametrize("c,h,w,n", [(8, 7, 9, 2), (16, 2, 2, 1), (12, 20, 20, 3), (5, 7, 9, 2), (6, 2, 3, 1), (58, 10, 10, 2), (3, 1, 4, 1), (96, 40, 40, 2)])
+def test_upsample_layer_both_rounding_rules(c, h, w, n):
+    """Bilinear x2 Upsample through the Net: channel counts the reference would pack (multiples of 4) and ones it would not
+    follow different coefficient and rounding rules; both must match the checker bit for bit."""
+    from graph_support import oracle_upsample
+    from tensor_b200 import Net
+    x = np.random.default_rng(c * 1000 + h * 10 + w).normal(size=(n, c, h, w)).astype(np.float32)
+    net = Net(0)
+    net.add_layer(type="Input", name="data", output="data", channel=c, height=h, width=w)
+    net.add_layer(type="Upsample", name="up", input="data", output="up", upsample_mode="bilinear", align_corner="false", stride="2.000000")
+    net.compile()
+    assert net.blob_shape("up")[1:] == (c, 2 * h, 2 * w)
+    got = net.forward("data", x, ["up"])[0]
+    want = oracle_upsample(x, 2 * h, 2 * w, 2.0, 1 if c % 4 == 0 else 0)
+    assert np.array_equal(bits(got), bits(want))
+    net.close()
+
+
+def test_detector_graph_bit_exact():
+    """NanoDet-Plus-style detector on the ShuffleNetV2-1.0x widths (58/116/232-wide layers, 96-wide Ghost-PAN neck, depthwise
+    5x5, Upsample, ShortCut, four heads), batch 2, against the layer-by-layer checker."""
+    from graph_support import build_net, oracle_conv, oracle_conv_for_calibration, oracle_upsample
+    L = graphs.nanodet_plus_layers(96, 128, batch=2)
+    params = graphs.make_params(L, seed=31)
+    x = np.random.default_rng(32).uniform(0, 1, size=(2, 3, 96, 128)).astype(np.float32)
+    graphs.calibrate(L, params, x[:1], oracle_conv_for_calibration, upsample_fn=oracle_upsample)
+    probes = ["r8", "up32", "td16", "td8", "dn8", "bu32", "p64"] + list(graphs.NANODET_OUTPUTS)
+    want = graphs.walk(L, x, oracle_conv(params), want=probes, upsample_fn=oracle_upsample)
+    net = build_net(L, params)
+    got = net.forward("data", x, probes)
+    for name, g in zip(probes, got):
+        assert g.shape == want[name].shape, name
+        assert np.array_equal(bits(g), bits(want[name])), f"blob {name} differs"
+    heads = net.forward("data", x, list(graphs.NANODET_OUTPUTS))
+    for name, g in zip(graphs.NANODET_OUTPUTS, heads):
+        assert np.array_equal(bits(g), bits(want[name])), name
+    net.close()
+
+
+def test_detector_graph_equals_the_reference_s_own_net(tmp_path):
+    """The detector graph, read from a .otter file, against blobs frozen from the reference's own Net."""
+    from graph_support import wide_nanodet_case
     from support import GOLDEN_DIR
     from tensor_b200 import Net
-    gold = np.load(GOLDEN_DIR / "net_shufflenet_wide_small.npz")
-    L, params, x, blobs = wide_shufflenet_case()
-    path = tmp_path / "graph.otter"
+    gold = np.load(GOLDEN_DIR / "net_nanodet_wide_small.npz")
+    L, params, x, blobs = wide_nanodet_case()
+    path = tmp_path / "detector.otter"
     path.write_text(graphs.to_otter_text(L))
     net = Net(0)
     net.load_otter(path)

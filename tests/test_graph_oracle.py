@@ -47,6 +47,36 @@ def test_numpy_glue_equals_reference_layers():
     assert np.array_equal(np.clip(y * 4, 0, 6), ref_layer("Relu6", "", [y * 4]))
 
 
+@pytest.mark.skipif(not have_ref(), reason="oracle/_ref/libotter_ref.so not built")
+@pytest.mark.parametrize("c,h,w", [(8, 7, 9), (16, 2, 2), (4, 5, 3), (12, 20, 20), (5, 7, 9), (6, 2, 3), (58, 10, 10), (3, 1, 4), (96, 40, 40)])
+def test_checker_upsample_equals_reference_layer(c, h, w):
+    """The reference resizes packed blobs (C % 4 == 0) and plain blobs with different coefficient rules and rounding;
+    the checker restates both. Sizes include the clamped borders (2 rows / columns) and one-row planes for the plain rule."""
+    from graph_support import oracle_upsample
+    x = np.random.default_rng(c * 1000 + h * 10 + w).normal(size=(1, c, h, w)).astype(np.float32)
+    want = ref_layer("Upsample", "upsample_mode=bilinear;align_corner=false;stride=2.000000", [x])
+    got = oracle_upsample(x, 2 * h, 2 * w, 2.0, 1 if c % 4 == 0 else 0)
+    assert got.shape == want.shape
+    assert np.array_equal(got.view(np.int32), want.view(np.int32))
+    if c % 4 == 0:  # the two rules really differ: the test above would not notice a swapped flag otherwise
+        assert not np.array_equal(oracle_upsample(x, 2 * h, 2 * w, 2.0, 0), want) or h * w <= 4
+
+
+def test_nanodet_plus_description():
+    L = graphs.nanodet_plus_layers(320, 320)
+    geo = graphs.conv_geometry(L)
+    hw, macs = graphs.conv_input_hw(L, 320, 320)
+    assert geo["r8"]["cin"] == 116 and geo["r32"]["cin"] == 464 and geo["td16_g1pw"]["cin"] == 192 and geo["td16_scdw"]["k"] == 5
+    assert hw["head8"] == (40, 40) and hw["head16"] == (20, 20) and hw["head32"] == (10, 10) and hw["head64"] == (5, 5)
+    assert all(geo[h]["cout"] == 80 + 4 * 8 for h in graphs.NANODET_OUTPUTS)
+    assert sum(1 for l in L if l["type"] == "Upsample") == 2 and sum(1 for l in L if l["type"] == "ShortCut") == 5
+    # every layer type of the graph is one the .otter writer/reader round-trips
+    from tensor_b200 import capi
+    back = capi.parse_otter_text(graphs.to_otter_text(L))
+    assert [l["name"] for l in back] == [l["name"] for l in L]
+    assert next(l for l in back if l["name"] == "up32")["upsample_mode"] == "bilinear"
+
+
 def test_shufflenetv2_description():
     L = graphs.shufflenetv2_layers(320, 320)
     geo = graphs.conv_geometry(L)
@@ -104,3 +134,26 @@ def test_reference_net_live_equals_walk():
     got = graphs.walk(L, x, oracle_conv(params), want=blobs)
     for b in blobs:
         assert np.array_equal(got[b].view(np.int32), ref[b].view(np.int32)), b
+
+
+DET_GOLD = np.load(__import__("support").GOLDEN_DIR / "net_nanodet_wide_small.npz")
+
+
+def test_detector_walk_equals_frozen_reference_net():
+    """Backbone + Ghost-PAN neck (bilinear Upsample, Concat, ShortCut, depthwise 5x5) + heads: the layer-by-layer checker
+    against blobs frozen from the reference's own Net."""
+    from graph_support import oracle_conv, oracle_upsample, wide_nanodet_case
+    L, params, x, blobs = wide_nanodet_case()
+    got = graphs.walk(L, x, oracle_conv(params), want=blobs, upsample_fn=oracle_upsample)
+    for b in blobs:
+        assert got[b].shape == DET_GOLD[b].shape, b
+        assert np.array_equal(got[b].view(np.int32), DET_GOLD[b].view(np.int32)), b
+
+
+@pytest.mark.skipif(not have_ref(), reason="oracle/_ref/libotter_ref.so not built")
+def test_reference_detector_net_live_equals_frozen():
+    from graph_support import reference_net_forward, wide_nanodet_case
+    L, params, x, blobs = wide_nanodet_case()
+    ref = reference_net_forward(L, params, x, blobs)
+    for b in blobs:
+        assert np.array_equal(ref[b].view(np.int32), DET_GOLD[b].view(np.int32)), b
