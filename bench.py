@@ -464,7 +464,22 @@ def run_gpu_arm(args, wl):
 # ----------------------------------------------------------------------------------------------------
 # whole-graph workload: ShuffleNetV2-1.0x int8 backbone (configuration 4), images/s
 
-NET_WORKLOADS = {"shufflenetv2_320": dict(height=320, width=320, batch=256)}
+# Graph workloads. `batch` = images per GPU and step (weak scaling); `total` = images per step over all GPUs (strong scaling, the
+# batch is sharded); `chunk` = images per Net forward inside a step.
+NET_WORKLOADS = {
+    "shufflenetv2_320": dict(height=320, width=320, batch=256, chunk=256, graph="shufflenetv2", outputs=("conv5",),
+                             metric="shufflenetv2_int8_images_per_s", title="ShuffleNetV2-1.0x backbone, int8 convolutions, fp32 glue"),
+    "nanodet_plus_320": dict(height=320, width=320, total=2048, chunk=256, graph="nanodet_plus", outputs=("head8", "head16", "head32", "head64"),
+                             metric="nanodet_plus_int8_images_per_s",
+                             title="NanoDet-Plus-style detector: ShuffleNetV2-1.0x backbone + 96-channel Ghost-PAN neck + 4 heads (80 classes, "
+                                   "reg_max 7), int8 convolutions, fp32 glue"),
+}
+
+
+def graph_layers(cfg, batch=1):
+    from tensor_b200 import graphs
+    build = {"shufflenetv2": graphs.shufflenetv2_layers, "nanodet_plus": graphs.nanodet_plus_layers}[cfg["graph"]]
+    return build(cfg["height"], cfg["width"], batch=batch)
 
 
 def _layer_wl(g, hw, in_f32):
@@ -506,8 +521,7 @@ def net_cpu_reference_time(layers, height, width, reps=2):
 def run_net_reference_arm(args, cfg):
     if int(os.environ.get("RANK", "0")) != 0:
         return
-    from tensor_b200 import graphs
-    layers = graphs.shufflenetv2_layers(cfg["height"], cfg["width"], batch=1)
+    layers = graph_layers(cfg)
     secs = []
     for i in range(args.warmup + args.steps):
         t, how, cores, kind = net_cpu_reference_time(layers, cfg["height"], cfg["width"], reps=1)
@@ -519,8 +533,9 @@ def run_net_reference_arm(args, cfg):
               f"reference cannot run them); glue layers not included; OpenMP {cores} threads")
     value = 1.0 / per_img
     print(json.dumps({
-        "impl": "reference", "metric": "shufflenetv2_int8_images_per_s", "value": value, "unit": "images/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_img * 1e3, "higher_is_better": True, "scaling": "weak",
+        "impl": "reference", "metric": cfg["metric"], "value": value, "unit": "images/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": per_img * 1e3, "higher_is_better": True,
+        "scaling": "strong" if "total" in cfg else "weak",
         "vs_baseline": None, "dtype": "s8xs8->s32", "data": "synthetic",
         "config": {"workload": args.workload, "input": f"3x{cfg['height']}x{cfg['width']} fp32", "images_per_step": 1},
         "cpu_baseline": {"value": value, "unit": "images/s", "cores": cores, "kind": kind, "sample": sample},
@@ -529,10 +544,10 @@ def run_net_reference_arm(args, cfg):
 
 
 def build_calibrated_net(cfg, batch, device, seed=0x0771E5):
-    """ShuffleNetV2 Net on `device` with seeded weights and activation scales calibrated on one synthetic image, the
+    """The workload's Net on `device` with seeded weights and activation scales calibrated on one synthetic image, the
     convolutions of the calibration walk running through the GPU library's own layer objects."""
     from tensor_b200 import F32_NCHW, S8_NHWC, ConvInt8, Context, Net, graphs, nhwc_channels as nc
-    layers = graphs.shufflenetv2_layers(cfg["height"], cfg["width"], batch=batch)
+    layers = graph_layers(cfg, batch)
     params = graphs.make_params(layers, seed)
     x1 = np.random.default_rng(seed).random(size=(1, 3, cfg["height"], cfg["width"]), dtype=np.float32)
     with Context(device) as ctx:
@@ -577,15 +592,24 @@ def run_net_gpu_arm(args, cfg):
         if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
             os.environ["NCCL_DEBUG"] = "WARN"  # NCCL's version banner goes to stdout and would precede the JSON line
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    n, H, W = (args.batch or cfg["batch"]), cfg["height"], cfg["width"]
-    net, layers = build_calibrated_net(cfg, n, local_rank)
+    H, W = cfg["height"], cfg["width"]
+    strong = "total" in cfg and not args.batch
+    n = args.batch or (cfg["total"] // world if strong else cfg["batch"])  # images per GPU and step
+    chunk = min(cfg["chunk"], n)
+    outputs = list(cfg["outputs"])
+    net, layers = build_calibrated_net(cfg, chunk, local_rank)
     ctx = net.context()
     lib = ctx.lib
     _, macs = graphs.conv_input_hw(layers, H, W)
-    out_shape = (n,) + net.blob_shape("conv5")[1:]
-    in_bytes, out_bytes = n * 3 * H * W * 4, int(np.prod(out_shape)) * 4
-    hin, hout = C.c_void_p(), C.c_void_p()
-    assert lib.ott_host_alloc(in_bytes, C.byref(hin)) == 0 and lib.ott_host_alloc(out_bytes, C.byref(hout)) == 0
+    out_elems = [int(np.prod(net.blob_shape(o)[1:])) for o in outputs]  # per image
+    in_bytes, out_bytes = n * 3 * H * W * 4, n * sum(out_elems) * 4
+    hin = C.c_void_p()
+    assert lib.ott_host_alloc(in_bytes, C.byref(hin)) == 0
+    houts = []
+    for e in out_elems:
+        hp = C.c_void_p()
+        assert lib.ott_host_alloc(n * e * 4, C.byref(hp)) == 0
+        houts.append(hp)
     host_in = np.ctypeslib.as_array(C.cast(hin, C.POINTER(C.c_float)), shape=(n, 3, H, W))
     rng = np.random.default_rng(4321 + rank)
     for i in range(0, n, 16):
@@ -593,10 +617,12 @@ def run_net_gpu_arm(args, cfg):
     din = ctx.malloc(in_bytes)
     ctx.check(lib.ott_memcpy_h2d(ctx.h, C.c_void_p(din), hin, in_bytes))
     ctx.sync()
-    shape = (n, 3, H, W)
+    img_bytes = 3 * H * W * 4
+    chunks = [(b0, min(chunk, n - b0)) for b0 in range(0, n, chunk)]
 
-    def step():
-        net.forward_raw("data", C.c_void_p(din), True, shape, ["conv5"], None)
+    def step():  # one pass over this GPU's n images, `chunk` images per Net forward, everything resident on the device
+        for b0, nb in chunks:
+            net.forward_raw("data", C.c_void_p(din + b0 * img_bytes), True, (nb, 3, H, W), outputs, None)
 
     def barrier():
         ctx.sync()
@@ -622,18 +648,24 @@ def run_net_gpu_arm(args, cfg):
     launches = ctx.launch_count() - l0
     clocks = sampler.stop() if rank == 0 else None
 
-    # per-layer device times (events around every layer; serialised) -> the dominant layer and kernel shares
-    prof = net.profile("data", C.c_void_p(din), True, shape, "conv5")
-    prof = net.profile("data", C.c_void_p(din), True, shape, "conv5")
+    # per-layer device times of one chunk (events around every layer; serialised) -> the dominant layer kind and its share.
+    # One profiling pass per output blob; a layer that several outputs need is counted once (its longest time).
+    cshape = (chunks[0][1], 3, H, W)
+    prof = None
+    for o in outputs:
+        net.profile("data", C.c_void_p(din), True, cshape, o)
+        p_o = net.profile("data", C.c_void_p(din), True, cshape, o)
+        prof = p_o if prof is None else [(t_, nm, max(a, b)) for (t_, nm, a), (_, _, b) in zip(prof, p_o)]
 
-    # end to end: host fp32 images in (pinned), host fp32 features out, every step
+    # end to end: host fp32 images in (pinned), host fp32 outputs out, every step
     e2e_steps = max(1, min(args.steps, args.e2e_steps))
-    names = ["conv5"]
-    net.forward_raw("data", hin, False, shape, names, [hout.value])
+    shape = (n, 3, H, W)
+    out_ptrs = [h.value for h in houts]
+    net.forward_raw("data", hin, False, shape, outputs, out_ptrs)
     barrier()
     t0 = time.perf_counter()
     for _ in range(e2e_steps):
-        net.forward_raw("data", hin, False, shape, names, [hout.value])
+        net.forward_raw("data", hin, False, shape, outputs, out_ptrs)
     barrier()
     e2e_s = (time.perf_counter() - t0) / e2e_steps
 
@@ -660,7 +692,7 @@ def run_net_gpu_arm(args, cfg):
                 continue
             g = geo[nm]
             wl = _layer_wl(g, hws[nm], in_f32=g["input"] not in int8_blobs)
-            ops, byts = algorithmic_work(wl, n)
+            ops, byts = algorithmic_work(wl, cshape[0])
             dom_bytes += byts
             dom_ops += ops
             dom_ms += ms
@@ -680,16 +712,18 @@ def run_net_gpu_arm(args, cfg):
             roof["traffic"] = json.loads(traffic_file.read_text()).get(args.workload)
         cpu = None
         if not args.no_cpu:
-            per_img, how, cores, kind = net_cpu_reference_time(graphs.shufflenetv2_layers(H, W, batch=1), H, W, reps=3)
+            per_img, how, cores, kind = net_cpu_reference_time(graph_layers(cfg), H, W, reps=3)
             cpu = {"value": 1.0 / per_img, "unit": "images/s", "cores": cores, "kind": kind,
                    "sample": f"3 images: sum of the convolution layers timed one by one, N=1 ({how['packed']} packed, {how['unpacked']} unpacked reference "
                              f"layers, {how['port']} depthwise layers with C%8!=0 on the C restatement); glue layers not included"}
         print(json.dumps({
-            "metric": "shufflenetv2_int8_images_per_s", "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "s8xs8->s32", "data": "synthetic",
-            "config": {"workload": args.workload, "graph": "ShuffleNetV2-1.0x backbone, int8 convolutions, fp32 glue", "batch_per_gpu": n,
-                       "input": f"3x{H}x{W} fp32 NCHW", "output": "1024x%dx%d fp32" % out_shape[2:], "conv_gop_per_image": 2 * macs / 1e9,
+            "metric": cfg["metric"], "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong" if strong else "weak",
+            "vs_baseline": None, "dtype": "s8xs8->s32", "data": "synthetic",
+            "config": {"workload": args.workload, "graph": cfg["title"], "batch_per_gpu": n, "images_per_forward": chunk,
+                       "input": f"3x{H}x{W} fp32 NCHW",
+                       "output": ", ".join("%s %dx%dx%d fp32" % ((o,) + tuple(net.blob_shape(o)[1:])) for o in outputs),
+                       "conv_gop_per_image": 2 * macs / 1e9,
                        "l2": f"input batch {in_bytes / 1e6:.0f} MB and every stage's activations exceed the 126 MB L2; no flush"},
             "conv_tops": 2.0 * macs * n * world / (step_ms * 1e-3) / 1e12,
             "clocks": clocks, "gpu_launches": int(launches),

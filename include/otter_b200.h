@@ -155,6 +155,12 @@ int ott_conv_int8_forward_gather(ott_ctx* ctx, const ott_conv* conv, const float
 int ott_gather_channels_f32(ott_ctx* ctx, const float* const* buffers, const int64_t* image_strides, int n_buffers,
                             const uint32_t* plane_refs, int channels, int n, int hw, float* dst_dev);
 
+/* ShortCutLayer (Tensor/ShortCutLayer.cpp) with both operands described as plane tables (see ott_conv_int8_forward_gather):
+ * dst[n][channels][hw] = a + b, so that the result of a Concat can be added without first being copied into one tensor. */
+int ott_add_gather_f32(ott_ctx* ctx, const float* const* a_buffers, const int64_t* a_image_strides, int a_n_buffers,
+                       const uint32_t* a_plane_refs, const float* const* b_buffers, const int64_t* b_image_strides, int b_n_buffers,
+                       const uint32_t* b_plane_refs, int channels, int n, int hw, float* dst_dev);
+
 /* First layer + the max-pool that consumes it, in one kernel: out = MaxPool3x3/stride2/pad1(forward(in)), fp32 NCHW
  * [n][cout][(oh-1)/2+1][(ow-1)/2+1]. Replaces the pair conv1 -> pool1 of the reference's graphs (Tensor/ConvolutionLayer.cpp:754-847
  * followed by Tensor/MaxPoolLayer.cpp:123-133) when nothing else reads conv1; the values pooled are exactly the ones the

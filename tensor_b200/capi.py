@@ -59,6 +59,7 @@ SIGNATURES = {
     "ott_conv_int8_forward_ex": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, vp, i32, vp]),
     "ott_conv_int8_forward_gather": (i32, [vp, vp, vp, vp, i32, vp, i32, i32, i32, vp, i32, vp]),
     "ott_gather_channels_f32": (i32, [vp, vp, vp, i32, vp, i32, i32, i32, vp]),
+    "ott_add_gather_f32": (i32, [vp, vp, vp, i32, vp, vp, vp, i32, vp, i32, i32, i32, vp]),
     "ott_conv_int8_forward_maxpool": (i32, [vp, vp, vp, i32, i32, i32, i32, vp]),
     "ott_conv_int8_forward_host": (i32, [vp, vp, vp, i32, i32, i32, i32, vp, i32]),
     "ott_conv_int8_forward_noalloc": (i32, [vp, vp, vp, i32, i32, i32, vp, i32]),

@@ -453,6 +453,29 @@ int ott_gather_channels_f32(ott_ctx* ctx, const float* const* buffers, const int
     return OTT_OK;
 }
 
+int ott_add_gather_f32(ott_ctx* ctx, const float* const* a_buffers, const int64_t* a_image_strides, int a_n_buffers, const uint32_t* a_plane_refs,
+                       const float* const* b_buffers, const int64_t* b_image_strides, int b_n_buffers, const uint32_t* b_plane_refs, int channels,
+                       int n, int hw, float* dst_dev) {
+    if (!ctx || !a_buffers || !a_image_strides || !a_plane_refs || !b_buffers || !b_image_strides || !b_plane_refs || !dst_dev || channels < 0 ||
+        n < 0 || hw < 0)
+        return OTT_ERR_INVALID;
+    if (a_n_buffers < 1 || a_n_buffers > kGatherMaxBufs || b_n_buffers < 1 || b_n_buffers > kGatherMaxBufs || channels > kGatherMaxChannels)
+        return ctx->fail(OTT_ERR_UNSUPPORTED, "gather: at most %d buffers and %d channels", kGatherMaxBufs, kGatherMaxChannels);
+    PlaneGather ga, gb;
+    for (int i = 0; i < a_n_buffers; ++i) { ga.base[i] = a_buffers[i]; ga.img_stride[i] = a_image_strides[i]; }
+    for (int i = 0; i < b_n_buffers; ++i) { gb.base[i] = b_buffers[i]; gb.img_stride[i] = b_image_strides[i]; }
+    for (int i = 0; i < channels; ++i) {
+        if ((int)(a_plane_refs[i] >> 24) >= a_n_buffers || (int)(b_plane_refs[i] >> 24) >= b_n_buffers)
+            return ctx->fail(OTT_ERR_INVALID, "plane reference names a buffer that was not given");
+        ga.ref[i] = a_plane_refs[i];
+        gb.ref[i] = b_plane_refs[i];
+    }
+    cudaSetDevice(ctx->device);
+    OTT_CUDA_CHECK(ctx, launch_add_planes(ctx->stream, ga, gb, dst_dev, n, channels, hw));
+    ctx->launches += 1;
+    return OTT_OK;
+}
+
 }  // extern "C"
 
 namespace {

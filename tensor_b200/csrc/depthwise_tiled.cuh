@@ -98,13 +98,19 @@ __device__ __forceinline__ void row_step(int oy, const uint32_t* __restrict__ pl
         for (int t = 0; t < 4; ++t) q[t] = epi_s8<EPI, ACT>(acc[t], si, bi, so, ep.has_bias, ep.act_param0);
         oplane_s[oy * T.orp + xq] = pack_sat_s8x4(q[0], q[1], q[2], q[3]);
     } else if (of32) {
+        float v[4];
 #pragma unroll
-        for (int t = 0; t < 4; ++t)
-            if (t < ow_left) {
-                const float a = __int2float_rn(acc[t]);
-                const float v = ep.has_bias ? __fmaf_rn(a, si, bi) : __fmul_rn(a, si);
-                of32[t] = activate_t<ACT>(v, ep.act_param0);
-            }
+        for (int t = 0; t < 4; ++t) {
+            const float a = __int2float_rn(acc[t]);
+            v[t] = activate_t<ACT>(ep.has_bias ? __fmaf_rn(a, si, bi) : __fmul_rn(a, si), ep.act_param0);
+        }
+        if (ow_left >= 4 && (reinterpret_cast<uintptr_t>(of32) & 15) == 0) {
+            *reinterpret_cast<float4*>(of32) = make_float4(v[0], v[1], v[2], v[3]);
+        } else {
+#pragma unroll
+            for (int t = 0; t < 4; ++t)
+                if (t < ow_left) of32[t] = v[t];
+        }
     }
 }
 

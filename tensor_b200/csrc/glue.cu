@@ -48,6 +48,12 @@ __global__ void maxpool_kernel(const float* __restrict__ x, float* __restrict__ 
 __global__ void add_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ o, long n) {
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) o[i] = __fadd_rn(a[i], b[i]);
 }
+__global__ void add4_kernel(const float4* __restrict__ a, const float4* __restrict__ b, float4* __restrict__ o, long n4) {
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long)gridDim.x * blockDim.x) {
+        const float4 u = __ldg(a + i), v = __ldg(b + i);
+        o[i] = make_float4(__fadd_rn(u.x, v.x), __fadd_rn(u.y, v.y), __fadd_rn(u.z, v.z), __fadd_rn(u.w, v.w));
+    }
+}
 
 __global__ void activation_kernel(float* __restrict__ x, long n, int act, float p0) {
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) {
@@ -96,16 +102,35 @@ __device__ __forceinline__ AxisTap axis_tap(int d, int in, int out, double user_
 // rounding per product and one per fused multiply-add, in the operand order of the reference build:
 //   rule 1: fma(S1, w1, S0 * w0)      (Tensor/TensorInterpolation.cpp:199-207,251-259)
 //   rule 0: fma(S0, w0, S1 * w1)      (Tensor/UpSampleKernel.cpp:125-139 as compiled with -Ofast -mfma)
-__global__ void upsample_bilinear_kernel(const float* __restrict__ x, float* __restrict__ y, int h, int w, int oh, int ow, double scale_h,
-                                         double scale_w, int rule, long total) {
-    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
-        const int ox = (int)(i % ow);
-        const long r = i / ow;
-        const int oy = (int)(r % oh);
-        const float* xp = x + (r / oh) * (long)h * w;
-        const AxisTap tx = axis_tap(ox, w, ow, scale_w, rule), ty = axis_tap(oy, h, oh, scale_h, rule);
-        const float a00 = __ldg(xp + (long)ty.i0 * w + tx.i0), a01 = __ldg(xp + (long)ty.i0 * w + tx.i1);
-        const float a10 = __ldg(xp + (long)ty.i1 * w + tx.i0), a11 = __ldg(xp + (long)ty.i1 * w + tx.i1);
+// Thread = one output position (ox, oy) of kUpsamplePlanes consecutive planes. The taps depend on the position only and need
+// double-precision arithmetic, so one thread per row and per column of the block computes them once into shared memory.
+constexpr int kUpsamplePlanes = 32;
+__global__ void __launch_bounds__(256)
+upsample_bilinear_kernel(const float* __restrict__ x, float* __restrict__ y, int h, int w, int oh, int ow, double scale_h,
+                         double scale_w, int rule, long planes) {
+    __shared__ AxisTap taps_x[32], taps_y[8];
+    const int tid = threadIdx.y * 32 + threadIdx.x;
+    if (tid < 32) {
+        const int ox = blockIdx.x * 32 + tid;
+        if (ox < ow) taps_x[tid] = axis_tap(ox, w, ow, scale_w, rule);
+    } else if (tid < 40) {
+        const int oy = blockIdx.y * 8 + (tid - 32);
+        if (oy < oh) taps_y[tid - 32] = axis_tap(oy, h, oh, scale_h, rule);
+    }
+    __syncthreads();
+    const int ox = blockIdx.x * 32 + threadIdx.x;
+    const int oy = blockIdx.y * 8 + threadIdx.y;
+    if (ox >= ow || oy >= oh) return;
+    const AxisTap tx = taps_x[threadIdx.x], ty = taps_y[threadIdx.y];
+    const int o00 = ty.i0 * w + tx.i0, o01 = ty.i0 * w + tx.i1, o10 = ty.i1 * w + tx.i0, o11 = ty.i1 * w + tx.i1;
+    const long p0 = (long)blockIdx.z * kUpsamplePlanes;
+    const long p1 = p0 + kUpsamplePlanes < planes ? p0 + kUpsamplePlanes : planes;
+    const long in_plane = (long)h * w, out_plane = (long)oh * ow;
+    const float* xp = x + p0 * in_plane;
+    float* yp = y + p0 * out_plane + (long)oy * ow + ox;
+#pragma unroll 4
+    for (long p = p0; p < p1; ++p, xp += in_plane, yp += out_plane) {
+        const float a00 = __ldg(xp + o00), a01 = __ldg(xp + o01), a10 = __ldg(xp + o10), a11 = __ldg(xp + o11);
         float v;
         if (rule == 1) {
             const float r0 = __fmaf_rn(a01, tx.w1, __fmul_rn(a00, tx.w0));
@@ -116,7 +141,7 @@ __global__ void upsample_bilinear_kernel(const float* __restrict__ x, float* __r
             const float r1 = __fmaf_rn(a10, tx.w0, __fmul_rn(a11, tx.w1));
             v = __fmaf_rn(r0, ty.w0, __fmul_rn(r1, ty.w1));
         }
-        y[i] = v;
+        *yp = v;
     }
 }
 
@@ -171,10 +196,13 @@ int ott_upsample_bilinear_f32_nchw(ott_ctx* ctx, const float* in, int n, int c, 
                                    int packed_rule, float* out) {
     if (!ctx || !in || !out || n < 0 || c < 0 || h < 1 || w < 1 || oh < 1 || ow < 1) return OTT_ERR_INVALID;
     if (packed_rule && (h < 2 || w < 2)) return ctx->fail(OTT_ERR_UNSUPPORTED, "bilinear resize of a packed blob needs at least 2 rows and 2 columns");
-    const long total = (long)n * c * oh * ow;
-    if (total == 0) return OTT_OK;
+    const long planes = (long)n * c;
+    if (planes == 0) return OTT_OK;
+    const long zblocks = (planes + kUpsamplePlanes - 1) / kUpsamplePlanes;
+    if (zblocks > 65535 || (oh + 7) / 8 > 65535) return ctx->fail(OTT_ERR_UNSUPPORTED, "Upsample: more than 2097120 planes or 524280 rows in one call");
     cudaSetDevice(ctx->device);
-    upsample_bilinear_kernel<<<grid_for(ctx, total, 256), 256, 0, ctx->stream>>>(in, out, h, w, oh, ow, scale_h, scale_w, packed_rule ? 1 : 0, total);
+    const dim3 block(32, 8), grid((unsigned)((ow + 31) / 32), (unsigned)((oh + 7) / 8), (unsigned)zblocks);
+    upsample_bilinear_kernel<<<grid, block, 0, ctx->stream>>>(in, out, h, w, oh, ow, scale_h, scale_w, packed_rule ? 1 : 0, planes);
     OTT_CUDA_CHECK(ctx, cudaGetLastError());
     ctx->launches += 1;
     return OTT_OK;
@@ -184,7 +212,11 @@ int ott_add_f32(ott_ctx* ctx, const float* a, const float* b, float* out, size_t
     if (!ctx || !a || !b || !out) return OTT_ERR_INVALID;
     if (count == 0) return OTT_OK;
     cudaSetDevice(ctx->device);
-    add_kernel<<<grid_for(ctx, (long)count, 256), 256, 0, ctx->stream>>>(a, b, out, (long)count);
+    if (count % 4 == 0 && ((uintptr_t)a | (uintptr_t)b | (uintptr_t)out) % 16 == 0)
+        add4_kernel<<<grid_for(ctx, (long)(count / 4), 256), 256, 0, ctx->stream>>>(reinterpret_cast<const float4*>(a), reinterpret_cast<const float4*>(b),
+                                                                                 reinterpret_cast<float4*>(out), (long)(count / 4));
+    else
+        add_kernel<<<grid_for(ctx, (long)count, 256), 256, 0, ctx->stream>>>(a, b, out, (long)count);
     OTT_CUDA_CHECK(ctx, cudaGetLastError());
     ctx->launches += 1;
     return OTT_OK;

@@ -48,6 +48,9 @@ cudaError_t launch_quantize_dense(cudaStream_t stream, const float* x, int c_tot
 // dense fp32 NCHW copy of the gathered planes (for consumers that want one contiguous tensor)
 cudaError_t launch_gather_planes(cudaStream_t stream, const PlaneGather& src, float* dst, int n, int c, long hw);
 
+// dst = a + b, fp32 NCHW, both operands read through plane tables
+cudaError_t launch_add_planes(cudaStream_t stream, const PlaneGather& a, const PlaneGather& b, float* dst, int n, int c, long hw);
+
 // Depthwise: x int8 NHWC [n,h,w,c_pad]; weights int8 [kh*kw][c_pad] (tap-major, channel innermost).
 cudaError_t launch_depthwise(cudaStream_t stream, const ConvShape& s, const int8_t* x, const int8_t* w_taps,
                              const EpilogueParams& ep, void* out, int out_dtype);

@@ -151,6 +151,43 @@ __global__ void gather_planes_kernel(const __grid_constant__ PlaneGather G, floa
     }
 }
 
+// dst[img][c][p] = A.plane(c, img)[p] + B.plane(c, img)[p]: the reference's ShortCut (Tensor/ShortCutLayer.cpp) reading both
+// operands where their planes lie. Block = one plane (or a slice of one), so the table look-up is per block, not per element.
+__global__ void add_planes_kernel(const __grid_constant__ PlaneGather A, const __grid_constant__ PlaneGather B, float* __restrict__ dst, int c,
+                                  long hw, int slices, int vec) {
+    const long plane = blockIdx.x / slices;
+    const int slice = (int)(blockIdx.x % slices);
+    const int ch = (int)(plane % c);
+    const int img = (int)(plane / c);
+    const float* a = A.plane(ch, img, hw);
+    const float* b = B.plane(ch, img, hw);
+    float* o = dst + plane * hw;
+    const long per = vec ? hw / 4 : hw;
+    const long lo = per * slice / slices, hi = per * (slice + 1) / slices;
+    if (vec) {
+        for (long i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+            const float4 u = __ldg(reinterpret_cast<const float4*>(a) + i), v = __ldg(reinterpret_cast<const float4*>(b) + i);
+            reinterpret_cast<float4*>(o)[i] = make_float4(__fadd_rn(u.x, v.x), __fadd_rn(u.y, v.y), __fadd_rn(u.z, v.z), __fadd_rn(u.w, v.w));
+        }
+    } else {
+        for (long i = lo + threadIdx.x; i < hi; i += blockDim.x) o[i] = __fadd_rn(__ldg(a + i), __ldg(b + i));
+    }
+}
+
+cudaError_t launch_add_planes(cudaStream_t stream, const PlaneGather& a, const PlaneGather& b, float* dst, int n, int c, long hw) {
+    if (n == 0 || c == 0 || hw == 0) return cudaSuccess;
+    if (c > kGatherMaxChannels) return cudaErrorInvalidValue;
+    const int vec = hw % 4 == 0 ? 1 : 0;
+    const long per = vec ? hw / 4 : hw;
+    const int threads = per >= 256 ? 256 : (per >= 128 ? 128 : 64);
+    int slices = (int)((per + 4L * threads - 1) / (4L * threads));  // about four elements (vectors) per thread
+    if (slices < 1) slices = 1;
+    const long blocks = (long)n * c * slices;
+    if (blocks > 0x7fffffffL) return cudaErrorInvalidValue;
+    add_planes_kernel<<<(unsigned)blocks, threads, 0, stream>>>(a, b, dst, c, hw, slices, vec);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_gather_planes(cudaStream_t stream, const PlaneGather& src, float* dst, int n, int c, long hw) {
     if (n == 0 || c == 0 || hw == 0) return cudaSuccess;
     if (c > kGatherMaxChannels) return cudaErrorInvalidValue;

@@ -174,15 +174,38 @@ public:
     int groups = 1;
 };
 
-// Tensor/ShortCutLayer.cpp (element-wise add of two blobs of the same shape)
+// Tensor/ShortCutLayer.cpp (element-wise add of two blobs of the same shape). Operands that are plane tables (the result of a
+// Concat in the Ghost blocks of the detector graphs) are read where their planes lie.
 class ShortCutLayer : public Layer {
 public:
-    ShortCutLayer() { one_blob_only = false; support_inplace = false; support_packing = true; }
+    ShortCutLayer() { one_blob_only = false; support_inplace = false; support_packing = true; accepts_tables = true; }
     int forward(const std::vector<Tensor>& bottoms, std::vector<Tensor>& tops, const NetOption& opt) const override {
-        if (bottoms.size() != 2 || !is_dev_f32(bottoms[0]) || !is_dev_f32(bottoms[1]) || bottoms[0].sizes() != bottoms[1].sizes()) return -1;
-        tops[0] = device_empty(opt, bottoms[0].sizes(), ScalarType::Float, Layout::NCHW);
+        if (bottoms.size() != 2 || !is_dev_f32_or_table(bottoms[0]) || !is_dev_f32_or_table(bottoms[1]) || bottoms[0].sizes() != bottoms[1].sizes())
+            return -1;
+        Tensor a = bottoms[0], b = bottoms[1];
+        const int n = (int)a.size(0), c = (int)a.size(1), hw = (int)(a.size(2) * a.size(3));
+        std::vector<const float*> abufs, bbufs;
+        std::vector<int64_t> astr, bstr;
+        std::vector<uint32_t> arefs, brefs;
+        auto describe = [&](Tensor& t, std::vector<const float*>& bufs, std::vector<int64_t>& strides, std::vector<uint32_t>& refs) {
+            if (t.is_table() && table_arrays(t, bufs, strides)) { refs = t.table_refs(); return true; }
+            if (t.is_table()) { t = materialize(opt, t); if (!t.defined()) return false; }
+            if (c > kMaxTableChannels) return false;
+            bufs.assign(1, t.data_ptr<float>());
+            strides.assign(1, (int64_t)c * hw);
+            refs.resize((size_t)c);
+            for (int i = 0; i < c; ++i) refs[(size_t)i] = (uint32_t)i;
+            return true;
+        };
+        tops[0] = device_empty(opt, a.sizes(), ScalarType::Float, Layout::NCHW);
         if (!tops[0].defined()) return -100;
-        return ott_add_f32(opt.gpu, bottoms[0].data_ptr<float>(), bottoms[1].data_ptr<float>(), tops[0].data_ptr<float>(), (size_t)bottoms[0].numel());
+        if ((a.is_table() || b.is_table()) && describe(a, abufs, astr, arefs) && describe(b, bbufs, bstr, brefs))
+            return ott_add_gather_f32(opt.gpu, abufs.data(), astr.data(), (int)abufs.size(), arefs.data(), bbufs.data(), bstr.data(), (int)bbufs.size(),
+                                      brefs.data(), c, n, hw, tops[0].data_ptr<float>());
+        a = materialize(opt, a);
+        b = materialize(opt, b);
+        if (!a.defined() || !b.defined()) return -100;
+        return ott_add_f32(opt.gpu, a.data_ptr<float>(), b.data_ptr<float>(), tops[0].data_ptr<float>(), (size_t)a.numel());
     }
     std::string type() const override { return "ShortCut"; }
 };

@@ -185,7 +185,7 @@ int ott_net_forward(ott_net* net, const char* input_blob, const void* in, int in
             rc = ott_memcpy_overlapped(ctx, 0, dptr, static_cast<const char*>(in) + img_bytes * b0, img_bytes * nb);
             if (rc != OTT_OK) break;
             otter::Extractor ex = net->net.create_extractor();
-            ex.set_lightmode(n_out == 1);
+            for (int i = 0; i < n_out; ++i) ex.keep(out_blobs[i]);
             ex.input(input_blob, otter::Tensor::wrap(dptr, img_bytes * nb, otter::Device::CUDA, nullptr, {nb, c, h, w}, otter::ScalarType::Float));
             std::vector<otter::Tensor> dev((size_t)n_out);
             for (int i = 0; i < n_out && rc == OTT_OK; ++i) rc = ex.extract(out_blobs[i], dev[(size_t)i], 1);
@@ -210,9 +210,9 @@ int ott_net_forward(ott_net* net, const char* input_blob, const void* in, int in
         x = otter::from_blob(const_cast<void*>(in), {n, c, h, w}, otter::ScalarType::Float);
     int rc = ex.input(input_blob, x);
     if (rc != 0) return fail(net, rc, "Extractor::input failed");
-    // outputs are pulled in order; with lightmode a blob consumed on the way to an earlier output is gone, so
-    // keep every requested blob alive by extracting device handles first
-    ex.set_lightmode(n_out == 1);
+    // outputs are pulled in order; a requested blob that is consumed on the way to another output must survive lightmode
+    for (int i = 0; i < n_out; ++i)
+        if (ex.keep(out_blobs[i]) != 0) return fail(net, OTT_ERR_INVALID, std::string("unknown blob ") + out_blobs[i]);
     std::vector<otter::Tensor> dev((size_t)n_out);
     for (int i = 0; i < n_out; ++i) {
         rc = ex.extract(out_blobs[i], dev[(size_t)i], 1);

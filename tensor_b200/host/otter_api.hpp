@@ -130,6 +130,7 @@ public:
     // reader's int8 input itself (same bytes as dequantize -> store -> load -> quantize); a blob asked for through
     // Extractor::extract is still delivered in fp32
     bool int8_handover = true;
+    const std::vector<char>* keep_blobs = nullptr;  // set by Extractor::keep: blobs lightmode must not release
     int blob_wanted = -1;  // set by Extractor::extract: the blob that must come out in the reference's own type
     int int8_rounding = OTT_ROUND_ADD_HALF_TRUNC;  // which reference build is mirrored (packed x86 default / aarch64)
     std::vector<float>* layer_ms = nullptr;  // when set: per-layer device time, indexed by layer (Extractor::benchmark_info)
@@ -302,6 +303,9 @@ class Extractor {
 public:
     void clear();
     void set_lightmode(bool lightmode) { option.lightmode = lightmode; }
+    // Blobs that will be extracted later from this Extractor: lightmode keeps them although their reader has run. (Every
+    // other blob read by two layers survives anyway, through the Split layer the Net inserted.)
+    int keep(const std::string& blob_name);
     // `in` may be a host fp32 NCHW tensor (copied to the GPU here) or a device tensor made by device_empty
     int input(const std::string& blob_name, const Tensor& in);
     int input(int blob_index, const Tensor& in);
@@ -318,6 +322,7 @@ private:
     Extractor(const Net* net, size_t blob_count);
     const Net* net_;
     std::vector<Tensor> blob_tensors_;
+    std::vector<char> keep_;
     NetOption option;
 };
 

@@ -502,7 +502,8 @@ int Net::do_forward_layer(const Layer* layer, std::vector<Tensor>& blob_tensors,
         Tensor bottom = prepared(blob_tensors[(size_t)layer->bottoms[0]]);
         if (!bottom.defined()) { error_ = "could not materialise the input of layer " + layer->name; return -100; }
         Tensor top;
-        if (opt.lightmode && layer->support_inplace && bottom.use_count() <= 2) {  // ours + the blob table's
+        const bool kept = opt.keep_blobs && (*opt.keep_blobs)[(size_t)layer->bottoms[0]];
+        if (opt.lightmode && layer->support_inplace && bottom.use_count() <= 2 && !kept) {  // ours + the blob table's
             top = bottom;
             ret = layer->forward_inplace(top, opt);
         } else {
@@ -521,7 +522,8 @@ int Net::do_forward_layer(const Layer* layer, std::vector<Tensor>& blob_tensors,
         for (size_t i = 0; i < tops.size(); ++i) blob_tensors[(size_t)layer->tops[i]] = tops[i];
     }
     if (opt.lightmode)  // Tensor/Net.cpp:449-451: a consumed blob is dropped at once (the allocator reuses it stream-ordered)
-        for (int b : layer->bottoms) blob_tensors[(size_t)b].reset();
+        for (int b : layer->bottoms)
+            if (!(opt.keep_blobs && (*opt.keep_blobs)[(size_t)b])) blob_tensors[(size_t)b].reset();
     return 0;
 }
 
@@ -529,6 +531,14 @@ int Net::do_forward_layer(const Layer* layer, std::vector<Tensor>& blob_tensors,
 Extractor::Extractor(const Net* net, size_t blob_count) : net_(net), blob_tensors_(blob_count), option(net->option) {}
 
 void Extractor::clear() { for (auto& t : blob_tensors_) t.reset(); }
+
+int Extractor::keep(const std::string& blob_name) {
+    const int idx = net_->find_blob_index_by_name(blob_name);
+    if (idx < 0) return -1;
+    if (keep_.empty()) keep_.assign(blob_tensors_.size(), 0);
+    keep_[(size_t)idx] = 1;
+    return 0;
+}
 
 int Extractor::input(const std::string& blob_name, const Tensor& in) {
     const int idx = net_->find_blob_index_by_name(blob_name);
@@ -597,6 +607,7 @@ int Extractor::extract(int blob_index, Tensor& feat, int type) {
     }
     if (!blob_tensors_[(size_t)blob_index].defined()) {
         option.blob_wanted = blob_index;
+        option.keep_blobs = keep_.empty() ? nullptr : &keep_;
         const int ret = net_->forward_layer(net_->blobs_[(size_t)blob_index].producer, blob_tensors_, option);
         option.blob_wanted = -1;
         if (ret != 0) return ret;
