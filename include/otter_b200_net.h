@@ -39,6 +39,14 @@ int ott_net_add_layer(ott_net* net, const char* options);
  * adds its layers and compiles. Use instead of ott_net_add_layer + ott_net_compile. */
 int ott_net_load_otter(ott_net* net, const char* path);
 
+/* A real model: Net::load_otter(otter_path, CompileMode::Inference) followed by Net::load_weight(weight_path, type)
+ * (Tensor/Net.cpp:518-607). weight_type 1 = WeightType::Ncnn, the ncnn `.bin` of a quantized model (int8 weights tagged
+ * 0x000D4B38, then bias, weight scales, input scale and - for requantizing layers - output scale per Convolution, in graph
+ * order: Tensor/ConvolutionLayer.cpp:245-296, Tensor/Initializer.cpp:64-188); 0 = WeightType::Otter (plain fp32, which only
+ * fp32 layers can use, so an int8 graph fails in create_pipeline). A file with bytes left over is an error, as in the
+ * reference. */
+int ott_net_load_model(ott_net* net, const char* otter_path, const char* weight_path, int weight_type);
+
 /* The `.otter` reader alone (no GPU needed): parses `text` and writes one line per layer, "key=value;key=value;..." with
  * the layer type under key "type", into out (NUL-terminated, at most cap bytes). Returns the number of layers, or a
  * negative status (OTT_ERR_INVALID on a syntax error or when cap is too small). */

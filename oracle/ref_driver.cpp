@@ -346,6 +346,21 @@ REF_API int ref_net_open(const char* otter_path, int packed) {
     } catch (const std::exception& e) { g_err = e.what(); g_net.reset(); return -2; } catch (const char* s) { g_err = s; g_net.reset(); return -3; } catch (...) { g_err = "unknown"; g_net.reset(); return -4; }
 }
 
+// The reference's own way in for real models: graph from the .otter text, parameters from an ncnn-format weight file
+// (Net::load_otter with CompileMode::Inference, then Net::load_weight(path, WeightType::Ncnn): Tensor/Net.cpp:518-607).
+REF_API int ref_net_open_weights(const char* otter_path, const char* ncnn_bin_path, int packed) {
+    try {
+        g_net.reset(new otter::Net());
+        g_net->option.use_packing_layout = packed != 0;
+        g_net->option.lightmode = true;
+        int rc = g_net->load_otter(otter_path, otter::CompileMode::Inference);
+        if (rc != 0) { g_err = "load_otter failed"; return rc; }
+        rc = g_net->load_weight(ncnn_bin_path, otter::Net::WeightType::Ncnn);
+        if (rc != 0) g_err = "load_weight failed (or bytes were left over in the file)";
+        return rc;
+    } catch (const std::exception& e) { g_err = e.what(); g_net.reset(); return -2; } catch (const char* s) { g_err = s; g_net.reset(); return -3; } catch (...) { g_err = "unknown"; g_net.reset(); return -4; }
+}
+
 REF_API void ref_net_close() { g_net.reset(); }
 
 REF_API int ref_net_set_conv(const char* layer_name, const int8_t* w_oihw, const float* bias, const float* w_scales, const float* in_scales,

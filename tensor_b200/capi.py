@@ -78,6 +78,7 @@ SIGNATURES = {
     "ott_net_add_layer": (i32, [vp, C.c_char_p]),
     "ott_net_compile": (i32, [vp]),
     "ott_net_load_otter": (i32, [vp, C.c_char_p]),
+    "ott_net_load_model": (i32, [vp, C.c_char_p, C.c_char_p, i32]),
     "ott_otter_parse_text": (i32, [C.c_char_p, C.c_char_p, i32]),
     "ott_net_layer_count": (i32, [vp]),
     "ott_net_layer_info": (i32, [vp, i32, C.c_char_p, i32, C.c_char_p, i32, C.POINTER(i32)]),
@@ -301,6 +302,10 @@ class Net:
     def load_otter(self, path: str):
         """Read a .otter text graph (the reference's model-structure format) and compile it."""
         self.check(self.lib.ott_net_load_otter(self.h, str(path).encode()))
+
+    def load_model(self, otter_path: str, weight_path: str, weight_type: str = "ncnn"):
+        """Graph from a .otter file, parameters from a weight file ("ncnn": the .bin of a quantized ncnn model)."""
+        self.check(self.lib.ott_net_load_model(self.h, str(otter_path).encode(), str(weight_path).encode(), 1 if weight_type == "ncnn" else 0))
 
     def context(self) -> "Context":
         ctx = Context.__new__(Context)

@@ -138,10 +138,48 @@ int ConvolutionLayer::init_model() {
     return 0;
 }
 
+// Tensor/ConvolutionLayer.cpp:245-296. Order of the values in an ncnn file: weights (tagged), bias, weight scales, the
+// input scale, and for a requantizing layer the output scale. Depthwise layers replicate the scalar scales to [groups];
+// int8_scale_term 2 / 102 on a depthwise layer means one weight scale for all channels.
+int ConvolutionLayer::load_model(const Initializer& initializer) {
+    const bool ncnn = initializer.type == InitializerType::Ncnn;
+    if (!ncnn && bias_term) bias_data = initializer.load({out_channels}, 1);
+    weight_data = initializer.load({out_channels, in_channels / groups, kernel_height, kernel_width}, 0);
+    if (!weight_data.defined()) return -1;
+    if (!ncnn) return 0;
+    if (bias_term) {
+        bias_data = initializer.load({out_channels}, 1);
+        if (!bias_data.defined()) return -1;
+    }
+    auto scalar_to = [&](int n) {
+        Tensor one = initializer.load({1}, 1);
+        return one.defined() ? full({n}, one.data_ptr<float>()[0], ScalarType::Float) : Tensor();
+    };
+    if (!int8_scale_term) return 0;
+    if (in_channels == groups && groups == out_channels) {
+        if (int8_scale_term == 1 || int8_scale_term == 101) {
+            weight_data_int8_scales = initializer.load({groups}, 1);
+            bottom_blob_int8_scales = scalar_to(groups);
+        } else {
+            weight_data_int8_scales = scalar_to(groups);
+            bottom_blob_int8_scales = scalar_to(groups);
+        }
+        if (int8_scale_term > 100) top_blob_int8_scales = scalar_to(groups);
+    } else {
+        weight_data_int8_scales = initializer.load({out_channels}, 1);
+        bottom_blob_int8_scales = initializer.load({1}, 1);
+        if (int8_scale_term > 100) top_blob_int8_scales = initializer.load({1}, 1);
+    }
+    if (!weight_data_int8_scales.defined() || !bottom_blob_int8_scales.defined()) return -1;
+    if (int8_scale_term > 100 && !top_blob_int8_scales.defined()) return -1;
+    return 0;
+}
+
 // Tensor/ConvolutionLayer.cpp:298-304 -> create_pipeline_int8 (:666-752)
 int ConvolutionLayer::create_pipeline(const NetOption& opt) {
     if (!int8_scale_term) return -1;  // the fp32 layer is not part of this build
     if (!opt.gpu) return -1;
+    if (weight_data.defined() && weight_data.scalar_type() != ScalarType::Byte) return -1;  // fp32 weights: the fp32 layer again
     if (!weight_data.defined() || !weight_data_int8_scales.defined() || !bottom_blob_int8_scales.defined()) return -1;
     release_gpu();
     gpu_ctx_ = opt.gpu;

@@ -48,6 +48,14 @@ const char* ott_net_last_error(const ott_net* net) {
 
 ott_ctx* ott_net_context(ott_net* net) { return net ? net->net.context() : nullptr; }
 
+int ott_net_load_model(ott_net* net, const char* otter_path, const char* weight_path, int weight_type) {
+    if (!net || !otter_path || !weight_path || (weight_type != 0 && weight_type != 1)) return OTT_ERR_INVALID;
+    net->error.clear();
+    int rc = net->net.load_otter(otter_path, otter::CompileMode::Inference);
+    if (rc != 0) return rc;
+    return net->net.load_weight(weight_path, weight_type == 1 ? otter::Net::WeightType::Ncnn : otter::Net::WeightType::Otter);
+}
+
 int ott_net_set_option(ott_net* net, const char* key, int value) {
     if (!net || !key) return OTT_ERR_INVALID;
     otter::NetOption& o = net->net.option;

@@ -136,7 +136,46 @@ public:
     std::vector<float>* layer_ms = nullptr;  // when set: per-layer device time, indexed by layer (Extractor::benchmark_info)
 };
 
-class Initializer;  // weight readers (Tensor/Initializer.hpp) are not part of this build
+// ---- weight files (Tensor/DataReader.hpp, Tensor/Initializer.hpp) ----
+class DataReader {
+public:
+    virtual ~DataReader() = default;
+    virtual size_t read(void* buf, size_t size) const = 0;
+    virtual size_t remain() const = 0;  // bytes not yet read
+};
+class DataReaderFromStdio : public DataReader {
+public:
+    explicit DataReaderFromStdio(FILE* file) : file_(file) {}
+    size_t read(void* buf, size_t size) const override;
+    size_t remain() const override;
+private:
+    FILE* file_;
+};
+enum class InitializerType { Otter, Ncnn };
+class Initializer {
+public:
+    virtual ~Initializer() = default;
+    // type 0: a weight blob with its 4-byte storage tag in front (ncnn files); type 1: plain fp32 values
+    virtual Tensor load(std::vector<int64_t> shape, int type) const = 0;
+    InitializerType type = InitializerType::Otter;
+};
+// Tensor/Initializer.cpp:21-51: the reference's own weight files, plain fp32 throughout
+class InitializerFromDataReader : public Initializer {
+public:
+    explicit InitializerFromDataReader(const DataReader& dr) : dr_(dr) { type = InitializerType::Otter; }
+    Tensor load(std::vector<int64_t> shape, int type) const override;
+private:
+    const DataReader& dr_;
+};
+// Tensor/Initializer.cpp:57-188: ncnn model files. Tags: 0x000D4B38 int8 values (padded to 4 bytes), 0x0002C056 / 0 raw fp32.
+// Half-precision (0x01306B47) and 256-entry table weights describe fp32 layers, which this build does not run: load fails.
+class InitializerNcnnFromDataReader : public Initializer {
+public:
+    explicit InitializerNcnnFromDataReader(const DataReader& dr) : dr_(dr) { type = InitializerType::Ncnn; }
+    Tensor load(std::vector<int64_t> shape, int type) const override;
+private:
+    const DataReader& dr_;
+};
 
 using LayerOption = std::unordered_map<std::string, std::string>;
 
@@ -216,6 +255,7 @@ public:
     int compute_output_shape(ParamDict& pd) override;
     int load_param(const ParamDict& pd) override;
     int init_model() override;
+    int load_model(const Initializer& initializer) override;
     int create_pipeline(const NetOption& opt) override;
     int forward(const Tensor& bottom_blob, Tensor& top_blob, const NetOption& opt) const override;
     std::string type() const override { return "Convolution"; }
@@ -253,7 +293,8 @@ struct Blob {
     Tensor shape;
 };
 
-enum class CompileMode { Initial, OnlyStructure };
+// Tensor/NetOption.hpp:26-29. Inference: structure only, parameters come from Net::load_weight; Initial: random parameters.
+enum class CompileMode { Inference, Initial };
 class Extractor;
 int parse_otter_text(const std::string& text, std::vector<LayerOption>& layers, std::string& err);  // the .otter reader
 
@@ -268,6 +309,12 @@ public:
     void addLayer(LayerOption option);
     int compile(CompileMode mode = CompileMode::Initial);  // 0 on success (the reference throws on a bad graph)
     int load_otter(const char* model_structure, CompileMode mode = CompileMode::Initial);  // Tensor/Net.cpp:518-536
+    enum class WeightType { Otter, Ncnn };
+    // Tensor/Net.cpp:538-607: every layer's load_model in graph order, then create_pipeline. An ncnn file must be consumed to
+    // its last byte (the reference returns non-zero otherwise).
+    int load_weight(const char* weight_path, WeightType type = WeightType::Otter);
+    int load_weight(const DataReader& dr, WeightType type);
+    int load_weight(const Initializer& initializer);
     Extractor create_extractor() const;
     void summary() const;
     int find_blob_index_by_name(const std::string& name) const;
@@ -286,6 +333,7 @@ public:
 private:
     void graph_construct();
     int refresh_handover(int producer_layer);
+    int plan_fusions();  // first layer + max-pool, int8 hand-over: after every create_pipeline
     int forward_layer(int layer_index, std::vector<Tensor>& blob_tensors, const NetOption& opt) const;
     int do_forward_layer(const Layer* layer, std::vector<Tensor>& blob_tensors, const NetOption& opt) const;
 

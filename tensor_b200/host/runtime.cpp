@@ -384,27 +384,11 @@ int Net::compile(CompileMode mode) {
             if (rc != 0) { error_ = "create_pipeline of " + layer->name + " failed: " + ott_last_error(option.gpu); return rc; }
         }
     }
-    // first layer + max-pool fusion: conv1's blob must have the pool as its only reader
     blob_fused_away_.assign(blobs_.size(), 0);
-    if (option.fuse_first_layer_pool && mode == CompileMode::Initial) {
-        for (Layer* l : layers_) {
-            auto* conv = dynamic_cast<ConvolutionLayer*>(l);
-            if (!conv || !conv->can_fuse_maxpool()) continue;
-            const Blob& b = blobs_[(size_t)conv->tops[0]];
-            if (b.consumer < 0) continue;
-            Layer* pool = layers_[(size_t)b.consumer];
-            if (!pool->is_pool3x3s2p1() || pool->bottoms.size() != 1) continue;
-            // same rule as MaxPoolLayer::forward: the reference's packed 3x3 s2 kernels pad with zeros
-            conv->fused_maxpool = (option.use_packing_layout && conv->out_channels % 4 == 0) ? 2 : 1;
-            pool->absorbed = true;
-            blob_fused_away_[(size_t)conv->tops[0]] = 1;
-        }
+    if (mode == CompileMode::Initial) {
+        const int rc = plan_fusions();
+        if (rc != 0) return rc;
     }
-    if (mode == CompileMode::Initial)
-        for (size_t i = 0; i < layers_.size(); ++i) {
-            const int rc = refresh_handover((int)i);
-            if (rc != 0) { error_ = "create_pipeline (int8 hand-over) of " + layers_[i]->name + " failed: " + ott_last_error(option.gpu); return rc; }
-        }
     input_names_.clear();
     output_names_.clear();
     for (Layer* l : layers_)
@@ -431,6 +415,30 @@ int Net::refresh_handover(int producer_layer) {
     }
     if (!scales.defined() && !conv->handover_scales.defined()) return 0;
     return conv->set_handover(option, scales);
+}
+
+int Net::plan_fusions() {
+    blob_fused_away_.assign(blobs_.size(), 0);
+    // first layer + max-pool fusion: conv1's blob must have the pool as its only reader
+    if (option.fuse_first_layer_pool) {
+        for (Layer* l : layers_) {
+            auto* conv = dynamic_cast<ConvolutionLayer*>(l);
+            if (!conv || !conv->can_fuse_maxpool()) continue;
+            const Blob& b = blobs_[(size_t)conv->tops[0]];
+            if (b.consumer < 0) continue;
+            Layer* pool = layers_[(size_t)b.consumer];
+            if (!pool->is_pool3x3s2p1() || pool->bottoms.size() != 1) continue;
+            // same rule as MaxPoolLayer::forward: the reference's packed 3x3 s2 kernels pad with zeros
+            conv->fused_maxpool = (option.use_packing_layout && conv->out_channels % 4 == 0) ? 2 : 1;
+            pool->absorbed = true;
+            blob_fused_away_[(size_t)conv->tops[0]] = 1;
+        }
+    }
+    for (size_t i = 0; i < layers_.size(); ++i) {
+        const int rc = refresh_handover((int)i);
+        if (rc != 0) { error_ = "create_pipeline (int8 hand-over) of " + layers_[i]->name + " failed: " + ott_last_error(option.gpu); return rc; }
+    }
+    return 0;
 }
 
 int Net::recreate_pipeline(int layer_index) {

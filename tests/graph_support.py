@@ -80,7 +80,27 @@ def wide_nanodet_case():
     return L, params, x, ["up32", "td16", "td8", "bu16", "bu32", "p64"] + list(graphs.NANODET_OUTPUTS)
 
 
-def reference_net_forward(layers, params, x, blobs, packed=1):
+def write_ncnn_bin(layers, params, path):
+    """The parameters as an ncnn model file, the way a quantized ncnn model stores them and ConvolutionLayer::load_model reads
+    them back (Tensor/ConvolutionLayer.cpp:245-296): per Convolution, in graph order, the int8 weights behind the tag
+    0x000D4B38 (padded to 4 bytes), the bias, the weight scales ([groups] for a depthwise layer with int8_scale_term 1/101,
+    [out_channels] for a dense one), the scalar input scale and, for int8_scale_term > 100, the scalar output scale."""
+    geo = graphs.conv_geometry(layers)
+    with open(path, "wb") as f:
+        for l in layers:
+            if l["type"] != "Convolution":
+                continue
+            g, p = geo[l["name"]], params[l["name"]]
+            w = np.ascontiguousarray(p["weight"], dtype=np.int8).tobytes()
+            f.write(np.uint32(0x000D4B38).tobytes() + w + b"\0" * (-len(w) % 4))
+            f.write(np.ascontiguousarray(p["bias"], dtype=np.float32).tobytes())
+            f.write(np.ascontiguousarray(p["w_scales"], dtype=np.float32).tobytes())
+            f.write(np.float32(p["in_scales"][0]).tobytes())
+            if g["term"] > 100:
+                f.write(np.float32(p["out_scales"][0]).tobytes())
+
+
+def reference_net_forward(layers, params, x, blobs, packed=1, weight_file=None):
     """The same graph through the compiled reference's own Net (oracle/_ref): .otter text -> Net::load_otter -> parameters
     replaced -> Extractor. One image."""
     import ctypes as C
@@ -91,8 +111,11 @@ def reference_net_forward(layers, params, x, blobs, packed=1):
         f.write(graphs.to_otter_text(layers))
         path = f.name
     try:
-        assert ref.ref_net_open(path.encode(), packed) == 0, ref.ref_last_error()
-        for name, p in params.items():
+        if weight_file is not None:  # parameters through the reference's own ncnn weight reader
+            assert ref.ref_net_open_weights(path.encode(), str(weight_file).encode(), packed) == 0, ref.ref_last_error()
+        else:
+            assert ref.ref_net_open(path.encode(), packed) == 0, ref.ref_last_error()
+        for name, p in ({} if weight_file is not None else params).items():
             os_ = p["out_scales"]
             rc = ref.ref_net_set_conv(name.encode(), _p(p["weight"], C.c_int8), _p(p["bias"], C.c_float), _p(p["w_scales"], C.c_float),
                                       _p(p["in_scales"], C.c_float), p["in_scales"].size, _p(os_, C.c_float) if os_ is not None else None,

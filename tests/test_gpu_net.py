@@ -199,6 +199,33 @@ def test_detector_graph_equals_the_reference_s_own_net(tmp_path):
     net.close()
 
 
+def test_model_from_otter_and_ncnn_weight_file(tmp_path):
+    """Net::load_otter(Inference) + Net::load_weight(Ncnn): graph and parameters both come from files, as for a real model.
+    The file layout is pinned on the CPU side by the reference's own reader."""
+    from graph_support import wide_nanodet_case, write_ncnn_bin
+    from support import GOLDEN_DIR
+    from tensor_b200 import Net, OtterB200Error
+    gold = np.load(GOLDEN_DIR / "net_nanodet_wide_small.npz")
+    L, params, x, blobs = wide_nanodet_case()
+    (tmp_path / "m.otter").write_text(graphs.to_otter_text(L))
+    write_ncnn_bin(L, params, tmp_path / "m.bin")
+    net = Net(0)
+    net.load_model(tmp_path / "m.otter", tmp_path / "m.bin", "ncnn")
+    got = net.forward("data", x, blobs)
+    for b, g in zip(blobs, got):
+        assert np.array_equal(bits(g), bits(gold[b])), b
+    net.close()
+    # a file with bytes left over, or too short, is refused (the reference returns non-zero for both)
+    data = (tmp_path / "m.bin").read_bytes()
+    (tmp_path / "long.bin").write_bytes(data + b"\0\0\0\0")
+    (tmp_path / "short.bin").write_bytes(data[:-8])
+    for bad in ("long.bin", "short.bin"):
+        net = Net(0)
+        with pytest.raises(OtterB200Error):
+            net.load_model(tmp_path / "m.otter", tmp_path / bad, "ncnn")
+        net.close()
+
+
 def test_chunked_host_forward_equals_plain_forward():
     """Large host batches run in chunks with overlapped copies; every image must come out as in a plain forward."""
     from graph_support import build_net, oracle_conv_for_calibration

@@ -157,3 +157,16 @@ def test_reference_detector_net_live_equals_frozen():
     ref = reference_net_forward(L, params, x, blobs)
     for b in blobs:
         assert np.array_equal(ref[b].view(np.int32), DET_GOLD[b].view(np.int32)), b
+
+
+@pytest.mark.skipif(not have_ref(), reason="oracle/_ref/libotter_ref.so not built")
+def test_reference_reads_our_ncnn_weight_file(tmp_path):
+    """The .bin written by the test helper, read by the reference's own Net::load_weight(…, Ncnn), gives the frozen blobs:
+    pins the file layout that the GPU Net's reader is then tested against."""
+    from graph_support import reference_net_forward, wide_nanodet_case, write_ncnn_bin
+    L, params, x, blobs = wide_nanodet_case()
+    path = tmp_path / "detector.bin"
+    write_ncnn_bin(L, params, path)
+    ref = reference_net_forward(L, params, x, blobs, weight_file=path)
+    for b in blobs:
+        assert np.array_equal(ref[b].view(np.int32), DET_GOLD[b].view(np.int32)), b
