@@ -320,30 +320,30 @@ dense_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 const long img = pix / plane, inimg = pix - img * plane;
                 out_f32 = reinterpret_cast<float*>(out) + (img * s.cout + n_tile * P.bn) * plane + inimg;
             }
-            for (int col0 = sub * 16; col0 < P.bn; col0 += col_step) {
-                int v[16];
-                __syncwarp();  // tcgen05.ld is warp-collective
-                tmem_ld16(taddr + (uint32_t)col0, v);
-                tmem_wait_ld16(v);
+            // 16 accumulator columns -> 16 outputs of this thread's pixel. int8 results come back as 4 packed words in wds
+            // (the caller stores them); the other output kinds are stored here.
+            auto emit16 = [&](const int (&v)[16], int col0, uint32_t (&wds)[4]) {
                 const int c0 = n_tile * P.bn + col0;  // first global output channel of this chunk
-                if (!valid || c0 >= s.cout_pad) continue;
                 if (OUT == DT_S32_NHWC) {
                     int4* o = reinterpret_cast<int4*>(out_s32 + col0);
 #pragma unroll
                     for (int g = 0; g < 4; ++g) o[g] = make_int4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
-                    continue;
+                    return;
                 }
+                // two fp32 lanes per instruction (fma.rn.f32x2 and friends): each lane rounds exactly like the scalar form
                 float y[16];
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
                     const float4 si = *reinterpret_cast<const float4*>(s_si + col0 + g * 4);
                     const float4 bi = *reinterpret_cast<const float4*>(s_bi + col0 + g * 4);
-                    const float sia[4] = {si.x, si.y, si.z, si.w}, bia[4] = {bi.x, bi.y, bi.z, bi.w};
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const float a = __int2float_rn(v[g * 4 + j]);
-                        const float t = BIAS ? __fmaf_rn(a, sia[j], bia[j]) : __fmul_rn(a, sia[j]);
-                        y[g * 4 + j] = activate_t<ACT>(t, ep.act_param0);
+                    for (int h = 0; h < 2; ++h) {
+                        const float2 a = make_float2(__int2float_rn(v[g * 4 + 2 * h]), __int2float_rn(v[g * 4 + 2 * h + 1]));
+                        const float2 s2 = h ? make_float2(si.z, si.w) : make_float2(si.x, si.y);
+                        const float2 b2 = h ? make_float2(bi.z, bi.w) : make_float2(bi.x, bi.y);
+                        const float2 t = BIAS ? __ffma2_rn(a, s2, b2) : __fmul2_rn(a, s2);
+                        y[g * 4 + 2 * h] = activate_t<ACT>(t.x, ep.act_param0);
+                        y[g * 4 + 2 * h + 1] = activate_t<ACT>(t.y, ep.act_param0);
                     }
                 }
                 if (OUT == DT_F32_NCHW) {
@@ -351,26 +351,57 @@ dense_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                     for (int j = 0; j < 16; ++j)
                         if (c0 + j < s.cout) out_f32[(long)(col0 + j) * plane] = y[j];
                 } else {
-                    uint32_t wds[4];
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {
                         const float4 so = *reinterpret_cast<const float4*>(s_so + col0 + g * 4);
-                        const float soa[4] = {so.x, so.y, so.z, so.w};
                         int qv[4];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const float t = __fmul_rn(y[g * 4 + j], soa[j]);
+                        for (int h = 0; h < 2; ++h) {
+                            const float2 t = __fmul2_rn(make_float2(y[g * 4 + 2 * h], y[g * 4 + 2 * h + 1]),
+                                                        h ? make_float2(so.z, so.w) : make_float2(so.x, so.y));
                             if (ROUND == ROUND_HALF_AWAY) {
-                                qv[j] = float2int8(t, ROUND_HALF_AWAY);
+                                qv[2 * h] = float2int8(t.x, ROUND_HALF_AWAY);
+                                qv[2 * h + 1] = float2int8(t.y, ROUND_HALF_AWAY);
                             } else if (ACT == ACT_RELU || ACT == ACT_RELU6) {
-                                qv[j] = f2i8_nonneg(t);
+                                // t >= 0 (or -0): trunc(t + 0.5), the upper clamp is the saturating pack
+                                const float2 r = __fadd2_rn(t, make_float2(0.5f, 0.5f));
+                                qv[2 * h] = __float2int_rz(r.x);
+                                qv[2 * h + 1] = __float2int_rz(r.y);
                             } else {
-                                qv[j] = f2i8_lo_clamped(t);  // the upper clamp is the saturating pack
+                                const float2 r = __fadd2_rn(t, make_float2(copysignf(0.5f, t.x), copysignf(0.5f, t.y)));
+                                qv[2 * h] = __float2int_rz(fmaxf(r.x, -127.5f));
+                                qv[2 * h + 1] = __float2int_rz(fmaxf(r.y, -127.5f));
                             }
                         }
                         wds[g] = pack_sat_s8x4(qv[0], qv[1], qv[2], qv[3]);
                     }
-                    *reinterpret_cast<uint4*>(out_s8 + col0) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+                }
+            };
+            // Chunks of 32 columns: two TMEM loads in flight, and int8 rows leave as one 32-byte store per thread, a whole
+            // DRAM sector (two 16-byte stores from different warps would each touch half of it).
+            const bool wide_ok = OUT == DT_S8_NHWC && ((s.cout_pad | (n_tile * P.bn)) & 31) == 0;
+            for (int col0 = sub * 32; col0 < P.bn; col0 += 2 * col_step) {
+                int va[16], vb[16];
+                const bool two = col0 + 16 < P.bn;
+                __syncwarp();  // tcgen05.ld is warp-collective
+                tmem_ld16(taddr + (uint32_t)col0, va);
+                if (two) tmem_ld16(taddr + (uint32_t)(col0 + 16), vb);
+                tmem_wait_ld16(va);
+                tmem_wait_ld16(vb);
+                if (!valid) continue;
+                uint32_t wa[4], wb[4];
+                const bool a_ok = n_tile * P.bn + col0 < s.cout_pad, b_ok = two && n_tile * P.bn + col0 + 16 < s.cout_pad;
+                if (a_ok) emit16(va, col0, wa);
+                if (b_ok) emit16(vb, col0 + 16, wb);
+                if (OUT == DT_S8_NHWC) {
+                    if (a_ok && b_ok && wide_ok) {
+                        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(out_s8 + col0), "r"(wa[0]), "r"(wa[1]),
+                                     "r"(wa[2]), "r"(wa[3]), "r"(wb[0]), "r"(wb[1]), "r"(wb[2]), "r"(wb[3])
+                                     : "memory");
+                    } else {
+                        if (a_ok) *reinterpret_cast<uint4*>(out_s8 + col0) = make_uint4(wa[0], wa[1], wa[2], wa[3]);
+                        if (b_ok) *reinterpret_cast<uint4*>(out_s8 + col0 + 16) = make_uint4(wb[0], wb[1], wb[2], wb[3]);
+                    }
                 }
             }
             tc_fence_before();
