@@ -431,7 +431,7 @@ int ott_conv_int8_forward_maxpool(ott_ctx* ctx, const ott_conv* c, const float* 
     ep.has_bias = d.bias_term ? 1 : 0;
     ep.act_type = d.act_type; ep.act_param0 = d.act_param0; ep.rounding = d.rounding;
     OTT_CUDA_CHECK(ctx, launch_dense_stem_pool(ctx->stream, s, in_dev, c->w_host.data(), c->scale_in_host.data(), c->bias_host.data(), c->in_scale0,
-                                                ep, out_dev, pad_with_zero));
+                                                ep, out_dev, pad_with_zero, ctx->status_dev));
     ctx->launches += 1;
     return OTT_OK;
 }

@@ -98,14 +98,15 @@ def test_unknown_layer_type_is_an_error_not_an_exit():
     net.close()
 
 
-@pytest.mark.parametrize("h,w,cout,act", [(45, 71, 24, "LRelu"), (64, 64, 16, "Relu"), (33, 130, 22, "LRelu")])
-def test_first_layer_and_maxpool_fused_kernel(h, w, cout, act):
+@pytest.mark.parametrize("h,w,cout,act,stride", [(45, 71, 24, "LRelu", 2), (64, 64, 16, "Relu", 2), (33, 130, 22, "LRelu", 2),
+                                                 (37, 50, 24, "LRelu", 1), (16, 16, 8, "Relu6", 1), (320, 320, 24, "Relu", 2)])
+def test_first_layer_and_maxpool_fused_kernel(h, w, cout, act, stride):
     """conv1 -> pool1 runs as one kernel; the pooled blob must equal the layer-by-layer checker, including the reference's
     packed zero-padding rule (cout % 4 == 0) after an activation that leaves negative values."""
     from graph_support import build_net, oracle_conv, oracle_conv_for_calibration
     from tensor_b200 import OtterB200Error
     L = [dict(type="Input", name="data", output="data", channel=3, height=h, width=w),
-         graphs._conv("conv1", "data", cout, 3, 2, 1, 2, act),
+         graphs._conv("conv1", "data", cout, 3, stride, 1, 2, act),
          dict(type="MaxPool", name="pool1", input="conv1", output="pool1", kernel_h=3, kernel_w=3, stride_h=2, stride_w=2, padding_h=1, padding_w=1)]
     params = graphs.make_params(L)
     x = (np.random.default_rng(21).uniform(0, 1, size=(2, 3, h, w)).astype(np.float32))
