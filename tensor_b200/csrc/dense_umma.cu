@@ -35,6 +35,8 @@ namespace {
 constexpr int kMaxEpiWarps = 8;                     // 2 per TMEM lane quarter
 constexpr int kMaxThreads = 64 + 32 * kMaxEpiWarps;  // UmmaPlan::epi_warps is 4 or 8
 constexpr int kTileM = 128;
+constexpr int kMaxAccBufs = 4;
+constexpr int kHaloTw = 8, kHaloTh = 16;  // pixel tile of the halo mode: 8 wide so that a tile row is one 8-row operand group
 using namespace umma;
 
 struct SmemLayout {
@@ -45,9 +47,9 @@ __host__ __device__ inline SmemLayout smem_layout(const UmmaPlan& p) {
     SmemLayout L;
     L.b_panel = 0;
     L.a_stages = (uint32_t)p.nkb * p.bn * p.bkc;
-    L.bars = L.a_stages + (uint32_t)p.stages * kTileM * p.bkc;
-    // barriers: full[stages], empty[stages], b_full, tmem_full[2], tmem_empty[2]
-    L.tmem_slot = L.bars + 8u * (2u * p.stages + 5u);
+    L.bars = L.a_stages + (uint32_t)p.stages * (uint32_t)p.a_stage_bytes;
+    // barriers: full[stages], empty[stages], b_full, tmem_full[kMaxAccBufs], tmem_empty[kMaxAccBufs]
+    L.tmem_slot = L.bars + 8u * (2u * p.stages + 1u + 2u * kMaxAccBufs);
     L.abort_flag = L.tmem_slot + 8;
     L.params = (L.abort_flag + 8 + 15u) & ~15u;  // scale_in[bn], bias[bn], scale_out[bn]; read as float4
     L.total = L.params + 3u * 4u * p.bn;
@@ -57,7 +59,7 @@ __host__ __device__ inline SmemLayout smem_layout(const UmmaPlan& p) {
 // MULTI: compiled for three resident CTAs per SM (64 registers per thread), which small layers need to hide latency; the
 // one-CTA-per-SM plans of large layers use the build without that register limit.
 template <int OUT, int ACT, bool BIAS, int ROUND, bool MULTI>
-__global__ void __launch_bounds__(kMaxThreads, MULTI ? 3 : 1)
+__global__ void __launch_bounds__(kMaxThreads, MULTI ? 2 : 1)
 dense_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const UmmaPlan P,
                   const ConvShape s, const EpilogueParams ep, void* __restrict__ out, uint32_t* __restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
@@ -66,14 +68,18 @@ dense_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const SmemLayout L = smem_layout(P);
     const uint32_t sB = base + L.b_panel, sA = base + L.a_stages;
     const uint32_t bar_full = base + L.bars, bar_empty = bar_full + 8u * P.stages, bar_b = bar_empty + 8u * P.stages;
-    const uint32_t bar_tfull = bar_b + 8, bar_tempty = bar_tfull + 16;
+    const uint32_t bar_tfull = bar_b + 8, bar_tempty = bar_tfull + 8u * kMaxAccBufs;
+    const uint32_t acc_mask = (uint32_t)P.acc_bufs - 1u, acc_shift = P.acc_bufs == 4 ? 2u : 1u;  // 2 or 4 accumulators in TMEM
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + L.tmem_slot);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + L.abort_flag);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_tile = blockIdx.x % P.n_tiles;
     const int m_first = blockIdx.x / P.n_tiles, m_step = gridDim.x / P.n_tiles;
-    const uint32_t a_stage_bytes = (uint32_t)kTileM * P.bkc, b_tile_bytes = (uint32_t)P.bn * P.bkc;
+    const uint32_t a_stage_bytes = (uint32_t)P.a_stage_bytes, b_tile_bytes = (uint32_t)P.bn * P.bkc;
+    // halo mode: the 8 pixels of one tile row are one 8-row operand group; groups (tile rows) are one halo row apart
+    const int halo_w = kHaloTw + s.kw - 1, halo_h = kHaloTh + s.kh - 1;
+    const int loads_per_tile = P.halo ? P.ncb : P.nkb;  // pipeline stages one pixel tile consumes
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < P.stages; ++i) {
@@ -81,7 +87,7 @@ dense_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             mbar_init(bar_empty + 8u * i, 1);
         }
         mbar_init(bar_b, 1);
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < P.acc_bufs; ++i) {
             mbar_init(bar_tfull + 8u * i, 1);
             mbar_init(bar_tempty + 8u * i, (uint32_t)P.epi_warps);  // one arrival per epilogue warp
         }
@@ -128,13 +134,19 @@ dense_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                     y0 = (r / P.tiles_x) * P.th - s.ph;
                     x0 = (r % P.tiles_x) * P.tw - s.pw;
                 }
-                for (int kb = 0; kb < P.nkb; ++kb, ++it) {
-                    const int tap = kb / P.ncb, cb = kb - tap * P.ncb;
-                    const int ky = tap / s.kw, kx = tap - ky * s.kw;
+                for (int kb = 0; kb < loads_per_tile; ++kb, ++it) {
                     const uint32_t st = it % P.stages, ph = (it / P.stages) & 1u;
                     if (!mbar_wait(bar_empty + 8u * st, ph ^ 1u, abort_flag, status, 1u)) { ok = false; break; }
-                    mbar_expect_tx(bar_full + 8u * st, a_stage_bytes);
-                    tma_load_4d(&tmA, bar_full + 8u * st, sA + st * a_stage_bytes, cb * P.bkc, x0 + kx * s.dw, y0 + ky * s.dh, img);
+                    if (P.halo) {
+                        // the (8 + kw - 1) x (16 + kh - 1) pixels under the tile, one channel block; out-of-image pixels arrive as zeros
+                        mbar_expect_tx(bar_full + 8u * st, (uint32_t)(halo_w * halo_h * P.bkc));
+                        tma_load_4d(&tmA, bar_full + 8u * st, sA + st * a_stage_bytes, kb * P.bkc, x0, y0, img);
+                    } else {
+                        const int tap = kb / P.ncb, cb = kb - tap * P.ncb;
+                        const int ky = tap / s.kw, kx = tap - ky * s.kw;
+                        mbar_expect_tx(bar_full + 8u * st, (uint32_t)kTileM * P.bkc);
+                        tma_load_4d(&tmA, bar_full + 8u * st, sA + st * a_stage_bytes, cb * P.bkc, x0 + kx * s.dw, y0 + ky * s.dh, img);
+                    }
                 }
             }
             if (!ok) {
@@ -150,18 +162,37 @@ dense_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             tc_fence_after();
             uint32_t it = 0, tile_i = 0;
             for (int m = m_first; ok && m < P.m_tiles; m += m_step, ++tile_i) {
-                const uint32_t buf = tile_i & 1u, use = tile_i >> 1;
+                const uint32_t buf = tile_i & acc_mask, use = tile_i >> acc_shift;
                 if (!mbar_wait(bar_tempty + 8u * buf, (use & 1u) ^ 1u, abort_flag, status, 4u)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d = tmem_base + buf * (uint32_t)P.acc_stride;
-                for (int kb = 0; kb < P.nkb; ++kb, ++it) {
+                for (int kb = 0; kb < loads_per_tile; ++kb, ++it) {
                     const uint32_t st = it % P.stages, ph = (it / P.stages) & 1u;
                     if (!mbar_wait(bar_full + 8u * st, ph, abort_flag, status, 2u)) { ok = false; break; }
                     tc_fence_after();
-                    const uint64_t adesc = make_smem_desc(sA + st * a_stage_bytes, P.bkc);
-                    const uint64_t bdesc = make_smem_desc(sB + kb * b_tile_bytes, P.bkc);
-                    for (int j = 0; j < P.bkc / 32; ++j)
-                        umma_i8(d, adesc + 2ull * j, bdesc + 2ull * j, P.idesc, (kb | j) != 0 ? 1u : 0u);
+                    if (P.halo) {
+                        // every filter tap reads the same halo tile through a view shifted by (ky, kx) pixels
+                        // (one thread issues all of these back to back, so the per-tap descriptors are the base descriptors plus
+                        // an offset in their 16-byte address field, not rebuilt from scratch)
+                        const uint64_t a0 = make_smem_desc(sA + st * a_stage_bytes, P.bkc, halo_w * P.bkc);
+                        const uint64_t b0 = make_smem_desc(sB + kb * b_tile_bytes, P.bkc);
+                        const uint32_t b_tap_step = ((uint32_t)P.ncb * b_tile_bytes) >> 4, a_px_step = (uint32_t)P.bkc >> 4;
+                        uint32_t accumulate = kb != 0 ? 1u : 0u, a_row = 0, b_off = 0;
+                        for (int ky = 0; ky < s.kh; ++ky, a_row += (uint32_t)halo_w * a_px_step) {
+                            uint32_t a_off = a_row;
+                            for (int kx = 0; kx < s.kw; ++kx, a_off += a_px_step, b_off += b_tap_step) {
+                                for (int j = 0; j < P.bkc / 32; ++j) {
+                                    umma_i8(d, a0 + a_off + 2u * j, b0 + b_off + 2u * j, P.idesc, accumulate);
+                                    accumulate = 1u;
+                                }
+                            }
+                        }
+                    } else {
+                        const uint64_t adesc = make_smem_desc(sA + st * a_stage_bytes, P.bkc);
+                        const uint64_t bdesc = make_smem_desc(sB + kb * b_tile_bytes, P.bkc);
+                        for (int j = 0; j < P.bkc / 32; ++j)
+                            umma_i8(d, adesc + 2ull * j, bdesc + 2ull * j, P.idesc, (kb | j) != 0 ? 1u : 0u);
+                    }
                     umma_commit(bar_empty + 8u * st);  // frees the A stage once these MMAs have read it
                 }
                 if (!ok) break;
@@ -182,7 +213,7 @@ dense_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         uint32_t tile_i = 0;
         bool ok = true;
         for (int m = m_first; ok && m < P.m_tiles; m += m_step, ++tile_i) {
-            const uint32_t buf = tile_i & 1u, use = tile_i >> 1;
+            const uint32_t buf = tile_i & acc_mask, use = tile_i >> acc_shift;
             if (!mbar_wait(bar_tfull + 8u * buf, use & 1u, abort_flag, status, 8u)) { ok = false; break; }
             tc_fence_after();
             // which output pixel this thread's TMEM lane holds
@@ -376,7 +407,9 @@ bool umma_plan_layer(int cin, int cout, int kh, int kw, int sh, int sw, int dh, 
     const long k_total = (long)p.nkb * p.bkc;
     // largest BN (multiple of 16, <= 256) whose weight panel leaves room for at least 3 A stages,
     // preferring a split of cout_pad into equal tiles
-    const long a_stage = (long)kTileM * p.bkc;
+    p.halo = (p.taps > 1 && dh == 1 && dw == 1) ? 1 : 0;
+    const long a_stage = p.halo ? ((long)p.bkc * (kHaloTw + kw - 1) * (kHaloTh + kh - 1) + 1023) / 1024 * 1024 : (long)kTileM * p.bkc;
+    p.a_stage_bytes = (int)a_stage;
     const long avail = (long)smem_budget - 1024 /*alignment slack*/ - 4096 /*barriers + epilogue parameters*/ - 3 * a_stage;
     if (avail <= 0) return false;
     long bn_max = avail / k_total;
@@ -393,10 +426,14 @@ bool umma_plan_layer(int cin, int cout, int kh, int kw, int sh, int sw, int dh, 
     // Small layers (few k-blocks, narrow panels) are latency-bound with one CTA per SM: keep the pipeline short so that
     // several CTAs fit an SM and overlap each other's TMA / MMA / epilogue latencies.
     if (p.nkb <= 2 && p.stages > 4) p.stages = 4;
+    // a halo stage feeds all the taps of a whole pixel tile and channel block: three are a deep enough pipeline
+    if (p.halo && p.stages > 3) p.stages = 3;
     if (p.stages < 2) return false;
     // two accumulators of bn columns each; TMEM allocations are powers of two >= 32 columns
     p.acc_stride = p.bn <= 32 ? 32 : (p.bn <= 64 ? 64 : (p.bn <= 128 ? 128 : 256));
-    p.tmem_cols = 2 * p.acc_stride;
+    // narrow tiles finish quickly; four accumulators let the MMA issuer run three tiles ahead of the epilogue
+    p.acc_bufs = p.acc_stride <= 64 ? 4 : 2;
+    p.tmem_cols = p.acc_bufs * p.acc_stride;
     // instruction descriptor: D=s32 (2<<4), A=B=signed int8 (1<<7, 1<<10), both K-major, N>>3 at bit 17, M>>4 at bit 24
     p.idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
     p.k_total = (int)k_total;
@@ -466,19 +503,20 @@ const char* launch_dense_umma(cudaStream_t stream, int sm_count, const UmmaPlan&
         r = enc(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)x, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 swizzle_for(p.bkc), CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     } else {
-        // rectangle of 128 output pixels with the least padding waste
+        // rectangle of 128 output pixels with the least padding waste (halo mode: always 8 x 16)
         long best = -1;
         for (int tw = 8; tw <= 128; tw *= 2) {
             const int th = kTileM / tw;
             const long cover = (long)((s.ow + tw - 1) / tw) * tw * ((s.oh + th - 1) / th) * th;
             if (best < 0 || cover < best) { best = cover; p.tw = tw; p.th = th; }
         }
+        if (p.halo) { p.tw = kHaloTw; p.th = kHaloTh; }
         p.tiles_x = (s.ow + p.tw - 1) / p.tw;
         p.tiles_y = (s.oh + p.th - 1) / p.th;
         p.m_tiles = s.n * p.tiles_x * p.tiles_y;
         cuuint64_t dims[4] = {(cuuint64_t)s.cin_pad, (cuuint64_t)s.w, (cuuint64_t)s.h, (cuuint64_t)s.n};
         cuuint64_t strides[3] = {(cuuint64_t)s.cin_pad, (cuuint64_t)s.cin_pad * s.w, (cuuint64_t)s.cin_pad * s.w * s.h};
-        cuuint32_t box[4] = {(cuuint32_t)p.bkc, (cuuint32_t)p.tw, (cuuint32_t)p.th, 1};
+        cuuint32_t box[4] = {(cuuint32_t)p.bkc, (cuuint32_t)(p.halo ? p.tw + s.kw - 1 : p.tw), (cuuint32_t)(p.halo ? p.th + s.kh - 1 : p.th), 1};
         r = enc(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)x, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 swizzle_for(p.bkc), CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     }

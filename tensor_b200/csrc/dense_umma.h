@@ -12,13 +12,16 @@ struct UmmaPlan {
     // N: n_tiles weight panels of bn output channels (multiple of 16, <= 256); cout_rows = n_tiles*bn
     int bn, n_tiles, cout_rows;
     int stages;      // activation tiles in flight
-    int tmem_cols;   // TMEM columns allocated (two accumulators)
-    int acc_stride;  // column offset of the second accumulator
+    int tmem_cols;   // TMEM columns allocated (acc_bufs accumulators)
+    int acc_stride;  // column offset from one accumulator to the next
+    int acc_bufs;    // accumulators in flight between the MMA issuer and the epilogue: 2, or 4 for narrow tiles
     uint32_t idesc;  // tcgen05 instruction descriptor
     int smem_bytes;  // dynamic shared memory of the launch
     int epi_warps;   // epilogue warps per CTA: 8 or 16
     int ctas_per_sm; // resident CTAs per SM the launch is sized for (limited by TMEM columns and shared memory)
     // per call
+    int halo;        // k x k layers: one TMA box per pixel tile and channel block holds the tile plus its halo; the taps read shifted views
+    int a_stage_bytes;  // bytes of one activation stage (a 128-pixel tile, or a halo tile rounded up to 1 KiB)
     int flat;                          // 1x1: activations viewed as one [pixels, channels] matrix
     int tw, th, tiles_x, tiles_y, m_tiles;  // 128-pixel output rectangles (tw*th == 128)
 };

@@ -81,11 +81,11 @@ __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence:
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
 // K-major shared-memory operand descriptor: rows of `row_bytes` (= the swizzle span), 8-row groups
-// `8*row_bytes` apart. Bits: [0,14) address>>4, [16,30) leading offset>>4 (unused for swizzled K-major),
+// `8*row_bytes` apart unless group_stride_bytes says otherwise (rows of a group are always contiguous). Bits: [0,14) address>>4, [16,30) leading offset>>4 (unused for swizzled K-major),
 // [32,46) stride offset>>4, [46,48) version=1, [61,64) swizzle (2=128B, 4=64B, 6=32B).
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, int row_bytes) {
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr, int row_bytes, int group_stride_bytes = 0) {
     const uint64_t swz = row_bytes == 128 ? 2ull : (row_bytes == 64 ? 4ull : 6ull);
-    const uint64_t sbo = (uint64_t)(8 * row_bytes) >> 4;
+    const uint64_t sbo = (uint64_t)(group_stride_bytes ? group_stride_bytes : 8 * row_bytes) >> 4;
     return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | (sbo << 32) | (1ull << 46) | (swz << 61);
 }
 

@@ -74,6 +74,13 @@ def test_batched_equals_single_images(ctx):
     ("stem_odd_s2", dict(cin=3, cout=24, k=3, stride=2, pad=1, n=2, h=45, w=71, int8_scale_term=2, act_type=ACT_RELU, x_lo=0.0)),
     ("stem_s1_lrelu_s8", dict(cin=3, cout=16, k=3, stride=1, pad=1, n=2, h=33, w=40, int8_scale_term=101, act_type=ACT_LRELU, act_param0=0.1, x_lo=0.0)),
     ("stem_tiles", dict(cin=3, cout=24, k=3, stride=2, pad=1, n=3, h=96, w=160, int8_scale_term=2, act_type=ACT_RELU, x_lo=0.0)),
+    # k x k dense layers read one halo tile per pixel tile through shifted operand views: every swizzle width, several
+    # channel blocks, ragged tiles in both directions, no padding / wide padding, 5x5
+    ("halo_3x3_c128", dict(cin=128, cout=128, k=3, pad=1, n=2, h=23, w=19, int8_scale_term=101, act_type=ACT_RELU, s8_input=True)),
+    ("halo_3x3_c160_two_blocks", dict(cin=160, cout=96, k=3, pad=1, n=2, h=17, w=30, int8_scale_term=2)),
+    ("halo_3x3_c32_nopad", dict(cin=32, cout=32, k=3, pad=0, n=2, h=21, w=12, int8_scale_term=2, act_type=ACT_LRELU, act_param0=0.1)),
+    ("halo_3x3_c64_pad2", dict(cin=64, cout=48, k=3, pad=2, n=1, h=9, w=9, int8_scale_term=101, s8_input=True)),
+    ("halo_5x5_c32", dict(cin=32, cout=64, k=5, pad=2, n=2, h=20, w=20, int8_scale_term=101, act_type=ACT_RELU6)),
     ("two_n_tiles", dict(cin=256, cout=512, k=1, n=3, h=28, w=28, int8_scale_term=101, act_type=ACT_RELU6)),
     ("four_n_tiles", dict(cin=512, cout=1024, k=1, n=2, h=14, w=14, int8_scale_term=101, act_type=ACT_RELU6)),
 ])
