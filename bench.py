@@ -64,6 +64,10 @@ WORKLOADS = {
     # dense 3x3 (config 1 batched): fp32 in, fp32 out
     "dense3x3_64_hw56_n256": dict(cin=64, cout=64, k=3, stride=1, pad=1, groups=1, n=256, h=56, w=56, term=2, act=ACT_NONE, in_f32=True),
     "dense3x3_64_hw56_n256_s8": dict(cin=64, cout=64, k=3, stride=1, pad=1, groups=1, n=256, h=56, w=56, term=102, act=ACT_RELU, in_f32=False),
+    # wider 3x3 layers (not in the benchmark configurations): where the tensor cores, not the per-tile overheads, set the pace
+    "dense3x3_128_hw56_n128_s8": dict(cin=128, cout=128, k=3, stride=1, pad=1, groups=1, n=128, h=56, w=56, term=102, act=ACT_RELU, in_f32=False),
+    "dense3x3_64_256_hw56_n128_s8": dict(cin=64, cout=256, k=3, stride=1, pad=1, groups=1, n=128, h=56, w=56, term=102, act=ACT_RELU, in_f32=False),
+    "dense3x3_256_hw28_n128_s8": dict(cin=256, cout=256, k=3, stride=1, pad=1, groups=1, n=128, h=28, w=28, term=102, act=ACT_RELU, in_f32=False),
 }
 DEFAULT_WORKLOAD = "shufflenetv2_320"
 
