@@ -204,6 +204,17 @@ int ott_add_f32(ott_ctx* ctx, const float* a, const float* b, float* out, size_t
 /* stand-alone ReluLayer / LReluLayer / Relu6Layer, in place (act_type as in ott_conv_desc) */
 int ott_activation_f32(ott_ctx* ctx, float* x, size_t count, int act_type, float param0);
 
+/* NanodetPlusDetectionOutputLayer::forward (Tensor/NanodetPlusDetectionOutputLayer.cpp:65-260) for a batch: heads_dev[l] is the
+ * fp32 NCHW output [n][num_class + 4*reg_bins][grid_h[l]][grid_w[l]] of pyramid level l on the device. Per image: best class
+ * logit per cell, sigmoid >= prob_threshold, softmax over the reg_bins distance bins of each box side, box (on the GPU);
+ * sort by score and greedy NMS (on the host, over the proposals that passed). out_host receives, per image, up to max_det
+ * rows {label + 1, score, x, y, width, height} at out_host + img*max_det*6; counts_host[img] the number of detections kept
+ * (which may exceed max_det). The reference decodes image 0 only; scores agree with it to 1-2 ulp and boxes to ~1e-4 pixels
+ * (its -Ofast build and the GPU round expf and the divisions differently). Synchronises the stream. */
+int ott_nanodet_detect(ott_ctx* ctx, const float* const* heads_dev, const int* grid_h, const int* grid_w, const int* strides,
+                       int n_levels, int n, int num_class, int reg_bins, float prob_threshold, float nms_threshold, float* out_host,
+                       int* counts_host, int max_det);
+
 /* The forward for hosts that may not allocate device memory while running. No counterpart in the
  * reference (its CPU path simply calls otter::empty for every temporary).
  * Who needs it: a process whose device memory was divided into fixed pools at start-up and must not grow

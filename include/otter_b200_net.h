@@ -75,6 +75,12 @@ int ott_net_set_conv_params(ott_net* net, const char* layer, const int8_t* w_oih
 int ott_net_forward(ott_net* net, const char* input_blob, const void* in, int in_on_device, int n, int c, int h, int w,
                     int n_out, const char* const* out_blobs, void* const* out_host);
 
+/* Extractor::input + Extractor::extract for a blob whose size is only known after the forward: the [count, 6] result of a
+ * NanodetPlusDetectionOutput layer (Tensor/NanodetPlusDetectionOutputLayer.cpp:65-110; image 0 of the batch, as in the
+ * reference). Up to capacity_rows rows are copied to out_host; *rows is the blob's row count, *cols its row length. */
+int ott_net_forward_rows(ott_net* net, const char* input_blob, const void* in, int in_on_device, int n, int c, int h, int w,
+                         const char* out_blob, float* out_host, int capacity_rows, int* rows, int* cols);
+
 /* Extractor::benchmark_info (Tensor/Net.cpp:811-850, Tensor/Benchmark.cpp:45-102): the same forward with CUDA events
  * around every layer; ms_per_layer[i] (ott_net_layer_count entries) receives layer i's device time in milliseconds.
  * Layers run serialised while profiling. */

@@ -7,6 +7,7 @@
  */
 #include "otter_int8_oracle.h"
 
+#include <float.h>
 #include <math.h>
 #include <stdlib.h>
 #include <string.h>
@@ -238,4 +239,82 @@ void orc_upsample_bilinear(const float* x, int n, int c, int h, int w, int oh, i
             }
         }
     }
+}
+
+/* ---- detection decode of the NanoDet-Plus head ---- */
+typedef struct { float x, y, w, h, prob; int label; int order; } orc_det;
+
+static int orc_det_cmp(const void* a, const void* b) {
+    const orc_det* p = (const orc_det*)a;
+    const orc_det* q = (const orc_det*)b;
+    if (p->prob != q->prob) return p->prob > q->prob ? -1 : 1;
+    return p->order - q->order;
+}
+
+static float orc_intersection(const orc_det* a, const orc_det* b) { /* :192-206 */
+    const float axmax = a->x + a->w, aymax = a->y + a->h, bxmax = b->x + b->w, bymax = b->y + b->h;
+    if (a->x > bxmax || axmax < b->x || a->y > bymax || aymax < b->y) return 0.f;
+    const float iw = fminf(axmax, bxmax) - fmaxf(a->x, b->x);
+    const float ih = fminf(aymax, bymax) - fmaxf(a->y, b->y);
+    return iw * ih;
+}
+
+int orc_nanodet_detect(const float* const* heads, const int* gh, const int* gw, const int* strides, int n_levels, int num_class,
+                       int reg_bins, float prob_threshold, float nms_threshold, float* out, int max_det) {
+    long cells = 0;
+    for (int l = 0; l < n_levels; ++l) cells += (long)gh[l] * gw[l];
+    orc_det* props = (orc_det*)malloc(sizeof(orc_det) * (size_t)(cells > 0 ? cells : 1));
+    int n = 0;
+    for (int l = 0; l < n_levels; ++l) { /* generate_proposals, :111-190 */
+        const long plane = (long)gh[l] * gw[l];
+        const float* pred = heads[l];
+        for (int i = 0; i < gh[l]; ++i)
+            for (int j = 0; j < gw[l]; ++j) {
+                int label = -1;
+                float score = -FLT_MAX;
+                for (int k = 0; k < num_class; ++k) {
+                    const float s = pred[k * plane + (long)i * gw[l] + j];
+                    if (s > score) { label = k; score = s; }
+                }
+                score = 1.0f / (1.0f + expf(-score));
+                if (!(score >= prob_threshold)) continue;
+                float ltrb[4];
+                for (int side = 0; side < 4; ++side) {
+                    float v[64], m = -FLT_MAX, sum = 0.f, dis = 0.f;
+                    for (int b = 0; b < reg_bins; ++b) {
+                        v[b] = pred[(num_class + side * reg_bins + b) * plane + (long)i * gw[l] + j];
+                        m = fmaxf(m, v[b]);
+                    }
+                    for (int b = 0; b < reg_bins; ++b) { v[b] = expf(v[b] - m); sum += v[b]; }
+                    for (int b = 0; b < reg_bins; ++b) { v[b] /= sum; dis += (float)b * v[b]; }
+                    ltrb[side] = dis * (float)strides[l];
+                }
+                const float cx = (float)(j * strides[l]), cy = (float)(i * strides[l]);
+                const float x0 = cx - ltrb[0], y0 = cy - ltrb[1], x1 = cx + ltrb[2], y1 = cy + ltrb[3];
+                orc_det d = {x0, y0, x1 - x0, y1 - y0, score, label, n};
+                props[n++] = d;
+            }
+    }
+    qsort(props, (size_t)n, sizeof(orc_det), orc_det_cmp);
+    int* picked = (int*)malloc(sizeof(int) * (size_t)(n > 0 ? n : 1));
+    int np = 0;
+    for (int i = 0; i < n; ++i) { /* nms_sorted_bboxes, :208-243 */
+        int keep = 1;
+        const float area_i = props[i].w * props[i].h;
+        for (int j = 0; j < np; ++j) {
+            const orc_det* b = &props[picked[j]];
+            const float inter = orc_intersection(&props[i], b);
+            const float uni = area_i + b->w * b->h - inter;
+            if (inter / uni > nms_threshold) keep = 0;
+        }
+        if (keep) picked[np++] = i;
+    }
+    for (int i = 0; i < np && i < max_det; ++i) {
+        const orc_det* r = &props[picked[i]];
+        float* o = out + 6 * i;
+        o[0] = (float)(r->label + 1); o[1] = r->prob; o[2] = r->x; o[3] = r->y; o[4] = r->w; o[5] = r->h;
+    }
+    free(picked);
+    free(props);
+    return np;
 }

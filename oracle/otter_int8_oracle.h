@@ -84,6 +84,16 @@ int orc_conv_int8_forward(const orc_conv_desc* d, const int8_t* w_oihw, const fl
 void orc_upsample_bilinear(const float* x, int n, int c, int h, int w, int oh, int ow, double scale_h, double scale_w,
                            int packed_rule, float* y);
 
+/* NanodetPlusDetectionOutputLayer::forward for one image (Tensor/NanodetPlusDetectionOutputLayer.cpp:65-260): per pyramid
+ * level and grid cell the best of num_class logits, its sigmoid against prob_threshold, a softmax over the reg_bins
+ * distance bins of each box side, the box; then all proposals sorted by score, greedy NMS. heads[l] is fp32
+ * [num_class + 4*reg_bins][gh[l]][gw[l]]. out receives up to max_det rows {label + 1, score, x, y, width, height};
+ * returns the number of detections kept (before truncation to max_det).
+ * Floating point: exp is the C library's expf, as in the reference build; ties in the sort (equal scores) are broken by
+ * proposal order (level, row, column), where the reference's quicksort leaves them unspecified. */
+int orc_nanodet_detect(const float* const* heads, const int* gh, const int* gw, const int* strides, int n_levels, int num_class,
+                       int reg_bins, float prob_threshold, float nms_threshold, float* out, int max_det);
+
 int orc_max_threads(void);
 void orc_set_threads(int n);
 

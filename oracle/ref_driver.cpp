@@ -320,8 +320,8 @@ REF_API int ref_layer_forward(const char* type, const char* options, int n_in, c
         }
         if (rc != 0) { g_err = "layer forward failed"; return rc; }
         otter::Tensor t1 = top.packing(1).contiguous();
-        for (int i = 0; i < 4; ++i) out_shape[i] = (int)t1.size(i);
-        if (out) std::memcpy(out, t1.raw_data(), (size_t)t1.numel() * 4);
+        for (int i = 0; i < 4; ++i) out_shape[i] = i < t1.dim() ? (int)t1.size(i) : 1;  // e.g. [count, 6] from the detection layer
+        if (out && t1.numel() > 0) std::memcpy(out, t1.raw_data(), (size_t)t1.numel() * 4);
         return 0;
     } catch (const std::exception& e) { g_err = e.what(); return -2; } catch (const char* s) { g_err = s; return -3; } catch (...) { g_err = "unknown"; return -4; }
 }

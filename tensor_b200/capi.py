@@ -68,6 +68,7 @@ SIGNATURES = {
     "ott_maxpool_f32_nchw": (i32, [vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp]),
     "ott_upsample_bilinear_f32_nchw": (i32, [vp, vp, i32, i32, i32, i32, i32, i32, C.c_double, C.c_double, i32, vp]),
     "ott_add_f32": (i32, [vp, vp, vp, vp, sz]),
+    "ott_nanodet_detect": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, C.c_float, C.c_float, vp, vp, i32]),
     "ott_activation_f32": (i32, [vp, vp, sz, i32, C.c_float]),
     # include/otter_b200_net.h
     "ott_net_create": (i32, [i32, C.POINTER(vp)]),
@@ -84,6 +85,7 @@ SIGNATURES = {
     "ott_net_layer_info": (i32, [vp, i32, C.c_char_p, i32, C.c_char_p, i32, C.POINTER(i32)]),
     "ott_net_blob_shape": (i32, [vp, C.c_char_p, C.POINTER(i32)]),
     "ott_net_set_conv_params": (i32, [vp, C.c_char_p, vp, vp, vp, vp, i32, vp, i32]),
+    "ott_net_forward_rows": (i32, [vp, C.c_char_p, vp, i32, i32, i32, i32, i32, C.c_char_p, vp, i32, C.POINTER(i32), C.POINTER(i32)]),
     "ott_net_profile": (i32, [vp, C.c_char_p, vp, i32, i32, i32, i32, i32, C.c_char_p, C.POINTER(C.c_float)]),
     "ott_net_forward": (i32, [vp, C.c_char_p, vp, i32, i32, i32, i32, i32, i32, C.POINTER(C.c_char_p), C.POINTER(vp)]),
 }
@@ -363,6 +365,17 @@ class Net:
             outs.append(np.empty(self.blob_shape(b)[:0] + (x.shape[0],) + self.blob_shape(b)[1:], dtype=dt))
         self.forward_raw(input_blob, _np_ptr(x), False, x.shape, out_blobs, [o.ctypes.data for o in outs])
         return outs
+
+    def forward_rows(self, input_blob: str, x: np.ndarray, out_blob: str, capacity_rows: int = 4096):
+        """Host fp32 NCHW in, a 2-D blob of data-dependent length out (the detection layer's [count, 6])."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        out = np.zeros((capacity_rows, 8), np.float32)
+        rows, cols = C.c_int(), C.c_int()
+        n, c, h, w = x.shape
+        self.check(self.lib.ott_net_forward_rows(self.h, input_blob.encode(), _np_ptr(x), 0, n, c, h, w, out_blob.encode(), _np_ptr(out),
+                                                 capacity_rows * 8 // 6, C.byref(rows), C.byref(cols)))
+        k = min(rows.value, capacity_rows * 8 // max(cols.value, 1))
+        return out.reshape(-1)[:k * cols.value].reshape(k, cols.value).copy(), rows.value
 
     def close(self):
         if self.h:

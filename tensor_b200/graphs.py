@@ -66,13 +66,14 @@ def shufflenetv2_layers(height=320, width=320, batch=1, stage_repeats=(4, 8, 4),
 
 
 def nanodet_plus_layers(height=320, width=320, batch=1, neck=96, classes=80, reg_max=7, stage_repeats=(4, 8, 4),
-                        stage_channels=(116, 232, 464), stem=24, act="LRelu"):
+                        stage_channels=(116, 232, 464), stem=24, act="LRelu", detect=False):
     """A NanoDet-Plus-style int8 detector in the wiring of the reference's own graph
     (benchmark/nanodet-plus-m-1.5x_416_int8_fused.otter, layers conv_56 ... conv_110) on the ShuffleNetV2-1.0x backbone:
     three 1x1 reductions to `neck` channels; a Ghost-PAN neck (top-down with bilinear x2 Upsample + Concat, bottom-up with
     depthwise 5x5 stride-2 + 1x1, each merge a Ghost block = two ghost modules [1x1 -> depthwise 3x3, Concat] plus a
     depthwise 5x5 -> 1x1 shortcut, added by ShortCut); an extra stride-64 level; and per level a head of
-    2 x [depthwise 5x5 -> 1x1] and a 1x1 to classes + 4*(reg_max+1) channels. Outputs: head8, head16, head32, head64."""
+    2 x [depthwise 5x5 -> 1x1] and a 1x1 to classes + 4*(reg_max+1) channels. Outputs: head8, head16, head32, head64;
+    with detect=True also the NanodetPlusDetectionOutput layer that decodes them into boxes."""
     L = shufflenetv2_layers(height, width, batch, stage_repeats, stage_channels, stem, last=0, act=act)
     half = neck // 2
     feats = [f"s{si + 2}b{rep - 1}_shuf" for si, rep in enumerate(stage_repeats)]
@@ -115,6 +116,9 @@ def nanodet_plus_layers(height=320, width=320, batch=1, neck=96, classes=80, reg
         L.append(_conv(f"{tag}_dw2", f"{tag}_pw1", neck, 5, 1, 2, 101, act, groups=neck))
         L.append(_conv(f"{tag}_pw2", f"{tag}_dw2", neck, 1, 1, 0, 102, act))
         L.append(_conv(tag, f"{tag}_pw2", classes + 4 * (reg_max + 1), 1, 1, 0, 2))
+    if detect:  # the decode layer at the end of the reference's graph (its last layer, "nanodet")
+        L.append(dict(type="NanodetPlusDetectionOutput", name="nanodet", input=", ".join(NANODET_OUTPUTS), output="nanodet",
+                      prob_threshold="0.400000", nms_threshold="0.500000", stride="8, 16, 32, 64"))
     return L
 
 
@@ -135,7 +139,7 @@ def to_otter_text(layers, name="generated by tensor_b200.graphs") -> str:
         params = [(k, v) for k, v in l.items() if k not in structural]
         if params:
             out.append("    Param {")
-            out += [f"        {k}: {v}" for k, v in params]
+            out += [f'        {k}: "{v}"' if ("," in str(v) or " " in str(v)) else f"        {k}: {v}" for k, v in params]
             out.append("    }")
         out.append("}")
     return "\n".join(out) + "\n"
@@ -238,7 +242,7 @@ def upsample_bilinear_approx(a, oh, ow, scale, packed_rule):
     return (rows[:, :, y0, :] * (1 - fy)[:, None] + rows[:, :, y1, :] * fy[:, None]).astype(np.float32)
 
 
-def walk(layers, x, conv_fn, want=None, on_conv=None, upsample_fn=None):
+def walk(layers, x, conv_fn, want=None, on_conv=None, upsample_fn=None, detect_fn=None):
     """Run the graph on host arrays. conv_fn(name, geometry, input_array) -> output array (fp32 NCHW, or int8 NCHW for
     int8_scale_term > 100). upsample_fn(array, oh, ow, scale, packed_rule) -> array does the bilinear Upsample layers
     (default: the float64 approximation above). Returns {blob name: array} for the names in `want` (default: the last
@@ -271,6 +275,11 @@ def walk(layers, x, conv_fn, want=None, on_conv=None, upsample_fn=None):
             blobs[out] = np.ascontiguousarray(a.reshape(n, g, c // g, h, w).transpose(0, 2, 1, 3, 4).reshape(n, c, h, w))
         elif t == "ShortCut":
             blobs[out] = blobs[ins[0]] + blobs[ins[1]]
+        elif t == "NanodetPlusDetectionOutput":
+            if detect_fn is None:
+                raise ValueError("walk needs detect_fn(heads, strides, prob_threshold, nms_threshold) for the detection layer")
+            strides = [int(v) for v in str(l.get("stride", "8, 16, 32, 64")).split(",")]
+            blobs[out] = detect_fn([blobs[i] for i in ins], strides, float(l.get("prob_threshold", 0.4)), float(l.get("nms_threshold", 0.5)))
         elif t == "Upsample":
             a = blobs[ins[0]]
             if l.get("upsample_mode") != "bilinear" or str(l.get("align_corner", "false")) != "false":

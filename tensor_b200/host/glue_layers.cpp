@@ -3,6 +3,8 @@
 // layer of the same name; forward enqueues one small CUDA kernel (include/otter_b200.h, "fp32 glue layers").
 // Blobs are device fp32 NCHW tensors.
 #include <algorithm>
+#include <cstring>
+#include <sstream>
 
 #include "otter_api.hpp"
 
@@ -265,6 +267,69 @@ public:
     float scale_height = 1.f, scale_width = 1.f;
 };
 
+// Tensor/NanodetPlusDetectionOutputLayer.cpp:22-110. Bottoms: the head blobs of the pyramid levels (fp32 NCHW on the device);
+// top: a HOST tensor [count, 6] {label + 1, score, x, y, width, height} for image 0, as in the reference (which reads only
+// the first image of each blob). Option keys prob_threshold (0.4), nms_threshold (0.5), stride ("8, 16, 32, 64").
+class NanodetPlusDetectionOutputLayer : public Layer {
+public:
+    NanodetPlusDetectionOutputLayer() { one_blob_only = false; support_inplace = false; }
+    int parse_param(LayerOption& option, ParamDict& pd) override {
+        pd.clear();
+        pd.set(0, opt_find_float(option, "prob_threshold", 0.4f));
+        pd.set(1, opt_find_float(option, "nms_threshold", 0.5f));
+        std::vector<int> st;
+        if (opt_check_string(option, "stride")) {
+            std::stringstream ss(option["stride"]);
+            int v;
+            char comma;
+            while (ss >> v) { st.push_back(v); ss >> comma; }
+        }
+        if (st.empty()) st = {8, 16, 32, 64};
+        pd.set(2, tensor(st, ScalarType::Int));
+        return 0;
+    }
+    int compute_output_shape(ParamDict& pd) override {
+        pd.set(OUTPUT_SHAPE_HINT, shape_tensor(6, 0, 0, 0));  // the reference's hint; the real shape is [count, 6]
+        return 0;
+    }
+    int load_param(const ParamDict& pd) override {
+        prob_threshold = pd.get(0, 0.45f);
+        nms_threshold = pd.get(1, 0.5f);
+        Tensor st = pd.get(2, Tensor());
+        strides.assign(st.data_ptr<int>(), st.data_ptr<int>() + st.numel());
+        return 0;
+    }
+    int forward(const std::vector<Tensor>& bottoms, std::vector<Tensor>& tops, const NetOption& opt) const override {
+        const int levels = (int)bottoms.size();
+        if (levels < 1 || levels > (int)strides.size()) return -1;
+        std::vector<const float*> heads;
+        std::vector<int> gh, gw;
+        const int channels = (int)bottoms[0].size(1);
+        const int num_class = 80;  // fixed in the reference (:120)
+        if ((channels - num_class) % 4 != 0 || channels <= num_class) return -1;
+        for (const Tensor& b : bottoms) {
+            if (!is_dev_f32(b) || b.size(1) != channels) return -1;
+            heads.push_back(b.data_ptr<float>());
+            gh.push_back((int)b.size(2));
+            gw.push_back((int)b.size(3));
+        }
+        int cells = 0;
+        for (int l = 0; l < levels; ++l) cells += gh[(size_t)l] * gw[(size_t)l];
+        std::vector<float> rows((size_t)cells * 6);
+        int count = 0;
+        // image 0 only: with n = 1 the decode reads the first image of every (batched) head blob
+        const int rc = ott_nanodet_detect(opt.gpu, heads.data(), gh.data(), gw.data(), strides.data(), levels, 1, num_class, (channels - num_class) / 4,
+                                          prob_threshold, nms_threshold, rows.data(), &count, cells);
+        if (rc != 0) return rc;
+        tops[0] = empty({count, 6}, ScalarType::Float);
+        if (count > 0) std::memcpy(tops[0].raw_data(), rows.data(), (size_t)count * 6 * sizeof(float));
+        return 0;
+    }
+    std::string type() const override { return "NanodetPlusDetectionOutput"; }
+    float prob_threshold = 0.4f, nms_threshold = 0.5f;
+    std::vector<int> strides{8, 16, 32, 64};
+};
+
 // Tensor/ReluLayer.cpp, Tensor/LReluLayer.cpp:28-113 (option "alpha", default 0.1), Tensor/Relu6Layer.cpp
 template <int ACT>
 class ActivationLayerT : public Layer {
@@ -306,6 +371,7 @@ REGISTER_LAYER_CLASS(Crop);
 REGISTER_LAYER_CLASS(ChannelShuffle);
 REGISTER_LAYER_CLASS(ShortCut);
 REGISTER_LAYER_CLASS(Upsample);
+REGISTER_LAYER_CLASS(NanodetPlusDetectionOutput);
 REGISTER_LAYER_CLASS(Relu);
 REGISTER_LAYER_CLASS(LRelu);
 REGISTER_LAYER_CLASS(Relu6);

@@ -234,6 +234,27 @@ int ott_net_forward(ott_net* net, const char* input_blob, const void* in, int in
     return OTT_OK;
 }
 
+int ott_net_forward_rows(ott_net* net, const char* input_blob, const void* in, int in_on_device, int n, int c, int h, int w, const char* out_blob,
+                         float* out_host, int capacity_rows, int* rows, int* cols) {
+    if (!net || !input_blob || !in || !out_blob || !out_host || !rows || !cols || capacity_rows < 0) return OTT_ERR_INVALID;
+    net->error.clear();
+    otter::Extractor ex = net->net.create_extractor();
+    otter::Tensor x = in_on_device ? otter::Tensor::wrap(const_cast<void*>(in), (size_t)n * c * h * w * 4, otter::Device::CUDA, nullptr,
+                                                          {n, c, h, w}, otter::ScalarType::Float)
+                                   : otter::from_blob(const_cast<void*>(in), {n, c, h, w}, otter::ScalarType::Float);
+    int rc = ex.input(input_blob, x);
+    if (rc != 0) return fail(net, rc, "Extractor::input failed");
+    otter::Tensor feat;
+    rc = ex.extract(out_blob, feat, 0);
+    if (rc != 0) return rc;
+    if (feat.dim() != 2 || feat.scalar_type() != otter::ScalarType::Float) return fail(net, OTT_ERR_INVALID, std::string(out_blob) + " is not a 2-D fp32 blob");
+    *rows = (int)feat.size(0);
+    *cols = (int)feat.size(1);
+    const int64_t take = feat.size(0) < capacity_rows ? feat.size(0) : capacity_rows;
+    if (take > 0) std::memcpy(out_host, feat.raw_data(), (size_t)(take * feat.size(1)) * sizeof(float));
+    return OTT_OK;
+}
+
 int ott_net_profile(ott_net* net, const char* input_blob, const void* in, int in_on_device, int n, int c, int h, int w,
                     const char* out_blob, float* ms_per_layer) {
     if (!net || !input_blob || !in || !out_blob || !ms_per_layer) return OTT_ERR_INVALID;

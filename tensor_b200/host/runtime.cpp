@@ -626,7 +626,7 @@ int Extractor::extract(int blob_index, Tensor& feat, int type) {
         blob_tensors_[(size_t)blob_index] = dense;
     }
     const Tensor& dev = blob_tensors_[(size_t)blob_index];
-    if (type != 0) { feat = dev; return 0; }
+    if (type != 0 || dev.device() == Device::CPU) { feat = dev; return 0; }  // (the detection layer's result is a host tensor)
     // plain host layout, like `feat.packing(1)` of the reference (Tensor/Net.cpp:729-731)
     if (dev.layout() == Layout::NCHW) {
         feat = empty(dev.sizes(), dev.scalar_type());

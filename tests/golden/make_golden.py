@@ -134,6 +134,11 @@ def main():
     det = {"input_sha256": np.frombuffer(digest(x, *[params[k]["weight"] for k in sorted(params)], *[params[k]["in_scales"] for k in sorted(params)]).encode(), dtype=np.uint8)}
     for b in blobs:
         det[b] = got[b]
+    # the reference's own decode of those heads (NanodetPlusDetectionOutput layer): rows {label + 1, score, x, y, w, h}
+    from test_graph_oracle import ref_layer
+    from tensor_b200 import graphs
+    det["detections"] = ref_layer("NanodetPlusDetectionOutput", "prob_threshold=0.4;nms_threshold=0.5;stride=8, 16, 32, 64",
+                                  [got[k] for k in graphs.NANODET_OUTPUTS], packed=0).reshape(-1, 6)
     np.savez_compressed(GOLDEN_DIR / "net_nanodet_wide_small.npz", **det)
     for f in ("conv_int8_small.npz", "epilogue_adversarial.npz", "net_shufflenet_wide_small.npz", "net_nanodet_wide_small.npz"):
         print(f, (GOLDEN_DIR / f).stat().st_size, "bytes")

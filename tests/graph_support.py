@@ -42,6 +42,35 @@ def oracle_upsample(a, oh, ow, scale, packed_rule):
     return y
 
 
+def oracle_detect(heads, strides, prob_threshold=0.4, nms_threshold=0.5, image=0, num_class=80):
+    """The C checker's detection decode of one image: rows {label + 1, score, x, y, width, height}."""
+    import ctypes as C
+    from support import load_port
+    lib = load_port()
+    lib.orc_nanodet_detect.restype = C.c_int
+    lib.orc_nanodet_detect.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_float, C.c_void_p,
+                                       C.c_int]
+    one = [np.ascontiguousarray(h[image], dtype=np.float32) for h in heads]
+    ptrs = (C.c_void_p * len(one))(*[h.ctypes.data for h in one])
+    gh = np.array([h.shape[1] for h in one], np.int32)
+    gw = np.array([h.shape[2] for h in one], np.int32)
+    st = np.array(strides, np.int32)
+    cells = int((gh * gw).sum())
+    out = np.zeros((cells, 6), np.float32)
+    n = lib.orc_nanodet_detect(ptrs, gh.ctypes.data, gw.ctypes.data, st.ctypes.data, len(one), num_class, (one[0].shape[0] - num_class) // 4,
+                               prob_threshold, nms_threshold, out.ctypes.data, cells)
+    return out[:n].copy()
+
+
+def assert_same_detections(got, want, score_tol=3e-7, box_tol=3e-4):
+    """Detection rows agree up to the documented floating-point tolerance of the decode (expf and divisions round differently
+    in the reference's -Ofast build, the C checker and the GPU): same count, labels and order, scores and boxes close."""
+    assert got.shape == want.shape, (got.shape, want.shape)
+    assert np.array_equal(got[:, 0], want[:, 0])
+    assert np.abs(got[:, 1] - want[:, 1]).max(initial=0) <= score_tol
+    assert np.abs(got[:, 2:] - want[:, 2:]).max(initial=0) <= box_tol
+
+
 def oracle_conv_for_calibration(name, g, p, a, as_float):
     term = g["term"] - 100 if (as_float and g["term"] > 100) else g["term"]
     return run_port(_case(name, g, p, a, term), 0, want_acc=False)["y"]

@@ -227,6 +227,61 @@ def test_model_from_otter_and_ncnn_weight_file(tmp_path):
         net.close()
 
 
+def test_detection_decode_kernel_batch():
+    """ott_nanodet_detect on a batch of random head blobs against the C checker, image by image (tolerance: see
+    graph_support.assert_same_detections)."""
+    import ctypes as C
+    from graph_support import assert_same_detections, oracle_detect
+    from tensor_b200 import Context
+    rng = np.random.default_rng(77)
+    n, grids, strides = 3, (40, 20, 10, 5), [8, 16, 32, 64]
+    heads = [(rng.normal(size=(n, 112, g, g)) * 2.0 - 2.5).astype(np.float32) for g in grids]
+    with Context(0) as ctx:
+        dev = []
+        for hd in heads:
+            p = ctx.malloc(hd.nbytes)
+            ctx.check(ctx.lib.ott_memcpy_h2d(ctx.h, C.c_void_p(p), hd.ctypes.data, hd.nbytes))
+            dev.append(p)
+        ptrs = (C.c_void_p * 4)(*dev)
+        gh = np.array(grids, np.int32)
+        st = np.array(strides, np.int32)
+        max_det = 2125
+        out = np.zeros((n, max_det, 6), np.float32)
+        counts = np.zeros(n, np.int32)
+        ctx.check(ctx.lib.ott_nanodet_detect(ctx.h, ptrs, gh.ctypes.data, gh.ctypes.data, st.ctypes.data, 4, n, 80, 8, 0.4, 0.5,
+                                             out.ctypes.data, counts.ctypes.data, max_det))
+        for img in range(n):
+            want = oracle_detect(heads, strides, image=img)
+            assert counts[img] == want.shape[0] and counts[img] > 10
+            assert_same_detections(out[img, :counts[img]], want)
+        # max_det smaller than the number of detections: the count is still reported, the rows are truncated
+        small = np.zeros((n, 5, 6), np.float32)
+        ctx.check(ctx.lib.ott_nanodet_detect(ctx.h, ptrs, gh.ctypes.data, gh.ctypes.data, st.ctypes.data, 4, n, 80, 8, 0.4, 0.5,
+                                             small.ctypes.data, counts.ctypes.data, 5))
+        assert np.array_equal(small[0], out[0, :5]) and counts[0] > 5
+        for p in dev:
+            ctx.free(p)
+
+
+def test_detector_with_decode_layer_from_files(tmp_path):
+    """The whole detector including the NanodetPlusDetectionOutput layer, graph and weights from files; the detections against
+    the reference's own decode of the reference's own head blobs (frozen)."""
+    from graph_support import assert_same_detections, wide_nanodet_case, write_ncnn_bin
+    from support import GOLDEN_DIR
+    from tensor_b200 import Net
+    gold = np.load(GOLDEN_DIR / "net_nanodet_wide_small.npz")
+    L, params, x, _ = wide_nanodet_case()
+    L = L + graphs.nanodet_plus_layers(64, 64, detect=True)[-1:]
+    (tmp_path / "m.otter").write_text(graphs.to_otter_text(L))
+    write_ncnn_bin(L, params, tmp_path / "m.bin")
+    net = Net(0)
+    net.load_model(tmp_path / "m.otter", tmp_path / "m.bin", "ncnn")
+    rows, count = net.forward_rows("data", x, "nanodet")
+    assert count == gold["detections"].shape[0] and count >= 1
+    assert_same_detections(rows, gold["detections"])
+    net.close()
+
+
 def test_chunked_host_forward_equals_plain_forward():
     """Large host batches run in chunks with overlapped copies; every image must come out as in a plain forward."""
     from graph_support import build_net, oracle_conv_for_calibration

@@ -170,3 +170,26 @@ def test_reference_reads_our_ncnn_weight_file(tmp_path):
     ref = reference_net_forward(L, params, x, blobs, weight_file=path)
     for b in blobs:
         assert np.array_equal(ref[b].view(np.int32), DET_GOLD[b].view(np.int32)), b
+
+
+@pytest.mark.skipif(not have_ref(), reason="oracle/_ref/libotter_ref.so not built")
+@pytest.mark.parametrize("seed,shift", [(3, -2.5), (4, -4.0), (5, -1.0)])
+def test_checker_detection_decode_against_reference_layer(seed, shift):
+    """NanodetPlusDetectionOutput: the restatement against the reference's own layer on random head blobs. Not bit-exact by
+    nature (see assert_same_detections); counts, labels and order must agree."""
+    from graph_support import assert_same_detections, oracle_detect
+    rng = np.random.default_rng(seed)
+    heads = [(rng.normal(size=(1, 112, g, g)) * 2.0 + shift).astype(np.float32) for g in (40, 20, 10, 5)]
+    want = ref_layer("NanodetPlusDetectionOutput", "prob_threshold=0.4;nms_threshold=0.5;stride=8, 16, 32, 64", heads, packed=0).reshape(-1, 6)
+    got = oracle_detect(heads, [8, 16, 32, 64])
+    assert want.shape[0] > 10
+    assert_same_detections(got, want)
+
+
+def test_detections_of_the_frozen_reference_heads():
+    """The decode of the head blobs frozen from the reference's own Net, against the reference's own decode of them."""
+    from graph_support import assert_same_detections, oracle_detect
+    heads = [DET_GOLD[k] for k in graphs.NANODET_OUTPUTS]
+    got = oracle_detect(heads, [8, 16, 32, 64])
+    assert got.shape[0] >= 1
+    assert_same_detections(got, DET_GOLD["detections"])
