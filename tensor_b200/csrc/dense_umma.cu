@@ -7,10 +7,13 @@
 //
 //   D[128 pixels, BN out-channels] (s32, in TMEM)  +=  A[128 pixels, 32..128 in-channels] * B[BN, same]^T
 //
-// * A tiles come straight from the NHWC int8 activations with 4-D TMA boxes {channels, TW, TH, 1}; one box
-//   per filter tap, shifted by the tap offset; out-of-image rows/columns are zero-filled by TMA, which is
-//   the reference's constant_pad (Tensor/Padding.cpp:22-36). 1x1 convolutions view the activations as a
-//   flat [pixels, channels] matrix so tiles never straddle anything.
+// * A tiles come straight from the NHWC int8 activations with 4-D TMA boxes {channels, TW, TH, 1};
+//   out-of-image rows/columns are zero-filled by TMA, which is the reference's constant_pad
+//   (Tensor/Padding.cpp:22-36). 1x1 convolutions view the activations as a flat [pixels, channels] matrix so
+//   tiles never straddle anything. k x k convolutions load, per pixel tile of 8 x 16 and channel block, ONE box
+//   that holds the tile and its halo; filter tap (ky, kx) is an MMA whose A descriptor starts (ky, kx) pixels
+//   into that box and steps one halo row per 8-row group (the swizzle is a function of the shared-memory
+//   address, so shifted views read what TMA wrote). Dilated layers load one shifted box per tap instead.
 // * B (the layer's weights for this CTA's BN output channels, all taps) is loaded once per CTA and stays in
 //   shared memory while the CTA walks over its pixel tiles (persistent, weight-stationary).
 // * tcgen05.mma.kind::i8 accumulates exact s32 in TMEM; two accumulators are double-buffered so the
