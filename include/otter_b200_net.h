@@ -75,6 +75,19 @@ int ott_net_set_conv_params(ott_net* net, const char* layer, const int8_t* w_oih
 int ott_net_forward(ott_net* net, const char* input_blob, const void* in, int in_on_device, int n, int c, int h, int w,
                     int n_out, const char* const* out_blobs, void* const* out_host);
 
+/* A whole forward frozen into a CUDA graph (see ott_graph_* in otter_b200.h): Extractor::input(input_blob, the device
+ * tensor [n,c,h,w] at in_dev) + Extractor::extract of every blob in out_blobs, captured once. ott_net_graph_launch replays
+ * it on the Net's stream (asynchronous); the caller refills in_dev between launches and reads the outputs from the device
+ * pointers ott_net_graph_output reports (dense fp32 NCHW, or int8 NHWC for a requantizing layer's blob; valid until
+ * ott_net_graph_destroy). One warm-up forward runs first so that nothing has to be allocated inside the capture. Layers
+ * that synchronise (NanodetPlusDetectionOutput) cannot be captured. Results are bit-identical to ott_net_forward. */
+typedef struct ott_net_graph ott_net_graph;
+int ott_net_capture(ott_net* net, const char* input_blob, const void* in_dev, int n, int c, int h, int w, int n_out,
+                    const char* const* out_blobs, ott_net_graph** out);
+int ott_net_graph_launch(ott_net_graph* graph);
+int ott_net_graph_output(ott_net_graph* graph, int index, void** dev_ptr, int shape[4]);
+int ott_net_graph_destroy(ott_net_graph* graph);
+
 /* Extractor::input + Extractor::extract for a blob whose size is only known after the forward: the [count, 6] result of a
  * NanodetPlusDetectionOutput layer (Tensor/NanodetPlusDetectionOutputLayer.cpp:65-110; image 0 of the batch, as in the
  * reference). Up to capacity_rows rows are copied to out_host; *rows is the blob's row count, *cols its row length. */

@@ -68,6 +68,11 @@ SIGNATURES = {
     "ott_maxpool_f32_nchw": (i32, [vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp]),
     "ott_upsample_bilinear_f32_nchw": (i32, [vp, vp, i32, i32, i32, i32, i32, i32, C.c_double, C.c_double, i32, vp]),
     "ott_add_f32": (i32, [vp, vp, vp, vp, sz]),
+    "ott_graph_capture_begin": (i32, [vp]),
+    "ott_graph_capture_end": (i32, [vp, C.POINTER(vp)]),
+    "ott_graph_seal": (i32, [vp, vp]),
+    "ott_graph_launch": (i32, [vp, vp]),
+    "ott_graph_destroy": (i32, [vp, vp]),
     "ott_nanodet_detect": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, C.c_float, C.c_float, vp, vp, i32]),
     "ott_activation_f32": (i32, [vp, vp, sz, i32, C.c_float]),
     # include/otter_b200_net.h
@@ -85,6 +90,10 @@ SIGNATURES = {
     "ott_net_layer_info": (i32, [vp, i32, C.c_char_p, i32, C.c_char_p, i32, C.POINTER(i32)]),
     "ott_net_blob_shape": (i32, [vp, C.c_char_p, C.POINTER(i32)]),
     "ott_net_set_conv_params": (i32, [vp, C.c_char_p, vp, vp, vp, vp, i32, vp, i32]),
+    "ott_net_capture": (i32, [vp, C.c_char_p, vp, i32, i32, i32, i32, i32, C.POINTER(C.c_char_p), C.POINTER(vp)]),
+    "ott_net_graph_launch": (i32, [vp]),
+    "ott_net_graph_output": (i32, [vp, i32, C.POINTER(vp), C.POINTER(i32)]),
+    "ott_net_graph_destroy": (i32, [vp]),
     "ott_net_forward_rows": (i32, [vp, C.c_char_p, vp, i32, i32, i32, i32, i32, C.c_char_p, vp, i32, C.POINTER(i32), C.POINTER(i32)]),
     "ott_net_profile": (i32, [vp, C.c_char_p, vp, i32, i32, i32, i32, i32, C.c_char_p, C.POINTER(C.c_float)]),
     "ott_net_forward": (i32, [vp, C.c_char_p, vp, i32, i32, i32, i32, i32, i32, C.POINTER(C.c_char_p), C.POINTER(vp)]),
@@ -258,6 +267,28 @@ class ConvInt8:
             self.h = None
 
 
+class NetGraph:
+    """A captured forward (ott_net_capture): launch() replays it on the Net's stream."""
+
+    def __init__(self, net, handle, n_out):
+        self.net, self.h, self.n_out = net, handle, n_out
+
+    def launch(self):
+        self.net.check(self.net.lib.ott_net_graph_launch(self.h))
+
+    def output(self, index: int):
+        """(device pointer, shape) of output `index`."""
+        p = C.c_void_p()
+        shape = (C.c_int * 4)()
+        self.net.check(self.net.lib.ott_net_graph_output(self.h, index, C.byref(p), shape))
+        return p.value, tuple(shape)
+
+    def close(self):
+        if self.h:
+            self.net.lib.ott_net_graph_destroy(self.h)
+            self.h = None
+
+
 def parse_otter_text(text: str):
     """The library's .otter reader on a string: list of option dictionaries (values as strings), in file order."""
     lib = library()
@@ -365,6 +396,14 @@ class Net:
             outs.append(np.empty(self.blob_shape(b)[:0] + (x.shape[0],) + self.blob_shape(b)[1:], dtype=dt))
         self.forward_raw(input_blob, _np_ptr(x), False, x.shape, out_blobs, [o.ctypes.data for o in outs])
         return outs
+
+    def capture(self, input_blob: str, in_dev_ptr, shape, out_blobs):
+        """Freeze one forward (device input at in_dev_ptr, device outputs) into a CUDA graph; returns a NetGraph."""
+        n, c, h, w = shape
+        names = (C.c_char_p * len(out_blobs))(*[b.encode() for b in out_blobs])
+        g = C.c_void_p()
+        self.check(self.lib.ott_net_capture(self.h, input_blob.encode(), in_dev_ptr, n, c, h, w, len(out_blobs), names, C.byref(g)))
+        return NetGraph(self, g, len(out_blobs))
 
     def forward_rows(self, input_blob: str, x: np.ndarray, out_blob: str, capacity_rows: int = 4096):
         """Host fp32 NCHW in, a 2-D blob of data-dependent length out (the detection layer's [count, 6])."""

@@ -199,6 +199,86 @@ int ott_memcpy_overlapped(ott_ctx* ctx, int direction, void* dst, const void* sr
     return OTT_OK;
 }
 
+// ---- CUDA graphs: a sequence of calls on the context's stream frozen into one launch ----
+struct ott_graph {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    std::vector<void*> pinned;  // allocator blocks the captured kernels address
+    uint64_t launches = 0;      // kernels inside
+};
+
+int ott_graph_capture_begin(ott_ctx* ctx) {
+    if (!ctx) return OTT_ERR_INVALID;
+    cudaSetDevice(ctx->device);
+    if (ctx->capture_launches0 != UINT64_MAX) return ctx->fail(OTT_ERR_INVALID, "a capture is already open on this context");
+    ctx->alloc->begin_log();
+    // relaxed mode: the calls in between may use cudaMalloc-class routines (a cache miss in the allocator) without
+    // invalidating the capture
+    cudaError_t e = cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeRelaxed);
+    if (e != cudaSuccess) {
+        (void)ctx->alloc->take_logged();
+        return ctx->fail(OTT_ERR_CUDA, "cudaStreamBeginCapture: %s", cudaGetErrorString(e));
+    }
+    ctx->capture_launches0 = ctx->launches;
+    return OTT_OK;
+}
+
+int ott_graph_capture_end(ott_ctx* ctx, ott_graph** out) {
+    if (!ctx || ctx->capture_launches0 == UINT64_MAX) return OTT_ERR_INVALID;
+    cudaSetDevice(ctx->device);
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+    const uint64_t launches = ctx->launches - ctx->capture_launches0;
+    ctx->capture_launches0 = UINT64_MAX;
+    if (e != cudaSuccess || !graph || !out) {
+        if (graph) cudaGraphDestroy(graph);
+        ctx->alloc->give_back(ctx->alloc->take_logged());
+        if (!out && e == cudaSuccess) return OTT_OK;  // capture abandoned by the caller
+        return ctx->fail(OTT_ERR_CUDA, "cudaStreamEndCapture: %s", cudaGetErrorString(e));
+    }
+    ott_graph* g = new (std::nothrow) ott_graph();
+    if (!g) { cudaGraphDestroy(graph); ctx->alloc->give_back(ctx->alloc->take_logged()); return OTT_ERR_ALLOC; }
+    g->graph = graph;
+    g->launches = launches;
+    e = cudaGraphInstantiate(&g->exec, graph, 0);
+    if (e != cudaSuccess) {
+        cudaGraphDestroy(graph);
+        delete g;
+        ctx->alloc->give_back(ctx->alloc->take_logged());
+        return ctx->fail(OTT_ERR_CUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(e));
+    }
+    *out = g;
+    return OTT_OK;
+}
+
+int ott_graph_seal(ott_ctx* ctx, ott_graph* g) {
+    if (!ctx || !g) return OTT_ERR_INVALID;
+    const std::vector<void*> taken = ctx->alloc->take_logged();
+    g->pinned.insert(g->pinned.end(), taken.begin(), taken.end());
+    return OTT_OK;
+}
+
+int ott_graph_launch(ott_ctx* ctx, ott_graph* g) {
+    if (!ctx || !g || !g->exec) return OTT_ERR_INVALID;
+    cudaSetDevice(ctx->device);
+    OTT_CUDA_CHECK(ctx, cudaGraphLaunch(g->exec, ctx->stream));
+    ctx->launches += g->launches;
+    return OTT_OK;
+}
+
+int ott_graph_destroy(ott_ctx* ctx, ott_graph* g) {
+    if (!g) return OTT_OK;
+    if (ctx) {
+        cudaSetDevice(ctx->device);
+        cudaStreamSynchronize(ctx->stream);  // no replay may still be addressing the blocks
+        ctx->alloc->give_back(g->pinned);
+    }
+    if (g->exec) cudaGraphExecDestroy(g->exec);
+    if (g->graph) cudaGraphDestroy(g->graph);
+    delete g;
+    return OTT_OK;
+}
+
 int ott_memset(ott_ctx* ctx, void* dst, int value, size_t bytes) {
     if (!ctx) return OTT_ERR_INVALID;
     cudaSetDevice(ctx->device);

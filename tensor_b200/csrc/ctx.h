@@ -11,6 +11,7 @@
 #include <mutex>
 #include <string>
 #include <unordered_map>
+#include <unordered_set>
 #include <vector>
 
 #include "../../include/otter_b200.h"
@@ -39,6 +40,7 @@ public:
             bytes_cached_ -= sz;
             bytes_in_use_ += sz;
             ++n_cache_hits_;
+            if (logging_) log_.insert(*out);
             return cudaSuccess;
         }
         void* p = nullptr;
@@ -54,7 +56,42 @@ public:
         sizes_[p] = sz;
         bytes_in_use_ += sz;
         *out = p;
+        if (logging_) log_.insert(p);
         return cudaSuccess;
+    }
+
+    // For work that is frozen into a CUDA graph: the graph keeps addressing the blocks that were handed out while it was
+    // captured, so those blocks must not go to anybody else (nor back to the driver) while the graph lives. begin_log starts
+    // recording every block handed out; take_logged ends it and takes the recorded blocks that are free again out of the
+    // cache (blocks still in use stay with their owner); give_back returns them to the cache.
+    void begin_log() {
+        std::lock_guard<std::mutex> g(mu_);
+        logging_ = true;
+        log_.clear();
+    }
+    std::vector<void*> take_logged() {
+        std::lock_guard<std::mutex> g(mu_);
+        logging_ = false;
+        std::vector<void*> taken;
+        for (auto& kv : available_) {
+            auto& v = kv.second;
+            for (size_t i = 0; i < v.size();) {
+                if (log_.count(v[i])) {
+                    taken.push_back(v[i]);
+                    bytes_cached_ -= kv.first;
+                    bytes_in_use_ += kv.first;
+                    v[i] = v.back();
+                    v.pop_back();
+                } else {
+                    ++i;
+                }
+            }
+        }
+        log_.clear();
+        return taken;
+    }
+    void give_back(const std::vector<void*>& blocks) {
+        for (void* p : blocks) free(p);
     }
 
     bool free(void* p) {
@@ -97,6 +134,8 @@ private:
     std::mutex mu_;
     std::map<size_t, std::vector<void*>> available_;
     std::unordered_map<void*, size_t> sizes_;
+    bool logging_ = false;
+    std::unordered_set<void*> log_;
     uint64_t n_device_mallocs_ = 0, n_cache_hits_ = 0, bytes_in_use_ = 0, bytes_cached_ = 0;
 };
 
@@ -108,6 +147,7 @@ struct ott_ctx {
     DeviceCachingAllocator* alloc = nullptr;
     std::string last_error;
     uint64_t launches = 0;
+    uint64_t capture_launches0 = UINT64_MAX;  // value of `launches` when the open graph capture began; UINT64_MAX: none open
     uint32_t* status_dev = nullptr;   // default status word the kernels report into
     uint32_t* status_host = nullptr;  // pinned mirror
     // pinned staging buffers of the *_host entry points

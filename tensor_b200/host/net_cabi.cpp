@@ -234,6 +234,80 @@ int ott_net_forward(ott_net* net, const char* input_blob, const void* in, int in
     return OTT_OK;
 }
 
+struct ott_net_graph {
+    ott_net* net = nullptr;
+    ott_graph* graph = nullptr;
+    std::vector<otter::Tensor> outputs;  // device tensors the replays write
+};
+
+int ott_net_capture(ott_net* net, const char* input_blob, const void* in_dev, int n, int c, int h, int w, int n_out,
+                    const char* const* out_blobs, ott_net_graph** out) {
+    if (!net || !input_blob || !in_dev || n_out < 1 || !out_blobs || !out) return OTT_ERR_INVALID;
+    net->error.clear();
+    ott_ctx* ctx = net->net.context();
+    if (!ctx) return fail(net, OTT_ERR_INVALID, "capture before compile");
+    const otter::Tensor x = otter::Tensor::wrap(const_cast<void*>(in_dev), (size_t)n * c * h * w * 4, otter::Device::CUDA, nullptr, {n, c, h, w},
+                                                otter::ScalarType::Float);
+    auto run = [&](std::vector<otter::Tensor>& outs) -> int {
+        otter::Extractor ex = net->net.create_extractor();
+        for (int i = 0; i < n_out; ++i)
+            if (ex.keep(out_blobs[i]) != 0) return fail(net, OTT_ERR_INVALID, std::string("unknown blob ") + out_blobs[i]);
+        int rc = ex.input(input_blob, x);
+        if (rc != 0) return fail(net, rc, "Extractor::input failed");
+        outs.assign((size_t)n_out, otter::Tensor());
+        for (int i = 0; i < n_out && rc == 0; ++i) rc = ex.extract(out_blobs[i], outs[(size_t)i], 1);
+        for (int i = 0; i < n_out && rc == 0; ++i)
+            if (outs[(size_t)i].device() != otter::Device::CUDA) rc = fail(net, OTT_ERR_UNSUPPORTED, std::string(out_blobs[i]) + " is produced on the host and cannot be captured");
+        return rc;
+    };
+    std::vector<otter::Tensor> outs;
+    int rc = run(outs);  // warm-up: every buffer size is in the allocator's cache afterwards, one-time kernel set-up is done
+    if (rc == 0) rc = ott_sync(ctx);
+    outs.clear();
+    if (rc != 0) return rc;
+    rc = ott_graph_capture_begin(ctx);
+    if (rc != 0) return rc;
+    rc = run(outs);
+    ott_graph* g = nullptr;
+    if (rc != 0) {
+        ott_graph_capture_end(ctx, nullptr);
+        return rc;
+    }
+    rc = ott_graph_capture_end(ctx, &g);
+    if (rc != 0) return rc;
+    // the Extractor inside run() is gone: its temporaries are back in the cache and can be set aside for the graph
+    ott_graph_seal(ctx, g);
+    ott_net_graph* ng = new (std::nothrow) ott_net_graph();
+    if (!ng) { ott_graph_destroy(ctx, g); return OTT_ERR_ALLOC; }
+    ng->net = net;
+    ng->graph = g;
+    ng->outputs = std::move(outs);
+    *out = ng;
+    return OTT_OK;
+}
+
+int ott_net_graph_launch(ott_net_graph* graph) {
+    if (!graph) return OTT_ERR_INVALID;
+    return ott_graph_launch(graph->net->net.context(), graph->graph);
+}
+
+int ott_net_graph_output(ott_net_graph* graph, int index, void** dev_ptr, int shape[4]) {
+    if (!graph || index < 0 || index >= (int)graph->outputs.size() || !dev_ptr) return OTT_ERR_INVALID;
+    const otter::Tensor& t = graph->outputs[(size_t)index];
+    *dev_ptr = t.raw_data();
+    if (shape)
+        for (int i = 0; i < 4; ++i) shape[i] = i < t.dim() ? (int)t.size(i) : 1;
+    return OTT_OK;
+}
+
+int ott_net_graph_destroy(ott_net_graph* graph) {
+    if (!graph) return OTT_OK;
+    ott_graph_destroy(graph->net->net.context(), graph->graph);  // synchronises, then releases the temporaries
+    graph->outputs.clear();
+    delete graph;
+    return OTT_OK;
+}
+
 int ott_net_forward_rows(ott_net* net, const char* input_blob, const void* in, int in_on_device, int n, int c, int h, int w, const char* out_blob,
                          float* out_host, int capacity_rows, int* rows, int* cols) {
     if (!net || !input_blob || !in || !out_blob || !out_host || !rows || !cols || capacity_rows < 0) return OTT_ERR_INVALID;

@@ -282,6 +282,59 @@ def test_detector_with_decode_layer_from_files(tmp_path):
     net.close()
 
 
+def test_captured_forward_replays_bit_exact():
+    """ott_net_capture: one forward frozen into a CUDA graph. Replays must give the bytes of the ordinary forward for whatever
+    the input buffer holds at launch time, also after other forwards have gone through the same allocator in between."""
+    import ctypes as C
+    from graph_support import build_net, oracle_conv_for_calibration
+    L = graphs.shufflenetv2_layers(64, 64, batch=4)
+    params = graphs.make_params(L, seed=5)
+    rng = np.random.default_rng(6)
+    x1 = rng.uniform(0, 1, size=(4, 3, 64, 64)).astype(np.float32)
+    x2 = rng.uniform(0, 1, size=(4, 3, 64, 64)).astype(np.float32)
+    graphs.calibrate(L, params, x1[:1], oracle_conv_for_calibration)
+    net = build_net(L, params)
+    ctx = net.context()
+    blobs = ["conv5", "s2b1_shuf", "s3b0_l_dw"]  # a dense fp32 blob, a plane table (materialised), an int8 blob
+    dtypes = [np.float32, np.float32, np.int8]
+    want1 = net.forward("data", x1, blobs, dtypes=dtypes)
+    want2 = net.forward("data", x2, blobs, dtypes=dtypes)
+    din = ctx.malloc(x1.nbytes)
+    graph = net.capture("data", C.c_void_p(din), x1.shape, blobs)
+
+    def replay(x):
+        ctx.check(ctx.lib.ott_memcpy_h2d(ctx.h, C.c_void_p(din), x.ctypes.data, x.nbytes))
+        before = ctx.launch_count()
+        graph.launch()
+        assert ctx.launch_count() - before > 50  # the kernels inside the graph are counted
+        outs = []
+        for i, dt in enumerate(dtypes):
+            ptr, shape = graph.output(i)
+            if dt == np.int8:  # int8 blobs are NHWC with the channel stride padded to 16
+                n, c, h, w = shape
+                raw = np.empty((n, h, w, (c + 15) // 16 * 16), np.int8)
+                ctx.check(ctx.lib.ott_memcpy_d2h(ctx.h, raw.ctypes.data, C.c_void_p(ptr), raw.nbytes))
+                ctx.sync()
+                outs.append(np.ascontiguousarray(raw[..., :c].transpose(0, 3, 1, 2)))
+            else:
+                a = np.empty(shape, np.float32)
+                ctx.check(ctx.lib.ott_memcpy_d2h(ctx.h, a.ctypes.data, C.c_void_p(ptr), a.nbytes))
+                ctx.sync()
+                outs.append(a)
+        return outs
+
+    for x, want in ((x1, want1), (x2, want2)):
+        for g, w_ in zip(replay(x), want):
+            assert np.array_equal(bits(g), bits(w_))
+    # other work through the same allocator must not get the graph's buffers
+    net.forward("data", np.concatenate([x2, x1]), ["conv5"])
+    for g, w_ in zip(replay(x1), want1):
+        assert np.array_equal(bits(g), bits(w_))
+    graph.close()
+    ctx.free(din)
+    net.close()
+
+
 def test_chunked_host_forward_equals_plain_forward():
     """Large host batches run in chunks with overlapped copies; every image must come out as in a plain forward."""
     from graph_support import build_net, oracle_conv_for_calibration
