@@ -1,16 +1,20 @@
 #!/usr/bin/env python
 """Benchmark of the int8 convolution path on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference] [--no-graph]
 
-A step is one pass of the hot path (quantize -> int8 convolution -> fused requantize/dequantize) over
-one batch of seeded synthetic activations that are already resident in HBM. The batch is larger than
-the 126 MB L2, so every step streams from HBM (no flush needed). Times are CUDA events recorded on
-the stream the kernels are launched on; with several GPUs (one process per GPU, torchrun) each rank
-runs the same per-GPU batch on its own GPU (weak scaling, no collective on the data path) and the step
-time is the maximum over ranks.
+Default workload: the ShuffleNetV2-1.0x int8 backbone on 256 images of 3x320x320 per GPU (metric
+shufflenetv2_int8_images_per_s); `--workload nanodet_plus_320` is the detector (2048 images per step, sharded over the GPUs);
+the other names are single layers (metric int8_conv_tops). A step is one pass of the path (quantize -> int8 convolution ->
+fused requantize/dequantize, layer after layer for the graphs) over seeded synthetic activations that are already resident
+in HBM. The batch is larger than the 126 MB L2, so every step streams from HBM (no flush needed). Times are CUDA events
+recorded on the stream the kernels are launched on; with several GPUs (one process per GPU, torchrun) each rank runs its
+own shard on its own GPU (no collective on the data path) and the step time is the maximum over ranks.
 
-One JSON line is printed by rank 0; see DESIGN.md for the meaning of each key.
+Rank 0 prints one JSON line. value: whole-job throughput, device-resident (graph workloads replay a captured CUDA graph of
+the forward); e2e: the same through the public call with pinned host buffers, copies included; roofline: the dominant
+kernel (or layer kind) against the measured HBM / int8 tensor peak; cpu_baseline: the reference's CPU path on this box's
+host cores; clocks: SM clock and throttle reasons sampled during the timed region; gpu_launches: kernels in the timed region.
 `--impl reference` times the reference's own CPU implementation (oracle/_ref, or the C restatement
 when the compiled reference is absent) on the host cores, on a bounded sample of the same workload.
 """
