@@ -43,6 +43,7 @@ quantize_nchw_to_nhwc_kernel(const __grid_constant__ PlaneGather G, int8_t* __re
     const int p = flat ? (int)(gp - (long)img * hw) : (int)gp;
 #pragma unroll
     for (int pass = 0; pass < QT_C / 32; ++pass) {
+        if (c0 + 32 * pass >= cpad) break;  // narrow tensors: nothing of this half of the tile is ever stored
         const int cword = cq + 8 * pass;
         uint32_t cw[4];  // channel i: its 4 pixels packed
         float4 v[4];
