@@ -27,7 +27,8 @@ ott_ctx* ott_net_context(ott_net* net); /* valid after ott_net_compile */
  * "use_packing_layout", "int8_rounding" (OTT_ROUND_*), and the two switches this library adds, both on by default:
  * "fuse_first_layer_pool" (first convolution + 3x3 stride-2 max-pool as one kernel) and "int8_handover" (a convolution
  * whose fp32 result is read only by another quantized convolution writes that layer's int8 input directly). Both
- * leave every extracted blob bit-identical. Unknown key: OTT_ERR_INVALID. */
+ * leave every extracted blob bit-identical. "host_chunk" (default 64): images per chunk when ott_net_forward pipelines a host
+ * batch (upload, kernels and download of different chunks overlap). Unknown key: OTT_ERR_INVALID. */
 int ott_net_set_option(ott_net* net, const char* key, int value);
 
 /* Net::addLayer (Tensor/Net.cpp:40-80). `options` is one LayerOption as "key=value;key=value;...", with the

@@ -5,9 +5,28 @@
 #include "../../include/otter_b200_net.h"
 #include "otter_api.hpp"
 
+struct ott_net;
+struct ott_net_graph {
+    ott_net* net = nullptr;
+    ott_graph* graph = nullptr;
+    std::vector<otter::Tensor> outputs;  // device tensors the replays write
+};
+
+// What ott_net_forward keeps between calls with host buffers of one shape: the device input buffer and one captured forward
+// per chunk of the batch (the chunks differ in where they read the input).
+struct HostPipeline {
+    std::string key;
+    void* dev_in = nullptr;
+    int chunk = 0;
+    std::vector<ott_net_graph*> graphs;
+};
+
 struct ott_net {
     otter::Net net;
     std::string error;
+    std::vector<HostPipeline> pipelines;
+    void drop_pipelines();
+    ~ott_net() { drop_pipelines(); }
 };
 
 namespace {
@@ -65,6 +84,7 @@ int ott_net_set_option(ott_net* net, const char* key, int value) {
     else if (k == "int8_rounding") o.int8_rounding = value;
     else if (k == "fuse_first_layer_pool") o.fuse_first_layer_pool = value != 0;
     else if (k == "int8_handover") o.int8_handover = value != 0;
+    else if (k == "host_chunk") o.host_chunk = value;
     else return fail(net, OTT_ERR_INVALID, "unknown Net option: " + k);
     return OTT_OK;
 }
@@ -168,6 +188,7 @@ int ott_net_set_conv_params(ott_net* net, const char* layer, const int8_t* w_oih
         c->top_blob_int8_scales = fvec(out_scales, n_out_scales);
     }
     net->error.clear();
+    net->drop_pipelines();  // captured forwards address the old parameters
     return net->net.recreate_pipeline(idx);
 }
 
@@ -176,39 +197,70 @@ int ott_net_forward(ott_net* net, const char* input_blob, const void* in, int in
     if (!net || !input_blob || !in || n_out < 1 || !out_blobs) return OTT_ERR_INVALID;
     net->error.clear();
     // Host in, host out, large batch: run the batch in chunks so that the upload of chunk i+1 and the download of chunk i-1
-    // overlap the kernels of chunk i (images are independent, so chunking changes no value).
+    // overlap the kernels of chunk i (images are independent, so chunking changes no value). Each chunk's forward is a
+    // captured CUDA graph, kept for the next call with the same shape: a chunk then costs the host one launch instead of one
+    // per kernel, which is what allows chunks small enough to keep the fill and drain of the pipeline short.
     bool all_host_out = out_host != nullptr;
     for (int i = 0; all_host_out && i < n_out; ++i) all_host_out = out_host[i] != nullptr;
-    const int chunk = 64;
+    const int chunk = net->net.option.host_chunk > 0 ? net->net.option.host_chunk : 64;
     if (!in_on_device && all_host_out && n >= 2 * chunk) {
         ott_ctx* ctx = net->net.context();
         const size_t img_bytes = (size_t)c * h * w * sizeof(float);
-        void* dev_in = nullptr;
-        if (ott_malloc(ctx, img_bytes * n, &dev_in) != OTT_OK) return fail(net, OTT_ERR_ALLOC, "device allocation for the input batch failed");
-        std::vector<otter::Tensor> keep;  // chunk outputs stay allocated until the final synchronisation
+        std::string key = std::string(input_blob) + "|" + std::to_string(n) + "x" + std::to_string(c) + "x" + std::to_string(h) + "x" + std::to_string(w) +
+                          "|" + std::to_string(chunk);
+        for (int i = 0; i < n_out; ++i) key += std::string("|") + out_blobs[i];
+        HostPipeline* pipe = nullptr;
+        for (HostPipeline& p : net->pipelines)
+            if (p.key == key) pipe = &p;
         int rc = OTT_OK;
-        for (int b0 = 0; b0 < n && rc == OTT_OK; b0 += chunk) {
-            const int nb = n - b0 < chunk ? n - b0 : chunk;
-            char* dptr = static_cast<char*>(dev_in) + img_bytes * b0;
-            rc = ott_memcpy_overlapped(ctx, 0, dptr, static_cast<const char*>(in) + img_bytes * b0, img_bytes * nb);
-            if (rc != OTT_OK) break;
-            otter::Extractor ex = net->net.create_extractor();
-            for (int i = 0; i < n_out; ++i) ex.keep(out_blobs[i]);
-            ex.input(input_blob, otter::Tensor::wrap(dptr, img_bytes * nb, otter::Device::CUDA, nullptr, {nb, c, h, w}, otter::ScalarType::Float));
-            std::vector<otter::Tensor> dev((size_t)n_out);
-            for (int i = 0; i < n_out && rc == OTT_OK; ++i) rc = ex.extract(out_blobs[i], dev[(size_t)i], 1);
-            for (int i = 0; i < n_out && rc == OTT_OK; ++i) {
-                const otter::Tensor& t = dev[(size_t)i];
-                if (t.layout() != otter::Layout::NCHW) { rc = OTT_ERR_UNSUPPORTED; break; }  // int8 NHWC blob: take the plain path below
-                const size_t per_img = (size_t)(t.numel() / t.size(0)) * otter::elementSize(t.scalar_type());
-                rc = ott_memcpy_overlapped(ctx, 1, static_cast<char*>(out_host[i]) + per_img * b0, t.raw_data(), per_img * nb);
-                keep.push_back(t);
+        if (!pipe) {
+            HostPipeline p;
+            p.key = key;
+            p.chunk = chunk;
+            if (ott_malloc(ctx, img_bytes * n, &p.dev_in) != OTT_OK) return fail(net, OTT_ERR_ALLOC, "device allocation for the input batch failed");
+            // the warm-up forward inside every capture reads the (not yet uploaded) buffer: give it defined contents
+            rc = ott_memset(ctx, p.dev_in, 0, img_bytes * n);
+            for (int b0 = 0; b0 < n && rc == OTT_OK; b0 += chunk) {
+                const int nb = n - b0 < chunk ? n - b0 : chunk;
+                ott_net_graph* g = nullptr;
+                rc = ott_net_capture(net, input_blob, static_cast<char*>(p.dev_in) + img_bytes * b0, nb, c, h, w, n_out, out_blobs, &g);
+                if (rc == OTT_OK) p.graphs.push_back(g);
             }
+            bool dense = rc == OTT_OK;
+            for (size_t gi = 0; dense && gi < p.graphs.size(); ++gi)
+                for (const otter::Tensor& t : p.graphs[gi]->outputs) dense = dense && t.layout() == otter::Layout::NCHW;
+            if (!dense) {  // a capture failed, or an output is an int8 NHWC blob: this shape takes the plain path below
+                for (ott_net_graph* g : p.graphs) ott_net_graph_destroy(g);
+                ott_free(ctx, p.dev_in);
+                if (rc != OTT_OK && rc != OTT_ERR_UNSUPPORTED) return rc;
+                p.graphs.clear();
+                p.dev_in = nullptr;  // remembered, so that the next call does not try again
+            }
+            if (net->pipelines.size() >= 4) {  // a handful of shapes is kept; the oldest goes
+                for (ott_net_graph* g : net->pipelines.front().graphs) ott_net_graph_destroy(g);
+                if (net->pipelines.front().dev_in) ott_free(ctx, net->pipelines.front().dev_in);
+                net->pipelines.erase(net->pipelines.begin());
+            }
+            net->pipelines.push_back(std::move(p));
+            pipe = &net->pipelines.back();
+            rc = OTT_OK;
         }
-        const int rc_sync = ott_sync(ctx);
-        keep.clear();
-        ott_free(ctx, dev_in);
-        if (rc != OTT_ERR_UNSUPPORTED) return rc != OTT_OK ? rc : rc_sync;
+        if (pipe && !pipe->graphs.empty()) {
+            size_t gi = 0;
+            for (int b0 = 0; b0 < n && rc == OTT_OK; b0 += chunk, ++gi) {
+                const int nb = n - b0 < chunk ? n - b0 : chunk;
+                char* dptr = static_cast<char*>(pipe->dev_in) + img_bytes * b0;
+                rc = ott_memcpy_overlapped(ctx, 0, dptr, static_cast<const char*>(in) + img_bytes * b0, img_bytes * nb);
+                if (rc == OTT_OK) rc = ott_net_graph_launch(pipe->graphs[gi]);
+                for (int i = 0; i < n_out && rc == OTT_OK; ++i) {
+                    const otter::Tensor& t = pipe->graphs[gi]->outputs[(size_t)i];
+                    const size_t per_img = (size_t)(t.numel() / t.size(0)) * otter::elementSize(t.scalar_type());
+                    rc = ott_memcpy_overlapped(ctx, 1, static_cast<char*>(out_host[i]) + per_img * b0, t.raw_data(), per_img * nb);
+                }
+            }
+            const int rc_sync = ott_sync(ctx);
+            return rc != OTT_OK ? rc : rc_sync;
+        }
     }
     otter::Extractor ex = net->net.create_extractor();
     otter::Tensor x;
@@ -233,12 +285,6 @@ int ott_net_forward(ott_net* net, const char* input_blob, const void* in, int in
     }
     return OTT_OK;
 }
-
-struct ott_net_graph {
-    ott_net* net = nullptr;
-    ott_graph* graph = nullptr;
-    std::vector<otter::Tensor> outputs;  // device tensors the replays write
-};
 
 int ott_net_capture(ott_net* net, const char* input_blob, const void* in_dev, int n, int c, int h, int w, int n_out,
                     const char* const* out_blobs, ott_net_graph** out) {
@@ -307,6 +353,18 @@ int ott_net_graph_destroy(ott_net_graph* graph) {
     delete graph;
     return OTT_OK;
 }
+
+}  // extern "C"
+
+void ott_net::drop_pipelines() {
+    for (HostPipeline& p : pipelines) {
+        for (ott_net_graph* g : p.graphs) ott_net_graph_destroy(g);
+        if (p.dev_in && net.context()) ott_free(net.context(), p.dev_in);
+    }
+    pipelines.clear();
+}
+
+extern "C" {
 
 int ott_net_forward_rows(ott_net* net, const char* input_blob, const void* in, int in_on_device, int n, int c, int h, int w, const char* out_blob,
                          float* out_host, int capacity_rows, int* rows, int* cols) {

@@ -130,6 +130,7 @@ public:
     // reader's int8 input itself (same bytes as dequantize -> store -> load -> quantize); a blob asked for through
     // Extractor::extract is still delivered in fp32
     bool int8_handover = true;
+    int host_chunk = 64;  // ott_net_forward from host memory: images per chunk of the upload / compute / download pipeline
     const std::vector<char>* keep_blobs = nullptr;  // set by Extractor::keep: blobs lightmode must not release
     int blob_wanted = -1;  // set by Extractor::extract: the blob that must come out in the reference's own type
     int int8_rounding = OTT_ROUND_ADD_HALF_TRUNC;  // which reference build is mirrored (packed x86 default / aarch64)

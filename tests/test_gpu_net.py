@@ -336,16 +336,34 @@ def test_captured_forward_replays_bit_exact():
 
 
 def test_chunked_host_forward_equals_plain_forward():
-    """Large host batches run in chunks with overlapped copies; every image must come out as in a plain forward."""
+    """Large host batches run in chunks (captured forwards, overlapped copies); every image must come out as in a plain
+    forward, on the first call (which captures), on later calls (which replay, with other data), after a parameter change
+    (which must drop the captured forwards) and for an int8 output (which takes the plain path)."""
     from graph_support import build_net, oracle_conv_for_calibration
     L = graphs.shufflenetv2_layers(32, 32, stage_repeats=(2, 2, 2))
     params = graphs.make_params(L)
-    x = np.random.default_rng(31).uniform(0, 1, size=(150, 3, 32, 32)).astype(np.float32)
+    rng = np.random.default_rng(31)
+    x = rng.uniform(0, 1, size=(150, 3, 32, 32)).astype(np.float32)
     graphs.calibrate(L, params, x[:1], oracle_conv_for_calibration)
     net = build_net(L, params)
-    whole = net.forward("data", x, ["conv5"])[0]              # 150 >= 128: chunks of 64, 64, 22
-    parts = [net.forward("data", x[i:i + 50], ["conv5"])[0] for i in range(0, 150, 50)]  # 50 < 128: plain path
-    assert np.array_equal(bits(whole), bits(np.concatenate(parts)))
+    net2 = build_net(L, params, options={"host_chunk": 32})
+
+    def plain(a):  # 50 < 2 * 64: no chunking
+        return np.concatenate([net.forward("data", a[i:i + 50], ["conv5"])[0] for i in range(0, a.shape[0], 50)])
+
+    whole = net.forward("data", x, ["conv5"])[0]              # chunks of 64, 64, 22
+    assert np.array_equal(bits(whole), bits(plain(x)))
+    assert np.array_equal(bits(net2.forward("data", x, ["conv5"])[0]), bits(whole))  # chunks of 32, ..., 22
+    y = rng.uniform(0, 1, size=x.shape).astype(np.float32)
+    assert np.array_equal(bits(net.forward("data", y, ["conv5"])[0]), bits(plain(y)))  # replay with other data
     two = net.forward("data", x, ["s2b1_shuf", "conv5"])      # two outputs, one of them a plane table
     assert np.array_equal(bits(two[1]), bits(whole))
+    s8 = net.forward("data", x, ["s2b1_dw"], dtypes=[np.int8])[0]  # int8 NHWC blob: plain path, twice
+    assert np.array_equal(s8, net.forward("data", x, ["s2b1_dw"], dtypes=[np.int8])[0])
+    assert np.array_equal(s8[:50], net.forward("data", x[:50], ["s2b1_dw"], dtypes=[np.int8])[0])
+    p = params["conv5"]
+    net.set_conv_params("conv5", p["weight"], p["bias"] + np.float32(1.0), p["w_scales"], p["in_scales"], p["out_scales"])
+    changed = net.forward("data", x, ["conv5"])[0]
+    assert not np.array_equal(changed, whole) and np.array_equal(bits(changed), bits(plain(x)))
     net.close()
+    net2.close()
