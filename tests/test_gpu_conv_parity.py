@@ -81,6 +81,9 @@ def test_batched_equals_single_images(ctx):
     ("halo_3x3_c32_nopad", dict(cin=32, cout=32, k=3, pad=0, n=2, h=21, w=12, int8_scale_term=2, act_type=ACT_LRELU, act_param0=0.1)),
     ("halo_3x3_c64_pad2", dict(cin=64, cout=48, k=3, pad=2, n=1, h=9, w=9, int8_scale_term=101, s8_input=True)),
     ("halo_5x5_c32", dict(cin=32, cout=64, k=5, pad=2, n=2, h=20, w=20, int8_scale_term=101, act_type=ACT_RELU6)),
+    ("halo_3x1_c64", dict(cin=64, cout=64, k=3, kw=1, pad=0, n=2, h=19, w=11, int8_scale_term=2)),
+    ("halo_1x3_c64", dict(cin=64, cout=32, k=1, kw=3, pad=0, n=2, h=10, w=21, int8_scale_term=101, act_type=ACT_RELU, s8_input=True)),
+    ("dilated_3x3_c64_per_tap_boxes", dict(cin=64, cout=64, k=3, pad=2, dil=2, n=2, h=18, w=15, int8_scale_term=2, act_type=ACT_RELU)),
     ("two_n_tiles", dict(cin=256, cout=512, k=1, n=3, h=28, w=28, int8_scale_term=101, act_type=ACT_RELU6)),
     ("four_n_tiles", dict(cin=512, cout=1024, k=1, n=2, h=14, w=14, int8_scale_term=101, act_type=ACT_RELU6)),
 ])
