@@ -603,7 +603,7 @@ def run_net_gpu_arm(args, cfg):
     H, W = cfg["height"], cfg["width"]
     strong = "total" in cfg and not args.batch
     n = args.batch or (cfg["total"] // world if strong else cfg["batch"])  # images per GPU and step
-    chunk = min(cfg["chunk"], n)
+    chunk = min(args.chunk or cfg["chunk"], n)
     outputs = list(cfg["outputs"])
     net, layers = build_calibrated_net(cfg, chunk, local_rank)
     ctx = net.context()
@@ -761,6 +761,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + sorted(NET_WORKLOADS))
     ap.add_argument("--batch", type=int, default=0, help="per-GPU batch of a graph workload (default: the configuration's)")
+    ap.add_argument("--chunk", type=int, default=0, help="graph workloads: images per Net forward inside a step (default: the configuration's)")
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-graph", dest="graph", action="store_false", help="graph workloads: launch every kernel of a forward separately "
