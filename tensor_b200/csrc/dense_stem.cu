@@ -11,6 +11,7 @@
 //  3. 7 dp4a per output channel against the packed filter, which lives in the kernel parameter bank so every
 //     multiply reads its weights as an immediate constant operand (warp-uniform, no loads);
 //  4. epilogue per channel; fp32 NCHW stores are coalesced along the tile row, int8 NHWC stores are 16-byte vectors.
+#include "launch.cuh"
 #include "store.cuh"
 #include "umma_primitives.cuh"
 
@@ -169,6 +170,7 @@ dense_stem_pool_mma_kernel(const float* __restrict__ x, const __grid_constant__ 
     const int ix_al = (ix_first >= 0 ? ix_first : ix_first - 3) / 4 * 4;
     const int sh = ix_first - ix_al;
 
+    pdl_launch_dependents();
     if (threadIdx.x == 0) {
         mbar_init(bar, 1);
         abort_flag = 0;
@@ -184,6 +186,7 @@ dense_stem_pool_mma_kernel(const float* __restrict__ x, const __grid_constant__ 
         const uint4 w4 = j == 0 ? make_uint4(P.w[o][0], P.w[o][1], P.w[o][2], P.w[o][3]) : make_uint4(P.w[o][4], P.w[o][5], P.w[o][6], 0u);
         *reinterpret_cast<uint4*>(sB + o * 32 + ((j ^ ((o >> 2) & 1)) << 4)) = w4;
     }
+    pdl_wait();  // set-up above overlaps the previous kernel; the image is read and the output written after it
     // quantized input halo tile, as int8 channel planes. All of a thread's loads are issued before the first is used: the CTA
     // runs its phases one after the other, so this phase's DRAM latency must be paid once, not once per loop trip.
     const float* ximg = x + (long)img * 3 * s.h * s.w;
@@ -372,8 +375,9 @@ static cudaError_t launch_pool_s(cudaStream_t stream, const float* x, const Stem
         auto kernel = dense_stem_pool_mma_kernel<S, ACT>;                                                                 \
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);            \
         if (e != cudaSuccess) return e;                                                                                   \
-        kernel<<<(unsigned)blocks, 256, smem, stream>>>(x, P, in_scale, ep.has_bias, ep.act_param0, ep.rounding, out, s, ph_out, pw_out,  \
-                                                        tiles_x, tiles_y, pad_zero, status);                              \
+        e = launch_overlapped(kernel, dim3((unsigned)blocks), dim3(256), smem, stream, x, P, in_scale, ep.has_bias, ep.act_param0,        \
+                              ep.rounding, out, s, ph_out, pw_out, tiles_x, tiles_y, pad_zero, status);                    \
+        if (e != cudaSuccess) return e;                                                                                   \
     }
     switch (ep.act_type) {
         case ACT_RELU: OTT_STEMPOOL_LAUNCH(ACT_RELU) break;

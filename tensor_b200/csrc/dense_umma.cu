@@ -29,6 +29,7 @@
 #include <cuda.h>
 
 #include "dense_umma.h"
+#include "launch.cuh"
 #include "umma_primitives.cuh"
 
 namespace ottk {
@@ -66,6 +67,7 @@ __global__ void __launch_bounds__(kMaxThreads, MULTI ? 2 : 1)
 dense_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const UmmaPlan P,
                   const ConvShape s, const EpilogueParams ep, void* __restrict__ out, uint32_t* __restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
+    pdl_launch_dependents();
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
     const SmemLayout L = smem_layout(P);
@@ -97,6 +99,9 @@ dense_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        // the weight panel does not depend on the previous kernel: start loading it before waiting for that kernel
+        mbar_expect_tx(bar_b, (uint32_t)P.nkb * b_tile_bytes);
+        for (int kb = 0; kb < P.nkb; ++kb) tma_load_2d(&tmB, bar_b, sB + kb * b_tile_bytes, kb * P.bkc, n_tile * P.bn);
     }
     {
         float* sp = reinterpret_cast<float*>(base_ptr + L.params);
@@ -118,12 +123,11 @@ dense_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_wait();  // from here on the kernel reads activations and writes outputs: the previous kernel must be complete
 
     if (warp == 0) {
         if (lane == 0) {
-            // ---- TMA producer ----
-            mbar_expect_tx(bar_b, (uint32_t)P.nkb * b_tile_bytes);
-            for (int kb = 0; kb < P.nkb; ++kb) tma_load_2d(&tmB, bar_b, sB + kb * b_tile_bytes, kb * P.bkc, n_tile * P.bn);
+            // ---- TMA producer (activations; the weights were requested during set-up) ----
             uint32_t it = 0;
             bool ok = true;
             for (int m = m_first; ok && m < P.m_tiles; m += m_step) {
@@ -390,7 +394,8 @@ const char* launch_variant(cudaStream_t stream, int sm_count, const CUtensorMap&
     if (per_n < 1) per_n = 1;
     if (per_n > p.m_tiles) per_n = p.m_tiles;
     const int grid = per_n * p.n_tiles;
-    kernel<<<grid, threads, p.smem_bytes, stream>>>(tmA, tmB, p, s, ep, out, status);
+    if (launch_overlapped(kernel, dim3(grid), dim3(threads), (size_t)p.smem_bytes, stream, tmA, tmB, p, s, ep, out, status) != cudaSuccess)
+        return "dense_umma_kernel launch failed";
     return nullptr;
 }
 

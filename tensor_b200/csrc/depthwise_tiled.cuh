@@ -19,6 +19,7 @@
 // so the variants compile in parallel.
 #pragma once
 
+#include "launch.cuh"
 #include "store.cuh"
 
 namespace ottk {
@@ -120,6 +121,8 @@ depthwise_tiled_kernel(const void* __restrict__ xin, const __grid_constant__ Pla
                        const float* __restrict__ in_scales, int n_in_scales, EpilogueParams ep, void* __restrict__ out, ConvShape s, Tile T) {
     constexpr int KK = Geo<K, S>::KK;
     extern __shared__ uint32_t smem[];
+    pdl_launch_dependents();
+    pdl_wait();
     uint32_t* tin = smem;                  // [32][ir][rp] (+pad): int8 channel planes of the input tile
     uint32_t* tout = smem + CG * T.ps;     // [32][ty][orp] (+pad): int8 channel planes of the output tile
 
@@ -330,8 +333,7 @@ cudaError_t launch_t(cudaStream_t stream, const ConvShape& s, const void* x, con
     }
     const long blocks = (long)s.n * T.tiles_y * T.tiles_x * T.cgroups;
     if (blocks == 0) return cudaSuccess;
-    kernel<<<(unsigned)blocks, T.threads, smem, stream>>>(x, G, wq, in_scales, n_in_scales, ep, out, s, T);
-    return cudaGetLastError();
+    return launch_overlapped(kernel, dim3((unsigned)blocks), dim3(T.threads), smem, stream, x, G, wq, in_scales, n_in_scales, ep, out, s, T);
 }
 
 template <int K, int S, bool IN_F32, int EPI>

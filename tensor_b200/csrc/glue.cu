@@ -5,6 +5,7 @@
 // Tensor/MaxPoolLayer.cpp:123-133 + Tensor/Pool.cpp:1166-1201, Tensor/ShortCutLayer.cpp, Tensor/ReluLayer.cpp,
 // Tensor/LReluLayer.cpp, Tensor/Relu6Layer.cpp, Tensor/UpsampleLayer.cpp:113-131.
 #include "ctx.h"
+#include "launch.cuh"
 
 namespace {
 
@@ -109,6 +110,7 @@ __global__ void __launch_bounds__(256)
 upsample_bilinear_kernel(const float* __restrict__ x, float* __restrict__ y, int h, int w, int oh, int ow, double scale_h,
                          double scale_w, int rule, long planes) {
     __shared__ AxisTap taps_x[32], taps_y[8];
+    ottk::pdl_launch_dependents();  // the taps below depend on the sizes only; the previous kernel is awaited after them
     const int tid = threadIdx.y * 32 + threadIdx.x;
     if (tid < 32) {
         const int ox = blockIdx.x * 32 + tid;
@@ -118,6 +120,7 @@ upsample_bilinear_kernel(const float* __restrict__ x, float* __restrict__ y, int
         if (oy < oh) taps_y[tid - 32] = axis_tap(oy, h, oh, scale_h, rule);
     }
     __syncthreads();
+    ottk::pdl_wait();
     const int ox = blockIdx.x * 32 + threadIdx.x;
     const int oy = blockIdx.y * 8 + threadIdx.y;
     if (ox >= ow || oy >= oh) return;
@@ -202,8 +205,8 @@ int ott_upsample_bilinear_f32_nchw(ott_ctx* ctx, const float* in, int n, int c, 
     if (zblocks > 65535 || (oh + 7) / 8 > 65535) return ctx->fail(OTT_ERR_UNSUPPORTED, "Upsample: more than 2097120 planes or 524280 rows in one call");
     cudaSetDevice(ctx->device);
     const dim3 block(32, 8), grid((unsigned)((ow + 31) / 32), (unsigned)((oh + 7) / 8), (unsigned)zblocks);
-    upsample_bilinear_kernel<<<grid, block, 0, ctx->stream>>>(in, out, h, w, oh, ow, scale_h, scale_w, packed_rule ? 1 : 0, planes);
-    OTT_CUDA_CHECK(ctx, cudaGetLastError());
+    OTT_CUDA_CHECK(ctx, ottk::launch_overlapped(upsample_bilinear_kernel, grid, block, 0, ctx->stream, in, out, h, w, oh, ow, scale_h, scale_w,
+                                                packed_rule ? 1 : 0, planes));
     ctx->launches += 1;
     return OTT_OK;
 }

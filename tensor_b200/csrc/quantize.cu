@@ -7,6 +7,7 @@
 // 4x4 blocks happens in registers, 32-bit words of 4 channels go through shared memory, and writes are
 // 16-byte groups of channels (the contiguous axis of NHWC).
 #include "kernels.h"
+#include "launch.cuh"
 
 namespace ottk {
 
@@ -24,6 +25,8 @@ quantize_nchw_to_nhwc_kernel(const __grid_constant__ PlaneGather G, int8_t* __re
                              int n_scales, int c, int cpad, int hw, int tiles_p, int tiles_c, int rounding, int out_stride, int scale_base, int flat,
                              long total_px) {
     __shared__ uint32_t tile[4 * 33 * QT_PITCH];
+    pdl_launch_dependents();
+    pdl_wait();
     const long tile_id = blockIdx.x;
     const int tc = (int)(tile_id % tiles_c);
     const int tp = (int)((tile_id / tiles_c) % tiles_p);
@@ -107,9 +110,8 @@ cudaError_t launch_quantize_nchw_to_nhwc(cudaStream_t stream, const PlaneGather&
     const long total_px = (long)n * hw;
     const int tiles_p = flat ? (int)((total_px + QT_P - 1) / QT_P) : (hw + QT_P - 1) / QT_P, tiles_c = (cpad + QT_C - 1) / QT_C;
     const long blocks = (long)(flat ? 1 : n) * tiles_p * tiles_c;
-    quantize_nchw_to_nhwc_kernel<<<(unsigned)blocks, QT_THREADS, 0, stream>>>(src, out, scales_dev, n_scales, c, cpad, hw, tiles_p, tiles_c,
-                                                                            rounding, cpad, 0, flat, total_px);
-    return cudaGetLastError();
+    return launch_overlapped(quantize_nchw_to_nhwc_kernel, dim3((unsigned)blocks), dim3(QT_THREADS), 0, stream, src, out, scales_dev, n_scales, c, cpad,
+                             hw, tiles_p, tiles_c, rounding, cpad, 0, flat, total_px);
 }
 
 // A plain tensor of any channel count: the plane table holds kGatherMaxChannels entries, so wider tensors are
@@ -130,9 +132,8 @@ cudaError_t launch_quantize_dense(cudaStream_t stream, const float* x, int c_tot
         for (int i = 0; i < chunk; ++i) g.ref[i] = (uint32_t)(base + i);
         const int tiles_c = (chunk_pad + QT_C - 1) / QT_C;
         const long blocks = (long)(flat ? 1 : n) * tiles_p * tiles_c;
-        quantize_nchw_to_nhwc_kernel<<<(unsigned)blocks, QT_THREADS, 0, stream>>>(g, out + base, scales_dev, n_scales, chunk, chunk_pad, hw,
-                                                                                tiles_p, tiles_c, rounding, cpad, base, flat, total_px);
-        cudaError_t e = cudaGetLastError();
+        cudaError_t e = launch_overlapped(quantize_nchw_to_nhwc_kernel, dim3((unsigned)blocks), dim3(QT_THREADS), 0, stream, g, out + base, scales_dev,
+                                          n_scales, chunk, chunk_pad, hw, tiles_p, tiles_c, rounding, cpad, base, flat, total_px);
         if (e != cudaSuccess) return e;
     }
     return cudaSuccess;
@@ -140,6 +141,8 @@ cudaError_t launch_quantize_dense(cudaStream_t stream, const float* x, int c_tot
 
 // dst[img][c][p] = plane(c, img)[p]
 __global__ void gather_planes_kernel(const __grid_constant__ PlaneGather G, float* __restrict__ dst, int c, long hw, long total4, int vec) {
+    pdl_launch_dependents();
+    pdl_wait();
     for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (long)gridDim.x * blockDim.x) {
         const long per = vec ? hw / 4 : hw;
         const long p = i % per;
@@ -156,6 +159,8 @@ __global__ void gather_planes_kernel(const __grid_constant__ PlaneGather G, floa
 // operands where their planes lie. Block = one plane (or a slice of one), so the table look-up is per block, not per element.
 __global__ void add_planes_kernel(const __grid_constant__ PlaneGather A, const __grid_constant__ PlaneGather B, float* __restrict__ dst, int c,
                                   long hw, int slices, int vec) {
+    pdl_launch_dependents();
+    pdl_wait();
     const long plane = blockIdx.x / slices;
     const int slice = (int)(blockIdx.x % slices);
     const int ch = (int)(plane % c);
@@ -185,8 +190,7 @@ cudaError_t launch_add_planes(cudaStream_t stream, const PlaneGather& a, const P
     if (slices < 1) slices = 1;
     const long blocks = (long)n * c * slices;
     if (blocks > 0x7fffffffL) return cudaErrorInvalidValue;
-    add_planes_kernel<<<(unsigned)blocks, threads, 0, stream>>>(a, b, dst, c, hw, slices, vec);
-    return cudaGetLastError();
+    return launch_overlapped(add_planes_kernel, dim3((unsigned)blocks), dim3(threads), 0, stream, a, b, dst, c, hw, slices, vec);
 }
 
 cudaError_t launch_gather_planes(cudaStream_t stream, const PlaneGather& src, float* dst, int n, int c, long hw) {
@@ -196,8 +200,7 @@ cudaError_t launch_gather_planes(cudaStream_t stream, const PlaneGather& src, fl
     const long total = (long)n * c * (vec ? hw / 4 : hw);
     long grid = (total + 255) / 256;
     if (grid > 148 * 16) grid = 148 * 16;
-    gather_planes_kernel<<<(unsigned)grid, 256, 0, stream>>>(src, dst, c, hw, total, vec);
-    return cudaGetLastError();
+    return launch_overlapped(gather_planes_kernel, dim3((unsigned)grid), dim3(256), 0, stream, src, dst, c, hw, total, vec);
 }
 
 }  // namespace ottk
