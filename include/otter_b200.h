@@ -151,6 +151,43 @@ int ott_conv_int8_forward_gather(ott_ctx* ctx, const ott_conv* conv, const float
                                  int n_buffers, const uint32_t* plane_refs, int n, int h, int w, void* out_dev, int out_dtype,
                                  uint32_t* status_word_dev);
 
+/* ---- int8 hand-over through Concat / Crop / ChannelShuffle ----
+ * The reference quantizes a layer's fp32 input with float2int8(v * bottom_blob_int8_scale) (ConvolutionLayer.cpp:763-779,
+ * Tensor/QuantizeX86.cpp:23-71) and the requantizing epilogue ends with float2int8(v * scale_out) on the same fp32 v
+ * (Tensor/QuantizeX86.cpp:1723-1870). So when every reader of an output channel is known, the producer can store that channel
+ * already quantized for its reader (per-channel out_scales) and the reader needs no quantize pass; the glue layers between the
+ * two only select and re-order channels. Two pieces:
+ *
+ * ott_conv_int8_create_gathered: a 1x1, stride-1, unpadded dense layer whose logical input channel i is channel
+ * channel_index[i] of int8 NHWC tensor channel_source[i] (n_sources tensors of source_channels[s] channels each, every one
+ * written whole by one producer, at most 12). The kernel reads, per source, the aligned 32-channel blocks that cover the
+ * channels it needs (at most 64 blocks) with weights laid out to match, zero for channels that belong to other readers.
+ * The other arguments are those of ott_conv_int8_create (n_in_scales must be 1). Such a layer only runs through
+ * ott_conv_int8_forward_io with `sources` set. */
+int ott_conv_int8_create_gathered(ott_ctx* ctx, const ott_conv_desc* desc, const int8_t* w_oihw, const float* bias,
+                                  const float* w_scales, const float* in_scales, int n_in_scales, const float* out_scales,
+                                  int n_out_scales, int n_sources, const int* source_channels, const int* channel_source,
+                                  const int* channel_index, ott_conv** out);
+
+/* One forward described by a struct. Plain use (sources NULL, out_f32_dev NULL) equals ott_conv_int8_forward.
+ *   sources / n_sources   the int8 NHWC inputs of a layer made by ott_conv_int8_create_gathered (in_dev is ignored)
+ *   out_f32_dev, f32_channel_mask   only with out_dtype OTT_S8_NHWC on the tensor-core kernel, cout <= 1024: output channel c
+ *       with bit (c & 31) of f32_channel_mask[c >> 5] set is ALSO stored as the fp32 NCHW plane c of the [n][cout][oh][ow]
+ *       tensor out_f32_dev, holding activation(dequantize(acc)), i.e. what the same layer with fp32 output stores; the other
+ *       planes of out_f32_dev are not touched. f32_channel_mask is a host array of (cout + 31) / 32 words. */
+typedef struct ott_conv_io {
+    const void* in_dev;
+    int in_dtype;
+    const int8_t* const* sources;
+    int n_sources;
+    void* out_dev;
+    int out_dtype;
+    float* out_f32_dev;
+    const uint32_t* f32_channel_mask;
+} ott_conv_io;
+int ott_conv_int8_forward_io(ott_ctx* ctx, const ott_conv* conv, const ott_conv_io* io, int n, int h, int w,
+                             uint32_t* status_word_dev);
+
 /* Dense fp32 NCHW copy [n][channels][hw] of planes described the same way (for consumers that need one tensor). */
 int ott_gather_channels_f32(ott_ctx* ctx, const float* const* buffers, const int64_t* image_strides, int n_buffers,
                             const uint32_t* plane_refs, int channels, int n, int hw, float* dst_dev);

@@ -24,10 +24,12 @@ const char* ott_net_last_error(const ott_net* net);
 ott_ctx* ott_net_context(ott_net* net); /* valid after ott_net_compile */
 
 /* The public fields of Net::option (Tensor/NetOption.hpp:16-24), to be set before ott_net_compile. Keys: "lightmode",
- * "use_packing_layout", "int8_rounding" (OTT_ROUND_*), and the two switches this library adds, both on by default:
- * "fuse_first_layer_pool" (first convolution + 3x3 stride-2 max-pool as one kernel) and "int8_handover" (a convolution
- * whose fp32 result is read only by another quantized convolution writes that layer's int8 input directly). Both
- * leave every extracted blob bit-identical. "host_chunk" (default 64): images per chunk when ott_net_forward pipelines a host
+ * "use_packing_layout", "int8_rounding" (OTT_ROUND_*), and the three switches this library adds, all on by default:
+ * "fuse_first_layer_pool" (first convolution + 3x3 stride-2 max-pool as one kernel), "int8_handover" (a convolution
+ * whose fp32 result is read only by another quantized convolution writes that layer's int8 input directly) and
+ * "int8_routing" (the same through Concat / Crop / ChannelShuffle / Split: a producer stores each output channel already
+ * quantized for the one 1x1 convolution that reads it, which then gathers its input from its producers' int8 tensors). All
+ * three leave every extracted blob bit-identical. "host_chunk" (default 64): images per chunk when ott_net_forward pipelines a host
  * batch (upload, kernels and download of different chunks overlap). Unknown key: OTT_ERR_INVALID. */
 int ott_net_set_option(ott_net* net, const char* key, int value);
 

@@ -58,6 +58,8 @@ SIGNATURES = {
     "ott_conv_int8_forward": (i32, [vp, vp, vp, i32, i32, i32, i32, vp, i32, vp]),
     "ott_conv_int8_forward_ex": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, vp, i32, vp]),
     "ott_conv_int8_forward_gather": (i32, [vp, vp, vp, vp, i32, vp, i32, i32, i32, vp, i32, vp]),
+    "ott_conv_int8_create_gathered": (i32, [vp, C.POINTER(OttConvDesc), vp, vp, vp, vp, i32, vp, i32, i32, vp, vp, vp, C.POINTER(vp)]),
+    "ott_conv_int8_forward_io": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "ott_gather_channels_f32": (i32, [vp, vp, vp, i32, vp, i32, i32, i32, vp]),
     "ott_add_gather_f32": (i32, [vp, vp, vp, i32, vp, vp, vp, i32, vp, i32, i32, i32, vp]),
     "ott_conv_int8_forward_maxpool": (i32, [vp, vp, vp, i32, i32, i32, i32, vp]),
@@ -98,6 +100,14 @@ SIGNATURES = {
     "ott_net_profile": (i32, [vp, C.c_char_p, vp, i32, i32, i32, i32, i32, C.c_char_p, C.POINTER(C.c_float)]),
     "ott_net_forward": (i32, [vp, C.c_char_p, vp, i32, i32, i32, i32, i32, i32, C.POINTER(C.c_char_p), C.POINTER(vp)]),
 }
+
+
+
+class OttConvIO(C.Structure):
+    """ott_conv_io of include/otter_b200.h"""
+    _fields_ = [("in_dev", C.c_void_p), ("in_dtype", C.c_int), ("sources", C.POINTER(C.c_void_p)), ("n_sources", C.c_int),
+                ("out_dev", C.c_void_p), ("out_dtype", C.c_int), ("out_f32_dev", C.c_void_p), ("f32_channel_mask", C.c_void_p)]
+
 
 _lib = None
 
@@ -214,7 +224,10 @@ class ConvInt8:
     reference's field layouts (weight OIHW int8, bias/scales fp32)."""
 
     def __init__(self, ctx: Context, *, cin, cout, kh, kw, sh=1, sw=1, ph=0, pw=0, dh=1, dw=1, groups=1, bias_term=1,
-                 int8_scale_term=2, act_type=0, act_param0=0.0, rounding=0, weight, bias, w_scales, in_scales, out_scales=None):
+                 int8_scale_term=2, act_type=0, act_param0=0.0, rounding=0, weight, bias, w_scales, in_scales, out_scales=None,
+                 gathered=None):
+        """gathered: None, or (source_channels, channel_source, channel_index) for a layer whose input channels live in
+        several int8 NHWC tensors (ott_conv_int8_create_gathered)."""
         self.ctx = ctx
         self.desc = OttConvDesc(cin, cout, kh, kw, sh, sw, ph, pw, dh, dw, groups, bias_term, int8_scale_term, act_type,
                                 act_param0, rounding)
@@ -224,9 +237,16 @@ class ConvInt8:
         in_scales = np.ascontiguousarray(in_scales, dtype=np.float32)
         out_scales = None if out_scales is None else np.ascontiguousarray(out_scales, dtype=np.float32)
         h = C.c_void_p()
-        ctx.check(ctx.lib.ott_conv_int8_create(ctx.h, C.byref(self.desc), _np_ptr(weight), _np_ptr(bias), _np_ptr(w_scales),
-                                               _np_ptr(in_scales), in_scales.size, _np_ptr(out_scales),
-                                               0 if out_scales is None else out_scales.size, C.byref(h)))
+        if gathered is None:
+            ctx.check(ctx.lib.ott_conv_int8_create(ctx.h, C.byref(self.desc), _np_ptr(weight), _np_ptr(bias), _np_ptr(w_scales),
+                                                   _np_ptr(in_scales), in_scales.size, _np_ptr(out_scales),
+                                                   0 if out_scales is None else out_scales.size, C.byref(h)))
+        else:
+            sc, cs, ci = (np.ascontiguousarray(a, dtype=np.int32) for a in gathered)
+            ctx.check(ctx.lib.ott_conv_int8_create_gathered(ctx.h, C.byref(self.desc), _np_ptr(weight), _np_ptr(bias), _np_ptr(w_scales),
+                                                            _np_ptr(in_scales), in_scales.size, _np_ptr(out_scales),
+                                                            0 if out_scales is None else out_scales.size, sc.size, _np_ptr(sc),
+                                                            _np_ptr(cs), _np_ptr(ci), C.byref(h)))
         self.h = h
 
     @property
@@ -241,6 +261,26 @@ class ConvInt8:
     def forward(self, in_dev: int, in_dtype: int, n, h, w, out_dev: int, out_dtype: int, status_dev=None):
         self.ctx.check(self.ctx.lib.ott_conv_int8_forward(self.ctx.h, self.h, C.c_void_p(in_dev), in_dtype, n, h, w,
                                                           C.c_void_p(out_dev), out_dtype, C.c_void_p(status_dev) if status_dev else None))
+
+    def forward_io(self, n, h, w, out_dev: int, out_dtype: int, *, in_dev: int = 0, in_dtype: int = S8_NHWC, sources=None,
+                   out_f32_dev: int = 0, f32_channels=None):
+        """ott_conv_int8_forward_io: `sources` = device pointers of a gathered layer's int8 inputs; `f32_channels` = output
+        channels that are also stored as fp32 planes of out_f32_dev."""
+        io = OttConvIO()
+        io.in_dev, io.in_dtype = (in_dev or None), in_dtype
+        keep = []
+        if sources is not None:
+            arr = (C.c_void_p * len(sources))(*[C.c_void_p(p) for p in sources])
+            keep.append(arr)
+            io.sources, io.n_sources = C.cast(arr, C.POINTER(C.c_void_p)), len(sources)
+        io.out_dev, io.out_dtype = out_dev, out_dtype
+        if out_f32_dev:
+            mask = np.zeros((self.desc.cout + 31) // 32, np.uint32)
+            for c in f32_channels:
+                mask[c >> 5] |= np.uint32(1 << (c & 31))
+            keep.append(mask)
+            io.out_f32_dev, io.f32_channel_mask = out_f32_dev, mask.ctypes.data
+        self.ctx.check(self.ctx.lib.ott_conv_int8_forward_io(self.ctx.h, self.h, C.byref(io), n, h, w, None))
 
     def out_array(self, n, h, w, out_dtype):
         oh, ow = self.out_hw(h, w)

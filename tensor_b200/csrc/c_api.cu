@@ -1,6 +1,7 @@
 // The C-ABI of the library (include/otter_b200.h): device context, caching allocator, and the quantized
 // ConvolutionLayer's create_pipeline_int8 / forward_int8 (Tensor/ConvolutionLayer.cpp:666-752, :754-847)
 // mapped onto the CUDA kernels. No CPU compute path exists here: every forward launches kernels.
+#include <algorithm>
 #include <cstring>
 #include <new>
 #include <vector>
@@ -335,8 +336,38 @@ int ott_quantize_f32_nchw_to_s8_nhwc(ott_ctx* ctx, const float* x_dev, int n, in
     return OTT_OK;
 }
 
+namespace {
+struct GatheredInput {
+    int n_sources;
+    const int* source_channels;  // [n_sources]
+    const int* channel_source;   // [cin]
+    const int* channel_index;    // [cin]
+};
+int conv_create_impl(ott_ctx* ctx, const ott_conv_desc* d, const int8_t* w_oihw, const float* bias, const float* w_scales,
+                     const float* in_scales, int n_in_scales, const float* out_scales, int n_out_scales, const GatheredInput* gi,
+                     ott_conv** out);
+}  // namespace
+
 int ott_conv_int8_create(ott_ctx* ctx, const ott_conv_desc* d, const int8_t* w_oihw, const float* bias, const float* w_scales,
                          const float* in_scales, int n_in_scales, const float* out_scales, int n_out_scales, ott_conv** out) {
+    return conv_create_impl(ctx, d, w_oihw, bias, w_scales, in_scales, n_in_scales, out_scales, n_out_scales, nullptr, out);
+}
+
+int ott_conv_int8_create_gathered(ott_ctx* ctx, const ott_conv_desc* d, const int8_t* w_oihw, const float* bias, const float* w_scales,
+                                  const float* in_scales, int n_in_scales, const float* out_scales, int n_out_scales, int n_sources,
+                                  const int* source_channels, const int* channel_source, const int* channel_index, ott_conv** out) {
+    if (!ctx || !d || !source_channels || !channel_source || !channel_index) return OTT_ERR_INVALID;
+    if (n_sources < 1 || n_sources > kUmmaMaxSources) return ctx->fail(OTT_ERR_UNSUPPORTED, "gathered input: 1..%d sources", kUmmaMaxSources);
+    if (d->kh != 1 || d->kw != 1 || d->sh != 1 || d->sw != 1 || d->ph != 0 || d->pw != 0 || d->groups != 1 || n_in_scales != 1)
+        return ctx->fail(OTT_ERR_UNSUPPORTED, "gathered input: 1x1 stride-1 unpadded dense layers with one input scale only");
+    const GatheredInput gi{n_sources, source_channels, channel_source, channel_index};
+    return conv_create_impl(ctx, d, w_oihw, bias, w_scales, in_scales, n_in_scales, out_scales, n_out_scales, &gi, out);
+}
+
+namespace {
+int conv_create_impl(ott_ctx* ctx, const ott_conv_desc* d, const int8_t* w_oihw, const float* bias, const float* w_scales,
+                     const float* in_scales, int n_in_scales, const float* out_scales, int n_out_scales, const GatheredInput* gi,
+                     ott_conv** out) {
     if (!ctx || !d || !w_oihw || !w_scales || !in_scales || !out) return OTT_ERR_INVALID;
     *out = nullptr;
     if (d->cin <= 0 || d->cout <= 0 || d->kh <= 0 || d->kw <= 0 || d->sh <= 0 || d->sw <= 0 || d->dh <= 0 || d->dw <= 0 ||
@@ -380,7 +411,56 @@ int ott_conv_int8_create(ott_ctx* ctx, const ott_conv_desc* d, const int8_t* w_o
     int rc = OTT_OK;
     std::vector<int8_t> wpacked;
     const int taps = d->kh * d->kw;
-    if (depthwise) {
+    if (gi) {
+        // K blocks: for every source the aligned 32-channel blocks that cover the channels this layer reads from it
+        std::vector<int> lo(gi->n_sources, 1 << 30), hi(gi->n_sources, -1), base(gi->n_sources, 0);
+        for (int i = 0; i < d->cin; ++i) {
+            const int sidx = gi->channel_source[i], pos = gi->channel_index[i];
+            if (sidx < 0 || sidx >= gi->n_sources || pos < 0 || pos >= gi->source_channels[sidx]) {
+                delete c;
+                return ctx->fail(OTT_ERR_INVALID, "gathered input: channel %d names channel %d of source %d", i, pos, sidx);
+            }
+            lo[sidx] = std::min(lo[sidx], pos / kUmmaGatherBlock);
+            hi[sidx] = std::max(hi[sidx], pos / kUmmaGatherBlock);
+        }
+        int nblocks = 0;
+        for (int sidx = 0; sidx < gi->n_sources; ++sidx) {
+            if (hi[sidx] < 0 || nhwc_channels(gi->source_channels[sidx]) < kUmmaGatherBlock) {
+                delete c;
+                return ctx->fail(OTT_ERR_UNSUPPORTED, "gathered input: source %d is unused or narrower than %d channels", sidx, kUmmaGatherBlock);
+            }
+            base[sidx] = nblocks;
+            for (int b = lo[sidx]; b <= hi[sidx]; ++b, ++nblocks) {
+                c->block_x.push_back((uint16_t)(b * kUmmaGatherBlock));
+                c->block_src.push_back((uint8_t)sidx);
+            }
+        }
+        int smem_optin = 0;
+        cudaDeviceGetAttribute(&smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, ctx->device);
+        const int kk = nblocks * kUmmaGatherBlock;
+        if (nblocks > kUmmaMaxGatherBlocks || !umma_plan_layer(kk, d->cout, 1, 1, 1, 1, 1, 1, smem_optin, &c->plan, kUmmaGatherBlock)) {
+            delete c;
+            return ctx->fail(OTT_ERR_UNSUPPORTED, "gathered input: %d K blocks do not fit the tensor-core kernel", nblocks);
+        }
+        c->plan.gather = gi->n_sources;
+        c->src_channels.assign(gi->source_channels, gi->source_channels + gi->n_sources);
+        c->kind = OTT_KERNEL_DENSE_UMMA;
+        // the layer's weights against that K order; channels of a block that other layers read get zero weights
+        std::vector<int8_t> wk((size_t)d->cout * kk, 0);
+        std::vector<char> taken((size_t)kk, 0);
+        for (int i = 0; i < d->cin; ++i) {
+            const int sidx = gi->channel_source[i], pos = gi->channel_index[i];
+            const int k = (base[sidx] + pos / kUmmaGatherBlock - lo[sidx]) * kUmmaGatherBlock + pos % kUmmaGatherBlock;
+            if (taken[(size_t)k]) {
+                delete c;
+                return ctx->fail(OTT_ERR_UNSUPPORTED, "gathered input: channel %d of source %d is read twice", pos, sidx);
+            }
+            taken[(size_t)k] = 1;
+            for (int o = 0; o < d->cout; ++o) wk[(size_t)o * kk + k] = w_oihw[(size_t)o * d->cin + i];
+        }
+        wpacked.resize((size_t)c->plan.cout_rows * c->plan.k_total);
+        umma_pack_weights(c->plan, wk.data(), kk, d->cout, 1, 1, wpacked.data());
+    } else if (depthwise) {
         c->kind = OTT_KERNEL_DEPTHWISE;
         // [tap][c_pad], channel innermost: what depthwise.cu reads as 32-bit words of 4 channels
         wpacked.assign((size_t)taps * c->cout_pad, 0);
@@ -427,6 +507,7 @@ int ott_conv_int8_create(ott_ctx* ctx, const ott_conv_desc* d, const int8_t* w_o
     *out = c;
     return OTT_OK;
 }
+}  // namespace
 
 int ott_conv_int8_destroy(ott_ctx* ctx, ott_conv* c) {
     if (!c) return OTT_OK;
@@ -453,7 +534,8 @@ int ott_conv_int8_out_shape(const ott_conv* c, int h, int w, int* oh, int* ow) {
 
 namespace {
 int conv_forward_impl(ott_ctx* ctx, const ott_conv* c, const void* in_dev, const PlaneGather* gather, int in_dtype, int n, int h, int w,
-                      void* out_dev, int out_dtype, uint32_t* status_word_dev);
+                      void* out_dev, int out_dtype, uint32_t* status_word_dev, const int8_t* const* sources = nullptr, int n_sources = 0,
+                      const UmmaMixedOut* mixed = nullptr);
 }
 
 int ott_conv_int8_forward(ott_ctx* ctx, const ott_conv* c, const void* in_dev, int in_dtype, int n, int h, int w, void* out_dev,
@@ -491,6 +573,20 @@ int ott_conv_int8_forward_gather(ott_ctx* ctx, const ott_conv* c, const float* c
         g.ref[i] = plane_refs[i];
     }
     return conv_forward_impl(ctx, c, buffers[0], &g, OTT_F32_NCHW, n, h, w, out_dev, out_dtype, status_word_dev);
+}
+
+int ott_conv_int8_forward_io(ott_ctx* ctx, const ott_conv* c, const ott_conv_io* io, int n, int h, int w, uint32_t* status_word_dev) {
+    if (!ctx || !c || !io) return OTT_ERR_INVALID;
+    UmmaMixedOut mixed{};
+    if (io->out_f32_dev) {
+        if (!io->f32_channel_mask) return ctx->fail(OTT_ERR_INVALID, "out_f32_dev without f32_channel_mask");
+        if (c->d.cout > 1024) return ctx->fail(OTT_ERR_UNSUPPORTED, "an fp32 side output is limited to 1024 output channels");
+        mixed.out_f32 = io->out_f32_dev;
+        for (int i = 0; i < (c->d.cout + 31) / 32 && i < 32; ++i) mixed.mask[i] = io->f32_channel_mask[i];
+        if (c->d.cout % 32) mixed.mask[c->d.cout / 32] &= (1u << (c->d.cout % 32)) - 1u;  // never a channel past cout
+    }
+    return conv_forward_impl(ctx, c, io->in_dev, nullptr, io->in_dtype, n, h, w, io->out_dev, io->out_dtype, status_word_dev, io->sources,
+                             io->sources ? io->n_sources : 0, io->out_f32_dev ? &mixed : nullptr);
 }
 
 int ott_conv_int8_forward_maxpool(ott_ctx* ctx, const ott_conv* c, const float* in_dev, int n, int h, int w, int pad_with_zero, float* out_dev) {
@@ -560,9 +656,18 @@ int ott_add_gather_f32(ott_ctx* ctx, const float* const* a_buffers, const int64_
 
 namespace {
 int conv_forward_impl(ott_ctx* ctx, const ott_conv* c, const void* in_dev, const PlaneGather* gather, int in_dtype, int n, int h, int w,
-                      void* out_dev, int out_dtype, uint32_t* status_word_dev) {
-    if (!ctx || !c || !in_dev || !out_dev || n < 0 || h <= 0 || w <= 0) return OTT_ERR_INVALID;
+                      void* out_dev, int out_dtype, uint32_t* status_word_dev, const int8_t* const* sources, int n_sources,
+                      const UmmaMixedOut* mixed) {
+    if (!ctx || !c || !out_dev || n < 0 || h <= 0 || w <= 0) return OTT_ERR_INVALID;
     const ott_conv_desc& d = c->d;
+    const bool gathered = c->plan.gather > 0 && c->kind == OTT_KERNEL_DENSE_UMMA;
+    if (gathered != (sources != nullptr) || (gathered && n_sources != c->plan.gather))
+        return ctx->fail(OTT_ERR_INVALID, "a layer created with gathered input runs on exactly its %d int8 sources, any other layer on one input",
+                         c->plan.gather);
+    if (!gathered && !in_dev) return OTT_ERR_INVALID;
+    if (mixed && (c->kind != OTT_KERNEL_DENSE_UMMA || out_dtype != OTT_S8_NHWC || d.cout > 1024))
+        return ctx->fail(OTT_ERR_UNSUPPORTED, "an fp32 side output needs an int8 launch of the tensor-core kernel with at most 1024 output channels");
+    if (gathered) in_dtype = OTT_S8_NHWC;
     if (in_dtype != OTT_F32_NCHW && in_dtype != OTT_S8_NHWC) return ctx->fail(OTT_ERR_INVALID, "input must be fp32 NCHW or int8 NHWC");
     const bool requant = d.int8_scale_term > 100;
     if (out_dtype == OTT_S8_NHWC && !requant) return ctx->fail(OTT_ERR_INVALID, "int8 output needs int8_scale_term > 100");
@@ -624,7 +729,21 @@ int conv_forward_impl(ott_ctx* ctx, const ott_conv* c, const void* in_dev, const
             OTT_CUDA_CHECK(ctx, launch_dense_direct(ctx->stream, s, x, c->w_dev, ep, out_dev, out_dtype));
             break;
         case OTT_KERNEL_DENSE_UMMA: {
-            const char* err = launch_dense_umma(ctx->stream, ctx->sm_count, c->plan, c->weight_map, s, x, ep, out_dev, out_dtype, status);
+            UmmaSources us{};
+            if (gathered) {
+                us.n_src = n_sources;
+                for (int i = 0; i < n_sources; ++i) {
+                    if (!sources[i]) return ctx->fail(OTT_ERR_INVALID, "null source tensor");
+                    us.src[i] = sources[i];
+                    us.src_cpad[i] = nhwc_channels(c->src_channels[(size_t)i]);
+                }
+                for (size_t kb = 0; kb < c->block_x.size(); ++kb) {
+                    us.block_x[kb] = c->block_x[kb];
+                    us.block_src[kb] = c->block_src[kb];
+                }
+            }
+            const char* err = launch_dense_umma(ctx->stream, ctx->sm_count, c->plan, c->weight_map, s, x, ep, out_dev, out_dtype, status,
+                                                gathered ? &us : nullptr, mixed);
             if (err) return ctx->fail(OTT_ERR_CUDA, "%s: %s", err, cudaGetErrorString(cudaGetLastError()));
             break;
         }

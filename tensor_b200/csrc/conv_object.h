@@ -25,5 +25,10 @@ struct ott_conv {
     std::vector<float> scale_in_host, bias_host, scale_out_host;
     float in_scale0 = 1.f;
     ottk::UmmaPlan plan{};
+    // a layer whose input channels are gathered from several int8 tensors (ott_conv_int8_create_gathered): which K block is
+    // which 32 channels of which source, and the channel count every source tensor must have
+    std::vector<uint16_t> block_x;
+    std::vector<uint8_t> block_src;
+    std::vector<int> src_channels;
     alignas(128) unsigned char weight_map[128];
 };

@@ -43,6 +43,14 @@ constexpr int kMaxAccBufs = 4;
 constexpr int kHaloTw = 8, kHaloTh = 16;  // pixel tile of the halo mode: 8 wide so that a tile row is one 8-row operand group
 using namespace umma;
 
+// Activation tensor maps of one launch: one for an ordinary layer; one per source tensor for a layer whose K blocks are
+// gathered from several int8 tensors.
+struct KernelMaps {
+    CUtensorMap tm[kUmmaMaxSources];
+    uint16_t block_x[kUmmaMaxGatherBlocks];
+    uint8_t block_src[kUmmaMaxGatherBlocks];
+};
+
 struct SmemLayout {
     uint32_t b_panel, a_stages, bars, tmem_slot, abort_flag, params, total;
 };
@@ -64,8 +72,9 @@ __host__ __device__ inline SmemLayout smem_layout(const UmmaPlan& p) {
 // one-CTA-per-SM plans of large layers use the build without that register limit.
 template <int OUT, int ACT, bool BIAS, int ROUND, bool MULTI>
 __global__ void __launch_bounds__(kMaxThreads, MULTI ? 2 : 1)
-dense_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const UmmaPlan P,
-                  const ConvShape s, const EpilogueParams ep, void* __restrict__ out, uint32_t* __restrict__ status) {
+dense_umma_kernel(const __grid_constant__ KernelMaps maps, const __grid_constant__ CUtensorMap tmB, const UmmaPlan P,
+                  const ConvShape s, const EpilogueParams ep, void* __restrict__ out, uint32_t* __restrict__ status,
+                  const __grid_constant__ UmmaMixedOut mixed) {
     extern __shared__ uint8_t smem_raw[];
     pdl_launch_dependents();
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -144,15 +153,19 @@ dense_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 for (int kb = 0; kb < loads_per_tile; ++kb, ++it) {
                     const uint32_t st = it % P.stages, ph = (it / P.stages) & 1u;
                     if (!mbar_wait(bar_empty + 8u * st, ph ^ 1u, abort_flag, status, 1u)) { ok = false; break; }
-                    if (P.halo) {
+                    if (P.gather) {
+                        // K block kb = 32 channels of one of the source tensors (channels past that tensor's end arrive as zeros)
+                        mbar_expect_tx(bar_full + 8u * st, (uint32_t)kTileM * P.bkc);
+                        tma_load_4d(&maps.tm[maps.block_src[kb]], bar_full + 8u * st, sA + st * a_stage_bytes, (int)maps.block_x[kb], x0, 0, 0);
+                    } else if (P.halo) {
                         // the (8 + kw - 1) x (16 + kh - 1) pixels under the tile, one channel block; out-of-image pixels arrive as zeros
                         mbar_expect_tx(bar_full + 8u * st, (uint32_t)(halo_w * halo_h * P.bkc));
-                        tma_load_4d(&tmA, bar_full + 8u * st, sA + st * a_stage_bytes, kb * P.bkc, x0, y0, img);
+                        tma_load_4d(&maps.tm[0], bar_full + 8u * st, sA + st * a_stage_bytes, kb * P.bkc, x0, y0, img);
                     } else {
                         const int tap = kb / P.ncb, cb = kb - tap * P.ncb;
                         const int ky = tap / s.kw, kx = tap - ky * s.kw;
                         mbar_expect_tx(bar_full + 8u * st, (uint32_t)kTileM * P.bkc);
-                        tma_load_4d(&tmA, bar_full + 8u * st, sA + st * a_stage_bytes, cb * P.bkc, x0 + kx * s.dw, y0 + ky * s.dh, img);
+                        tma_load_4d(&maps.tm[0], bar_full + 8u * st, sA + st * a_stage_bytes, cb * P.bkc, x0 + kx * s.dw, y0 + ky * s.dh, img);
                     }
                 }
             }
@@ -242,9 +255,9 @@ dense_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
             int8_t* out_s8 = reinterpret_cast<int8_t*>(out) + pix * s.cout_pad + n_tile * P.bn;
             int32_t* out_s32 = reinterpret_cast<int32_t*>(out) + pix * s.cout_pad + n_tile * P.bn;
             float* out_f32 = nullptr;
-            if (OUT == DT_F32_NCHW) {
+            if (OUT == DT_F32_NCHW || (OUT == DT_S8_NHWC && mixed.out_f32 != nullptr)) {
                 const long img = pix / plane, inimg = pix - img * plane;
-                out_f32 = reinterpret_cast<float*>(out) + (img * s.cout + n_tile * P.bn) * plane + inimg;
+                out_f32 = (OUT == DT_F32_NCHW ? reinterpret_cast<float*>(out) : mixed.out_f32) + (img * s.cout + n_tile * P.bn) * plane + inimg;
             }
             // 16 accumulator columns -> 16 outputs of this thread's pixel. int8 results come back as 4 packed words in wds
             // (the caller stores them); the other output kinds are stored here.
@@ -277,6 +290,15 @@ dense_umma_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                     for (int j = 0; j < 16; ++j)
                         if (c0 + j < s.cout) out_f32[(long)(col0 + j) * plane] = y[j];
                 } else {
+                    if (out_f32 != nullptr) {
+                        // channels that some reader wants in fp32: the planes an fp32-output layer would have written
+                        const uint32_t m = (mixed.mask[(c0 >> 5) & 31] >> (c0 & 31)) & 0xFFFFu;
+                        if (m != 0u) {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                if ((m >> j) & 1u) out_f32[(long)(col0 + j) * plane] = y[j];
+                        }
+                    }
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {
                         const float4 so = *reinterpret_cast<const float4*>(s_so + col0 + g * 4);
@@ -366,8 +388,8 @@ CUtensorMapSwizzle swizzle_for(int bkc) {
 }
 
 template <int OUT, int ACT, bool BIAS, int ROUND, bool MULTI>
-const char* launch_variant(cudaStream_t stream, int sm_count, const CUtensorMap& tmA, const CUtensorMap& tmB, const UmmaPlan& p,
-                           const ConvShape& s, const EpilogueParams& ep, void* out, uint32_t* status) {
+const char* launch_variant(cudaStream_t stream, int sm_count, const KernelMaps& maps, const CUtensorMap& tmB, const UmmaPlan& p,
+                           const ConvShape& s, const EpilogueParams& ep, void* out, uint32_t* status, const UmmaMixedOut& mixed) {
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -394,7 +416,7 @@ const char* launch_variant(cudaStream_t stream, int sm_count, const CUtensorMap&
     if (per_n < 1) per_n = 1;
     if (per_n > p.m_tiles) per_n = p.m_tiles;
     const int grid = per_n * p.n_tiles;
-    if (launch_overlapped(kernel, dim3(grid), dim3(threads), (size_t)p.smem_bytes, stream, tmA, tmB, p, s, ep, out, status) != cudaSuccess)
+    if (launch_overlapped(kernel, dim3(grid), dim3(threads), (size_t)p.smem_bytes, stream, maps, tmB, p, s, ep, out, status, mixed) != cudaSuccess)
         return "dense_umma_kernel launch failed";
     return nullptr;
 }
@@ -403,12 +425,13 @@ const char* launch_variant(cudaStream_t stream, int sm_count, const CUtensorMap&
 
 static int round_up(int a, int b) { return (a + b - 1) / b * b; }
 
-bool umma_plan_layer(int cin, int cout, int kh, int kw, int sh, int sw, int dh, int dw, int smem_budget, UmmaPlan* plan) {
+bool umma_plan_layer(int cin, int cout, int kh, int kw, int sh, int sw, int dh, int dw, int smem_budget, UmmaPlan* plan, int bkc_override) {
     UmmaPlan p{};
     const int cin_pad = nhwc_channels(cin), cout_pad = nhwc_channels(cout);
     if (sh != 1 || sw != 1) return false;  // strided dense convolutions go to the direct kernel
     if (cin_pad < 32) return false;        // a TMA box may not be wider than the tensor
     p.bkc = cin_pad >= 128 ? 128 : (cin_pad >= 64 ? 64 : 32);
+    if (bkc_override == 32 || bkc_override == 64 || bkc_override == 128) p.bkc = bkc_override;
     p.ncb = (cin_pad + p.bkc - 1) / p.bkc;
     p.taps = kh * kw;
     p.nkb = p.taps * p.ncb;
@@ -491,18 +514,41 @@ const char* umma_encode_weight_map(const UmmaPlan& p, const int8_t* w_dev, void*
 
 const char* launch_dense_umma(cudaStream_t stream, int sm_count, const UmmaPlan& plan_in, const void* weight_map,
                               const ConvShape& s, const int8_t* x, const EpilogueParams& ep, void* out, int out_dtype,
-                              uint32_t* status) {
+                              uint32_t* status, const UmmaSources* sources, const UmmaMixedOut* mixed_in) {
     EncodeTiledFn enc = get_encode_fn();
     if (!enc) return "cuTensorMapEncodeTiled entry point not available";
     UmmaPlan p = plan_in;
     const long pixels = (long)s.n * s.oh * s.ow;
     if (pixels == 0) return nullptr;
-    CUtensorMap tmA;
+    KernelMaps km;  // only the entries the plan uses are filled in
+    CUtensorMap& tmA = km.tm[0];
+    UmmaMixedOut mixed{};
+    if (mixed_in) {
+        if (out_dtype != DT_S8_NHWC || s.cout > 1024) return "fp32 side output needs an int8 launch with at most 1024 output channels";
+        mixed = *mixed_in;
+    }
     const bool flat = s.kh == 1 && s.kw == 1 && s.ph == 0 && s.pw == 0;
     p.flat = flat ? 1 : 0;
     cuuint32_t estr[4] = {1, 1, 1, 1};
-    CUresult r;
-    if (flat) {
+    CUresult r = CUDA_SUCCESS;
+    if ((p.gather > 0) != (sources != nullptr)) return "gathered layer launched without its sources (or the reverse)";
+    if (p.gather > 0) {
+        if (!flat || sources->n_src != p.gather || p.nkb > kUmmaMaxGatherBlocks || p.bkc != kUmmaGatherBlock) return "bad gathered launch";
+        p.tw = kTileM; p.th = 1; p.tiles_x = (int)((pixels + kTileM - 1) / kTileM); p.tiles_y = 1;
+        p.m_tiles = p.tiles_x;
+        for (int i = 0; i < sources->n_src && r == CUDA_SUCCESS; ++i) {
+            const cuuint64_t cp = (cuuint64_t)sources->src_cpad[i];
+            cuuint64_t dims[4] = {cp, (cuuint64_t)pixels, 1, 1};
+            cuuint64_t strides[3] = {cp, cp * pixels, cp * pixels};
+            cuuint32_t box[4] = {(cuuint32_t)p.bkc, (cuuint32_t)kTileM, 1, 1};
+            r = enc(&km.tm[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)sources->src[i], dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    swizzle_for(p.bkc), CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        }
+        for (int kb = 0; kb < p.nkb; ++kb) {
+            km.block_x[kb] = sources->block_x[kb];
+            km.block_src[kb] = sources->block_src[kb];
+        }
+    } else if (flat) {
         p.tw = kTileM; p.th = 1; p.tiles_x = (int)((pixels + kTileM - 1) / kTileM); p.tiles_y = 1;
         p.m_tiles = p.tiles_x;
         cuuint64_t dims[4] = {(cuuint64_t)s.cin_pad, (cuuint64_t)pixels, 1, 1};
@@ -533,8 +579,8 @@ const char* launch_dense_umma(cudaStream_t stream, int sm_count, const UmmaPlan&
     const CUtensorMap& tmB = *reinterpret_cast<const CUtensorMap*>(weight_map);
     const char* err = nullptr;
 #define OTT_UMMA_LAUNCH(OUT, ACT, BIAS, ROUND)                                                                       \
-    err = p.ctas_per_sm > 1 ? launch_variant<OUT, ACT, BIAS, ROUND, true>(stream, sm_count, tmA, tmB, p, s, ep, out, status) \
-                            : launch_variant<OUT, ACT, BIAS, ROUND, false>(stream, sm_count, tmA, tmB, p, s, ep, out, status)
+    err = p.ctas_per_sm > 1 ? launch_variant<OUT, ACT, BIAS, ROUND, true>(stream, sm_count, km, tmB, p, s, ep, out, status, mixed) \
+                            : launch_variant<OUT, ACT, BIAS, ROUND, false>(stream, sm_count, km, tmB, p, s, ep, out, status, mixed)
 #define OTT_UMMA_ACT(OUT, BIAS, ROUND)                                   \
     switch (ep.act_type) {                                               \
         case ACT_RELU: OTT_UMMA_LAUNCH(OUT, ACT_RELU, BIAS, ROUND); break;   \

@@ -23,12 +23,34 @@ struct UmmaPlan {
     int halo;        // k x k layers: one TMA box per pixel tile and channel block holds the tile plus its halo; the taps read shifted views
     int a_stage_bytes;  // bytes of one activation stage (a 128-pixel tile, or a halo tile rounded up to 1 KiB)
     int flat;                          // 1x1: activations viewed as one [pixels, channels] matrix
+    int gather;                        // > 0: the K blocks come from this many int8 NHWC tensors (see UmmaSources)
     int tw, th, tiles_x, tiles_y, m_tiles;  // 128-pixel output rectangles (tw*th == 128)
 };
 
 // Decide whether the tensor-core kernel takes this layer and how it tiles it. smem_budget = opt-in
-// shared memory per block of the device.
-bool umma_plan_layer(int cin, int cout, int kh, int kw, int sh, int sw, int dh, int dw, int smem_budget, UmmaPlan* plan);
+// shared memory per block of the device. bkc_override (32/64/128) fixes the channel-block width instead of deriving it
+// from cin.
+bool umma_plan_layer(int cin, int cout, int kh, int kw, int sh, int sw, int dh, int dw, int smem_budget, UmmaPlan* plan,
+                     int bkc_override = 0);
+
+// A 1x1 layer whose input channels are spread over several int8 NHWC tensors (each written by one producer layer): K block
+// kb of the implicit GEMM is the 32 channels starting at block_x[kb] of tensor block_src[kb]. The layer's weights are laid
+// out to match (zero for channels of a block that belong to another reader).
+constexpr int kUmmaMaxSources = 12, kUmmaMaxGatherBlocks = 64, kUmmaGatherBlock = 32;
+struct UmmaSources {
+    int n_src;
+    const int8_t* src[kUmmaMaxSources];  // device, [pixels][src_cpad]
+    int src_cpad[kUmmaMaxSources];       // channel stride of each tensor (multiple of 16, >= 32)
+    uint16_t block_x[kUmmaMaxGatherBlocks];
+    uint8_t block_src[kUmmaMaxGatherBlocks];
+};
+
+// A requantizing launch that also stores selected output channels as fp32 NCHW planes (activation(dequantize), the value an
+// fp32-output layer stores): channel c when bit c of mask is set. out_f32 is a whole [n][cout][oh][ow] tensor.
+struct UmmaMixedOut {
+    float* out_f32;
+    uint32_t mask[32];  // output channels 0..1023
+};
 
 // OIHW int8 -> [cout_rows][k_total] K-major panel, zero padded (host memory, dst sized cout_rows*k_total).
 void umma_pack_weights(const UmmaPlan& p, const int8_t* w_oihw, int cin, int cout, int kh, int kw, int8_t* dst);
@@ -37,8 +59,10 @@ void umma_pack_weights(const UmmaPlan& p, const int8_t* w_oihw, int cin, int cou
 const char* umma_encode_weight_map(const UmmaPlan& p, const int8_t* w_dev, void* map_out);
 
 // Launch. Returns NULL or an error text.
+// sources: NULL, or where the K blocks of a plan with gather > 0 come from (x is then unused). mixed: NULL, or the fp32 side
+// output of an int8 launch.
 const char* launch_dense_umma(cudaStream_t stream, int sm_count, const UmmaPlan& plan, const void* weight_map,
                               const ConvShape& s, const int8_t* x, const EpilogueParams& ep, void* out, int out_dtype,
-                              uint32_t* status);
+                              uint32_t* status, const UmmaSources* sources = nullptr, const UmmaMixedOut* mixed = nullptr);
 
 }  // namespace ottk

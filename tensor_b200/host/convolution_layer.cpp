@@ -217,7 +217,136 @@ int ConvolutionLayer::make_gpu_conv(const NetOption& opt, int scale_term, const 
 void ConvolutionLayer::release_gpu() {
     if (gpu_conv_) ott_conv_int8_destroy(gpu_ctx_, gpu_conv_);
     if (gpu_conv_handover_) ott_conv_int8_destroy(gpu_ctx_, gpu_conv_handover_);
-    gpu_conv_ = gpu_conv_handover_ = nullptr;
+    if (gpu_conv_routed_) ott_conv_int8_destroy(gpu_ctx_, gpu_conv_routed_);
+    gpu_conv_ = gpu_conv_handover_ = gpu_conv_routed_ = nullptr;
+}
+
+bool ConvolutionLayer::routable_consumer() const {
+    return gpu_conv_ && int8_scale_term > 0 && groups == 1 && kernel_height == 1 && kernel_width == 1 && stride_height == 1 &&
+           stride_width == 1 && padding_height == 0 && padding_width == 0 && !fused_maxpool &&
+           bottom_blob_int8_scales.defined() && bottom_blob_int8_scales.numel() == 1 &&
+           ott_conv_int8_kernel_kind(gpu_conv_) == OTT_KERNEL_DENSE_UMMA;
+}
+
+bool ConvolutionLayer::routable_producer() const {
+    return gpu_conv_ && int8_scale_term > 0 && int8_scale_term < 100 && groups == 1 && !fused_maxpool && out_channels <= 1024 &&
+           ott_nhwc_channels(out_channels) >= 32 && ott_conv_int8_kernel_kind(gpu_conv_) == OTT_KERNEL_DENSE_UMMA;
+}
+
+// The routed twin of the layer: its input gathered from the producers' int8 tensors and / or its output channels quantized
+// for their readers. Same arithmetic as the plain layer; only where the bytes come from and go to differs.
+int ConvolutionLayer::set_routing(const NetOption& opt, const Routing* plan) {
+    if (gpu_conv_routed_) {
+        ott_conv_int8_destroy(gpu_ctx_, gpu_conv_routed_);
+        gpu_conv_routed_ = nullptr;
+    }
+    routing_ = Routing();
+    if (!plan || (!plan->gathered && !plan->routed_out) || !gpu_conv_) return 0;
+    ott_conv_desc d{};
+    d.cin = in_channels; d.cout = out_channels; d.kh = kernel_height; d.kw = kernel_width;
+    d.sh = stride_height; d.sw = stride_width; d.ph = padding_height; d.pw = padding_width;
+    d.dh = dilation_height; d.dw = dilation_width; d.groups = groups; d.bias_term = bias_term;
+    d.int8_scale_term = plan->routed_out ? 101 : int8_scale_term;
+    d.act_type = activation_type;
+    d.act_param0 = activation_params.defined() ? activation_params.data_ptr<float>()[0] : (activation_type == 2 ? 0.1f : 0.f);
+    d.rounding = opt.int8_rounding;
+    const bool requant = d.int8_scale_term > 100;
+    const float* out_scales = nullptr;
+    int n_out = 0;
+    if (plan->routed_out) {
+        if ((int)plan->out_scales.size() != out_channels) return -1;
+        out_scales = plan->out_scales.data();
+        n_out = out_channels;
+    } else if (requant) {
+        if (!top_blob_int8_scales.defined()) return -1;
+        out_scales = top_blob_int8_scales.data_ptr<float>();
+        n_out = (int)top_blob_int8_scales.numel();
+    }
+    const float* bias = bias_term ? bias_data.data_ptr<float>() : nullptr;
+    int rc;
+    if (plan->gathered)
+        rc = ott_conv_int8_create_gathered(opt.gpu, &d, weight_data.data_ptr<int8_t>(), bias, weight_data_int8_scales.data_ptr<float>(),
+                                           bottom_blob_int8_scales.data_ptr<float>(), (int)bottom_blob_int8_scales.numel(), out_scales, n_out,
+                                           (int)plan->source_layers.size(), plan->source_channels.data(), plan->channel_source.data(),
+                                           plan->channel_index.data(), &gpu_conv_routed_);
+    else
+        rc = ott_conv_int8_create(opt.gpu, &d, weight_data.data_ptr<int8_t>(), bias, weight_data_int8_scales.data_ptr<float>(),
+                                  bottom_blob_int8_scales.data_ptr<float>(), (int)bottom_blob_int8_scales.numel(), out_scales, n_out,
+                                  &gpu_conv_routed_);
+    if (rc != 0) return rc;
+    routing_ = *plan;
+    return 0;
+}
+
+int ConvolutionLayer::forward_routed(const Tensor& bottom_blob, Tensor& top_blob, const NetOption& opt) const {
+    const Routing& R = routing_;
+    const int n = (int)bottom_blob.size(0), h = (int)bottom_blob.size(2), w = (int)bottom_blob.size(3);
+    int oh = 0, ow = 0;
+    ott_conv_int8_out_shape(gpu_conv_routed_, h, w, &oh, &ow);
+    ott_conv_io io{};
+    std::vector<const int8_t*> srcs;
+    Tensor src = bottom_blob;
+    if (R.gathered) {
+        // the producers' int8 tensors, found through the plane table (or the plain tensor) the glue layers handed down; the
+        // table must say exactly what the plan was made for
+        const bool table = src.is_table();
+        const size_t nbuf = table ? src.table_bufs().size() : 1;
+        auto buf = [&](size_t b) -> const Tensor& { return table ? src.table_bufs()[b] : src; };
+        srcs.assign(R.source_layers.size(), nullptr);
+        for (size_t s = 0; s < R.source_layers.size(); ++s)
+            for (size_t b = 0; b < nbuf; ++b)
+                if (buf(b).companion_tag() == R.source_layers[s]) srcs[s] = buf(b).companion()->data_ptr<int8_t>();
+        for (int i = 0; i < in_channels; ++i) {
+            const uint32_t ref = table ? src.table_refs()[(size_t)i] : (uint32_t)i;
+            const Tensor& b = buf(ref >> 24);
+            const int s = R.channel_source[(size_t)i];
+            if (!srcs[(size_t)s] || b.companion_tag() != R.source_layers[(size_t)s] || (int)(ref & 0xFFFFFFu) != R.channel_index[(size_t)i] ||
+                (int)b.size(1) != R.source_channels[(size_t)s])
+                return -1;  // not the graph this layer was planned for
+        }
+        io.sources = srcs.data();
+        io.n_sources = (int)srcs.size();
+        io.in_dtype = OTT_S8_NHWC;
+    } else {
+        if (src.is_table()) {
+            src = materialize(opt, src);
+            if (!src.defined()) return -100;
+        }
+        if (src.scalar_type() == ScalarType::Float && src.layout() == Layout::NCHW) io.in_dtype = OTT_F32_NCHW;
+        else if (src.scalar_type() == ScalarType::Byte && src.layout() == Layout::NHWC16) io.in_dtype = OTT_S8_NHWC;
+        else return -1;
+        io.in_dev = src.raw_data();
+    }
+    const bool requant = R.routed_out || int8_scale_term > 100;
+    Tensor s8;
+    if (requant) {
+        s8 = device_empty(opt, {n, out_channels, oh, ow}, ScalarType::Byte, Layout::NHWC16);
+        if (!s8.defined()) return -100;
+    }
+    if (R.routed_out) {
+        // the fp32 blob of the layer: only the planes named in f32_mask are written, which are the only ones anyone reads
+        top_blob = device_empty(opt, {n, out_channels, oh, ow}, ScalarType::Float, Layout::NCHW);
+        if (!top_blob.defined()) return -100;
+        top_blob.set_companion(s8, R.self_layer);
+        io.out_dev = s8.raw_data();
+        io.out_dtype = OTT_S8_NHWC;
+        bool any = false;
+        for (uint32_t m : R.f32_mask) any = any || m != 0u;
+        if (any) {
+            io.out_f32_dev = top_blob.data_ptr<float>();
+            io.f32_channel_mask = R.f32_mask.data();
+        }
+    } else if (requant) {
+        top_blob = s8;
+        io.out_dev = s8.raw_data();
+        io.out_dtype = OTT_S8_NHWC;
+    } else {
+        top_blob = device_empty(opt, {n, out_channels, oh, ow}, ScalarType::Float, Layout::NCHW);
+        if (!top_blob.defined()) return -100;
+        io.out_dev = top_blob.raw_data();
+        io.out_dtype = OTT_F32_NCHW;
+    }
+    return ott_conv_int8_forward_io(opt.gpu, gpu_conv_routed_, &io, n, h, w, nullptr);
 }
 
 // The consumer quantizes its fp32 input with float2int8(v * scale) (Tensor/QuantizeX86.cpp:23-71, called from
@@ -245,6 +374,7 @@ int ConvolutionLayer::forward(const Tensor& bottom_blob, Tensor& top_blob, const
     if (!gpu_conv_ || !bottom_blob.defined() || bottom_blob.device() != Device::CUDA || bottom_blob.dim() != 4) return -1;
     const int n = (int)bottom_blob.size(0), c = (int)bottom_blob.size(1), h = (int)bottom_blob.size(2), w = (int)bottom_blob.size(3);
     if (c != in_channels) return -1;
+    if (opt.routing_active && gpu_conv_routed_) return forward_routed(bottom_blob, top_blob, opt);
     int oh = 0, ow = 0;
     ott_conv_int8_out_shape(gpu_conv_, h, w, &oh, &ow);
     // int8 hand-over: the only reader of the top blob is a quantized convolution, and nobody asked for the blob itself
@@ -310,6 +440,11 @@ public:
     int forward(const std::vector<Tensor>& bottom_blobs, std::vector<Tensor>& top_blobs, const NetOption&) const override {
         for (auto& t : top_blobs) t = bottom_blobs[0];
         return 0;
+    }
+    bool map_channels(const std::vector<std::vector<int>>& in, std::vector<std::vector<int>>& out) const override {
+        if (in.size() != 1 || in[0].empty()) return false;
+        for (auto& t : out) t = in[0];
+        return true;
     }
     std::string type() const override { return "Split"; }
 };

@@ -106,6 +106,15 @@ public:
         tops[0] = Tensor::concat_channels(bottoms);
         return tops[0].defined() ? 0 : -1;
     }
+    bool map_channels(const std::vector<std::vector<int>>& in, std::vector<std::vector<int>>& out) const override {
+        if (out.size() != 1) return false;
+        out[0].clear();
+        for (const auto& b : in) {
+            if (b.empty()) return false;
+            out[0].insert(out[0].end(), b.begin(), b.end());
+        }
+        return true;
+    }
     std::string type() const override { return "Concat"; }
 };
 
@@ -143,6 +152,13 @@ public:
         top = bottom.select_channels(pick);  // a selection of planes, as the view native::slice gives the reference
         return top.defined() ? 0 : -1;
     }
+    bool map_channels(const std::vector<std::vector<int>>& in, std::vector<std::vector<int>>& out) const override {
+        if (in.size() != 1 || out.size() != 1 || in[0].empty()) return false;
+        const int c = (int)in[0].size(), e = end == -1 ? c : end;
+        if (start < 0 || e > c || e <= start) return false;
+        out[0].assign(in[0].begin() + start, in[0].begin() + e);
+        return true;
+    }
     std::string type() const override { return "Crop"; }
     int start = -1, end = -1;
 };
@@ -171,6 +187,16 @@ public:
             for (int k = 0; k < groups; ++k) pick[(size_t)(i * groups + k)] = k * per + i;
         top = bottom.select_channels(pick);
         return top.defined() ? 0 : -1;
+    }
+    bool map_channels(const std::vector<std::vector<int>>& in, std::vector<std::vector<int>>& out) const override {
+        if (in.size() != 1 || out.size() != 1 || in[0].empty()) return false;
+        const int c = (int)in[0].size();
+        if (groups < 1 || c % groups != 0) return false;
+        const int per = c / groups;
+        out[0].resize((size_t)c);
+        for (int i = 0; i < per; ++i)
+            for (int k = 0; k < groups; ++k) out[0][(size_t)(i * groups + k)] = in[0][(size_t)(k * per + i)];
+        return true;
     }
     std::string type() const override { return "ChannelShuffle"; }
     int groups = 1;

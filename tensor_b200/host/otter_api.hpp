@@ -66,6 +66,11 @@ public:
     // buffers no picked channel uses are dropped
     Tensor select_channels(const std::vector<int>& pick) const;
     static Tensor concat_channels(const std::vector<Tensor>& parts);
+    // The int8 NHWC tensor a producer layer wrote beside this fp32 tensor, for readers that take their input already
+    // quantized (see Net::plan_routing); tag = the producer's layer index. Travels with the handle, also inside plane tables.
+    void set_companion(const Tensor& int8_tensor, int tag) { companion_ = std::make_shared<const Tensor>(int8_tensor); companion_tag_ = tag; }
+    const Tensor* companion() const { return companion_.get(); }
+    int companion_tag() const { return companion_ ? companion_tag_ : -1; }
 
     static Tensor wrap(void* ptr, size_t bytes, Device dev, std::function<void(void*)> deleter, std::vector<int64_t> sizes,
                        ScalarType dtype, Layout layout = Layout::NCHW);
@@ -88,6 +93,8 @@ private:
         std::vector<uint32_t> refs;  // per logical channel: (buffer << 24) | plane
     };
     std::shared_ptr<const PlaneTable> table_;
+    std::shared_ptr<const Tensor> companion_;
+    int companion_tag_ = -1;
 };
 
 Tensor empty(std::vector<int64_t> sizes, ScalarType dtype);                       // host, zero-initialised
@@ -130,6 +137,12 @@ public:
     // reader's int8 input itself (same bytes as dequantize -> store -> load -> quantize); a blob asked for through
     // Extractor::extract is still delivered in fp32
     bool int8_handover = true;
+    // the same hand-over through Concat / Crop / ChannelShuffle / Split: a producer stores each output channel already
+    // quantized for the one convolution that will read it, and that convolution gathers its input channels from its producers'
+    // int8 tensors (Net::plan_routing). routing_active is set per Extractor::extract call: off when the wanted blob (or a kept
+    // one) contains a channel that would then exist in int8 only.
+    bool int8_routing = true;
+    bool routing_active = false;
     int host_chunk = 64;  // ott_net_forward from host memory: images per chunk of the upload / compute / download pipeline
     const std::vector<char>* keep_blobs = nullptr;  // set by Extractor::keep: blobs lightmode must not release
     int blob_wanted = -1;  // set by Extractor::extract: the blob that must come out in the reference's own type
@@ -214,6 +227,12 @@ public:
     // extension: a 3x3 stride-2 pad-1 max-pool can be absorbed into the first convolution layer (Net::compile decides)
     virtual bool is_pool3x3s2p1() const { return false; }
     bool absorbed = false;  // this layer's work is done by its producer; forward passes the blob through
+    // extension: a layer that only selects / re-orders channel planes says which input channel each output channel is.
+    // bottom_ids[b][c] is an opaque id of channel c of bottom b; top_ids gets the same ids. false for every other layer.
+    virtual bool map_channels(const std::vector<std::vector<int>>& bottom_ids, std::vector<std::vector<int>>& top_ids) const {
+        (void)bottom_ids; (void)top_ids;
+        return false;
+    }
     std::vector<int> bottoms, tops;
     std::vector<Tensor> bottom_shapes, top_shapes;  // Int tensors [1,4] {N,C,H,W}
     std::string name;
@@ -279,7 +298,26 @@ public:
     int set_handover(const NetOption& opt, const Tensor& consumer_input_scales);
     bool hands_over_int8() const { return gpu_conv_handover_ != nullptr; }
 
+    // Hand-over through glue layers (Net::plan_routing). As a reader: logical input channel i is channel channel_index[i] of
+    // the int8 tensor that layer source_layers[channel_source[i]] writes. As a producer: output channel c is stored quantized
+    // with out_scales[c] (0: nobody reads it in int8) and, when bit c of f32_mask is set, also as an fp32 plane.
+    struct Routing {
+        int self_layer = -1;
+        bool gathered = false;
+        std::vector<int> source_layers, source_channels, channel_source, channel_index;
+        bool routed_out = false;
+        std::vector<float> out_scales;
+        std::vector<uint32_t> f32_mask;
+    };
+    int set_routing(const NetOption& opt, const Routing* plan);  // NULL: drop the routed twin
+    const Routing* routing() const { return gpu_conv_routed_ ? &routing_ : nullptr; }
+    bool routable_consumer() const;
+    bool routable_producer() const;
+
 private:
+    int forward_routed(const Tensor& bottom_blob, Tensor& top_blob, const NetOption& opt) const;
+    Routing routing_;
+    ott_conv* gpu_conv_routed_ = nullptr;
     int make_gpu_conv(const NetOption& opt, int scale_term, const Tensor& top_scales, ott_conv** out) const;
     void release_gpu();
     ott_conv* gpu_conv_ = nullptr;
@@ -335,6 +373,9 @@ private:
     void graph_construct();
     int refresh_handover(int producer_layer);
     int plan_fusions();  // first layer + max-pool, int8 hand-over: after every create_pipeline
+    // Which channels travel in int8 through the glue layers: done lazily before the first forward after a change.
+    int plan_routing();
+    int ensure_routing() const;
     int forward_layer(int layer_index, std::vector<Tensor>& blob_tensors, const NetOption& opt) const;
     int do_forward_layer(const Layer* layer, std::vector<Tensor>& blob_tensors, const NetOption& opt) const;
 
@@ -343,6 +384,8 @@ private:
     std::vector<LayerOption> layer_options_;
     std::vector<std::string> input_names_, output_names_;
     std::vector<char> blob_fused_away_;  // blobs that exist only inside a fused kernel
+    std::vector<char> blob_needs_f32_;   // blobs holding a channel that exists in int8 only while routing is active
+    bool routing_dirty_ = true, has_routing_ = false;
     mutable std::string error_;
     bool owns_ctx_ = false;
 };
@@ -371,7 +414,8 @@ private:
     Extractor(const Net* net, size_t blob_count);
     const Net* net_;
     std::vector<Tensor> blob_tensors_;
-    std::vector<char> keep_;
+    std::vector<char> keep_, is_input_;
+    int last_mode_ = -1;  // -1 nothing computed yet, 0 / 1 = the blobs present were computed with routing off / on
     NetOption option;
 };
 

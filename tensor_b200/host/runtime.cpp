@@ -438,6 +438,141 @@ int Net::plan_fusions() {
         const int rc = refresh_handover((int)i);
         if (rc != 0) { error_ = "create_pipeline (int8 hand-over) of " + layers_[i]->name + " failed: " + ott_last_error(option.gpu); return rc; }
     }
+    routing_dirty_ = true;
+    return 0;
+}
+
+int Net::ensure_routing() const {
+    if (!routing_dirty_) return 0;
+    return const_cast<Net*>(this)->plan_routing();
+}
+
+// int8 hand-over through Concat / Crop / ChannelShuffle / Split. Those layers only select and re-order channel planes, so
+// every channel a convolution reads can be traced back to the output channel of the layer that computed it. A 1x1
+// convolution all of whose input channels come from quantized convolutions, each of those channels read by nobody else,
+// needs no quantize pass: its producers store these channels as float2int8(v * its input scale), which is what the pass
+// would have computed from the fp32 v (ConvolutionLayer.cpp:763-779 after QuantizeX86.cpp:851-903), and it gathers them from
+// the producers' int8 tensors. Channels with any other reader (a depthwise layer, a second branch, a graph output) stay fp32.
+int Net::plan_routing() {
+    routing_dirty_ = false;
+    has_routing_ = false;
+    blob_needs_f32_.assign(blobs_.size(), 0);
+    std::vector<ConvolutionLayer*> convs(layers_.size(), nullptr);
+    for (size_t i = 0; i < layers_.size(); ++i) {
+        convs[i] = dynamic_cast<ConvolutionLayer*>(layers_[i]);
+        if (convs[i]) convs[i]->set_routing(option, nullptr);
+    }
+    if (!option.int8_routing || !option.gpu) return 0;
+
+    // 1. where every channel of every blob was computed: id -> (layer, channel of its first top blob)
+    std::vector<std::vector<int>> prov(blobs_.size());
+    std::vector<std::pair<int, int>> origin;
+    std::vector<char> glue(layers_.size(), 0);
+    for (size_t li = 0; li < layers_.size(); ++li) {
+        const Layer* l = layers_[li];
+        std::vector<std::vector<int>> in, out(l->tops.size());
+        for (int b : l->bottoms) in.push_back(prov[(size_t)b]);
+        if (!in.empty() && l->map_channels(in, out)) {
+            glue[li] = 1;
+            for (size_t j = 0; j < l->tops.size(); ++j) prov[(size_t)l->tops[j]] = out[j];
+            continue;
+        }
+        for (size_t j = 0; j < l->tops.size(); ++j) {
+            const Tensor& shape = blobs_[(size_t)l->tops[j]].shape;
+            const int c = shape.defined() && shape.numel() >= 4 ? shape.data_ptr<int>()[1] : 0;
+            for (int ch = 0; ch < c; ++ch) {
+                prov[(size_t)l->tops[j]].push_back((int)origin.size());
+                origin.emplace_back(j == 0 ? (int)li : -1, ch);
+            }
+        }
+    }
+    // 2. who reads each channel: layer indices, -2 for "leaves the graph"
+    std::vector<std::vector<int>> readers(origin.size());
+    auto add_reader = [&](int id, int who) {
+        auto& r = readers[(size_t)id];
+        if (std::find(r.begin(), r.end(), who) == r.end()) r.push_back(who);
+    };
+    for (size_t li = 0; li < layers_.size(); ++li) {
+        if (glue[li]) continue;
+        for (int b : layers_[li]->bottoms)
+            for (int id : prov[(size_t)b]) add_reader(id, (int)li);
+    }
+    for (size_t b = 0; b < blobs_.size(); ++b)
+        if (blobs_[b].consumer < 0)
+            for (int id : prov[b]) add_reader(id, -2);
+
+    // 3. readers that can gather their whole input from int8 tensors
+    std::vector<ConvolutionLayer::Routing> plans(layers_.size());
+    std::vector<int> routed_to(origin.size(), -1);
+    for (size_t li = 0; li < layers_.size(); ++li) {
+        ConvolutionLayer* conv = convs[li];
+        if (!conv || !conv->routable_consumer() || conv->bottoms.size() != 1) continue;
+        const int b = conv->bottoms[0];
+        const int direct = blobs_[(size_t)b].producer;
+        if (direct >= 0 && !glue[(size_t)direct]) continue;  // reads its producer's blob as it is: the plain hand-over covers that
+        const std::vector<int>& ids = prov[(size_t)b];
+        if ((int)ids.size() != conv->in_channels) continue;
+        ConvolutionLayer::Routing plan;
+        plan.self_layer = (int)li;
+        plan.gathered = true;
+        bool ok = true;
+        std::vector<int> seen;
+        for (int id : ids) {
+            const int pl = origin[(size_t)id].first, ch = origin[(size_t)id].second;
+            const ConvolutionLayer* pc = pl >= 0 ? convs[(size_t)pl] : nullptr;
+            if (!pc || !pc->routable_producer() || readers[(size_t)id].size() != 1 || readers[(size_t)id][0] != (int)li ||
+                std::find(seen.begin(), seen.end(), id) != seen.end()) { ok = false; break; }
+            seen.push_back(id);
+            size_t s = 0;
+            for (; s < plan.source_layers.size(); ++s)
+                if (plan.source_layers[s] == pl) break;
+            if (s == plan.source_layers.size()) {
+                plan.source_layers.push_back(pl);
+                plan.source_channels.push_back(pc->out_channels);
+            }
+            plan.channel_source.push_back((int)s);
+            plan.channel_index.push_back(ch);
+        }
+        if (!ok || plan.source_layers.size() > 12) continue;
+        // 32-channel blocks the kernel would read
+        int blocks = 0;
+        for (size_t s = 0; s < plan.source_layers.size(); ++s) {
+            int lo = 1 << 30, hi = -1;
+            for (size_t i = 0; i < ids.size(); ++i)
+                if (plan.channel_source[i] == (int)s) { lo = std::min(lo, plan.channel_index[i] / 32); hi = std::max(hi, plan.channel_index[i] / 32); }
+            blocks += hi - lo + 1;
+        }
+        if (blocks > 64) continue;
+        plans[li] = plan;
+        for (int id : ids) routed_to[(size_t)id] = (int)li;
+    }
+    // 4. their producers: per-channel output scales and the fp32 planes other readers still need
+    for (size_t id = 0; id < origin.size(); ++id) {
+        if (routed_to[id] < 0) continue;
+        const int pl = origin[id].first;
+        ConvolutionLayer::Routing& plan = plans[(size_t)pl];
+        if (!plan.routed_out) {
+            plan.self_layer = pl;
+            plan.routed_out = true;
+            plan.out_scales.assign((size_t)convs[(size_t)pl]->out_channels, 0.f);
+            plan.f32_mask.assign((size_t)(convs[(size_t)pl]->out_channels + 31) / 32, 0u);
+        }
+        plan.out_scales[(size_t)origin[id].second] = convs[(size_t)routed_to[id]]->bottom_blob_int8_scales.data_ptr<float>()[0];
+    }
+    for (size_t id = 0; id < origin.size(); ++id) {
+        const int pl = origin[id].first;
+        if (pl < 0 || !plans[(size_t)pl].routed_out || routed_to[id] >= 0 || readers[id].empty()) continue;
+        plans[(size_t)pl].f32_mask[(size_t)origin[id].second >> 5] |= 1u << (origin[id].second & 31);
+    }
+    for (size_t li = 0; li < layers_.size(); ++li) {
+        if (!convs[li] || (!plans[li].gathered && !plans[li].routed_out)) continue;
+        const int rc = convs[li]->set_routing(option, &plans[li]);
+        if (rc != 0) { error_ = "int8 hand-over through the glue layers: layer " + layers_[li]->name + " failed: " + ott_last_error(option.gpu); return rc; }
+        has_routing_ = true;
+    }
+    for (size_t b = 0; b < blobs_.size(); ++b)
+        for (int id : prov[b])
+            if (routed_to[(size_t)id] >= 0) { blob_needs_f32_[b] = 1; break; }
     return 0;
 }
 
@@ -445,6 +580,7 @@ int Net::recreate_pipeline(int layer_index) {
     if (layer_index < 0 || layer_index >= (int)layers_.size()) return -1;
     Layer* layer = layers_[(size_t)layer_index];
     int rc = layer->create_pipeline(option);
+    routing_dirty_ = true;
     // the layer's input scales are the hand-over scales of the layer before it
     if (rc == 0) rc = refresh_handover(layer_index);
     for (int b : layer->bottoms)
@@ -556,6 +692,8 @@ int Extractor::input(const std::string& blob_name, const Tensor& in) {
 
 int Extractor::input(int blob_index, const Tensor& in) {
     if (blob_index < 0 || blob_index >= (int)blob_tensors_.size() || !in.defined()) return -1;
+    if (is_input_.empty()) is_input_.assign(blob_tensors_.size(), 0);
+    is_input_[(size_t)blob_index] = 1;
     if (in.device() == Device::CUDA) {
         blob_tensors_[(size_t)blob_index] = in;
         return 0;
@@ -613,12 +751,26 @@ int Extractor::extract(int blob_index, Tensor& feat, int type) {
         const Tensor& have = blob_tensors_[(size_t)blob_index];
         if (conv && conv->int8_scale_term < 100 && have.defined() && have.scalar_type() == ScalarType::Byte) blob_tensors_[(size_t)blob_index].reset();
     }
+    {
+        // Routing on or off for this call: off when the wanted blob, or one the caller keeps, holds a channel that would then
+        // exist in int8 only. Blobs computed under the other setting are dropped first (their fp32 planes may be partial).
+        const int rc = net_->ensure_routing();
+        if (rc != 0) return rc;
+        bool routed = option.int8_routing && net_->has_routing_ && !net_->blob_needs_f32_[(size_t)blob_index];
+        for (size_t b = 0; routed && b < keep_.size(); ++b)
+            if (keep_[b] && net_->blob_needs_f32_[b]) routed = false;
+        if (last_mode_ >= 0 && last_mode_ != (int)routed)
+            for (size_t b = 0; b < blob_tensors_.size(); ++b)
+                if (is_input_.empty() || !is_input_[b]) blob_tensors_[b].reset();
+        option.routing_active = routed;
+    }
     if (!blob_tensors_[(size_t)blob_index].defined()) {
         option.blob_wanted = blob_index;
         option.keep_blobs = keep_.empty() ? nullptr : &keep_;
         const int ret = net_->forward_layer(net_->blobs_[(size_t)blob_index].producer, blob_tensors_, option);
         option.blob_wanted = -1;
         if (ret != 0) return ret;
+        last_mode_ = (int)option.routing_active;
     }
     if (blob_tensors_[(size_t)blob_index].is_table()) {
         Tensor dense = materialize(option, blob_tensors_[(size_t)blob_index]);

@@ -87,6 +87,47 @@ def test_int8_handover_between_convolutions_changes_no_blob():
     off.close()
 
 
+def test_int8_routing_through_glue_layers_changes_no_blob():
+    """Inside a ShuffleNetV2 stage every unit's result reaches the next units through Concat / ChannelShuffle / Crop. With
+    "int8_routing" the producers store those channels quantized for their one reader and the readers run without a
+    quantize pass; the graph's outputs and every intermediate blob asked for must not change by a bit."""
+    from graph_support import build_net, oracle_conv, oracle_conv_for_calibration
+    L = graphs.shufflenetv2_layers(64, 64, batch=3)
+    params = graphs.make_params(L, seed=5)
+    x = np.random.default_rng(21).uniform(0, 1, size=(3, 3, 64, 64)).astype(np.float32)
+    graphs.calibrate(L, params, x[:1], oracle_conv_for_calibration)
+    probes = ["s2b0_shuf", "s2b1_pw2", "s2b2_shuf", "s3b5_pw2", "s3b7_shuf", "s4b0_r_pw2", "s4b3_shuf", "conv5"]
+    want = graphs.walk(L, x, oracle_conv(params), want=probes)
+    on = build_net(L, params)
+    off = build_net(L, params, options={"int8_routing": 0})
+    counts = []
+    for net in (on, off):
+        before = net.context().launch_count()
+        final = net.forward("data", x, ["conv5"])[0]
+        counts.append(net.context().launch_count() - before)
+        assert np.array_equal(bits(final), bits(want["conv5"]))
+    # 13 stride-1 units and conv5 lose their quantize pass
+    assert counts[1] - counts[0] == 14, counts
+    for net in (on, off):
+        # blobs that hold routed channels come out in fp32 all the same (the Net computes them without routing)
+        got = net.forward("data", x, probes)
+        for name, g in zip(probes, got):
+            assert g.dtype == np.float32 and g.shape == want[name].shape, name
+            assert np.array_equal(bits(g), bits(want[name])), f"blob {name} differs"
+        # and the routed path still works afterwards
+        assert np.array_equal(bits(net.forward("data", x, ["conv5"])[0]), bits(want["conv5"]))
+    # a larger input (several pixel tiles per layer): routed and plain agree
+    L2 = graphs.shufflenetv2_layers(160, 160, batch=2)
+    p2 = graphs.make_params(L2, seed=6)
+    x2 = np.random.default_rng(22).uniform(0, 1, size=(2, 3, 160, 160)).astype(np.float32)
+    a = build_net(L2, p2)
+    b = build_net(L2, p2, options={"int8_routing": 0})
+    ya, yb = a.forward("data", x2, ["conv5"])[0], b.forward("data", x2, ["conv5"])[0]
+    assert np.array_equal(bits(ya), bits(yb)) and np.abs(ya).max() > 0
+    for net in (on, off, a, b):
+        net.close()
+
+
 def test_unknown_layer_type_is_an_error_not_an_exit():
     from tensor_b200 import Net, OtterB200Error
     net = Net(0)

@@ -1,0 +1,131 @@
+"""GPU parity of the two building blocks of the int8 hand-over through Concat / Crop / ChannelShuffle, through the C-ABI:
+a layer that reads its input channels from several int8 tensors (ott_conv_int8_create_gathered) and a requantizing launch
+that also stores chosen channels as fp32 planes (ott_conv_int8_forward_io). Bit-exact against the CPU checker."""
+import numpy as np
+import pytest
+
+from support import ACT_NONE, ACT_RELU, ACT_RELU6, ConvCase, nchw_to_nhwc_padded, nhwc_padded_to_nchw, run_port
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    from tensor_b200 import Context
+    with Context(0) as c:
+        yield c
+
+
+def _layer(ctx, case, **kw):
+    from tensor_b200 import ConvInt8
+    return ConvInt8(ctx, cin=case.cin, cout=case.cout, kh=1, kw=1, bias_term=case.bias_term, int8_scale_term=case.int8_scale_term,
+                    act_type=case.act_type, act_param0=case.act_param0, rounding=0, weight=case.weight,
+                    bias=case.bias if case.bias_term else None, w_scales=case.w_scales, in_scales=case.in_scales,
+                    out_scales=case.out_scales if case.requant else None, **kw)
+
+
+# (source channel counts, [(source, first channel, count) in the order of the layer's input channels], cout, term, act)
+GATHER_CASES = [
+    ("two_halves", [58, 58], [(0, 29, 29), (1, 29, 29)], 58, 101, ACT_RELU),
+    ("three_ranges_f32", [58, 116, 40], [(1, 30, 31), (0, 29, 29), (2, 5, 10)], 96, 1, ACT_NONE),
+    ("tail_block_past_end", [232, 240], [(0, 200, 32), (1, 100, 140)], 232, 101, ACT_RELU6),
+    ("single_source_whole", [64], [(0, 0, 64)], 128, 101, ACT_RELU),
+    ("eight_sources", [116] * 8, [(s, 7 * s, 9 + s) for s in range(8)], 116, 2, ACT_RELU),
+]
+
+
+@pytest.mark.parametrize("name,src_ch,picks,cout,term,act", GATHER_CASES, ids=[c[0] for c in GATHER_CASES])
+def test_gathered_input_bit_exact(ctx, name, src_ch, picks, cout, term, act):
+    from gpu_support import bits
+    from tensor_b200 import F32_NCHW, KERNEL_DENSE_UMMA, S8_NHWC, nhwc_channels
+    rng = np.random.default_rng(len(name) * 1000 + cout)
+    n, h, w = 3, 13, 21
+    sources = [rng.integers(-127, 128, size=(n, c, h, w), dtype=np.int8) for c in src_ch]
+    chan_src = np.concatenate([np.full(cnt, s) for s, _, cnt in picks]).astype(np.int32)
+    chan_idx = np.concatenate([np.arange(f, f + cnt) for _, f, cnt in picks]).astype(np.int32)
+    # interleave the logical channel order, as a ChannelShuffle does
+    perm = rng.permutation(chan_src.size)
+    chan_src, chan_idx = chan_src[perm], chan_idx[perm]
+    case = ConvCase(name, int(chan_src.size), cout, 1, n=n, h=h, w=w, int8_scale_term=term, act_type=act, s8_input=True, seed=77).make()
+    case.x_s8 = np.ascontiguousarray(np.stack([sources[s][:, c] for s, c in zip(chan_src, chan_idx)], axis=1))
+    want = run_port(case, 0, want_acc=False)["y"]
+
+    layer = _layer(ctx, case, gathered=(src_ch, chan_src, chan_idx))
+    assert layer.kernel_kind == KERNEL_DENSE_UMMA
+    ptrs = []
+    try:
+        for s, c in zip(sources, src_ch):
+            padded = nchw_to_nhwc_padded(s, nhwc_channels(c))
+            padded[..., c:] = 55  # what lies in the padding channels must not matter
+            ptrs.append(ctx.to_device(padded))
+        out_dtype = S8_NHWC if case.requant else F32_NCHW
+        out = layer.out_array(n, h, w, out_dtype)
+        out_dev = ctx.malloc(out.nbytes)
+        layer.forward_io(n, h, w, out_dev, out_dtype, sources=ptrs)
+        got = ctx.to_host(out_dev, out.shape, out.dtype)
+        ctx.free(out_dev)
+        if case.requant:
+            got = nhwc_padded_to_nchw(got, cout)
+        assert np.array_equal(bits(got), bits(want))
+        # an ordinary forward of a gathered layer is refused
+        from tensor_b200 import OtterB200Error
+        with pytest.raises(OtterB200Error):
+            layer.forward(ptrs[0], S8_NHWC, n, h, w, ptrs[0], out_dtype)
+    finally:
+        for p in ptrs:
+            ctx.free(p)
+        layer.close()
+
+
+def test_gathered_rejects_bad_layouts(ctx):
+    from tensor_b200 import OtterB200Error
+    case = ConvCase("bad", 8, 32, 1, n=1, h=4, w=4, int8_scale_term=1, s8_input=True).make()
+    with pytest.raises(OtterB200Error):  # the same source channel twice
+        _layer(ctx, case, gathered=([64], np.zeros(8, np.int32), np.array([1, 1, 2, 3, 4, 5, 6, 7], np.int32)))
+    with pytest.raises(OtterB200Error):  # a source narrower than one K block
+        _layer(ctx, case, gathered=([8], np.zeros(8, np.int32), np.arange(8, dtype=np.int32)))
+    with pytest.raises(OtterB200Error):  # channel index past the source
+        _layer(ctx, case, gathered=([64], np.zeros(8, np.int32), np.arange(60, 68, dtype=np.int32)))
+
+
+@pytest.mark.parametrize("cin,cout,act,s8_in", [(64, 58, ACT_RELU, True), (116, 116, ACT_NONE, False), (256, 512, ACT_RELU6, True)])
+def test_fp32_side_output(ctx, cin, cout, act, s8_in):
+    """int8 output with per-channel scales (0 for the fp32 channels) plus fp32 planes for a subset of the channels: the int8
+    tensor equals that of the plain int8 launch, the chosen planes equal the fp32-output layer's, the others stay untouched."""
+    from gpu_support import bits
+    from tensor_b200 import F32_NCHW, S8_NHWC, nhwc_channels
+    rng = np.random.default_rng(cin + cout)
+    n, h, w = 2, 11, 17
+    case = ConvCase("mixed", cin, cout, 1, n=n, h=h, w=w, int8_scale_term=101, act_type=act, s8_input=s8_in, seed=5).make()
+    f32_channels = sorted(rng.choice(cout, size=cout // 3, replace=False).tolist())
+    scales = np.full(cout, case.out_scales[0], np.float32) * rng.uniform(0.5, 1.5, cout).astype(np.float32)
+    scales[f32_channels] = 0.0
+    case.out_scales = scales
+    want_s8 = run_port(case, 0, want_acc=False)["y"]
+    import copy
+    fcase = copy.copy(case)
+    fcase.int8_scale_term = 1
+    fcase.out_scales = np.zeros(1, np.float32)
+    want_f32 = run_port(fcase, 0, want_acc=False)["y"]
+
+    layer = _layer(ctx, case)
+    x = nchw_to_nhwc_padded(case.x_s8, nhwc_channels(cin)) if s8_in else case.x_f32
+    x_dev = ctx.to_device(x)
+    out = layer.out_array(n, h, w, S8_NHWC)
+    out_dev = ctx.malloc(out.nbytes)
+    side = np.full((n, cout, h, w), -12345.0, np.float32)
+    side_dev = ctx.to_device(side)
+    try:
+        layer.forward_io(n, h, w, out_dev, S8_NHWC, in_dev=x_dev, in_dtype=S8_NHWC if s8_in else F32_NCHW, out_f32_dev=side_dev,
+                         f32_channels=f32_channels)
+        got_s8 = nhwc_padded_to_nchw(ctx.to_host(out_dev, out.shape, out.dtype), cout)
+        got_f32 = ctx.to_host(side_dev, side.shape, side.dtype)
+        assert np.array_equal(got_s8, want_s8)
+        assert not got_s8[:, f32_channels].any()
+        assert np.array_equal(bits(got_f32[:, f32_channels]), bits(want_f32[:, f32_channels]))
+        others = [c for c in range(cout) if c not in set(f32_channels)]
+        assert (got_f32[:, others] == -12345.0).all()
+    finally:
+        for p in (x_dev, out_dev, side_dev):
+            ctx.free(p)
+        layer.close()
