@@ -698,6 +698,7 @@ def run_net_gpu_arm(args, cfg):
         total_prof = sum(by_type.values())
         # dominant layer kind: its layers' algorithmic bytes (boundary dtypes) over their measured device time
         int8_blobs = {k for k, g in geo.items() if g["term"] > 100}
+        routing = {li["name"]: li for li in net.layer_infos()}  # which layers hand over / take over int8 through the glue layers
         kind_of = lambda g: "Convolution/depthwise" if g["groups"] > 1 else ("Convolution/1x1" if g["k"] == 1 else "Convolution/stem3x3")  # noqa: E731
         dom = max((k for k in by_type if k.startswith("Convolution")), key=lambda k: by_type[k])
         dom_bytes = dom_ops = dom_ms = 0.0
@@ -706,14 +707,20 @@ def run_net_gpu_arm(args, cfg):
             if t_ != "Convolution" or kind_of(geo[nm]) != dom:
                 continue
             g = geo[nm]
-            wl = _layer_wl(g, hws[nm], in_f32=g["input"] not in int8_blobs)
+            r = routing.get(nm, {})
+            wl = _layer_wl(g, hws[nm], in_f32=g["input"] not in int8_blobs and not r.get("gathered_sources"))
             ops, byts = algorithmic_work(wl, cshape[0])
+            if r.get("out_int8_channels") or r.get("out_f32_channels"):
+                # a layer that stores its channels quantized for their readers, and only the others in fp32
+                oh_, ow_ = out_hw(wl)
+                byts -= cshape[0] * wl["cout"] * oh_ * ow_ * (1 if wl["term"] > 100 else 4)
+                byts += cshape[0] * oh_ * ow_ * (r["out_int8_channels"] + 4 * r["out_f32_channels"])
             dom_bytes += byts
             dom_ops += ops
             dom_ms += ms
             dom_layers += 1
         ach = dom_bytes / (dom_ms * 1e-3) / 1e9
-        kernels = {"Convolution/1x1": "quantize_nchw_to_nhwc_kernel (fp32 inputs) + dense_umma_kernel", "Convolution/depthwise": "depthwise_tiled_kernel",
+        kernels = {"Convolution/1x1": "dense_umma_kernel (+ quantize_nchw_to_nhwc_kernel where the input is fp32)", "Convolution/depthwise": "depthwise_tiled_kernel",
                    "Convolution/stem3x3": "dense_stem_pool_kernel"}[dom]
         roof = {"bound": "hbm", "achieved": ach, "peak": hbm_peak, "unit": "GB/s", "frac": ach / hbm_peak, "traffic": None,
                 "peak_source": hbm_src, "kernel": f"{kernels}: the {dom_layers} {dom} layers of the graph",

@@ -163,11 +163,19 @@ int ott_conv_int8_forward_gather(ott_ctx* ctx, const ott_conv* conv, const float
  * written whole by one producer, at most 12). The kernel reads, per source, the aligned 32-channel blocks that cover the
  * channels it needs (at most 64 blocks) with weights laid out to match, zero for channels that belong to other readers.
  * The other arguments are those of ott_conv_int8_create (n_in_scales must be 1). Such a layer only runs through
- * ott_conv_int8_forward_io with `sources` set. */
+ * ott_conv_int8_forward_io with `sources` set.
+ * A depthwise layer (groups == cin == cout, 3x3 / 5x5, stride 1 / 2, int8 output, equal input scales) can be created the same
+ * way. Its kernel reads whole 16-channel groups, so the layer runs on a permuted and padded channel order made of the sources'
+ * aligned groups, and its OUTPUT tensor has that order as well: ott_conv_int8_gathered_layout gives the number of channels
+ * stored (a multiple of 16) and, for every logical channel, its position; the other positions hold zeros. (The layer that
+ * reads this output is in turn created with ott_conv_int8_create_gathered over one source.) For any other layer
+ * stored_channels comes back 0. */
 int ott_conv_int8_create_gathered(ott_ctx* ctx, const ott_conv_desc* desc, const int8_t* w_oihw, const float* bias,
                                   const float* w_scales, const float* in_scales, int n_in_scales, const float* out_scales,
                                   int n_out_scales, int n_sources, const int* source_channels, const int* channel_source,
                                   const int* channel_index, ott_conv** out);
+
+int ott_conv_int8_gathered_layout(const ott_conv* conv, int* stored_channels, int* position, int n_position);
 
 /* One forward described by a struct. Plain use (sources NULL, out_f32_dev NULL) equals ott_conv_int8_forward.
  *   sources / n_sources   the int8 NHWC inputs of a layer made by ott_conv_int8_create_gathered (in_dev is ignored)

@@ -64,6 +64,11 @@ int ott_net_layer_count(const ott_net* net);
  * int8_scale_term, activation_type}, else zeros */
 int ott_net_layer_info(const ott_net* net, int i, char* type, int type_cap, char* name, int name_cap, int geom[12]);
 int ott_net_blob_shape(const ott_net* net, const char* blob, int shape[4]);
+/* How Convolution layer i takes part in the "int8_routing" hand-over (zeros for every other layer, or with the switch off):
+ * info[0] = number of int8 tensors its input channels are gathered from (0: it reads its input blob as usual),
+ * info[1] = output channels it stores quantized for their reader, info[2] = output channels it (also) stores as fp32 planes
+ * because something else reads them. Plans the hand-over if that has not happened yet. */
+int ott_net_layer_routing(ott_net* net, int i, int info[3]);
 
 /* Replace a Convolution layer's parameters (the public fields weight_data, bias_data, weight_data_int8_scales,
  * bottom_blob_int8_scales, top_blob_int8_scales of Tensor/ConvolutionLayer.hpp:62-77) and rebuild its pipeline. */

@@ -59,6 +59,7 @@ SIGNATURES = {
     "ott_conv_int8_forward_ex": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, vp, i32, vp]),
     "ott_conv_int8_forward_gather": (i32, [vp, vp, vp, vp, i32, vp, i32, i32, i32, vp, i32, vp]),
     "ott_conv_int8_create_gathered": (i32, [vp, C.POINTER(OttConvDesc), vp, vp, vp, vp, i32, vp, i32, i32, vp, vp, vp, C.POINTER(vp)]),
+    "ott_conv_int8_gathered_layout": (i32, [vp, C.POINTER(i32), vp, i32]),
     "ott_conv_int8_forward_io": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "ott_gather_channels_f32": (i32, [vp, vp, vp, i32, vp, i32, i32, i32, vp]),
     "ott_add_gather_f32": (i32, [vp, vp, vp, i32, vp, vp, vp, i32, vp, i32, i32, i32, vp]),
@@ -91,6 +92,7 @@ SIGNATURES = {
     "ott_net_layer_count": (i32, [vp]),
     "ott_net_layer_info": (i32, [vp, i32, C.c_char_p, i32, C.c_char_p, i32, C.POINTER(i32)]),
     "ott_net_blob_shape": (i32, [vp, C.c_char_p, C.POINTER(i32)]),
+    "ott_net_layer_routing": (i32, [vp, i32, C.POINTER(i32)]),
     "ott_net_set_conv_params": (i32, [vp, C.c_char_p, vp, vp, vp, vp, i32, vp, i32]),
     "ott_net_capture": (i32, [vp, C.c_char_p, vp, i32, i32, i32, i32, i32, C.POINTER(C.c_char_p), C.POINTER(vp)]),
     "ott_net_graph_launch": (i32, [vp]),
@@ -262,6 +264,13 @@ class ConvInt8:
         self.ctx.check(self.ctx.lib.ott_conv_int8_forward(self.ctx.h, self.h, C.c_void_p(in_dev), in_dtype, n, h, w,
                                                           C.c_void_p(out_dev), out_dtype, C.c_void_p(status_dev) if status_dev else None))
 
+    def gathered_layout(self):
+        """(stored channels, position of every logical channel) of a depthwise layer with gathered input; (0, []) otherwise."""
+        stored = C.c_int()
+        pos = np.zeros(self.desc.cout, np.int32)
+        self.ctx.check(self.ctx.lib.ott_conv_int8_gathered_layout(self.h, C.byref(stored), _np_ptr(pos), pos.size))
+        return stored.value, pos
+
     def forward_io(self, n, h, w, out_dev: int, out_dtype: int, *, in_dev: int = 0, in_dtype: int = S8_NHWC, sources=None,
                    out_f32_dev: int = 0, f32_channels=None):
         """ott_conv_int8_forward_io: `sources` = device pointers of a gathered layer's int8 inputs; `f32_channels` = output
@@ -392,7 +401,10 @@ class Net:
             g = (C.c_int * 12)()
             self.check(self.lib.ott_net_layer_info(self.h, i, t, 64, n, 128, g))
             keys = ("cin", "cout", "kh", "kw", "sh", "sw", "ph", "pw", "groups", "bias_term", "int8_scale_term", "act_type")
-            out.append({"type": t.value.decode(), "name": n.value.decode(), **dict(zip(keys, list(g)))})
+            r = (C.c_int * 3)()
+            self.check(self.lib.ott_net_layer_routing(self.h, i, r))
+            out.append({"type": t.value.decode(), "name": n.value.decode(), **dict(zip(keys, list(g))),
+                        "gathered_sources": r[0], "out_int8_channels": r[1], "out_f32_channels": r[2]})
         return out
 
     def blob_shape(self, name: str):

@@ -353,13 +353,91 @@ int ott_conv_int8_create(ott_ctx* ctx, const ott_conv_desc* d, const int8_t* w_o
     return conv_create_impl(ctx, d, w_oihw, bias, w_scales, in_scales, n_in_scales, out_scales, n_out_scales, nullptr, out);
 }
 
+namespace {
+// Depthwise layer over gathered int8 input. The kernel reads whole 16-channel groups, each from one source tensor, so the
+// layer is rebuilt over the channel order "for every source, the aligned 16-channel groups that cover what is read from it":
+// filters, scales and bias move to their channel's new position, every other channel of a group gets zero parameters (its
+// output is 0). The output tensor has that order too (ott_conv_int8_gathered_layout tells the reader).
+int create_gathered_depthwise(ott_ctx* ctx, const ott_conv_desc* d, const int8_t* w_oihw, const float* bias, const float* w_scales,
+                              const float* in_scales, int n_in_scales, const float* out_scales, int n_out_scales, int n_sources,
+                              const int* source_channels, const int* channel_source, const int* channel_index, ott_conv** out) {
+    if (!w_oihw || !w_scales || !in_scales || !out) return OTT_ERR_INVALID;
+    ConvShape probe{};
+    probe.kh = d->kh; probe.kw = d->kw; probe.sh = d->sh; probe.sw = d->sw; probe.dh = d->dh; probe.dw = d->dw;
+    if (!depthwise_tiled_supports(probe, d->int8_scale_term > 100 ? DT_S8_NHWC : DT_F32_NCHW) || d->int8_scale_term < 100)
+        return ctx->fail(OTT_ERR_UNSUPPORTED, "gathered input: depthwise layers need a 3x3 / 5x5, stride 1 / 2, undilated filter and int8 output");
+    for (int i = 1; i < n_in_scales; ++i)
+        if (in_scales[i] != in_scales[0]) return ctx->fail(OTT_ERR_UNSUPPORTED, "gathered input: one input scale for all channels");
+    const int C = d->cin, G16 = 16;
+    std::vector<int> lo(n_sources, 1 << 30), hi(n_sources, -1), base(n_sources, 0);
+    for (int i = 0; i < C; ++i) {
+        const int sidx = channel_source[i], pos = channel_index[i];
+        if (sidx < 0 || sidx >= n_sources || pos < 0 || pos >= source_channels[sidx])
+            return ctx->fail(OTT_ERR_INVALID, "gathered input: channel %d names channel %d of source %d", i, pos, sidx);
+        lo[sidx] = std::min(lo[sidx], pos / G16);
+        hi[sidx] = std::max(hi[sidx], pos / G16);
+    }
+    std::vector<uint16_t> block_x;
+    std::vector<uint8_t> block_src;
+    for (int sidx = 0; sidx < n_sources; ++sidx) {
+        if (hi[sidx] < 0) return ctx->fail(OTT_ERR_UNSUPPORTED, "gathered input: source %d is unused", sidx);
+        base[sidx] = (int)block_x.size();
+        for (int b = lo[sidx]; b <= hi[sidx]; ++b) {
+            block_x.push_back((uint16_t)(b * G16));
+            block_src.push_back((uint8_t)sidx);
+        }
+    }
+    const int Cs = (int)block_x.size() * G16, taps = d->kh * d->kw;
+    if (Cs > kGatherMaxChannels * G16) return ctx->fail(OTT_ERR_UNSUPPORTED, "gathered input: too many channel groups");
+    std::vector<int> position(C);
+    std::vector<int8_t> w2((size_t)Cs * taps, 0);
+    std::vector<float> ws2(Cs, 0.f), b2(Cs, 0.f), os2(Cs, 0.f);
+    std::vector<char> taken(Cs, 0);
+    for (int i = 0; i < C; ++i) {
+        const int sidx = channel_source[i], pos = channel_index[i];
+        const int p = (base[sidx] + pos / G16 - lo[sidx]) * G16 + pos % G16;
+        if (taken[p]) return ctx->fail(OTT_ERR_UNSUPPORTED, "gathered input: channel %d of source %d is read twice", pos, sidx);
+        taken[p] = 1;
+        position[i] = p;
+        std::memcpy(&w2[(size_t)p * taps], w_oihw + (size_t)i * taps, (size_t)taps);
+        ws2[p] = w_scales[i];
+        if (d->bias_term && bias) b2[p] = bias[i];
+        if (out_scales) os2[p] = n_out_scales == 1 ? out_scales[0] : out_scales[i];
+    }
+    ott_conv_desc d2 = *d;
+    d2.cin = d2.cout = d2.groups = Cs;
+    const float in0 = in_scales[0];
+    int rc = conv_create_impl(ctx, &d2, w2.data(), d->bias_term ? b2.data() : nullptr, ws2.data(), &in0, 1, out_scales ? os2.data() : nullptr,
+                              out_scales ? Cs : 0, nullptr, out);
+    if (rc != OTT_OK) return rc;
+    ott_conv* c = *out;
+    c->block_x = block_x;
+    c->block_src = block_src;
+    c->src_channels.assign(source_channels, source_channels + n_sources);
+    c->position = position;
+    c->stored_channels = Cs;
+    return OTT_OK;
+}
+}  // namespace
+
+int ott_conv_int8_gathered_layout(const ott_conv* c, int* stored_channels, int* position, int n_position) {
+    if (!c || !stored_channels) return OTT_ERR_INVALID;
+    *stored_channels = c->stored_channels;
+    if (position)
+        for (int i = 0; i < n_position && i < (int)c->position.size(); ++i) position[i] = c->position[(size_t)i];
+    return OTT_OK;
+}
+
 int ott_conv_int8_create_gathered(ott_ctx* ctx, const ott_conv_desc* d, const int8_t* w_oihw, const float* bias, const float* w_scales,
                                   const float* in_scales, int n_in_scales, const float* out_scales, int n_out_scales, int n_sources,
                                   const int* source_channels, const int* channel_source, const int* channel_index, ott_conv** out) {
     if (!ctx || !d || !source_channels || !channel_source || !channel_index) return OTT_ERR_INVALID;
     if (n_sources < 1 || n_sources > kUmmaMaxSources) return ctx->fail(OTT_ERR_UNSUPPORTED, "gathered input: 1..%d sources", kUmmaMaxSources);
+    if (d->groups > 1 && d->groups == d->cin && d->groups == d->cout)
+        return create_gathered_depthwise(ctx, d, w_oihw, bias, w_scales, in_scales, n_in_scales, out_scales, n_out_scales, n_sources, source_channels,
+                                         channel_source, channel_index, out);
     if (d->kh != 1 || d->kw != 1 || d->sh != 1 || d->sw != 1 || d->ph != 0 || d->pw != 0 || d->groups != 1 || n_in_scales != 1)
-        return ctx->fail(OTT_ERR_UNSUPPORTED, "gathered input: 1x1 stride-1 unpadded dense layers with one input scale only");
+        return ctx->fail(OTT_ERR_UNSUPPORTED, "gathered input: 1x1 stride-1 unpadded dense layers with one input scale, or depthwise layers");
     const GatheredInput gi{n_sources, source_channels, channel_source, channel_index};
     return conv_create_impl(ctx, d, w_oihw, bias, w_scales, in_scales, n_in_scales, out_scales, n_out_scales, &gi, out);
 }
@@ -660,10 +738,10 @@ int conv_forward_impl(ott_ctx* ctx, const ott_conv* c, const void* in_dev, const
                       const UmmaMixedOut* mixed) {
     if (!ctx || !c || !out_dev || n < 0 || h <= 0 || w <= 0) return OTT_ERR_INVALID;
     const ott_conv_desc& d = c->d;
-    const bool gathered = c->plan.gather > 0 && c->kind == OTT_KERNEL_DENSE_UMMA;
-    if (gathered != (sources != nullptr) || (gathered && n_sources != c->plan.gather))
+    const bool gathered = !c->src_channels.empty();
+    if (gathered != (sources != nullptr) || (gathered && n_sources != (int)c->src_channels.size()))
         return ctx->fail(OTT_ERR_INVALID, "a layer created with gathered input runs on exactly its %d int8 sources, any other layer on one input",
-                         c->plan.gather);
+                         (int)c->src_channels.size());
     if (!gathered && !in_dev) return OTT_ERR_INVALID;
     if (mixed && (c->kind != OTT_KERNEL_DENSE_UMMA || out_dtype != OTT_S8_NHWC || d.cout > 1024))
         return ctx->fail(OTT_ERR_UNSUPPORTED, "an fp32 side output needs an int8 launch of the tensor-core kernel with at most 1024 output channels");
@@ -690,6 +768,18 @@ int conv_forward_impl(ott_ctx* ctx, const ott_conv* c, const void* in_dev, const
     ep.act_type = d.act_type; ep.act_param0 = d.act_param0; ep.rounding = d.rounding;
 
     uint32_t* status = status_word_dev ? status_word_dev : ctx->status_dev;
+    PlaneGather groups8;  // depthwise over gathered int8 input: where each 16-channel group lies
+    if (gathered && c->kind == OTT_KERNEL_DEPTHWISE) {
+        if (!c->w_tiled_dev || !depthwise_tiled_supports(s, out_dtype)) return ctx->fail(OTT_ERR_UNSUPPORTED, "gathered depthwise layer: tiled kernel only");
+        for (int i = 0; i < n_sources; ++i) {
+            if (!sources[i]) return ctx->fail(OTT_ERR_INVALID, "null source tensor");
+            groups8.base[i] = reinterpret_cast<const float*>(sources[i]);
+            groups8.img_stride[i] = nhwc_channels(c->src_channels[(size_t)i]);
+        }
+        for (size_t g = 0; g < c->block_x.size(); ++g) groups8.ref[g] = ((uint32_t)c->block_src[g] << 24) | c->block_x[g];
+        gather = &groups8;
+        in_dev = sources[0];
+    }
     if (c->kind == OTT_KERNEL_DEPTHWISE && c->w_tiled_dev && depthwise_tiled_supports(s, out_dtype) &&
         (in_dtype != OTT_F32_NCHW || d.cin <= kGatherMaxChannels)) {
         // one pass over HBM: quantize (when the input is fp32), depthwise and epilogue in the same kernel
@@ -730,6 +820,7 @@ int conv_forward_impl(ott_ctx* ctx, const ott_conv* c, const void* in_dev, const
             break;
         case OTT_KERNEL_DENSE_UMMA: {
             UmmaSources us{};
+            if (gathered && c->plan.gather != n_sources) return ctx->fail(OTT_ERR_INVALID, "corrupt gathered layer");
             if (gathered) {
                 us.n_src = n_sources;
                 for (int i = 0; i < n_sources; ++i) {

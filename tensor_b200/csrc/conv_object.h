@@ -30,5 +30,9 @@ struct ott_conv {
     std::vector<uint16_t> block_x;
     std::vector<uint8_t> block_src;
     std::vector<int> src_channels;
+    // a depthwise layer with gathered input runs on a permuted, padded channel order (whole 16-channel groups of the sources):
+    // position[c] = where logical channel c lies in that order, stored_channels = its length (also the output's channels)
+    std::vector<int> position;
+    int stored_channels = 0;
     alignas(128) unsigned char weight_map[128];
 };

@@ -195,19 +195,29 @@ depthwise_tiled_kernel(const void* __restrict__ xin, const __grid_constant__ Pla
             }
         }
     } else {
-        const int8_t* x = static_cast<const int8_t*>(xin) + (long)img * s.h * s.w * s.cin_pad;
+        // Each 16-channel group is read from one tensor: the layer's own input, or (a layer created with gathered input)
+        // 16 channels of one of several source tensors, named by the table: ref = (tensor << 24) | first channel, and
+        // img_stride[tensor] = that tensor's channel stride.
+        const int half = threadIdx.x & 1;  // blockDim.x is even: a thread stays on its half
+        const int c = c0 + half * 16;
+        const int8_t* x = static_cast<const int8_t*>(xin) + (long)img * s.h * s.w * s.cin_pad + c;
+        long pitch = s.cin_pad;
+        if (G.base[0] != nullptr && c < s.cin_pad) {
+            const uint32_t ref = G.ref[c >> 4];
+            pitch = (long)G.img_stride[ref >> 24];
+            x = reinterpret_cast<const int8_t*>(G.base[ref >> 24]) + (long)img * s.h * s.w * pitch + (ref & 0xFFFFFFu);
+        }
         const int items = T.ir * T.rp * 2;  // (pixel quad, 16-channel half)
         for (int i = threadIdx.x; i < items; i += (int)blockDim.x) {
-            const int half = i & 1;
             const int xw = (i >> 1) % T.rp;
             const int r = (i >> 1) / T.rp;
-            const int iy = iy0 + r, ix = ix_al + xw * 4, c = c0 + half * 16;
+            const int iy = iy0 + r, ix = ix_al + xw * 4;
             uint4 v[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 v[j] = make_uint4(0, 0, 0, 0);
                 if (c < s.cin_pad && iy >= 0 && iy < s.h && ix + j >= 0 && ix + j < s.w)
-                    v[j] = __ldg(reinterpret_cast<const uint4*>(x + ((long)iy * s.w + ix + j) * s.cin_pad + c));
+                    v[j] = __ldg(reinterpret_cast<const uint4*>(x + ((long)iy * s.w + ix + j) * pitch));
             }
             uint32_t* dst = tin + (half * 16) * T.ps + r * T.rp + xw;
             uint32_t o[4];

@@ -228,6 +228,17 @@ bool ConvolutionLayer::routable_consumer() const {
            ott_conv_int8_kernel_kind(gpu_conv_) == OTT_KERNEL_DENSE_UMMA;
 }
 
+bool ConvolutionLayer::routable_depthwise_reader() const {
+    if (!gpu_conv_ || int8_scale_term <= 100 || groups <= 16 || groups != in_channels || groups != out_channels) return false;
+    if (kernel_height != kernel_width || (kernel_height != 3 && kernel_height != 5) || stride_height != stride_width ||
+        (stride_height != 1 && stride_height != 2) || dilation_height != 1 || dilation_width != 1)
+        return false;
+    if (!bottom_blob_int8_scales.defined() || !top_blob_int8_scales.defined()) return false;
+    for (int64_t i = 1; i < bottom_blob_int8_scales.numel(); ++i)
+        if (bottom_blob_int8_scales.data_ptr<float>()[i] != bottom_blob_int8_scales.data_ptr<float>()[0]) return false;
+    return true;
+}
+
 bool ConvolutionLayer::routable_producer() const {
     return gpu_conv_ && int8_scale_term > 0 && int8_scale_term < 100 && groups == 1 && !fused_maxpool && out_channels <= 1024 &&
            ott_nhwc_channels(out_channels) >= 32 && ott_conv_int8_kernel_kind(gpu_conv_) == OTT_KERNEL_DENSE_UMMA;
@@ -275,6 +286,10 @@ int ConvolutionLayer::set_routing(const NetOption& opt, const Routing* plan) {
                                   &gpu_conv_routed_);
     if (rc != 0) return rc;
     routing_ = *plan;
+    if (plan->gathered && groups > 1) {
+        routing_.position.assign((size_t)out_channels, 0);
+        ott_conv_int8_gathered_layout(gpu_conv_routed_, &routing_.stored_channels, routing_.position.data(), out_channels);
+    }
     return 0;
 }
 
@@ -286,7 +301,14 @@ int ConvolutionLayer::forward_routed(const Tensor& bottom_blob, Tensor& top_blob
     ott_conv_io io{};
     std::vector<const int8_t*> srcs;
     Tensor src = bottom_blob;
-    if (R.gathered) {
+    if (R.gathered && R.direct) {
+        // the output of the depthwise layer in front, in that layer's stored channel order
+        if (src.scalar_type() != ScalarType::Byte || src.layout() != Layout::NHWC16 || (int)src.size(1) != R.source_channels[0]) return -1;
+        srcs.assign(1, src.data_ptr<int8_t>());
+        io.sources = srcs.data();
+        io.n_sources = 1;
+        io.in_dtype = OTT_S8_NHWC;
+    } else if (R.gathered) {
         // the producers' int8 tensors, found through the plane table (or the plain tensor) the glue layers handed down; the
         // table must say exactly what the plan was made for
         const bool table = src.is_table();
@@ -320,7 +342,7 @@ int ConvolutionLayer::forward_routed(const Tensor& bottom_blob, Tensor& top_blob
     const bool requant = R.routed_out || int8_scale_term > 100;
     Tensor s8;
     if (requant) {
-        s8 = device_empty(opt, {n, out_channels, oh, ow}, ScalarType::Byte, Layout::NHWC16);
+        s8 = device_empty(opt, {n, R.stored_channels > 0 ? R.stored_channels : out_channels, oh, ow}, ScalarType::Byte, Layout::NHWC16);
         if (!s8.defined()) return -100;
     }
     if (R.routed_out) {
@@ -373,8 +395,8 @@ bool ConvolutionLayer::can_fuse_maxpool() const {
 int ConvolutionLayer::forward(const Tensor& bottom_blob, Tensor& top_blob, const NetOption& opt) const {
     if (!gpu_conv_ || !bottom_blob.defined() || bottom_blob.device() != Device::CUDA || bottom_blob.dim() != 4) return -1;
     const int n = (int)bottom_blob.size(0), c = (int)bottom_blob.size(1), h = (int)bottom_blob.size(2), w = (int)bottom_blob.size(3);
-    if (c != in_channels) return -1;
     if (opt.routing_active && gpu_conv_routed_) return forward_routed(bottom_blob, top_blob, opt);
+    if (c != in_channels) return -1;
     int oh = 0, ow = 0;
     ott_conv_int8_out_shape(gpu_conv_, h, w, &oh, &ow);
     // int8 hand-over: the only reader of the top blob is a quantized convolution, and nobody asked for the blob itself

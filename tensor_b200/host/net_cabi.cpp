@@ -156,6 +156,23 @@ int ott_net_layer_info(const ott_net* net, int i, char* type, int type_cap, char
     return OTT_OK;
 }
 
+int ott_net_layer_routing(ott_net* net, int i, int info[3]) {
+    if (!net || !info || i < 0 || i >= net->net.layer_count()) return OTT_ERR_INVALID;
+    info[0] = info[1] = info[2] = 0;
+    const auto* c = dynamic_cast<const otter::ConvolutionLayer*>(net->net.layer(i));
+    if (!c) return OTT_OK;
+    const int rc = net->net.prepare();
+    if (rc != 0) return fail(net, rc, net->net.last_error());
+    if (const auto* r = c->routing()) {
+        info[0] = r->gathered ? (int)r->source_layers.size() : 0;
+        if (r->routed_out) {
+            for (float sc : r->out_scales) info[1] += sc != 0.f;
+            for (uint32_t m : r->f32_mask) info[2] += __builtin_popcount(m);
+        }
+    }
+    return OTT_OK;
+}
+
 int ott_net_blob_shape(const ott_net* net, const char* blob, int shape[4]) {
     if (!net || !blob || !shape) return OTT_ERR_INVALID;
     const int b = net->net.find_blob_index_by_name(blob);

@@ -304,7 +304,11 @@ public:
     struct Routing {
         int self_layer = -1;
         bool gathered = false;
+        bool direct = false;  // the one source is the bottom blob itself: the output of a depthwise layer with gathered input
         std::vector<int> source_layers, source_channels, channel_source, channel_index;
+        // a depthwise layer with gathered input computes and stores its channels in the order of its sources' 16-channel groups
+        int stored_channels = 0;
+        std::vector<int> position;
         bool routed_out = false;
         std::vector<float> out_scales;
         std::vector<uint32_t> f32_mask;
@@ -312,6 +316,7 @@ public:
     int set_routing(const NetOption& opt, const Routing* plan);  // NULL: drop the routed twin
     const Routing* routing() const { return gpu_conv_routed_ ? &routing_ : nullptr; }
     bool routable_consumer() const;
+    bool routable_depthwise_reader() const;
     bool routable_producer() const;
 
 private:
@@ -365,6 +370,7 @@ public:
     const std::vector<std::string>& output_names() const { return output_names_; }
     const Blob& blob(int index) const { return blobs_[(size_t)index]; }
     const std::string& last_error() const { return error_; }
+    int prepare() const { return ensure_routing(); }  // finish the lazy planning now (otherwise done by the first extract)
     ott_ctx* context() const { return option.gpu; }
 
     NetOption option;

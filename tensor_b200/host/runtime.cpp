@@ -2,6 +2,7 @@
 // (declarations and reference citations in otter_api.hpp).
 #include <algorithm>
 #include <cstring>
+#include <set>
 #include <sstream>
 
 #include "otter_api.hpp"
@@ -501,48 +502,85 @@ int Net::plan_routing() {
         if (blobs_[b].consumer < 0)
             for (int id : prov[b]) add_reader(id, -2);
 
-    // 3. readers that can gather their whole input from int8 tensors
+    // 3. Readers that can take their whole input from int8 tensors: 1x1 layers (any number of sources), and depthwise
+    // layers that feed a 1x1 layer directly (they run on a permuted channel order, which that layer's weights absorb). A
+    // channel may have several such readers when all of them quantize it with the same scale (layers reading the same blob
+    // were calibrated on the same values). Start from every layer that could, and drop layers until the set is closed.
+    enum : char { kNot = 0, kPointwise = 1, kDepthwise = 2 };
+    std::vector<char> cand(layers_.size(), kNot);
+    auto in_scale = [&](size_t li) { return convs[li]->bottom_blob_int8_scales.data_ptr<float>()[0]; };
+    for (size_t li = 0; li < layers_.size(); ++li) {
+        ConvolutionLayer* conv = convs[li];
+        if (!conv || conv->bottoms.size() != 1 || conv->tops.size() != 1) continue;
+        const int direct = blobs_[(size_t)conv->bottoms[0]].producer;
+        if (direct >= 0 && !glue[(size_t)direct]) continue;  // reads its producer's blob as it is: the plain hand-over covers that
+        if ((int)prov[(size_t)conv->bottoms[0]].size() != conv->in_channels) continue;
+        if (conv->routable_consumer()) cand[li] = kPointwise;
+        else if (conv->routable_depthwise_reader()) {
+            const int next = blobs_[(size_t)conv->tops[0]].consumer;
+            if (next >= 0 && convs[(size_t)next] && convs[(size_t)next]->routable_consumer()) cand[li] = kDepthwise;
+        }
+    }
+    for (bool changed = true; changed;) {
+        changed = false;
+        for (size_t li = 0; li < layers_.size(); ++li) {
+            if (!cand[li]) continue;
+            const std::vector<int>& ids = prov[(size_t)convs[li]->bottoms[0]];
+            bool ok = std::set<int>(ids.begin(), ids.end()).size() == ids.size();
+            std::set<int> sources;
+            for (size_t i = 0; ok && i < ids.size(); ++i) {
+                const int pl = origin[(size_t)ids[i]].first;
+                const ConvolutionLayer* pc = pl >= 0 ? convs[(size_t)pl] : nullptr;
+                ok = pc && pc->routable_producer();
+                if (ok) sources.insert(pl);
+                for (int r : readers[(size_t)ids[i]])
+                    ok = ok && r >= 0 && cand[(size_t)r] && in_scale((size_t)r) == in_scale(li);
+            }
+            if (ok && sources.size() > 12) ok = false;
+            if (ok && cand[li] == kPointwise) {
+                // the 32-channel blocks the kernel would read, per source from the first to the last one it needs: at most 64
+                int blocks = 0;
+                for (int pl : sources) {
+                    int lo = 1 << 30, hi = -1;
+                    for (int id : ids)
+                        if (origin[(size_t)id].first == pl) { lo = std::min(lo, origin[(size_t)id].second / 32); hi = std::max(hi, origin[(size_t)id].second / 32); }
+                    blocks += hi - lo + 1;
+                }
+                ok = blocks <= 64;
+            }
+            if (!ok) { cand[li] = kNot; changed = true; }
+        }
+    }
     std::vector<ConvolutionLayer::Routing> plans(layers_.size());
     std::vector<int> routed_to(origin.size(), -1);
     for (size_t li = 0; li < layers_.size(); ++li) {
+        if (!cand[li]) continue;
         ConvolutionLayer* conv = convs[li];
-        if (!conv || !conv->routable_consumer() || conv->bottoms.size() != 1) continue;
-        const int b = conv->bottoms[0];
-        const int direct = blobs_[(size_t)b].producer;
-        if (direct >= 0 && !glue[(size_t)direct]) continue;  // reads its producer's blob as it is: the plain hand-over covers that
-        const std::vector<int>& ids = prov[(size_t)b];
-        if ((int)ids.size() != conv->in_channels) continue;
+        const std::vector<int>& ids = prov[(size_t)conv->bottoms[0]];
         ConvolutionLayer::Routing plan;
         plan.self_layer = (int)li;
         plan.gathered = true;
-        bool ok = true;
-        std::vector<int> seen;
         for (int id : ids) {
             const int pl = origin[(size_t)id].first, ch = origin[(size_t)id].second;
-            const ConvolutionLayer* pc = pl >= 0 ? convs[(size_t)pl] : nullptr;
-            if (!pc || !pc->routable_producer() || readers[(size_t)id].size() != 1 || readers[(size_t)id][0] != (int)li ||
-                std::find(seen.begin(), seen.end(), id) != seen.end()) { ok = false; break; }
-            seen.push_back(id);
             size_t s = 0;
             for (; s < plan.source_layers.size(); ++s)
                 if (plan.source_layers[s] == pl) break;
             if (s == plan.source_layers.size()) {
                 plan.source_layers.push_back(pl);
-                plan.source_channels.push_back(pc->out_channels);
+                plan.source_channels.push_back(convs[(size_t)pl]->out_channels);
             }
             plan.channel_source.push_back((int)s);
             plan.channel_index.push_back(ch);
         }
-        if (!ok || plan.source_layers.size() > 12) continue;
-        // 32-channel blocks the kernel would read
-        int blocks = 0;
-        for (size_t s = 0; s < plan.source_layers.size(); ++s) {
-            int lo = 1 << 30, hi = -1;
-            for (size_t i = 0; i < ids.size(); ++i)
-                if (plan.channel_source[i] == (int)s) { lo = std::min(lo, plan.channel_index[i] / 32); hi = std::max(hi, plan.channel_index[i] / 32); }
-            blocks += hi - lo + 1;
+        if (cand[li] == kDepthwise) {
+            // the 1x1 layer behind the depthwise layer reads that layer's output where the permuted order put each channel
+            // (filled in once the depthwise twin exists)
+            ConvolutionLayer::Routing& next = plans[(size_t)blobs_[(size_t)conv->tops[0]].consumer];
+            next.self_layer = blobs_[(size_t)conv->tops[0]].consumer;
+            next.gathered = true;
+            next.direct = true;
+            next.source_layers.assign(1, (int)li);
         }
-        if (blocks > 64) continue;
         plans[li] = plan;
         for (int id : ids) routed_to[(size_t)id] = (int)li;
     }
@@ -557,7 +595,7 @@ int Net::plan_routing() {
             plan.out_scales.assign((size_t)convs[(size_t)pl]->out_channels, 0.f);
             plan.f32_mask.assign((size_t)(convs[(size_t)pl]->out_channels + 31) / 32, 0u);
         }
-        plan.out_scales[(size_t)origin[id].second] = convs[(size_t)routed_to[id]]->bottom_blob_int8_scales.data_ptr<float>()[0];
+        plan.out_scales[(size_t)origin[id].second] = in_scale((size_t)routed_to[id]);
     }
     for (size_t id = 0; id < origin.size(); ++id) {
         const int pl = origin[id].first;
@@ -566,9 +604,18 @@ int Net::plan_routing() {
     }
     for (size_t li = 0; li < layers_.size(); ++li) {
         if (!convs[li] || (!plans[li].gathered && !plans[li].routed_out)) continue;
-        const int rc = convs[li]->set_routing(option, &plans[li]);
+        ConvolutionLayer::Routing& plan = plans[li];
+        if (plan.direct) {
+            const ConvolutionLayer::Routing* dw = convs[(size_t)plan.source_layers[0]]->routing();
+            if (!dw || dw->stored_channels <= 0) { error_ = "int8 hand-over: depthwise twin of " + layers_[li]->name + " is missing"; return -1; }
+            plan.source_channels.assign(1, dw->stored_channels);
+            plan.channel_source.assign((size_t)convs[li]->in_channels, 0);
+            plan.channel_index = dw->position;
+        }
+        const int rc = convs[li]->set_routing(option, &plan);
         if (rc != 0) { error_ = "int8 hand-over through the glue layers: layer " + layers_[li]->name + " failed: " + ott_last_error(option.gpu); return rc; }
         has_routing_ = true;
+        if (cand[li] == kDepthwise) blob_needs_f32_[(size_t)convs[li]->tops[0]] = 1;  // exists in the permuted order only
     }
     for (size_t b = 0; b < blobs_.size(); ++b)
         for (int id : prov[b])

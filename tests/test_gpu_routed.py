@@ -129,3 +129,52 @@ def test_fp32_side_output(ctx, cin, cout, act, s8_in):
         for p in (x_dev, out_dev, side_dev):
             ctx.free(p)
         layer.close()
+
+
+DW_GATHER_CASES = [
+    ("s2_three_sources", [58, 58, 116], [(0, 0, 8), (1, 0, 7), (2, 0, 58)], 3, 2),
+    ("s1_ranges_mid_group", [116, 232], [(1, 100, 60), (0, 20, 30)], 3, 1),
+    ("k5_s2", [64, 64], [(0, 3, 20), (1, 40, 24)], 5, 2),
+]
+
+
+@pytest.mark.parametrize("name,src_ch,picks,k,stride", DW_GATHER_CASES, ids=[c[0] for c in DW_GATHER_CASES])
+def test_gathered_depthwise_bit_exact(ctx, name, src_ch, picks, k, stride):
+    """A depthwise layer whose channels come from several int8 tensors: it runs over whole 16-channel groups of its sources
+    and writes its output in that order; the logical channels, read back through the reported positions, equal the checker."""
+    from tensor_b200 import ConvInt8, S8_NHWC, nhwc_channels
+    rng = np.random.default_rng(len(name) + k)
+    n, h, w = 2, 23, 37
+    sources = [rng.integers(-127, 128, size=(n, c, h, w), dtype=np.int8) for c in src_ch]
+    chan_src = np.concatenate([np.full(cnt, s) for s, _, cnt in picks]).astype(np.int32)
+    chan_idx = np.concatenate([np.arange(f, f + cnt) for _, f, cnt in picks]).astype(np.int32)
+    perm = rng.permutation(chan_src.size)
+    chan_src, chan_idx = chan_src[perm], chan_idx[perm]
+    C_ = int(chan_src.size)
+    case = ConvCase(name, C_, C_, k, stride=stride, pad=k // 2, groups=C_, n=n, h=h, w=w, int8_scale_term=101, act_type=ACT_RELU,
+                    w_std=0.1, s8_input=True, seed=31).make()
+    case.x_s8 = np.ascontiguousarray(np.stack([sources[s][:, c] for s, c in zip(chan_src, chan_idx)], axis=1))
+    want = run_port(case, 0, want_acc=False)["y"]
+    layer = ConvInt8(ctx, cin=C_, cout=C_, kh=k, kw=k, sh=stride, sw=stride, ph=k // 2, pw=k // 2, groups=C_, bias_term=1,
+                     int8_scale_term=101, act_type=ACT_RELU, rounding=0, weight=case.weight, bias=case.bias, w_scales=case.w_scales,
+                     in_scales=case.in_scales, out_scales=case.out_scales, gathered=(src_ch, chan_src, chan_idx))
+    stored, pos = layer.gathered_layout()
+    assert stored % 16 == 0 and stored >= C_ and len(set(pos.tolist())) == C_ and pos.max() < stored
+    ptrs = []
+    try:
+        for s, c in zip(sources, src_ch):
+            padded = nchw_to_nhwc_padded(s, nhwc_channels(c))
+            padded[..., c:] = -77
+            ptrs.append(ctx.to_device(padded))
+        oh, ow = layer.out_hw(h, w)
+        out_dev = ctx.malloc(n * oh * ow * stored)
+        layer.forward_io(n, h, w, out_dev, S8_NHWC, sources=ptrs)
+        got = ctx.to_host(out_dev, (n, oh, ow, stored), np.int8)
+        ctx.free(out_dev)
+        assert np.array_equal(np.ascontiguousarray(got[..., pos].transpose(0, 3, 1, 2)), want)
+        rest = np.setdiff1d(np.arange(stored), pos)
+        assert not got[..., rest].any()
+    finally:
+        for p in ptrs:
+            ctx.free(p)
+        layer.close()
