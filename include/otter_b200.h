@@ -213,6 +213,11 @@ int ott_add_gather_f32(ott_ctx* ctx, const float* const* a_buffers, const int64_
  * pad_with_zero as in ott_maxpool_f32_nchw. */
 int ott_conv_int8_forward_maxpool(ott_ctx* ctx, const ott_conv* conv, const float* in_dev, int n, int h, int w, int pad_with_zero,
                                   float* out_dev);
+/* The same with the pooled values quantized on the way out: int8 NHWC [n][ph][pw][ott_nhwc_channels(cout)], channel c holding
+ * float2int8(pooled * out_scales[c]): what the quantize pass of a layer reading the pooled blob computes (ConvolutionLayer.cpp:
+ * 763-779). For a layer created with int8_scale_term > 100. */
+int ott_conv_int8_forward_maxpool_s8(ott_ctx* ctx, const ott_conv* conv, const float* in_dev, int n, int h, int w, int pad_with_zero,
+                                     int8_t* out_dev);
 
 /* The same forward on HOST buffers: copies the input to the device, runs, copies the output back and
  * waits for it. This is the call a host-tensor Layer::forward maps to (Tensor/Net.cpp:442). */

@@ -64,6 +64,7 @@ SIGNATURES = {
     "ott_gather_channels_f32": (i32, [vp, vp, vp, i32, vp, i32, i32, i32, vp]),
     "ott_add_gather_f32": (i32, [vp, vp, vp, i32, vp, vp, vp, i32, vp, i32, i32, i32, vp]),
     "ott_conv_int8_forward_maxpool": (i32, [vp, vp, vp, i32, i32, i32, i32, vp]),
+    "ott_conv_int8_forward_maxpool_s8": (i32, [vp, vp, vp, i32, i32, i32, i32, vp]),
     "ott_conv_int8_forward_host": (i32, [vp, vp, vp, i32, i32, i32, i32, vp, i32]),
     "ott_conv_int8_forward_noalloc": (i32, [vp, vp, vp, i32, i32, i32, vp, i32]),
     "ott_launch_count": (C.c_uint64, [vp]),

@@ -667,7 +667,20 @@ int ott_conv_int8_forward_io(ott_ctx* ctx, const ott_conv* c, const ott_conv_io*
                              io->sources ? io->n_sources : 0, io->out_f32_dev ? &mixed : nullptr);
 }
 
+namespace {
+int forward_maxpool_impl(ott_ctx* ctx, const ott_conv* c, const float* in_dev, int n, int h, int w, int pad_with_zero, void* out_dev, int out_dtype);
+}
+
 int ott_conv_int8_forward_maxpool(ott_ctx* ctx, const ott_conv* c, const float* in_dev, int n, int h, int w, int pad_with_zero, float* out_dev) {
+    return forward_maxpool_impl(ctx, c, in_dev, n, h, w, pad_with_zero, out_dev, OTT_F32_NCHW);
+}
+
+int ott_conv_int8_forward_maxpool_s8(ott_ctx* ctx, const ott_conv* c, const float* in_dev, int n, int h, int w, int pad_with_zero, int8_t* out_dev) {
+    return forward_maxpool_impl(ctx, c, in_dev, n, h, w, pad_with_zero, out_dev, OTT_S8_NHWC);
+}
+
+namespace {
+int forward_maxpool_impl(ott_ctx* ctx, const ott_conv* c, const float* in_dev, int n, int h, int w, int pad_with_zero, void* out_dev, int out_dtype) {
     if (!ctx || !c || !in_dev || !out_dev || n < 0 || h <= 0 || w <= 0) return OTT_ERR_INVALID;
     const ott_conv_desc& d = c->d;
     ConvShape s{};
@@ -676,19 +689,21 @@ int ott_conv_int8_forward_maxpool(ott_ctx* ctx, const ott_conv* c, const float* 
     s.ow = out_dim(w, d.kw, d.sw, d.pw, d.dw);
     s.cin = d.cin; s.cout = d.cout; s.cin_pad = c->cin_pad; s.cout_pad = c->cout_pad;
     s.kh = d.kh; s.kw = d.kw; s.sh = d.sh; s.sw = d.sw; s.ph = d.ph; s.pw = d.pw; s.dh = d.dh; s.dw = d.dw;
-    if (d.int8_scale_term > 100 || c->kind != OTT_KERNEL_DENSE_DIRECT || !dense_stem_supports(s, OTT_F32_NCHW, OTT_F32_NCHW) || s.oh < 1 || s.ow < 1)
-        return ctx->fail(OTT_ERR_UNSUPPORTED, "the fused max-pool exists for the 3-channel 3x3 first layer with fp32 output only");
+    if ((d.int8_scale_term > 100) != (out_dtype == OTT_S8_NHWC) || c->kind != OTT_KERNEL_DENSE_DIRECT ||
+        !dense_stem_supports(s, OTT_F32_NCHW, OTT_F32_NCHW) || s.oh < 1 || s.ow < 1)
+        return ctx->fail(OTT_ERR_UNSUPPORTED, "the fused max-pool exists for the 3-channel 3x3 first layer (fp32 output: int8_scale_term < 100, int8: > 100)");
     if (n == 0) return OTT_OK;
     cudaSetDevice(ctx->device);
     EpilogueParams ep{};
     ep.scale_in = c->scale_in_dev; ep.bias = c->bias_dev; ep.scale_out = c->scale_out_dev;
     ep.has_bias = d.bias_term ? 1 : 0;
     ep.act_type = d.act_type; ep.act_param0 = d.act_param0; ep.rounding = d.rounding;
-    OTT_CUDA_CHECK(ctx, launch_dense_stem_pool(ctx->stream, s, in_dev, c->w_host.data(), c->scale_in_host.data(), c->bias_host.data(), c->in_scale0,
-                                                ep, out_dev, pad_with_zero, ctx->status_dev));
+    OTT_CUDA_CHECK(ctx, launch_dense_stem_pool(ctx->stream, s, in_dev, c->w_host.data(), c->scale_in_host.data(), c->bias_host.data(),
+                                                c->scale_out_host.data(), c->in_scale0, ep, out_dev, out_dtype, pad_with_zero, ctx->status_dev));
     ctx->launches += 1;
     return OTT_OK;
 }
+}  // namespace
 
 int ott_gather_channels_f32(ott_ctx* ctx, const float* const* buffers, const int64_t* image_strides, int n_buffers, const uint32_t* plane_refs,
                             int channels, int n, int hw, float* dst_dev) {

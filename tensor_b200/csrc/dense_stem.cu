@@ -139,10 +139,12 @@ constexpr int SP_CX = 2 * SP_PX + 1, SP_CY = 2 * SP_PY + 1;  // convolution outp
 constexpr int SPM_ROWS = 512;                 // im2col rows: 495 convolution pixels rounded up to 4 MMA tiles
 constexpr uint32_t SPM_TMEM_COLS = 128;       // 4 accumulators of 32 columns
 
-template <int S, int ACT>
+// OUT8: the pooled values leave quantized, float2int8(v * scale_out[channel]), as an int8 NHWC tensor (what the quantize pass of
+// the layers reading the pooled blob would compute from the fp32 values) instead of fp32 NCHW planes.
+template <int S, int ACT, bool OUT8>
 __global__ void __launch_bounds__(256)
 dense_stem_pool_mma_kernel(const float* __restrict__ x, const __grid_constant__ StemParams P, float in_scale, int has_bias, float act_p0,
-                           int rounding, float* __restrict__ out, ConvShape s, int ph_out, int pw_out, int tiles_x, int tiles_y, int pad_zero,
+                           int rounding, void* __restrict__ out_any, ConvShape s, int ph_out, int pw_out, int tiles_x, int tiles_y, int pad_zero,
                            uint32_t* __restrict__ status) {
     using namespace umma;
     constexpr int IW = (SP_CX - 1) * S + 3, IH = (SP_CY - 1) * S + 3;
@@ -310,6 +312,36 @@ dense_stem_pool_mma_kernel(const float* __restrict__ x, const __grid_constant__ 
     }
     if (!ok) return;
 
+    if (OUT8) {
+        // thread = (pooled pixel, 4 channels): the 8 threads of a pixel write its 32-byte row, a warp four neighbouring rows
+        int8_t* out8 = static_cast<int8_t*>(out_any);
+        const int quads = s.cout_pad / 4;
+        for (int i = threadIdx.x; i < quads * SP_PY * SP_PX; i += 256) {
+            const int g = i % quads, lx = (i / quads) % SP_PX, ly = i / (quads * SP_PX);
+            const int px = px0 + lx, py = py0 + ly;
+            if (px >= pw_out || py >= ph_out) continue;
+            int q[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int co = g * 4 + j;
+                q[j] = 0;
+                if (co < s.cout) {
+                    const float* cp = conv + (co * SP_CY + 2 * ly) * SP_CX + 2 * lx;
+                    float m = cp[0];
+#pragma unroll
+                    for (int dy = 0; dy < 3; ++dy)
+#pragma unroll
+                        for (int dx = 0; dx < 3; ++dx) m = fmaxf(m, cp[dy * SP_CX + dx]);
+                    const float t = __fmul_rn(m, P.scale_out[co]);
+                    // after ReLU / ReLU6 t >= 0 (scales are positive): trunc(t + 0.5), the saturating pack clamps at 127
+                    q[j] = ((ACT == ACT_RELU || ACT == ACT_RELU6) && rounding == ROUND_ADD_HALF_TRUNC) ? f2i8_nonneg(t) : float2int8(t, rounding);
+                }
+            }
+            *reinterpret_cast<uint32_t*>(out8 + (((long)img * ph_out + py) * pw_out + px) * s.cout_pad + g * 4) = pack_sat_s8x4(q[0], q[1], q[2], q[3]);
+        }
+        return;
+    }
+    float* out = static_cast<float*>(out_any);
     const long pplane = (long)ph_out * pw_out;
     for (int i = threadIdx.x; i < s.cout * SP_PY * SP_PX; i += 256) {
         const int lx = i % SP_PX, ly = (i / SP_PX) % SP_PY, co = i / (SP_PX * SP_PY);
@@ -360,8 +392,8 @@ static void fill_stem_params(StemParams& P, const ConvShape& s, const int8_t* w,
     }
 }
 
-template <int S>
-static cudaError_t launch_pool_s(cudaStream_t stream, const float* x, const StemParams& P, float in_scale, const EpilogueParams& ep, float* out,
+template <int S, bool OUT8>
+static cudaError_t launch_pool_s(cudaStream_t stream, const float* x, const StemParams& P, float in_scale, const EpilogueParams& ep, void* out,
                                  const ConvShape& s, int pad_zero, uint32_t* status) {
     const int ph_out = (s.oh + 2 - 3) / 2 + 1, pw_out = (s.ow + 2 - 3) / 2 + 1;
     const int tiles_x = (pw_out + SP_PX - 1) / SP_PX, tiles_y = (ph_out + SP_PY - 1) / SP_PY;
@@ -372,7 +404,7 @@ static cudaError_t launch_pool_s(cudaStream_t stream, const float* x, const Stem
     const size_t smem = 1024 + (size_t)SPM_ROWS * 32 + 1024 + (size_t)3 * IH * RP * 4 + (size_t)s.cout * SP_CY * SP_CX * 4;
 #define OTT_STEMPOOL_LAUNCH(ACT)                                                                                          \
     {                                                                                                                     \
-        auto kernel = dense_stem_pool_mma_kernel<S, ACT>;                                                                 \
+        auto kernel = dense_stem_pool_mma_kernel<S, ACT, OUT8>;                                                           \
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);            \
         if (e != cudaSuccess) return e;                                                                                   \
         e = launch_overlapped(kernel, dim3((unsigned)blocks), dim3(256), smem, stream, x, P, in_scale, ep.has_bias, ep.act_param0,        \
@@ -391,12 +423,15 @@ static cudaError_t launch_pool_s(cudaStream_t stream, const float* x, const Stem
 
 // first layer (fp32 output) + MaxPool 3x3 s2 p1 of its result; out is [n][cout][(oh+1)/2... pooled] fp32 NCHW
 cudaError_t launch_dense_stem_pool(cudaStream_t stream, const ConvShape& s, const float* x, const int8_t* w_oihw_host, const float* scale_in_host,
-                                   const float* bias_host, float in_scale, const EpilogueParams& ep, float* out, int pad_zero,
-                                   uint32_t* status) {
+                                   const float* bias_host, const float* scale_out_host, float in_scale, const EpilogueParams& ep, void* out,
+                                   int out_dtype, int pad_zero, uint32_t* status) {
     StemParams P{};
-    fill_stem_params(P, s, w_oihw_host, scale_in_host, bias_host, nullptr);
-    return s.sh == 1 ? launch_pool_s<1>(stream, x, P, in_scale, ep, out, s, pad_zero, status)
-                     : launch_pool_s<2>(stream, x, P, in_scale, ep, out, s, pad_zero, status);
+    fill_stem_params(P, s, w_oihw_host, scale_in_host, bias_host, out_dtype == DT_S8_NHWC ? scale_out_host : nullptr);
+    if (out_dtype == DT_S8_NHWC)
+        return s.sh == 1 ? launch_pool_s<1, true>(stream, x, P, in_scale, ep, out, s, pad_zero, status)
+                         : launch_pool_s<2, true>(stream, x, P, in_scale, ep, out, s, pad_zero, status);
+    return s.sh == 1 ? launch_pool_s<1, false>(stream, x, P, in_scale, ep, out, s, pad_zero, status)
+                     : launch_pool_s<2, false>(stream, x, P, in_scale, ep, out, s, pad_zero, status);
 }
 
 // Host-side parameter block: filters OIHW int8 [cout][3][3][3] and the per-channel epilogue vectors.

@@ -75,9 +75,10 @@ cudaError_t launch_dense_stem(cudaStream_t stream, const ConvShape& s, const flo
                               int out_dtype);
 
 // The first layer (fp32 output) and the 3x3 stride-2 pad-1 max-pool that consumes it, in one kernel; out is the pooled
-// fp32 NCHW tensor [n][cout][(oh-1)/2+1][(ow-1)/2+1]. Runs on the tensor cores; status: the word a timed-out wait is reported in.
+// fp32 NCHW tensor [n][cout][(oh-1)/2+1][(ow-1)/2+1], or (out_dtype DT_S8_NHWC) the same values quantized with scale_out_host per
+// channel as an int8 NHWC tensor. Runs on the tensor cores; status: the word a timed-out wait is reported in.
 cudaError_t launch_dense_stem_pool(cudaStream_t stream, const ConvShape& s, const float* x, const int8_t* w_oihw_host, const float* scale_in_host,
-                                   const float* bias_host, float in_scale, const EpilogueParams& ep, float* out, int pad_zero,
-                                   uint32_t* status);
+                                   const float* bias_host, const float* scale_out_host, float in_scale, const EpilogueParams& ep, void* out,
+                                   int out_dtype, int pad_zero, uint32_t* status);
 
 }  // namespace ottk

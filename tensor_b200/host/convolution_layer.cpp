@@ -240,8 +240,9 @@ bool ConvolutionLayer::routable_depthwise_reader() const {
 }
 
 bool ConvolutionLayer::routable_producer() const {
-    return gpu_conv_ && int8_scale_term > 0 && int8_scale_term < 100 && groups == 1 && !fused_maxpool && out_channels <= 1024 &&
-           ott_nhwc_channels(out_channels) >= 32 && ott_conv_int8_kernel_kind(gpu_conv_) == OTT_KERNEL_DENSE_UMMA;
+    if (!gpu_conv_ || int8_scale_term <= 0 || int8_scale_term >= 100 || groups != 1 || ott_nhwc_channels(out_channels) < 32) return false;
+    if (fused_maxpool) return true;  // the first-layer + max-pool kernel: all of its channels or none (routes_all_or_nothing)
+    return out_channels <= 1024 && ott_conv_int8_kernel_kind(gpu_conv_) == OTT_KERNEL_DENSE_UMMA;
 }
 
 // The routed twin of the layer: its input gathered from the producers' int8 tensors and / or its output channels quantized
@@ -293,11 +294,31 @@ int ConvolutionLayer::set_routing(const NetOption& opt, const Routing* plan) {
     return 0;
 }
 
+// An fp32 NCHW tensor of the given logical shape none of whose planes is ever read or written: the blob of a layer all of
+// whose channels travel in the int8 companion (plane tables still need a tensor to point into).
+static Tensor device_shell(const NetOption& opt, std::vector<int64_t> sizes) {
+    void* p = nullptr;
+    if (!opt.gpu || ott_malloc(opt.gpu, 16, &p) != OTT_OK) return Tensor();
+    ott_ctx* ctx = opt.gpu;
+    return Tensor::wrap(p, 16, Device::CUDA, [ctx](void* q) { ott_free(ctx, q); }, std::move(sizes), ScalarType::Float, Layout::NCHW);
+}
+
 int ConvolutionLayer::forward_routed(const Tensor& bottom_blob, Tensor& top_blob, const NetOption& opt) const {
     const Routing& R = routing_;
     const int n = (int)bottom_blob.size(0), h = (int)bottom_blob.size(2), w = (int)bottom_blob.size(3);
     int oh = 0, ow = 0;
     ott_conv_int8_out_shape(gpu_conv_routed_, h, w, &oh, &ow);
+    if (fused_maxpool) {
+        // first layer + max-pool: the pooled values leave quantized for the layers that read the pooled blob
+        if (bottom_blob.is_table() || bottom_blob.scalar_type() != ScalarType::Float || !R.routed_out) return -1;
+        const int ph = (oh - 1) / 2 + 1, pw = (ow - 1) / 2 + 1;
+        Tensor q = device_empty(opt, {n, out_channels, ph, pw}, ScalarType::Byte, Layout::NHWC16);
+        top_blob = device_shell(opt, {n, out_channels, ph, pw});
+        if (!q.defined() || !top_blob.defined()) return -100;
+        top_blob.set_companion(q, R.self_layer);
+        return ott_conv_int8_forward_maxpool_s8(opt.gpu, gpu_conv_routed_, bottom_blob.data_ptr<float>(), n, h, w, fused_maxpool == 2 ? 1 : 0,
+                                                q.data_ptr<int8_t>());
+    }
     ott_conv_io io{};
     std::vector<const int8_t*> srcs;
     Tensor src = bottom_blob;
@@ -347,13 +368,13 @@ int ConvolutionLayer::forward_routed(const Tensor& bottom_blob, Tensor& top_blob
     }
     if (R.routed_out) {
         // the fp32 blob of the layer: only the planes named in f32_mask are written, which are the only ones anyone reads
-        top_blob = device_empty(opt, {n, out_channels, oh, ow}, ScalarType::Float, Layout::NCHW);
+        bool any = false;
+        for (uint32_t m : R.f32_mask) any = any || m != 0u;
+        top_blob = any ? device_empty(opt, {n, out_channels, oh, ow}, ScalarType::Float, Layout::NCHW) : device_shell(opt, {n, out_channels, oh, ow});
         if (!top_blob.defined()) return -100;
         top_blob.set_companion(s8, R.self_layer);
         io.out_dev = s8.raw_data();
         io.out_dtype = OTT_S8_NHWC;
-        bool any = false;
-        for (uint32_t m : R.f32_mask) any = any || m != 0u;
         if (any) {
             io.out_f32_dev = top_blob.data_ptr<float>();
             io.f32_channel_mask = R.f32_mask.data();

@@ -318,6 +318,7 @@ public:
     bool routable_consumer() const;
     bool routable_depthwise_reader() const;
     bool routable_producer() const;
+    bool routes_all_or_nothing() const { return fused_maxpool != 0; }  // no fp32 side output: every channel in int8, or none
 
 private:
     int forward_routed(const Tensor& bottom_blob, Tensor& top_blob, const NetOption& opt) const;

@@ -478,6 +478,12 @@ int Net::plan_routing() {
             for (size_t j = 0; j < l->tops.size(); ++j) prov[(size_t)l->tops[j]] = out[j];
             continue;
         }
+        if (l->absorbed && in.size() == 1 && l->tops.size() == 1 && !in[0].empty()) {
+            // a max-pool computed inside its producer's kernel: its channels are that kernel's output channels
+            glue[li] = 1;
+            prov[(size_t)l->tops[0]] = in[0];
+            continue;
+        }
         for (size_t j = 0; j < l->tops.size(); ++j) {
             const Tensor& shape = blobs_[(size_t)l->tops[j]].shape;
             const int c = shape.defined() && shape.numel() >= 4 ? shape.data_ptr<int>()[1] : 0;
@@ -535,6 +541,12 @@ int Net::plan_routing() {
                 if (ok) sources.insert(pl);
                 for (int r : readers[(size_t)ids[i]])
                     ok = ok && r >= 0 && cand[(size_t)r] && in_scale((size_t)r) == in_scale(li);
+                if (ok && pc->routes_all_or_nothing())  // then every channel of that producer needs readers like these
+                    for (size_t id2 = 0; ok && id2 < origin.size(); ++id2) {
+                        if (origin[id2].first != pl) continue;
+                        ok = !readers[id2].empty();
+                        for (int r : readers[id2]) ok = ok && r >= 0 && cand[(size_t)r] && in_scale((size_t)r) == in_scale(li);
+                    }
             }
             if (ok && sources.size() > 12) ok = false;
             if (ok && cand[li] == kPointwise) {

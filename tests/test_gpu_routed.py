@@ -178,3 +178,38 @@ def test_gathered_depthwise_bit_exact(ctx, name, src_ch, picks, k, stride):
         for p in ptrs:
             ctx.free(p)
         layer.close()
+
+
+@pytest.mark.parametrize("h,w,cout,stride,pad_zero", [(45, 71, 24, 2, 1), (64, 64, 16, 2, 0), (33, 40, 22, 1, 1)])
+def test_first_layer_maxpool_int8_output(ctx, h, w, cout, stride, pad_zero):
+    """The fused first layer + max-pool kernel with quantized output: float2int8(pooled * scale[c]) of exactly the fp32 values
+    its fp32 form stores (that form is checked against the CPU checker elsewhere)."""
+    import ctypes as C
+    from tensor_b200 import ConvInt8, nhwc_channels
+    n = 2
+    case = ConvCase("stem", 3, cout, 3, stride=stride, pad=1, n=n, h=h, w=w, int8_scale_term=2, act_type=ACT_RELU, x_lo=0.0, seed=3).make()
+    rng = np.random.default_rng(h + cout)
+    scales = rng.uniform(5.0, 60.0, cout).astype(np.float32)
+    kw = dict(cin=3, cout=cout, kh=3, kw=3, sh=stride, sw=stride, ph=1, pw=1, bias_term=1, act_type=ACT_RELU, rounding=0, weight=case.weight,
+              bias=case.bias, w_scales=case.w_scales, in_scales=case.in_scales)
+    f32_layer = ConvInt8(ctx, int8_scale_term=2, **kw)
+    s8_layer = ConvInt8(ctx, int8_scale_term=101, out_scales=scales, **kw)
+    oh, ow = f32_layer.out_hw(h, w)
+    ph, pw = (oh - 1) // 2 + 1, (ow - 1) // 2 + 1
+    cp = nhwc_channels(cout)
+    x_dev = ctx.to_device(case.x_f32)
+    f_dev, q_dev = ctx.malloc(n * cout * ph * pw * 4), ctx.malloc(n * ph * pw * cp)
+    try:
+        ctx.check(ctx.lib.ott_conv_int8_forward_maxpool(ctx.h, f32_layer.h, C.c_void_p(x_dev), n, h, w, pad_zero, C.c_void_p(f_dev)))
+        ctx.check(ctx.lib.ott_conv_int8_forward_maxpool_s8(ctx.h, s8_layer.h, C.c_void_p(x_dev), n, h, w, pad_zero, C.c_void_p(q_dev)))
+        pooled = ctx.to_host(f_dev, (n, cout, ph, pw), np.float32)
+        got = ctx.to_host(q_dev, (n, ph, pw, cp), np.int8)
+        t = pooled * scales[None, :, None, None]  # fp32 products, as __fmul_rn
+        want = np.clip(np.trunc(t + np.copysign(np.float32(0.5), t)), -127, 127).astype(np.int8)
+        assert np.array_equal(nhwc_padded_to_nchw(got, cout), want) and np.abs(want).max() > 5
+        assert not got[..., cout:].any()
+    finally:
+        for p in (x_dev, f_dev, q_dev):
+            ctx.free(p)
+        f32_layer.close()
+        s8_layer.close()
