@@ -182,7 +182,13 @@ int ott_conv_int8_gathered_layout(const ott_conv* conv, int* stored_channels, in
  *   out_f32_dev, f32_channel_mask   only with out_dtype OTT_S8_NHWC on the tensor-core kernel, cout <= 1024: output channel c
  *       with bit (c & 31) of f32_channel_mask[c >> 5] set is ALSO stored as the fp32 NCHW plane c of the [n][cout][oh][ow]
  *       tensor out_f32_dev, holding activation(dequantize(acc)), i.e. what the same layer with fp32 output stores; the other
- *       planes of out_f32_dev are not touched. f32_channel_mask is a host array of (cout + 31) / 32 words. */
+ *       planes of out_f32_dev are not touched. f32_channel_mask is a host array of (cout + 31) / 32 words. After
+ *       ott_conv_int8_set_f32_plane_map(conv, plane_of_channel, planes_total) channel c is instead stored as plane
+ *       plane_of_channel[c] of a tensor with planes_total channels (a layer whose output channels were re-ordered).
+ *   chunk_dst, chunk_pitch, n_chunks   scattered int8 output (tensor-core kernel, out_dtype OTT_S8_NHWC; out_dev is ignored):
+ *       output channels 16c..16c+15 of every pixel p are stored at chunk_dst[c] + p * chunk_pitch[c] (NULL: not stored), so that a
+ *       layer whose channels were laid out reader by reader writes each reader's channels straight into that reader's input
+ *       tensor. n_chunks = ott_nhwc_channels(cout) / 16, at most 64; addresses and pitches multiples of 16 bytes. Host arrays. */
 typedef struct ott_conv_io {
     const void* in_dev;
     int in_dtype;
@@ -192,9 +198,13 @@ typedef struct ott_conv_io {
     int out_dtype;
     float* out_f32_dev;
     const uint32_t* f32_channel_mask;
+    int8_t* const* chunk_dst;
+    const uint32_t* chunk_pitch;
+    int n_chunks;
 } ott_conv_io;
 int ott_conv_int8_forward_io(ott_ctx* ctx, const ott_conv* conv, const ott_conv_io* io, int n, int h, int w,
                              uint32_t* status_word_dev);
+int ott_conv_int8_set_f32_plane_map(ott_ctx* ctx, ott_conv* conv, const int* plane_of_channel, int planes_total);
 
 /* Dense fp32 NCHW copy [n][channels][hw] of planes described the same way (for consumers that need one tensor). */
 int ott_gather_channels_f32(ott_ctx* ctx, const float* const* buffers, const int64_t* image_strides, int n_buffers,

@@ -60,6 +60,7 @@ SIGNATURES = {
     "ott_conv_int8_forward_gather": (i32, [vp, vp, vp, vp, i32, vp, i32, i32, i32, vp, i32, vp]),
     "ott_conv_int8_create_gathered": (i32, [vp, C.POINTER(OttConvDesc), vp, vp, vp, vp, i32, vp, i32, i32, vp, vp, vp, C.POINTER(vp)]),
     "ott_conv_int8_gathered_layout": (i32, [vp, C.POINTER(i32), vp, i32]),
+    "ott_conv_int8_set_f32_plane_map": (i32, [vp, vp, vp, i32]),
     "ott_conv_int8_forward_io": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "ott_gather_channels_f32": (i32, [vp, vp, vp, i32, vp, i32, i32, i32, vp]),
     "ott_add_gather_f32": (i32, [vp, vp, vp, i32, vp, vp, vp, i32, vp, i32, i32, i32, vp]),
@@ -109,7 +110,8 @@ SIGNATURES = {
 class OttConvIO(C.Structure):
     """ott_conv_io of include/otter_b200.h"""
     _fields_ = [("in_dev", C.c_void_p), ("in_dtype", C.c_int), ("sources", C.POINTER(C.c_void_p)), ("n_sources", C.c_int),
-                ("out_dev", C.c_void_p), ("out_dtype", C.c_int), ("out_f32_dev", C.c_void_p), ("f32_channel_mask", C.c_void_p)]
+                ("out_dev", C.c_void_p), ("out_dtype", C.c_int), ("out_f32_dev", C.c_void_p), ("f32_channel_mask", C.c_void_p),
+                ("chunk_dst", C.POINTER(C.c_void_p)), ("chunk_pitch", C.c_void_p), ("n_chunks", C.c_int)]
 
 
 _lib = None
@@ -272,8 +274,12 @@ class ConvInt8:
         self.ctx.check(self.ctx.lib.ott_conv_int8_gathered_layout(self.h, C.byref(stored), _np_ptr(pos), pos.size))
         return stored.value, pos
 
+    def set_f32_plane_map(self, plane_of_channel, planes_total: int):
+        m = np.ascontiguousarray(plane_of_channel, dtype=np.int32)
+        self.ctx.check(self.ctx.lib.ott_conv_int8_set_f32_plane_map(self.ctx.h, self.h, _np_ptr(m), planes_total))
+
     def forward_io(self, n, h, w, out_dev: int, out_dtype: int, *, in_dev: int = 0, in_dtype: int = S8_NHWC, sources=None,
-                   out_f32_dev: int = 0, f32_channels=None):
+                   out_f32_dev: int = 0, f32_channels=None, chunk_dst=None, chunk_pitch=None):
         """ott_conv_int8_forward_io: `sources` = device pointers of a gathered layer's int8 inputs; `f32_channels` = output
         channels that are also stored as fp32 planes of out_f32_dev."""
         io = OttConvIO()
@@ -290,6 +296,11 @@ class ConvInt8:
                 mask[c >> 5] |= np.uint32(1 << (c & 31))
             keep.append(mask)
             io.out_f32_dev, io.f32_channel_mask = out_f32_dev, mask.ctypes.data
+        if chunk_dst is not None:
+            arr = (C.c_void_p * len(chunk_dst))(*[C.c_void_p(p) if p else None for p in chunk_dst])
+            pitch = np.ascontiguousarray(chunk_pitch, dtype=np.uint32)
+            keep += [arr, pitch]
+            io.chunk_dst, io.chunk_pitch, io.n_chunks = C.cast(arr, C.POINTER(C.c_void_p)), pitch.ctypes.data, len(chunk_dst)
         self.ctx.check(self.ctx.lib.ott_conv_int8_forward_io(self.ctx.h, self.h, C.byref(io), n, h, w, None))
 
     def out_array(self, n, h, w, out_dtype):

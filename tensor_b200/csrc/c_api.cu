@@ -596,6 +596,7 @@ int ott_conv_int8_destroy(ott_ctx* ctx, ott_conv* c) {
         ctx->alloc->free(c->bias_dev);
         ctx->alloc->free(c->scale_out_dev);
         ctx->alloc->free(c->in_scales_dev);
+        ctx->alloc->free(c->plane_map_dev);
     }
     delete c;
     return OTT_OK;
@@ -653,9 +654,47 @@ int ott_conv_int8_forward_gather(ott_ctx* ctx, const ott_conv* c, const float* c
     return conv_forward_impl(ctx, c, buffers[0], &g, OTT_F32_NCHW, n, h, w, out_dev, out_dtype, status_word_dev);
 }
 
+int ott_conv_int8_set_f32_plane_map(ott_ctx* ctx, ott_conv* c, const int* plane_of_channel, int planes_total) {
+    if (!ctx || !c || !plane_of_channel || planes_total <= 0 || planes_total > 32767) return OTT_ERR_INVALID;
+    std::vector<int16_t> m((size_t)c->cout_pad, 0);
+    for (int i = 0; i < c->d.cout; ++i) {
+        if (plane_of_channel[i] >= planes_total) return ctx->fail(OTT_ERR_INVALID, "plane %d of %d", plane_of_channel[i], planes_total);
+        m[(size_t)i] = (int16_t)(plane_of_channel[i] < 0 ? 0 : plane_of_channel[i]);
+    }
+    ctx->alloc->free(c->plane_map_dev);
+    c->plane_map_dev = nullptr;
+    int rc = upload(ctx, m.data(), m.size() * sizeof(int16_t), (void**)&c->plane_map_dev);
+    if (rc == OTT_OK && cudaStreamSynchronize(ctx->stream) != cudaSuccess) rc = ctx->fail(OTT_ERR_CUDA, "upload failed");
+    if (rc == OTT_OK) c->f32_planes = planes_total;
+    return rc;
+}
+
 int ott_conv_int8_forward_io(ott_ctx* ctx, const ott_conv* c, const ott_conv_io* io, int n, int h, int w, uint32_t* status_word_dev) {
     if (!ctx || !c || !io) return OTT_ERR_INVALID;
     UmmaMixedOut mixed{};
+    void* out_dev = io->out_dev;
+    if (io->n_chunks > 0) {
+        if (!io->chunk_dst || !io->chunk_pitch || io->out_dtype != OTT_S8_NHWC || io->n_chunks != c->cout_pad / 16 || io->n_chunks > 64 ||
+            c->kind != OTT_KERNEL_DENSE_UMMA)
+            return ctx->fail(OTT_ERR_INVALID, "scattered output: int8 launch of the tensor-core kernel, one destination per 16 output channels (at most 64)");
+        mixed.n_chunks = io->n_chunks;
+        for (int i = 0; i < io->n_chunks; ++i) {
+            mixed.dst[i] = io->chunk_dst[i];
+            mixed.pitch[i] = io->chunk_pitch[i];
+            if (mixed.dst[i] && ((reinterpret_cast<uintptr_t>(mixed.dst[i]) | mixed.pitch[i]) & 15u))
+                return ctx->fail(OTT_ERR_INVALID, "scattered output: destinations and pitches must be multiples of 16 bytes");
+            if (mixed.dst[i] && !out_dev) out_dev = mixed.dst[i];
+        }
+        for (int i = 0; i + 1 < io->n_chunks; i += 2)
+            if (mixed.dst[i] && mixed.dst[i + 1] == mixed.dst[i] + 16 && mixed.pitch[i] == mixed.pitch[i + 1] &&
+                ((reinterpret_cast<uintptr_t>(mixed.dst[i]) | mixed.pitch[i]) & 31u) == 0)
+                mixed.pair_ok |= 1ull << (i >> 1);
+        if (!out_dev) return OTT_OK;  // nobody reads any channel in int8
+    }
+    if (c->plane_map_dev && io->out_f32_dev) {
+        mixed.plane_of_col = c->plane_map_dev;
+        mixed.f32_planes = c->f32_planes;
+    }
     if (io->out_f32_dev) {
         if (!io->f32_channel_mask) return ctx->fail(OTT_ERR_INVALID, "out_f32_dev without f32_channel_mask");
         if (c->d.cout > 1024) return ctx->fail(OTT_ERR_UNSUPPORTED, "an fp32 side output is limited to 1024 output channels");
@@ -663,8 +702,8 @@ int ott_conv_int8_forward_io(ott_ctx* ctx, const ott_conv* c, const ott_conv_io*
         for (int i = 0; i < (c->d.cout + 31) / 32 && i < 32; ++i) mixed.mask[i] = io->f32_channel_mask[i];
         if (c->d.cout % 32) mixed.mask[c->d.cout / 32] &= (1u << (c->d.cout % 32)) - 1u;  // never a channel past cout
     }
-    return conv_forward_impl(ctx, c, io->in_dev, nullptr, io->in_dtype, n, h, w, io->out_dev, io->out_dtype, status_word_dev, io->sources,
-                             io->sources ? io->n_sources : 0, io->out_f32_dev ? &mixed : nullptr);
+    return conv_forward_impl(ctx, c, io->in_dev, nullptr, io->in_dtype, n, h, w, out_dev, io->out_dtype, status_word_dev, io->sources,
+                             io->sources ? io->n_sources : 0, (io->out_f32_dev || mixed.n_chunks > 0) ? &mixed : nullptr);
 }
 
 namespace {

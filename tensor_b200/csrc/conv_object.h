@@ -20,6 +20,8 @@ struct ott_conv {
     float* bias_dev = nullptr;
     float* scale_out_dev = nullptr;
     float* in_scales_dev = nullptr;
+    int16_t* plane_map_dev = nullptr;  // optional: fp32 side output, output channel -> plane of a tensor with f32_planes channels
+    int f32_planes = 0;
     // host copies for the kernels that take their parameters by value (stem kernel)
     std::vector<int8_t> w_host;
     std::vector<float> scale_in_host, bias_host, scale_out_host;

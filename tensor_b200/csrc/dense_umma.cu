@@ -257,7 +257,10 @@ dense_umma_kernel(const __grid_constant__ KernelMaps maps, const __grid_constant
             float* out_f32 = nullptr;
             if (OUT == DT_F32_NCHW || (OUT == DT_S8_NHWC && mixed.out_f32 != nullptr)) {
                 const long img = pix / plane, inimg = pix - img * plane;
-                out_f32 = (OUT == DT_F32_NCHW ? reinterpret_cast<float*>(out) : mixed.out_f32) + (img * s.cout + n_tile * P.bn) * plane + inimg;
+                if (OUT == DT_S8_NHWC && mixed.plane_of_col != nullptr)
+                    out_f32 = mixed.out_f32 + img * mixed.f32_planes * plane + inimg;  // plane chosen per column below
+                else
+                    out_f32 = (OUT == DT_F32_NCHW ? reinterpret_cast<float*>(out) : mixed.out_f32) + (img * s.cout + n_tile * P.bn) * plane + inimg;
             }
             // 16 accumulator columns -> 16 outputs of this thread's pixel. int8 results come back as 4 packed words in wds
             // (the caller stores them); the other output kinds are stored here.
@@ -296,7 +299,10 @@ dense_umma_kernel(const __grid_constant__ KernelMaps maps, const __grid_constant
                         if (m != 0u) {
 #pragma unroll
                             for (int j = 0; j < 16; ++j)
-                                if ((m >> j) & 1u) out_f32[(long)(col0 + j) * plane] = y[j];
+                                if ((m >> j) & 1u) {
+                                    const long pl = mixed.plane_of_col != nullptr ? (long)mixed.plane_of_col[c0 + j] : (long)(col0 + j);
+                                    out_f32[pl * plane] = y[j];
+                                }
                         }
                     }
 #pragma unroll
@@ -341,7 +347,20 @@ dense_umma_kernel(const __grid_constant__ KernelMaps maps, const __grid_constant
                 const bool a_ok = n_tile * P.bn + col0 < s.cout_pad, b_ok = two && n_tile * P.bn + col0 + 16 < s.cout_pad;
                 if (a_ok) emit16(va, col0, wa);
                 if (b_ok) emit16(vb, col0 + 16, wb);
-                if (OUT == DT_S8_NHWC) {
+                if (OUT == DT_S8_NHWC && mixed.n_chunks > 0) {
+                    // scattered output: each 16-column chunk has its own destination tensor
+                    const int ch = (n_tile * P.bn + col0) >> 4;
+                    int8_t* da = a_ok ? mixed.dst[ch] : nullptr;
+                    int8_t* db = b_ok ? mixed.dst[ch + 1] : nullptr;
+                    if (da != nullptr && db != nullptr && ((mixed.pair_ok >> (ch >> 1)) & 1ull) != 0ull && (ch & 1) == 0) {
+                        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(da + pix * mixed.pitch[ch]), "r"(wa[0]),
+                                     "r"(wa[1]), "r"(wa[2]), "r"(wa[3]), "r"(wb[0]), "r"(wb[1]), "r"(wb[2]), "r"(wb[3])
+                                     : "memory");
+                    } else {
+                        if (da != nullptr) *reinterpret_cast<uint4*>(da + pix * mixed.pitch[ch]) = make_uint4(wa[0], wa[1], wa[2], wa[3]);
+                        if (db != nullptr) *reinterpret_cast<uint4*>(db + pix * mixed.pitch[ch + 1]) = make_uint4(wb[0], wb[1], wb[2], wb[3]);
+                    }
+                } else if (OUT == DT_S8_NHWC) {
                     if (a_ok && b_ok && wide_ok) {
                         asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(out_s8 + col0), "r"(wa[0]), "r"(wa[1]),
                                      "r"(wa[2]), "r"(wa[3]), "r"(wb[0]), "r"(wb[1]), "r"(wb[2]), "r"(wb[3])

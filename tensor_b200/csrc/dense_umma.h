@@ -50,6 +50,15 @@ struct UmmaSources {
 struct UmmaMixedOut {
     float* out_f32;
     uint32_t mask[32];  // output channels 0..1023
+    // Scattered int8 output (n_chunks > 0): the layer's output columns were laid out reader by reader, and 16-column chunk c
+    // goes to dst[c] + pixel * pitch[c], straight into the input tensor of the layer that reads it (dst NULL: nobody does).
+    // The fp32 planes then use plane_of_col (device array, one entry per output column) inside a tensor of f32_planes channels.
+    int n_chunks;
+    int f32_planes;
+    const int16_t* plane_of_col;
+    int8_t* dst[64];
+    uint32_t pitch[64];
+    unsigned long long pair_ok;  // bit c/2: chunks c and c+1 are 32 contiguous, 32-byte aligned bytes
 };
 
 // OIHW int8 -> [cout_rows][k_total] K-major panel, zero padded (host memory, dst sized cout_rows*k_total).

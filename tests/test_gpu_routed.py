@@ -213,3 +213,62 @@ def test_first_layer_maxpool_int8_output(ctx, h, w, cout, stride, pad_zero):
             ctx.free(p)
         f32_layer.close()
         s8_layer.close()
+
+
+@pytest.mark.parametrize("cin,cout", [(64, 96), (128, 250)])
+def test_scattered_int8_output(ctx, cin, cout):
+    """Every 16-channel chunk of the int8 output goes to its own destination (tensor, channel offset, pitch); fp32 planes of
+    chosen channels go where the plane map says. Same bytes as the plain launch."""
+    from gpu_support import bits
+    from tensor_b200 import S8_NHWC, nhwc_channels
+    rng = np.random.default_rng(cin * cout)
+    n, h, w = 2, 9, 31
+    case = ConvCase("scatter", cin, cout, 1, n=n, h=h, w=w, int8_scale_term=101, act_type=ACT_RELU, s8_input=True, seed=8).make()
+    case.out_scales = np.full(cout, case.out_scales[0], np.float32) * rng.uniform(0.5, 1.5, cout).astype(np.float32)
+    want = run_port(case, 0, want_acc=False)["y"]
+    import copy
+    fcase = copy.copy(case)
+    fcase.int8_scale_term, fcase.out_scales = 1, np.zeros(1, np.float32)
+    want_f32 = run_port(fcase, 0, want_acc=False)["y"]
+    layer = _layer(ctx, case)
+    cp = nhwc_channels(cout)
+    nch, pixels = cp // 16, n * h * w
+    # three destination tensors of different widths; chunks dealt round-robin, one chunk dropped, two neighbours kept adjacent
+    widths = [48, 32 * ((nch + 2) // 3), 16 * nch]
+    bufs = [ctx.malloc(pixels * wd) for wd in widths]
+    for b, wd in zip(bufs, widths):
+        ctx.memset(b, 0x11, pixels * wd)
+    used = [0, 0, 0]
+    dst, pitch, where = [], [], []
+    for c in range(nch):
+        t = 0 if c < 2 else (1 if c % 2 else 2)
+        if c == nch - 1 or used[t] + 16 > widths[t]:
+            dst.append(0); pitch.append(0); where.append(None)
+            continue
+        dst.append(bufs[t] + used[t]); pitch.append(widths[t]); where.append((t, used[t]))
+        used[t] += 16
+    f32_channels = sorted(rng.choice(cout, size=cout // 4, replace=False).tolist())
+    planes_total = cout + 7
+    plane_of = rng.permutation(planes_total)[:cout]
+    layer.set_f32_plane_map(plane_of, planes_total)
+    side = np.full((n, planes_total, h, w), -7.0, np.float32)
+    side_dev = ctx.to_device(side)
+    x_dev = ctx.to_device(nchw_to_nhwc_padded(case.x_s8, nhwc_channels(cin)))
+    try:
+        layer.forward_io(n, h, w, 0, S8_NHWC, in_dev=x_dev, chunk_dst=dst, chunk_pitch=pitch, out_f32_dev=side_dev, f32_channels=f32_channels)
+        got = [ctx.to_host(b, (pixels, wd), np.int8) for b, wd in zip(bufs, widths)]
+        ref = nchw_to_nhwc_padded(want, cp).reshape(pixels, cp)
+        for c, wh in enumerate(where):
+            if wh is not None:
+                assert np.array_equal(got[wh[0]][:, wh[1]:wh[1] + 16], ref[:, 16 * c:16 * c + 16]), c
+        for t in range(3):
+            assert (got[t][:, used[t]:] == 0x11).all()  # nothing written past the chunks placed there
+        got_f32 = ctx.to_host(side_dev, side.shape, np.float32)
+        for c in f32_channels:
+            assert np.array_equal(bits(got_f32[:, plane_of[c]]), bits(want_f32[:, c])), c
+        untouched = np.setdiff1d(np.arange(planes_total), plane_of[f32_channels])
+        assert (got_f32[:, untouched] == -7.0).all()
+    finally:
+        for p in bufs + [side_dev, x_dev]:
+            ctx.free(p)
+        layer.close()
