@@ -628,7 +628,7 @@ def run_net_gpu_arm(args, cfg):
     img_bytes = 3 * H * W * 4
     chunks = [(b0, min(chunk, n - b0)) for b0 in range(0, n, chunk)]
 
-    # one CUDA graph per chunk: the ~70 (ShuffleNetV2) or ~150 (detector) kernels of a forward replay as one launch
+    # one CUDA graph per chunk: the ~56 (ShuffleNetV2) or ~125 (detector) kernels of a forward replay as one launch
     chunk_graphs = [net.capture("data", C.c_void_p(din + b0 * img_bytes), (nb, 3, H, W), outputs) for b0, nb in chunks] if args.graph else None
 
     def step():  # one pass over this GPU's n images, `chunk` images per Net forward, everything resident on the device
