@@ -516,7 +516,9 @@ int conv_create_impl(ott_ctx* ctx, const ott_conv_desc* d, const int8_t* w_oihw,
         int smem_optin = 0;
         cudaDeviceGetAttribute(&smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, ctx->device);
         const int kk = nblocks * kUmmaGatherBlock;
-        if (nblocks > kUmmaMaxGatherBlocks || !umma_plan_layer(kk, d->cout, 1, 1, 1, 1, 1, 1, smem_optin, &c->plan, kUmmaGatherBlock)) {
+        // a stage that holds the whole K extent of a tile when shared memory allows (one barrier round trip per tile)
+        if (nblocks > kUmmaMaxGatherBlocks || (!umma_plan_layer(kk, d->cout, 1, 1, 1, 1, 1, 1, smem_optin, &c->plan, kUmmaGatherBlock, true) &&
+                                               !umma_plan_layer(kk, d->cout, 1, 1, 1, 1, 1, 1, smem_optin, &c->plan, kUmmaGatherBlock, false))) {
             delete c;
             return ctx->fail(OTT_ERR_UNSUPPORTED, "gathered input: %d K blocks do not fit the tensor-core kernel", nblocks);
         }

@@ -93,7 +93,9 @@ dense_umma_kernel(const __grid_constant__ KernelMaps maps, const __grid_constant
     const uint32_t a_stage_bytes = (uint32_t)P.a_stage_bytes, b_tile_bytes = (uint32_t)P.bn * P.bkc;
     // halo mode: the 8 pixels of one tile row are one 8-row operand group; groups (tile rows) are one halo row apart
     const int halo_w = kHaloTw + s.kw - 1, halo_h = kHaloTh + s.kh - 1;
-    const int loads_per_tile = P.halo ? P.ncb : P.nkb;  // pipeline stages one pixel tile consumes
+    // pipeline stages one pixel tile consumes (a gathered layer's stage holds all the K blocks of a tile: one barrier round
+    // trip per tile instead of one per 32-channel block)
+    const int loads_per_tile = P.halo ? P.ncb : (P.gather && P.gather_whole ? 1 : P.nkb);
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < P.stages; ++i) {
@@ -153,7 +155,12 @@ dense_umma_kernel(const __grid_constant__ KernelMaps maps, const __grid_constant
                 for (int kb = 0; kb < loads_per_tile; ++kb, ++it) {
                     const uint32_t st = it % P.stages, ph = (it / P.stages) & 1u;
                     if (!mbar_wait(bar_empty + 8u * st, ph ^ 1u, abort_flag, status, 1u)) { ok = false; break; }
-                    if (P.gather) {
+                    if (P.gather && P.gather_whole) {
+                        mbar_expect_tx(bar_full + 8u * st, (uint32_t)(kTileM * P.bkc * P.nkb));
+                        for (int g = 0; g < P.nkb; ++g)
+                            tma_load_4d(&maps.tm[maps.block_src[g]], bar_full + 8u * st, sA + st * a_stage_bytes + (uint32_t)(g * kTileM * P.bkc),
+                                        (int)maps.block_x[g], x0, 0, 0);
+                    } else if (P.gather) {
                         // K block kb = 32 channels of one of the source tensors (channels past that tensor's end arrive as zeros)
                         mbar_expect_tx(bar_full + 8u * st, (uint32_t)kTileM * P.bkc);
                         tma_load_4d(&maps.tm[maps.block_src[kb]], bar_full + 8u * st, sA + st * a_stage_bytes, (int)maps.block_x[kb], x0, 0, 0);
@@ -206,6 +213,12 @@ dense_umma_kernel(const __grid_constant__ KernelMaps maps, const __grid_constant
                                     accumulate = 1u;
                                 }
                             }
+                        }
+                    } else if (P.gather && P.gather_whole) {
+                        for (int g = 0; g < P.nkb; ++g) {
+                            const uint64_t adesc = make_smem_desc(sA + st * a_stage_bytes + (uint32_t)(g * kTileM * P.bkc), P.bkc);
+                            const uint64_t bdesc = make_smem_desc(sB + g * b_tile_bytes, P.bkc);
+                            for (int j = 0; j < P.bkc / 32; ++j) umma_i8(d, adesc + 2ull * j, bdesc + 2ull * j, P.idesc, (g | j) != 0 ? 1u : 0u);
                         }
                     } else {
                         const uint64_t adesc = make_smem_desc(sA + st * a_stage_bytes, P.bkc);
@@ -444,7 +457,8 @@ const char* launch_variant(cudaStream_t stream, int sm_count, const KernelMaps& 
 
 static int round_up(int a, int b) { return (a + b - 1) / b * b; }
 
-bool umma_plan_layer(int cin, int cout, int kh, int kw, int sh, int sw, int dh, int dw, int smem_budget, UmmaPlan* plan, int bkc_override) {
+bool umma_plan_layer(int cin, int cout, int kh, int kw, int sh, int sw, int dh, int dw, int smem_budget, UmmaPlan* plan, int bkc_override,
+                     bool whole_tile_stages) {
     UmmaPlan p{};
     const int cin_pad = nhwc_channels(cin), cout_pad = nhwc_channels(cout);
     if (sh != 1 || sw != 1) return false;  // strided dense convolutions go to the direct kernel
@@ -458,7 +472,10 @@ bool umma_plan_layer(int cin, int cout, int kh, int kw, int sh, int sw, int dh, 
     // largest BN (multiple of 16, <= 256) whose weight panel leaves room for at least 3 A stages,
     // preferring a split of cout_pad into equal tiles
     p.halo = (p.taps > 1 && dh == 1 && dw == 1) ? 1 : 0;
-    const long a_stage = p.halo ? ((long)p.bkc * (kHaloTw + kw - 1) * (kHaloTh + kh - 1) + 1023) / 1024 * 1024 : (long)kTileM * p.bkc;
+    const bool whole = whole_tile_stages && !p.halo && p.taps == 1;
+    p.gather_whole = whole ? 1 : 0;
+    const long a_stage = p.halo ? ((long)p.bkc * (kHaloTw + kw - 1) * (kHaloTh + kh - 1) + 1023) / 1024 * 1024
+                                : (long)kTileM * p.bkc * (whole ? p.nkb : 1);
     p.a_stage_bytes = (int)a_stage;
     const long avail = (long)smem_budget - 1024 /*alignment slack*/ - 4096 /*barriers + epilogue parameters*/ - 3 * a_stage;
     if (avail <= 0) return false;
@@ -475,7 +492,7 @@ bool umma_plan_layer(int cin, int cout, int kh, int kw, int sh, int sw, int dh, 
     if (p.stages > 8) p.stages = 8;
     // Small layers (few k-blocks, narrow panels) are latency-bound with one CTA per SM: keep the pipeline short so that
     // several CTAs fit an SM and overlap each other's TMA / MMA / epilogue latencies.
-    if (p.nkb <= 2 && p.stages > 4) p.stages = 4;
+    if ((p.nkb <= 2 || whole) && p.stages > 4) p.stages = 4;
     // a halo stage feeds all the taps of a whole pixel tile and channel block: three are a deep enough pipeline
     if (p.halo && p.stages > 3) p.stages = 3;
     if (p.stages < 2) return false;

@@ -24,14 +24,15 @@ struct UmmaPlan {
     int a_stage_bytes;  // bytes of one activation stage (a 128-pixel tile, or a halo tile rounded up to 1 KiB)
     int flat;                          // 1x1: activations viewed as one [pixels, channels] matrix
     int gather;                        // > 0: the K blocks come from this many int8 NHWC tensors (see UmmaSources)
+    int gather_whole;                  // gathered layer whose pipeline stage holds all the K blocks of a pixel tile
     int tw, th, tiles_x, tiles_y, m_tiles;  // 128-pixel output rectangles (tw*th == 128)
 };
 
 // Decide whether the tensor-core kernel takes this layer and how it tiles it. smem_budget = opt-in
 // shared memory per block of the device. bkc_override (32/64/128) fixes the channel-block width instead of deriving it
-// from cin.
+// from cin. whole_tile_stages (1x1 layers): one pipeline stage holds all the K blocks of a pixel tile.
 bool umma_plan_layer(int cin, int cout, int kh, int kw, int sh, int sw, int dh, int dw, int smem_budget, UmmaPlan* plan,
-                     int bkc_override = 0);
+                     int bkc_override = 0, bool whole_tile_stages = false);
 
 // A 1x1 layer whose input channels are spread over several int8 NHWC tensors (each written by one producer layer): K block
 // kb of the implicit GEMM is the 32 channels starting at block_x[kb] of tensor block_src[kb]. The layer's weights are laid
