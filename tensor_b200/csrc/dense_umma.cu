@@ -493,6 +493,7 @@ bool umma_plan_layer(int cin, int cout, int kh, int kw, int sh, int sw, int dh, 
     // Small layers (few k-blocks, narrow panels) are latency-bound with one CTA per SM: keep the pipeline short so that
     // several CTAs fit an SM and overlap each other's TMA / MMA / epilogue latencies.
     if ((p.nkb <= 2 || whole) && p.stages > 4) p.stages = 4;
+    if (whole && p.stages > 2) p.stages = 2;  // two whole tiles in flight, and room for a second CTA on the SM
     // a halo stage feeds all the taps of a whole pixel tile and channel block: three are a deep enough pipeline
     if (p.halo && p.stages > 3) p.stages = 3;
     if (p.stages < 2) return false;
