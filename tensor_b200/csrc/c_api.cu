@@ -517,8 +517,13 @@ int conv_create_impl(ott_ctx* ctx, const ott_conv_desc* d, const int8_t* w_oihw,
         cudaDeviceGetAttribute(&smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, ctx->device);
         const int kk = nblocks * kUmmaGatherBlock;
         // a stage that holds the whole K extent of a tile when shared memory allows (one barrier round trip per tile)
-        if (nblocks > kUmmaMaxGatherBlocks || (!umma_plan_layer(kk, d->cout, 1, 1, 1, 1, 1, 1, smem_optin, &c->plan, kUmmaGatherBlock, true) &&
-                                               !umma_plan_layer(kk, d->cout, 1, 1, 1, 1, 1, 1, smem_optin, &c->plan, kUmmaGatherBlock, false))) {
+        // (unless that would cost weight panels: every extra panel fetches the activations once more)
+        ottk::UmmaPlan per_block{}, per_tile{};
+        const bool ok_block = nblocks <= kUmmaMaxGatherBlocks && umma_plan_layer(kk, d->cout, 1, 1, 1, 1, 1, 1, smem_optin, &per_block, kUmmaGatherBlock, false);
+        const bool ok_tile = nblocks <= kUmmaMaxGatherBlocks && umma_plan_layer(kk, d->cout, 1, 1, 1, 1, 1, 1, smem_optin, &per_tile, kUmmaGatherBlock, true);
+        if (ok_tile && (!ok_block || per_tile.n_tiles <= per_block.n_tiles)) c->plan = per_tile;
+        else if (ok_block) c->plan = per_block;
+        if (!ok_tile && !ok_block) {
             delete c;
             return ctx->fail(OTT_ERR_UNSUPPORTED, "gathered input: %d K blocks do not fit the tensor-core kernel", nblocks);
         }

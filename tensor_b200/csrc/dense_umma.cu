@@ -477,7 +477,7 @@ bool umma_plan_layer(int cin, int cout, int kh, int kw, int sh, int sw, int dh, 
     const long a_stage = p.halo ? ((long)p.bkc * (kHaloTw + kw - 1) * (kHaloTh + kh - 1) + 1023) / 1024 * 1024
                                 : (long)kTileM * p.bkc * (whole ? p.nkb : 1);
     p.a_stage_bytes = (int)a_stage;
-    const long avail = (long)smem_budget - 1024 /*alignment slack*/ - 4096 /*barriers + epilogue parameters*/ - 3 * a_stage;
+    const long avail = (long)smem_budget - 1024 /*alignment slack*/ - 4096 /*barriers + epilogue parameters*/ - (whole ? 2 : 3) * a_stage;
     if (avail <= 0) return false;
     long bn_max = avail / k_total;
     bn_max = bn_max > 256 ? 256 : bn_max;
