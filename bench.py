@@ -34,6 +34,7 @@ import numpy as np
 
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
+sys.path.insert(1, str(ROOT / "tests"))  # graph_walk (activation-scale calibration, output self-check) and the checker bindings
 
 ACT_NONE, ACT_RELU, ACT_LRELU, ACT_RELU6 = 0, 1, 2, 3
 
@@ -211,9 +212,15 @@ class _Desc(C.Structure):
                                        "int8_scale_term", "act_type")] + [("act_param0", C.c_float)]
 
 
+def cpu_threads():
+    """Host threads the CPU arm runs on: every core this process may use, whatever OMP_NUM_THREADS the launcher exported
+    (torchrun sets it to 1 for its workers)."""
+    return max(1, len(os.sched_getaffinity(0)))
+
+
 def cpu_reference_time(wl, images, warmup=1, iters=None, packed=1, force_port=False):
     """Time the reference's CPU int8 ConvolutionLayer on `images` single-image forwards (its int8 path is
-    batch-1), all host threads. Returns (seconds per image, kind, cores)."""
+    batch-1), on cpu_threads() OpenMP threads (set explicitly). Returns (seconds per image, kind, cores)."""
     ref_so = ROOT / "oracle" / "_ref" / "libotter_ref.so"
     port_so = ROOT / "oracle" / "_build" / "libotter_oracle.so"
     weight, bias, w_scales, in_scales, out_scales = make_layer_arrays(wl)
@@ -231,6 +238,9 @@ def cpu_reference_time(wl, images, warmup=1, iters=None, packed=1, force_port=Fa
         lib = C.CDLL(str(ref_so))
         lib.ref_conv_int8_time_ms.restype = C.c_double
         lib.ref_max_threads.restype = C.c_int
+        lib.ref_set_threads.argtypes = [C.c_int]
+        lib.ref_set_threads.restype = None
+        lib.ref_set_threads(cpu_threads())
         cores = lib.ref_max_threads()
         mean = C.c_double()
         best = lib.ref_conv_int8_time_ms(C.byref(d), fp(weight, C.c_int8), fp(bias, C.c_float), fp(w_scales, C.c_float), fp(in_scales, C.c_float),
@@ -243,6 +253,9 @@ def cpu_reference_time(wl, images, warmup=1, iters=None, packed=1, force_port=Fa
         subprocess.run(["make", "-s", "-C", str(ROOT / "oracle"), "port"], check=True)
     lib = C.CDLL(str(port_so))
     lib.orc_max_threads.restype = C.c_int
+    lib.orc_set_threads.argtypes = [C.c_int]
+    lib.orc_set_threads.restype = None
+    lib.orc_set_threads(cpu_threads())
     cores = lib.orc_max_threads()
     oh, ow = out_hw(wl)
     y8 = np.empty((1, wl["cout"], oh, ow), np.int8)
@@ -554,6 +567,7 @@ def run_net_reference_arm(args, cfg):
 def build_calibrated_net(cfg, batch, device, seed=0x0771E5):
     """The workload's Net on `device` with seeded weights and activation scales calibrated on one synthetic image, the
     convolutions of the calibration walk running through the GPU library's own layer objects."""
+    from graph_walk import calibrate
     from tensor_b200 import F32_NCHW, S8_NHWC, ConvInt8, Context, Net, graphs, nhwc_channels as nc
     layers = graph_layers(cfg, batch)
     params = graphs.make_params(layers, seed)
@@ -576,14 +590,98 @@ def build_calibrated_net(cfg, batch, device, seed=0x0771E5):
             if term > 100:
                 y = np.ascontiguousarray(y[..., :g["cout"]].transpose(0, 3, 1, 2))
             return y
-        graphs.calibrate(layers, params, x1, conv)
+        calibrate(layers, params, x1, conv)
     net = Net(device)
     for l in layers:
         net.add_layer(**l)
     net.compile()
     for name, p in params.items():
         net.set_conv_params(name, p["weight"], p["bias"], p["w_scales"], p["in_scales"], p["out_scales"])
-    return net, layers
+    return net, layers, params
+
+
+def checker_outputs(layers, params, x, outputs):
+    """The graph on host images x through the layer-by-layer CPU checker (C restatement of the reference's int8 layer,
+    numpy glue layers): what every output blob must equal bit for bit. Used outside the timed regions only."""
+    from graph_support import oracle_conv, oracle_upsample
+    from graph_walk import walk
+    return walk(layers, np.ascontiguousarray(x), oracle_conv(params), want=list(outputs), upsample_fn=oracle_upsample)
+
+
+def kernel_records(device, names, int8_peak, hbm_peak, steps=10, warmup=3):
+    """The single-layer configurations as one record each: the layer's convolution kernel timed alone with CUDA events
+    on the context's stream (input resident in HBM and larger than L2 together with the output), against the roof that
+    bounds it: the measured int8 GEMM peak when 2*ops/bytes * HBM peak exceeds it, else the measured HBM peak."""
+    from tensor_b200 import F32_NCHW, S8_NHWC, ConvInt8, Context
+    out = {}
+    with Context(device) as ctx:
+        lib = ctx.lib
+        for name in names:
+            wl = WORKLOADS[name]
+            n = wl["n"]
+            oh, ow = out_hw(wl)
+            weight, bias, w_scales, in_scales, out_scales = make_layer_arrays(wl)
+            layer = ConvInt8(ctx, cin=wl["cin"], cout=wl["cout"], kh=wl["k"], kw=wl["k"], sh=wl["stride"], sw=wl["stride"], ph=wl["pad"],
+                             pw=wl["pad"], groups=wl["groups"], bias_term=1, int8_scale_term=wl["term"], act_type=wl["act"], weight=weight,
+                             bias=bias, w_scales=w_scales, in_scales=in_scales, out_scales=out_scales)
+            in_dtype = F32_NCHW if wl["in_f32"] else S8_NHWC
+            out_dtype = S8_NHWC if wl["term"] > 100 else F32_NCHW
+            if wl["in_f32"]:
+                img_shape, in_np = (wl["cin"], wl["h"], wl["w"]), np.float32
+            else:
+                img_shape, in_np = (wl["h"], wl["w"], nhwc_channels(wl["cin"])), np.int8
+            img_bytes = int(np.prod(img_shape)) * np.dtype(in_np).itemsize
+            out_bytes = n * oh * ow * (nhwc_channels(wl["cout"]) if out_dtype == S8_NHWC else wl["cout"] * 4)
+            din, dout = ctx.malloc(n * img_bytes), ctx.malloc(out_bytes)
+            rng = np.random.default_rng(99)
+            # eight distinct random images, repeated over the batch (the kernels' time does not depend on the values)
+            for i in range(min(n, 8)):
+                if wl["in_f32"]:
+                    a = rng.random(size=img_shape, dtype=np.float32) * 2.0 - 1.0
+                else:
+                    a = rng.integers(-127, 128, size=img_shape, dtype=np.int8)
+                    a[..., wl["cin"]:] = 0
+                for j in range(i, n, 8):
+                    ctx.check(lib.ott_memcpy_h2d(ctx.h, C.c_void_p(din + j * img_bytes), a.ctypes.data_as(C.c_void_p), img_bytes))
+                ctx.sync()
+            fused = layer.kernel_kind == 1  # the tiled depthwise kernel quantizes fp32 input itself
+            src, src_dtype, dq = din, in_dtype, None
+            if wl["in_f32"] and not fused:
+                dq = ctx.malloc(n * wl["h"] * wl["w"] * nhwc_channels(wl["cin"]))
+                ctx.quantize(din, n, wl["cin"], wl["h"], wl["w"], in_scales, 0, dq)
+                src, src_dtype = dq, S8_NHWC
+            for _ in range(warmup):
+                layer.forward(src, src_dtype, n, wl["h"], wl["w"], dout, out_dtype)
+            ctx.sync()
+            e0, e1 = ctx.event(), ctx.event()
+            ctx.record(e0)
+            for _ in range(steps):
+                layer.forward(src, src_dtype, n, wl["h"], wl["w"], dout, out_dtype)
+            ctx.record(e1)
+            ctx.sync()
+            ms = ctx.elapsed_ms(e0, e1) / steps
+            ops, byts = algorithmic_work(wl if fused else {**wl, "in_f32": False}, n)
+            tops, gbs = ops / (ms * 1e-3) / 1e12, byts / (ms * 1e-3) / 1e9
+            tensor_bound = int8_peak is not None and (ops / byts) * hbm_peak / 1e3 >= int8_peak
+            rec = {"kernel": {1: "depthwise_tiled_kernel", 2: "dense_umma_kernel", 3: "dense_direct_kernel"}[layer.kernel_kind],
+                   "ms": ms, "tops": tops, "gbs": gbs, "ops": ops, "algorithmic_bytes": byts, "launches_timed": steps,
+                   "input": "fp32 NCHW" if (wl["in_f32"] and fused) else "int8 NHWC", "output": "int8 NHWC" if wl["term"] > 100 else "fp32 NCHW",
+                   "bound": "tensor" if tensor_bound else "hbm",
+                   "frac": tops / int8_peak if tensor_bound else gbs / hbm_peak}
+            if int8_peak:
+                rec["frac_of_int8_peak"] = tops / int8_peak
+            rec["frac_of_hbm_peak"] = gbs / hbm_peak
+            out[name] = rec
+            layer.close()
+            for p_ in (din, dout, dq):
+                if p_:
+                    ctx.free(p_)
+            lib.ott_alloc_release_cached(ctx.h)
+    return out
+
+
+KERNEL_RECORD_WORKLOADS = ("pw_512_1024_hw56_s8", "pw_256_512_hw56_s8", "pw_64_256_hw56_s8", "dense3x3_64_hw56_n256_s8", "dw3x3s1_c256",
+                           "dw3x3s2_c256", "dw3x3s1_c256_s8", "dw3x3s2_c256_s8")
 
 
 def run_net_gpu_arm(args, cfg):
@@ -605,7 +703,7 @@ def run_net_gpu_arm(args, cfg):
     n = args.batch or (cfg["total"] // world if strong else cfg["batch"])  # images per GPU and step
     chunk = min(args.chunk or cfg["chunk"], n)
     outputs = list(cfg["outputs"])
-    net, layers = build_calibrated_net(cfg, chunk, local_rank)
+    net, layers, params = build_calibrated_net(cfg, chunk, local_rank)
     ctx = net.context()
     lib = ctx.lib
     _, macs = graphs.conv_input_hw(layers, H, W)
@@ -651,18 +749,38 @@ def run_net_gpu_arm(args, cfg):
     if rank == 0:
         sampler.start()
         time.sleep(0.25)
-    e0, e1 = ctx.event(), ctx.event()
-    l0 = ctx.launch_count()
-    barrier()
-    ctx.record(e0)
-    for _ in range(args.steps):
-        step()
-    ctx.record(e1)
-    barrier()
-    step_ms = ctx.elapsed_ms(e0, e1) / args.steps
-    launches = ctx.launch_count() - l0
+    # The K-step region is timed `repeats` times back to back (events on the Net's stream, a barrier around each); the
+    # reported step time is the median repeat, so that a change of a per cent or two shows above the run-to-run noise.
+    repeat_ms, launches = [], 0
+    for _ in range(max(1, args.repeats)):
+        e0, e1 = ctx.event(), ctx.event()
+        l0 = ctx.launch_count()
+        barrier()
+        ctx.record(e0)
+        for _ in range(args.steps):
+            step()
+        ctx.record(e1)
+        barrier()
+        repeat_ms.append(ctx.elapsed_ms(e0, e1) / args.steps)
+        launches = ctx.launch_count() - l0
+    repeat_ms = max_over_ranks(repeat_ms, dist)  # per repeat, the slowest rank
+    step_ms = float(np.median(repeat_ms))
     clocks = sampler.stop() if rank == 0 else None
 
+    # Output self-check, outside every timed region: the first and the last image of this rank's batch, as the replayed
+    # graphs left them on the device, against the layer-by-layer CPU checker, bit for bit.
+    parity = None
+    if chunk_graphs and not args.no_check:
+        check_imgs = sorted({0, n - 1})
+        want = [checker_outputs(layers, params, host_in[i:i + 1], outputs) for i in check_imgs]
+        parity = True
+        for ci, i in enumerate(check_imgs):
+            gi, off = i // chunk, i % chunk
+            for oi, o in enumerate(outputs):
+                dptr, shp = chunk_graphs[gi].output(oi)
+                per = int(np.prod(shp[1:]))
+                got = ctx.to_host(dptr + off * per * 4, (1,) + tuple(shp[1:]), np.float32)
+                parity = parity and bool(np.array_equal(got.view(np.int32), want[ci][o].view(np.int32)))
     # per-layer device times of one chunk (events around every layer; serialised) -> the dominant layer kind and its share.
     # One profiling pass per output blob; a layer that several outputs need is counted once (its longest time).
     cshape = (chunks[0][1], 3, H, W)
@@ -684,10 +802,33 @@ def run_net_gpu_arm(args, cfg):
     barrier()
     e2e_s = (time.perf_counter() - t0) / e2e_steps
 
-    step_ms, e2e_s = max_over_ranks([step_ms, e2e_s], dist)
+    parity_e2e = None
+    if parity is not None:
+        parity_e2e = True
+        for ci, i in enumerate(check_imgs):
+            for oi, (o, e) in enumerate(zip(outputs, out_elems)):
+                got = np.ctypeslib.as_array(C.cast(houts[oi], C.POINTER(C.c_float)), shape=(n, e))[i]
+                parity_e2e = parity_e2e and bool(np.array_equal(got.view(np.int32), want[ci][o].reshape(-1).view(np.int32)))
+    if dist is not None and parity is not None:  # every rank checks its own shard; the line carries the conjunction
+        import torch
+        flags = torch.tensor([int(parity), int(parity_e2e)], device="cuda")
+        dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+        parity, parity_e2e = bool(flags[0].item()), bool(flags[1].item())
+    (e2e_s,) = max_over_ranks([e2e_s], dist)
     value = whole_job_rate(n, world, step_ms)
+    int8_peak, kernels = None, None
+    if rank == 0 and world == 1 and not args.no_peak:
+        try:
+            int8_peak = int8_tensor_peak_tops()
+        except Exception as e:  # informative, never required
+            print(f"int8 peak measurement skipped: {e}", file=sys.stderr)
     if rank == 0:
         hbm_peak, hbm_src = measured_peaks()
+        if world == 1 and not args.no_kernels:
+            # the other half of the metric: the single-layer configurations' kernels against their roofs, same process, after
+            # the graph steps (the Net's buffers are released first)
+            lib.ott_alloc_release_cached(ctx.h)
+            kernels = kernel_records(local_rank, KERNEL_RECORD_WORKLOADS, int8_peak, hbm_peak)
         geo = graphs.conv_geometry(layers)
         hws, _ = graphs.conv_input_hw(layers, H, W)
         by_type = {}
@@ -726,6 +867,9 @@ def run_net_gpu_arm(args, cfg):
                 "peak_source": hbm_src, "kernel": f"{kernels}: the {dom_layers} {dom} layers of the graph",
                 "kernel_ms": dom_ms / dom_layers, "algorithmic_bytes_per_launch": dom_bytes / dom_layers, "ops_per_launch": dom_ops / dom_layers,
                 "launches_per_step": dom_layers,
+                "timed": "serialised per-layer pass (CUDA events around every layer of one forward, kernels launched one by one: no graph "
+                         "replay, no overlap between consecutive kernels); the headline step is the replayed graph",
+                "frac_scaled_to_timed_step": (dom_bytes / (by_type[dom] / total_prof * step_ms * 1e-3) / 1e9) / hbm_peak,
                 "time_share_by_layer_kind": {k: round(v / total_prof, 4) for k, v in sorted(by_type.items(), key=lambda kv: -kv[1])},
                 "profiled_ms_per_step": total_prof,
                 "top_layers_ms": [[nm_, round(ms_, 4)] for _, nm_, ms_ in sorted(prof, key=lambda p: -p[2])[:12]]}
@@ -740,7 +884,10 @@ def run_net_gpu_arm(args, cfg):
                              f"layers, {how['port']} depthwise layers with C%8!=0 on the C restatement); glue layers not included"}
         print(json.dumps({
             "metric": cfg["metric"], "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong" if strong else "weak",
+            "warmup": args.warmup, "ms_per_step": step_ms, "repeats": len(repeat_ms), "repeat_ms_per_step": [round(v, 5) for v in repeat_ms],
+            "parity_checked": parity, "parity_checked_e2e": parity_e2e,
+            "parity_check": None if parity is None else f"images {check_imgs} of rank 0's batch (every rank checks its own), outputs {outputs}, bit for bit against the layer-by-layer CPU checker",
+            "higher_is_better": True, "scaling": "strong" if strong else "weak",
             "vs_baseline": None, "dtype": "s8xs8->s32", "data": "synthetic",
             "config": {"workload": args.workload, "graph": cfg["title"], "batch_per_gpu": n, "images_per_forward": chunk,
                        "input": f"3x{H}x{W} fp32 NCHW",
@@ -752,6 +899,8 @@ def run_net_gpu_arm(args, cfg):
             "e2e": {"value": n * world / e2e_s, "unit": "images/s", "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes,
                     "ms_per_step": e2e_s * 1e3, "steps": e2e_steps},
             "roofline": roof, "cpu_baseline": cpu,
+            "int8_peak": None if int8_peak is None else {"tops": int8_peak, "how": "torch._int_mm 8192^3 int8 (cuBLASLt), best of 10, CUDA events, same process"},
+            "kernels": kernels,
         }))
     for g in chunk_graphs or []:
         g.close()
@@ -774,6 +923,9 @@ def main():
     ap.add_argument("--no-graph", dest="graph", action="store_false", help="graph workloads: launch every kernel of a forward separately "
                     "instead of replaying the captured CUDA graph")
     ap.add_argument("--no-peak", action="store_true", help="skip the live int8 GEMM peak measurement")
+    ap.add_argument("--repeats", type=int, default=5, help="graph workloads: how many times the K-step region is timed (the median is reported)")
+    ap.add_argument("--no-check", action="store_true", help="graph workloads: skip the bit-for-bit output self-check against the CPU checker")
+    ap.add_argument("--no-kernels", action="store_true", help="graph workloads: skip the single-layer kernel records")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.workload in NET_WORKLOADS:

@@ -74,6 +74,20 @@ const char* ott_last_error(const ott_ctx* ctx); /* never NULL; valid until the n
 void* ott_ctx_stream(ott_ctx* ctx);             /* the cudaStream_t every call on ctx is ordered on */
 int ott_sync(ott_ctx* ctx);
 
+/* Failure detection (no counterpart in the reference, whose CPU kernels cannot wait on anything). Every wait inside a kernel
+ * (on an mbarrier that a TMA copy or an MMA completes) is bounded: when the limit passes the kernel gives up, frees what it
+ * holds, and ORs a code into the context's status word; the next ott_sync (or *_host call) then returns OTT_ERR_DEVICE_WAIT,
+ * names the word in ott_last_error, and clears it, and the context stays usable. The limit is 2000 ms per wait unless changed
+ * here (calls enqueued afterwards use the new value). */
+int ott_set_wait_limit_ms(ott_ctx* ctx, int ms);
+/* Test hooks for the failure paths; neither touches a GPU in a way that can fault it.
+ * ott_debug_wait_probe enqueues a one-CTA kernel whose only wait can never complete (nobody arrives on its barrier), so
+ * it runs out after the context's wait limit and reports through the status word like the real kernels.
+ * ott_debug_fail_alloc_after makes the n-th allocation of the context's allocator from now on fail on the host
+ * (cudaErrorMemoryAllocation without calling cudaMalloc); n <= 0 switches the injection off. */
+int ott_debug_wait_probe(ott_ctx* ctx);
+int ott_debug_fail_alloc_after(ott_ctx* ctx, int n);
+
 /* Stream-ordered, size-keyed caching allocator: a freed block is handed back to the next request of the
  * same rounded size without touching cudaMalloc (the policy of CPUCachingAllocator::allocate/free,
  * Tensor/CPUCachingAllocator.hpp:62-70, moved to device memory). */
@@ -301,8 +315,13 @@ int ott_nanodet_detect(ott_ctx* ctx, const float* const* heads_dev, const int* g
  *   - Input is fp32 NCHW on the device; output as for ott_conv_int8_forward; the caller owns both.
  *   - n*h*w*ott_nhwc_channels(cin) must fit OTT_NOALLOC_SCRATCH_BYTES; larger calls fail with
  *     OTT_ERR_INVALID and a message naming both sizes (split the batch, or use the ordinary forward).
- *   - The first call on each GPU looks up the array's device address (cudaGetSymbolAddress); make that
- *     first call before starting any stream capture.
+ *   - The first call on each GPU looks up the array's device address (cudaGetSymbolAddress). With CUDA's
+ *     default lazy module loading that look-up is also the moment the module holding the array is loaded
+ *     onto that GPU, i.e. when its OTT_NOALLOC_SCRATCH_BYTES are reserved; it can synchronise the device and
+ *     it can fail for lack of memory. So make one call per GPU during start-up: before the pools are
+ *     carved, before the latency-bound loop begins, and before starting any stream capture.
+ *   - A call that the layer would refuse (a layer created with gathered input, an output type the layer
+ *     does not produce, an empty output) fails before anything is launched or the array is touched.
  *   - All calls on one GPU share the one array. It keeps whatever the last call left; this entry point
  *     overwrites every byte it later reads, so nothing has to be cleared. Two calls whose kernels can be
  *     in flight on the same GPU at once (different contexts or streams) race on it: serialise them. */

@@ -35,6 +35,9 @@ SIGNATURES = {
     "ott_last_error": (C.c_char_p, [vp]),
     "ott_ctx_stream": (vp, [vp]),
     "ott_sync": (i32, [vp]),
+    "ott_set_wait_limit_ms": (i32, [vp, i32]),
+    "ott_debug_wait_probe": (i32, [vp]),
+    "ott_debug_fail_alloc_after": (i32, [vp, i32]),
     "ott_malloc": (i32, [vp, sz, C.POINTER(vp)]),
     "ott_free": (i32, [vp, vp]),
     "ott_alloc_stats": (i32, [vp, u64p, u64p, u64p, u64p]),

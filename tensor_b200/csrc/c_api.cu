@@ -123,6 +123,26 @@ int ott_sync(ott_ctx* ctx) {
     return check_status_word(ctx);
 }
 
+int ott_set_wait_limit_ms(ott_ctx* ctx, int ms) {
+    if (!ctx || ms <= 0) return OTT_ERR_INVALID;
+    ctx->wait_limit_ns = (unsigned long long)ms * 1000000ull;
+    return OTT_OK;
+}
+
+int ott_debug_fail_alloc_after(ott_ctx* ctx, int n) {
+    if (!ctx) return OTT_ERR_INVALID;
+    ctx->alloc->fail_after(n);
+    return OTT_OK;
+}
+
+int ott_debug_wait_probe(ott_ctx* ctx) {
+    if (!ctx) return OTT_ERR_INVALID;
+    cudaSetDevice(ctx->device);
+    OTT_CUDA_CHECK(ctx, launch_wait_probe(ctx->stream, ctx->status_dev, ctx->wait_limit_ns));
+    ctx->launches += 1;
+    return OTT_OK;
+}
+
 int ott_malloc(ott_ctx* ctx, size_t bytes, void** out) {
     if (!ctx || !out) return OTT_ERR_INVALID;
     cudaSetDevice(ctx->device);
@@ -330,7 +350,7 @@ int ott_quantize_f32_nchw_to_s8_nhwc(ott_ctx* ctx, const float* x_dev, int n, in
     if (sc.alloc(ctx, sizeof(float) * n_scales) != cudaSuccess) return ctx->fail(OTT_ERR_ALLOC, "scale upload allocation failed");
     OTT_CUDA_CHECK(ctx, cudaMemcpyAsync(sc.p, scales_host, sizeof(float) * n_scales, cudaMemcpyHostToDevice, ctx->stream));
     OTT_CUDA_CHECK(ctx, launch_quantize_dense(ctx->stream, x_dev, c, out_dev, (const float*)sc.p, n_scales, n, c, h, w, rounding));
-    ctx->launches += 1;
+    ctx->launches += (uint64_t)((nhwc_channels(c) + kGatherMaxChannels - 1) / kGatherMaxChannels);
     // the pageable scale array must stay readable until the copy has been issued; it has (pageable copies
     // are staged synchronously)
     return OTT_OK;
@@ -869,7 +889,7 @@ int conv_forward_impl(ott_ctx* ctx, const ott_conv* c, const void* in_dev, const
             OTT_CUDA_CHECK(ctx, launch_quantize_dense(ctx->stream, static_cast<const float*>(in_dev), d.cin, (int8_t*)xq.p, c->in_scales_dev,
                                                        c->n_in_scales, n, d.cin, h, w, d.rounding));
         }
-        ctx->launches += 1;
+        ctx->launches += gather ? 1u : (uint64_t)((c->cin_pad + kGatherMaxChannels - 1) / kGatherMaxChannels);
         x = (const int8_t*)xq.p;
     }
     switch (c->kind) {
@@ -895,7 +915,7 @@ int conv_forward_impl(ott_ctx* ctx, const ott_conv* c, const void* in_dev, const
                 }
             }
             const char* err = launch_dense_umma(ctx->stream, ctx->sm_count, c->plan, c->weight_map, s, x, ep, out_dev, out_dtype, status,
-                                                gathered ? &us : nullptr, mixed);
+                                                gathered ? &us : nullptr, mixed, ctx->wait_limit_ns);
             if (err) return ctx->fail(OTT_ERR_CUDA, "%s: %s", err, cudaGetErrorString(cudaGetLastError()));
             break;
         }

@@ -30,9 +30,17 @@ public:
         return (bytes + (size_t(2) << 20) - 1) & ~((size_t(2) << 20) - 1);  // 2 MiB granules above
     }
 
+    // Failure injection for tests of the error paths (host side only): the n-th allocate call from now on fails with
+    // cudaErrorMemoryAllocation without touching the device; n <= 0 switches it off.
+    void fail_after(long n) {
+        std::lock_guard<std::mutex> g(mu_);
+        fail_countdown_ = n;
+    }
+
     cudaError_t allocate(size_t bytes, void** out) {
         const size_t sz = round_size(bytes);
         std::lock_guard<std::mutex> g(mu_);
+        if (fail_countdown_ > 0 && --fail_countdown_ == 0) return cudaErrorMemoryAllocation;
         auto it = available_.find(sz);
         if (it != available_.end() && !it->second.empty()) {
             *out = it->second.back();
@@ -135,6 +143,7 @@ private:
     std::map<size_t, std::vector<void*>> available_;
     std::unordered_map<void*, size_t> sizes_;
     bool logging_ = false;
+    long fail_countdown_ = 0;
     std::unordered_set<void*> log_;
     uint64_t n_device_mallocs_ = 0, n_cache_hits_ = 0, bytes_in_use_ = 0, bytes_cached_ = 0;
 };
@@ -148,6 +157,7 @@ struct ott_ctx {
     std::string last_error;
     uint64_t launches = 0;
     uint64_t capture_launches0 = UINT64_MAX;  // value of `launches` when the open graph capture began; UINT64_MAX: none open
+    unsigned long long wait_limit_ns = 2000000000ull;  // limit of every bounded wait inside the kernels (ott_set_wait_limit_ms)
     uint32_t* status_dev = nullptr;   // default status word the kernels report into
     uint32_t* status_host = nullptr;  // pinned mirror
     // pinned staging buffers of the *_host entry points

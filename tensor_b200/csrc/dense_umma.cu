@@ -28,6 +28,8 @@
 // into the status word, and all roles fall through to the common teardown, which frees TMEM.
 #include <cuda.h>
 
+#include <mutex>
+
 #include "dense_umma.h"
 #include "launch.cuh"
 #include "umma_primitives.cuh"
@@ -68,8 +70,8 @@ __host__ __device__ inline SmemLayout smem_layout(const UmmaPlan& p) {
     return L;
 }
 
-// MULTI: compiled for three resident CTAs per SM (64 registers per thread), which small layers need to hide latency; the
-// one-CTA-per-SM plans of large layers use the build without that register limit.
+// MULTI: compiled for two resident CTAs per SM (at most 102 registers per thread), which small layers need to hide latency;
+// the one-CTA-per-SM plans of large layers use the build without that register limit.
 template <int OUT, int ACT, bool BIAS, int ROUND, bool MULTI>
 __global__ void __launch_bounds__(kMaxThreads, MULTI ? 2 : 1)
 dense_umma_kernel(const __grid_constant__ KernelMaps maps, const __grid_constant__ CUtensorMap tmB, const UmmaPlan P,
@@ -154,7 +156,7 @@ dense_umma_kernel(const __grid_constant__ KernelMaps maps, const __grid_constant
                 }
                 for (int kb = 0; kb < loads_per_tile; ++kb, ++it) {
                     const uint32_t st = it % P.stages, ph = (it / P.stages) & 1u;
-                    if (!mbar_wait(bar_empty + 8u * st, ph ^ 1u, abort_flag, status, 1u)) { ok = false; break; }
+                    if (!mbar_wait(bar_empty + 8u * st, ph ^ 1u, abort_flag, status, 1u, P.wait_ns)) { ok = false; break; }
                     if (P.gather && P.gather_whole) {
                         mbar_expect_tx(bar_full + 8u * st, (uint32_t)(kTileM * P.bkc * P.nkb));
                         for (int g = 0; g < P.nkb; ++g)
@@ -185,17 +187,17 @@ dense_umma_kernel(const __grid_constant__ KernelMaps maps, const __grid_constant
     } else if (warp == 1) {
         if (lane == 0) {
             // ---- MMA issuer ----
-            bool ok = mbar_wait(bar_b, 0, abort_flag, status, 16u);
+            bool ok = mbar_wait(bar_b, 0, abort_flag, status, 16u, P.wait_ns);
             tc_fence_after();
             uint32_t it = 0, tile_i = 0;
             for (int m = m_first; ok && m < P.m_tiles; m += m_step, ++tile_i) {
                 const uint32_t buf = tile_i & acc_mask, use = tile_i >> acc_shift;
-                if (!mbar_wait(bar_tempty + 8u * buf, (use & 1u) ^ 1u, abort_flag, status, 4u)) { ok = false; break; }
+                if (!mbar_wait(bar_tempty + 8u * buf, (use & 1u) ^ 1u, abort_flag, status, 4u, P.wait_ns)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d = tmem_base + buf * (uint32_t)P.acc_stride;
                 for (int kb = 0; kb < loads_per_tile; ++kb, ++it) {
                     const uint32_t st = it % P.stages, ph = (it / P.stages) & 1u;
-                    if (!mbar_wait(bar_full + 8u * st, ph, abort_flag, status, 2u)) { ok = false; break; }
+                    if (!mbar_wait(bar_full + 8u * st, ph, abort_flag, status, 2u, P.wait_ns)) { ok = false; break; }
                     tc_fence_after();
                     if (P.halo) {
                         // every filter tap reads the same halo tile through a view shifted by (ky, kx) pixels
@@ -247,7 +249,7 @@ dense_umma_kernel(const __grid_constant__ KernelMaps maps, const __grid_constant
         bool ok = true;
         for (int m = m_first; ok && m < P.m_tiles; m += m_step, ++tile_i) {
             const uint32_t buf = tile_i & acc_mask, use = tile_i >> acc_shift;
-            if (!mbar_wait(bar_tfull + 8u * buf, use & 1u, abort_flag, status, 8u)) { ok = false; break; }
+            if (!mbar_wait(bar_tfull + 8u * buf, use & 1u, abort_flag, status, 8u, P.wait_ns)) { ok = false; break; }
             tc_fence_after();
             // which output pixel this thread's TMEM lane holds
             long pix;  // linear (img, oy, ox) index
@@ -404,14 +406,15 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 EncodeTiledFn get_encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
+    // initialised once, by whichever host thread comes first (function-local statics are thread-safe)
+    static const EncodeTiledFn fn = []() -> EncodeTiledFn {
         void* p = nullptr;
         cudaDriverEntryPointQueryResult qres;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
             qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
+            return reinterpret_cast<EncodeTiledFn>(p);
+        return nullptr;
+    }();
     return fn;
 }
 
@@ -422,24 +425,29 @@ CUtensorMapSwizzle swizzle_for(int bkc) {
 template <int OUT, int ACT, bool BIAS, int ROUND, bool MULTI>
 const char* launch_variant(cudaStream_t stream, int sm_count, const KernelMaps& maps, const CUtensorMap& tmB, const UmmaPlan& p,
                            const ConvShape& s, const EpilogueParams& ep, void* out, uint32_t* status, const UmmaMixedOut& mixed) {
+    // per-device, per-instantiation set-up; several host threads may drive different GPUs through this function at once
+    static std::mutex mu;
     static bool attr_set[64] = {};
+    static int regs_per_thread[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
     auto kernel = dense_umma_kernel<OUT, ACT, BIAS, ROUND, MULTI>;
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
-            return "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed";
-        attr_set[dev] = true;
+    int regs = 128;
+    if (dev >= 0 && dev < 64) {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!attr_set[dev]) {
+            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
+                return "cudaFuncSetAttribute(MaxDynamicSharedMemorySize) failed";
+            cudaFuncAttributes fa{};
+            regs_per_thread[dev] = cudaFuncGetAttributes(&fa, kernel) == cudaSuccess && fa.numRegs > 0 ? fa.numRegs : 128;
+            attr_set[dev] = true;
+        }
+        regs = regs_per_thread[dev];
     }
     // Tiles are dealt statically to the CTAs of the grid, so a grid larger than what is resident at once runs in waves.
     // The plan bounds residency by shared memory and TMEM; registers and threads are bounded here.
     const int threads = 64 + 32 * p.epi_warps;
-    static int regs_per_thread[64] = {};
-    if (dev >= 0 && dev < 64 && regs_per_thread[dev] == 0) {
-        cudaFuncAttributes fa{};
-        regs_per_thread[dev] = cudaFuncGetAttributes(&fa, kernel) == cudaSuccess && fa.numRegs > 0 ? fa.numRegs : 128;
-    }
-    const int regs_per_warp = (((dev >= 0 && dev < 64) ? regs_per_thread[dev] : 128) * 32 + 255) / 256 * 256;
+    const int regs_per_warp = (regs * 32 + 255) / 256 * 256;
     int resident = 65536 / (regs_per_warp * (threads / 32));
     if (resident > 2048 / threads) resident = 2048 / threads;
     if (resident < 1) resident = 1;
@@ -511,7 +519,7 @@ bool umma_plan_layer(int cin, int cout, int kh, int kw, int sh, int sw, int dh, 
     // CTAs per SM: TMEM has 512 columns per SM and the hardware scheduler does not account for them, so the shared-memory
     // request is padded until no more CTAs fit an SM than TMEM can serve (a CTA that cannot get its columns would wait
     // inside tcgen05.alloc for a neighbour to finish).
-    // wide tiles run alone on their SM: give them 16 epilogue warps so the per-element epilogue keeps up with the MMAs
+    // eight epilogue warps, two per TMEM lane quarter (sixteen were measured slower on the wide tiles)
     p.epi_warps = 8;
     int by_tmem = 512 / p.tmem_cols;
     int by_smem = smem_budget / p.smem_bytes;
@@ -551,10 +559,11 @@ const char* umma_encode_weight_map(const UmmaPlan& p, const int8_t* w_dev, void*
 
 const char* launch_dense_umma(cudaStream_t stream, int sm_count, const UmmaPlan& plan_in, const void* weight_map,
                               const ConvShape& s, const int8_t* x, const EpilogueParams& ep, void* out, int out_dtype,
-                              uint32_t* status, const UmmaSources* sources, const UmmaMixedOut* mixed_in) {
+                              uint32_t* status, const UmmaSources* sources, const UmmaMixedOut* mixed_in, unsigned long long wait_limit_ns) {
     EncodeTiledFn enc = get_encode_fn();
     if (!enc) return "cuTensorMapEncodeTiled entry point not available";
     UmmaPlan p = plan_in;
+    p.wait_ns = wait_limit_ns;
     const long pixels = (long)s.n * s.oh * s.ow;
     if (pixels == 0) return nullptr;
     KernelMaps km;  // only the entries the plan uses are filled in

@@ -26,6 +26,7 @@ struct UmmaPlan {
     int gather;                        // > 0: the K blocks come from this many int8 NHWC tensors (see UmmaSources)
     int gather_whole;                  // gathered layer whose pipeline stage holds all the K blocks of a pixel tile
     int tw, th, tiles_x, tiles_y, m_tiles;  // 128-pixel output rectangles (tw*th == 128)
+    unsigned long long wait_ns;        // limit of every mbarrier wait inside the kernel
 };
 
 // Decide whether the tensor-core kernel takes this layer and how it tiles it. smem_budget = opt-in
@@ -73,6 +74,7 @@ const char* umma_encode_weight_map(const UmmaPlan& p, const int8_t* w_dev, void*
 // output of an int8 launch.
 const char* launch_dense_umma(cudaStream_t stream, int sm_count, const UmmaPlan& plan, const void* weight_map,
                               const ConvShape& s, const int8_t* x, const EpilogueParams& ep, void* out, int out_dtype,
-                              uint32_t* status, const UmmaSources* sources = nullptr, const UmmaMixedOut* mixed = nullptr);
+                              uint32_t* status, const UmmaSources* sources = nullptr, const UmmaMixedOut* mixed = nullptr,
+                              unsigned long long wait_limit_ns = 2000000000ull);
 
 }  // namespace ottk

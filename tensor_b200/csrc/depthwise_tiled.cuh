@@ -19,6 +19,8 @@
 // so the variants compile in parallel.
 #pragma once
 
+#include <mutex>
+
 #include "launch.cuh"
 #include "store.cuh"
 
@@ -333,13 +335,17 @@ cudaError_t launch_t(cudaStream_t stream, const ConvShape& s, const void* x, con
     const Tile T = plan_tile<K, S>(s);
     const size_t smem = ((size_t)CG * T.ps + (EPI != EPI_F32 ? (size_t)CG * T.ops : 0)) * 4;
     auto kernel = depthwise_tiled_kernel<K, S, IN_F32, EPI, ACT>;
+    static std::mutex mu;  // several host threads may drive different GPUs through this function at once
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
-        if (e != cudaSuccess) return e;
-        attr_set[dev] = true;
+    if (dev >= 0 && dev < 64) {
+        std::lock_guard<std::mutex> lock(mu);
+        if (!attr_set[dev]) {
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+            if (e != cudaSuccess) return e;
+            attr_set[dev] = true;
+        }
     }
     const long blocks = (long)s.n * T.tiles_y * T.tiles_x * T.cgroups;
     if (blocks == 0) return cudaSuccess;

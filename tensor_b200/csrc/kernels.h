@@ -81,4 +81,9 @@ cudaError_t launch_dense_stem_pool(cudaStream_t stream, const ConvShape& s, cons
                                    const float* bias_host, const float* scale_out_host, float in_scale, const EpilogueParams& ep, void* out,
                                    int out_dtype, int pad_zero, uint32_t* status);
 
+// Test support for the bounded waits: one CTA waits on an mbarrier that nothing ever completes, with the given limit, and
+// reports the expiry in *status exactly as the tensor-core kernels do (code 0x100). It loads nothing, issues no MMA and
+// owns no TMEM, so giving up leaves nothing in flight.
+cudaError_t launch_wait_probe(cudaStream_t stream, uint32_t* status, unsigned long long limit_ns);
+
 }  // namespace ottk

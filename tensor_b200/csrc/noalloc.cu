@@ -52,6 +52,17 @@ extern "C" int ott_conv_int8_forward_noalloc(ott_ctx* ctx, const ott_conv* conv,
                          "ott_conv_int8_forward_noalloc: %zu bytes of quantized activations (n=%d h=%d w=%d channel stride %d) exceed the "
                          "fixed scratch of %u bytes; split the batch or use ott_conv_int8_forward",
                          need, n, h, w, conv->cin_pad, (unsigned)OTT_NOALLOC_SCRATCH_BYTES);
+    // Everything the convolution stage would refuse is refused here, before the quantize kernel has touched the shared array.
+    if (!conv->src_channels.empty())
+        return ctx->fail(OTT_ERR_INVALID, "ott_conv_int8_forward_noalloc: a layer created with gathered input reads its producers' int8 tensors, "
+                                          "not an fp32 tensor; use ott_conv_int8_forward_io");
+    const bool requant = conv->d.int8_scale_term > 100;
+    if (out_dtype != OTT_S8_NHWC && out_dtype != OTT_F32_NCHW && out_dtype != OTT_S32_NHWC) return ctx->fail(OTT_ERR_INVALID, "bad output dtype");
+    if (out_dtype == OTT_S8_NHWC && !requant) return ctx->fail(OTT_ERR_INVALID, "int8 output needs int8_scale_term > 100");
+    if (out_dtype == OTT_F32_NCHW && requant) return ctx->fail(OTT_ERR_INVALID, "fp32 output needs int8_scale_term < 100");
+    int oh = 0, ow = 0;
+    ott_conv_int8_out_shape(conv, h, w, &oh, &ow);
+    if (oh <= 0 || ow <= 0) return ctx->fail(OTT_ERR_INVALID, "empty output");
     if (n == 0) return OTT_OK;
     unsigned char* scratch = nullptr;
     int rc = scratch_address(ctx, &scratch);
@@ -61,7 +72,7 @@ extern "C" int ott_conv_int8_forward_noalloc(ott_ctx* ctx, const ott_conv* conv,
     // so nothing left in the array by an earlier call can leak into this one and nothing needs clearing.
     OTT_CUDA_CHECK(ctx, launch_quantize_dense(ctx->stream, in_f32_nchw_dev, conv->d.cin, reinterpret_cast<int8_t*>(scratch), conv->in_scales_dev,
                                                       conv->n_in_scales, n, conv->d.cin, h, w, conv->d.rounding));
-    ctx->launches += 1;
+    ctx->launches += (uint64_t)((conv->cin_pad + kGatherMaxChannels - 1) / kGatherMaxChannels);  // one launch per 512-channel slice
     // int8 input: this path of the ordinary forward launches the convolution kernel and takes no scratch
     return ott_conv_int8_forward(ctx, conv, scratch, OTT_S8_NHWC, n, h, w, out_dev, out_dtype, nullptr);
 }

@@ -8,7 +8,7 @@
 namespace ottk {
 namespace umma {
 
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per wait
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // default limit of one wait: 2 s (ott_set_wait_limit_ms changes it per context)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -44,17 +44,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Bounded wait. Returns false (after raising the CTA's abort flag) when the limit passes or another
+// Bounded wait. Returns false (after raising the CTA's abort flag) when limit_ns passes or another
 // role has already aborted.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, uint32_t* status,
-                                          uint32_t code) {
+                                          uint32_t code, unsigned long long limit_ns = kWaitLimitNs) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = globaltimer_ns();
     for (uint32_t spin = 1;; ++spin) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((spin & 255u) == 0) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > kWaitLimitNs) {
+            if (globaltimer_ns() - t0 > limit_ns) {
                 *abort_flag = 1;
                 if (status) atomicOr(status, code);
                 return false;

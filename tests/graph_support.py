@@ -5,6 +5,7 @@ from __future__ import annotations
 import numpy as np
 
 from support import ConvCase, run_port
+from graph_walk import calibrate, walk
 from tensor_b200 import graphs
 
 
@@ -28,7 +29,7 @@ def oracle_conv(params, rounding=0):
 
 
 def oracle_upsample(a, oh, ow, scale, packed_rule):
-    """The C checker's bilinear Upsample (exact fused multiply-adds), for graphs.walk(upsample_fn=...)."""
+    """The C checker's bilinear Upsample (exact fused multiply-adds), for walk(upsample_fn=...)."""
     import ctypes as C
     from support import _p, load_port
     lib = load_port()
@@ -95,7 +96,7 @@ def wide_shufflenet_case():
     L = graphs.shufflenetv2_layers(64, 64, stage_repeats=(2, 3, 2), stage_channels=(176, 352, 704), stem=24, last=512)
     params = graphs.make_params(L, seed=0x0771E5 + 15)
     x = np.random.default_rng(515).uniform(0, 1, size=(1, 3, 64, 64)).astype(np.float32)
-    graphs.calibrate(L, params, x, oracle_conv_for_calibration)
+    calibrate(L, params, x, oracle_conv_for_calibration)
     return L, params, x, ["pool1", "s2b1_shuf", "s3b2_shuf", "conv5"]
 
 
@@ -105,7 +106,7 @@ def wide_nanodet_case():
     L = graphs.nanodet_plus_layers(64, 64, neck=96, stage_repeats=(2, 2, 2), stage_channels=(176, 352, 704))
     params = graphs.make_params(L, seed=0x0771E5 + 25)
     x = np.random.default_rng(525).uniform(0, 1, size=(1, 3, 64, 64)).astype(np.float32)
-    graphs.calibrate(L, params, x, oracle_conv_for_calibration, upsample_fn=oracle_upsample)
+    calibrate(L, params, x, oracle_conv_for_calibration, upsample_fn=oracle_upsample)
     return L, params, x, ["up32", "td16", "td8", "bu16", "bu32", "p64"] + list(graphs.NANODET_OUTPUTS)
 
 

@@ -2,6 +2,7 @@
 import numpy as np
 import pytest
 
+from graph_walk import calibrate, walk
 from tensor_b200 import graphs
 
 pytestmark = pytest.mark.gpu
@@ -24,8 +25,8 @@ def test_single_convolution_layer_net():
         l.update(kernel_h=k, kernel_w=k, stride_h=1, stride_w=1, padding_h=p, padding_w=p)
     params = graphs.make_params(L)
     x = np.random.default_rng(11).uniform(-1, 1, size=(3, 64, 14, 14)).astype(np.float32)
-    graphs.calibrate(L, params, x, oracle_conv_for_calibration)
-    want = graphs.walk(L, x, oracle_conv(params), want=["c1", "c2", "c3"])
+    calibrate(L, params, x, oracle_conv_for_calibration)
+    want = walk(L, x, oracle_conv(params), want=["c1", "c2", "c3"])
     net = build_net(L, params)
     got = net.forward("data", x, ["c1", "c2", "c3"], dtypes=[np.int8, np.int8, np.float32])
     for name, g in zip(["c1", "c2", "c3"], got):
@@ -38,9 +39,9 @@ def test_shufflenetv2_small_input_bit_exact():
     L = graphs.shufflenetv2_layers(64, 64, batch=2)
     params = graphs.make_params(L)
     x = np.random.default_rng(12).uniform(0, 1, size=(2, 3, 64, 64)).astype(np.float32)
-    graphs.calibrate(L, params, x[:1], oracle_conv_for_calibration)
+    calibrate(L, params, x[:1], oracle_conv_for_calibration)
     probes = ["pool1", "s2b0_shuf", "s2b3_shuf", "s3b0_shuf", "s4b3_shuf", "conv5"]
-    want = graphs.walk(L, x, oracle_conv(params), want=probes)
+    want = walk(L, x, oracle_conv(params), want=probes)
     net = build_net(L, params)
     got = net.forward("data", x, probes)
     for name, g in zip(probes, got):
@@ -62,9 +63,9 @@ def test_int8_handover_between_convolutions_changes_no_blob():
             l["int8_scale_term"] = int(l["int8_scale_term"]) - 100
     params = graphs.make_params(L, seed=77)
     x = np.random.default_rng(13).uniform(0, 1, size=(3, 3, 64, 64)).astype(np.float32)
-    graphs.calibrate(L, params, x[:1], oracle_conv_for_calibration)
+    calibrate(L, params, x[:1], oracle_conv_for_calibration)
     probes = ["s2b0_l_dw", "s2b0_r_pw1", "s2b0_r_dw", "s2b1_pw1", "s2b1_dw", "s2b1_pw2", "s3b0_shuf", "s4b0_l_dw", "conv5"]
-    want = graphs.walk(L, x, oracle_conv(params), want=probes)
+    want = walk(L, x, oracle_conv(params), want=probes)
     on = build_net(L, params)
     off = build_net(L, params, options={"int8_handover": 0})
     for net in (on, off):
@@ -95,9 +96,9 @@ def test_int8_routing_through_glue_layers_changes_no_blob():
     L = graphs.shufflenetv2_layers(64, 64, batch=3)
     params = graphs.make_params(L, seed=5)
     x = np.random.default_rng(21).uniform(0, 1, size=(3, 3, 64, 64)).astype(np.float32)
-    graphs.calibrate(L, params, x[:1], oracle_conv_for_calibration)
+    calibrate(L, params, x[:1], oracle_conv_for_calibration)
     probes = ["s2b0_shuf", "s2b1_pw2", "s2b2_shuf", "s3b5_pw2", "s3b7_shuf", "s4b0_r_pw2", "s4b3_shuf", "conv5"]
-    want = graphs.walk(L, x, oracle_conv(params), want=probes)
+    want = walk(L, x, oracle_conv(params), want=probes)
     on = build_net(L, params)
     off = build_net(L, params, options={"int8_routing": 0})
     counts = []
@@ -153,9 +154,9 @@ def test_first_layer_and_maxpool_fused_kernel(h, w, cout, act, stride):
          dict(type="MaxPool", name="pool1", input="conv1", output="pool1", kernel_h=3, kernel_w=3, stride_h=2, stride_w=2, padding_h=1, padding_w=1)]
     params = graphs.make_params(L)
     x = (np.random.default_rng(21).uniform(0, 1, size=(2, 3, h, w)).astype(np.float32))
-    graphs.calibrate(L, params, x[:1], oracle_conv_for_calibration)
+    calibrate(L, params, x[:1], oracle_conv_for_calibration)
     params["conv1"]["bias"] -= np.float32(0.3)  # push many outputs negative so the padding rule decides border maxima
-    want = graphs.walk(L, x, oracle_conv(params))["pool1"]
+    want = walk(L, x, oracle_conv(params))["pool1"]
     net = build_net(L, params)
     got = net.forward("data", x, ["pool1"])[0]
     assert got.shape == want.shape
@@ -210,9 +211,9 @@ def test_detector_graph_bit_exact():
     L = graphs.nanodet_plus_layers(96, 128, batch=2)
     params = graphs.make_params(L, seed=31)
     x = np.random.default_rng(32).uniform(0, 1, size=(2, 3, 96, 128)).astype(np.float32)
-    graphs.calibrate(L, params, x[:1], oracle_conv_for_calibration, upsample_fn=oracle_upsample)
+    calibrate(L, params, x[:1], oracle_conv_for_calibration, upsample_fn=oracle_upsample)
     probes = ["r8", "up32", "td16", "td8", "dn8", "bu32", "p64"] + list(graphs.NANODET_OUTPUTS)
-    want = graphs.walk(L, x, oracle_conv(params), want=probes, upsample_fn=oracle_upsample)
+    want = walk(L, x, oracle_conv(params), want=probes, upsample_fn=oracle_upsample)
     net = build_net(L, params)
     got = net.forward("data", x, probes)
     for name, g in zip(probes, got):
@@ -335,7 +336,7 @@ def test_captured_forward_replays_bit_exact():
     rng = np.random.default_rng(6)
     x1 = rng.uniform(0, 1, size=(4, 3, 64, 64)).astype(np.float32)
     x2 = rng.uniform(0, 1, size=(4, 3, 64, 64)).astype(np.float32)
-    graphs.calibrate(L, params, x1[:1], oracle_conv_for_calibration)
+    calibrate(L, params, x1[:1], oracle_conv_for_calibration)
     net = build_net(L, params)
     ctx = net.context()
     blobs = ["conv5", "s2b1_shuf", "s3b0_l_dw"]  # a dense fp32 blob, a plane table (materialised), an int8 blob
@@ -387,7 +388,7 @@ def test_chunked_host_forward_equals_plain_forward():
     params = graphs.make_params(L)
     rng = np.random.default_rng(31)
     x = rng.uniform(0, 1, size=(150, 3, 32, 32)).astype(np.float32)
-    graphs.calibrate(L, params, x[:1], oracle_conv_for_calibration)
+    calibrate(L, params, x[:1], oracle_conv_for_calibration)
     net = build_net(L, params)
     net2 = build_net(L, params, options={"host_chunk": 32})
 

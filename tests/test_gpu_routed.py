@@ -31,15 +31,21 @@ GATHER_CASES = [
     ("tail_block_past_end", [232, 240], [(0, 200, 32), (1, 100, 140)], 232, 101, ACT_RELU6),
     ("single_source_whole", [64], [(0, 0, 64)], 128, 101, ACT_RELU),
     ("eight_sources", [116] * 8, [(s, 7 * s, 9 + s) for s in range(8)], 116, 2, ACT_RELU),
+    # the benchmarked geometry: a stage-2 unit (58 channels, 40x40) and a stage-3 unit (116 channels, 20x20) of ShuffleNetV2-1.0x at
+    # 320x320 input, with batches that give 800 / 600 pixel tiles, more than twice the CTAs resident on 148 SMs: every
+    # persistent CTA walks over several tiles and the two-CTA-per-SM plans are taken
+    ("stage2_unit_hw40", [58, 58, 58], [(0, 29, 29), (1, 0, 15), (2, 43, 14)], 58, 102, ACT_RELU, (64, 40, 40)),
+    ("stage3_unit_hw20", [116] * 4, [(0, 87, 29), (1, 58, 29), (2, 29, 29), (3, 0, 29)], 116, 2, ACT_RELU, (192, 20, 20)),
 ]
 
 
-@pytest.mark.parametrize("name,src_ch,picks,cout,term,act", GATHER_CASES, ids=[c[0] for c in GATHER_CASES])
-def test_gathered_input_bit_exact(ctx, name, src_ch, picks, cout, term, act):
+@pytest.mark.parametrize("gcase", GATHER_CASES, ids=[c[0] for c in GATHER_CASES])
+def test_gathered_input_bit_exact(ctx, gcase):
     from gpu_support import bits
     from tensor_b200 import F32_NCHW, KERNEL_DENSE_UMMA, S8_NHWC, nhwc_channels
+    name, src_ch, picks, cout, term, act = gcase[:6]
     rng = np.random.default_rng(len(name) * 1000 + cout)
-    n, h, w = 3, 13, 21
+    n, h, w = gcase[6] if len(gcase) > 6 else (3, 13, 21)
     sources = [rng.integers(-127, 128, size=(n, c, h, w), dtype=np.int8) for c in src_ch]
     chan_src = np.concatenate([np.full(cnt, s) for s, _, cnt in picks]).astype(np.int32)
     chan_idx = np.concatenate([np.arange(f, f + cnt) for _, f, cnt in picks]).astype(np.int32)
@@ -135,16 +141,22 @@ DW_GATHER_CASES = [
     ("s2_three_sources", [58, 58, 116], [(0, 0, 8), (1, 0, 7), (2, 0, 58)], 3, 2),
     ("s1_ranges_mid_group", [116, 232], [(1, 100, 60), (0, 20, 30)], 3, 1),
     ("k5_s2", [64, 64], [(0, 3, 20), (1, 40, 24)], 5, 2),
+    # the benchmarked geometry: the stride-2 depthwise layers that open stages 3 and 4 of ShuffleNetV2-1.0x at 320x320 input
+    # (116 channels at 40x40, 232 at 20x20), their channels spread over the previous stage's producers
+    ("stage3_first_dw_hw40", [58, 58, 58], [(0, 0, 29), (1, 0, 29), (2, 0, 58)], 3, 2, (16, 40, 40)),
+    ("stage4_first_dw_hw20", [116, 116, 116], [(0, 0, 58), (1, 0, 58), (2, 0, 116)], 3, 2, (24, 20, 20)),
+    ("stage2_unit_dw_hw40", [58], [(0, 0, 58)], 3, 1, (16, 40, 40)),
 ]
 
 
-@pytest.mark.parametrize("name,src_ch,picks,k,stride", DW_GATHER_CASES, ids=[c[0] for c in DW_GATHER_CASES])
-def test_gathered_depthwise_bit_exact(ctx, name, src_ch, picks, k, stride):
+@pytest.mark.parametrize("dcase", DW_GATHER_CASES, ids=[c[0] for c in DW_GATHER_CASES])
+def test_gathered_depthwise_bit_exact(ctx, dcase):
     """A depthwise layer whose channels come from several int8 tensors: it runs over whole 16-channel groups of its sources
     and writes its output in that order; the logical channels, read back through the reported positions, equal the checker."""
     from tensor_b200 import ConvInt8, S8_NHWC, nhwc_channels
+    name, src_ch, picks, k, stride = dcase[:5]
     rng = np.random.default_rng(len(name) + k)
-    n, h, w = 2, 23, 37
+    n, h, w = dcase[5] if len(dcase) > 5 else (2, 23, 37)
     sources = [rng.integers(-127, 128, size=(n, c, h, w), dtype=np.int8) for c in src_ch]
     chan_src = np.concatenate([np.full(cnt, s) for s, _, cnt in picks]).astype(np.int32)
     chan_idx = np.concatenate([np.arange(f, f + cnt) for _, f, cnt in picks]).astype(np.int32)

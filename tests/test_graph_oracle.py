@@ -6,6 +6,7 @@ import numpy as np
 import pytest
 
 from support import _p, have_ref, load_ref
+from graph_walk import calibrate, walk
 from tensor_b200 import graphs
 
 
@@ -28,17 +29,17 @@ def test_numpy_glue_equals_reference_layers():
     layers = [dict(type="Input", name="d", output="d", channel=24, height=17, width=19),
               dict(type="MaxPool", name="p", input="d", output="p", kernel_h=3, kernel_w=3, stride_h=2, stride_w=2, padding_h=1, padding_w=1)]
     want = ref_layer("MaxPool", "kernel_h=3;kernel_w=3;stride_h=2;stride_w=2;padding_h=1;padding_w=1", [x])
-    assert np.array_equal(graphs.walk(layers, x, None)["p"], want)
+    assert np.array_equal(walk(layers, x, None)["p"], want)
     x5 = np.ascontiguousarray(x[:, :5])  # 5 channels: not packed by the reference -> plain kernel, padding never wins
     want5 = ref_layer("MaxPool", "kernel_h=3;kernel_w=3;stride_h=2;stride_w=2;padding_h=1;padding_w=1", [x5])
     layers[0]["channel"] = 5
-    assert np.array_equal(graphs.walk(layers, x5, None)["p"], want5)
+    assert np.array_equal(walk(layers, x5, None)["p"], want5)
     y = rng.normal(size=(1, 12, 4, 6)).astype(np.float32)
     z = rng.normal(size=(1, 12, 4, 6)).astype(np.float32)
     g = [dict(type="Input", name="a", output="a", channel=12, height=4, width=6),
          dict(type="ChannelShuffle", name="s", input="a", output="s", groups=2),
          dict(type="Crop", name="c", input="s", output="c", start=6, end=12, axis=1)]
-    got = graphs.walk(g, y, None, want=["s", "c"])
+    got = walk(g, y, None, want=["s", "c"])
     assert np.array_equal(got["s"], ref_layer("ChannelShuffle", "groups=2", [y]))
     assert np.array_equal(got["c"], ref_layer("Crop", "start=6;end=12;axis=1", [got["s"]]))
     assert np.array_equal(np.concatenate([y, z], 1), ref_layer("Concat", "axis=1", [y, z]))
@@ -106,8 +107,8 @@ def test_calibration_walk_gives_usable_scales():
     L = graphs.shufflenetv2_layers(32, 32, stage_repeats=(2, 2, 2))
     params = graphs.make_params(L)
     x = np.random.default_rng(3).uniform(0, 1, size=(1, 3, 32, 32)).astype(np.float32)
-    graphs.calibrate(L, params, x, oracle_conv_for_calibration)
-    out = graphs.walk(L, x, oracle_conv(params))["conv5"]
+    calibrate(L, params, x, oracle_conv_for_calibration)
+    out = walk(L, x, oracle_conv(params))["conv5"]
     assert out.shape == (1, 1024, 1, 1) and np.isfinite(out).all() and (out != 0).mean() > 0.2
     # an int8 blob's producer and consumer agree on its scale
     assert params["s2b1_pw1"]["out_scales"][0] == params["s2b1_dw"]["in_scales"][0]
@@ -121,7 +122,7 @@ def test_layer_by_layer_walk_equals_frozen_reference_net():
     own Net on a whole graph."""
     from graph_support import oracle_conv, wide_shufflenet_case
     L, params, x, blobs = wide_shufflenet_case()
-    got = graphs.walk(L, x, oracle_conv(params), want=blobs)
+    got = walk(L, x, oracle_conv(params), want=blobs)
     for b in blobs:
         assert np.array_equal(got[b].view(np.int32), NET_GOLD[b].view(np.int32)), b
 
@@ -131,7 +132,7 @@ def test_reference_net_live_equals_walk():
     from graph_support import oracle_conv, reference_net_forward, wide_shufflenet_case
     L, params, x, blobs = wide_shufflenet_case()
     ref = reference_net_forward(L, params, x, blobs)
-    got = graphs.walk(L, x, oracle_conv(params), want=blobs)
+    got = walk(L, x, oracle_conv(params), want=blobs)
     for b in blobs:
         assert np.array_equal(got[b].view(np.int32), ref[b].view(np.int32)), b
 
@@ -144,7 +145,7 @@ def test_detector_walk_equals_frozen_reference_net():
     against blobs frozen from the reference's own Net."""
     from graph_support import oracle_conv, oracle_upsample, wide_nanodet_case
     L, params, x, blobs = wide_nanodet_case()
-    got = graphs.walk(L, x, oracle_conv(params), want=blobs, upsample_fn=oracle_upsample)
+    got = walk(L, x, oracle_conv(params), want=blobs, upsample_fn=oracle_upsample)
     for b in blobs:
         assert got[b].shape == DET_GOLD[b].shape, b
         assert np.array_equal(got[b].view(np.int32), DET_GOLD[b].view(np.int32)), b

@@ -1,5 +1,6 @@
 """The `.otter` model-structure reader (C++ side) against the writer in tensor_b200.graphs and, where the reference
 checkout is present, against the reference's own shipped int8 graph file."""
+import os
 from pathlib import Path
 
 import pytest
@@ -7,7 +8,7 @@ import pytest
 from tensor_b200 import graphs
 from tensor_b200.capi import parse_otter_text
 
-REF_GRAPH = Path("/root/reference/benchmark/nanodet-plus-m-1.5x_416_int8_fused.otter")
+REF_GRAPH = Path(os.environ.get("OTTER_REFERENCE", "/root/reference")) / "benchmark" / "nanodet-plus-m-1.5x_416_int8_fused.otter"
 
 
 @pytest.fixture(scope="module", autouse=True)

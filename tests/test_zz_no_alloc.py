@@ -73,3 +73,26 @@ def test_noalloc_rejects_oversized_calls(ctx):
     msg = ctx.lib.ott_last_error(ctx.h).decode()
     assert str(SCRATCH_BYTES) in msg and "exceed" in msg
     layer.close()
+
+
+def test_noalloc_refuses_before_it_launches_anything(ctx):
+    """A call the convolution stage would refuse (a layer with gathered input, an output type the layer does not produce)
+    must fail before the quantize kernel has been enqueued and the shared array overwritten."""
+    from gpu_support import make_layer
+    from tensor_b200 import ConvInt8, F32_NCHW, S8_NHWC
+    case = ConvCase("noalloc_gathered", 58, 58, 1, n=1, h=8, w=8, int8_scale_term=101, act_type=ACT_RELU, s8_input=True, seed=206).make()
+    gathered = ConvInt8(ctx, cin=58, cout=58, kh=1, kw=1, bias_term=1, int8_scale_term=101, act_type=ACT_RELU, weight=case.weight, bias=case.bias,
+                        w_scales=case.w_scales, in_scales=case.in_scales, out_scales=case.out_scales,
+                        gathered=([64], np.zeros(58, np.int32), np.arange(58, dtype=np.int32)))
+    plain = make_layer(ctx, case, 0)
+    x = ctx.malloc(58 * 8 * 8 * 4)
+    o = ctx.malloc(64 * 8 * 8 * 4)
+    before = ctx.launch_count()
+    assert ctx.lib.ott_conv_int8_forward_noalloc(ctx.h, gathered.h, C.c_void_p(x), 1, 8, 8, C.c_void_p(o), S8_NHWC) == -2
+    assert "gathered" in ctx.lib.ott_last_error(ctx.h).decode()
+    assert ctx.lib.ott_conv_int8_forward_noalloc(ctx.h, plain.h, C.c_void_p(x), 1, 8, 8, C.c_void_p(o), F32_NCHW) == -2
+    assert ctx.launch_count() == before
+    ctx.free(x)
+    ctx.free(o)
+    gathered.close()
+    plain.close()
