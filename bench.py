@@ -861,10 +861,10 @@ def run_net_gpu_arm(args, cfg):
             dom_ms += ms
             dom_layers += 1
         ach = dom_bytes / (dom_ms * 1e-3) / 1e9
-        kernels = {"Convolution/1x1": "dense_umma_kernel (+ quantize_nchw_to_nhwc_kernel where the input is fp32)", "Convolution/depthwise": "depthwise_tiled_kernel",
-                   "Convolution/stem3x3": "dense_stem_pool_kernel"}[dom]
+        dom_kernel = {"Convolution/1x1": "dense_umma_kernel (+ quantize_nchw_to_nhwc_kernel where the input is fp32)", "Convolution/depthwise": "depthwise_tiled_kernel",
+                      "Convolution/stem3x3": "dense_stem_pool_kernel"}[dom]
         roof = {"bound": "hbm", "achieved": ach, "peak": hbm_peak, "unit": "GB/s", "frac": ach / hbm_peak, "traffic": None,
-                "peak_source": hbm_src, "kernel": f"{kernels}: the {dom_layers} {dom} layers of the graph",
+                "peak_source": hbm_src, "kernel": f"{dom_kernel}: the {dom_layers} {dom} layers of the graph",
                 "kernel_ms": dom_ms / dom_layers, "algorithmic_bytes_per_launch": dom_bytes / dom_layers, "ops_per_launch": dom_ops / dom_layers,
                 "launches_per_step": dom_layers,
                 "timed": "serialised per-layer pass (CUDA events around every layer of one forward, kernels launched one by one: no graph "

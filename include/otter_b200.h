@@ -303,6 +303,16 @@ int ott_nanodet_detect(ott_ctx* ctx, const float* const* heads_dev, const int* g
                        int n_levels, int n, int num_class, int reg_bins, float prob_threshold, float nms_threshold, float* out_host,
                        int* counts_host, int max_det);
 
+/* ---- the fp32 layer: ConvolutionLayer with int8_scale_term == 0 (Tensor/ConvolutionLayer.cpp:507-664), which a "mixed"
+ *      quantized model keeps for its first convolution (benchmark/nanodet-plus-m-1.5x_416_int8_mixed.otter:26). Dense or
+ *      depthwise, bias and activation (none/ReLU/LeakyReLU/ReLU6) fused; fp32 NCHW device tensors in and out. w_oihw (fp32
+ *      [cout][cin/groups][kh][kw]) and bias are HOST pointers. The result agrees with the reference's fp32 kernels to rounding
+ *      (a few units in the last place of sum |w*x| + |bias|: its -ffast-math build sums in its own vector order), not to the bit. ---- */
+typedef struct ott_conv_f32 ott_conv_f32;
+int ott_conv_f32_create(ott_ctx* ctx, const ott_conv_desc* desc, const float* w_oihw, const float* bias, ott_conv_f32** out);
+int ott_conv_f32_forward(ott_ctx* ctx, const ott_conv_f32* conv, const float* in_dev, int n, int h, int w, float* out_dev);
+int ott_conv_f32_destroy(ott_ctx* ctx, ott_conv_f32* conv);
+
 /* The forward for hosts that may not allocate device memory while running. No counterpart in the
  * reference (its CPU path simply calls otter::empty for every temporary).
  * Who needs it: a process whose device memory was divided into fixed pools at start-up and must not grow

@@ -64,6 +64,7 @@ int ott_net_layer_count(const ott_net* net);
  * int8_scale_term, activation_type}, else zeros */
 int ott_net_layer_info(const ott_net* net, int i, char* type, int type_cap, char* name, int name_cap, int geom[12]);
 int ott_net_blob_shape(const ott_net* net, const char* blob, int shape[4]);
+int ott_net_blob_element_size(const ott_net* net, const char* blob); /* 1: the int8 blob of a requantizing convolution; 4: fp32; 0: unknown blob */
 /* How Convolution layer i takes part in the "int8_routing" hand-over (zeros for every other layer, or with the switch off):
  * info[0] = number of int8 tensors its input channels are gathered from (0: it reads its input blob as usual),
  * info[1] = output channels it stores quantized for their reader, info[2] = output channels it (also) stores as fp32 planes
@@ -74,6 +75,9 @@ int ott_net_layer_routing(ott_net* net, int i, int info[3]);
  * bottom_blob_int8_scales, top_blob_int8_scales of Tensor/ConvolutionLayer.hpp:62-77) and rebuild its pipeline. */
 int ott_net_set_conv_params(ott_net* net, const char* layer, const int8_t* w_oihw, const float* bias, const float* w_scales,
                             const float* in_scales, int n_in_scales, const float* out_scales, int n_out_scales);
+
+/* The same for an fp32 Convolution layer (int8_scale_term == 0): weight_data fp32 [cout][cin/groups][kh][kw] and bias_data. */
+int ott_net_set_conv_params_f32(ott_net* net, const char* layer, const float* w_oihw, const float* bias);
 
 /* Extractor::input + Extractor::extract (Tensor/Net.cpp:686-736) for one input blob and n_out output blobs.
  * in: fp32 NCHW, on the host (in_on_device = 0; copied to the GPU) or already on the GPU (1).
@@ -107,6 +111,25 @@ int ott_net_forward_rows(ott_net* net, const char* input_blob, const void* in, i
  * Layers run serialised while profiling. */
 int ott_net_profile(ott_net* net, const char* input_blob, const void* in, int in_on_device, int n, int c, int h, int w,
                     const char* out_blob, float* ms_per_layer);
+
+/* ---- several GPUs behind one call (no counterpart in the reference, which runs one image on the host cores) ----
+ * A group holds one Net replica per listed device (a device may be listed more than once: each entry gets its own context
+ * and stream). Configure every member the same way through the ott_net_* calls (ott_net_group_member), then:
+ * ott_net_group_forward = Extractor::input + Extractor::extract (Tensor/Net.cpp:686-736) for a host batch of n images: the
+ * batch is cut into contiguous slices (ott_net_group_partition: sizes differ by at most one, earlier slices take the extra
+ * images), slice p runs on member p through ott_net_forward on its own host thread, and its outputs are copied to
+ * out_host[i] + first_image_of_slice * bytes_per_image(out_blobs[i]). Returns when every slice is done. Images are
+ * independent, so the result equals the unsharded forward bit for bit; no data moves between the GPUs. Host buffers
+ * should be pinned (ott_host_alloc) for the copies to overlap the kernels. */
+typedef struct ott_net_group ott_net_group;
+int ott_net_group_create(const int* devices, int n_devices, ott_net_group** out);
+int ott_net_group_destroy(ott_net_group* group);
+int ott_net_group_size(const ott_net_group* group);
+ott_net* ott_net_group_member(ott_net_group* group, int index); /* owned by the group */
+const char* ott_net_group_last_error(const ott_net_group* group);
+void ott_net_group_partition(int n, int parts, int index, int* first, int* count);
+int ott_net_group_forward(ott_net_group* group, const char* input_blob, const float* in_host, int n, int c, int h, int w, int n_out,
+                          const char* const* out_blobs, void* const* out_host);
 
 #if defined(__GNUC__)
 #pragma GCC visibility pop

@@ -197,6 +197,60 @@ REF_API int ref_conv_int8_forward(const RefConvDesc* d, const int8_t* w_oihw, co
     }
 }
 
+// The fp32 ConvolutionLayer (int8_scale_term == 0; Tensor/ConvolutionLayer.cpp:298-664): fp32 OIHW weights, one image at a time.
+// Used to state how far the GPU's fp32 first layer may lie from the reference's -Ofast fp32 kernels.
+REF_API int ref_conv_f32_forward(const RefConvDesc* d, const float* w_oihw, const float* bias, const float* x_f32, int n, int h, int w,
+                                 int packed, float* y_f32) {
+    try {
+        RefLayer L;
+        L.d = *d;
+        L.opt.use_packing_layout = packed != 0;
+        otter::LayerOption option;
+        option["in_channels"] = std::to_string(d->cin);
+        option["out_channels"] = std::to_string(d->cout);
+        option["kernel_h"] = std::to_string(d->kh);
+        option["kernel_w"] = std::to_string(d->kw);
+        option["stride_h"] = std::to_string(d->sh);
+        option["stride_w"] = std::to_string(d->sw);
+        option["padding_h"] = std::to_string(d->ph);
+        option["padding_w"] = std::to_string(d->pw);
+        option["dilation_h"] = std::to_string(d->dh);
+        option["dilation_w"] = std::to_string(d->dw);
+        option["groups"] = std::to_string(d->groups);
+        option["bias_term"] = d->bias_term ? "true" : "false";
+        option["int8_scale_term"] = "0";
+        if (d->act_type == 1) option["activation"] = "Relu";
+        if (d->act_type == 2) { option["activation"] = "LRelu"; option["activation_params"] = std::to_string(d->act_param0); }
+        if (d->act_type == 3) option["activation"] = "Relu6";
+        otter::ParamDict pd;
+        L.layer.parse_param(option, pd);
+        L.layer.bottom_shapes.clear();
+        L.layer.bottom_shapes.push_back(otter::tensor({1, d->cin, h, w}, otter::ScalarType::Int).view({1, -1}));
+        L.layer.compute_output_shape(pd);
+        L.layer.load_param(pd);
+        if (d->act_type == 2) L.layer.activation_params = vec_tensor(&d->act_param0, 1);
+        const int wsize = d->cout * (d->cin / d->groups) * d->kh * d->kw;
+        L.layer.weight_data = otter::empty({d->cout, d->cin / d->groups, d->kh, d->kw}, otter::ScalarType::Float);
+        std::memcpy(L.layer.weight_data.raw_data(), w_oihw, sizeof(float) * wsize);
+        if (d->bias_term) L.layer.bias_data = vec_tensor(bias, d->cout);
+        int rc = L.layer.create_pipeline(L.opt);
+        if (rc != 0) { g_err = "create_pipeline failed"; return rc; }
+        const int oh = (h + 2 * d->ph - d->dh * (d->kh - 1) - 1) / d->sh + 1;
+        const int ow = (w + 2 * d->pw - d->dw * (d->kw - 1) - 1) / d->sw + 1;
+        const size_t in_elems = (size_t)d->cin * h * w, out_elems = (size_t)d->cout * oh * ow;
+        for (int i = 0; i < n; ++i) {
+            otter::Tensor x = otter::from_blob((void*)(x_f32 + i * in_elems), {1, d->cin, h, w}, otter::ScalarType::Float);
+            otter::Tensor bottom = to_layer_layout(x, packed != 0, false);
+            otter::Tensor top;
+            rc = L.layer.forward(bottom, top, L.opt);
+            if (rc != 0) { g_err = "forward failed"; return rc; }
+            otter::Tensor t1 = top.packing(1).contiguous();
+            std::memcpy(y_f32 + i * out_elems, t1.raw_data(), out_elems * 4);
+        }
+        return 0;
+    } catch (const std::exception& e) { g_err = e.what(); return -2; } catch (const char* s) { g_err = s; return -3; } catch (...) { g_err = "unknown"; return -4; }
+}
+
 // Best-of-`iters` wall time (ms) of ONE N=1 ConvolutionLayer::forward on image 0, after `warmup` runs.
 REF_API double ref_conv_int8_time_ms(const RefConvDesc* d, const int8_t* w_oihw, const float* bias,
                                      const float* w_scales, const float* in_scales, int n_in_scales,

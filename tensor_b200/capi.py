@@ -71,6 +71,9 @@ SIGNATURES = {
     "ott_conv_int8_forward_maxpool_s8": (i32, [vp, vp, vp, i32, i32, i32, i32, vp]),
     "ott_conv_int8_forward_host": (i32, [vp, vp, vp, i32, i32, i32, i32, vp, i32]),
     "ott_conv_int8_forward_noalloc": (i32, [vp, vp, vp, i32, i32, i32, vp, i32]),
+    "ott_conv_f32_create": (i32, [vp, C.POINTER(OttConvDesc), vp, vp, C.POINTER(vp)]),
+    "ott_conv_f32_forward": (i32, [vp, vp, vp, i32, i32, i32, vp]),
+    "ott_conv_f32_destroy": (i32, [vp, vp]),
     "ott_launch_count": (C.c_uint64, [vp]),
     "ott_copy_channels_f32": (i32, [vp, vp, i32, i32, i32, vp, i32, i32, i32, i32, i32, i32]),
     "ott_maxpool_f32_nchw": (i32, [vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp]),
@@ -97,8 +100,17 @@ SIGNATURES = {
     "ott_net_layer_count": (i32, [vp]),
     "ott_net_layer_info": (i32, [vp, i32, C.c_char_p, i32, C.c_char_p, i32, C.POINTER(i32)]),
     "ott_net_blob_shape": (i32, [vp, C.c_char_p, C.POINTER(i32)]),
+    "ott_net_blob_element_size": (i32, [vp, C.c_char_p]),
+    "ott_net_group_create": (i32, [C.POINTER(i32), i32, C.POINTER(vp)]),
+    "ott_net_group_destroy": (i32, [vp]),
+    "ott_net_group_size": (i32, [vp]),
+    "ott_net_group_member": (vp, [vp, i32]),
+    "ott_net_group_last_error": (C.c_char_p, [vp]),
+    "ott_net_group_partition": (None, [i32, i32, i32, C.POINTER(i32), C.POINTER(i32)]),
+    "ott_net_group_forward": (i32, [vp, C.c_char_p, vp, i32, i32, i32, i32, i32, C.POINTER(C.c_char_p), C.POINTER(vp)]),
     "ott_net_layer_routing": (i32, [vp, i32, C.POINTER(i32)]),
     "ott_net_set_conv_params": (i32, [vp, C.c_char_p, vp, vp, vp, vp, i32, vp, i32]),
+    "ott_net_set_conv_params_f32": (i32, [vp, C.c_char_p, vp, vp]),
     "ott_net_capture": (i32, [vp, C.c_char_p, vp, i32, i32, i32, i32, i32, C.POINTER(C.c_char_p), C.POINTER(vp)]),
     "ott_net_graph_launch": (i32, [vp]),
     "ott_net_graph_output": (i32, [vp, i32, C.POINTER(vp), C.POINTER(i32)]),
@@ -331,6 +343,39 @@ class ConvInt8:
             self.h = None
 
 
+class ConvF32:
+    """An fp32 ConvolutionLayer (int8_scale_term == 0) on the GPU (ott_conv_f32); weight fp32 OIHW, host arrays."""
+
+    def __init__(self, ctx: Context, *, cin, cout, kh, kw, sh=1, sw=1, ph=0, pw=0, dh=1, dw=1, groups=1, act_type=0, act_param0=0.0, weight, bias=None):
+        self.ctx = ctx
+        self.desc = OttConvDesc(cin, cout, kh, kw, sh, sw, ph, pw, dh, dw, groups, 0 if bias is None else 1, 0, act_type, act_param0, 0)
+        weight = np.ascontiguousarray(weight, dtype=np.float32)
+        bias = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+        h = C.c_void_p()
+        ctx.check(ctx.lib.ott_conv_f32_create(ctx.h, C.byref(self.desc), _np_ptr(weight), _np_ptr(bias), C.byref(h)))
+        self.h = h
+
+    def forward_host(self, x: np.ndarray) -> np.ndarray:
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        n, _, h, w = x.shape
+        d = self.desc
+        oh = (h + 2 * d.ph - d.dh * (d.kh - 1) - 1) // d.sh + 1
+        ow = (w + 2 * d.pw - d.dw * (d.kw - 1) - 1) // d.sw + 1
+        xd = self.ctx.to_device(x)
+        od = self.ctx.malloc(n * d.cout * oh * ow * 4)
+        try:
+            self.ctx.check(self.ctx.lib.ott_conv_f32_forward(self.ctx.h, self.h, C.c_void_p(xd), n, h, w, C.c_void_p(od)))
+            return self.ctx.to_host(od, (n, d.cout, oh, ow), np.float32)
+        finally:
+            self.ctx.free(xd)
+            self.ctx.free(od)
+
+    def close(self):
+        if self.h:
+            self.ctx.lib.ott_conv_f32_destroy(self.ctx.h, self.h)
+            self.h = None
+
+
 class NetGraph:
     """A captured forward (ott_net_capture): launch() replays it on the Net's stream."""
 
@@ -370,13 +415,15 @@ def parse_otter_text(text: str):
 class Net:
     """ctypes wrapper over include/otter_b200_net.h: a Net built from the reference's LayerOption key/value pairs."""
 
-    def __init__(self, device: int = 0):
+    def __init__(self, device: int = 0, handle=None):
         self.lib = library()
-        h = C.c_void_p()
-        rc = self.lib.ott_net_create(device, C.byref(h))
-        if rc != 0:
-            raise OtterB200Error(rc, "ott_net_create failed")
-        self.h = h
+        self.owned = handle is None
+        if handle is None:
+            handle = C.c_void_p()
+            rc = self.lib.ott_net_create(device, C.byref(handle))
+            if rc != 0:
+                raise OtterB200Error(rc, "ott_net_create failed")
+        self.h = handle
         self.layers = []
 
     def check(self, rc: int):
@@ -437,6 +484,11 @@ class Net:
                                                     _np_ptr(in_scales), in_scales.size, _np_ptr(out_scales),
                                                     0 if out_scales is None else out_scales.size))
 
+    def set_conv_params_f32(self, layer: str, weight, bias=None):
+        weight = np.ascontiguousarray(weight, dtype=np.float32)
+        bias = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+        self.check(self.lib.ott_net_set_conv_params_f32(self.h, layer.encode(), _np_ptr(weight), _np_ptr(bias)))
+
     def forward_raw(self, input_blob: str, in_ptr, in_on_device: bool, shape, out_blobs, out_ptrs=None):
         n, c, h, w = shape
         names = (C.c_char_p * len(out_blobs))(*[b.encode() for b in out_blobs])
@@ -484,6 +536,51 @@ class Net:
         return out.reshape(-1)[:k * cols.value].reshape(k, cols.value).copy(), rows.value
 
     def close(self):
-        if self.h:
+        if self.h and self.owned:
             self.lib.ott_net_destroy(self.h)
+        self.h = None
+
+
+def partition(n: int, parts: int, index: int):
+    """(first image, image count) of slice `index` when n images are cut into `parts` contiguous slices (ott_net_group_partition)."""
+    first, count = C.c_int(), C.c_int()
+    library().ott_net_group_partition(n, parts, index, C.byref(first), C.byref(count))
+    return first.value, count.value
+
+
+class NetGroup:
+    """One Net replica per listed device behind one forward call (ott_net_group_*). `members` are Net wrappers over the
+    replicas: configure each the same way (add_layer / compile / set_conv_params or load_model)."""
+
+    def __init__(self, devices):
+        self.lib = library()
+        arr = (C.c_int * len(devices))(*devices)
+        h = C.c_void_p()
+        rc = self.lib.ott_net_group_create(arr, len(devices), C.byref(h))
+        if rc != 0:
+            raise OtterB200Error(rc, "ott_net_group_create failed")
+        self.h = h
+        self.members = [Net(handle=C.c_void_p(self.lib.ott_net_group_member(h, i))) for i in range(len(devices))]
+
+    def forward_raw(self, input_blob: str, in_ptr, shape, out_blobs, out_ptrs):
+        n, c, h, w = shape
+        names = (C.c_char_p * len(out_blobs))(*[b.encode() for b in out_blobs])
+        ptrs = (C.c_void_p * len(out_blobs))(*out_ptrs)
+        rc = self.lib.ott_net_group_forward(self.h, input_blob.encode(), in_ptr, n, c, h, w, len(out_blobs), names, ptrs)
+        if rc != 0:
+            raise OtterB200Error(rc, self.lib.ott_net_group_last_error(self.h).decode(errors="replace"))
+
+    def forward(self, input_blob: str, x: np.ndarray, out_blobs):
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        m = self.members[0]
+        outs = [np.empty((x.shape[0],) + m.blob_shape(b)[1:], dtype=np.int8 if self.lib.ott_net_blob_element_size(m.h, b.encode()) == 1 else np.float32)
+                for b in out_blobs]
+        self.forward_raw(input_blob, _np_ptr(x), x.shape, out_blobs, [o.ctypes.data for o in outs])
+        return outs
+
+    def close(self):
+        if self.h:
+            for m in self.members:
+                m.h = None
+            self.lib.ott_net_group_destroy(self.h)
             self.h = None

@@ -629,6 +629,72 @@ int ott_conv_int8_destroy(ott_ctx* ctx, ott_conv* c) {
     return OTT_OK;
 }
 
+// ---- the fp32 layer (int8_scale_term == 0) ----
+struct ott_conv_f32 {
+    ott_conv_desc d{};
+    bool depthwise = false;
+    float* w_dev = nullptr;
+    float* bias_dev = nullptr;
+};
+
+int ott_conv_f32_create(ott_ctx* ctx, const ott_conv_desc* d, const float* w_oihw, const float* bias, ott_conv_f32** out) {
+    if (!ctx || !d || !w_oihw || !out) return OTT_ERR_INVALID;
+    *out = nullptr;
+    if (d->cin <= 0 || d->cout <= 0 || d->kh <= 0 || d->kw <= 0 || d->sh <= 0 || d->sw <= 0 || d->dh <= 0 || d->dw <= 0 || d->ph < 0 || d->pw < 0 ||
+        d->groups <= 0)
+        return ctx->fail(OTT_ERR_INVALID, "bad convolution geometry");
+    if (d->int8_scale_term != 0) return ctx->fail(OTT_ERR_INVALID, "ott_conv_f32_create is the fp32 layer (int8_scale_term == 0)");
+    if (d->act_type < 0 || d->act_type > 3) return ctx->fail(OTT_ERR_UNSUPPORTED, "activation %d is not supported (none/ReLU/LeakyReLU/ReLU6)", d->act_type);
+    if (d->bias_term && !bias) return ctx->fail(OTT_ERR_INVALID, "bias_term set but bias is NULL");
+    const bool depthwise = d->groups > 1 && d->groups == d->cin && d->groups == d->cout;
+    if (!depthwise && d->groups != 1) return ctx->fail(OTT_ERR_UNSUPPORTED, "grouped (non-depthwise) fp32 convolution is not supported");
+    cudaSetDevice(ctx->device);
+    ott_conv_f32* c = new (std::nothrow) ott_conv_f32();
+    if (!c) return OTT_ERR_ALLOC;
+    c->d = *d;
+    c->depthwise = depthwise;
+    const int cp = conv_f32_channel_stride(d->cout), taps = d->kh * d->kw, cin_g = d->cin / d->groups;
+    std::vector<float> wp((size_t)(depthwise ? 1 : cin_g) * taps * cp), bp((size_t)cp, 0.f);
+    conv_f32_pack_weights(w_oihw, cin_g, d->cout, taps, depthwise, wp.data());
+    for (int i = 0; i < d->cout && d->bias_term; ++i) bp[(size_t)i] = bias[i];
+    int rc = upload(ctx, wp.data(), wp.size() * sizeof(float), (void**)&c->w_dev);
+    if (rc == OTT_OK) rc = upload(ctx, bp.data(), bp.size() * sizeof(float), (void**)&c->bias_dev);
+    if (rc == OTT_OK && cudaStreamSynchronize(ctx->stream) != cudaSuccess) rc = ctx->fail(OTT_ERR_CUDA, "upload failed");
+    if (rc != OTT_OK) {
+        ott_conv_f32_destroy(ctx, c);
+        return rc;
+    }
+    *out = c;
+    return OTT_OK;
+}
+
+int ott_conv_f32_destroy(ott_ctx* ctx, ott_conv_f32* c) {
+    if (!c) return OTT_OK;
+    if (ctx) {
+        ctx->alloc->free(c->w_dev);
+        ctx->alloc->free(c->bias_dev);
+    }
+    delete c;
+    return OTT_OK;
+}
+
+int ott_conv_f32_forward(ott_ctx* ctx, const ott_conv_f32* c, const float* in_dev, int n, int h, int w, float* out_dev) {
+    if (!ctx || !c || !in_dev || !out_dev || n < 0 || h <= 0 || w <= 0) return OTT_ERR_INVALID;
+    const ott_conv_desc& d = c->d;
+    ConvShape s{};
+    s.n = n; s.h = h; s.w = w;
+    s.oh = out_dim(h, d.kh, d.sh, d.ph, d.dh);
+    s.ow = out_dim(w, d.kw, d.sw, d.pw, d.dw);
+    if (s.oh <= 0 || s.ow <= 0) return ctx->fail(OTT_ERR_INVALID, "empty output");
+    s.cin = d.cin; s.cout = d.cout; s.cin_pad = d.cin; s.cout_pad = d.cout;
+    s.kh = d.kh; s.kw = d.kw; s.sh = d.sh; s.sw = d.sw; s.ph = d.ph; s.pw = d.pw; s.dh = d.dh; s.dw = d.dw;
+    if (n == 0) return OTT_OK;
+    cudaSetDevice(ctx->device);
+    OTT_CUDA_CHECK(ctx, launch_conv_f32(ctx->stream, s, c->depthwise ? 1 : 0, in_dev, c->w_dev, c->bias_dev, d.act_type, d.act_param0, out_dev));
+    ctx->launches += 1;
+    return OTT_OK;
+}
+
 int ott_conv_int8_kernel_kind(const ott_conv* c) { return c ? c->kind : OTT_ERR_INVALID; }
 
 int ott_conv_int8_out_shape(const ott_conv* c, int h, int w, int* oh, int* ow) {

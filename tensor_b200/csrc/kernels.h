@@ -81,6 +81,13 @@ cudaError_t launch_dense_stem_pool(cudaStream_t stream, const ConvShape& s, cons
                                    const float* bias_host, const float* scale_out_host, float in_scale, const EpilogueParams& ep, void* out,
                                    int out_dtype, int pad_zero, uint32_t* status);
 
+// fp32 convolution (the layers a mixed model keeps in floating point): x, out fp32 NCHW; weights packed by
+// conv_f32_pack_weights into [cin/groups][tap][conv_f32_channel_stride(cout)] (depthwise: [tap][stride]); bias padded to the same stride.
+int conv_f32_channel_stride(int cout);
+void conv_f32_pack_weights(const float* w_oihw, int cin_per_group, int cout, int taps, bool depthwise, float* dst);
+cudaError_t launch_conv_f32(cudaStream_t stream, const ConvShape& s, int depthwise, const float* x, const float* w_packed, const float* bias_padded,
+                            int act_type, float act_param0, float* out);
+
 // Test support for the bounded waits: one CTA waits on an mbarrier that nothing ever completes, with the given limit, and
 // reports the expiry in *status exactly as the tensor-core kernels do (code 0x100). It loads nothing, issues no MMA and
 // owns no TMEM, so giving up leaves nothing in flight.

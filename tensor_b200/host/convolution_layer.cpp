@@ -1,7 +1,8 @@
 // ConvolutionLayer of the host-side API mirror: the quantized (int8_scale_term != 0) layer of
 // Tensor/ConvolutionLayer.cpp, with create_pipeline_int8 (:666-752) and forward_int8 (:754-847) handed to the
 // CUDA library through its C-ABI. Option keys, ParamDict ids, shape rule and field names follow the reference
-// (:58-206); the fp32 half of the layer (int8_scale_term == 0) does not exist here and create_pipeline refuses it.
+// (:58-206). The fp32 half of the layer (int8_scale_term == 0, :507-664) runs as one direct fp32 kernel: it is what a
+// "mixed" quantized model keeps for its first convolution.
 #include <cstring>
 #include <random>
 #include <sstream>
@@ -119,8 +120,17 @@ int ConvolutionLayer::load_param(const ParamDict& pd) {
 // (Tensor/ConvolutionLayer.cpp:208-243: int8 weights, [groups] or [1] activation scales, [Cout] weight scales).
 // Deterministic here: the generator is seeded from the layer name.
 int ConvolutionLayer::init_model() {
-    if (!int8_scale_term) return 0;
     std::mt19937 rng((unsigned)std::hash<std::string>{}(name) ^ 0x0771E5u);
+    if (!int8_scale_term) {  // the fp32 layer: fp32 weights of the right shape
+        std::normal_distribution<float> nd(0.f, 0.05f);
+        weight_data = empty({out_channels, in_channels / groups, kernel_height, kernel_width}, ScalarType::Float);
+        for (int64_t i = 0; i < weight_data.numel(); ++i) weight_data.data_ptr<float>()[i] = nd(rng);
+        if (bias_term) {
+            bias_data = empty({out_channels}, ScalarType::Float);
+            for (int i = 0; i < out_channels; ++i) bias_data.data_ptr<float>()[i] = 0.1f * nd(rng);
+        }
+        return 0;
+    }
     std::uniform_int_distribution<int> wd(-127, 127);
     std::uniform_real_distribution<float> u(0.f, 1.f);
     const bool depthwise = in_channels == groups && groups == out_channels && groups > 1;
@@ -177,9 +187,22 @@ int ConvolutionLayer::load_model(const Initializer& initializer) {
 
 // Tensor/ConvolutionLayer.cpp:298-304 -> create_pipeline_int8 (:666-752)
 int ConvolutionLayer::create_pipeline(const NetOption& opt) {
-    if (!int8_scale_term) return -1;  // the fp32 layer is not part of this build
     if (!opt.gpu) return -1;
-    if (weight_data.defined() && weight_data.scalar_type() != ScalarType::Byte) return -1;  // fp32 weights: the fp32 layer again
+    if (!int8_scale_term) {
+        // Tensor/ConvolutionLayer.cpp:298-503: the fp32 layer. One kernel, no weight transforms to choose from.
+        if (!weight_data.defined() || weight_data.scalar_type() != ScalarType::Float) return -1;
+        if (bias_term && !bias_data.defined()) return -1;
+        release_gpu();
+        gpu_ctx_ = opt.gpu;
+        ott_conv_desc d{};
+        d.cin = in_channels; d.cout = out_channels; d.kh = kernel_height; d.kw = kernel_width;
+        d.sh = stride_height; d.sw = stride_width; d.ph = padding_height; d.pw = padding_width;
+        d.dh = dilation_height; d.dw = dilation_width; d.groups = groups; d.bias_term = bias_term;
+        d.int8_scale_term = 0; d.act_type = activation_type;
+        d.act_param0 = activation_params.defined() ? activation_params.data_ptr<float>()[0] : (activation_type == 2 ? 0.1f : 0.f);
+        return ott_conv_f32_create(opt.gpu, &d, weight_data.data_ptr<float>(), bias_term ? bias_data.data_ptr<float>() : nullptr, &gpu_conv_f32_);
+    }
+    if (weight_data.defined() && weight_data.scalar_type() != ScalarType::Byte) return -1;  // int8 layer with fp32 weights
     if (!weight_data.defined() || !weight_data_int8_scales.defined() || !bottom_blob_int8_scales.defined()) return -1;
     release_gpu();
     gpu_ctx_ = opt.gpu;
@@ -218,7 +241,9 @@ void ConvolutionLayer::release_gpu() {
     if (gpu_conv_) ott_conv_int8_destroy(gpu_ctx_, gpu_conv_);
     if (gpu_conv_handover_) ott_conv_int8_destroy(gpu_ctx_, gpu_conv_handover_);
     if (gpu_conv_routed_) ott_conv_int8_destroy(gpu_ctx_, gpu_conv_routed_);
+    if (gpu_conv_f32_) ott_conv_f32_destroy(gpu_ctx_, gpu_conv_f32_);
     gpu_conv_ = gpu_conv_handover_ = gpu_conv_routed_ = nullptr;
+    gpu_conv_f32_ = nullptr;
 }
 
 bool ConvolutionLayer::routable_consumer() const {
@@ -414,6 +439,19 @@ bool ConvolutionLayer::can_fuse_maxpool() const {
 
 // Tensor/ConvolutionLayer.cpp:507-511 -> forward_int8 (:754-847). Device tensors in and out; asynchronous.
 int ConvolutionLayer::forward(const Tensor& bottom_blob, Tensor& top_blob, const NetOption& opt) const {
+    if (gpu_conv_f32_) {
+        if (!bottom_blob.defined() || bottom_blob.device() != Device::CUDA || bottom_blob.dim() != 4 || bottom_blob.scalar_type() != ScalarType::Float ||
+            (int)bottom_blob.size(1) != in_channels)
+            return -1;
+        Tensor src = materialize(opt, bottom_blob);
+        if (!src.defined()) return -100;
+        const int n = (int)src.size(0), h = (int)src.size(2), w = (int)src.size(3);
+        const int oh = (h + 2 * padding_height - dilation_height * (kernel_height - 1) - 1) / stride_height + 1;
+        const int ow = (w + 2 * padding_width - dilation_width * (kernel_width - 1) - 1) / stride_width + 1;
+        top_blob = device_empty(opt, {n, out_channels, oh, ow}, ScalarType::Float, Layout::NCHW);
+        if (!top_blob.defined()) return -100;
+        return ott_conv_f32_forward(opt.gpu, gpu_conv_f32_, src.data_ptr<float>(), n, h, w, top_blob.data_ptr<float>());
+    }
     if (!gpu_conv_ || !bottom_blob.defined() || bottom_blob.device() != Device::CUDA || bottom_blob.dim() != 4) return -1;
     const int n = (int)bottom_blob.size(0), c = (int)bottom_blob.size(1), h = (int)bottom_blob.size(2), w = (int)bottom_blob.size(3);
     if (opt.routing_active && gpu_conv_routed_) return forward_routed(bottom_blob, top_blob, opt);

@@ -181,6 +181,16 @@ int ott_net_blob_shape(const ott_net* net, const char* blob, int shape[4]) {
     return OTT_OK;
 }
 
+int ott_net_blob_element_size(const ott_net* net, const char* blob) {
+    if (!net || !blob) return 0;
+    const int b = net->net.find_blob_index_by_name(blob);
+    if (b < 0) return 0;
+    // a requantizing convolution's blob is int8 (Tensor/ConvolutionLayer.cpp:834-844); every other blob is fp32
+    const int prod = net->net.blob(b).producer;
+    const auto* c = prod >= 0 ? dynamic_cast<const otter::ConvolutionLayer*>(net->net.layer(prod)) : nullptr;
+    return (c && c->int8_scale_term > 100) ? 1 : 4;
+}
+
 int ott_net_set_conv_params(ott_net* net, const char* layer, const int8_t* w_oihw, const float* bias, const float* w_scales,
                             const float* in_scales, int n_in_scales, const float* out_scales, int n_out_scales) {
     if (!net || !layer || !w_oihw || !w_scales || !in_scales) return OTT_ERR_INVALID;
@@ -207,6 +217,23 @@ int ott_net_set_conv_params(ott_net* net, const char* layer, const int8_t* w_oih
     }
     net->error.clear();
     net->drop_pipelines();  // captured forwards address the old parameters
+    return net->net.recreate_pipeline(idx);
+}
+
+int ott_net_set_conv_params_f32(ott_net* net, const char* layer, const float* w_oihw, const float* bias) {
+    if (!net || !layer || !w_oihw) return OTT_ERR_INVALID;
+    const int idx = net->net.find_layer_index_by_name(layer);
+    auto* c = idx < 0 ? nullptr : dynamic_cast<otter::ConvolutionLayer*>(net->net.layer(idx));
+    if (!c || c->int8_scale_term != 0) return fail(net, OTT_ERR_INVALID, std::string("no fp32 Convolution layer named ") + layer);
+    c->weight_data = otter::empty({c->out_channels, c->in_channels / c->groups, c->kernel_height, c->kernel_width}, otter::ScalarType::Float);
+    std::memcpy(c->weight_data.raw_data(), w_oihw, (size_t)c->weight_data.numel() * sizeof(float));
+    if (c->bias_term) {
+        if (!bias) return fail(net, OTT_ERR_INVALID, "layer has a bias term but bias is NULL");
+        c->bias_data = otter::empty({c->out_channels}, otter::ScalarType::Float);
+        std::memcpy(c->bias_data.raw_data(), bias, sizeof(float) * (size_t)c->out_channels);
+    }
+    net->error.clear();
+    net->drop_pipelines();
     return net->net.recreate_pipeline(idx);
 }
 

@@ -260,7 +260,7 @@ bool table_arrays(const Tensor& t, std::vector<const float*>& bufs, std::vector<
 Tensor materialize(const NetOption& opt, const Tensor& t);  // dense fp32 NCHW copy of a plane table (or t itself)
 constexpr int kMaxTableBufs = 12, kMaxTableChannels = 512;  // limits of the kernels' plane tables
 
-// ---- ConvolutionLayer (Tensor/ConvolutionLayer.hpp:15-99): the quantized half only ----
+// ---- ConvolutionLayer (Tensor/ConvolutionLayer.hpp:15-99): the quantized layer, and the plain fp32 layer as one kernel ----
 enum class ConvParam : int {
     In_channels, Out_channels, Kernel_height, Kernel_width, Stride_height, Stride_width, Padding_height, Padding_width,
     Dilation_height, Dilation_width, Output_padding_height, Output_padding_width, Group, Bias_term, Weight_data_size,
@@ -328,6 +328,7 @@ private:
     void release_gpu();
     ott_conv* gpu_conv_ = nullptr;
     ott_conv* gpu_conv_handover_ = nullptr;
+    ott_conv_f32* gpu_conv_f32_ = nullptr;  // the fp32 layer (int8_scale_term == 0)
     ott_ctx* gpu_ctx_ = nullptr;
 };
 
