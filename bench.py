@@ -123,11 +123,13 @@ def measured_peaks():
     return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
 
 
-def max_over_ranks(values, dist, device="cuda"):
+def max_over_ranks(values, dist, device=None):
     """Element-wise maximum of a list of per-rank numbers over all ranks (the slowest rank sets the step time)."""
     if dist is None:
         return [float(v) for v in values]
     import torch
+    if device is None:  # this rank's own GPU, whatever device the library made current last
+        device = f"cuda:{os.environ.get('LOCAL_RANK', '0')}"
     t = torch.tensor([float(v) for v in values], device=device, dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return [float(v) for v in t.tolist()]
@@ -608,6 +610,22 @@ def checker_outputs(layers, params, x, outputs):
     return walk(layers, np.ascontiguousarray(x), oracle_conv(params), want=list(outputs), upsample_fn=oracle_upsample)
 
 
+def e2e_record(n, world, proc_s, copy_s, group_s, group_parity, in_bytes, out_bytes, steps):
+    """The end-to-end entry of the line. One GPU: ott_net_forward on pinned host buffers. Several GPUs: the headline is
+    ott_net_group_forward driven by one process (when it ran), and the one-process-per-GPU figure stands beside it."""
+    rec = {"unit": "images/s", "steps": steps, "h2d_bytes_per_step": in_bytes * (world if group_s else 1), "d2h_bytes_per_step": out_bytes * (world if group_s else 1),
+           "copy_only_ms": copy_s * 1e3,
+           "copy_only": "the step's host->device and device->host copies alone, same chunks and streams, no kernels (per GPU, slowest rank)"}
+    if group_s:
+        rec.update({"value": n * world / group_s, "ms_per_step": group_s * 1e3,
+                    "call": f"ott_net_group_forward: one process, one Net replica and host thread per GPU, {n * world} images per call",
+                    "parity_checked": group_parity,
+                    "one_process_per_gpu": {"value": n * world / proc_s, "ms_per_step": proc_s * 1e3, "call": "ott_net_forward in every rank, slowest rank"}})
+    else:
+        rec.update({"value": n * world / proc_s, "ms_per_step": proc_s * 1e3, "call": "ott_net_forward"})
+    return rec
+
+
 def kernel_records(device, names, int8_peak, hbm_peak, steps=10, warmup=3):
     """The single-layer configurations as one record each: the layer's convolution kernel timed alone with CUDA events
     on the context's stream (input resident in HBM and larger than L2 together with the output), against the roof that
@@ -802,6 +820,82 @@ def run_net_gpu_arm(args, cfg):
     barrier()
     e2e_s = (time.perf_counter() - t0) / e2e_steps
 
+    # the same step with the kernels left out: this rank's input batch up, its outputs down, through the two copy streams the
+    # host-buffer forward uses, in the same chunks. What remains of e2e above this is pipeline fill/drain and launch cost.
+    dout = ctx.malloc(out_bytes)
+    host_chunk = 64
+
+    def copy_only():
+        for b0 in range(0, n, host_chunk):
+            nb = min(host_chunk, n - b0)
+            ctx.check(lib.ott_memcpy_overlapped(ctx.h, 0, C.c_void_p(din + b0 * img_bytes), C.c_void_p(hin.value + b0 * img_bytes), nb * img_bytes))
+            off = 0
+            for hp, e in zip(houts, out_elems):
+                ctx.check(lib.ott_memcpy_overlapped(ctx.h, 1, C.c_void_p(hp.value + b0 * e * 4), C.c_void_p(dout + off + b0 * e * 4), nb * e * 4))
+                off += n * e * 4
+        ctx.sync()
+
+    saved_out = [np.ctypeslib.as_array(C.cast(hp, C.POINTER(C.c_float)), shape=(n * e,)).copy() for hp, e in zip(houts, out_elems)] if parity is not None else None
+    copy_only()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        copy_only()
+    barrier()
+    copy_s = (time.perf_counter() - t0) / e2e_steps
+    ctx.free(dout)
+    if saved_out is not None:  # the copy-only leg overwrote the host outputs the self-check below reads
+        for hp, e, sv in zip(houts, out_elems, saved_out):
+            np.ctypeslib.as_array(C.cast(hp, C.POINTER(C.c_float)), shape=(n * e,))[:] = sv
+
+    # Several GPUs: the product's own multi-GPU call. Rank 0 alone builds one Net replica per GPU (ott_net_group_*) and pushes
+    # the whole job's batch, world * n images in one pinned buffer, through ott_net_group_forward: one process, one host thread
+    # per GPU. The other ranks wait on the host (a gloo barrier), their GPUs idle.
+    group_e2e_s, group_parity = None, None
+    if world > 1:
+        import torch.distributed as tdist
+        side = tdist.new_group(backend="gloo")
+        tdist.barrier(group=side)
+        if rank == 0:
+            from tensor_b200 import NetGroup
+            group = NetGroup(list(range(world)))
+            for m in group.members:
+                for l in layers:
+                    m.add_layer(**l)
+                m.compile()
+                for name, p in params.items():
+                    m.set_conv_params(name, p["weight"], p["bias"], p["w_scales"], p["in_scales"], p["out_scales"])
+            gn = n * world
+            ghin = C.c_void_p()
+            assert lib.ott_host_alloc(gn * img_bytes, C.byref(ghin)) == 0
+            gin = np.ctypeslib.as_array(C.cast(ghin, C.POINTER(C.c_float)), shape=(gn, 3, H, W))
+            for r in range(world):
+                gin[r * n:(r + 1) * n] = host_in  # the same images on every GPU: the check below knows their outputs
+            ghouts = []
+            for e in out_elems:
+                hp = C.c_void_p()
+                assert lib.ott_host_alloc(gn * e * 4, C.byref(hp)) == 0
+                ghouts.append(hp)
+            gptrs = [h.value for h in ghouts]
+            group.forward_raw("data", ghin, (gn, 3, H, W), outputs, gptrs)
+            t0 = time.perf_counter()
+            for _ in range(e2e_steps):
+                group.forward_raw("data", ghin, (gn, 3, H, W), outputs, gptrs)
+            group_e2e_s = (time.perf_counter() - t0) / e2e_steps
+            if parity is not None:
+                group_parity = True
+                for ci, i in enumerate(check_imgs):
+                    for r in (0, world - 1):
+                        for oi, (o, e) in enumerate(zip(outputs, out_elems)):
+                            got = np.ctypeslib.as_array(C.cast(ghouts[oi], C.POINTER(C.c_float)), shape=(gn, e))[r * n + i]
+                            group_parity = group_parity and bool(np.array_equal(got.view(np.int32), want[ci][o].reshape(-1).view(np.int32)))
+            group.close()
+            lib.ott_host_free(ghin)
+            for hp in ghouts:
+                lib.ott_host_free(hp)
+            torch.cuda.set_device(local_rank)  # the replicas made other devices current on this thread
+        tdist.barrier(group=side)
+
     parity_e2e = None
     if parity is not None:
         parity_e2e = True
@@ -811,10 +905,10 @@ def run_net_gpu_arm(args, cfg):
                 parity_e2e = parity_e2e and bool(np.array_equal(got.view(np.int32), want[ci][o].reshape(-1).view(np.int32)))
     if dist is not None and parity is not None:  # every rank checks its own shard; the line carries the conjunction
         import torch
-        flags = torch.tensor([int(parity), int(parity_e2e)], device="cuda")
+        flags = torch.tensor([int(parity), int(parity_e2e)], device=f"cuda:{local_rank}")
         dist.all_reduce(flags, op=dist.ReduceOp.MIN)
         parity, parity_e2e = bool(flags[0].item()), bool(flags[1].item())
-    (e2e_s,) = max_over_ranks([e2e_s], dist)
+    e2e_s, copy_s = max_over_ranks([e2e_s, copy_s], dist)
     value = whole_job_rate(n, world, step_ms)
     int8_peak, kernels = None, None
     if rank == 0 and world == 1 and not args.no_peak:
@@ -896,8 +990,7 @@ def run_net_gpu_arm(args, cfg):
                        "l2": f"input batch {in_bytes / 1e6:.0f} MB and every stage's activations exceed the 126 MB L2; no flush"},
             "conv_tops": 2.0 * macs * n * world / (step_ms * 1e-3) / 1e12,
             "clocks": clocks, "gpu_launches": int(launches),
-            "e2e": {"value": n * world / e2e_s, "unit": "images/s", "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes,
-                    "ms_per_step": e2e_s * 1e3, "steps": e2e_steps},
+            "e2e": e2e_record(n, world, e2e_s, copy_s, group_e2e_s, group_parity, in_bytes, out_bytes, e2e_steps),
             "roofline": roof, "cpu_baseline": cpu,
             "int8_peak": None if int8_peak is None else {"tops": int8_peak, "how": "torch._int_mm 8192^3 int8 (cuBLASLt), best of 10, CUDA events, same process"},
             "kernels": kernels,
