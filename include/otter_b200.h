@@ -220,6 +220,19 @@ int ott_conv_int8_forward_io(ott_ctx* ctx, const ott_conv* conv, const ott_conv_
                              uint32_t* status_word_dev);
 int ott_conv_int8_set_f32_plane_map(ott_ctx* ctx, ott_conv* conv, const int* plane_of_channel, int planes_total);
 
+/* One ShuffleNetV2 unit branch as one launch: the chain 1x1 convolution -> depthwise 3x3 (stride 1, pad 1) -> 1x1 convolution,
+ * i.e. three consecutive ConvolutionLayer::forward_int8 calls (Tensor/ConvolutionLayer.cpp:754-847) whose two intermediate int8
+ * blobs stay in shared memory. Built from three existing layer objects (the last one must outlive the unit): pw1 and dw
+ * requantizing (int8_scale_term > 100), pw1 plain or created with gathered input, pw2 with either output kind; all with a
+ * bias, the 1x1 layers sharing one activation, the depthwise layer without one; at most 128 channels between the layers.
+ * OTT_ERR_UNSUPPORTED otherwise (run the three layers one by one). The result equals theirs bit for bit.
+ * ott_unit_int8_forward_io takes the first layer's input (io->sources for a gathered layer, else io->in_dev as int8 NHWC) and
+ * delivers the last layer's output (out_dev / out_dtype / out_f32_dev / f32_channel_mask as for ott_conv_int8_forward_io). */
+typedef struct ott_unit ott_unit;
+int ott_unit_int8_create(ott_ctx* ctx, const ott_conv* pw1, const ott_conv* dw, const ott_conv* pw2, ott_unit** out);
+int ott_unit_int8_forward_io(ott_ctx* ctx, const ott_unit* unit, const ott_conv_io* io, int n, int h, int w, uint32_t* status_word_dev);
+int ott_unit_int8_destroy(ott_ctx* ctx, ott_unit* unit);
+
 /* Dense fp32 NCHW copy [n][channels][hw] of planes described the same way (for consumers that need one tensor). */
 int ott_gather_channels_f32(ott_ctx* ctx, const float* const* buffers, const int64_t* image_strides, int n_buffers,
                             const uint32_t* plane_refs, int channels, int n, int hw, float* dst_dev);

@@ -65,6 +65,9 @@ SIGNATURES = {
     "ott_conv_int8_gathered_layout": (i32, [vp, C.POINTER(i32), vp, i32]),
     "ott_conv_int8_set_f32_plane_map": (i32, [vp, vp, vp, i32]),
     "ott_conv_int8_forward_io": (i32, [vp, vp, vp, i32, i32, i32, vp]),
+    "ott_unit_int8_create": (i32, [vp, vp, vp, vp, C.POINTER(vp)]),
+    "ott_unit_int8_forward_io": (i32, [vp, vp, vp, i32, i32, i32, vp]),
+    "ott_unit_int8_destroy": (i32, [vp, vp]),
     "ott_gather_channels_f32": (i32, [vp, vp, vp, i32, vp, i32, i32, i32, vp]),
     "ott_add_gather_f32": (i32, [vp, vp, vp, i32, vp, vp, vp, i32, vp, i32, i32, i32, vp]),
     "ott_conv_int8_forward_maxpool": (i32, [vp, vp, vp, i32, i32, i32, i32, vp]),
@@ -340,6 +343,38 @@ class ConvInt8:
     def close(self):
         if self.h:
             self.ctx.lib.ott_conv_int8_destroy(self.ctx.h, self.h)
+            self.h = None
+
+
+class UnitInt8:
+    """The chain pw1 -> depthwise 3x3 -> pw2 of three ConvInt8 layers as one launch (ott_unit). pw2 must outlive the unit."""
+
+    def __init__(self, ctx: Context, pw1: "ConvInt8", dw: "ConvInt8", pw2: "ConvInt8"):
+        self.ctx, self.cout = ctx, pw2.desc.cout
+        h = C.c_void_p()
+        ctx.check(ctx.lib.ott_unit_int8_create(ctx.h, pw1.h, dw.h, pw2.h, C.byref(h)))
+        self.h = h
+
+    def forward_io(self, n, h, w, out_dev: int, out_dtype: int, *, in_dev: int = 0, sources=None, out_f32_dev: int = 0, f32_channels=None):
+        io = OttConvIO()
+        io.in_dev, io.in_dtype = (in_dev or None), S8_NHWC
+        keep = []
+        if sources is not None:
+            arr = (C.c_void_p * len(sources))(*[C.c_void_p(p) for p in sources])
+            keep.append(arr)
+            io.sources, io.n_sources = C.cast(arr, C.POINTER(C.c_void_p)), len(sources)
+        io.out_dev, io.out_dtype = out_dev, out_dtype
+        if out_f32_dev:
+            mask = np.zeros((self.cout + 31) // 32, np.uint32)
+            for c in f32_channels:
+                mask[c >> 5] |= np.uint32(1 << (c & 31))
+            keep.append(mask)
+            io.out_f32_dev, io.f32_channel_mask = out_f32_dev, mask.ctypes.data
+        self.ctx.check(self.ctx.lib.ott_unit_int8_forward_io(self.ctx.h, self.h, C.byref(io), n, h, w, None))
+
+    def close(self):
+        if self.h:
+            self.ctx.lib.ott_unit_int8_destroy(self.ctx.h, self.h)
             self.h = None
 
 

@@ -565,6 +565,7 @@ int conv_create_impl(ott_ctx* ctx, const ott_conv_desc* d, const int8_t* w_oihw,
         }
         wpacked.resize((size_t)c->plan.cout_rows * c->plan.k_total);
         umma_pack_weights(c->plan, wk.data(), kk, d->cout, 1, 1, wpacked.data());
+        c->w_korder = std::move(wk);
     } else if (depthwise) {
         c->kind = OTT_KERNEL_DEPTHWISE;
         // [tap][c_pad], channel innermost: what depthwise.cu reads as 32-bit words of 4 channels

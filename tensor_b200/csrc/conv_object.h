@@ -32,6 +32,7 @@ struct ott_conv {
     std::vector<uint16_t> block_x;
     std::vector<uint8_t> block_src;
     std::vector<int> src_channels;
+    std::vector<int8_t> w_korder;  // gathered 1x1 layer: the weights against that K order, [cout][block_x.size() * 32]
     // a depthwise layer with gathered input runs on a permuted, padded channel order (whole 16-channel groups of the sources):
     // position[c] = where logical channel c lies in that order, stored_channels = its length (also the output's channels)
     std::vector<int> position;
