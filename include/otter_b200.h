@@ -80,6 +80,11 @@ int ott_sync(ott_ctx* ctx);
  * names the word in ott_last_error, and clears it, and the context stays usable. The limit is 2000 ms per wait unless changed
  * here (calls enqueued afterwards use the new value). */
 int ott_set_wait_limit_ms(ott_ctx* ctx, int ms);
+/* Depthwise 3x3 layers (stride 1 / 2, pad 1) whose input is int8 NHWC can run on the tensor cores (each filter tap one
+ * tcgen05.mma against a diagonal weight matrix, so the channel-innermost layout needs no byte transposes). mode 1 (default):
+ * layers of at most 64 channels do, where that is faster (every tap costs one 128-row MMA per 32 channels, which wide layers
+ * lose against the CUDA-core kernel); 0: none; 2: every layer the kernel supports. Same bits in every mode. */
+int ott_set_depthwise_tensor_cores(ott_ctx* ctx, int mode);
 /* Test hooks for the failure paths; neither touches a GPU in a way that can fault it.
  * ott_debug_wait_probe enqueues a one-CTA kernel whose only wait can never complete (nobody arrives on its barrier), so
  * it runs out after the context's wait limit and reports through the status word like the real kernels.

@@ -129,6 +129,13 @@ int ott_set_wait_limit_ms(ott_ctx* ctx, int ms) {
     return OTT_OK;
 }
 
+int ott_set_depthwise_tensor_cores(ott_ctx* ctx, int on) {
+    if (!ctx) return OTT_ERR_INVALID;
+    if (on < 0 || on > 2) return OTT_ERR_INVALID;
+    ctx->dw_tensor_cores = on;
+    return OTT_OK;
+}
+
 int ott_debug_fail_alloc_after(ott_ctx* ctx, int n) {
     if (!ctx) return OTT_ERR_INVALID;
     ctx->alloc->fail_after(n);
@@ -596,6 +603,22 @@ int conv_create_impl(ott_ctx* ctx, const ott_conv_desc* d, const int8_t* w_oihw,
         depthwise_tiled_pack_weights(w_oihw, d->cout, c->cout_pad, d->kh, wtiled.data());
         rc = upload(ctx, wtiled.data(), wtiled.size() * 4, (void**)&c->w_tiled_dev);
     }
+    if (rc == OTT_OK && depthwise && !gi && d->kh == 3 && d->kw == 3 && d->ph == 1 && d->pw == 1 && d->dh == 1 && d->dw == 1 && d->sh == d->sw &&
+        (d->sh == 1 || d->sh == 2) && d->rounding == OTT_ROUND_ADD_HALF_TRUNC) {
+        int smem_optin = 0;
+        cudaDeviceGetAttribute(&smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, ctx->device);
+        if (dw_umma_plan(d->cout, d->sh, smem_optin, &c->dw_plan)) {
+            std::vector<int8_t> wd(dw_umma_weight_bytes(c->dw_plan));
+            dw_umma_pack_weights(c->dw_plan, w_oihw, d->cout, wd.data());
+            rc = upload(ctx, wd.data(), wd.size(), (void**)&c->w_dwu_dev);
+            if (rc == OTT_OK) {
+                rc = cudaStreamSynchronize(ctx->stream) == cudaSuccess ? OTT_OK : ctx->fail(OTT_ERR_CUDA, "upload failed");  // wd dies here
+                const char* err = rc == OTT_OK ? dw_umma_encode_weight_map(c->dw_plan, c->w_dwu_dev, c->weight_map_dw) : nullptr;
+                if (err) rc = ctx->fail(OTT_ERR_CUDA, "%s", err);
+                c->dw_umma = rc == OTT_OK;
+            }
+        }
+    }
     if (rc == OTT_OK) rc = upload(ctx, scale_in.data(), sizeof(float) * c->cout_pad, (void**)&c->scale_in_dev);
     if (rc == OTT_OK) rc = upload(ctx, bias_p.data(), sizeof(float) * c->cout_pad, (void**)&c->bias_dev);
     if (rc == OTT_OK) rc = upload(ctx, scale_out.data(), sizeof(float) * c->cout_pad, (void**)&c->scale_out_dev);
@@ -620,6 +643,7 @@ int ott_conv_int8_destroy(ott_ctx* ctx, ott_conv* c) {
     if (ctx) {
         ctx->alloc->free(c->w_dev);
         ctx->alloc->free(c->w_tiled_dev);
+        ctx->alloc->free(c->w_dwu_dev);
         ctx->alloc->free(c->scale_in_dev);
         ctx->alloc->free(c->bias_dev);
         ctx->alloc->free(c->scale_out_dev);
@@ -927,6 +951,22 @@ int conv_forward_impl(ott_ctx* ctx, const ott_conv* c, const void* in_dev, const
         for (size_t g = 0; g < c->block_x.size(); ++g) groups8.ref[g] = ((uint32_t)c->block_src[g] << 24) | c->block_x[g];
         gather = &groups8;
         in_dev = sources[0];
+    }
+    // A depthwise layer with gathered input whose channel groups are one source tensor's first groups, in order, reads that
+    // tensor like a plain layer does.
+    bool whole_source = gathered && c->kind == OTT_KERNEL_DEPTHWISE && n_sources == 1;
+    for (size_t g = 0; whole_source && g < c->block_x.size(); ++g) whole_source = c->block_x[g] == 16 * g;
+    // Narrow layers (at most 64 channels) with int8 NHWC input: the multiply-adds go to the tensor cores as the data lies, no
+    // byte transposes. Wider layers pay one 128-row MMA per tap and 32 channels, which the CUDA-core kernel beats.
+    if (c->kind == OTT_KERNEL_DEPTHWISE && c->dw_umma && (ctx->dw_tensor_cores == 2 || (ctx->dw_tensor_cores == 1 && c->dw_plan.ncb <= 2)) && (!gathered || whole_source) &&
+        in_dtype == OTT_S8_NHWC && out_dtype != OTT_S32_NHWC) {
+        ConvShape st = s;
+        if (gathered) st.cin_pad = nhwc_channels(c->src_channels[0]);
+        const char* err = launch_dw_umma(ctx->stream, ctx->sm_count, c->dw_plan, c->weight_map_dw, st, static_cast<const int8_t*>(in_dev), ep, out_dev,
+                                         out_dtype, status, ctx->wait_limit_ns);
+        if (err) return ctx->fail(OTT_ERR_CUDA, "%s: %s", err, cudaGetErrorString(cudaGetLastError()));
+        ctx->launches += 1;
+        return OTT_OK;
     }
     if (c->kind == OTT_KERNEL_DEPTHWISE && c->w_tiled_dev && depthwise_tiled_supports(s, out_dtype) &&
         (in_dtype != OTT_F32_NCHW || d.cin <= kGatherMaxChannels)) {

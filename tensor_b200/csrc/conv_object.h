@@ -6,6 +6,7 @@
 
 #include "../../include/otter_b200.h"
 #include "dense_umma.h"
+#include "dw_umma.h"
 
 struct ott_conv {
     ott_conv_desc d{};
@@ -38,4 +39,9 @@ struct ott_conv {
     std::vector<int> position;
     int stored_channels = 0;
     alignas(128) unsigned char weight_map[128];
+    // depthwise 3x3 (stride 1 / 2, pad 1) with int8 input: the tensor-core kernel's plan, diagonal weight panel and its TMA descriptor
+    bool dw_umma = false;
+    ottk::DwPlan dw_plan{};
+    int8_t* w_dwu_dev = nullptr;
+    alignas(128) unsigned char weight_map_dw[128];
 };

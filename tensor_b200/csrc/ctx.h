@@ -157,6 +157,7 @@ struct ott_ctx {
     std::string last_error;
     uint64_t launches = 0;
     uint64_t capture_launches0 = UINT64_MAX;  // value of `launches` when the open graph capture began; UINT64_MAX: none open
+    int dw_tensor_cores = 1;  // depthwise 3x3 layers with int8 input on the tensor cores: 0 never, 1 narrow layers, 2 always (ott_set_depthwise_tensor_cores)
     unsigned long long wait_limit_ns = 2000000000ull;  // limit of every bounded wait inside the kernels (ott_set_wait_limit_ms)
     uint32_t* status_dev = nullptr;   // default status word the kernels report into
     uint32_t* status_host = nullptr;  // pinned mirror
