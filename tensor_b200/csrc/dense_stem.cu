@@ -155,7 +155,12 @@ dense_stem_pool_mma_kernel(const float* __restrict__ x, const __grid_constant__ 
     uint8_t* sA = bp;                                   // [512 rows][32 B], 32-byte swizzle
     uint8_t* sB = bp + SPM_ROWS * 32;                   // [32 output channels][32 B]
     uint32_t(*tin)[IH][RP] = reinterpret_cast<uint32_t(*)[IH][RP]>(bp + SPM_ROWS * 32 + 1024);  // [3][IH][RP]
-    float* conv = reinterpret_cast<float*>(bp + SPM_ROWS * 32 + 1024 + 3 * IH * RP * 4);          // [cout][SP_CY][SP_CX]
+    // The s32 accumulators of the convolution tile, [pixel][pitch]: written once the MMAs have completed, over the im2col
+    // rows, the filter rows and the input planes, which are all dead by then.
+    int* cacc = reinterpret_cast<int*>(bp);
+    const int cout4 = (s.cout + 3) >> 2;   // 4-channel groups
+    const int pitch = cout4 * 4 + 4;       // s32 per pixel row: 4 mod 8 words, so the 16-byte accesses of both phases spread over the banks
+    __shared__ __align__(16) float sprm[3][ST_COUT_MAX];  // scale_in, bias, scale_out
     __shared__ __align__(8) unsigned long long bar_storage;
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
@@ -177,6 +182,12 @@ dense_stem_pool_mma_kernel(const float* __restrict__ x, const __grid_constant__ 
         mbar_init(bar, 1);
         abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (threadIdx.x >= 64 && threadIdx.x < 64 + ST_COUT_MAX) {
+        const int o = threadIdx.x - 64;
+        sprm[0][o] = P.scale_in[o];
+        sprm[1][o] = P.bias[o];
+        sprm[2][o] = P.scale_out[o];
     }
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(SPM_TMEM_COLS) : "memory");
@@ -274,7 +285,10 @@ dense_stem_pool_mma_kernel(const float* __restrict__ x, const __grid_constant__ 
     tc_fence_after();
 
     if (ok) {
-        const float outside = pad_zero ? 0.f : -INFINITY;
+        // Accumulators -> shared memory as they are (one 16-byte store per four channels). Max-pooling happens on these exact
+        // s32 sums: dequantize + activation is non-decreasing in the sum for the non-negative scales the layer is prepared with,
+        // so the maximum of the window's outputs is the output of the window's maximum, bit for bit, and the float epilogue
+        // runs once per pooled value instead of once per convolution output. Pixels outside the image never win.
         const int q = warp & 3;  // TMEM lane quarter this warp may read
 #pragma unroll
         for (int rep = 0; rep < 2; ++rep) {
@@ -284,24 +298,17 @@ dense_stem_pool_mma_kernel(const float* __restrict__ x, const __grid_constant__ 
             const int ox = cx0 + lx, oy = cy0 + ly;
             const bool inside = ox >= 0 && ox < s.ow && oy >= 0 && oy < s.oh;
             const uint32_t taddr = tmem_base + 32u * t + ((uint32_t)(q * 32) << 16);
+            int v[32];
+            __syncwarp();
+            tmem_ld16(taddr, *reinterpret_cast<int(*)[16]>(&v[0]));
+            if (s.cout > 16) tmem_ld16(taddr + 16u, *reinterpret_cast<int(*)[16]>(&v[16]));  // warp-uniform
+            tmem_wait_ld16(*reinterpret_cast<int(*)[16]>(&v[0]));
+            tmem_wait_ld16(*reinterpret_cast<int(*)[16]>(&v[16]));
+            if (p >= SP_CX * SP_CY) continue;
+            int4* dst = reinterpret_cast<int4*>(cacc + p * pitch);
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                if (half * 16 >= s.cout) break;  // warp-uniform
-                int v[16];
-                __syncwarp();
-                tmem_ld16(taddr + 16u * half, v);
-                tmem_wait_ld16(v);
-                if (p >= SP_CX * SP_CY) continue;
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int co = half * 16 + j;
-                    if (co >= s.cout) break;
-                    const float a = __int2float_rn(v[j]);
-                    float y = has_bias ? __fmaf_rn(a, P.scale_in[co], P.bias[co]) : __fmul_rn(a, P.scale_in[co]);
-                    y = activate_t<ACT>(y, act_p0);
-                    conv[(co * SP_CY + ly) * SP_CX + lx] = inside ? y : outside;
-                }
-            }
+            for (int g = 0; g < ST_COUT_MAX / 4; ++g)
+                if (g < cout4) dst[g] = inside ? make_int4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]) : make_int4(INT_MIN, INT_MIN, INT_MIN, INT_MIN);
         }
     }
     tc_fence_before();
@@ -312,48 +319,61 @@ dense_stem_pool_mma_kernel(const float* __restrict__ x, const __grid_constant__ 
     }
     if (!ok) return;
 
-    if (OUT8) {
-        // thread = (pooled pixel, 4 channels): the 8 threads of a pixel write its 32-byte row, a warp four neighbouring rows
-        int8_t* out8 = static_cast<int8_t*>(out_any);
-        const int quads = s.cout_pad / 4;
-        for (int i = threadIdx.x; i < quads * SP_PY * SP_PX; i += 256) {
-            const int g = i % quads, lx = (i / quads) % SP_PX, ly = i / (quads * SP_PX);
-            const int px = px0 + lx, py = py0 + ly;
-            if (px >= pw_out || py >= ph_out) continue;
-            int q[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int co = g * 4 + j;
-                q[j] = 0;
-                if (co < s.cout) {
-                    const float* cp = conv + (co * SP_CY + 2 * ly) * SP_CX + 2 * lx;
-                    float m = cp[0];
-#pragma unroll
-                    for (int dy = 0; dy < 3; ++dy)
-#pragma unroll
-                        for (int dx = 0; dx < 3; ++dx) m = fmaxf(m, cp[dy * SP_CX + dx]);
-                    const float t = __fmul_rn(m, P.scale_out[co]);
-                    // after ReLU / ReLU6 t >= 0 (scales are positive): trunc(t + 0.5), the saturating pack clamps at 127
-                    q[j] = ((ACT == ACT_RELU || ACT == ACT_RELU6) && rounding == ROUND_ADD_HALF_TRUNC) ? f2i8_nonneg(t) : float2int8(t, rounding);
-                }
-            }
-            *reinterpret_cast<uint32_t*>(out8 + (((long)img * ph_out + py) * pw_out + px) * s.cout_pad + g * 4) = pack_sat_s8x4(q[0], q[1], q[2], q[3]);
-        }
-        return;
-    }
-    float* out = static_cast<float*>(out_any);
+    // thread = (pooled pixel, half of the channels): the two threads of a pixel are neighbours, so its channels leave together
+    const int half_groups = (cout4 + 1) >> 1;
     const long pplane = (long)ph_out * pw_out;
-    for (int i = threadIdx.x; i < s.cout * SP_PY * SP_PX; i += 256) {
-        const int lx = i % SP_PX, ly = (i / SP_PX) % SP_PY, co = i / (SP_PX * SP_PY);
+    for (int i = threadIdx.x; i < 2 * SP_PY * SP_PX; i += 256) {
+        const int g = i & 1, lx = (i >> 1) % SP_PX, ly = (i >> 1) / SP_PX;
         const int px = px0 + lx, py = py0 + ly;
         if (px >= pw_out || py >= ph_out) continue;
-        const float* cp = conv + (co * SP_CY + 2 * ly) * SP_CX + 2 * lx;
-        float m = cp[0];
+        // the reference's packed max-pool lets the padding take part as 0 (Tensor/Pool.cpp:972-975); its plain one never lets it win
+        const bool pad_counts = pad_zero && (2 * py - 1 < 0 || 2 * py + 1 >= s.oh || 2 * px - 1 < 0 || 2 * px + 1 >= s.ow);
+        const int* cp = cacc + ((2 * ly) * SP_CX + 2 * lx) * pitch;
+        const int q_end = g == 0 ? half_groups : cout4;
+        for (int q4 = g == 0 ? 0 : half_groups; q4 < q_end; ++q4) {
+            const int4* w0 = reinterpret_cast<const int4*>(cp + 4 * q4);
+            int4 v[9];
 #pragma unroll
-        for (int dy = 0; dy < 3; ++dy)
+            for (int dy = 0; dy < 3; ++dy)
 #pragma unroll
-            for (int dx = 0; dx < 3; ++dx) m = fmaxf(m, cp[dy * SP_CX + dx]);
-        out[((long)img * s.cout + co) * pplane + (long)py * pw_out + px] = m;
+                for (int dx = 0; dx < 3; ++dx) v[dy * 3 + dx] = *reinterpret_cast<const int4*>(reinterpret_cast<const int*>(w0) + (dy * SP_CX + dx) * pitch);
+            int m[4];
+#define OTT_MAX9(F) __vimax3_s32(__vimax3_s32(v[0].F, v[1].F, v[2].F), __vimax3_s32(v[3].F, v[4].F, v[5].F), __vimax3_s32(v[6].F, v[7].F, v[8].F))
+            m[0] = OTT_MAX9(x); m[1] = OTT_MAX9(y); m[2] = OTT_MAX9(z); m[3] = OTT_MAX9(w);
+#undef OTT_MAX9
+            const float4 si = *reinterpret_cast<const float4*>(&sprm[0][4 * q4]);
+            const float4 bi = *reinterpret_cast<const float4*>(&sprm[1][4 * q4]);
+            const float sia[4] = {si.x, si.y, si.z, si.w}, bia[4] = {bi.x, bi.y, bi.z, bi.w};
+            float y[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float a = __int2float_rn(m[j]);
+                y[j] = activate_t<ACT>(has_bias ? __fmaf_rn(a, sia[j], bia[j]) : __fmul_rn(a, sia[j]), act_p0);
+                if (pad_counts) y[j] = fmaxf(y[j], 0.f);
+            }
+            if (OUT8) {
+                const float4 so = *reinterpret_cast<const float4*>(&sprm[2][4 * q4]);
+                const float soa[4] = {so.x, so.y, so.z, so.w};
+                int qv[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float t = __fmul_rn(y[j], soa[j]);
+                    // after ReLU / ReLU6 t >= 0 (scales are positive): trunc(t + 0.5), the saturating pack clamps at 127
+                    qv[j] = 4 * q4 + j >= s.cout ? 0
+                            : ((ACT == ACT_RELU || ACT == ACT_RELU6) && rounding == ROUND_ADD_HALF_TRUNC) ? f2i8_nonneg(t) : float2int8(t, rounding);
+                }
+                *reinterpret_cast<uint32_t*>(static_cast<int8_t*>(out_any) + (((long)img * ph_out + py) * pw_out + px) * s.cout_pad + 4 * q4) =
+                    pack_sat_s8x4(qv[0], qv[1], qv[2], qv[3]);
+            } else {
+                float* o = static_cast<float*>(out_any) + ((long)img * s.cout + 4 * q4) * pplane + (long)py * pw_out + px;
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (4 * q4 + j < s.cout) o[j * pplane] = y[j];
+            }
+        }
+        if (OUT8 && g == 1)  // padding channels of the int8 row (the stride is a multiple of 16 channels): zeros
+            for (int c4 = cout4; c4 < s.cout_pad / 4; ++c4)
+                *reinterpret_cast<uint32_t*>(static_cast<int8_t*>(out_any) + (((long)img * ph_out + py) * pw_out + px) * s.cout_pad + 4 * c4) = 0u;
     }
 }
 
@@ -385,8 +405,11 @@ bool dense_stem_supports(const ConvShape& s, int in_dtype, int out_dtype) {
 
 static void fill_stem_params(StemParams& P, const ConvShape& s, const int8_t* w, const float* scale_in, const float* bias, const float* scale_out) {
     for (int o = 0; o < s.cout; ++o) {
-        for (int k = 0; k < 27; ++k) P.w[o][k / 4] |= (uint32_t)(uint8_t)w[o * 27 + k] << (8 * (k % 4));
-        P.scale_in[o] = scale_in[o];
+        // The kernels assume scale_in >= 0 (it is 1 / (positive scales)). Should one ever be negative, the channel's filter and
+        // scale are negated together: (-acc) * (-scale) is the same product, exactly.
+        const int sign = scale_in[o] < 0.f ? -1 : 1;
+        for (int k = 0; k < 27; ++k) P.w[o][k / 4] |= (uint32_t)(uint8_t)(int8_t)(sign * w[o * 27 + k]) << (8 * (k % 4));
+        P.scale_in[o] = sign * scale_in[o];
         P.bias[o] = bias ? bias[o] : 0.f;
         P.scale_out[o] = scale_out ? scale_out[o] : 0.f;
     }
@@ -400,8 +423,10 @@ static cudaError_t launch_pool_s(cudaStream_t stream, const float* x, const Stem
     const long blocks = (long)s.n * tiles_x * tiles_y;
     if (blocks <= 0) return cudaSuccess;
     constexpr int IW = (SP_CX - 1) * S + 3, IH = (SP_CY - 1) * S + 3, RP = (IW + 3 + 3) / 4 + 1;
-    // alignment slack + im2col rows + filter rows + input tile + convolution tile
-    const size_t smem = 1024 + (size_t)SPM_ROWS * 32 + 1024 + (size_t)3 * IH * RP * 4 + (size_t)s.cout * SP_CY * SP_CX * 4;
+    // alignment slack + the larger of (im2col rows + filter rows + input tile) and the s32 convolution tile that later overlays them
+    const size_t front = (size_t)SPM_ROWS * 32 + 1024 + (size_t)3 * IH * RP * 4;
+    const size_t tile = (size_t)SP_CY * SP_CX * (((s.cout + 3) / 4) * 4 + 4) * 4;
+    const size_t smem = 1024 + (front > tile ? front : tile);
 #define OTT_STEMPOOL_LAUNCH(ACT)                                                                                          \
     {                                                                                                                     \
         auto kernel = dense_stem_pool_mma_kernel<S, ACT, OUT8>;                                                           \
