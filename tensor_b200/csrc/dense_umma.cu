@@ -151,8 +151,8 @@ dense_umma_kernel(const __grid_constant__ KernelMaps maps, const __grid_constant
                     const int per_img = P.tiles_x * P.tiles_y;
                     img = m / per_img;
                     const int r = m - img * per_img;
-                    y0 = (r / P.tiles_x) * P.th - s.ph;
-                    x0 = (r % P.tiles_x) * P.tw - s.pw;
+                    y0 = (r / P.tiles_x) * P.th * s.sh - s.ph;
+                    x0 = (r % P.tiles_x) * P.tw * s.sw - s.pw;
                 }
                 for (int kb = 0; kb < loads_per_tile; ++kb, ++it) {
                     const uint32_t st = it % P.stages, ph = (it / P.stages) & 1u;
@@ -469,7 +469,7 @@ bool umma_plan_layer(int cin, int cout, int kh, int kw, int sh, int sw, int dh, 
                      bool whole_tile_stages) {
     UmmaPlan p{};
     const int cin_pad = nhwc_channels(cin), cout_pad = nhwc_channels(cout);
-    if (sh != 1 || sw != 1) return false;  // strided dense convolutions go to the direct kernel
+    if (sh < 1 || sw < 1 || sh > 4 || sw > 4) return false;
     if (cin_pad < 32) return false;        // a TMA box may not be wider than the tensor
     p.bkc = cin_pad >= 128 ? 128 : (cin_pad >= 64 ? 64 : 32);
     if (bkc_override == 32 || bkc_override == 64 || bkc_override == 128) p.bkc = bkc_override;
@@ -479,7 +479,9 @@ bool umma_plan_layer(int cin, int cout, int kh, int kw, int sh, int sw, int dh, 
     const long k_total = (long)p.nkb * p.bkc;
     // largest BN (multiple of 16, <= 256) whose weight panel leaves room for at least 3 A stages,
     // preferring a split of cout_pad into equal tiles
-    p.halo = (p.taps > 1 && dh == 1 && dw == 1) ? 1 : 0;
+    // strided and dilated layers load one box per filter tap (a strided layer's box takes every sw-th / sh-th pixel: TMA
+    // element strides); undilated stride-1 k x k layers load one halo tile per pixel tile
+    p.halo = (p.taps > 1 && dh == 1 && dw == 1 && sh == 1 && sw == 1) ? 1 : 0;
     const bool whole = whole_tile_stages && !p.halo && p.taps == 1;
     p.gather_whole = whole ? 1 : 0;
     const long a_stage = p.halo ? ((long)p.bkc * (kHaloTw + kw - 1) * (kHaloTh + kh - 1) + 1023) / 1024 * 1024
@@ -573,7 +575,7 @@ const char* launch_dense_umma(cudaStream_t stream, int sm_count, const UmmaPlan&
         if (out_dtype != DT_S8_NHWC || s.cout > 1024) return "fp32 side output needs an int8 launch with at most 1024 output channels";
         mixed = *mixed_in;
     }
-    const bool flat = s.kh == 1 && s.kw == 1 && s.ph == 0 && s.pw == 0;
+    const bool flat = s.kh == 1 && s.kw == 1 && s.ph == 0 && s.pw == 0 && s.sh == 1 && s.sw == 1;
     p.flat = flat ? 1 : 0;
     cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = CUDA_SUCCESS;
@@ -607,6 +609,7 @@ const char* launch_dense_umma(cudaStream_t stream, int sm_count, const UmmaPlan&
         long best = -1;
         for (int tw = 8; tw <= 128; tw *= 2) {
             const int th = kTileM / tw;
+            if ((tw - 1) * s.sw + 1 > 256 || (th - 1) * s.sh + 1 > 256) continue;  // a TMA box spans at most 256 elements per dimension
             const long cover = (long)((s.ow + tw - 1) / tw) * tw * ((s.oh + th - 1) / th) * th;
             if (best < 0 || cover < best) { best = cover; p.tw = tw; p.th = th; }
         }
@@ -616,7 +619,11 @@ const char* launch_dense_umma(cudaStream_t stream, int sm_count, const UmmaPlan&
         p.m_tiles = s.n * p.tiles_x * p.tiles_y;
         cuuint64_t dims[4] = {(cuuint64_t)s.cin_pad, (cuuint64_t)s.w, (cuuint64_t)s.h, (cuuint64_t)s.n};
         cuuint64_t strides[3] = {(cuuint64_t)s.cin_pad, (cuuint64_t)s.cin_pad * s.w, (cuuint64_t)s.cin_pad * s.w * s.h};
-        cuuint32_t box[4] = {(cuuint32_t)p.bkc, (cuuint32_t)(p.halo ? p.tw + s.kw - 1 : p.tw), (cuuint32_t)(p.halo ? p.th + s.kh - 1 : p.th), 1};
+        // a strided layer's box spans (tw - 1) * sw + 1 columns of which the traversal takes every sw-th: tw land in shared memory
+        cuuint32_t box[4] = {(cuuint32_t)p.bkc, (cuuint32_t)(p.halo ? p.tw + s.kw - 1 : (p.tw - 1) * s.sw + 1),
+                             (cuuint32_t)(p.halo ? p.th + s.kh - 1 : (p.th - 1) * s.sh + 1), 1};
+        estr[1] = (cuuint32_t)s.sw;
+        estr[2] = (cuuint32_t)s.sh;
         r = enc(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)x, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 swizzle_for(p.bkc), CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     }

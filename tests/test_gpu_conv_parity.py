@@ -39,7 +39,7 @@ def test_kernel_selection(ctx):
     from gpu_support import make_layer
     from tensor_b200 import KERNEL_DENSE_DIRECT, KERNEL_DENSE_UMMA, KERNEL_DEPTHWISE
     expect = {"dw3x3s1_256_relu_s8": KERNEL_DEPTHWISE, "pw_64_256_relu6_s8": KERNEL_DENSE_UMMA,
-              "dense3x3_64_f32": KERNEL_DENSE_UMMA, "stem_3_24_s2_f32": KERNEL_DENSE_DIRECT, "dense3x3_s2": KERNEL_DENSE_DIRECT,
+              "dense3x3_64_f32": KERNEL_DENSE_UMMA, "stem_3_24_s2_f32": KERNEL_DENSE_DIRECT, "dense3x3_s2": KERNEL_DENSE_UMMA,
               "pw_512_1024_relu6_s8": KERNEL_DENSE_UMMA, "pw_464_1024": KERNEL_DENSE_UMMA}
     for case, _ in small_cases():
         if case.name in expect:
@@ -84,6 +84,13 @@ def test_batched_equals_single_images(ctx):
     ("halo_3x1_c64", dict(cin=64, cout=64, k=3, kw=1, pad=0, n=2, h=19, w=11, int8_scale_term=2)),
     ("halo_1x3_c64", dict(cin=64, cout=32, k=1, kw=3, pad=0, n=2, h=10, w=21, int8_scale_term=101, act_type=ACT_RELU, s8_input=True)),
     ("dilated_3x3_c64_per_tap_boxes", dict(cin=64, cout=64, k=3, pad=2, dil=2, n=2, h=18, w=15, int8_scale_term=2, act_type=ACT_RELU)),
+    # strided dense layers on the tensor cores: one TMA box per filter tap that takes every second (third) pixel
+    ("strided_3x3_s2_c64_128", dict(cin=64, cout=128, k=3, stride=2, pad=1, n=3, h=56, w=56, int8_scale_term=101, act_type=ACT_RELU, s8_input=True)),
+    ("strided_3x3_s2_odd_f32", dict(cin=32, cout=48, k=3, stride=2, pad=1, n=2, h=37, w=45, int8_scale_term=2)),
+    ("strided_1x1_s2", dict(cin=64, cout=96, k=1, stride=2, pad=0, n=2, h=28, w=30, int8_scale_term=101, act_type=ACT_RELU6)),
+    ("strided_5x5_s2_c32", dict(cin=32, cout=32, k=5, stride=2, pad=2, n=2, h=31, w=29, int8_scale_term=2, act_type=ACT_LRELU, act_param0=0.1)),
+    ("strided_3x3_s3_nopad", dict(cin=48, cout=64, k=3, stride=3, pad=0, n=2, h=40, w=33, int8_scale_term=101, act_type=ACT_RELU, s8_input=True)),
+    ("strided_3x3_s2_wide_rows", dict(cin=32, cout=32, k=3, stride=2, pad=1, n=1, h=6, w=300, int8_scale_term=2)),
     ("two_n_tiles", dict(cin=256, cout=512, k=1, n=3, h=28, w=28, int8_scale_term=101, act_type=ACT_RELU6)),
     ("four_n_tiles", dict(cin=512, cout=1024, k=1, n=2, h=14, w=14, int8_scale_term=101, act_type=ACT_RELU6)),
 ])
