@@ -447,7 +447,7 @@ def run_gpu_arm(args, wl):
             achieved = ops / (conv_ms * 1e-3) / 1e12
             roof = {"bound": "tensor", "achieved": achieved, "peak": tensor_peak, "unit": "TOP/s", "frac": achieved / tensor_peak,
                     "traffic": None, "peak_source": tensor_src}
-        roof["kernel"] = {1: "depthwise_kernel", 2: "dense_umma_kernel", 3: "dense_direct_kernel"}[layer.kernel_kind]
+        roof["kernel"] = lib.ott_conv_int8_kernel_name(ctx.h, layer.h, in_dtype if fused_prologue else S8_NHWC, out_dtype, wl["h"], wl["w"]).decode()
         roof["kernel_ms"] = conv_ms
         roof["algorithmic_bytes_per_launch"] = conv_bytes
         roof["ops_per_launch"] = ops
@@ -681,7 +681,7 @@ def kernel_records(device, names, int8_peak, hbm_peak, steps=10, warmup=3):
             ops, byts = algorithmic_work(wl if fused else {**wl, "in_f32": False}, n)
             tops, gbs = ops / (ms * 1e-3) / 1e12, byts / (ms * 1e-3) / 1e9
             tensor_bound = int8_peak is not None and (ops / byts) * hbm_peak / 1e3 >= int8_peak
-            rec = {"kernel": {1: "depthwise_tiled_kernel", 2: "dense_umma_kernel", 3: "dense_direct_kernel"}[layer.kernel_kind],
+            rec = {"kernel": lib.ott_conv_int8_kernel_name(ctx.h, layer.h, src_dtype, out_dtype, wl["h"], wl["w"]).decode(),
                    "ms": ms, "tops": tops, "gbs": gbs, "ops": ops, "algorithmic_bytes": byts, "launches_timed": steps,
                    "input": "fp32 NCHW" if (wl["in_f32"] and fused) else "int8 NHWC", "output": "int8 NHWC" if wl["term"] > 100 else "fp32 NCHW",
                    "bound": "tensor" if tensor_bound else "hbm",

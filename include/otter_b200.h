@@ -82,8 +82,9 @@ int ott_sync(ott_ctx* ctx);
 int ott_set_wait_limit_ms(ott_ctx* ctx, int ms);
 /* Depthwise 3x3 layers (stride 1 / 2, pad 1) whose input is int8 NHWC can run on the tensor cores (each filter tap one
  * tcgen05.mma against a diagonal weight matrix, so the channel-innermost layout needs no byte transposes). mode 1 (default):
- * layers of at most 64 channels do, where that is faster (every tap costs one 128-row MMA per 32 channels, which wide layers
- * lose against the CUDA-core kernel); 0: none; 2: every layer the kernel supports. Same bits in every mode. */
+ * where that is faster (layers of at most 64 channels, and wider stride-1 layers on maps of 2048 pixels or more: every tap
+ * costs one 128-row MMA per 32 channels, which small wide layers lose against the CUDA-core kernel); 0: none; 2: every layer
+ * the kernel supports. Same bits in every mode. */
 int ott_set_depthwise_tensor_cores(ott_ctx* ctx, int mode);
 /* Test hooks for the failure paths; neither touches a GPU in a way that can fault it.
  * ott_debug_wait_probe enqueues a one-CTA kernel whose only wait can never complete (nobody arrives on its barrier), so
@@ -143,6 +144,9 @@ int ott_conv_int8_create(ott_ctx* ctx, const ott_conv_desc* desc, const int8_t* 
 int ott_conv_int8_destroy(ott_ctx* ctx, ott_conv* conv);
 int ott_conv_int8_kernel_kind(const ott_conv* conv); /* enum ott_kernel_kind */
 int ott_conv_int8_out_shape(const ott_conv* conv, int h, int w, int* oh, int* ow);
+/* name of the convolution kernel a plain (not gathered) forward of this layer launches for the given input / output types and
+ * input size (the choice between the two depthwise kernels depends on them); for benchmark records */
+const char* ott_conv_int8_kernel_name(const ott_ctx* ctx, const ott_conv* conv, int in_dtype, int out_dtype, int h, int w);
 
 /* One forward on DEVICE buffers, asynchronous on the context's stream.
  *   in_dtype  OTT_F32_NCHW (quantized on the way in, as ConvolutionLayer.cpp:770-775) or OTT_S8_NHWC

@@ -58,6 +58,7 @@ SIGNATURES = {
     "ott_conv_int8_create": (i32, [vp, C.POINTER(OttConvDesc), vp, vp, vp, vp, i32, vp, i32, C.POINTER(vp)]),
     "ott_conv_int8_destroy": (i32, [vp, vp]),
     "ott_conv_int8_kernel_kind": (i32, [vp]),
+    "ott_conv_int8_kernel_name": (C.c_char_p, [vp, vp, i32, i32, i32, i32]),
     "ott_conv_int8_out_shape": (i32, [vp, i32, i32, C.POINTER(i32), C.POINTER(i32)]),
     "ott_conv_int8_forward": (i32, [vp, vp, vp, i32, i32, i32, i32, vp, i32, vp]),
     "ott_conv_int8_forward_ex": (i32, [vp, vp, vp, i32, i32, i32, i32, i32, vp, i32, vp]),

@@ -722,6 +722,25 @@ int ott_conv_f32_forward(ott_ctx* ctx, const ott_conv_f32* c, const float* in_de
 
 int ott_conv_int8_kernel_kind(const ott_conv* c) { return c ? c->kind : OTT_ERR_INVALID; }
 
+const char* ott_conv_int8_kernel_name(const ott_ctx* ctx, const ott_conv* c, int in_dtype, int out_dtype, int h, int w) {
+    if (!ctx || !c) return "";
+    const ott_conv_desc& d = c->d;
+    ConvShape s{};
+    s.h = h; s.w = w;
+    s.oh = out_dim(h, d.kh, d.sh, d.ph, d.dh);
+    s.ow = out_dim(w, d.kw, d.sw, d.pw, d.dw);
+    s.cin = d.cin; s.cout = d.cout; s.cin_pad = c->cin_pad; s.cout_pad = c->cout_pad;
+    s.kh = d.kh; s.kw = d.kw; s.sh = d.sh; s.sw = d.sw; s.ph = d.ph; s.pw = d.pw; s.dh = d.dh; s.dw = d.dw;
+    if (c->kind == OTT_KERNEL_DENSE_UMMA) return "dense_umma_kernel";
+    if (c->kind == OTT_KERNEL_DENSE_DIRECT) return dense_stem_supports(s, in_dtype, out_dtype) ? "dense_stem_kernel" : "dense_direct_kernel";
+    const bool gathered = !c->src_channels.empty();
+    const bool tc_wins = c->dw_plan.ncb <= 2 || (d.sh == 1 && (long)s.oh * s.ow >= 2048);
+    if (c->dw_umma && (ctx->dw_tensor_cores == 2 || (ctx->dw_tensor_cores == 1 && tc_wins)) && !gathered && in_dtype == OTT_S8_NHWC && out_dtype != OTT_S32_NHWC)
+        return "dw_umma_kernel";
+    if (c->w_tiled_dev && depthwise_tiled_supports(s, out_dtype)) return "depthwise_tiled_kernel";
+    return "depthwise_kernel";
+}
+
 int ott_conv_int8_out_shape(const ott_conv* c, int h, int w, int* oh, int* ow) {
     if (!c || !oh || !ow) return OTT_ERR_INVALID;
     *oh = out_dim(h, c->d.kh, c->d.sh, c->d.ph, c->d.dh);
@@ -956,9 +975,11 @@ int conv_forward_impl(ott_ctx* ctx, const ott_conv* c, const void* in_dev, const
     // tensor like a plain layer does.
     bool whole_source = gathered && c->kind == OTT_KERNEL_DEPTHWISE && n_sources == 1;
     for (size_t g = 0; whole_source && g < c->block_x.size(); ++g) whole_source = c->block_x[g] == 16 * g;
-    // Narrow layers (at most 64 channels) with int8 NHWC input: the multiply-adds go to the tensor cores as the data lies, no
-    // byte transposes. Wider layers pay one 128-row MMA per tap and 32 channels, which the CUDA-core kernel beats.
-    if (c->kind == OTT_KERNEL_DEPTHWISE && c->dw_umma && (ctx->dw_tensor_cores == 2 || (ctx->dw_tensor_cores == 1 && c->dw_plan.ncb <= 2)) && (!gathered || whole_source) &&
+    // int8 NHWC input: the multiply-adds can go to the tensor cores as the data lies, no byte transposes. Every tap costs one
+    // 128-row MMA (about 100 cycles) per 32 channels and 8 x 16 pixel tile, so this wins for narrow layers (at most 64
+    // channels) and for wide stride-1 layers on maps large enough for the tiles to fit well; elsewhere the CUDA cores do.
+    const bool dw_tc_wins = c->dw_plan.ncb <= 2 || (d.sh == 1 && (long)s.oh * s.ow >= 2048);
+    if (c->kind == OTT_KERNEL_DEPTHWISE && c->dw_umma && (ctx->dw_tensor_cores == 2 || (ctx->dw_tensor_cores == 1 && dw_tc_wins)) && (!gathered || whole_source) &&
         in_dtype == OTT_S8_NHWC && out_dtype != OTT_S32_NHWC) {
         ConvShape st = s;
         if (gathered) st.cin_pad = nhwc_channels(c->src_channels[0]);

@@ -60,10 +60,10 @@ dw_umma_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         mbar_init(bar_w, 1);
         for (int i = 0; i < P.stages; ++i) {
             mbar_init(bar_full + 8u * i, 1);
-            mbar_init(bar_empty + 8u * i, 1);
+            mbar_init(bar_empty + 8u * i, (uint32_t)P.ncb);  // one commit per issuing lane
         }
         for (int i = 0; i < P.acc_bufs; ++i) {
-            mbar_init(bar_afull + 8u * i, 1);
+            mbar_init(bar_afull + 8u * i, (uint32_t)P.ncb);
             mbar_init(bar_aempty + 8u * i, kEpiWarps);
         }
         *abort_flag = 0;
@@ -115,10 +115,15 @@ dw_umma_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            // ---- MMA issuer ----
+        if (lane < P.ncb) {
+            // ---- MMA issuers: lane cb issues the nine taps of channel block cb (an MMA is started by one thread; the lanes of
+            // the warp execute the instruction together, so a tile costs nine issue slots however many channel blocks it has),
+            // and commits its own MMAs to the barriers, whose arrival counts are the number of issuing lanes ----
+            const int cb = lane;
             bool ok = mbar_wait(bar_w, 0, abort_flag, status, 16u, P.wait_ns);
             tc_fence_after();
+            const uint64_t b0 = make_smem_desc(sW + (uint32_t)cb * 9u * 1024u, kBlock);
+            const uint32_t sbo = (uint32_t)(P.stride * P.set_w * kBlock);
             uint32_t it = 0;
             for (int m = m_first; ok && m < P.m_tiles; m += m_step, ++it) {
                 const uint32_t buf = it & acc_mask, use = it / (uint32_t)P.acc_bufs;
@@ -126,22 +131,18 @@ dw_umma_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                 if (!mbar_wait(bar_aempty + 8u * buf, (use & 1u) ^ 1u, abort_flag, status, 4u, P.wait_ns)) { ok = false; break; }
                 if (!mbar_wait(bar_full + 8u * st, ph, abort_flag, status, 2u, P.wait_ns)) { ok = false; break; }
                 tc_fence_after();
-                const uint32_t xs = sX + st * (uint32_t)P.stage_bytes;
-                for (int cb = 0; cb < P.ncb; ++cb) {
-                    const uint32_t d = tmem_base + buf * (uint32_t)P.cols + (uint32_t)(cb * kBlock);
-                    const uint64_t b0 = make_smem_desc(sW + (uint32_t)cb * 9u * 1024u, kBlock);
-                    const uint32_t blk = xs + (uint32_t)(cb * P.block_bytes);
-                    // 8-row groups (one tile row of 8 pixels each) are `stride` input rows apart
-                    const uint64_t a_s0 = make_smem_desc(blk, kBlock, P.stride * P.set_w * kBlock);
-                    const uint64_t a_s1 = make_smem_desc(blk + (uint32_t)P.set_bytes, kBlock, P.stride * P.set_w * kBlock);
+                const uint32_t d = tmem_base + buf * (uint32_t)P.cols + (uint32_t)(cb * kBlock);
+                const uint32_t blk = sX + st * (uint32_t)P.stage_bytes + (uint32_t)(cb * P.block_bytes);
+                // 8-row groups (one tile row of 8 pixels each) are `stride` input rows apart
+                const uint64_t a_s0 = make_smem_desc(blk, kBlock, (int)sbo);
+                const uint64_t a_s1 = make_smem_desc(blk + (uint32_t)P.set_bytes, kBlock, (int)sbo);
 #pragma unroll
-                    for (int tap = 0; tap < 9; ++tap) {
-                        const int ky = tap / 3, kx = tap % 3;
-                        // stride 1: pixel offset (ky, kx) in the one tile; stride 2: kx = 1 reads the second column set, kx = 2 one column on
-                        const uint32_t col = P.stride == 1 ? (uint32_t)kx : (uint32_t)(kx >> 1);
-                        const uint64_t a0 = (P.stride == 2 && kx == 1) ? a_s1 : a_s0;
-                        umma_i8(d, a0 + (uint32_t)(ky * P.set_w + (int)col) * (kBlock >> 4), b0 + (uint32_t)tap * (1024u >> 4), P.idesc, tap != 0 ? 1u : 0u);
-                    }
+                for (int tap = 0; tap < 9; ++tap) {
+                    const int ky = tap / 3, kx = tap % 3;
+                    // stride 1: pixel offset (ky, kx) in the one tile; stride 2: kx = 1 reads the second column set, kx = 2 one column on
+                    const uint32_t col = P.stride == 1 ? (uint32_t)kx : (uint32_t)(kx >> 1);
+                    const uint64_t a0 = (P.stride == 2 && kx == 1) ? a_s1 : a_s0;
+                    umma_i8(d, a0 + (uint32_t)(ky * P.set_w + (int)col) * (kBlock >> 4), b0 + (uint32_t)tap * (1024u >> 4), P.idesc, tap != 0 ? 1u : 0u);
                 }
                 umma_commit(bar_empty + 8u * st);
                 umma_commit(bar_afull + 8u * buf);
