@@ -395,7 +395,12 @@ int create_gathered_depthwise(ott_ctx* ctx, const ott_conv_desc* d, const int8_t
         return ctx->fail(OTT_ERR_UNSUPPORTED, "gathered input: depthwise layers need a 3x3 / 5x5, stride 1 / 2, undilated filter and int8 output");
     for (int i = 1; i < n_in_scales; ++i)
         if (in_scales[i] != in_scales[0]) return ctx->fail(OTT_ERR_UNSUPPORTED, "gathered input: one input scale for all channels");
-    const int C = d->cin, G16 = 16;
+    // Granularity of the groups: 32 channels when the layer will run on the tensor cores (3x3, pad 1, stride 1 / 2: one K block
+    // of the MMA per group; every source must then be at least 32 channels wide), else the CUDA-core kernel's 16.
+    bool tensor = ctx->dw_tensor_cores != 0 && d->kh == 3 && d->kw == 3 && d->ph == 1 && d->pw == 1 && d->sh == d->sw && (d->sh == 1 || d->sh == 2) &&
+                  d->rounding == OTT_ROUND_ADD_HALF_TRUNC;
+    for (int i = 0; tensor && i < n_sources; ++i) tensor = nhwc_channels(source_channels[i]) >= 32;
+    const int C = d->cin, G16 = tensor ? 32 : 16;
     std::vector<int> lo(n_sources, 1 << 30), hi(n_sources, -1), base(n_sources, 0);
     for (int i = 0; i < C; ++i) {
         const int sidx = channel_source[i], pos = channel_index[i];
@@ -415,7 +420,8 @@ int create_gathered_depthwise(ott_ctx* ctx, const ott_conv_desc* d, const int8_t
         }
     }
     const int Cs = (int)block_x.size() * G16, taps = d->kh * d->kw;
-    if (Cs > kGatherMaxChannels * G16) return ctx->fail(OTT_ERR_UNSUPPORTED, "gathered input: too many channel groups");
+    if ((int)block_x.size() > (tensor ? kUmmaMaxGatherBlocks : kGatherMaxChannels))
+        return ctx->fail(OTT_ERR_UNSUPPORTED, "gathered input: too many channel groups");
     std::vector<int> position(C);
     std::vector<int8_t> w2((size_t)Cs * taps, 0);
     std::vector<float> ws2(Cs, 0.f), b2(Cs, 0.f), os2(Cs, 0.f);
@@ -443,6 +449,12 @@ int create_gathered_depthwise(ott_ctx* ctx, const ott_conv_desc* d, const int8_t
     c->src_channels.assign(source_channels, source_channels + n_sources);
     c->position = position;
     c->stored_channels = Cs;
+    c->gather_group = G16;
+    if (tensor && !c->dw_umma) {  // the tensor-core plan did not fit: the groups are of no use to the other kernel
+        ott_conv_int8_destroy(ctx, c);
+        *out = nullptr;
+        return ctx->fail(OTT_ERR_UNSUPPORTED, "gathered input: the depthwise layer does not fit the tensor-core kernel");
+    }
     return OTT_OK;
 }
 }  // namespace
@@ -734,7 +746,7 @@ const char* ott_conv_int8_kernel_name(const ott_ctx* ctx, const ott_conv* c, int
     if (c->kind == OTT_KERNEL_DENSE_UMMA) return "dense_umma_kernel";
     if (c->kind == OTT_KERNEL_DENSE_DIRECT) return dense_stem_supports(s, in_dtype, out_dtype) ? "dense_stem_kernel" : "dense_direct_kernel";
     const bool gathered = !c->src_channels.empty();
-    const bool tc_wins = c->dw_plan.ncb <= 2 || (d.sh == 1 && (long)s.oh * s.ow >= 2048);
+    const bool tc_wins = c->dw_plan.ncb_total <= 2 || (d.sh == 1 && (long)s.oh * s.ow >= 2048);
     if (c->dw_umma && (ctx->dw_tensor_cores == 2 || (ctx->dw_tensor_cores == 1 && tc_wins)) && !gathered && in_dtype == OTT_S8_NHWC && out_dtype != OTT_S32_NHWC)
         return "dw_umma_kernel";
     if (c->w_tiled_dev && depthwise_tiled_supports(s, out_dtype)) return "depthwise_tiled_kernel";
@@ -960,7 +972,11 @@ int conv_forward_impl(ott_ctx* ctx, const ott_conv* c, const void* in_dev, const
 
     uint32_t* status = status_word_dev ? status_word_dev : ctx->status_dev;
     PlaneGather groups8;  // depthwise over gathered int8 input: where each 16-channel group lies
-    if (gathered && c->kind == OTT_KERNEL_DEPTHWISE) {
+    if (gathered && c->kind == OTT_KERNEL_DEPTHWISE && c->gather_group == 32) {
+        for (int i = 0; i < n_sources; ++i)
+            if (!sources[i]) return ctx->fail(OTT_ERR_INVALID, "null source tensor");
+        in_dev = sources[0];
+    } else if (gathered && c->kind == OTT_KERNEL_DEPTHWISE) {
         if (!c->w_tiled_dev || !depthwise_tiled_supports(s, out_dtype)) return ctx->fail(OTT_ERR_UNSUPPORTED, "gathered depthwise layer: tiled kernel only");
         for (int i = 0; i < n_sources; ++i) {
             if (!sources[i]) return ctx->fail(OTT_ERR_INVALID, "null source tensor");
@@ -971,20 +987,25 @@ int conv_forward_impl(ott_ctx* ctx, const ott_conv* c, const void* in_dev, const
         gather = &groups8;
         in_dev = sources[0];
     }
-    // A depthwise layer with gathered input whose channel groups are one source tensor's first groups, in order, reads that
-    // tensor like a plain layer does.
-    bool whole_source = gathered && c->kind == OTT_KERNEL_DEPTHWISE && n_sources == 1;
-    for (size_t g = 0; whole_source && g < c->block_x.size(); ++g) whole_source = c->block_x[g] == 16 * g;
     // int8 NHWC input: the multiply-adds can go to the tensor cores as the data lies, no byte transposes. Every tap costs one
     // 128-row MMA (about 100 cycles) per 32 channels and 8 x 16 pixel tile, so this wins for narrow layers (at most 64
     // channels) and for wide stride-1 layers on maps large enough for the tiles to fit well; elsewhere the CUDA cores do.
-    const bool dw_tc_wins = c->dw_plan.ncb <= 2 || (d.sh == 1 && (long)s.oh * s.ow >= 2048);
-    if (c->kind == OTT_KERNEL_DEPTHWISE && c->dw_umma && (ctx->dw_tensor_cores == 2 || (ctx->dw_tensor_cores == 1 && dw_tc_wins)) && (!gathered || whole_source) &&
-        in_dtype == OTT_S8_NHWC && out_dtype != OTT_S32_NHWC) {
-        ConvShape st = s;
-        if (gathered) st.cin_pad = nhwc_channels(c->src_channels[0]);
-        const char* err = launch_dw_umma(ctx->stream, ctx->sm_count, c->dw_plan, c->weight_map_dw, st, static_cast<const int8_t*>(in_dev), ep, out_dev,
-                                         out_dtype, status, ctx->wait_limit_ns);
+    // A layer with gathered input that was laid out in 32-channel groups always runs here (its groups are the MMA's K blocks).
+    const bool dw_tc_wins = c->dw_plan.ncb_total <= 2 || (d.sh == 1 && (long)s.oh * s.ow >= 2048);
+    const bool dw_gathered_tc = gathered && c->kind == OTT_KERNEL_DEPTHWISE && c->gather_group == 32;
+    if (c->kind == OTT_KERNEL_DEPTHWISE && c->dw_umma && in_dtype == OTT_S8_NHWC && out_dtype != OTT_S32_NHWC &&
+        (dw_gathered_tc || (!gathered && (ctx->dw_tensor_cores == 2 || (ctx->dw_tensor_cores == 1 && dw_tc_wins))))) {
+        UmmaSources us{};
+        if (gathered) {
+            us.n_src = n_sources;
+            for (int i = 0; i < n_sources; ++i) {
+                us.src[i] = sources[i];
+                us.src_cpad[i] = nhwc_channels(c->src_channels[(size_t)i]);
+            }
+            for (size_t b = 0; b < c->block_x.size(); ++b) { us.block_x[b] = c->block_x[b]; us.block_src[b] = c->block_src[b]; }
+        }
+        const char* err = launch_dw_umma(ctx->stream, ctx->sm_count, c->dw_plan, c->weight_map_dw, s, static_cast<const int8_t*>(in_dev), gathered ? &us : nullptr,
+                                         ep, out_dev, out_dtype, status, ctx->wait_limit_ns);
         if (err) return ctx->fail(OTT_ERR_CUDA, "%s: %s", err, cudaGetErrorString(cudaGetLastError()));
         ctx->launches += 1;
         return OTT_OK;

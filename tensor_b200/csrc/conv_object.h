@@ -38,6 +38,7 @@ struct ott_conv {
     // position[c] = where logical channel c lies in that order, stored_channels = its length (also the output's channels)
     std::vector<int> position;
     int stored_channels = 0;
+    int gather_group = 16;  // channels per group of that order: 16 (CUDA-core kernel) or 32 (tensor-core kernel)
     alignas(128) unsigned char weight_map[128];
     // depthwise 3x3 (stride 1 / 2, pad 1) with int8 input: the tensor-core kernel's plan, diagonal weight panel and its TMA descriptor
     bool dw_umma = false;

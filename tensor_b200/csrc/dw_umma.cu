@@ -35,6 +35,13 @@ constexpr int kEpiWarps = 8;
 constexpr int kThreads = 64 + 32 * kEpiWarps;
 constexpr int kMaxStages = 3, kMaxAcc = 2;
 
+// Where the channel blocks come from: one tensor map per source tensor, and per block its source and first channel.
+struct DwMaps {
+    CUtensorMap tm[kUmmaMaxSources];
+    uint16_t block_x[kUmmaMaxGatherBlocks];
+    uint8_t block_src[kUmmaMaxGatherBlocks];
+};
+
 struct DwGeom {
     int n, h, w, oh, ow;
     int cout, cpad;  // real channels, channel stride of the int8 tensors
@@ -42,7 +49,7 @@ struct DwGeom {
 
 template <int ACT, int OUT, bool MULTI>
 __global__ void __launch_bounds__(kThreads, MULTI ? 2 : 1)
-dw_umma_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, const DwPlan P, const DwGeom G, const EpilogueParams ep,
+dw_umma_kernel(const __grid_constant__ DwMaps maps, const __grid_constant__ CUtensorMap tmW, const DwPlan P, const DwGeom G, const EpilogueParams ep,
                void* __restrict__ out, uint32_t* __restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
     pdl_launch_dependents();
@@ -56,27 +63,32 @@ dw_umma_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     float* sp = reinterpret_cast<float*>(base_ptr + P.params);  // scale_in, bias, scale_out: [cols] each
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // this CTA's slice of the layer's channel blocks (depthwise channels are independent, so wide layers are dealt to CTA groups)
+    const int grp = blockIdx.x % P.n_groups;
+    const int cb0 = grp * P.ncb;
+    const int nb = P.ncb_total - cb0 < P.ncb ? P.ncb_total - cb0 : P.ncb;
+    const int c_base = cb0 * kBlock;
     if (threadIdx.x == 0) {
         mbar_init(bar_w, 1);
         for (int i = 0; i < P.stages; ++i) {
             mbar_init(bar_full + 8u * i, 1);
-            mbar_init(bar_empty + 8u * i, (uint32_t)P.ncb);  // one commit per issuing lane
+            mbar_init(bar_empty + 8u * i, (uint32_t)nb);  // one commit per issuing lane
         }
         for (int i = 0; i < P.acc_bufs; ++i) {
-            mbar_init(bar_afull + 8u * i, (uint32_t)P.ncb);
+            mbar_init(bar_afull + 8u * i, (uint32_t)nb);
             mbar_init(bar_aempty + 8u * i, kEpiWarps);
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        mbar_expect_tx(bar_w, (uint32_t)P.ncb * 9u * 1024u);  // the filters do not depend on the previous kernel
-        for (int i = 0; i < P.ncb * 9; ++i) tma_load_2d(&tmW, bar_w, sW + i * 1024u, 0, i * kBlock);
+        mbar_expect_tx(bar_w, (uint32_t)nb * 9u * 1024u);  // the filters do not depend on the previous kernel
+        for (int i = 0; i < nb * 9; ++i) tma_load_2d(&tmW, bar_w, sW + i * 1024u, 0, (cb0 * 9 + i) * kBlock);
     }
     for (int i = threadIdx.x; i < P.cols; i += (int)blockDim.x) {
-        const bool in = i < G.cpad;
-        sp[i] = in ? ep.scale_in[i] : 0.f;
-        sp[P.cols + i] = in ? ep.bias[i] : 0.f;
-        sp[2 * P.cols + i] = in ? ep.scale_out[i] : 0.f;
+        const bool in = c_base + i < G.cpad;
+        sp[i] = in ? ep.scale_in[c_base + i] : 0.f;
+        sp[P.cols + i] = in ? ep.bias[c_base + i] : 0.f;
+        sp[2 * P.cols + i] = in ? ep.scale_out[c_base + i] : 0.f;
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"((uint32_t)P.tmem_cols)
@@ -90,7 +102,7 @@ dw_umma_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     pdl_wait();  // from here on the kernel reads activations and writes outputs
 
     const int per_img = P.tiles_x * P.tiles_y;
-    const int m_first = blockIdx.x, m_step = gridDim.x;
+    const int m_first = blockIdx.x / P.n_groups, m_step = gridDim.x / P.n_groups;
     const uint32_t acc_mask = (uint32_t)P.acc_bufs - 1u;
 
     if (warp == 0) {
@@ -103,11 +115,11 @@ dw_umma_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                 const int y0 = (r / P.tiles_x) * kTh * P.stride - 1, x0 = (r % P.tiles_x) * kTw * P.stride - 1;
                 const uint32_t st = it % P.stages, ph = (it / P.stages) & 1u;
                 if (!mbar_wait(bar_empty + 8u * st, ph ^ 1u, abort_flag, status, 1u, P.wait_ns)) { ok = false; break; }
-                mbar_expect_tx(bar_full + 8u * st, (uint32_t)(P.ncb * P.sets * P.set_load_bytes));
-                for (int cb = 0; cb < P.ncb; ++cb)
+                mbar_expect_tx(bar_full + 8u * st, (uint32_t)(nb * P.sets * P.set_load_bytes));
+                for (int cb = 0; cb < nb; ++cb)
                     for (int s = 0; s < P.sets; ++s)
-                        tma_load_4d(&tmX, bar_full + 8u * st, sX + st * (uint32_t)P.stage_bytes + (uint32_t)(cb * P.block_bytes + s * P.set_bytes), cb * kBlock,
-                                    x0 + s, y0, img);
+                        tma_load_4d(&maps.tm[maps.block_src[cb0 + cb]], bar_full + 8u * st,
+                                    sX + st * (uint32_t)P.stage_bytes + (uint32_t)(cb * P.block_bytes + s * P.set_bytes), (int)maps.block_x[cb0 + cb], x0 + s, y0, img);
             }
             if (!ok) {
                 const unsigned long long t0 = globaltimer_ns();
@@ -115,7 +127,7 @@ dw_umma_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             }
         }
     } else if (warp == 1) {
-        if (lane < P.ncb) {
+        if (lane < nb) {
             // ---- MMA issuers: lane cb issues the nine taps of channel block cb (an MMA is started by one thread; the lanes of
             // the warp execute the instruction together, so a tile costs nine issue slots however many channel blocks it has),
             // and commits its own MMAs to the barriers, whose arrival counts are the number of issuing lanes ----
@@ -163,8 +175,8 @@ dw_umma_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             tc_fence_after();
             const int img = m / per_img, r = m - img * per_img;
             const int oy = (r / P.tiles_x) * kTh + (row >> 3), ox = (r % P.tiles_x) * kTw + (row & 7);
-            store_accumulator_row<ACT, OUT>(tmem_base + buf * (uint32_t)P.cols + lane_sel, P.cols, sub, nsub, oy < G.oh && ox < G.ow, img, (long)oy * G.ow + ox,
-                                            plane, sp, sp + P.cols, sp + 2 * P.cols, ep.act_param0, G.cpad, G.cout, out, no_side);
+            store_accumulator_row<ACT, OUT>(tmem_base + buf * (uint32_t)P.cols + lane_sel, nb * kBlock, sub, nsub, oy < G.oh && ox < G.ow, img,
+                                            (long)oy * G.ow + ox, plane, sp, sp + P.cols, sp + 2 * P.cols, ep.act_param0, G.cpad, G.cout, out, no_side, c_base);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_aempty + 8u * buf);
@@ -195,7 +207,7 @@ EncodeTiledFn encode_fn() {
 }
 
 template <int ACT, int OUT, bool MULTI>
-const char* launch_variant(cudaStream_t stream, int grid, const CUtensorMap& tmX, const CUtensorMap& tmW, const DwPlan& p, const DwGeom& g,
+const char* launch_variant(cudaStream_t stream, int grid, const DwMaps& tmX, const CUtensorMap& tmW, const DwPlan& p, const DwGeom& g,
                            const EpilogueParams& ep, void* out, uint32_t* status) {
     static std::mutex mu;  // several host threads may drive different GPUs through this function at once
     static bool attr_set[64] = {};
@@ -221,9 +233,14 @@ bool dw_umma_plan(int channels, int stride, int smem_budget, DwPlan* plan) {
     DwPlan p{};
     if (channels < 1 || (stride != 1 && stride != 2)) return false;
     p.stride = stride;
-    p.ncb = (channels + kBlock - 1) / kBlock;
+    p.ncb_total = (channels + kBlock - 1) / kBlock;
+    if (p.ncb_total > kUmmaMaxGatherBlocks) return false;
+    // Blocks per CTA: two accumulators of `cols` columns must fit the 512 TMEM columns (8 blocks), and two input stages plus the
+    // filters the shared memory (stride 2 needs 20 KB per block and stage: 4 blocks). Wider layers are dealt to CTA groups.
+    const int max_blocks = stride == 1 ? 8 : 4;
+    p.n_groups = (p.ncb_total + max_blocks - 1) / max_blocks;
+    p.ncb = (p.ncb_total + p.n_groups - 1) / p.n_groups;
     p.cols = p.ncb * kBlock;
-    if (p.cols > 256) return false;  // two accumulators of `cols` columns in the 512 TMEM columns
     p.acc_bufs = 2;
     const int cols = p.acc_bufs * p.cols;
     p.tmem_cols = cols <= 32 ? 32 : cols <= 64 ? 64 : cols <= 128 ? 128 : cols <= 256 ? 256 : 512;
@@ -266,7 +283,7 @@ bool dw_umma_plan(int channels, int stride, int smem_budget, DwPlan* plan) {
     return true;
 }
 
-size_t dw_umma_weight_bytes(const DwPlan& p) { return (size_t)p.ncb * 9 * 1024; }
+size_t dw_umma_weight_bytes(const DwPlan& p) { return (size_t)p.ncb_total * 9 * 1024; }
 
 void dw_umma_pack_weights(const DwPlan& p, const int8_t* w_dw, int channels, int8_t* dst) {
     const size_t total = dw_umma_weight_bytes(p);
@@ -280,7 +297,7 @@ void dw_umma_pack_weights(const DwPlan& p, const int8_t* w_dw, int channels, int
 const char* dw_umma_encode_weight_map(const DwPlan& p, const int8_t* w_dev, void* map_out) {
     EncodeTiledFn enc = encode_fn();
     if (!enc) return "cuTensorMapEncodeTiled entry point not available";
-    cuuint64_t dims[2] = {(cuuint64_t)kBlock, (cuuint64_t)p.ncb * 9 * kBlock};
+    cuuint64_t dims[2] = {(cuuint64_t)kBlock, (cuuint64_t)p.ncb_total * 9 * kBlock};
     cuuint64_t strides[1] = {(cuuint64_t)kBlock};
     cuuint32_t box[2] = {(cuuint32_t)kBlock, (cuuint32_t)kBlock};
     cuuint32_t estr[2] = {1, 1};
@@ -291,7 +308,8 @@ const char* dw_umma_encode_weight_map(const DwPlan& p, const int8_t* w_dev, void
 }
 
 const char* launch_dw_umma(cudaStream_t stream, int sm_count, const DwPlan& plan_in, const void* weight_map, const ConvShape& s, const int8_t* x,
-                           const EpilogueParams& ep, void* out, int out_dtype, uint32_t* status, unsigned long long wait_limit_ns) {
+                           const UmmaSources* sources, const EpilogueParams& ep, void* out, int out_dtype, uint32_t* status,
+                           unsigned long long wait_limit_ns) {
     EncodeTiledFn enc = encode_fn();
     if (!enc) return "cuTensorMapEncodeTiled entry point not available";
     if (s.n == 0) return nullptr;
@@ -301,23 +319,35 @@ const char* launch_dw_umma(cudaStream_t stream, int sm_count, const DwPlan& plan
     p.tiles_x = (s.ow + kTw - 1) / kTw;
     p.tiles_y = (s.oh + kTh - 1) / kTh;
     p.m_tiles = s.n * p.tiles_x * p.tiles_y;
-    CUtensorMap tmX;
-    cuuint64_t dims[4] = {(cuuint64_t)s.cin_pad, (cuuint64_t)s.w, (cuuint64_t)s.h, (cuuint64_t)s.n};
-    cuuint64_t strides[3] = {(cuuint64_t)s.cin_pad, (cuuint64_t)s.cin_pad * s.w, (cuuint64_t)s.cin_pad * s.w * s.h};
+    DwMaps km;
+    const int n_src = sources ? sources->n_src : 1;
+    if (n_src < 1 || n_src > kUmmaMaxSources) return "bad source count";
     // stride 2: the box spans 17 columns and the traversal takes every other one (9 land in shared memory)
     cuuint32_t box[4] = {(cuuint32_t)kBlock, (cuuint32_t)(p.stride == 1 ? p.set_w : 2 * p.set_w - 1), (cuuint32_t)p.tile_rows, 1};
     cuuint32_t estr[4] = {1, (cuuint32_t)p.stride, 1, 1};
-    if (enc(&tmX, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void*)x, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B,
-            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return "cuTensorMapEncodeTiled(activations) failed";
+    for (int i = 0; i < n_src; ++i) {
+        const cuuint64_t cp = (cuuint64_t)(sources ? sources->src_cpad[i] : s.cin_pad);
+        const void* base = sources ? (const void*)sources->src[i] : (const void*)x;
+        cuuint64_t dims[4] = {cp, (cuuint64_t)s.w, (cuuint64_t)s.h, (cuuint64_t)s.n};
+        cuuint64_t strides[3] = {cp, cp * s.w, cp * s.w * s.h};
+        if (enc(&km.tm[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return "cuTensorMapEncodeTiled(activations) failed";
+    }
+    for (int b = 0; b < p.ncb_total; ++b) {
+        km.block_x[b] = sources ? sources->block_x[b] : (uint16_t)(b * kBlock);
+        km.block_src[b] = sources ? sources->block_src[b] : (uint8_t)0;
+    }
     DwGeom g{s.n, s.h, s.w, s.oh, s.ow, s.cout, s.cout_pad};
-    int grid = sm_count * p.ctas_per_sm;
-    if (grid > p.m_tiles) grid = p.m_tiles;
+    int per_group = sm_count * p.ctas_per_sm / p.n_groups;  // CTAs walking over the pixel tiles, per channel group
+    if (per_group < 1) per_group = 1;
+    if (per_group > p.m_tiles) per_group = p.m_tiles;
+    const int grid = per_group * p.n_groups;
     const CUtensorMap& tmW = *reinterpret_cast<const CUtensorMap*>(weight_map);
     const char* err = nullptr;
 #define OTT_DW_LAUNCH(ACT, OUT)                                                                                  \
-    err = p.ctas_per_sm > 1 ? launch_variant<ACT, OUT, true>(stream, grid, tmX, tmW, p, g, ep, out, status)       \
-                            : launch_variant<ACT, OUT, false>(stream, grid, tmX, tmW, p, g, ep, out, status)
+    err = p.ctas_per_sm > 1 ? launch_variant<ACT, OUT, true>(stream, grid, km, tmW, p, g, ep, out, status)       \
+                            : launch_variant<ACT, OUT, false>(stream, grid, km, tmW, p, g, ep, out, status)
 #define OTT_DW_ACT(OUT)                                       \
     switch (ep.act_type) {                                    \
         case ACT_RELU: OTT_DW_LAUNCH(ACT_RELU, OUT); break;   \

@@ -53,14 +53,15 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t
 // activation -> fp32 NCHW planes, or float2int8(v * scale_out) as int8 NHWC (32-byte stores where the channel stride allows)
 // with chosen channels also stored as fp32 planes (mixed). taddr = accumulator address with this warp's lane window selected;
 // ncols = accumulator columns (a multiple of 32); warps sharing a lane quarter take every nsub-th 32-column chunk, starting
-// at chunk sub. s_si / s_bi / s_so: the layer's per-channel parameters in shared memory. inimg = oy * w + ox.
+// at chunk sub. s_si / s_bi / s_so: the per-channel parameters of these columns in shared memory. inimg = oy * w + ox.
+// c_base: the layer's channel that accumulator column 0 holds (a CTA may own a slice of the layer's channels).
 template <int ACT, int OUT>
 __device__ __forceinline__ void store_accumulator_row(uint32_t taddr, int ncols, int sub, int nsub, bool valid, int img, long inimg, long plane,
                                                       const float* __restrict__ s_si, const float* __restrict__ s_bi, const float* __restrict__ s_so,
-                                                      float p0, int cpad, int cout, void* __restrict__ out, const UmmaMixedOut& mixed) {
+                                                      float p0, int cpad, int cout, void* __restrict__ out, const UmmaMixedOut& mixed, int c_base = 0) {
     using namespace umma;
     const long pix = (long)img * plane + inimg;
-    int8_t* out_s8 = reinterpret_cast<int8_t*>(out) + pix * cpad;
+    int8_t* out_s8 = reinterpret_cast<int8_t*>(out) + pix * cpad + c_base;
     float* out_f32 = nullptr;
     if (OUT == DT_F32_NCHW) out_f32 = reinterpret_cast<float*>(out) + (long)img * cout * plane + inimg;
     else if (mixed.out_f32 != nullptr)
@@ -75,7 +76,7 @@ __device__ __forceinline__ void store_accumulator_row(uint32_t taddr, int ncols,
         tmem_wait_ld16(v[1]);
         if (!valid) continue;
         uint32_t wds[2][4];
-        const bool have[2] = {c0 < cpad, two && c0 + 16 < cpad};
+        const bool have[2] = {c_base + c0 < cpad, two && c_base + c0 + 16 < cpad};
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
             if (!have[half]) continue;
@@ -99,17 +100,18 @@ __device__ __forceinline__ void store_accumulator_row(uint32_t taddr, int ncols,
             if (OUT == DT_F32_NCHW) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j)
-                    if (cc + j < cout) out_f32[(long)(cc + j) * plane] = y[j];
+                    if (c_base + cc + j < cout) out_f32[(long)(c_base + cc + j) * plane] = y[j];
                 continue;
             }
             if (out_f32 != nullptr) {
                 // channels that some reader wants in fp32: the planes an fp32-output layer would have written
-                const uint32_t mk = (mixed.mask[(cc >> 5) & 31] >> (cc & 31)) & 0xFFFFu;
+                const int gc = c_base + cc;
+                const uint32_t mk = (mixed.mask[(gc >> 5) & 31] >> (gc & 31)) & 0xFFFFu;
                 if (mk != 0u) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
                         if ((mk >> j) & 1u) {
-                            const long pl = mixed.plane_of_col != nullptr ? (long)mixed.plane_of_col[cc + j] : (long)(cc + j);
+                            const long pl = mixed.plane_of_col != nullptr ? (long)mixed.plane_of_col[gc + j] : (long)(gc + j);
                             out_f32[pl * plane] = y[j];
                         }
                 }
