@@ -294,6 +294,14 @@ int ott_maxpool_f32_nchw(ott_ctx* ctx, const float* in, int n, int c, int h, int
 int ott_upsample_bilinear_f32_nchw(ott_ctx* ctx, const float* in, int n, int c, int h, int w, int oh, int ow, double scale_h,
                                    double scale_w, int packed_rule, float* out);
 
+/* UpsampleLayer::forward, nearest (Tensor/UpsampleLayer.cpp:113-131 -> otter::Interpolate): every output pixel is a copy of
+ * one source pixel. packed_rule = 1 picks it as the reference does on a packed blob (min((int)(d * (in / (float)out)),
+ * in - 1), Tensor/TensorInterpolation.cpp:660-676), 0 as on a plain blob (Tensor/UpSampleKernel.cpp:41-60: the index itself
+ * for equal sizes, d >> 1 for a doubled size, else min(floor(d * (float)(1 / scale)), in - 1)); the two differ only for
+ * scale factors that are not integers. scale_h / scale_w as for the bilinear call. */
+int ott_upsample_nearest_f32_nchw(ott_ctx* ctx, const float* in, int n, int c, int h, int w, int oh, int ow, double scale_h,
+                                  double scale_w, int packed_rule, float* out);
+
 /* ShortCutLayer: out = a + b (Tensor/ShortCutLayer.cpp) */
 int ott_add_f32(ott_ctx* ctx, const float* a, const float* b, float* out, size_t count);
 

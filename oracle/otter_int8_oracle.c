@@ -241,6 +241,37 @@ void orc_upsample_bilinear(const float* x, int n, int c, int h, int w, int oh, i
     }
 }
 
+/* Source index of the nearest resize along one axis. Packed blobs: ratio in/out in fp32, product truncated
+ * (Tensor/TensorInterpolation.cpp:660-676). Plain blobs: copy when the sizes agree, index >> 1 when the size doubles,
+ * else floor(d * (float)(1 / scale)) (Tensor/UpSampleKernel.cpp:41-60, Tensor/UpSample.hpp:30-51). */
+static int orc_nearest_index(int d, int in, int out, double user_scale, int packed_rule) {
+    int i;
+    if (packed_rule) {
+        const float ratio = (float)in / (float)out;
+        i = (int)((float)d * ratio);
+    } else {
+        if (out == in) return d;
+        if (out == 2 * in) return d >> 1;
+        const float ratio = user_scale > 0. ? (float)(1.0 / user_scale) : (float)in / (float)out;
+        i = (int)floorf((float)d * ratio);
+    }
+    return i < in - 1 ? i : in - 1;
+}
+
+void orc_upsample_nearest(const float* x, int n, int c, int h, int w, int oh, int ow, double scale_h, double scale_w,
+                          int packed_rule, float* y) {
+    const long planes = (long)n * c;
+#pragma omp parallel for schedule(static)
+    for (long p = 0; p < planes; ++p) {
+        const float* xp = x + p * (long)h * w;
+        float* yp = y + p * (long)oh * ow;
+        for (int oy = 0; oy < oh; ++oy) {
+            const int iy = orc_nearest_index(oy, h, oh, scale_h, packed_rule);
+            for (int ox = 0; ox < ow; ++ox) yp[(long)oy * ow + ox] = xp[(long)iy * w + orc_nearest_index(ox, w, ow, scale_w, packed_rule)];
+        }
+    }
+}
+
 /* ---- detection decode of the NanoDet-Plus head ---- */
 typedef struct { float x, y, w, h, prob; int label; int order; } orc_det;
 

@@ -84,6 +84,11 @@ int orc_conv_int8_forward(const orc_conv_desc* d, const int8_t* w_oihw, const fl
 void orc_upsample_bilinear(const float* x, int n, int c, int h, int w, int oh, int ow, double scale_h, double scale_w,
                            int packed_rule, float* y);
 
+/* UpsampleLayer::forward for upsample_mode = nearest (Tensor/UpsampleLayer.cpp:113-131 -> otter::Interpolate): a copy of
+ * the source pixel whose index the reference's two rules give (packed_rule as above). */
+void orc_upsample_nearest(const float* x, int n, int c, int h, int w, int oh, int ow, double scale_h, double scale_w,
+                          int packed_rule, float* y);
+
 /* NanodetPlusDetectionOutputLayer::forward for one image (Tensor/NanodetPlusDetectionOutputLayer.cpp:65-260): per pyramid
  * level and grid cell the best of num_class logits, its sigmoid against prob_threshold, a softmax over the reg_bins
  * distance bins of each box side, the box; then all proposals sorted by score, greedy NMS. heads[l] is fp32

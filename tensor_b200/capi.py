@@ -83,6 +83,7 @@ SIGNATURES = {
     "ott_copy_channels_f32": (i32, [vp, vp, i32, i32, i32, vp, i32, i32, i32, i32, i32, i32]),
     "ott_maxpool_f32_nchw": (i32, [vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp]),
     "ott_upsample_bilinear_f32_nchw": (i32, [vp, vp, i32, i32, i32, i32, i32, i32, C.c_double, C.c_double, i32, vp]),
+    "ott_upsample_nearest_f32_nchw": (i32, [vp, vp, i32, i32, i32, i32, i32, i32, C.c_double, C.c_double, i32, vp]),
     "ott_add_f32": (i32, [vp, vp, vp, vp, sz]),
     "ott_graph_capture_begin": (i32, [vp]),
     "ott_graph_capture_end": (i32, [vp, C.POINTER(vp)]),

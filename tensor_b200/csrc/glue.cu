@@ -148,6 +148,52 @@ upsample_bilinear_kernel(const float* __restrict__ x, float* __restrict__ y, int
     }
 }
 
+// Source index of the nearest resize along one axis: rule 1 is the reference's packed resize (ratio in / out in fp32, product
+// truncated: Tensor/TensorInterpolation.cpp:660-676), rule 0 its plain resize (copy for equal sizes, index >> 1 for a doubled
+// size, else floor(d * (float)(1 / scale)): Tensor/UpSampleKernel.cpp:41-60, Tensor/UpSample.hpp:30-51).
+__device__ __forceinline__ int nearest_index(int d, int in, int out, double user_scale, int rule) {
+    int i;
+    if (rule == 1) {
+        i = (int)__fmul_rn((float)d, __fdiv_rn((float)in, (float)out));
+    } else {
+        if (out == in) return d;
+        if (out == 2 * in) return d >> 1;
+        const float ratio = user_scale > 0. ? (float)(1.0 / user_scale) : __fdiv_rn((float)in, (float)out);
+        i = (int)floorf(__fmul_rn((float)d, ratio));
+    }
+    return i < in - 1 ? i : in - 1;
+}
+
+// Nearest resize of fp32 NCHW planes: the same thread layout as the bilinear kernel (one output position of kUpsamplePlanes
+// consecutive planes per thread; the source indices are computed once per block row and column).
+__global__ void __launch_bounds__(256)
+upsample_nearest_kernel(const float* __restrict__ x, float* __restrict__ y, int h, int w, int oh, int ow, double scale_h, double scale_w,
+                        int rule, long planes) {
+    __shared__ int src_x[32], src_y[8];
+    ottk::pdl_launch_dependents();
+    const int tid = threadIdx.y * 32 + threadIdx.x;
+    if (tid < 32) {
+        const int ox = blockIdx.x * 32 + tid;
+        if (ox < ow) src_x[tid] = nearest_index(ox, w, ow, scale_w, rule);
+    } else if (tid < 40) {
+        const int oy = blockIdx.y * 8 + (tid - 32);
+        if (oy < oh) src_y[tid - 32] = nearest_index(oy, h, oh, scale_h, rule);
+    }
+    __syncthreads();
+    ottk::pdl_wait();
+    const int ox = blockIdx.x * 32 + threadIdx.x;
+    const int oy = blockIdx.y * 8 + threadIdx.y;
+    if (ox >= ow || oy >= oh) return;
+    const int src = src_y[threadIdx.y] * w + src_x[threadIdx.x];
+    const long p0 = (long)blockIdx.z * kUpsamplePlanes;
+    const long p1 = p0 + kUpsamplePlanes < planes ? p0 + kUpsamplePlanes : planes;
+    const long in_plane = (long)h * w, out_plane = (long)oh * ow;
+    const float* xp = x + p0 * in_plane + src;
+    float* yp = y + p0 * out_plane + (long)oy * ow + ox;
+#pragma unroll 4
+    for (long p = p0; p < p1; ++p, xp += in_plane, yp += out_plane) *yp = __ldg(xp);
+}
+
 unsigned grid_for(const ott_ctx* ctx, long total, int block) {
     long g = (total + block - 1) / block;
     const long cap = (long)ctx->sm_count * 16;
@@ -206,6 +252,21 @@ int ott_upsample_bilinear_f32_nchw(ott_ctx* ctx, const float* in, int n, int c, 
     cudaSetDevice(ctx->device);
     const dim3 block(32, 8), grid((unsigned)((ow + 31) / 32), (unsigned)((oh + 7) / 8), (unsigned)zblocks);
     OTT_CUDA_CHECK(ctx, ottk::launch_overlapped(upsample_bilinear_kernel, grid, block, 0, ctx->stream, in, out, h, w, oh, ow, scale_h, scale_w,
+                                                packed_rule ? 1 : 0, planes));
+    ctx->launches += 1;
+    return OTT_OK;
+}
+
+int ott_upsample_nearest_f32_nchw(ott_ctx* ctx, const float* in, int n, int c, int h, int w, int oh, int ow, double scale_h, double scale_w,
+                                  int packed_rule, float* out) {
+    if (!ctx || !in || !out || n < 0 || c < 0 || h < 1 || w < 1 || oh < 1 || ow < 1) return OTT_ERR_INVALID;
+    const long planes = (long)n * c;
+    if (planes == 0) return OTT_OK;
+    const long zblocks = (planes + kUpsamplePlanes - 1) / kUpsamplePlanes;
+    if (zblocks > 65535 || (oh + 7) / 8 > 65535) return ctx->fail(OTT_ERR_UNSUPPORTED, "Upsample: more than 2097120 planes or 524280 rows in one call");
+    cudaSetDevice(ctx->device);
+    const dim3 block(32, 8), grid((unsigned)((ow + 31) / 32), (unsigned)((oh + 7) / 8), (unsigned)zblocks);
+    OTT_CUDA_CHECK(ctx, ottk::launch_overlapped(upsample_nearest_kernel, grid, block, 0, ctx->stream, in, out, h, w, oh, ow, scale_h, scale_w,
                                                 packed_rule ? 1 : 0, planes));
     ctx->launches += 1;
     return OTT_OK;

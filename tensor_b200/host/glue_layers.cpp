@@ -239,15 +239,18 @@ public:
 };
 
 // Tensor/UpsampleLayer.cpp:26-131, the one-input form. Option keys upsample_mode, output_height/width, scale_height/width,
-// stride (wins over the scales when non-zero, :80-83) and align_corner. Built: bilinear with align_corner = false, which is
-// what the detector graphs use; nearest, bicubic and align_corner = true return -1.
+// stride (wins over the scales when non-zero, :80-83) and align_corner. Built: nearest and bilinear, both as the reference's
+// default options run them (NetOption::use_non_lib_optimize = true -> otter::Interpolate, which never sees align_corner, so
+// the flag changes nothing there and is ignored here too). Bicubic is refused by the reference's own parse_param (:50).
 class UpsampleLayer : public Layer {
 public:
     UpsampleLayer() { one_blob_only = true; support_inplace = false; support_packing = true; }
     int parse_param(LayerOption& option, ParamDict& pd) override {
         pd.clear();
         const std::string m = opt_find_string(option, "upsample_mode", "nearest");
-        pd.set(0, m == "nearest" ? 1 : m == "bilinear" ? 2 : m == "bicubic" ? 3 : -1);
+        const int mode_id = m == "nearest" ? 1 : m == "bilinear" ? 2 : m == "bicubic" ? 3 : -1;
+        if (mode_id > 2) return -1;  // "Unsupport upsample type" in the reference
+        pd.set(0, mode_id);
         pd.set(1, opt_find_int(option, "output_height", 0));
         pd.set(2, opt_find_int(option, "output_width", 0));
         pd.set(3, opt_find_float(option, "scale_height", 1.f));
@@ -276,7 +279,7 @@ public:
     }
     int forward(const Tensor& bottom, Tensor& top, const NetOption& opt) const override {
         if (!is_dev_f32(bottom)) return -1;
-        if (mode != 2 || align_corner) return -1;
+        if (mode != 1 && mode != 2) return -1;
         const int n = (int)bottom.size(0), c = (int)bottom.size(1), h = (int)bottom.size(2), w = (int)bottom.size(3);
         const int oh = (int)(h * scale_height), ow = (int)(w * scale_width);
         if (oh < 1 || ow < 1) return -1;
@@ -285,6 +288,9 @@ public:
         // The reference's Net hands this layer a packed blob when the channel count is a multiple of 4 (Tensor/Net.cpp:380-411),
         // and its resize of packed blobs rounds differently from its resize of plain ones (see ott_upsample_bilinear_f32_nchw).
         const bool packed = opt.use_packing_layout && c % 4 == 0;
+        if (mode == 1)
+            return ott_upsample_nearest_f32_nchw(opt.gpu, bottom.data_ptr<float>(), n, c, h, w, oh, ow, scale_height, scale_width, packed ? 1 : 0,
+                                                 top.data_ptr<float>());
         return ott_upsample_bilinear_f32_nchw(opt.gpu, bottom.data_ptr<float>(), n, c, h, w, oh, ow, scale_height, scale_width, packed ? 1 : 0,
                                               top.data_ptr<float>());
     }

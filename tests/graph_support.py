@@ -28,18 +28,19 @@ def oracle_conv(params, rounding=0):
     return fn
 
 
-def oracle_upsample(a, oh, ow, scale, packed_rule):
-    """The C checker's bilinear Upsample (exact fused multiply-adds), for walk(upsample_fn=...)."""
+def oracle_upsample(a, oh, ow, scale, packed_rule, mode="bilinear"):
+    """The C checker's Upsample (bilinear with exact fused multiply-adds, or nearest), for walk(upsample_fn=...)."""
     import ctypes as C
     from support import _p, load_port
     lib = load_port()
-    lib.orc_upsample_bilinear.restype = None
-    lib.orc_upsample_bilinear.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_double, C.c_double, C.c_int,
-                                          C.c_void_p]
+    fn = getattr(lib, "orc_upsample_" + mode)
+    fn.restype = None
+    fn.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_double, C.c_double, C.c_int, C.c_void_p]
     a = np.ascontiguousarray(a, dtype=np.float32)
     n, c, h, w = a.shape
     y = np.empty((n, c, oh, ow), np.float32)
-    lib.orc_upsample_bilinear(a.ctypes.data, n, c, h, w, oh, ow, float(scale), float(scale), int(packed_rule), y.ctypes.data)
+    sh, sw = scale if isinstance(scale, tuple) else (scale, scale)
+    fn(a.ctypes.data, n, c, h, w, oh, ow, float(sh), float(sw), int(packed_rule), y.ctypes.data)
     return y
 
 

@@ -186,6 +186,31 @@ def test_whole_graph_equals_the_reference_s_own_net(tmp_path):
     net.close()
 
 
+@pytest.mark.parametrize("c,h,w,n,opts,sh,sw", [(8, 7, 9, 2, dict(stride="2.000000"), 2.0, 2.0), (5, 7, 9, 2, dict(stride="2.000000"), 2.0, 2.0),
+                                                (4, 5, 3, 1, dict(stride="3.000000"), 3.0, 3.0), (8, 6, 10, 3, dict(stride="1.500000"), 1.5, 1.5),
+                                                (6, 6, 10, 2, dict(stride="1.500000"), 1.5, 1.5),
+                                                (12, 7, 11, 2, dict(stride="0", scale_height="2.500000", scale_width="1.300000"), 2.5, 1.3),
+                                                (7, 7, 11, 1, dict(stride="0", scale_height="2.500000", scale_width="1.300000"), 2.5, 1.3),
+                                                (16, 9, 13, 2, dict(stride="1.700000"), 1.7, 1.7), (2, 9, 13, 2, dict(stride="1.700000"), 1.7, 1.7),
+                                                (96, 40, 40, 2, dict(stride="2.000000"), 2.0, 2.0)])
+def test_nearest_upsample_layer_both_index_rules(c, h, w, n, opts, sh, sw):
+    """Nearest Upsample through the Net: the source pixel follows the reference's packed rule for channel counts that are
+    multiples of 4 and its plain rule otherwise (they part for fractional scale factors)."""
+    from graph_support import oracle_upsample
+    from tensor_b200 import Net
+    x = np.random.default_rng(c * 1000 + h * 10 + w).normal(size=(n, c, h, w)).astype(np.float32)
+    net = Net(0)
+    net.add_layer(type="Input", name="data", output="data", channel=c, height=h, width=w)
+    net.add_layer(type="Upsample", name="up", input="data", output="up", upsample_mode="nearest", **opts)
+    net.compile()
+    oh, ow = int(h * np.float32(sh)), int(w * np.float32(sw))
+    assert net.blob_shape("up")[1:] == (c, oh, ow)
+    got = net.forward("data", x, ["up"])[0]
+    want = oracle_upsample(x, oh, ow, (float(np.float32(sh)), float(np.float32(sw))), 1 if c % 4 == 0 else 0, mode="nearest")
+    assert np.array_equal(bits(got), bits(want))
+    net.close()
+
+
 @pytest.mark.parametrize("c,h,w,n", [(8, 7, 9, 2), (16, 2, 2, 1), (12, 20, 20, 3), (5, 7, 9, 2), (6, 2, 3, 1), (58, 10, 10, 2), (3, 1, 4, 1), (96, 40, 40, 2)])
 def test_upsample_layer_both_rounding_rules(c, h, w, n):
     """Bilinear x2 Upsample through the Net: channel counts the reference would pack (multiples of 4) and ones it would not

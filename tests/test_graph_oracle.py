@@ -63,6 +63,38 @@ def test_checker_upsample_equals_reference_layer(c, h, w):
         assert not np.array_equal(oracle_upsample(x, 2 * h, 2 * w, 2.0, 0), want) or h * w <= 4
 
 
+NEAREST_CASES = [(8, 7, 9, "stride=2.000000", 2.0, 2.0), (5, 7, 9, "stride=2.000000", 2.0, 2.0), (4, 5, 3, "stride=3.000000", 3.0, 3.0),
+                 (3, 5, 3, "stride=3.000000", 3.0, 3.0), (8, 6, 10, "stride=1.500000", 1.5, 1.5), (6, 6, 10, "stride=1.500000", 1.5, 1.5),
+                 (12, 7, 11, "stride=0;scale_height=2.500000;scale_width=1.300000", 2.5, 1.3),
+                 (7, 7, 11, "stride=0;scale_height=2.500000;scale_width=1.300000", 2.5, 1.3),
+                 (16, 9, 13, "stride=1.700000", 1.7, 1.7), (2, 9, 13, "stride=1.700000", 1.7, 1.7), (4, 3, 5, "stride=1.000000", 1.0, 1.0)]
+
+
+@pytest.mark.skipif(not have_ref(), reason="oracle/_ref/libotter_ref.so not built")
+@pytest.mark.parametrize("c,h,w,opts,sh,sw", NEAREST_CASES)
+def test_checker_nearest_upsample_equals_reference_layer(c, h, w, opts, sh, sw):
+    """Nearest Upsample: the reference picks the source pixel by two different rules (packed / plain blob); fractional scale
+    factors are where they part."""
+    from graph_support import oracle_upsample
+    x = np.random.default_rng(c * 1000 + h * 10 + w).normal(size=(1, c, h, w)).astype(np.float32)
+    want = ref_layer("Upsample", "upsample_mode=nearest;" + opts, [x])
+    oh, ow = int(h * np.float32(sh)), int(w * np.float32(sw))
+    assert want.shape == (1, c, oh, ow)
+    got = oracle_upsample(x, oh, ow, (float(np.float32(sh)), float(np.float32(sw))), 1 if c % 4 == 0 else 0, mode="nearest")
+    assert np.array_equal(got.view(np.int32), want.view(np.int32))
+
+
+@pytest.mark.skipif(not have_ref(), reason="oracle/_ref/libotter_ref.so not built")
+def test_reference_upsample_ignores_align_corner_under_default_options():
+    """With NetOption's defaults the reference's layer resizes through otter::Interpolate without handing align_corner on
+    (Tensor/UpsampleLayer.cpp:120-121), so the flag changes nothing; the GPU layer relies on that."""
+    x = np.random.default_rng(3).normal(size=(1, 8, 6, 5)).astype(np.float32)
+    for c in (8, 5):
+        a = ref_layer("Upsample", "upsample_mode=bilinear;align_corner=false;stride=2.000000", [x[:, :c]])
+        b = ref_layer("Upsample", "upsample_mode=bilinear;align_corner=true;stride=2.000000", [x[:, :c]])
+        assert np.array_equal(a.view(np.int32), b.view(np.int32))
+
+
 def test_nanodet_plus_description():
     L = graphs.nanodet_plus_layers(320, 320)
     geo = graphs.conv_geometry(L)
