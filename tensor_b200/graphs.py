@@ -123,6 +123,17 @@ def nanodet_plus_layers(height=320, width=320, batch=1, neck=96, classes=80, reg
 NANODET_OUTPUTS = ("head8", "head16", "head32", "head64")
 
 
+def shipped_nanodet_plus_layers(batch=1, mixed=False, detect=True):
+    """The detector the reference ships as benchmark/nanodet-plus-m-1.5x_416_int8_fused.otter (mixed=True:
+    ..._int8_mixed.otter, whose first convolution stays fp32, int8_scale_term 0): ShuffleNetV2-1.5x widths, 128 neck channels,
+    416x416 input. Same layers in the same order with the same parameters and wiring as those files; only names differ."""
+    L = nanodet_plus_layers(416, 416, batch=batch, neck=128, stage_channels=(176, 352, 704), detect=detect)
+    if mixed:
+        conv1 = next(l for l in L if l["type"] == "Convolution")
+        conv1["int8_scale_term"] = 0
+    return L
+
+
 def to_otter_text(layers, name="generated by tensor_b200.graphs") -> str:
     """The layer list as a `.otter` text graph, in the layout of the reference's own files: structural keys first,
     the layer's parameters in a nested Param block."""

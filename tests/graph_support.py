@@ -111,6 +111,17 @@ def wide_nanodet_case():
     return L, params, x, ["up32", "td16", "td8", "bu16", "bu32", "p64"] + list(graphs.NANODET_OUTPUTS)
 
 
+def shipped_nanodet_case():
+    """The detector the reference ships (benchmark/nanodet-plus-m-1.5x_416_int8_fused.otter: 1.5x widths, 128 neck channels,
+    416x416; graphs.shipped_nanodet_plus_layers is that file layer for layer) with seeded parameters, one image. Every width
+    is a multiple of 8, so the reference's packed Net runs it whole."""
+    L = graphs.shipped_nanodet_plus_layers(detect=False)
+    params = graphs.make_params(L, seed=0x0771E5 + 416)
+    x = np.random.default_rng(416).uniform(0, 1, size=(1, 3, 416, 416)).astype(np.float32)
+    calibrate(L, params, x, oracle_conv_for_calibration, upsample_fn=oracle_upsample)
+    return L, params, x, list(graphs.NANODET_OUTPUTS)
+
+
 def write_ncnn_bin(layers, params, path):
     """The parameters as an ncnn model file, the way a quantized ncnn model stores them and ConvolutionLayer::load_model reads
     them back (Tensor/ConvolutionLayer.cpp:245-296): per Convolution, in graph order, the int8 weights behind the tag
@@ -164,3 +175,15 @@ def reference_net_forward(layers, params, x, blobs, packed=1, weight_file=None):
         ref.ref_net_close()
         import os
         os.unlink(path)
+
+
+def assert_equals_shipped_golden(heads, gold):
+    """heads: {name: fp32 array} of graph_support.shipped_nanodet_case; gold: tests/golden/net_nanodet_shipped_416.npz (the
+    reference's own Net on that case). Bit for bit: full arrays where the fixture keeps them, SHA-256 of the bytes for all."""
+    import hashlib
+    for name in graphs.NANODET_OUTPUTS:
+        a = np.ascontiguousarray(heads[name])
+        assert tuple(a.shape) == tuple(gold[name + "_shape"]), name
+        if name in gold.files:
+            assert np.array_equal(a.view(np.int32), gold[name].view(np.int32)), f"head {name} differs from the reference's Net"
+        assert hashlib.sha256(a.tobytes()).hexdigest() == gold[name + "_sha256"].tobytes().decode(), f"head {name}: digest differs"

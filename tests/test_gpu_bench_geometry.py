@@ -93,3 +93,63 @@ def test_detector_at_320x320(routing):
         assert g.shape == want[name].shape, name
         assert np.array_equal(bits(g), bits(want[name])), f"blob {name} differs"
     net.close()
+
+
+@pytest.mark.parametrize("routing", [1, 0], ids=["routed", "unrouted"])
+def test_shipped_detector_equals_the_reference_s_own_net(routing, tmp_path):
+    """The detector the reference ships (benchmark/nanodet-plus-m-1.5x_416_int8_fused.otter: 1.5x widths, 416x416; the
+    generated description equals that file layer for layer, tests/test_otter_format.py), read from a .otter file, seeded
+    parameters: the four heads against what the reference's own Net computed for the same inputs (frozen fixture), bit for bit."""
+    from graph_support import assert_equals_shipped_golden, shipped_nanodet_case
+    from support import GOLDEN_DIR
+    from tensor_b200 import Net
+    gold = np.load(GOLDEN_DIR / "net_nanodet_shipped_416.npz")
+    L, params, x, heads = shipped_nanodet_case()
+    path = tmp_path / "shipped.otter"
+    path.write_text(graphs.to_otter_text(L))
+    net = Net(0)
+    net.set_option("int8_routing", routing)
+    net.load_otter(path)
+    for name, p in params.items():
+        net.set_conv_params(name, p["weight"], p["bias"], p["w_scales"], p["in_scales"], p["out_scales"])
+    got = dict(zip(heads, net.forward("data", x, heads)))
+    assert_equals_shipped_golden(got, gold)
+    # the same through a batch of three copies: every image of a batch equals the single-image answer
+    xb = np.ascontiguousarray(np.repeat(x, 3, axis=0))
+    for name, g in zip(heads, net.forward("data", xb, heads)):
+        for i in range(3):
+            assert np.array_equal(bits(g[i]), bits(got[name][0])), f"head {name}, image {i}"
+    net.close()
+
+
+def test_shipped_mixed_detector_fp32_first_layer():
+    """The "mixed" flavour of the shipped detector (..._int8_mixed.otter: conv_1 keeps fp32, int8_scale_term 0): the fp32 blob
+    is within the fp32 layer's tolerance of float64 arithmetic, and all four heads equal the CPU checker fed with that blob."""
+    from graph_support import build_net, oracle_conv, oracle_conv_for_calibration, oracle_upsample
+    from test_f32_layer import TOL_ULP, activation, conv_f64
+    L = graphs.shipped_nanodet_plus_layers(mixed=True, detect=False)
+    conv1_name = next(l["name"] for l in L if l["type"] == "Convolution")
+    rng = np.random.default_rng(4160)
+    x = rng.uniform(0, 1, size=(1, 3, 416, 416)).astype(np.float32)
+    w1 = rng.normal(0, 0.2, size=(24, 3, 3, 3)).astype(np.float32)
+    b1 = rng.normal(0, 0.1, size=(24,)).astype(np.float32)
+    exact, mag = conv_f64(x, w1, b1, 2, 1, 1, 1)
+    conv1_f64 = activation(exact, 2, 0.1)
+    params = graphs.make_params(L, seed=4161)
+    int8_params = {k: v for k, v in params.items() if k != conv1_name}
+
+    def first_layer_then(fn, conv1_blob):
+        return lambda name, g, *a: conv1_blob(*a) if name == conv1_name else fn(name, g, *a)
+
+    calibrate(L, params, x, first_layer_then(oracle_conv_for_calibration, lambda p, a, as_float: conv1_f64.astype(np.float32)),
+              upsample_fn=oracle_upsample)
+    net = build_net(L, int8_params)
+    net.set_conv_params_f32(conv1_name, w1, b1)
+    conv1 = net.forward("data", x, [conv1_name])[0]
+    err = np.abs(conv1.astype(np.float64) - conv1_f64) / (mag * 2.0 ** -23 + 1e-30)
+    assert err.max() <= TOL_ULP
+    heads = list(graphs.NANODET_OUTPUTS)
+    want = walk(L, x, first_layer_then(oracle_conv(params), lambda a: conv1), want=heads, upsample_fn=oracle_upsample)
+    for name, g in zip(heads, net.forward("data", x, heads)):
+        assert np.array_equal(bits(g), bits(want[name])), f"head {name} differs"
+    net.close()

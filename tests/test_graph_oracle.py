@@ -226,3 +226,21 @@ def test_detections_of_the_frozen_reference_heads():
     got = oracle_detect(heads, [8, 16, 32, 64])
     assert got.shape[0] >= 1
     assert_same_detections(got, DET_GOLD["detections"])
+
+
+def test_shipped_detector_walk_equals_frozen_reference_net():
+    """The detector the reference ships (1.5x widths, 416x416, 190 layers), seeded parameters: the layer-by-layer checker
+    against the heads frozen from the reference's own Net at that full geometry."""
+    from graph_support import assert_equals_shipped_golden, oracle_conv, oracle_upsample, shipped_nanodet_case
+    gold = np.load(__import__("support").GOLDEN_DIR / "net_nanodet_shipped_416.npz")
+    L, params, x, heads = shipped_nanodet_case()
+    got = walk(L, x, oracle_conv(params), want=heads, upsample_fn=oracle_upsample)
+    assert_equals_shipped_golden(got, gold)
+
+
+@pytest.mark.skipif(not have_ref(), reason="oracle/_ref/libotter_ref.so not built")
+def test_shipped_detector_reference_net_live_equals_fixture():
+    from graph_support import assert_equals_shipped_golden, reference_net_forward, shipped_nanodet_case
+    gold = np.load(__import__("support").GOLDEN_DIR / "net_nanodet_shipped_416.npz")
+    L, params, x, heads = shipped_nanodet_case()
+    assert_equals_shipped_golden(reference_net_forward(L, params, x, heads), gold)

@@ -52,3 +52,29 @@ def test_reads_the_reference_s_own_int8_graph():
     assert conv4["int8_scale_term"] == "102" and conv4["activation"] == "LRelu" and conv4["input"] == "pool_1"
     cat = next(l for l in got if l.get("name") == "concat_1")
     assert cat["input"] == "conv_3, conv_6"
+
+
+def _canonical(layers):
+    """Layers with blob names replaced by the index of the layer that produced them, so that two files which differ only in
+    names compare equal."""
+    ids, out = {}, []
+    for l in layers:
+        ins = [t.strip() for t in l.get("input", "").split(",") if t.strip()]
+        sig = {k: (f"{float(v):.6f}" if k.endswith("_threshold") else v) for k, v in l.items() if k not in ("name", "input", "output", "batchsize")}
+        sig["in"] = tuple(ids[i] for i in ins)
+        ids[l.get("output", l.get("name"))] = len(ids)
+        out.append(sig)
+    return out
+
+
+@pytest.mark.skipif(not REF_GRAPH.exists(), reason="reference checkout not present")
+@pytest.mark.parametrize("flavour", ["fused", "mixed"])
+def test_generator_reproduces_the_reference_s_shipped_detector(flavour):
+    """graphs.shipped_nanodet_plus_layers is layer for layer (types, parameters, wiring; 190 layers) the graph the reference
+    ships as benchmark/nanodet-plus-m-1.5x_416_int8_{fused,mixed}.otter, so the GPU parity test of that description
+    (tests/test_gpu_bench_geometry.py) runs the reference's own model structure."""
+    ref = parse_otter_text(REF_GRAPH.with_name(f"nanodet-plus-m-1.5x_416_int8_{flavour}.otter").read_text())
+    gen = parse_otter_text(graphs.to_otter_text(graphs.shipped_nanodet_plus_layers(mixed=flavour == "mixed")))
+    assert len(ref) == len(gen) == 190
+    for i, (a, b) in enumerate(zip(_canonical(ref), _canonical(gen))):
+        assert a == b, f"layer {i} ({ref[i].get('name')}) differs"
