@@ -242,6 +242,21 @@ int ott_unit_int8_create(ott_ctx* ctx, const ott_conv* pw1, const ott_conv* dw, 
 int ott_unit_int8_forward_io(ott_ctx* ctx, const ott_unit* unit, const ott_conv_io* io, int n, int h, int w, uint32_t* status_word_dev);
 int ott_unit_int8_destroy(ott_ctx* ctx, ott_unit* unit);
 
+/* A depthwise 3x3 layer (pad 1, stride 1 or 2) and the 1x1 layer that reads its output, as one launch: two consecutive
+ * ConvolutionLayer::forward_int8 calls (Tensor/ConvolutionLayer.cpp:754-847) whose intermediate int8 blob stays in shared
+ * memory; unlike the whole unit above, nothing is computed twice (the depthwise layer's halo is input that already exists).
+ * Built from two existing layer objects (both must outlive the pair): dw requantizing (int8_scale_term > 100), without
+ * activation, plain or created with gathered input in 32-channel groups; pw plain, or created with gathered input whose one
+ * source is dw's output tensor; both with a bias and the add-half-truncate rounding rule; at most 256 stored depthwise
+ * channels and 256 output channels. OTT_ERR_UNSUPPORTED otherwise (run the two layers one by one). Same bits as the two layers.
+ * ott_dwpw_int8_forward_io takes the depthwise layer's input (io->sources for a gathered layer, else io->in_dev as int8 NHWC;
+ * h, w = its input size) and delivers the 1x1 layer's output (out_dev / out_dtype / out_f32_dev / f32_channel_mask as for
+ * ott_conv_int8_forward_io). */
+typedef struct ott_dwpw ott_dwpw;
+int ott_dwpw_int8_create(ott_ctx* ctx, const ott_conv* dw, const ott_conv* pw, ott_dwpw** out);
+int ott_dwpw_int8_forward_io(ott_ctx* ctx, const ott_dwpw* pair, const ott_conv_io* io, int n, int h, int w, uint32_t* status_word_dev);
+int ott_dwpw_int8_destroy(ott_ctx* ctx, ott_dwpw* pair);
+
 /* Dense fp32 NCHW copy [n][channels][hw] of planes described the same way (for consumers that need one tensor). */
 int ott_gather_channels_f32(ott_ctx* ctx, const float* const* buffers, const int64_t* image_strides, int n_buffers,
                             const uint32_t* plane_refs, int channels, int n, int hw, float* dst_dev);

@@ -29,7 +29,9 @@ ott_ctx* ott_net_context(ott_net* net); /* valid after ott_net_compile */
  * whose fp32 result is read only by another quantized convolution writes that layer's int8 input directly) and
  * "int8_routing" (the same through Concat / Crop / ChannelShuffle / Split: a producer stores each output channel already
  * quantized for the one 1x1 convolution that reads it, which then gathers its input from its producers' int8 tensors). All
- * three leave every extracted blob bit-identical. "host_chunk" (default 64): images per chunk when ott_net_forward pipelines a host
+ * three leave every extracted blob bit-identical. "fuse_depthwise_pointwise" (default 0): a depthwise 3x3 layer whose int8
+ * output only the 1x1 layer behind it reads runs inside that layer's kernel (ott_dwpw_*; same bits; fewer launches, which pays
+ * for small batches). "host_chunk" (default 64): images per chunk when ott_net_forward pipelines a host
  * batch (upload, kernels and download of different chunks overlap). Unknown key: OTT_ERR_INVALID. */
 int ott_net_set_option(ott_net* net, const char* key, int value);
 

@@ -7,4 +7,4 @@ and has no CPU path: if the library is missing or no GPU is present, calls fail.
 """
 from .capi import (ACT_LRELU, ACT_NONE, ACT_RELU, ACT_RELU6, F32_NCHW, KERNEL_DENSE_DIRECT, KERNEL_DENSE_UMMA,  # noqa: F401
                    KERNEL_DEPTHWISE, ROUND_ADD_HALF_TRUNC, ROUND_HALF_AWAY, S8_NHWC, S32_NHWC, ConvF32, ConvInt8, Context,
-                   Net, NetGroup, OtterB200Error, UnitInt8, library, library_path, nhwc_channels, partition)
+                   DwPwInt8, Net, NetGroup, OtterB200Error, UnitInt8, library, library_path, nhwc_channels, partition)

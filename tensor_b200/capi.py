@@ -70,6 +70,9 @@ SIGNATURES = {
     "ott_unit_int8_create": (i32, [vp, vp, vp, vp, C.POINTER(vp)]),
     "ott_unit_int8_forward_io": (i32, [vp, vp, vp, i32, i32, i32, vp]),
     "ott_unit_int8_destroy": (i32, [vp, vp]),
+    "ott_dwpw_int8_create": (i32, [vp, vp, vp, C.POINTER(vp)]),
+    "ott_dwpw_int8_forward_io": (i32, [vp, vp, vp, i32, i32, i32, vp]),
+    "ott_dwpw_int8_destroy": (i32, [vp, vp]),
     "ott_gather_channels_f32": (i32, [vp, vp, vp, i32, vp, i32, i32, i32, vp]),
     "ott_add_gather_f32": (i32, [vp, vp, vp, i32, vp, vp, vp, i32, vp, i32, i32, i32, vp]),
     "ott_conv_int8_forward_maxpool": (i32, [vp, vp, vp, i32, i32, i32, i32, vp]),
@@ -349,6 +352,38 @@ class ConvInt8:
             self.h = None
 
 
+class DwPwInt8:
+    """A depthwise 3x3 layer and the 1x1 layer behind it as one launch (ott_dwpw). Both layers must outlive the pair."""
+
+    def __init__(self, ctx: Context, dw: "ConvInt8", pw: "ConvInt8"):
+        self.ctx, self.cout = ctx, pw.desc.cout
+        h = C.c_void_p()
+        ctx.check(ctx.lib.ott_dwpw_int8_create(ctx.h, dw.h, pw.h, C.byref(h)))
+        self.h = h
+
+    def forward_io(self, n, h, w, out_dev: int, out_dtype: int, *, in_dev: int = 0, sources=None, out_f32_dev: int = 0, f32_channels=None):
+        io = OttConvIO()
+        io.in_dev, io.in_dtype = (in_dev or None), S8_NHWC
+        keep = []
+        if sources is not None:
+            arr = (C.c_void_p * len(sources))(*[C.c_void_p(p) for p in sources])
+            keep.append(arr)
+            io.sources, io.n_sources = C.cast(arr, C.POINTER(C.c_void_p)), len(sources)
+        io.out_dev, io.out_dtype = out_dev, out_dtype
+        if out_f32_dev:
+            mask = np.zeros((self.cout + 31) // 32, np.uint32)
+            for c in f32_channels:
+                mask[c >> 5] |= np.uint32(1 << (c & 31))
+            keep.append(mask)
+            io.out_f32_dev, io.f32_channel_mask = out_f32_dev, mask.ctypes.data
+        self.ctx.check(self.ctx.lib.ott_dwpw_int8_forward_io(self.ctx.h, self.h, C.byref(io), n, h, w, None))
+
+    def close(self):
+        if self.h:
+            self.ctx.lib.ott_dwpw_int8_destroy(self.ctx.h, self.h)
+            self.h = None
+
+
 class UnitInt8:
     """The chain pw1 -> depthwise 3x3 -> pw2 of three ConvInt8 layers as one launch (ott_unit). pw2 must outlive the unit."""
 
@@ -545,11 +580,12 @@ class Net:
         return [(i["type"], i["name"], float(m)) for i, m in zip(infos, ms)]
 
     def forward(self, input_blob: str, x: np.ndarray, out_blobs, dtypes=None):
-        """Host fp32 NCHW in, list of host arrays out (fp32 NCHW, or int8 NCHW for blobs listed in dtypes as np.int8)."""
+        """Host fp32 NCHW in, list of host arrays out: fp32 NCHW, or int8 NCHW for the blob of a requantizing layer
+        (int8_scale_term > 100); dtypes overrides the per-blob choice."""
         x = np.ascontiguousarray(x, dtype=np.float32)
         outs = []
         for i, b in enumerate(out_blobs):
-            dt = np.float32 if not dtypes else dtypes[i]
+            dt = dtypes[i] if dtypes else (np.int8 if self.lib.ott_net_blob_element_size(self.h, b.encode()) == 1 else np.float32)
             outs.append(np.empty(self.blob_shape(b)[:0] + (x.shape[0],) + self.blob_shape(b)[1:], dtype=dt))
         self.forward_raw(input_blob, _np_ptr(x), False, x.shape, out_blobs, [o.ctypes.data for o in outs])
         return outs

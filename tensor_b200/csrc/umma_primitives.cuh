@@ -8,6 +8,7 @@
 namespace ottk {
 namespace umma {
 
+constexpr uint32_t kTryWaitHintNs = 2000u;  // how long one mbarrier.try_wait may keep the warp suspended (it wakes when the phase completes)
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // default limit of one wait: 2 s (ott_set_wait_limit_ms changes it per context)
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -35,11 +36,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t"
         "}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(kTryWaitHintNs)
         : "memory");
     return ok != 0;
 }

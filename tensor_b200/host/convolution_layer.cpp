@@ -238,6 +238,7 @@ int ConvolutionLayer::make_gpu_conv(const NetOption& opt, int scale_term, const 
 }
 
 void ConvolutionLayer::release_gpu() {
+    set_pair_fusion(NetOption(), nullptr, -1);
     if (gpu_conv_) ott_conv_int8_destroy(gpu_ctx_, gpu_conv_);
     if (gpu_conv_handover_) ott_conv_int8_destroy(gpu_ctx_, gpu_conv_handover_);
     if (gpu_conv_routed_) ott_conv_int8_destroy(gpu_ctx_, gpu_conv_routed_);
@@ -328,24 +329,8 @@ static Tensor device_shell(const NetOption& opt, std::vector<int64_t> sizes) {
     return Tensor::wrap(p, 16, Device::CUDA, [ctx](void* q) { ott_free(ctx, q); }, std::move(sizes), ScalarType::Float, Layout::NCHW);
 }
 
-int ConvolutionLayer::forward_routed(const Tensor& bottom_blob, Tensor& top_blob, const NetOption& opt) const {
+int ConvolutionLayer::routed_input(const Tensor& bottom_blob, const NetOption& opt, ott_conv_io& io, std::vector<const int8_t*>& srcs, Tensor& hold) const {
     const Routing& R = routing_;
-    const int n = (int)bottom_blob.size(0), h = (int)bottom_blob.size(2), w = (int)bottom_blob.size(3);
-    int oh = 0, ow = 0;
-    ott_conv_int8_out_shape(gpu_conv_routed_, h, w, &oh, &ow);
-    if (fused_maxpool) {
-        // first layer + max-pool: the pooled values leave quantized for the layers that read the pooled blob
-        if (bottom_blob.is_table() || bottom_blob.scalar_type() != ScalarType::Float || !R.routed_out) return -1;
-        const int ph = (oh - 1) / 2 + 1, pw = (ow - 1) / 2 + 1;
-        Tensor q = device_empty(opt, {n, out_channels, ph, pw}, ScalarType::Byte, Layout::NHWC16);
-        top_blob = device_shell(opt, {n, out_channels, ph, pw});
-        if (!q.defined() || !top_blob.defined()) return -100;
-        top_blob.set_companion(q, R.self_layer);
-        return ott_conv_int8_forward_maxpool_s8(opt.gpu, gpu_conv_routed_, bottom_blob.data_ptr<float>(), n, h, w, fused_maxpool == 2 ? 1 : 0,
-                                                q.data_ptr<int8_t>());
-    }
-    ott_conv_io io{};
-    std::vector<const int8_t*> srcs;
     Tensor src = bottom_blob;
     if (R.gathered && R.direct) {
         // the output of the depthwise layer in front, in that layer's stored channel order
@@ -384,7 +369,13 @@ int ConvolutionLayer::forward_routed(const Tensor& bottom_blob, Tensor& top_blob
         else if (src.scalar_type() == ScalarType::Byte && src.layout() == Layout::NHWC16) io.in_dtype = OTT_S8_NHWC;
         else return -1;
         io.in_dev = src.raw_data();
+        hold = src;
     }
+    return 0;
+}
+
+int ConvolutionLayer::routed_output(const NetOption& opt, int n, int oh, int ow, ott_conv_io& io, Tensor& top_blob) const {
+    const Routing& R = routing_;
     const bool requant = R.routed_out || int8_scale_term > 100;
     Tensor s8;
     if (requant) {
@@ -414,7 +405,118 @@ int ConvolutionLayer::forward_routed(const Tensor& bottom_blob, Tensor& top_blob
         io.out_dev = top_blob.raw_data();
         io.out_dtype = OTT_F32_NCHW;
     }
+    return 0;
+}
+
+int ConvolutionLayer::forward_routed(const Tensor& bottom_blob, Tensor& top_blob, const NetOption& opt) const {
+    const Routing& R = routing_;
+    const int n = (int)bottom_blob.size(0), h = (int)bottom_blob.size(2), w = (int)bottom_blob.size(3);
+    int oh = 0, ow = 0;
+    ott_conv_int8_out_shape(gpu_conv_routed_, h, w, &oh, &ow);
+    if (fused_maxpool) {
+        // first layer + max-pool: the pooled values leave quantized for the layers that read the pooled blob
+        if (bottom_blob.is_table() || bottom_blob.scalar_type() != ScalarType::Float || !R.routed_out) return -1;
+        const int ph = (oh - 1) / 2 + 1, pw = (ow - 1) / 2 + 1;
+        Tensor q = device_empty(opt, {n, out_channels, ph, pw}, ScalarType::Byte, Layout::NHWC16);
+        top_blob = device_shell(opt, {n, out_channels, ph, pw});
+        if (!q.defined() || !top_blob.defined()) return -100;
+        top_blob.set_companion(q, R.self_layer);
+        return ott_conv_int8_forward_maxpool_s8(opt.gpu, gpu_conv_routed_, bottom_blob.data_ptr<float>(), n, h, w, fused_maxpool == 2 ? 1 : 0,
+                                                q.data_ptr<int8_t>());
+    }
+    ott_conv_io io{};
+    std::vector<const int8_t*> srcs;
+    Tensor hold;
+    int rc = routed_input(bottom_blob, opt, io, srcs, hold);
+    if (rc == 0) rc = routed_output(opt, n, oh, ow, io, top_blob);
+    if (rc != 0) return rc;
     return ott_conv_int8_forward_io(opt.gpu, gpu_conv_routed_, &io, n, h, w, nullptr);
+}
+
+// ---- depthwise + 1x1 pair fusion ----
+int ConvolutionLayer::set_pair_fusion(const NetOption& opt, ConvolutionLayer* dw, int dw_index) {
+    if (pair_plain_ && pair_plain_ != pair_routed_) ott_dwpw_int8_destroy(gpu_ctx_, pair_plain_);
+    if (pair_routed_) ott_dwpw_int8_destroy(gpu_ctx_, pair_routed_);
+    pair_plain_ = pair_routed_ = nullptr;
+    if (pair_front_) const_cast<ConvolutionLayer*>(pair_front_)->pair_next_ = nullptr;
+    if (pair_next_) {  // (a depthwise layer being released: its reader must not run the pair any more)
+        ConvolutionLayer* next = const_cast<ConvolutionLayer*>(pair_next_);
+        pair_next_ = nullptr;
+        next->pair_front_ = nullptr;
+        next->set_pair_fusion(opt, nullptr, -1);
+    }
+    pair_front_ = nullptr;
+    pair_tag_ = -1;
+    if (!dw || !opt.gpu || !gpu_conv_ || !dw->gpu_conv_) return 0;
+    auto make = [&](const ott_conv* dc, const ott_conv* pc, ott_dwpw** out) -> int {
+        *out = nullptr;
+        if (!dc || !pc) return 0;
+        const int rc = ott_dwpw_int8_create(opt.gpu, dc, pc, out);
+        return rc == OTT_ERR_UNSUPPORTED ? 0 : rc;  // a pair the library cannot fuse runs as two layers
+    };
+    // the layer objects forward() would run with routing off (a layer with an int8 hand-over twin picks per call: not fused)
+    const ott_conv* p_plain = gpu_conv_handover_ ? nullptr : gpu_conv_;
+    const ott_conv* d_plain = dw->gpu_conv_handover_ ? nullptr : dw->gpu_conv_;
+    // ... and with routing on
+    const ott_conv* p_routed = gpu_conv_routed_ ? gpu_conv_routed_ : p_plain;
+    const ott_conv* d_routed = dw->gpu_conv_routed_ ? dw->gpu_conv_routed_ : d_plain;
+    int rc = make(d_plain, p_plain, &pair_plain_);
+    if (rc != 0) return rc;
+    if (d_routed == d_plain && p_routed == p_plain) pair_routed_ = pair_plain_;
+    else rc = make(d_routed, p_routed, &pair_routed_);
+    if (rc != 0) return rc;
+    if (pair_plain_ || pair_routed_) {
+        pair_front_ = dw;
+        dw->pair_next_ = this;
+        pair_tag_ = dw->pair_tag_ = kDeferredTag + dw_index;
+    }
+    return 0;
+}
+
+// (on the depthwise layer) may this call leave the work to the 1x1 layer behind? Only when that layer's fused state exists for
+// the mode of this call, nobody wants this layer's own blob, and the input is int8 already.
+bool ConvolutionLayer::defers(const Tensor& bottom_blob, const NetOption& opt) const {
+    if (!pair_next_ || !opt.fuse_depthwise_pointwise || tops.empty() || opt.layer_ms) return false;
+    const bool routed = opt.routing_active;
+    if (!pair_next_->pair_ready(routed)) return false;
+    if (opt.blob_wanted == tops[0] || (opt.keep_blobs && (*opt.keep_blobs)[(size_t)tops[0]])) return false;
+    if (routed && gpu_conv_routed_ && routing_.gathered && !routing_.direct) return true;  // reads its producers' int8 tensors
+    return !bottom_blob.is_table() && bottom_blob.scalar_type() == ScalarType::Byte && bottom_blob.layout() == Layout::NHWC16 &&
+           (int)bottom_blob.size(1) == in_channels;
+}
+
+// (on the 1x1 layer) both layers in one launch: the input side is the depthwise layer's, the output side this layer's
+int ConvolutionLayer::forward_pair(const Tensor& dwb, Tensor& top_blob, const NetOption& opt) const {
+    const ConvolutionLayer* dw = pair_front_;
+    const bool routed = opt.routing_active;
+    const ott_dwpw* pair = routed ? pair_routed_ : pair_plain_;
+    if (!dw || !pair || !dwb.defined() || dwb.dim() != 4) return -1;
+    const int n = (int)dwb.size(0), h = (int)dwb.size(2), w = (int)dwb.size(3);
+    const int oh = (h + 2 - 3) / dw->stride_height + 1, ow = (w + 2 - 3) / dw->stride_width + 1;
+    ott_conv_io io{};
+    std::vector<const int8_t*> srcs;
+    Tensor hold;
+    int rc = 0;
+    if (routed && dw->gpu_conv_routed_) {
+        rc = dw->routed_input(dwb, opt, io, srcs, hold);
+        if (rc == 0 && io.in_dtype != OTT_S8_NHWC) rc = -1;
+    } else {
+        if (dwb.is_table() || dwb.scalar_type() != ScalarType::Byte || dwb.layout() != Layout::NHWC16) return -1;
+        io.in_dev = dwb.raw_data();
+        io.in_dtype = OTT_S8_NHWC;
+    }
+    if (rc != 0) return rc;
+    if (routed && gpu_conv_routed_) {
+        rc = routed_output(opt, n, oh, ow, io, top_blob);
+        if (rc != 0) return rc;
+    } else {
+        const bool requant = int8_scale_term > 100;
+        top_blob = device_empty(opt, {n, out_channels, oh, ow}, requant ? ScalarType::Byte : ScalarType::Float, requant ? Layout::NHWC16 : Layout::NCHW);
+        if (!top_blob.defined()) return -100;
+        io.out_dev = top_blob.raw_data();
+        io.out_dtype = requant ? OTT_S8_NHWC : OTT_F32_NCHW;
+    }
+    return ott_dwpw_int8_forward_io(opt.gpu, pair, &io, n, h, w, nullptr);
 }
 
 // The consumer quantizes its fp32 input with float2int8(v * scale) (Tensor/QuantizeX86.cpp:23-71, called from
@@ -453,7 +555,17 @@ int ConvolutionLayer::forward(const Tensor& bottom_blob, Tensor& top_blob, const
         return ott_conv_f32_forward(opt.gpu, gpu_conv_f32_, src.data_ptr<float>(), n, h, w, top_blob.data_ptr<float>());
     }
     if (!gpu_conv_ || !bottom_blob.defined() || bottom_blob.device() != Device::CUDA || bottom_blob.dim() != 4) return -1;
+    // a deferred depthwise layer in front: its input arrives as the companion of an empty shell, and this layer runs both
+    if (pair_front_ && bottom_blob.companion_tag() == pair_tag_) return forward_pair(*bottom_blob.companion(), top_blob, opt);
     const int n = (int)bottom_blob.size(0), c = (int)bottom_blob.size(1), h = (int)bottom_blob.size(2), w = (int)bottom_blob.size(3);
+    if (defers(bottom_blob, opt)) {
+        // this depthwise layer runs inside the 1x1 layer behind it: hand the input on
+        const int oh = (h + 2 - 3) / stride_height + 1, ow = (w + 2 - 3) / stride_width + 1;
+        top_blob = device_shell(opt, {n, out_channels, oh, ow});
+        if (!top_blob.defined()) return -100;
+        top_blob.set_companion(bottom_blob, pair_tag_);
+        return 0;
+    }
     if (opt.routing_active && gpu_conv_routed_) return forward_routed(bottom_blob, top_blob, opt);
     if (c != in_channels) return -1;
     int oh = 0, ow = 0;

@@ -85,6 +85,7 @@ int ott_net_set_option(ott_net* net, const char* key, int value) {
     else if (k == "fuse_first_layer_pool") o.fuse_first_layer_pool = value != 0;
     else if (k == "int8_handover") o.int8_handover = value != 0;
     else if (k == "int8_routing") o.int8_routing = value != 0;
+    else if (k == "fuse_depthwise_pointwise") o.fuse_depthwise_pointwise = value != 0;
     else if (k == "host_chunk") o.host_chunk = value;
     else return fail(net, OTT_ERR_INVALID, "unknown Net option: " + k);
     return OTT_OK;

@@ -143,6 +143,11 @@ public:
     // one) contains a channel that would then exist in int8 only.
     bool int8_routing = true;
     bool routing_active = false;
+    // a depthwise 3x3 layer (pad 1, stride 1 / 2) whose int8 output only the 1x1 layer behind it reads runs inside that layer's
+    // kernel (ott_dwpw): one launch instead of two, the tensor between them never leaves the SM. Asking for the depthwise
+    // layer's blob through Extractor::extract still delivers it (the pair then runs as two layers). Off by default: it pays
+    // for small batches only (fewer launches), large batches run faster as two kernels whose epilogues overlap.
+    bool fuse_depthwise_pointwise = false;
     int host_chunk = 64;  // ott_net_forward from host memory: images per chunk of the upload / compute / download pipeline
     const std::vector<char>* keep_blobs = nullptr;  // set by Extractor::keep: blobs lightmode must not release
     int blob_wanted = -1;  // set by Extractor::extract: the blob that must come out in the reference's own type
@@ -320,8 +325,26 @@ public:
     bool routable_producer() const;
     bool routes_all_or_nothing() const { return fused_maxpool != 0; }  // no fp32 side output: every channel in int8, or none
 
+    // Depthwise + 1x1 pair fusion (Net::plan_pair_fusions), called on the 1x1 layer with the depthwise layer in front of it
+    // (NULL: drop). Builds the fused state for the layer objects the two layers would run with routing on and with routing
+    // off, wherever the library can fuse them. The depthwise layer's forward then hands its input on in a deferred tensor
+    // (Tensor::companion_tag() == kDeferredTag + its layer index) and this layer's forward runs both.
+    static constexpr int kDeferredTag = 1 << 28;
+    int set_pair_fusion(const NetOption& opt, ConvolutionLayer* depthwise_front, int depthwise_layer_index);
+    bool pair_ready(bool routed) const { return (routed ? pair_routed_ : pair_plain_) != nullptr; }
+
 private:
     int forward_routed(const Tensor& bottom_blob, Tensor& top_blob, const NetOption& opt) const;
+    // the two halves of forward_routed: where the routed twin's input bytes are, where its output goes
+    int routed_input(const Tensor& bottom_blob, const NetOption& opt, ott_conv_io& io, std::vector<const int8_t*>& srcs, Tensor& hold) const;
+    int routed_output(const NetOption& opt, int n, int oh, int ow, ott_conv_io& io, Tensor& top_blob) const;
+    int forward_pair(const Tensor& depthwise_bottom, Tensor& top_blob, const NetOption& opt) const;
+    bool defers(const Tensor& bottom_blob, const NetOption& opt) const;
+    const ConvolutionLayer* pair_front_ = nullptr;  // on the 1x1 layer
+    const ConvolutionLayer* pair_next_ = nullptr;   // on the depthwise layer
+    int pair_tag_ = -1;                              // on both: kDeferredTag + the depthwise layer's index
+    ott_dwpw* pair_routed_ = nullptr;
+    ott_dwpw* pair_plain_ = nullptr;
     Routing routing_;
     ott_conv* gpu_conv_routed_ = nullptr;
     int make_gpu_conv(const NetOption& opt, int scale_term, const Tensor& top_scales, ott_conv** out) const;
@@ -383,6 +406,8 @@ private:
     int plan_fusions();  // first layer + max-pool, int8 hand-over: after every create_pipeline
     // Which channels travel in int8 through the glue layers: done lazily before the first forward after a change.
     int plan_routing();
+    int plan_channel_routing();
+    int plan_pair_fusions();
     int ensure_routing() const;
     int forward_layer(int layer_index, std::vector<Tensor>& blob_tensors, const NetOption& opt) const;
     int do_forward_layer(const Layer* layer, std::vector<Tensor>& blob_tensors, const NetOption& opt) const;

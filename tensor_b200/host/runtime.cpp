@@ -455,6 +455,32 @@ int Net::ensure_routing() const {
 // would have computed from the fp32 v (ConvolutionLayer.cpp:763-779 after QuantizeX86.cpp:851-903), and it gathers them from
 // the producers' int8 tensors. Channels with any other reader (a depthwise layer, a second branch, a graph output) stay fp32.
 int Net::plan_routing() {
+    // fused pairs point into the layer objects the routing plan is about to replace
+    for (Layer* l : layers_)
+        if (auto* conv = dynamic_cast<ConvolutionLayer*>(l)) conv->set_pair_fusion(option, nullptr, -1);
+    const int rc = plan_channel_routing();
+    return rc != 0 ? rc : plan_pair_fusions();
+}
+
+// A depthwise 3x3 layer whose output blob has exactly one reader, a 1x1 convolution: the two run as one kernel wherever the
+// library can fuse the layer objects they would run with (ConvolutionLayer::set_pair_fusion decides; not fusable is not an error).
+int Net::plan_pair_fusions() {
+    if (!option.fuse_depthwise_pointwise || !option.gpu) return 0;
+    for (size_t li = 0; li < layers_.size(); ++li) {
+        auto* dw = dynamic_cast<ConvolutionLayer*>(layers_[li]);
+        if (!dw || dw->tops.size() != 1 || dw->bottoms.size() != 1) continue;
+        if (dw->groups <= 1 || dw->groups != dw->in_channels || dw->groups != dw->out_channels || dw->kernel_height != 3 || dw->kernel_width != 3) continue;
+        const int next = blobs_[(size_t)dw->tops[0]].consumer;
+        if (next < 0) continue;
+        auto* pw = dynamic_cast<ConvolutionLayer*>(layers_[(size_t)next]);
+        if (!pw || pw->bottoms.size() != 1 || pw->bottoms[0] != dw->tops[0] || pw->groups != 1 || pw->kernel_height != 1 || pw->kernel_width != 1) continue;
+        const int rc = pw->set_pair_fusion(option, dw, (int)li);
+        if (rc != 0) { error_ = "depthwise + 1x1 fusion of " + dw->name + " and " + pw->name + " failed: " + ott_last_error(option.gpu); return rc; }
+    }
+    return 0;
+}
+
+int Net::plan_channel_routing() {
     routing_dirty_ = false;
     has_routing_ = false;
     blob_needs_f32_.assign(blobs_.size(), 0);
@@ -809,6 +835,8 @@ int Extractor::extract(int blob_index, Tensor& feat, int type) {
         const auto* conv = prod >= 0 ? dynamic_cast<const ConvolutionLayer*>(net_->layers_[(size_t)prod]) : nullptr;
         const Tensor& have = blob_tensors_[(size_t)blob_index];
         if (conv && conv->int8_scale_term < 100 && have.defined() && have.scalar_type() == ScalarType::Byte) blob_tensors_[(size_t)blob_index].reset();
+        // a depthwise layer's blob that an earlier extract left deferred (computed inside the next layer's kernel) likewise
+        if (have.defined() && have.companion_tag() >= ConvolutionLayer::kDeferredTag) blob_tensors_[(size_t)blob_index].reset();
     }
     {
         // Routing on or off for this call: off when the wanted blob, or one the caller keeps, holds a channel that would then

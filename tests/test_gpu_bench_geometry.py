@@ -153,3 +153,34 @@ def test_shipped_mixed_detector_fp32_first_layer():
     for name, g in zip(heads, net.forward("data", x, heads)):
         assert np.array_equal(bits(g), bits(want[name])), f"head {name} differs"
     net.close()
+
+
+@pytest.mark.parametrize("routing", [1, 0], ids=["routed", "unrouted"])
+def test_depthwise_pointwise_fusion_changes_no_blob(shufflenet_320, routing):
+    """"fuse_depthwise_pointwise": every depthwise 3x3 layer whose only reader is a 1x1 layer runs inside that layer's kernel
+    (plain and gathered inputs, stride 1 and 2, 24 to 232 channels, int8 + fp32 side outputs). Same bits at the benchmarked
+    geometry, fewer launches; a depthwise layer's own blob can still be extracted (the pair then runs as two layers)."""
+    from graph_support import build_net
+    L, params, x, probes, want = shufflenet_320
+    fused = build_net(L, params, options={"int8_routing": routing, "fuse_depthwise_pointwise": 1})
+    plain = build_net(L, params, options={"int8_routing": routing})
+    counts = []
+    for net in (fused, plain):
+        before = net.context().launch_count()
+        got = net.forward("data", x, ["conv5"])[0]
+        counts.append(net.context().launch_count() - before)
+        assert np.array_equal(bits(got), bits(want["conv5"]))
+    # routed: 18 of the 19 depthwise layers fuse (the one behind the first layer's 24-channel pooled output is laid out in
+    # 16-channel groups, which the pair kernel does not read); unrouted: the 13 stride-1 units and the three right branches
+    # (the left-branch depthwise layers of the stride-2 units read fp32 blobs there and run by themselves)
+    assert counts[1] - counts[0] == (18 if routing else 16), counts
+    got = fused.forward("data", x, probes)
+    for name, g in zip(probes, got):
+        assert np.array_equal(bits(g), bits(want[name])), f"blob {name} differs"
+    # a fused-away blob is still there for the asking, and the fused path still works afterwards
+    dw_blob = fused.forward("data", x, ["s2b1_dw"])[0]
+    ref_blob = plain.forward("data", x, ["s2b1_dw"])[0]
+    assert dw_blob.shape == ref_blob.shape and np.array_equal(bits(dw_blob), bits(ref_blob))
+    assert np.array_equal(bits(fused.forward("data", x, ["conv5"])[0]), bits(want["conv5"]))
+    fused.close()
+    plain.close()
