@@ -93,6 +93,10 @@ int ott_set_depthwise_tensor_cores(ott_ctx* ctx, int mode);
  * (cudaErrorMemoryAllocation without calling cudaMalloc); n <= 0 switches the injection off. */
 int ott_debug_wait_probe(ott_ctx* ctx);
 int ott_debug_fail_alloc_after(ott_ctx* ctx, int n);
+/* Measurement hook: cycles one tcgen05.mma kind::i8 (M = 128, K = 32, N = n_cols) occupies an SM when issuing_warps x
+ * issuing_lanes threads of each of ctas_per_sm CTAs per SM issue `reps` of them back to back (zero operands; the design notes
+ * argue tile shapes from these numbers: 128 / 64 / 48 / 40 cycles at N = 256 / 128 / 64 / 32, one issuing thread alone 56). */
+int ott_debug_mma_rate(ott_ctx* ctx, int n_cols, int issuing_warps, int issuing_lanes, int ctas_per_sm, int reps, float* cycles_per_mma);
 
 /* Stream-ordered, size-keyed caching allocator: a freed block is handed back to the next request of the
  * same rounded size without touching cudaMalloc (the policy of CPUCachingAllocator::allocate/free,

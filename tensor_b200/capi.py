@@ -37,6 +37,7 @@ SIGNATURES = {
     "ott_sync": (i32, [vp]),
     "ott_set_wait_limit_ms": (i32, [vp, i32]),
     "ott_debug_wait_probe": (i32, [vp]),
+    "ott_debug_mma_rate": (i32, [vp, i32, i32, i32, i32, i32, C.POINTER(C.c_float)]),
     "ott_set_depthwise_tensor_cores": (i32, [vp, i32]),
     "ott_debug_fail_alloc_after": (i32, [vp, i32]),
     "ott_malloc": (i32, [vp, sz, C.POINTER(vp)]),

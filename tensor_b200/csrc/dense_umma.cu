@@ -100,6 +100,8 @@ dense_umma_kernel(const __grid_constant__ KernelMaps maps, const __grid_constant
     const int loads_per_tile = P.halo ? P.ncb : (P.gather && P.gather_whole ? 1 : P.nkb);
 
     if (threadIdx.x == 0) {
+        prefetch_tensormap(&tmB);
+        for (int i = 0; i < (P.gather > 0 ? P.gather : 1); ++i) prefetch_tensormap(&maps.tm[i]);
         for (int i = 0; i < P.stages; ++i) {
             mbar_init(bar_full + 8u * i, 1);
             mbar_init(bar_empty + 8u * i, 1);

@@ -69,6 +69,8 @@ dw_umma_kernel(const __grid_constant__ DwMaps maps, const __grid_constant__ CUte
     const int nb = P.ncb_total - cb0 < P.ncb ? P.ncb_total - cb0 : P.ncb;
     const int c_base = cb0 * kBlock;
     if (threadIdx.x == 0) {
+        prefetch_tensormap(&tmW);
+        for (int cb = 0; cb < nb; ++cb) prefetch_tensormap(&maps.tm[maps.block_src[cb0 + cb]]);
         mbar_init(bar_w, 1);
         for (int i = 0; i < P.stages; ++i) {
             mbar_init(bar_full + 8u * i, 1);

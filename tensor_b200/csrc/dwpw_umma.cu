@@ -74,6 +74,9 @@ dwpw_umma_kernel(const __grid_constant__ DwPwMaps maps, const __grid_constant__ 
     const uint32_t wpw_block = (uint32_t)P.c2 * kBlock;
 
     if (threadIdx.x == 0) {
+        prefetch_tensormap(&tmWdw);
+        prefetch_tensormap(&tmWpw);
+        for (int cb = 0; cb < P.ncb; ++cb) prefetch_tensormap(&maps.tm[maps.block_src[cb]]);
         mbar_init(bar(B_W), 1);
         for (int i = 0; i < P.stages; ++i) {
             mbar_init(bar(B_FULL + i), 1);
