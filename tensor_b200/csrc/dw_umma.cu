@@ -136,7 +136,18 @@ dw_umma_kernel(const __grid_constant__ DwMaps maps, const __grid_constant__ CUte
             const int cb = lane;
             bool ok = mbar_wait(bar_w, 0, abort_flag, status, 16u, P.wait_ns);
             tc_fence_after();
-            const uint64_t b0 = make_smem_desc(sW + (uint32_t)cb * 9u * 1024u, kBlock);
+            // Per tap: the filter matrix's descriptor and the offset of the shifted input view inside a block (16-byte units;
+            // stride 2: the taps kx = 1 read the second column set, kx = 2 one column on). Worked out once: between two MMAs the
+            // issuing thread then only adds a constant to the low word of the block's descriptor (the address field cannot carry).
+            uint64_t bdesc[9];
+            uint32_t aoff[9];
+#pragma unroll
+            for (int tap = 0; tap < 9; ++tap) {
+                const int ky = tap / 3, kx = tap % 3;
+                bdesc[tap] = make_smem_desc(sW + (uint32_t)(cb * 9 + tap) * 1024u, kBlock);
+                const int col = P.stride == 1 ? kx : (kx >> 1);
+                aoff[tap] = (uint32_t)((ky * P.set_w + col) * (kBlock >> 4)) + ((P.stride == 2 && kx == 1) ? (uint32_t)(P.set_bytes >> 4) : 0u);
+            }
             const uint32_t sbo = (uint32_t)(P.stride * P.set_w * kBlock);
             uint32_t it = 0;
             for (int m = m_first; ok && m < P.m_tiles; m += m_step, ++it) {
@@ -148,16 +159,11 @@ dw_umma_kernel(const __grid_constant__ DwMaps maps, const __grid_constant__ CUte
                 const uint32_t d = tmem_base + buf * (uint32_t)P.cols + (uint32_t)(cb * kBlock);
                 const uint32_t blk = sX + st * (uint32_t)P.stage_bytes + (uint32_t)(cb * P.block_bytes);
                 // 8-row groups (one tile row of 8 pixels each) are `stride` input rows apart
-                const uint64_t a_s0 = make_smem_desc(blk, kBlock, (int)sbo);
-                const uint64_t a_s1 = make_smem_desc(blk + (uint32_t)P.set_bytes, kBlock, (int)sbo);
+                const uint64_t a_base = make_smem_desc(blk, kBlock, (int)sbo);
+                const uint32_t a_lo = (uint32_t)a_base;
+                const uint64_t a_hi = a_base & 0xFFFFFFFF00000000ull;
 #pragma unroll
-                for (int tap = 0; tap < 9; ++tap) {
-                    const int ky = tap / 3, kx = tap % 3;
-                    // stride 1: pixel offset (ky, kx) in the one tile; stride 2: kx = 1 reads the second column set, kx = 2 one column on
-                    const uint32_t col = P.stride == 1 ? (uint32_t)kx : (uint32_t)(kx >> 1);
-                    const uint64_t a0 = (P.stride == 2 && kx == 1) ? a_s1 : a_s0;
-                    umma_i8(d, a0 + (uint32_t)(ky * P.set_w + (int)col) * (kBlock >> 4), b0 + (uint32_t)tap * (1024u >> 4), P.idesc, tap != 0 ? 1u : 0u);
-                }
+                for (int tap = 0; tap < 9; ++tap) umma_i8(d, a_hi | (uint64_t)(a_lo + aoff[tap]), bdesc[tap], P.idesc, tap != 0 ? 1u : 0u);
                 umma_commit(bar_empty + 8u * st);
                 umma_commit(bar_afull + 8u * buf);
             }

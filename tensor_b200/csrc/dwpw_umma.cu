@@ -162,6 +162,15 @@ dwpw_umma_kernel(const __grid_constant__ DwPwMaps maps, const __grid_constant__ 
             bool ok = mbar_wait(bar(B_W), 0, abort_flag, status, 16u, P.wait_ns);
             tc_fence_after();
             const uint32_t sbo = (uint32_t)(P.stride * P.set_w * kBlock);
+            // offset of each tap's shifted input view inside a block, in 16-byte units (stride 2: the taps kx = 1 read the second
+            // column set, kx = 2 one column on), worked out once
+            uint32_t aoff[9];
+#pragma unroll
+            for (int tap = 0; tap < 9; ++tap) {
+                const int ky = tap / 3, kx = tap % 3;
+                const int col = P.stride == 1 ? kx : (kx >> 1);
+                aoff[tap] = (uint32_t)((ky * P.set_w + col) * (kBlock >> 4)) + ((P.stride == 2 && kx == 1) ? (uint32_t)(P.set_bytes >> 4) : 0u);
+            }
             uint32_t cnt = 0;
             // depthwise stage of this CTA's tile number t: lane l issues the nine taps of block l of every chunk
             auto issue_dw = [&](uint32_t t) -> bool {
@@ -176,15 +185,12 @@ dwpw_umma_kernel(const __grid_constant__ DwPwMaps maps, const __grid_constant__ 
                         const uint32_t d = t_dw + buf * (uint32_t)P.dwcols + (uint32_t)(cb * kBlock);
                         const uint32_t blk = sX + st * (uint32_t)P.chunk_bytes + (uint32_t)(lane * P.block_bytes);
                         const uint64_t b0 = make_smem_desc(sWdw + (uint32_t)cb * 9u * 1024u, kBlock);
-                        const uint64_t a_s0 = make_smem_desc(blk, kBlock, (int)sbo);
-                        const uint64_t a_s1 = make_smem_desc(blk + (uint32_t)P.set_bytes, kBlock, (int)sbo);
+                        const uint64_t a_base = make_smem_desc(blk, kBlock, (int)sbo);
+                        const uint32_t a_lo = (uint32_t)a_base;
+                        const uint64_t a_hi = a_base & 0xFFFFFFFF00000000ull;
 #pragma unroll
-                        for (int tap = 0; tap < 9; ++tap) {
-                            const int ky = tap / 3, kx = tap % 3;
-                            const uint32_t col = P.stride == 1 ? (uint32_t)kx : (uint32_t)(kx >> 1);
-                            const uint64_t a0 = (P.stride == 2 && kx == 1) ? a_s1 : a_s0;
-                            umma_i8(d, a0 + (uint32_t)(ky * P.set_w + (int)col) * (kBlock >> 4), b0 + (uint32_t)tap * (1024u >> 4), P.idesc_dw, tap != 0 ? 1u : 0u);
-                        }
+                        for (int tap = 0; tap < 9; ++tap)
+                            umma_i8(d, a_hi | (uint64_t)(a_lo + aoff[tap]), b0 + (uint32_t)tap * (1024u >> 4), P.idesc_dw, tap != 0 ? 1u : 0u);
                     }
                     umma_commit(bar(B_EMPTY + st));
                 }

@@ -51,15 +51,17 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
                                           uint32_t code, unsigned long long limit_ns = kWaitLimitNs) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = globaltimer_ns();
-    for (uint32_t spin = 1;; ++spin) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((spin & 255u) == 0) {
-            if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > limit_ns) {
-                *abort_flag = 1;
-                if (status) atomicOr(status, code);
-                return false;
-            }
+    for (;;) {
+        // a short inner loop of bare polls (each may keep the warp suspended for the hint's duration); the abort flag and the
+        // clock are looked at between such bursts only
+#pragma unroll 1
+        for (int i = 0; i < 32; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (globaltimer_ns() - t0 > limit_ns) {
+            *abort_flag = 1;
+            if (status) atomicOr(status, code);
+            return false;
         }
     }
 }
