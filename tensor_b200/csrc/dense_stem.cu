@@ -141,12 +141,19 @@ constexpr uint32_t SPM_TMEM_COLS = 128;       // 4 accumulators of 32 columns
 
 // OUT8: the pooled values leave quantized, float2int8(v * scale_out[channel]), as an int8 NHWC tensor (what the quantize pass of
 // the layers reading the pooled blob would compute from the fp32 values) instead of fp32 NCHW planes.
-template <int S, int ACT, bool OUT8>
+// C24: the instance for the usual first layer (24 output channels, a bias, the add-half-truncate rounding rule): channel-group
+// counts, the accumulator tile's pitch, the bias switch and the rounding rule are compile-time constants there, so the
+// channel loops unroll and their addresses are immediates (a fifth fewer instructions in a kernel bound by instruction issue).
+template <int S, int ACT, bool OUT8, bool C24>
 __global__ void __launch_bounds__(256)
-dense_stem_pool_mma_kernel(const float* __restrict__ x, const __grid_constant__ StemParams P, float in_scale, int has_bias, float act_p0,
-                           int rounding, void* __restrict__ out_any, ConvShape s, int ph_out, int pw_out, int tiles_x, int tiles_y, int pad_zero,
+dense_stem_pool_mma_kernel(const float* __restrict__ x, const __grid_constant__ StemParams P, float in_scale, int has_bias_arg, float act_p0,
+                           int rounding_arg, void* __restrict__ out_any, ConvShape s_arg, int ph_out, int pw_out, int tiles_x, int tiles_y, int pad_zero,
                            uint32_t* __restrict__ status) {
     using namespace umma;
+    const int has_bias = C24 ? 1 : has_bias_arg;
+    const int rounding = C24 ? (int)ROUND_ADD_HALF_TRUNC : rounding_arg;
+    ConvShape s = s_arg;
+    if (C24) { s.cout = 24; s.cout_pad = 32; }
     constexpr int IW = (SP_CX - 1) * S + 3, IH = (SP_CY - 1) * S + 3;
     constexpr int RP = (IW + 3 + 3) / 4 + 1;
     extern __shared__ uint8_t smem_spm[];
@@ -306,9 +313,15 @@ dense_stem_pool_mma_kernel(const float* __restrict__ x, const __grid_constant__ 
             tmem_wait_ld16(*reinterpret_cast<int(*)[16]>(&v[16]));
             if (p >= SP_CX * SP_CY) continue;
             int4* dst = reinterpret_cast<int4*>(cacc + p * pitch);
+            if (inside) {
 #pragma unroll
-            for (int g = 0; g < ST_COUT_MAX / 4; ++g)
-                if (g < cout4) dst[g] = inside ? make_int4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]) : make_int4(INT_MIN, INT_MIN, INT_MIN, INT_MIN);
+                for (int g = 0; g < ST_COUT_MAX / 4; ++g)
+                    if (g < cout4) dst[g] = make_int4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+            } else {
+#pragma unroll
+                for (int g = 0; g < ST_COUT_MAX / 4; ++g)
+                    if (g < cout4) dst[g] = make_int4(INT_MIN, INT_MIN, INT_MIN, INT_MIN);
+            }
         }
     }
     tc_fence_before();
@@ -349,7 +362,7 @@ dense_stem_pool_mma_kernel(const float* __restrict__ x, const __grid_constant__ 
             for (int j = 0; j < 4; ++j) {
                 const float a = __int2float_rn(m[j]);
                 y[j] = activate_t<ACT>(has_bias ? __fmaf_rn(a, sia[j], bia[j]) : __fmul_rn(a, sia[j]), act_p0);
-                if (pad_counts) y[j] = fmaxf(y[j], 0.f);
+                if (ACT != ACT_RELU && ACT != ACT_RELU6 && pad_counts) y[j] = fmaxf(y[j], 0.f);  // (after a ReLU nothing is below the padding's 0)
             }
             if (OUT8) {
                 const float4 so = *reinterpret_cast<const float4*>(&sprm[2][4 * q4]);
@@ -427,9 +440,10 @@ static cudaError_t launch_pool_s(cudaStream_t stream, const float* x, const Stem
     const size_t front = (size_t)SPM_ROWS * 32 + 1024 + (size_t)3 * IH * RP * 4;
     const size_t tile = (size_t)SP_CY * SP_CX * (((s.cout + 3) / 4) * 4 + 4) * 4;
     const size_t smem = 1024 + (front > tile ? front : tile);
+    const bool c24 = s.cout == 24 && s.cout_pad == 32 && ep.has_bias && ep.rounding == ROUND_ADD_HALF_TRUNC;
 #define OTT_STEMPOOL_LAUNCH(ACT)                                                                                          \
     {                                                                                                                     \
-        auto kernel = dense_stem_pool_mma_kernel<S, ACT, OUT8>;                                                           \
+        auto kernel = c24 ? dense_stem_pool_mma_kernel<S, ACT, OUT8, true> : dense_stem_pool_mma_kernel<S, ACT, OUT8, false>;    \
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);            \
         if (e != cudaSuccess) return e;                                                                                   \
         e = launch_overlapped(kernel, dim3((unsigned)blocks), dim3(256), smem, stream, x, P, in_scale, ep.has_bias, ep.act_param0,        \
