@@ -339,7 +339,7 @@ dense_umma_kernel(const __grid_constant__ KernelMaps maps, const __grid_constant
                                 qv[2 * h] = __float2int_rz(r.x);
                                 qv[2 * h + 1] = __float2int_rz(r.y);
                             } else {
-                                const float2 r = __fadd2_rn(t, make_float2(copysignf(0.5f, t.x), copysignf(0.5f, t.y)));
+                                const float2 r = __fadd2_rn(t, make_float2(half_signed(t.x), half_signed(t.y)));
                                 qv[2 * h] = __float2int_rz(fmaxf(r.x, -127.5f));
                                 qv[2 * h + 1] = __float2int_rz(fmaxf(r.y, -127.5f));
                             }

@@ -54,6 +54,14 @@ __device__ __forceinline__ float activate(float v, int act, float p0) {
     }
 }
 
+// copysign(0.5, v) as one logic instruction: (bits(v) & 0x80000000) | bits(0.5). Written as lop3 with both constants in
+// registers; the compiler's own form takes two instructions per value (a logic instruction carries one immediate).
+__device__ __forceinline__ float half_signed(float v) {
+    uint32_t r;
+    asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(__float_as_uint(v)), "r"(0x80000000u), "r"(0x3F000000u));
+    return __uint_as_float(r);
+}
+
 // float -> int in [-127,127], kept as int so four of them can be packed by the caller.
 __device__ __forceinline__ int float2int8(float v, int rounding) {
     int i;
@@ -63,7 +71,7 @@ __device__ __forceinline__ int float2int8(float v, int rounding) {
         i = __float2int_rz(t);
         if (fabsf(frac) >= 0.5f) i += (v < 0.f) ? -1 : 1;
     } else {
-        const float adj = __fadd_rn(v, copysignf(0.5f, v));
+        const float adj = __fadd_rn(v, half_signed(v));
         i = __float2int_rz(adj);
     }
     return max(-127, min(127, i));
@@ -100,7 +108,7 @@ __device__ __forceinline__ uint32_t pack_sat_s8x4(int a, int b, int c, int d) {
 // float2int8 with rounding 0, clamped below at -127 only: trunc(max(adj, -127.5)) == max(trunc(adj), -127).
 // The clamp at +127 is left to pack_sat_s8x4.
 __device__ __forceinline__ int f2i8_lo_clamped(float v) {
-    return __float2int_rz(fmaxf(__fadd_rn(v, copysignf(0.5f, v)), -127.5f));
+    return __float2int_rz(fmaxf(__fadd_rn(v, half_signed(v)), -127.5f));
 }
 
 // the same for v >= 0 (after ReLU / ReLU6): copysign(0.5, v) is +0.5; v == -0 truncates to 0 either way
@@ -111,8 +119,8 @@ __device__ __forceinline__ uint32_t quantize4_pack(float x, float y, float z, fl
     // the multiplies and the additions of +-0.5 as packed pairs (same IEEE operations, half the instructions)
     const float2 sc = make_float2(scale, scale);
     const float2 a = __fmul2_rn(make_float2(x, y), sc), b = __fmul2_rn(make_float2(z, w), sc);
-    const float2 ra = __fadd2_rn(a, make_float2(copysignf(0.5f, a.x), copysignf(0.5f, a.y)));
-    const float2 rb = __fadd2_rn(b, make_float2(copysignf(0.5f, b.x), copysignf(0.5f, b.y)));
+    const float2 ra = __fadd2_rn(a, make_float2(half_signed(a.x), half_signed(a.y)));
+    const float2 rb = __fadd2_rn(b, make_float2(half_signed(b.x), half_signed(b.y)));
     return pack_sat_s8x4(__float2int_rz(fmaxf(ra.x, -127.5f)), __float2int_rz(fmaxf(ra.y, -127.5f)), __float2int_rz(fmaxf(rb.x, -127.5f)),
                          __float2int_rz(fmaxf(rb.y, -127.5f)));
 }

@@ -29,7 +29,7 @@ __device__ __forceinline__ void requant16(const int (&v)[16], const float* __res
                 qv[2 * h] = __float2int_rz(r.x);
                 qv[2 * h + 1] = __float2int_rz(r.y);
             } else {
-                const float2 r = __fadd2_rn(u, make_float2(copysignf(0.5f, u.x), copysignf(0.5f, u.y)));
+                const float2 r = __fadd2_rn(u, make_float2(half_signed(u.x), half_signed(u.y)));
                 qv[2 * h] = __float2int_rz(fmaxf(r.x, -127.5f));
                 qv[2 * h + 1] = __float2int_rz(fmaxf(r.y, -127.5f));
             }
@@ -128,7 +128,7 @@ __device__ __forceinline__ void store_accumulator_row(uint32_t taddr, int ncols,
                         qv[2 * h] = __float2int_rz(rr.x);
                         qv[2 * h + 1] = __float2int_rz(rr.y);
                     } else {
-                        const float2 rr = __fadd2_rn(u, make_float2(copysignf(0.5f, u.x), copysignf(0.5f, u.y)));
+                        const float2 rr = __fadd2_rn(u, make_float2(half_signed(u.x), half_signed(u.y)));
                         qv[2 * h] = __float2int_rz(fmaxf(rr.x, -127.5f));
                         qv[2 * h + 1] = __float2int_rz(fmaxf(rr.y, -127.5f));
                     }
