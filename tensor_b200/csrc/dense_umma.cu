@@ -28,6 +28,8 @@
 // into the status word, and all roles fall through to the common teardown, which frees TMEM.
 #include <cuda.h>
 
+#include <type_traits>
+
 #include <mutex>
 
 #include "dense_umma.h"
@@ -209,6 +211,28 @@ dense_umma_kernel(const __grid_constant__ KernelMaps maps, const __grid_constant
                         const uint64_t b0 = make_smem_desc(sB + kb * b_tile_bytes, P.bkc);
                         const uint32_t b_tap_step = ((uint32_t)P.ncb * b_tile_bytes) >> 4, a_px_step = (uint32_t)P.bkc >> 4;
                         uint32_t accumulate = kb != 0 ? 1u : 0u, a_row = 0, b_off = 0;
+                        if (s.kh == 3 && s.kw == 3) {
+                            // the common filter: all loops unrolled, every descriptor the base's low word plus a constant (the
+                            // address field cannot carry), so that the one issuing thread spends its time issuing
+                            const uint32_t a_lo = (uint32_t)a0, b_lo = (uint32_t)b0;
+                            const uint64_t a_hi = a0 & 0xFFFFFFFF00000000ull, b_hi = b0 & 0xFFFFFFFF00000000ull;
+                            const uint32_t row_step = (uint32_t)(kHaloTw + 2) * a_px_step;
+                            auto taps = [&](auto steps) {
+                                constexpr int J = decltype(steps)::value;
+#pragma unroll
+                                for (int tap = 0; tap < 9; ++tap) {
+                                    const uint32_t ao = (uint32_t)(tap / 3) * row_step + (uint32_t)(tap % 3) * a_px_step, bo = (uint32_t)tap * b_tap_step;
+#pragma unroll
+                                    for (int j = 0; j < J; ++j) {
+                                        umma_i8(d, a_hi | (uint64_t)(a_lo + ao + 2u * j), b_hi | (uint64_t)(b_lo + bo + 2u * j), P.idesc, accumulate);
+                                        accumulate = 1u;
+                                    }
+                                }
+                            };
+                            if (P.bkc == 128) taps(std::integral_constant<int, 4>{});
+                            else if (P.bkc == 64) taps(std::integral_constant<int, 2>{});
+                            else taps(std::integral_constant<int, 1>{});
+                        } else
                         for (int ky = 0; ky < s.kh; ++ky, a_row += (uint32_t)halo_w * a_px_step) {
                             uint32_t a_off = a_row;
                             for (int kx = 0; kx < s.kw; ++kx, a_off += a_px_step, b_off += b_tap_step) {
@@ -219,16 +243,28 @@ dense_umma_kernel(const __grid_constant__ KernelMaps maps, const __grid_constant
                             }
                         }
                     } else if (P.gather && P.gather_whole) {
-                        for (int g = 0; g < P.nkb; ++g) {
-                            const uint64_t adesc = make_smem_desc(sA + st * a_stage_bytes + (uint32_t)(g * kTileM * P.bkc), P.bkc);
-                            const uint64_t bdesc = make_smem_desc(sB + g * b_tile_bytes, P.bkc);
-                            for (int j = 0; j < P.bkc / 32; ++j) umma_i8(d, adesc + 2ull * j, bdesc + 2ull * j, P.idesc, (g | j) != 0 ? 1u : 0u);
-                        }
+                        // one stage holds all the K blocks of the tile; per block only the low words of the two descriptors move
+                        const uint64_t a0 = make_smem_desc(sA + st * a_stage_bytes, P.bkc), b0 = make_smem_desc(sB, P.bkc);
+                        const uint32_t a_lo = (uint32_t)a0, b_lo = (uint32_t)b0;
+                        const uint64_t a_hi = a0 & 0xFFFFFFFF00000000ull, b_hi = b0 & 0xFFFFFFFF00000000ull;
+                        const uint32_t a_step = (uint32_t)(kTileM * P.bkc) >> 4, b_step = b_tile_bytes >> 4;
+                        uint32_t ao = 0, bo = 0;
+                        for (int g = 0; g < P.nkb; ++g, ao += a_step, bo += b_step)
+                            for (int j = 0; j < P.bkc / 32; ++j)
+                                umma_i8(d, a_hi | (uint64_t)(a_lo + ao + 2u * j), b_hi | (uint64_t)(b_lo + bo + 2u * j), P.idesc, (g | j) != 0 ? 1u : 0u);
                     } else {
                         const uint64_t adesc = make_smem_desc(sA + st * a_stage_bytes, P.bkc);
                         const uint64_t bdesc = make_smem_desc(sB + kb * b_tile_bytes, P.bkc);
-                        for (int j = 0; j < P.bkc / 32; ++j)
-                            umma_i8(d, adesc + 2ull * j, bdesc + 2ull * j, P.idesc, (kb | j) != 0 ? 1u : 0u);
+                        const uint32_t a_lo = (uint32_t)adesc, b_lo = (uint32_t)bdesc;
+                        const uint64_t a_hi = adesc & 0xFFFFFFFF00000000ull, b_hi = bdesc & 0xFFFFFFFF00000000ull;
+                        auto steps = [&](auto n) {
+                            constexpr int J = decltype(n)::value;
+#pragma unroll
+                            for (int j = 0; j < J; ++j) umma_i8(d, a_hi | (uint64_t)(a_lo + 2u * j), b_hi | (uint64_t)(b_lo + 2u * j), P.idesc, (kb | j) != 0 ? 1u : 0u);
+                        };
+                        if (P.bkc == 128) steps(std::integral_constant<int, 4>{});
+                        else if (P.bkc == 64) steps(std::integral_constant<int, 2>{});
+                        else steps(std::integral_constant<int, 1>{});
                     }
                     umma_commit(bar_empty + 8u * st);  // frees the A stage once these MMAs have read it
                 }
