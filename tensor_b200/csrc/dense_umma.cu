@@ -41,7 +41,7 @@ namespace ottk {
 namespace {
 
 constexpr int kMaxEpiWarps = 8;                     // 2 per TMEM lane quarter
-constexpr int kMaxThreads = 64 + 32 * kMaxEpiWarps;  // UmmaPlan::epi_warps is 4 or 8
+constexpr int kMaxThreads = 64 + 32 * kMaxEpiWarps;  // UmmaPlan::epi_warps is 4 or 8 (16 in the wide-tile build)
 constexpr int kTileM = 128;
 constexpr int kMaxAccBufs = 4;
 constexpr int kHaloTw = 8, kHaloTh = 16;  // pixel tile of the halo mode: 8 wide so that a tile row is one 8-row operand group
@@ -72,10 +72,11 @@ __host__ __device__ inline SmemLayout smem_layout(const UmmaPlan& p) {
     return L;
 }
 
-// MULTI: compiled for two resident CTAs per SM (at most 102 registers per thread), which small layers need to hide latency;
+// BUILD 1: compiled for two resident CTAs per SM (at most 102 registers per thread), which small layers need to hide latency;
+// BUILD 2: 576 threads (sixteen epilogue warps) for wide tiles with one CTA per SM; BUILD 0: 320 threads, one CTA per SM;
 // the one-CTA-per-SM plans of large layers use the build without that register limit.
-template <int OUT, int ACT, bool BIAS, int ROUND, bool MULTI>
-__global__ void __launch_bounds__(kMaxThreads, MULTI ? 2 : 1)
+template <int OUT, int ACT, bool BIAS, int ROUND, int BUILD>
+__global__ void __launch_bounds__(BUILD == 2 ? 64 + 32 * 16 : kMaxThreads, BUILD == 1 ? 2 : 1)
 dense_umma_kernel(const __grid_constant__ KernelMaps maps, const __grid_constant__ CUtensorMap tmB, const UmmaPlan P,
                   const ConvShape s, const EpilogueParams ep, void* __restrict__ out, uint32_t* __restrict__ status,
                   const __grid_constant__ UmmaMixedOut mixed) {
@@ -460,7 +461,7 @@ CUtensorMapSwizzle swizzle_for(int bkc) {
     return bkc == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (bkc == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
 }
 
-template <int OUT, int ACT, bool BIAS, int ROUND, bool MULTI>
+template <int OUT, int ACT, bool BIAS, int ROUND, int BUILD>
 const char* launch_variant(cudaStream_t stream, int sm_count, const KernelMaps& maps, const CUtensorMap& tmB, const UmmaPlan& p,
                            const ConvShape& s, const EpilogueParams& ep, void* out, uint32_t* status, const UmmaMixedOut& mixed) {
     // per-device, per-instantiation set-up; several host threads may drive different GPUs through this function at once
@@ -469,7 +470,7 @@ const char* launch_variant(cudaStream_t stream, int sm_count, const KernelMaps& 
     static int regs_per_thread[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
-    auto kernel = dense_umma_kernel<OUT, ACT, BIAS, ROUND, MULTI>;
+    auto kernel = dense_umma_kernel<OUT, ACT, BIAS, ROUND, BUILD>;
     int regs = 128;
     if (dev >= 0 && dev < 64) {
         std::lock_guard<std::mutex> lock(mu);
@@ -559,13 +560,18 @@ bool umma_plan_layer(int cin, int cout, int kh, int kw, int sh, int sw, int dh, 
     // CTAs per SM: TMEM has 512 columns per SM and the hardware scheduler does not account for them, so the shared-memory
     // request is padded until no more CTAs fit an SM than TMEM can serve (a CTA that cannot get its columns would wait
     // inside tcgen05.alloc for a neighbour to finish).
-    // eight epilogue warps, two per TMEM lane quarter (sixteen were measured slower on the wide tiles)
+    // eight epilogue warps, two per TMEM lane quarter (sixteen for wide single-CTA tiles, below)
     p.epi_warps = 8;
     int by_tmem = 512 / p.tmem_cols;
     int by_smem = smem_budget / p.smem_bytes;
     p.ctas_per_sm = by_tmem < by_smem ? by_tmem : by_smem;
     if (p.ctas_per_sm > 4) p.ctas_per_sm = 4;
     if (p.ctas_per_sm < 1) p.ctas_per_sm = 1;
+    // Wide tiles with one CTA per SM: sixteen epilogue warps (four per lane quarter, 576 threads, the build without a register
+    // cap). Requantizing a 128 x 256 tile costs the CUDA cores as much as its MMAs cost the tensor pipe, and eight warps reach
+    // only two thirds of the SM's requantize rate (measured: 512 -> 1024: 1660 -> 1837 TOP/s; 256 -> 512: 881 -> 1025; with
+    // 128-column tiles it loses, 3x3 128 -> 128: 1938 -> 1865).
+    if (p.ctas_per_sm == 1 && p.bn > 128) p.epi_warps = 16;
     const int min_smem = smem_budget / (p.ctas_per_sm + 1) + 1;
     if (p.smem_bytes < min_smem) p.smem_bytes = min_smem;
     *plan = p;
@@ -670,8 +676,9 @@ const char* launch_dense_umma(cudaStream_t stream, int sm_count, const UmmaPlan&
     const CUtensorMap& tmB = *reinterpret_cast<const CUtensorMap*>(weight_map);
     const char* err = nullptr;
 #define OTT_UMMA_LAUNCH(OUT, ACT, BIAS, ROUND)                                                                       \
-    err = p.ctas_per_sm > 1 ? launch_variant<OUT, ACT, BIAS, ROUND, true>(stream, sm_count, km, tmB, p, s, ep, out, status, mixed) \
-                            : launch_variant<OUT, ACT, BIAS, ROUND, false>(stream, sm_count, km, tmB, p, s, ep, out, status, mixed)
+    err = p.ctas_per_sm > 1   ? launch_variant<OUT, ACT, BIAS, ROUND, 1>(stream, sm_count, km, tmB, p, s, ep, out, status, mixed) \
+          : p.epi_warps == 16 ? launch_variant<OUT, ACT, BIAS, ROUND, 2>(stream, sm_count, km, tmB, p, s, ep, out, status, mixed) \
+                              : launch_variant<OUT, ACT, BIAS, ROUND, 0>(stream, sm_count, km, tmB, p, s, ep, out, status, mixed)
 #define OTT_UMMA_ACT(OUT, BIAS, ROUND)                                   \
     switch (ep.act_type) {                                               \
         case ACT_RELU: OTT_UMMA_LAUNCH(OUT, ACT_RELU, BIAS, ROUND); break;   \
