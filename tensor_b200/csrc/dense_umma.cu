@@ -343,9 +343,16 @@ dense_umma_kernel(const __grid_constant__ KernelMaps maps, const __grid_constant
                     }
                 }
                 if (OUT == DT_F32_NCHW) {
+                    // one plane further per channel: a pointer that walks, and one bounds test per chunk where the chunk is whole
+                    float* o = out_f32 + (long)col0 * plane;
+                    if (c0 + 16 <= s.cout) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        if (c0 + j < s.cout) out_f32[(long)(col0 + j) * plane] = y[j];
+                        for (int j = 0; j < 16; ++j, o += plane) *o = y[j];
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j, o += plane)
+                            if (c0 + j < s.cout) *o = y[j];
+                    }
                 } else {
                     if (out_f32 != nullptr) {
                         // channels that some reader wants in fp32: the planes an fp32-output layer would have written

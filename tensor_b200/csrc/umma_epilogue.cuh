@@ -98,9 +98,15 @@ __device__ __forceinline__ void store_accumulator_row(uint32_t taddr, int ncols,
                 }
             }
             if (OUT == DT_F32_NCHW) {
+                float* o = out_f32 + (long)(c_base + cc) * plane;
+                if (c_base + cc + 16 <= cout) {
 #pragma unroll
-                for (int j = 0; j < 16; ++j)
-                    if (c_base + cc + j < cout) out_f32[(long)(c_base + cc + j) * plane] = y[j];
+                    for (int j = 0; j < 16; ++j, o += plane) *o = y[j];
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j, o += plane)
+                        if (c_base + cc + j < cout) *o = y[j];
+                }
                 continue;
             }
             if (out_f32 != nullptr) {
