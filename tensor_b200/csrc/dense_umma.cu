@@ -310,7 +310,16 @@ dense_umma_kernel(const __grid_constant__ KernelMaps maps, const __grid_constant
             int32_t* out_s32 = reinterpret_cast<int32_t*>(out) + pix * s.cout_pad + n_tile * P.bn;
             float* out_f32 = nullptr;
             if (OUT == DT_F32_NCHW || (OUT == DT_S8_NHWC && mixed.out_f32 != nullptr)) {
-                const long img = pix / plane, inimg = pix - img * plane;
+                // (a 64-bit division costs about a hundred instructions per thread and tile; 32 bits cover any real tensor)
+                long img, inimg;
+                if (total_pix <= 0xFFFFFFFFll) {
+                    const uint32_t q32 = (uint32_t)pix / (uint32_t)plane;
+                    img = (long)q32;
+                    inimg = (long)((uint32_t)pix - q32 * (uint32_t)plane);
+                } else {
+                    img = pix / plane;
+                    inimg = pix - img * plane;
+                }
                 if (OUT == DT_S8_NHWC && mixed.plane_of_col != nullptr)
                     out_f32 = mixed.out_f32 + img * mixed.f32_planes * plane + inimg;  // plane chosen per column below
                 else
