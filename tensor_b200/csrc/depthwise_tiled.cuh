@@ -76,6 +76,32 @@ __device__ __forceinline__ int epi_s8(int acc, float si, float bi, float so, int
     return f2i8_lo_clamped(t);
 }
 
+// Four accumulators of one channel -> four int8 in one word, the arithmetic as packed pairs (each lane rounds like epi_s8).
+template <int EPI, int ACT>
+__device__ __forceinline__ uint32_t epi_s8x4(const int (&acc)[4], float si, float bi, float so, int has_bias, float p0) {
+    if (EPI == EPI_S8_HALF_AWAY)
+        return pack_sat_s8x4(epi_s8<EPI, ACT>(acc[0], si, bi, so, has_bias, p0), epi_s8<EPI, ACT>(acc[1], si, bi, so, has_bias, p0),
+                             epi_s8<EPI, ACT>(acc[2], si, bi, so, has_bias, p0), epi_s8<EPI, ACT>(acc[3], si, bi, so, has_bias, p0));
+    const float2 s2 = make_float2(si, si), b2 = make_float2(bi, bi), o2 = make_float2(so, so);
+    int q[4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const float2 a = make_float2(__int2float_rn(acc[2 * h]), __int2float_rn(acc[2 * h + 1]));
+        const float2 v = has_bias ? __ffma2_rn(a, s2, b2) : __fmul2_rn(a, s2);
+        const float2 t = __fmul2_rn(make_float2(activate_t<ACT>(v.x, p0), activate_t<ACT>(v.y, p0)), o2);
+        if (ACT == ACT_RELU || ACT == ACT_RELU6) {
+            const float2 r = __fadd2_rn(t, make_float2(0.5f, 0.5f));
+            q[2 * h] = __float2int_rz(r.x);
+            q[2 * h + 1] = __float2int_rz(r.y);
+        } else {
+            const float2 r = __fadd2_rn(t, make_float2(half_signed(t.x), half_signed(t.y)));
+            q[2 * h] = __float2int_rz(fmaxf(r.x, -127.5f));
+            q[2 * h + 1] = __float2int_rz(fmaxf(r.y, -127.5f));
+        }
+    }
+    return pack_sat_s8x4(q[0], q[1], q[2], q[3]);
+}
+
 // One output row for the thread. R = (output row index) % K selects, at compile time, which ring slots hold
 // the K input rows: input row r lives in slot r % K, and output row oy needs rows oy*S + ky.
 template <int K, int S, int EPI, int ACT, int R>
@@ -96,10 +122,7 @@ __device__ __forceinline__ void row_step(int oy, const uint32_t* __restrict__ pl
 #pragma unroll
             for (int t = 0; t < 4; ++t) acc[t] = __dp4a((int)win[(base + ky) % K][t][kk], (int)wk[ky][kk], acc[t]);
     if (EPI != EPI_F32) {
-        int q[4];
-#pragma unroll
-        for (int t = 0; t < 4; ++t) q[t] = epi_s8<EPI, ACT>(acc[t], si, bi, so, ep.has_bias, ep.act_param0);
-        oplane_s[oy * T.orp + xq] = pack_sat_s8x4(q[0], q[1], q[2], q[3]);
+        oplane_s[oy * T.orp + xq] = epi_s8x4<EPI, ACT>(acc, si, bi, so, ep.has_bias, ep.act_param0);
     } else if (of32) {
         float v[4];
 #pragma unroll
