@@ -702,6 +702,38 @@ KERNEL_RECORD_WORKLOADS = ("pw_512_1024_hw56_s8", "pw_256_512_hw56_s8", "pw_64_2
                            "dw3x3s2_c256", "dw3x3s1_c256_s8", "dw3x3s2_c256_s8")
 
 
+def detect_record(ctx, graph, outputs, images, height, reps=3):
+    """The detector's decode step (NanodetPlusDetectionOutput: proposals, sort, NMS; ott_nanodet_detect) on the head blobs one
+    replayed chunk left on the device, timed by itself with the host clock (the call ends with the rows on the host). It is
+    not part of the timed step: the reference's layer decodes one image, and the benchmark's outputs are the heads."""
+    strides = [8, 16, 32, 64][:len(outputs)]
+    ptrs, grids = [], []
+    for i in range(len(outputs)):
+        dptr, shp = graph.output(i)
+        ptrs.append(dptr)
+        grids.append(int(shp[2]))
+        num_class = int(shp[1]) - 32
+    arr = (C.c_void_p * len(ptrs))(*ptrs)
+    gh = np.array(grids, np.int32)
+    st = np.array(strides, np.int32)
+    cells = int((gh.astype(np.int64) ** 2).sum())
+    rows = np.zeros((images, cells, 6), np.float32)
+    counts = np.zeros(images, np.int32)
+
+    def run():
+        ctx.check(ctx.lib.ott_nanodet_detect(ctx.h, arr, gh.ctypes.data, gh.ctypes.data, st.ctypes.data, len(ptrs), images, num_class, 8,
+                                             C.c_float(0.4), C.c_float(0.5), rows.ctypes.data, counts.ctypes.data, cells))
+    run()
+    ctx.sync()
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        run()
+    dt = (time.perf_counter() - t0) / reps
+    return {"ms_per_chunk": dt * 1e3, "images": images, "images_per_s": images / dt, "detections": int(counts.sum()),
+            "what": "ott_nanodet_detect on the heads of one chunk: proposals, per-image sort and NMS on the GPU, one copy of the rows to the host; "
+                    "host clock; not included in the timed step"}
+
+
 def run_net_gpu_arm(args, cfg):
     from tensor_b200 import graphs, library
     library()
@@ -970,6 +1002,9 @@ def run_net_gpu_arm(args, cfg):
         traffic_file = ROOT / "profiles" / "traffic.json"
         if traffic_file.exists():
             roof["traffic"] = json.loads(traffic_file.read_text()).get(args.workload)
+        decode = None
+        if cfg["graph"] == "nanodet_plus" and chunk_graphs:
+            decode = detect_record(ctx, chunk_graphs[0], outputs, chunks[0][1], H)
         cpu = None
         if not args.no_cpu:
             per_img, how, cores, kind = net_cpu_reference_time(graph_layers(cfg), H, W, reps=3)
@@ -994,6 +1029,7 @@ def run_net_gpu_arm(args, cfg):
             "roofline": roof, "cpu_baseline": cpu,
             "int8_peak": None if int8_peak is None else {"tops": int8_peak, "how": "torch._int_mm 8192^3 int8 (cuBLASLt), best of 10, CUDA events, same process"},
             "kernels": kernels,
+            **({"decode": decode} if decode else {}),
         }))
     for g in chunk_graphs or []:
         g.close()

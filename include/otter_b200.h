@@ -343,8 +343,9 @@ int ott_graph_destroy(ott_ctx* ctx, ott_graph* graph);
 
 /* NanodetPlusDetectionOutputLayer::forward (Tensor/NanodetPlusDetectionOutputLayer.cpp:65-260) for a batch: heads_dev[l] is the
  * fp32 NCHW output [n][num_class + 4*reg_bins][grid_h[l]][grid_w[l]] of pyramid level l on the device. Per image: best class
- * logit per cell, sigmoid >= prob_threshold, softmax over the reg_bins distance bins of each box side, box (on the GPU);
- * sort by score and greedy NMS (on the host, over the proposals that passed). out_host receives, per image, up to max_det
+ * logit per cell, sigmoid >= prob_threshold, softmax over the reg_bins distance bins of each box side, box; then sort by
+ * score and greedy NMS, one CTA per image, all on the GPU (an image with more than 4096 proposals is sorted and filtered on
+ * the host); one copy brings every image's rows back. out_host receives, per image, up to max_det
  * rows {label + 1, score, x, y, width, height} at out_host + img*max_det*6; counts_host[img] the number of detections kept
  * (which may exceed max_det). The reference decodes image 0 only; scores agree with it to 1-2 ulp and boxes to ~1e-4 pixels
  * (its -Ofast build and the GPU round expf and the divisions differently). Synchronises the stream. */

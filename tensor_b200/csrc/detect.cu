@@ -1,13 +1,16 @@
 // Detection decode of the NanoDet-Plus head: NanodetPlusDetectionOutputLayer (Tensor/NanodetPlusDetectionOutputLayer.cpp:65-260).
 // The per-cell work of generate_proposals (:111-190) — best class logit, sigmoid, threshold, softmax over the distance bins
 // of the four box sides, box — runs on the GPU for every image and pyramid level; the proposals that pass the threshold
-// are compacted per image with an atomic counter. Sorting by score and the greedy NMS (:208-243) see only those few rows and
-// run on the host, per image, with the reference's formulas.
+// are compacted per image with an atomic counter. Sorting by score and the greedy NMS (:208-243) run on the GPU as well, one
+// CTA per image (bitonic sort of the image's proposals in shared memory, then the greedy pass as "every kept box strikes the
+// later boxes it overlaps"), with the reference's formulas in the reference's operand order; one copy brings all images'
+// rows back. An image with more proposals than the CTA's shared memory holds (4096) is sorted and filtered on the host.
 // Floating point: expf/division here and in the reference's -Ofast build round differently in the last place, so scores
 // agree to 1-2 ulp and box coordinates to about 1e-4 pixels; labels, order and counts are the same unless a score sits
 // within that distance of the threshold or of another score.
 #include <algorithm>
 #include <cfloat>
+#include <mutex>
 #include <vector>
 
 #include "ctx.h"
@@ -61,12 +64,89 @@ __global__ void nanodet_proposals_kernel(const float* __restrict__ pred, int n, 
     props[(long)img * capacity + slot] = q;
 }
 
-float intersection(const Proposal& a, const Proposal& b) {
+__host__ __device__ inline float intersection(const Proposal& a, const Proposal& b) {
     const float axmax = a.x + a.w, aymax = a.y + a.h, bxmax = b.x + b.w, bymax = b.y + b.h;
     if (a.x > bxmax || axmax < b.x || a.y > bymax || aymax < b.y) return 0.f;
-    const float iw = std::min(axmax, bxmax) - std::max(a.x, b.x);
-    const float ih = std::min(aymax, bymax) - std::max(a.y, b.y);
+    const float iw = fminf(axmax, bxmax) - fmaxf(a.x, b.x);
+    const float ih = fminf(aymax, bymax) - fmaxf(a.y, b.y);
     return iw * ih;
+}
+
+constexpr int kNmsThreads = 256, kNmsMaxProposals = 4096;
+
+// One CTA per image. slots = power of two >= the image's proposal count (at most kNmsMaxProposals). Shared memory: the sort
+// keys (score bits, then ~order: scores are positive, so their bit patterns order like the values), the proposal index
+// behind each key, the sorted boxes, and one "struck" flag per box.
+__global__ void __launch_bounds__(kNmsThreads)
+nanodet_nms_kernel(const Proposal* __restrict__ props, const int* __restrict__ counts, int capacity, int slots, float nms_threshold, int max_det,
+                   float* __restrict__ out, int* __restrict__ out_counts) {
+    extern __shared__ unsigned long long nms_smem[];
+    unsigned long long* key = nms_smem;
+    int* idx = reinterpret_cast<int*>(key + slots);
+    Proposal* box = reinterpret_cast<Proposal*>(idx + slots);
+    unsigned char* struck = reinterpret_cast<unsigned char*>(box + slots);
+    const int img = blockIdx.x;
+    const int c = counts[img] < capacity ? counts[img] : capacity;
+    if (c > slots) {  // more than this launch was sized for: the caller finishes this image on the host
+        if (threadIdx.x == 0) out_counts[img] = -1;
+        return;
+    }
+    const Proposal* mine = props + (long)img * capacity;
+    int used = 32;  // the sort runs over the power of two that holds this image's proposals, not over the launch's maximum
+    while (used < c) used <<= 1;
+    slots = used;
+    for (int i = threadIdx.x; i < slots; i += kNmsThreads) {
+        if (i < c) {
+            key[i] = ((unsigned long long)__float_as_uint(mine[i].score) << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned)mine[i].order);
+            idx[i] = i;
+        } else {
+            key[i] = 0ull;  // below every real key (a proposal's score passed a positive threshold)
+            idx[i] = -1;
+        }
+    }
+    __syncthreads();
+    // bitonic sort, descending
+    for (int k = 2; k <= slots; k <<= 1)
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            for (int i = threadIdx.x; i < slots; i += kNmsThreads) {
+                const int l = i ^ j;
+                if (l > i) {
+                    const bool desc = (i & k) == 0;
+                    const unsigned long long a = key[i], b = key[l];
+                    if (desc ? a < b : a > b) {
+                        key[i] = b; key[l] = a;
+                        const int t = idx[i]; idx[i] = idx[l]; idx[l] = t;
+                    }
+                }
+            }
+            __syncthreads();
+        }
+    for (int i = threadIdx.x; i < c; i += kNmsThreads) {
+        box[i] = mine[idx[i]];
+        struck[i] = 0;
+    }
+    __syncthreads();
+    // greedy NMS (:208-243): box i is kept unless an earlier kept box overlaps it by more than the threshold
+    int kept = 0;
+    float* o = out + (long)img * max_det * 6;
+    for (int i = 0; i < c; ++i) {
+        if (struck[i]) continue;  // block-uniform: every thread reads the same flag after the barrier below
+        const Proposal a = box[i];
+        if (threadIdx.x == 0 && kept < max_det) {
+            o[6 * kept + 0] = a.label; o[6 * kept + 1] = a.score; o[6 * kept + 2] = a.x; o[6 * kept + 3] = a.y; o[6 * kept + 4] = a.w; o[6 * kept + 5] = a.h;
+        }
+        ++kept;
+        const float area_a = a.w * a.h;
+        for (int j = i + 1 + (int)threadIdx.x; j < c; j += kNmsThreads) {
+            if (struck[j]) continue;
+            const Proposal b = box[j];
+            const float inter = intersection(b, a);
+            const float uni = __fsub_rn(__fadd_rn(__fmul_rn(b.w, b.h), area_a), inter);
+            if (__fdiv_rn(inter, uni) > nms_threshold) struck[j] = 1;
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) out_counts[img] = kept;
 }
 
 }  // namespace
@@ -104,13 +184,37 @@ extern "C" int ott_nanodet_detect(ott_ctx* ctx, const float* const* heads_dev, c
         ctx->launches += 1;
         order_base += grid_h[l] * grid_w[l];
     }
-    std::vector<int> cnt((size_t)n);
-    OTT_CUDA_CHECK(ctx, cudaMemcpyAsync(cnt.data(), counts.p, (size_t)n * sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    // sort + NMS per image on the GPU, rows and counts back in one go
+    int slots = 32;
+    while (slots < capacity && slots < kNmsMaxProposals) slots <<= 1;
+    const size_t nms_smem = (size_t)slots * (sizeof(unsigned long long) + sizeof(int) + sizeof(Proposal) + 1);
+    DeviceBlock rows_dev, kept_dev;
+    if (rows_dev.alloc(ctx, (size_t)n * (max_det > 0 ? max_det : 1) * 6 * sizeof(float)) != cudaSuccess || kept_dev.alloc(ctx, (size_t)n * sizeof(int)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return ctx->fail(OTT_ERR_ALLOC, "device allocation for the detections failed");
+    }
+    {
+        static std::mutex mu;  // several host threads may drive different GPUs through this function at once
+        std::lock_guard<std::mutex> lock(mu);
+        OTT_CUDA_CHECK(ctx, cudaFuncSetAttribute(nanodet_nms_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(kNmsMaxProposals * (8 + 4 + sizeof(Proposal) + 1))));
+    }
+    nanodet_nms_kernel<<<(unsigned)n, kNmsThreads, nms_smem, ctx->stream>>>(static_cast<const Proposal*>(props.p), static_cast<const int*>(counts.p), capacity, slots,
+                                                                          nms_threshold, max_det, static_cast<float*>(rows_dev.p), static_cast<int*>(kept_dev.p));
+    OTT_CUDA_CHECK(ctx, cudaGetLastError());
+    ctx->launches += 1;
+    OTT_CUDA_CHECK(ctx, cudaMemcpyAsync(counts_host, kept_dev.p, (size_t)n * sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    if (max_det > 0)
+        OTT_CUDA_CHECK(ctx, cudaMemcpyAsync(out_host, rows_dev.p, (size_t)n * max_det * 6 * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
     OTT_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+    // images whose proposals did not fit the CTA's shared memory (count marked -1): same steps on the host
     std::vector<Proposal> host;
     std::vector<int> picked;
     for (int img = 0; img < n; ++img) {
-        const int c = std::min(cnt[(size_t)img], capacity);
+        if (counts_host[img] >= 0) continue;
+        int c = 0;
+        OTT_CUDA_CHECK(ctx, cudaMemcpyAsync(&c, static_cast<int*>(counts.p) + img, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+        OTT_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+        c = std::min(c, capacity);
         host.resize((size_t)c);
         if (c > 0) {
             OTT_CUDA_CHECK(ctx, cudaMemcpyAsync(host.data(), static_cast<Proposal*>(props.p) + (long)img * capacity, (size_t)c * sizeof(Proposal),

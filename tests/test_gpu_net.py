@@ -332,6 +332,37 @@ def test_detection_decode_kernel_batch():
             ctx.free(p)
 
 
+def test_detection_decode_many_proposals_per_image():
+    """One image whose proposals (6400: every cell of an 80x80 level passes the threshold) exceed what the per-image sort /
+    NMS kernel holds in shared memory, next to one with a handful: the first is finished on the host, the second on the GPU,
+    both equal the checker."""
+    import ctypes as C
+    from graph_support import assert_same_detections, oracle_detect
+    from tensor_b200 import Context
+    rng = np.random.default_rng(78)
+    n, grids, strides = 2, (80,), [8]
+    head = (rng.normal(size=(n, 112, 80, 80)) * 2.0).astype(np.float32)
+    head[0, :80] += 3.0   # image 0: every cell's best class logit is well above the threshold
+    head[1, :80] -= 7.0   # image 1: hardly any
+    with Context(0) as ctx:
+        p = ctx.malloc(head.nbytes)
+        ctx.check(ctx.lib.ott_memcpy_h2d(ctx.h, C.c_void_p(p), head.ctypes.data, head.nbytes))
+        ptrs = (C.c_void_p * 1)(p)
+        gh = np.array(grids, np.int32)
+        st = np.array(strides, np.int32)
+        max_det = 6400
+        out = np.zeros((n, max_det, 6), np.float32)
+        counts = np.zeros(n, np.int32)
+        ctx.check(ctx.lib.ott_nanodet_detect(ctx.h, ptrs, gh.ctypes.data, gh.ctypes.data, st.ctypes.data, 1, n, 80, 8, 0.4, 0.5,
+                                             out.ctypes.data, counts.ctypes.data, max_det))
+        for img in range(n):
+            want = oracle_detect([head], strides, image=img)
+            assert counts[img] == want.shape[0], (img, counts[img], want.shape)
+            assert_same_detections(out[img, :counts[img]], want)
+        assert counts[0] > 10 and counts[1] > 0, counts
+        ctx.free(p)
+
+
 def test_detector_with_decode_layer_from_files(tmp_path):
     """The whole detector including the NanodetPlusDetectionOutput layer, graph and weights from files; the detections against
     the reference's own decode of the reference's own head blobs (frozen)."""
