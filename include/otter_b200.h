@@ -93,6 +93,13 @@ int ott_set_depthwise_tensor_cores(ott_ctx* ctx, int mode);
  * (cudaErrorMemoryAllocation without calling cudaMalloc); n <= 0 switches the injection off. */
 int ott_debug_wait_probe(ott_ctx* ctx);
 int ott_debug_fail_alloc_after(ott_ctx* ctx, int n);
+/* Guard bands, the tests' stand-in for a device memory checker: after ott_debug_guard_bands(ctx, bytes) every block the
+ * context's allocator obtains from the driver carries `bytes` (rounded up to 512) of a fill pattern on both sides;
+ * ott_debug_check_guards synchronizes the stream, reads every band of every block (in use or cached) back and returns
+ * OTT_ERR_CUDA with *bad_blocks > 0 if a kernel wrote outside a block. Call the first before anything is allocated; the
+ * environment variable OTT_DEBUG_GUARD_BYTES=<bytes> does the same for every context created afterwards (the GPU tests set it). */
+int ott_debug_guard_bands(ott_ctx* ctx, size_t bytes);
+int ott_debug_check_guards(ott_ctx* ctx, long* bad_blocks);
 /* Measurement hook: cycles one tcgen05.mma kind::i8 (M = 128, K = 32, N = n_cols) occupies an SM when issuing_warps x
  * issuing_lanes threads of each of ctas_per_sm CTAs per SM issue `reps` of them back to back (zero operands; the design notes
  * argue tile shapes from these numbers: 128 / 64 / 48 / 40 cycles at N = 256 / 128 / 64 / 32, one issuing thread alone 56). */

@@ -3,6 +3,7 @@ convenience classes used by the tests and the benchmark)."""
 from __future__ import annotations
 
 import ctypes as C
+import os
 from pathlib import Path
 
 import numpy as np
@@ -40,6 +41,8 @@ SIGNATURES = {
     "ott_debug_mma_rate": (i32, [vp, i32, i32, i32, i32, i32, C.POINTER(C.c_float)]),
     "ott_set_depthwise_tensor_cores": (i32, [vp, i32]),
     "ott_debug_fail_alloc_after": (i32, [vp, i32]),
+    "ott_debug_guard_bands": (i32, [vp, C.c_size_t]),
+    "ott_debug_check_guards": (i32, [vp, C.POINTER(C.c_long)]),
     "ott_malloc": (i32, [vp, sz, C.POINTER(vp)]),
     "ott_free": (i32, [vp, vp]),
     "ott_alloc_stats": (i32, [vp, u64p, u64p, u64p, u64p]),
@@ -184,10 +187,22 @@ class Context:
         if rc != 0:
             raise OtterB200Error(rc, self.lib.ott_last_error(self.h).decode(errors="replace"))
 
+    def check_guards(self):
+        """With guard bands on (OTT_DEBUG_GUARD_BYTES, ott_debug_guard_bands): raises if a kernel wrote outside a device block."""
+        bad = C.c_long(0)
+        self.check(self.lib.ott_debug_check_guards(self.h, C.byref(bad)))
+
     def close(self):
         if self.h:
-            self.lib.ott_ctx_destroy(self.h)
-            self.h = None
+            h, self.h = self.h, None
+            try:
+                if os.environ.get("OTT_DEBUG_GUARD_BYTES"):
+                    bad = C.c_long(0)
+                    rc = self.lib.ott_debug_check_guards(h, C.byref(bad))
+                    if rc != 0:
+                        raise OtterB200Error(rc, self.lib.ott_last_error(h).decode(errors="replace"))
+            finally:
+                self.lib.ott_ctx_destroy(h)
 
     def __enter__(self):
         return self
@@ -612,7 +627,16 @@ class Net:
 
     def close(self):
         if self.h and self.owned:
-            self.lib.ott_net_destroy(self.h)
+            h, self.h = self.h, None
+            try:
+                if os.environ.get("OTT_DEBUG_GUARD_BYTES"):
+                    ctx = self.lib.ott_net_context(h)
+                    bad = C.c_long(0)
+                    rc = self.lib.ott_debug_check_guards(C.c_void_p(ctx), C.byref(bad)) if ctx else 0
+                    if rc != 0:
+                        raise OtterB200Error(rc, self.lib.ott_last_error(C.c_void_p(ctx)).decode(errors="replace"))
+            finally:
+                self.lib.ott_net_destroy(h)
         self.h = None
 
 

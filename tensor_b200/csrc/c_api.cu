@@ -2,6 +2,7 @@
 // ConvolutionLayer's create_pipeline_int8 / forward_int8 (Tensor/ConvolutionLayer.cpp:666-752, :754-847)
 // mapped onto the CUDA kernels. No CPU compute path exists here: every forward launches kernels.
 #include <algorithm>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <vector>
@@ -86,6 +87,10 @@ int ott_ctx_create(int device, ott_ctx** out) {
         return OTT_ERR_CUDA;
     }
     ctx->alloc = new DeviceCachingAllocator(device);
+    if (const char* g = std::getenv("OTT_DEBUG_GUARD_BYTES")) {  // the tests' guard bands for every context, also those a Net makes
+        const long v = std::atol(g);
+        if (v > 0) ctx->alloc->set_guard((size_t)v);
+    }
     if (cudaMalloc((void**)&ctx->status_dev, sizeof(uint32_t)) != cudaSuccess ||
         cudaMallocHost((void**)&ctx->status_host, sizeof(uint32_t)) != cudaSuccess) {
         ott_ctx_destroy(ctx);
@@ -139,6 +144,22 @@ int ott_set_depthwise_tensor_cores(ott_ctx* ctx, int on) {
 int ott_debug_fail_alloc_after(ott_ctx* ctx, int n) {
     if (!ctx) return OTT_ERR_INVALID;
     ctx->alloc->fail_after(n);
+    return OTT_OK;
+}
+
+int ott_debug_guard_bands(ott_ctx* ctx, size_t bytes) {
+    if (!ctx) return OTT_ERR_INVALID;
+    ctx->alloc->set_guard(bytes);
+    return OTT_OK;
+}
+
+int ott_debug_check_guards(ott_ctx* ctx, long* bad_blocks) {
+    if (!ctx || !bad_blocks) return OTT_ERR_INVALID;
+    cudaSetDevice(ctx->device);
+    OTT_CUDA_CHECK(ctx, cudaStreamSynchronize(ctx->stream));
+    size_t first = 0;
+    OTT_CUDA_CHECK(ctx, ctx->alloc->check_guards(bad_blocks, &first));
+    if (*bad_blocks != 0) return ctx->fail(OTT_ERR_CUDA, "%ld device block(s) written outside their bounds (first: a block of %zu bytes)", *bad_blocks, first);
     return OTT_OK;
 }
 

@@ -37,6 +37,32 @@ public:
         fail_countdown_ = n;
     }
 
+    // Guard bands for tests (the memory checker this pool does not offer): every block obtained from the driver from now on is
+    // `bytes` (a multiple of 512) larger on both sides, the bands hold kGuardByte, and check_guards reads every band of every
+    // block, in use or cached, back and counts the blocks a kernel has written outside of. 0 switches it off for new blocks.
+    static constexpr int kGuardByte = 0xC5;
+    void set_guard(size_t bytes) {
+        std::lock_guard<std::mutex> g(mu_);
+        guard_ = (bytes + 511) & ~size_t(511);
+    }
+    cudaError_t check_guards(long* bad_blocks, size_t* first_bad_size) {
+        std::lock_guard<std::mutex> g(mu_);
+        *bad_blocks = 0;
+        std::vector<unsigned char> host;
+        for (const auto& kv : guards_) {
+            const size_t gb = kv.second, sz = sizes_.at(kv.first);
+            host.resize(2 * gb);
+            char* user = static_cast<char*>(kv.first);
+            cudaError_t e = cudaMemcpy(host.data(), user - gb, gb, cudaMemcpyDeviceToHost);
+            if (e == cudaSuccess) e = cudaMemcpy(host.data() + gb, user + sz, gb, cudaMemcpyDeviceToHost);
+            if (e != cudaSuccess) return e;
+            bool ok = true;
+            for (size_t i = 0; i < 2 * gb && ok; ++i) ok = host[i] == kGuardByte;
+            if (!ok && (*bad_blocks)++ == 0 && first_bad_size) *first_bad_size = sz;
+        }
+        return cudaSuccess;
+    }
+
     cudaError_t allocate(size_t bytes, void** out) {
         const size_t sz = round_size(bytes);
         std::lock_guard<std::mutex> g(mu_);
@@ -52,13 +78,24 @@ public:
             return cudaSuccess;
         }
         void* p = nullptr;
-        cudaError_t e = cudaMalloc(&p, sz);
+        const size_t gb = guard_;
+        cudaError_t e = cudaMalloc(&p, sz + 2 * gb);
         if (e != cudaSuccess) {
             // give cached blocks back to the driver and retry once
             (void)cudaGetLastError();
             release_cached_locked();
-            e = cudaMalloc(&p, sz);
+            e = cudaMalloc(&p, sz + 2 * gb);
             if (e != cudaSuccess) return e;
+        }
+        if (gb != 0) {
+            e = cudaMemset(p, kGuardByte, gb);
+            if (e == cudaSuccess) e = cudaMemset(static_cast<char*>(p) + gb + sz, kGuardByte, gb);
+            if (e != cudaSuccess) {
+                cudaFree(p);
+                return e;
+            }
+            p = static_cast<char*>(p) + gb;
+            guards_[p] = gb;
         }
         ++n_device_mallocs_;
         sizes_[p] = sz;
@@ -130,7 +167,9 @@ private:
     void release_cached_locked() {
         for (auto& kv : available_) {
             for (void* p : kv.second) {
-                cudaFree(p);
+                auto gi = guards_.find(p);
+                cudaFree(gi == guards_.end() ? p : static_cast<void*>(static_cast<char*>(p) - gi->second));
+                if (gi != guards_.end()) guards_.erase(gi);
                 sizes_.erase(p);
             }
             kv.second.clear();
@@ -142,6 +181,8 @@ private:
     std::mutex mu_;
     std::map<size_t, std::vector<void*>> available_;
     std::unordered_map<void*, size_t> sizes_;
+    std::unordered_map<void*, size_t> guards_;  // blocks with guard bands: user pointer -> band size
+    size_t guard_ = 0;
     bool logging_ = false;
     long fail_countdown_ = 0;
     std::unordered_set<void*> log_;
