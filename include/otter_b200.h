@@ -82,7 +82,7 @@ int ott_sync(ott_ctx* ctx);
 int ott_set_wait_limit_ms(ott_ctx* ctx, int ms);
 /* Depthwise 3x3 layers (stride 1 / 2, pad 1) whose input is int8 NHWC can run on the tensor cores (each filter tap one
  * tcgen05.mma against a diagonal weight matrix, so the channel-innermost layout needs no byte transposes). mode 1 (default):
- * where that is faster (layers of at most 64 channels, and wider stride-1 layers on maps of 2048 pixels or more: every tap
+ * where that is faster (layers of at most 64 channels, and wider layers on input maps of 2048 pixels or more: every tap
  * costs one 128-row MMA per 32 channels, which small wide layers lose against the CUDA-core kernel); 0: none; 2: every layer
  * the kernel supports. Same bits in every mode. */
 int ott_set_depthwise_tensor_cores(ott_ctx* ctx, int mode);

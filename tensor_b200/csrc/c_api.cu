@@ -767,7 +767,7 @@ const char* ott_conv_int8_kernel_name(const ott_ctx* ctx, const ott_conv* c, int
     if (c->kind == OTT_KERNEL_DENSE_UMMA) return "dense_umma_kernel";
     if (c->kind == OTT_KERNEL_DENSE_DIRECT) return dense_stem_supports(s, in_dtype, out_dtype) ? "dense_stem_kernel" : "dense_direct_kernel";
     const bool gathered = !c->src_channels.empty();
-    const bool tc_wins = c->dw_plan.ncb_total <= 2 || (d.sh == 1 && (long)s.oh * s.ow >= 2048);
+    const bool tc_wins = c->dw_plan.ncb_total <= 2 || (long)s.h * s.w >= 2048;
     if (c->dw_umma && (ctx->dw_tensor_cores == 2 || (ctx->dw_tensor_cores == 1 && tc_wins)) && !gathered && in_dtype == OTT_S8_NHWC && out_dtype != OTT_S32_NHWC)
         return "dw_umma_kernel";
     if (c->w_tiled_dev && depthwise_tiled_supports(s, out_dtype)) return "depthwise_tiled_kernel";
@@ -1009,10 +1009,11 @@ int conv_forward_impl(ott_ctx* ctx, const ott_conv* c, const void* in_dev, const
         in_dev = sources[0];
     }
     // int8 NHWC input: the multiply-adds can go to the tensor cores as the data lies, no byte transposes. Every tap costs one
-    // 128-row MMA (about 100 cycles) per 32 channels and 8 x 16 pixel tile, so this wins for narrow layers (at most 64
-    // channels) and for wide stride-1 layers on maps large enough for the tiles to fit well; elsewhere the CUDA cores do.
+    // 128-row MMA per 32 channels and 8 x 16 pixel tile, so this wins for narrow layers (at most 64 channels) and for wide
+    // layers on input maps large enough for the tiles to fit well (256 channels, 56 x 56, 64 images: stride 1 41.8 us against
+    // 49.1, stride 2 16.3 against 22.2; 116 channels on 20 x 20 lose, 18.5 against 13.6 and 10.5 against 9.2); elsewhere the CUDA cores do.
     // A layer with gathered input that was laid out in 32-channel groups always runs here (its groups are the MMA's K blocks).
-    const bool dw_tc_wins = c->dw_plan.ncb_total <= 2 || (d.sh == 1 && (long)s.oh * s.ow >= 2048);
+    const bool dw_tc_wins = c->dw_plan.ncb_total <= 2 || (long)s.h * s.w >= 2048;
     const bool dw_gathered_tc = gathered && c->kind == OTT_KERNEL_DEPTHWISE && c->gather_group == 32;
     if (c->kind == OTT_KERNEL_DEPTHWISE && c->dw_umma && in_dtype == OTT_S8_NHWC && out_dtype != OTT_S32_NHWC &&
         (dw_gathered_tc || (!gathered && (ctx->dw_tensor_cores == 2 || (ctx->dw_tensor_cores == 1 && dw_tc_wins))))) {
