@@ -100,3 +100,36 @@ def test_argument_errors_are_reported(ctx):
     with pytest.raises(OtterB200Error):  # int8 output from a layer without top_blob_int8_scales
         layer.forward_host(np.zeros((1, 8, 4, 4), np.float32), F32_NCHW, S8_NHWC)
     layer.close()
+
+
+@pytest.mark.parametrize("name,kw", [
+    ("pw", dict(cin=64, cout=64, k=1, int8_scale_term=101, act_type=1)),
+    ("dense3x3", dict(cin=64, cout=64, k=3, pad=1, int8_scale_term=2)),
+    ("dw_f32in", dict(cin=32, cout=32, k=3, pad=1, groups=32, int8_scale_term=101, w_std=0.1)),
+    ("dw_s8in", dict(cin=58, cout=58, k=3, pad=1, groups=58, int8_scale_term=101, w_std=0.1, s8_input=True)),
+    ("stem", dict(cin=3, cout=24, k=3, stride=2, pad=1, int8_scale_term=2, act_type=1, x_lo=0.0)),
+])
+def test_empty_batch_and_single_pixel(ctx, name, kw):
+    """Edges of the batch and map sizes: a call with zero images succeeds and launches nothing (the output buffer is not
+    touched); a 1 x 1 map (all padding around one pixel) equals the CPU checker."""
+    from gpu_support import bits, make_layer, run_gpu
+    from support import ConvCase, run_port
+    from tensor_b200 import F32_NCHW, S8_NHWC
+    case = ConvCase("edge_" + name, n=1, h=1, w=1, seed=77, **kw).make()
+    want = run_port(case, 0, want_acc=False)["y"]
+    got = run_gpu(ctx, case, 0, want_acc=False)["y"]
+    assert np.array_equal(bits(got), bits(want))
+    layer = make_layer(ctx, case, 0)
+    try:
+        in_dtype = S8_NHWC if case.s8_input else F32_NCHW
+        out_dtype = S8_NHWC if case.requant else F32_NCHW
+        buf = ctx.malloc(4096)
+        ctx.memset(buf, 0x5A, 4096)
+        before = ctx.launch_count()
+        layer.forward(buf, in_dtype, 0, 7, 9, buf + 2048, out_dtype)
+        ctx.sync()
+        assert ctx.launch_count() == before
+        assert (ctx.to_host(buf, (4096,), np.uint8) == 0x5A).all()
+        ctx.free(buf)
+    finally:
+        layer.close()
