@@ -196,7 +196,7 @@ dense_stem_pool_mma_kernel(const float* __restrict__ x, const __grid_constant__ 
         sprm[1][o] = P.bias[o];
         sprm[2][o] = P.scale_out[o];
     }
-    if (warp == 0) {
+    if (warp == 7) {  // the warp that pools nothing (224 of the 256 threads do): its de-allocation below delays nobody
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(SPM_TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -326,7 +326,7 @@ dense_stem_pool_mma_kernel(const float* __restrict__ x, const __grid_constant__ 
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 0) {
+    if (warp == 7) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(SPM_TMEM_COLS) : "memory");
     }
